@@ -1,0 +1,142 @@
+/*
+ * mace_b200 — C ABI of the B200 (sm_100a) device library for MACE's
+ * quantized-GEMM / convolution path.
+ *
+ * This is the boundary a MACE maintainer binds a "CUDA runtime" to: the C++
+ * delegators and operators registered for that runtime (see
+ * mace_b200/host/) call nothing but these functions.  Plain pointers and
+ * sizes only; no C++ or torch types.
+ *
+ * Conventions
+ *  - Every function returns a MaceStatus::Code integer
+ *    (include/mace/public/mace.h:244-250 of the reference): 0 success,
+ *    1 invalid args, 2 out of resources, 3 unsupported, 4 runtime error.
+ *    Nothing throws.  mb_last_error() gives the message of the last failure.
+ *  - All data pointers passed to compute functions are DEVICE pointers (from
+ *    mb_malloc or any cudaMalloc'd memory of the context's device).  Work is
+ *    enqueued on the context's stream; mb_stream_sync() waits for it and
+ *    reports device-side failures (bounded waits that ran out).
+ *  - A context is used by one host thread at a time, like one MACE engine
+ *    (test/ccunit/mace/libmace/mace_api_mt_test.cc:100-110: engines may run in
+ *    parallel threads, one engine is not re-entrant).  Use one context per
+ *    engine / per GPU.
+ *  - There is no CPU fallback: on a machine without a CUDA device mb_init
+ *    fails with MB_RUNTIME_ERROR.
+ */
+#ifndef MACE_B200_H_
+#define MACE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  MB_SUCCESS = 0,
+  MB_INVALID_ARGS = 1,
+  MB_OUT_OF_RESOURCES = 2,
+  MB_UNSUPPORTED = 3,
+  MB_RUNTIME_ERROR = 4
+};
+
+typedef struct mb_context mb_context;
+
+/* ---- runtime: replaces CpuRuntime / CpuRefAllocator ----------------------
+ * (mace/runtimes/cpu/cpu_runtime.cc:28-109, cpu_ref_allocator.cc:26-40;
+ * buffer mapping of a device runtime: mace/core/runtime/runtime.cc:59-82). */
+int mb_init(int device, mb_context **ctx);
+int mb_destroy(mb_context *ctx);
+const char *mb_last_error(const mb_context *ctx);
+int mb_malloc(mb_context *ctx, size_t bytes, void **dptr);
+int mb_free(mb_context *ctx, void *dptr);
+/* Pinned host memory for staging (Map/UnMap of a device buffer). */
+int mb_host_alloc(mb_context *ctx, size_t bytes, void **hptr);
+int mb_host_free(mb_context *ctx, void *hptr);
+/* Asynchronous copies on the context's stream. */
+int mb_memcpy_h2d(mb_context *ctx, void *dst_dev, const void *src_host, size_t bytes);
+int mb_memcpy_d2h(mb_context *ctx, void *dst_host, const void *src_dev, size_t bytes);
+int mb_memset(mb_context *ctx, void *dst_dev, int value, size_t bytes);
+int mb_stream_sync(mb_context *ctx);
+/* The cudaStream_t of the context, as an opaque pointer (for event timing). */
+void *mb_stream(mb_context *ctx);
+/* Number of kernels launched through this context so far; the second form
+ * counts only tcgen05 tensor-core GEMM launches. */
+uint64_t mb_launch_count(const mb_context *ctx);
+uint64_t mb_launch_count_tensor_core(const mb_context *ctx);
+/* Options for A/B tests: "tensor_cores" (1 default; 0 forces the CUDA-core
+ * GEMM), "mn_major" (1 default; 0 transposes MN-major operands to K-major
+ * in scratch instead of describing them to the tensor core directly). */
+int mb_set_option(mb_context *ctx, const char *name, int value);
+
+/* ---- uint8 GEMM: replaces the gemmlowp calls of MatMulOp<RT_CPU,uint8_t>
+ * (mace/ops/matmul.cc:228-309 uint8 output, :311-394 int32 output) and of
+ * Conv2dOp<RT_CPU,uint8_t> (mace/ops/conv_2d.cc:301-315).
+ *
+ * Per batch entry: acc[m,n] = sum_k (A[m,k]-zp_a)(B[k,n]-zp_b) (+ bias),
+ * C = clamp(RoundingDivideByPOT(SRDHM(acc, multiplier), right_shift) + zp_c).
+ * A is M x K, row-major unless a_col_major; B is K x N; C is M x N.
+ * out_is_int32: C is int32 and receives acc (+bias) unrequantized.
+ * bias may be NULL; bias_per_row selects bias[m] (Conv2D's per-output-channel
+ * bias on gemmlowp result rows) or bias[n].  multiplier/right_shift come from
+ * GetOutputMultiplierAndShift (mace/core/quantize.h:116-126). */
+int mb_gemm_u8(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+               const int32_t *bias, void *C, int out_is_int32, int64_t batch,
+               int64_t M, int64_t N, int64_t K, int a_col_major,
+               int b_col_major, int c_col_major, int a_batched, int b_batched,
+               int32_t zp_a, int32_t zp_b, int32_t multiplier,
+               int32_t right_shift, int32_t zp_c, int bias_per_row);
+
+/* ---- uint8 GEMV: replaces arm::q8::Gemv / ref::q8::Gemv
+ * (mace/ops/arm/q8/gemv.cc:36-171, mace/ops/ref/q8/gemv.cc:80-162), the
+ * delegator behind FullyConnectedOp<RT_CPU,uint8_t>
+ * (mace/ops/fully_connected.cc:141-179).
+ * out[b,h] = Saturate<u8>(roundf(acc * multiplier [+ zp_out])) with the
+ * product and the sum rounded separately; add_zp_out = 0 gives the REF
+ * delegator's formula, which omits zp_out.  lhs is [rows x K] row-major. */
+int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rhs,
+               const int32_t *bias, void *out, int out_is_int32, int64_t batch,
+               int64_t rows, int64_t K, int lhs_batched, int rhs_batched,
+               int32_t zp_lhs, int32_t zp_rhs, float multiplier,
+               int32_t zp_out, int add_zp_out);
+
+/* ---- uint8 Conv2D, NHWC x OHWI -> NHWC: replaces Conv2dOp<RT_CPU,uint8_t>::
+ * Run including its Im2col (mace/ops/conv_2d.cc:201-412).  pad_top/pad_left
+ * are the leading paddings (total padding >> 1); taps outside the image
+ * contribute zero, which equals padding with the input zero point. */
+int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in,
+                      const uint8_t *filter_ohwi, const int32_t *bias,
+                      uint8_t *out, int64_t N, int64_t H, int64_t W, int64_t C,
+                      int64_t O, int64_t KH, int64_t KW, int stride_h,
+                      int stride_w, int pad_top, int pad_left, int64_t Ho,
+                      int64_t Wo, int32_t zp_in, int32_t zp_f,
+                      int32_t multiplier, int32_t right_shift, int32_t zp_out);
+
+/* ---- uint8 DepthwiseConv2d, NHWC x HWIM -> NHWC: replaces
+ * DepthwiseConv2dOp<RT_CPU,uint8_t>::Run (mace/ops/depthwise_conv2d.cc:
+ * 152-250, fixed-point requantization) and, with use_float_multiplier != 0,
+ * its dilated fallback DepthwiseConv2dGeneral (:252-320,
+ * int(round(acc * multiplier_f)) + zp_out). */
+int mb_dwconv_u8_nhwc(mb_context *ctx, const uint8_t *in,
+                      const uint8_t *filter_hwim, const int32_t *bias,
+                      uint8_t *out, int64_t N, int64_t H, int64_t W, int64_t C,
+                      int64_t channel_multiplier, int64_t KH, int64_t KW,
+                      int stride_h, int stride_w, int dil_h, int dil_w,
+                      int pad_top, int pad_left, int64_t Ho, int64_t Wo,
+                      int32_t zp_in, int32_t zp_f, int32_t multiplier,
+                      int32_t right_shift, int32_t zp_out,
+                      int use_float_multiplier, float multiplier_f);
+
+/* ---- uint8 average pooling, NHWC: replaces PoolingOp<RT_CPU,uint8_t> AVG
+ * (mace/ops/pooling.cc:638-871): (sum + n/2) / n over the in-bounds window. */
+int mb_avgpool_u8_nhwc(mb_context *ctx, const uint8_t *in, uint8_t *out,
+                       int64_t N, int64_t H, int64_t W, int64_t C, int64_t KH,
+                       int64_t KW, int stride_h, int stride_w, int pad_top,
+                       int pad_left, int64_t Ho, int64_t Wo);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MACE_B200_H_ */

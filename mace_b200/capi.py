@@ -1,0 +1,203 @@
+"""ctypes binding of ``libmace_b200.so`` (the C ABI of include/mace_b200.h)."""
+import ctypes as C
+import os
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "libmace_b200.so")
+
+STATUS = {0: "MACE_SUCCESS", 1: "MACE_INVALID_ARGS", 2: "MACE_OUT_OF_RESOURCES",
+          3: "MACE_UNSUPPORTED", 4: "MACE_RUNTIME_ERROR"}
+
+
+class MaceB200Error(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("%s: %s" % (STATUS.get(code, code), msg))
+        self.code = code
+
+
+def lib_path():
+    return _LIB
+
+
+def build(verbose=False):
+    """Compile the device library for sm_100a with nvcc (in-tree)."""
+    out = None if verbose else subprocess.DEVNULL
+    subprocess.check_call(["make", "-C", os.path.join(_HERE, "csrc"), "-j8"], stdout=out)
+    return _LIB
+
+
+_vp = C.c_void_p
+_i64 = C.c_int64
+_i32 = C.c_int32
+_int = C.c_int
+_f32 = C.c_float
+_sz = C.c_size_t
+
+# name -> (restype, argtypes); every symbol that include/mace_b200.h declares
+PROTOTYPES = {
+    "mb_init": (_int, [_int, C.POINTER(_vp)]),
+    "mb_destroy": (_int, [_vp]),
+    "mb_last_error": (C.c_char_p, [_vp]),
+    "mb_malloc": (_int, [_vp, _sz, C.POINTER(_vp)]),
+    "mb_free": (_int, [_vp, _vp]),
+    "mb_host_alloc": (_int, [_vp, _sz, C.POINTER(_vp)]),
+    "mb_host_free": (_int, [_vp, _vp]),
+    "mb_memcpy_h2d": (_int, [_vp, _vp, _vp, _sz]),
+    "mb_memcpy_d2h": (_int, [_vp, _vp, _vp, _sz]),
+    "mb_memset": (_int, [_vp, _vp, _int, _sz]),
+    "mb_stream_sync": (_int, [_vp]),
+    "mb_stream": (_vp, [_vp]),
+    "mb_launch_count": (C.c_uint64, [_vp]),
+    "mb_launch_count_tensor_core": (C.c_uint64, [_vp]),
+    "mb_set_option": (_int, [_vp, C.c_char_p, _int]),
+    "mb_gemm_u8": (_int, [_vp] * 5 + [_int] + [_i64] * 4 + [_int] * 5 + [_i32] * 5 + [_int]),
+    "mb_gemv_u8": (_int, [_vp] * 5 + [_int] + [_i64] * 3 + [_int] * 2 + [_i32] * 2 +
+                   [_f32, _i32, _int]),
+    "mb_conv2d_u8_nhwc": (_int, [_vp] * 5 + [_i64] * 7 + [_int] * 4 + [_i64] * 2 + [_i32] * 5),
+    "mb_dwconv_u8_nhwc": (_int, [_vp] * 5 + [_i64] * 7 + [_int] * 6 + [_i64] * 2 + [_i32] * 5 +
+                          [_int, _f32]),
+    "mb_avgpool_u8_nhwc": (_int, [_vp] * 3 + [_i64] * 6 + [_int] * 4 + [_i64] * 2),
+}
+
+_lib = None
+
+
+def lib():
+    """Load the library; raises if it has not been built (no fallback)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB):
+            raise ImportError(
+                "libmace_b200.so is missing: run `python -c 'import __graft_entry__ as g; "
+                "g.build()'` (or make -C mace_b200/csrc). There is no CPU fallback.")
+        _lib = C.CDLL(_LIB)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(_lib, name)
+            fn.restype = res
+            fn.argtypes = args
+    return _lib
+
+
+class DeviceBuffer:
+    """A device allocation owned by a Context."""
+
+    def __init__(self, ctx, nbytes):
+        self.ctx = ctx
+        self.nbytes = int(nbytes)
+        p = _vp()
+        ctx._check(lib().mb_malloc(ctx.h, max(self.nbytes, 1), C.byref(p)))
+        self.ptr = p.value
+
+    def free(self):
+        if self.ptr:
+            lib().mb_free(self.ctx.h, self.ptr)
+            self.ptr = None
+
+
+class Context:
+    """One device context (stream + scratch arena) on a GPU."""
+
+    def __init__(self, device=0):
+        self.h = _vp()
+        st = lib().mb_init(int(device), C.byref(self.h))
+        if st != 0:
+            raise MaceB200Error(st, "mb_init failed (no sm_100a CUDA device?)")
+        self._bufs = []
+
+    def _check(self, st):
+        if st != 0:
+            raise MaceB200Error(st, lib().mb_last_error(self.h).decode())
+
+    def close(self):
+        if self.h:
+            for b in self._bufs:
+                b.free()
+            lib().mb_destroy(self.h)
+            self.h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    # -- memory ---------------------------------------------------------------
+    def alloc(self, nbytes):
+        b = DeviceBuffer(self, nbytes)
+        self._bufs.append(b)
+        return b
+
+    def upload(self, arr):
+        """numpy array -> new device buffer (synchronous)."""
+        import numpy as np
+        arr = np.ascontiguousarray(arr)
+        b = self.alloc(arr.nbytes)
+        if arr.nbytes:
+            self._check(lib().mb_memcpy_h2d(self.h, b.ptr, arr.ctypes.data, arr.nbytes))
+            self.sync()
+        return b
+
+    def download(self, buf, shape, dtype):
+        import numpy as np
+        out = np.empty(shape, dtype)
+        if out.nbytes:
+            self._check(lib().mb_memcpy_d2h(self.h, out.ctypes.data, buf.ptr, out.nbytes))
+        self.sync()
+        return out
+
+    def sync(self):
+        self._check(lib().mb_stream_sync(self.h))
+
+    def set_option(self, name, value):
+        self._check(lib().mb_set_option(self.h, name.encode(), int(value)))
+
+    @property
+    def launches(self):
+        return int(lib().mb_launch_count(self.h))
+
+    @property
+    def launches_tensor_core(self):
+        return int(lib().mb_launch_count_tensor_core(self.h))
+
+    @property
+    def stream(self):
+        return lib().mb_stream(self.h)
+
+    # -- ops (device pointers in, status checked) --------------------------------
+    def gemm_u8(self, A, B, bias, Cout, batch, M, N, K, zp_a, zp_b, mult=1 << 30, shift=0,
+                zp_c=0, a_col_major=False, b_col_major=False, c_col_major=False,
+                a_batched=True, b_batched=True, out_int32=False, bias_per_row=False):
+        self._check(lib().mb_gemm_u8(
+            self.h, A.ptr, B.ptr, bias.ptr if bias is not None else None, Cout.ptr,
+            int(out_int32), batch, M, N, K, int(a_col_major), int(b_col_major),
+            int(c_col_major), int(a_batched), int(b_batched), zp_a, zp_b, mult, shift, zp_c,
+            int(bias_per_row)))
+
+    def gemv_u8(self, lhs, rhs, bias, out, batch, rows, K, zp_l, zp_r, multiplier=0.0,
+                zp_out=0, add_zp_out=True, lhs_batched=False, rhs_batched=True,
+                out_int32=False):
+        self._check(lib().mb_gemv_u8(
+            self.h, lhs.ptr, rhs.ptr, bias.ptr if bias is not None else None, out.ptr,
+            int(out_int32), batch, rows, K, int(lhs_batched), int(rhs_batched), zp_l, zp_r,
+            float(multiplier), zp_out, int(add_zp_out)))
+
+    def conv2d_u8(self, x, f, bias, out, N, H, W, Cc, O, KH, KW, strides, pad_tl, out_hw,
+                  zp_in, zp_f, mult, shift, zp_out):
+        self._check(lib().mb_conv2d_u8_nhwc(
+            self.h, x.ptr, f.ptr, bias.ptr if bias is not None else None, out.ptr, N, H, W, Cc,
+            O, KH, KW, strides[0], strides[1], pad_tl[0], pad_tl[1], out_hw[0], out_hw[1],
+            zp_in, zp_f, mult, shift, zp_out))
+
+    def dwconv_u8(self, x, f, bias, out, N, H, W, Cc, Mc, KH, KW, strides, dil, pad_tl, out_hw,
+                  zp_in, zp_f, mult=1 << 30, shift=0, zp_out=0, float_multiplier=None):
+        self._check(lib().mb_dwconv_u8_nhwc(
+            self.h, x.ptr, f.ptr, bias.ptr if bias is not None else None, out.ptr, N, H, W, Cc,
+            Mc, KH, KW, strides[0], strides[1], dil[0], dil[1], pad_tl[0], pad_tl[1],
+            out_hw[0], out_hw[1], zp_in, zp_f, mult, shift, zp_out,
+            int(float_multiplier is not None), float(float_multiplier or 0.0)))
+
+    def avgpool_u8(self, x, out, N, H, W, Cc, kernel, strides, pad_tl, out_hw):
+        self._check(lib().mb_avgpool_u8_nhwc(
+            self.h, x.ptr, out.ptr, N, H, W, Cc, kernel[0], kernel[1], strides[0], strides[1],
+            pad_tl[0], pad_tl[1], out_hw[0], out_hw[1]))

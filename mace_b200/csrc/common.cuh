@@ -1,0 +1,94 @@
+// Shared declarations of the device library: status codes, the context that
+// every C-ABI call receives, the requantization arithmetic used by all uint8
+// epilogues, and small launch helpers.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/mace_b200.h"
+
+// Device-side status word values written by kernels whose bounded waits run
+// out; the host turns any non-zero value into MB_RUNTIME_ERROR.
+enum : int {
+  MB_DEV_OK = 0,
+  MB_DEV_TIMEOUT_PRODUCER = 1,
+  MB_DEV_TIMEOUT_MMA = 2,
+  MB_DEV_TIMEOUT_EPILOGUE = 3,
+};
+
+struct mb_context {
+  int device = 0;
+  int num_sms = 0;
+  int max_smem_optin = 0;
+  cudaStream_t stream = nullptr;
+  // Scratch arena, the analogue of the runtime's RENT_SCRATCH buffers
+  // (mace/core/runtime/runtime.cc:153-182): one growable device block that a
+  // call carves from the start; contents do not survive the call.
+  void *scratch = nullptr;
+  size_t scratch_bytes = 0;
+  int *dev_status = nullptr;   // device status word (bounded-wait failures)
+  int *host_status = nullptr;  // pinned mirror read at sync
+  void *encode_tiled = nullptr;  // cuTensorMapEncodeTiled, resolved at init
+  int use_tensor_cores = 1;      // cleared by mb_set_option for A/B tests
+  int use_mn_major = 1;
+  uint64_t launches = 0;         // kernels launched through this context
+  uint64_t launches_tc = 0;      // of which tcgen05 GEMM launches
+  uint64_t func_attr_mask = 0;   // kernels whose shared-memory limit was raised
+  char last_error[512] = {0};
+};
+
+int mb_fail(mb_context *ctx, int code, const char *fmt, ...);
+int mb_check_cuda(mb_context *ctx, cudaError_t e, const char *what);
+// Returns a device pointer to at least `bytes` of scratch (256-byte aligned),
+// growing the arena if needed.  offset allows several carve-outs per call.
+int mb_scratch(mb_context *ctx, size_t bytes, void **ptr);
+
+#define MB_RETURN_IF_ERROR(expr)        \
+  do {                                  \
+    int _st = (expr);                   \
+    if (_st != MB_SUCCESS) return _st;  \
+  } while (0)
+
+#define MB_CUDA(ctx, expr) MB_RETURN_IF_ERROR(mb_check_cuda((ctx), (expr), #expr))
+
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---- requantization arithmetic ---------------------------------------------
+// gemmlowp's output stage as MACE wires it (mace/ops/common/gemmlowp_util.h:
+// 37-74): SaturatingRoundingDoublingHighMul, RoundingDivideByPOT, + offset,
+// clamp to [0, 255].
+
+__device__ __forceinline__ int32_t mb_srdhm(int32_t a, int32_t b) {
+  // (a*b + nudge) / 2^31 with truncating division; nudge = 2^30 when a*b >= 0,
+  // 1 - 2^30 otherwise.  b is a positive multiplier in [2^30, 2^31), so the
+  // a == b == INT32_MIN saturation case cannot occur.
+  const int64_t ab = static_cast<int64_t>(a) * static_cast<int64_t>(b);
+  const int64_t t = ab + (ab >= 0 ? (1ll << 30) : (1ll - (1ll << 30)));
+  return static_cast<int32_t>(t / (1ll << 31));
+}
+
+__device__ __forceinline__ int32_t mb_rdivpot(int32_t x, int shift) {
+  const int32_t mask = static_cast<int32_t>((1u << shift) - 1u);
+  const int32_t remainder = x & mask;
+  const int32_t threshold = (mask >> 1) + (x < 0 ? 1 : 0);
+  return (x >> shift) + (remainder > threshold ? 1 : 0);
+}
+
+__device__ __forceinline__ uint32_t mb_requant(int32_t acc, int32_t mult,
+                                               int shift, int32_t zp_out) {
+  int32_t v = mb_rdivpot(mb_srdhm(acc, mult), shift) + zp_out;
+  return static_cast<uint32_t>(min(255, max(0, v)));
+}
+
+// Saturate<uint8_t>(roundf(v)) of mace/core/quantize.h:69-83.
+__device__ __forceinline__ uint32_t mb_saturate_round_u8(float v) {
+  const int r = static_cast<int>(roundf(v));
+  return static_cast<uint32_t>(min(255, max(0, r)));
+}

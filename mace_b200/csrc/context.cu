@@ -1,0 +1,198 @@
+// Runtime part of the C ABI: context creation, device and pinned-host memory,
+// stream copies and synchronisation.  It plays the role that CpuRuntime and
+// its allocator play for the CPU path (mace/runtimes/cpu/cpu_runtime.cc:28-109)
+// for a CUDA device.
+#include <cstdarg>
+
+#include "common.cuh"
+
+int mb_fail(mb_context *ctx, int code, const char *fmt, ...) {
+  if (ctx != nullptr) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(ctx->last_error, sizeof(ctx->last_error), fmt, ap);
+    va_end(ap);
+  }
+  return code;
+}
+
+int mb_check_cuda(mb_context *ctx, cudaError_t e, const char *what) {
+  if (e == cudaSuccess) return MB_SUCCESS;
+  const int code =
+      (e == cudaErrorMemoryAllocation) ? MB_OUT_OF_RESOURCES : MB_RUNTIME_ERROR;
+  return mb_fail(ctx, code, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int mb_scratch(mb_context *ctx, size_t bytes, void **ptr) {
+  if (bytes > ctx->scratch_bytes) {
+    // Growing invalidates earlier carve-outs, so drain the stream first.
+    MB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->scratch != nullptr) {
+      MB_CUDA(ctx, cudaFree(ctx->scratch));
+      ctx->scratch = nullptr;
+      ctx->scratch_bytes = 0;
+    }
+    const size_t want = align_up(bytes + bytes / 4, 1 << 20);
+    MB_CUDA(ctx, cudaMalloc(&ctx->scratch, want));
+    ctx->scratch_bytes = want;
+  }
+  *ptr = ctx->scratch;
+  return MB_SUCCESS;
+}
+
+extern "C" {
+
+int mb_init(int device, mb_context **out) {
+  if (out == nullptr) return MB_INVALID_ARGS;
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 ||
+      device >= count) {
+    return MB_RUNTIME_ERROR;  // no CUDA device: there is no CPU fallback
+  }
+  mb_context *ctx = new mb_context();
+  ctx->device = device;
+  cudaDeviceProp prop;
+  if (cudaSetDevice(device) != cudaSuccess ||
+      cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+    delete ctx;
+    return MB_RUNTIME_ERROR;
+  }
+  if (prop.major != 10) {
+    // The kernels are built for sm_100a only.
+    delete ctx;
+    return MB_UNSUPPORTED;
+  }
+  ctx->num_sms = prop.multiProcessorCount;
+  ctx->max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+  if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) !=
+          cudaSuccess ||
+      cudaMalloc(&ctx->dev_status, sizeof(int)) != cudaSuccess ||
+      cudaMemset(ctx->dev_status, 0, sizeof(int)) != cudaSuccess ||
+      cudaMallocHost(&ctx->host_status, sizeof(int)) != cudaSuccess) {
+    delete ctx;
+    return MB_RUNTIME_ERROR;
+  }
+  *ctx->host_status = 0;
+  // The tensor-map encoder lives in the driver; resolve it at run time so the
+  // library has no link-time dependency on libcuda.
+  cudaDriverEntryPointQueryResult qres;
+  void *fn = nullptr;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault,
+                              &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess) {
+    fn = nullptr;
+  }
+  ctx->encode_tiled = fn;
+  *out = ctx;
+  return MB_SUCCESS;
+}
+
+int mb_destroy(mb_context *ctx) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  cudaSetDevice(ctx->device);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->host_status) cudaFreeHost(ctx->host_status);
+  if (ctx->stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return MB_SUCCESS;
+}
+
+const char *mb_last_error(const mb_context *ctx) {
+  return ctx ? ctx->last_error : "null context";
+}
+
+int mb_malloc(mb_context *ctx, size_t bytes, void **dptr) {
+  if (ctx == nullptr || dptr == nullptr) return MB_INVALID_ARGS;
+  *dptr = nullptr;
+  if (bytes == 0) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  MB_CUDA(ctx, cudaMalloc(dptr, bytes));
+  return MB_SUCCESS;
+}
+
+int mb_free(mb_context *ctx, void *dptr) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (dptr == nullptr) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  MB_CUDA(ctx, cudaFree(dptr));
+  return MB_SUCCESS;
+}
+
+int mb_host_alloc(mb_context *ctx, size_t bytes, void **hptr) {
+  if (ctx == nullptr || hptr == nullptr) return MB_INVALID_ARGS;
+  *hptr = nullptr;
+  if (bytes == 0) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  MB_CUDA(ctx, cudaMallocHost(hptr, bytes));
+  return MB_SUCCESS;
+}
+
+int mb_host_free(mb_context *ctx, void *hptr) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (hptr == nullptr) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaFreeHost(hptr));
+  return MB_SUCCESS;
+}
+
+int mb_memcpy_h2d(mb_context *ctx, void *dst, const void *src, size_t bytes) {
+  if (ctx == nullptr || (bytes && (!dst || !src))) return MB_INVALID_ARGS;
+  if (bytes == 0) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice,
+                               ctx->stream));
+  return MB_SUCCESS;
+}
+
+int mb_memcpy_d2h(mb_context *ctx, void *dst, const void *src, size_t bytes) {
+  if (ctx == nullptr || (bytes && (!dst || !src))) return MB_INVALID_ARGS;
+  if (bytes == 0) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost,
+                               ctx->stream));
+  return MB_SUCCESS;
+}
+
+int mb_memset(mb_context *ctx, void *dst, int value, size_t bytes) {
+  if (ctx == nullptr || (bytes && !dst)) return MB_INVALID_ARGS;
+  if (bytes == 0) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaMemsetAsync(dst, value, bytes, ctx->stream));
+  return MB_SUCCESS;
+}
+
+int mb_stream_sync(mb_context *ctx) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  MB_CUDA(ctx, cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(int),
+                               cudaMemcpyDeviceToHost, ctx->stream));
+  MB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (*ctx->host_status != 0) {
+    const int code = *ctx->host_status;
+    *ctx->host_status = 0;
+    cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream);
+    return mb_fail(ctx, MB_RUNTIME_ERROR,
+                   "a kernel gave up a bounded wait (device status %d)", code);
+  }
+  return MB_SUCCESS;
+}
+
+void *mb_stream(mb_context *ctx) { return ctx ? ctx->stream : nullptr; }
+
+uint64_t mb_launch_count(const mb_context *ctx) { return ctx ? ctx->launches : 0; }
+
+uint64_t mb_launch_count_tensor_core(const mb_context *ctx) {
+  return ctx ? ctx->launches_tc : 0;
+}
+
+int mb_set_option(mb_context *ctx, const char *name, int value) {
+  if (ctx == nullptr || name == nullptr) return MB_INVALID_ARGS;
+  if (strcmp(name, "tensor_cores") == 0) {
+    ctx->use_tensor_cores = value;
+  } else if (strcmp(name, "mn_major") == 0) {
+    ctx->use_mn_major = value;
+  } else {
+    return mb_fail(ctx, MB_INVALID_ARGS, "unknown option %s", name);
+  }
+  return MB_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,217 @@
+// uint8 Conv2D, NHWC input, OHWI filter, NHWC output.
+//
+// Reference behaviour: Conv2dOp<RT_CPU,uint8_t>::Run (mace/ops/conv_2d.cc:
+// 201-318): [im2col with the input zero point as pad value, :322-412] then a
+// GEMM filter[O x depth] * patches[depth x pixels] with a per-output-channel
+// int32 bias and the fixed-point output pipeline.  Padding with the zero point
+// contributes (zp - zp) * w = 0, i.e. exactly the sum over in-bounds taps.
+//
+// Three routes:
+//   1x1 stride 1      -> the NHWC tensor already is the [pixels x C] K-major
+//                        GEMM operand; no copy (conv_2d.cc:279-281)
+//   small depth * O   -> direct kernel, one thread per output pixel, the whole
+//                        filter in shared memory (MobileNet's 3x3x3 stem)
+//   everything else   -> patch gather into scratch (rows padded to 16 bytes)
+//                        + tensor-core GEMM
+#include "common.cuh"
+
+int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, const int32_t *bias,
+                        void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
+                        int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
+                        int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
+                        int bias_per_row);
+
+namespace {
+
+struct ConvParams {
+  const uint8_t *in, *filter;
+  const int32_t *bias;
+  uint8_t *out;
+  int N, H, W, C, O, KH, KW, stride_h, stride_w, pad_top, pad_left, Ho, Wo;
+  int depth, depth_padded;
+  int32_t zp_in, zp_f, mult, shift, zp_out;
+};
+
+// Direct convolution: thread = one output pixel, OT output channels at a time.
+// Filter (zero point removed, int16) lives in shared memory as [depth][O].
+template <int OT>
+__global__ void __launch_bounds__(128) conv_u8_direct_kernel(const ConvParams p) {
+  extern __shared__ int16_t fsm[];  // [depth][O]
+  for (int i = threadIdx.x; i < p.depth * p.O; i += blockDim.x) {
+    const int d = i / p.O, o = i % p.O;
+    fsm[i] = static_cast<int16_t>(static_cast<int32_t>(p.filter[o * p.depth + d]) - p.zp_f);
+  }
+  __syncthreads();
+  const int64_t pix = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t npix = static_cast<int64_t>(p.N) * p.Ho * p.Wo;
+  if (pix >= npix) return;
+  const int wo = static_cast<int>(pix % p.Wo);
+  const int ho = static_cast<int>((pix / p.Wo) % p.Ho);
+  const int n = static_cast<int>(pix / (static_cast<int64_t>(p.Wo) * p.Ho));
+  const int hi0 = ho * p.stride_h - p.pad_top, wi0 = wo * p.stride_w - p.pad_left;
+  const uint8_t *in_n = p.in + static_cast<int64_t>(n) * p.H * p.W * p.C;
+  uint8_t *outp = p.out + pix * p.O;
+  for (int o0 = 0; o0 < p.O; o0 += OT) {
+    int32_t acc[OT];
+#pragma unroll
+    for (int j = 0; j < OT; ++j)
+      acc[j] = (p.bias != nullptr && o0 + j < p.O) ? p.bias[o0 + j] : 0;
+    for (int kh = 0; kh < p.KH; ++kh) {
+      const int hi = hi0 + kh;
+      if (hi < 0 || hi >= p.H) continue;
+      for (int kw = 0; kw < p.KW; ++kw) {
+        const int wi = wi0 + kw;
+        if (wi < 0 || wi >= p.W) continue;
+        const uint8_t *ip = in_n + (static_cast<int64_t>(hi) * p.W + wi) * p.C;
+        const int16_t *fp = fsm + ((kh * p.KW + kw) * p.C) * p.O + o0;
+        for (int c = 0; c < p.C; ++c) {
+          const int32_t iv = static_cast<int32_t>(__ldg(ip + c)) - p.zp_in;
+#pragma unroll
+          for (int j = 0; j < OT; ++j)
+            if (o0 + j < p.O) acc[j] += iv * fp[c * p.O + j];
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < OT; ++j)
+      if (o0 + j < p.O)
+        outp[o0 + j] = static_cast<uint8_t>(mb_requant(acc[j], p.mult, p.shift, p.zp_out));
+  }
+}
+
+// Patch gather: row `pix` of the [pixels x depth_padded] matrix receives the
+// KH*KW*C bytes under the filter window.  Out-of-image taps and the alignment
+// tail beyond `depth` hold zp_in, so that they contribute
+// (zp_in - zp_in) * (w - zp_f) = 0 whatever the filter side holds.
+__global__ void __launch_bounds__(256) im2col_u8_kernel(const ConvParams p, uint8_t *col) {
+  const int64_t npix = static_cast<int64_t>(p.N) * p.Ho * p.Wo;
+  const int taps = p.KH * p.KW;
+  // one thread per (pixel, tap): copies C bytes
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (tid >= npix * (taps + 1)) return;
+  const int64_t pix = tid / (taps + 1);
+  const int tap = static_cast<int>(tid % (taps + 1));
+  uint8_t *dst = col + pix * p.depth_padded;
+  if (tap == taps) {  // alignment tail
+    for (int i = p.depth; i < p.depth_padded; ++i) dst[i] = static_cast<uint8_t>(p.zp_in);
+    return;
+  }
+  const int kh = tap / p.KW, kw = tap % p.KW;
+  const int wo = static_cast<int>(pix % p.Wo);
+  const int ho = static_cast<int>((pix / p.Wo) % p.Ho);
+  const int n = static_cast<int>(pix / (static_cast<int64_t>(p.Wo) * p.Ho));
+  const int hi = ho * p.stride_h - p.pad_top + kh, wi = wo * p.stride_w - p.pad_left + kw;
+  dst += tap * p.C;
+  if (hi < 0 || hi >= p.H || wi < 0 || wi >= p.W) {
+    const uint8_t padv = static_cast<uint8_t>(p.zp_in);
+    for (int c = 0; c < p.C; ++c) dst[c] = padv;
+  } else {
+    const uint8_t *src = p.in + ((static_cast<int64_t>(n) * p.H + hi) * p.W + wi) * p.C;
+    if ((p.C & 15) == 0 && (p.depth_padded & 15) == 0 &&
+        ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0) {
+      for (int c = 0; c < p.C; c += 16)
+        *reinterpret_cast<uint4 *>(dst + c) = __ldg(reinterpret_cast<const uint4 *>(src + c));
+    } else {
+      for (int c = 0; c < p.C; ++c) dst[c] = src[c];
+    }
+  }
+}
+
+// Copy the [O x depth] filter into [O x depth_padded] with a zero tail.
+__global__ void __launch_bounds__(256) pad_rows_u8_kernel(const uint8_t *__restrict__ src,
+                                                          uint8_t *__restrict__ dst, int64_t rows,
+                                                          int len, int len_padded) {
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (tid >= rows * len_padded) return;
+  const int64_t r = tid / len_padded;
+  const int i = static_cast<int>(tid % len_padded);
+  dst[tid] = i < len ? src[r * len + i] : 0;
+}
+
+}  // namespace
+
+extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8_t *filter,
+                                 const int32_t *bias, uint8_t *out, int64_t N, int64_t H,
+                                 int64_t W, int64_t C, int64_t O, int64_t KH, int64_t KW,
+                                 int stride_h, int stride_w, int pad_top, int pad_left,
+                                 int64_t Ho, int64_t Wo, int32_t zp_in, int32_t zp_f,
+                                 int32_t multiplier, int32_t right_shift, int32_t zp_out) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (N < 0 || H < 1 || W < 1 || C < 1 || O < 1 || KH < 1 || KW < 1 || Ho < 0 || Wo < 0 ||
+      stride_h < 1 || stride_w < 1 || pad_top < 0 || pad_left < 0)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_conv2d_u8_nhwc: bad shape argument");
+  if (N == 0 || Ho == 0 || Wo == 0) return MB_SUCCESS;
+  if (in == nullptr || filter == nullptr || out == nullptr)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_conv2d_u8_nhwc: null operand");
+  if (multiplier <= 0 || right_shift < 0 || right_shift > 31)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_conv2d_u8_nhwc: bad multiplier/shift");
+  if (zp_in < 0 || zp_in > 255)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_conv2d_u8_nhwc: input zero point outside uint8");
+  const int64_t depth = C * KH * KW;
+  const int64_t pixels = N * Ho * Wo;
+  if (depth > (1 << 24) || pixels >= (1ll << 31) || H > (1 << 20) || W > (1 << 20))
+    return mb_fail(ctx, MB_UNSUPPORTED, "mb_conv2d_u8_nhwc: tensor too large");
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+
+  if (KH == 1 && KW == 1 && stride_h == 1 && stride_w == 1 && pad_top == 0 && pad_left == 0 &&
+      Ho == H && Wo == W) {
+    // out[pixel][o] = sum_c in[pixel][c] * filter[o][c]: A = input (K-major),
+    // B^T = filter (K-major), C row-major = NHWC, bias per column (= channel).
+    return mb_gemm_u8_rowmajor(ctx, in, filter, bias, out, 0, 1, pixels, O, depth, false, false,
+                               0, 0, zp_in, zp_f, multiplier, right_shift, zp_out, 0);
+  }
+
+  ConvParams p;
+  p.in = in; p.filter = filter; p.bias = bias; p.out = out;
+  p.N = static_cast<int>(N); p.H = static_cast<int>(H); p.W = static_cast<int>(W);
+  p.C = static_cast<int>(C); p.O = static_cast<int>(O);
+  p.KH = static_cast<int>(KH); p.KW = static_cast<int>(KW);
+  p.stride_h = stride_h; p.stride_w = stride_w; p.pad_top = pad_top; p.pad_left = pad_left;
+  p.Ho = static_cast<int>(Ho); p.Wo = static_cast<int>(Wo);
+  p.depth = static_cast<int>(depth);
+  p.depth_padded = static_cast<int>(align_up(static_cast<size_t>(depth), 16));
+  p.zp_in = zp_in; p.zp_f = zp_f; p.mult = multiplier; p.shift = right_shift; p.zp_out = zp_out;
+
+  const size_t direct_smem = static_cast<size_t>(depth) * O * sizeof(int16_t);
+  if (direct_smem <= 32 * 1024 && depth <= 256) {
+    const unsigned blocks = static_cast<unsigned>(ceil_div64(pixels, 128));
+    if (O % 32 == 0 || O > 16) conv_u8_direct_kernel<32><<<blocks, 128, direct_smem, ctx->stream>>>(p);
+    else conv_u8_direct_kernel<8><<<blocks, 128, direct_smem, ctx->stream>>>(p);
+    MB_CUDA(ctx, cudaGetLastError());
+    ctx->launches++;
+    return MB_SUCCESS;
+  }
+
+  // Patch gather + GEMM.  The scratch block is carved here and by the GEMM;
+  // the GEMM carves from the start of the arena, so the patch matrix and the
+  // padded filter live in memory obtained separately for the duration of the
+  // call.
+  uint8_t *col = nullptr, *fpad = nullptr;
+  const size_t col_bytes = static_cast<size_t>(pixels) * p.depth_padded;
+  const bool pad_filter = p.depth_padded != p.depth;
+  const size_t f_bytes = pad_filter ? static_cast<size_t>(O) * p.depth_padded : 0;
+  MB_CUDA(ctx, cudaMallocAsync(reinterpret_cast<void **>(&col), col_bytes + f_bytes + 256, ctx->stream));
+  fpad = col + align_up(col_bytes, 256);
+  {
+    const int64_t threads = pixels * (KH * KW + 1);
+    im2col_u8_kernel<<<static_cast<unsigned>(ceil_div64(threads, 256)), 256, 0, ctx->stream>>>(p, col);
+    ctx->launches++;
+  }
+  const uint8_t *f_use = filter;
+  if (pad_filter) {
+    const int64_t threads = O * p.depth_padded;
+    pad_rows_u8_kernel<<<static_cast<unsigned>(ceil_div64(threads, 256)), 256, 0, ctx->stream>>>(
+        filter, fpad, O, p.depth, p.depth_padded);
+    ctx->launches++;
+    f_use = fpad;
+  }
+  int st = mb_check_cuda(ctx, cudaGetLastError(), "im2col launch");
+  if (st == MB_SUCCESS) {
+    // The GEMM runs over depth_padded; the tail columns hold zp_in on the
+    // patch side and therefore add nothing to the accumulator.
+    st = mb_gemm_u8_rowmajor(ctx, col, f_use, bias, out, 0, 1, pixels, O, p.depth_padded, false,
+                             false, 0, 0, zp_in, zp_f, multiplier, right_shift, zp_out, 0);
+  }
+  cudaFreeAsync(col, ctx->stream);
+  return st;
+}

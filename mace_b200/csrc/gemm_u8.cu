@@ -1,0 +1,334 @@
+// mb_gemm_u8: argument checks, operand preparation (row/column byte sums for
+// the zero-point correction, optional transposes) and the choice between the
+// tensor-core kernel (gemm_u8_tc.cu) and a CUDA-core kernel that takes any
+// layout, alignment and depth.
+//
+// Reference behaviour: MatMulFixpointImpl (mace/ops/matmul.cc:228-394) and the
+// GEMM of the quantized Conv2D (mace/ops/conv_2d.cc:301-315).
+#include "common.cuh"
+
+bool mb_gemm_u8_tc_supported(const mb_context *ctx, const void *A, const void *B, int64_t M,
+                             int64_t N, int64_t K, bool a_mn, bool b_mn, int a_batched,
+                             int b_batched);
+int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+                         const uint32_t *sum_a, const uint32_t *sum_b, const int32_t *bias,
+                         void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
+                         int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
+                         int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
+                         int bias_per_row);
+
+namespace {
+
+// ---- CUDA-core GEMM: any major order, any size --------------------------------
+// 64 x 64 output tile per 256-thread block, 4 x 4 outputs per thread.  Operands
+// are read element-wise with their own strides, the zero points are subtracted
+// on load, so no correction terms and no overflow for any depth whose true
+// result fits int32.
+constexpr int GT = 64;   // tile edge
+constexpr int GK = 32;   // depth per step
+
+struct GenericParams {
+  const uint8_t *A, *B;
+  const int32_t *bias;
+  void *C;
+  int64_t M, N, K;
+  int64_t a_rs, a_cs;  // strides of A(m,k): m * a_rs + k * a_cs
+  int64_t b_rs, b_cs;  // strides of B(k,n): k * b_rs + n * b_cs
+  int64_t a_bs, b_bs;  // batch strides (0 when not batched)
+  int32_t zp_a, zp_b, mult, shift, zp_c;
+  int out_is_int32, bias_per_row;
+};
+
+__global__ void __launch_bounds__(256) gemm_u8_generic_kernel(const GenericParams p) {
+  __shared__ int16_t As[GK][GT + 2];
+  __shared__ int16_t Bs[GK][GT + 2];
+  const int b = blockIdx.z;
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * GT;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.x) * GT;
+  const uint8_t *A = p.A + b * p.a_bs;
+  const uint8_t *B = p.B + b * p.b_bs;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  int32_t acc[4][4] = {};
+  for (int64_t k0 = 0; k0 < p.K; k0 += GK) {
+    for (int i = threadIdx.x; i < GK * GT; i += 256) {
+      // pick the fastest-varying index so that loads coalesce for either major
+      int kk, mm;
+      if (p.a_cs == 1) { kk = i % GK; mm = i / GK; } else { mm = i % GT; kk = i / GT; }
+      const int64_t m = m0 + mm, k = k0 + kk;
+      As[kk][mm] = (m < p.M && k < p.K)
+                       ? static_cast<int16_t>(static_cast<int32_t>(A[m * p.a_rs + k * p.a_cs]) - p.zp_a)
+                       : 0;
+      int nn;
+      if (p.b_cs == 1) { nn = i % GT; kk = i / GT; } else { kk = i % GK; nn = i / GK; }
+      const int64_t n = n0 + nn;
+      const int64_t kb = k0 + kk;
+      Bs[kk][nn] = (n < p.N && kb < p.K)
+                       ? static_cast<int16_t>(static_cast<int32_t>(B[kb * p.b_rs + n * p.b_cs]) - p.zp_b)
+                       : 0;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < GK; ++kk) {
+      int32_t a[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * bv[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t m = m0 + ty * 4 + i;
+    if (m >= p.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t n = n0 + tx * 4 + j;
+      if (n >= p.N) continue;
+      int32_t v = acc[i][j];
+      if (p.bias != nullptr) v += p.bias_per_row ? p.bias[m] : p.bias[n];
+      const int64_t idx = (static_cast<int64_t>(b) * p.M + m) * p.N + n;
+      if (p.out_is_int32) {
+        static_cast<int32_t *>(p.C)[idx] = v;
+      } else {
+        static_cast<uint8_t *>(p.C)[idx] =
+            static_cast<uint8_t>(mb_requant(v, p.mult, p.shift, p.zp_c));
+      }
+    }
+  }
+}
+
+// ---- byte sums ----------------------------------------------------------------
+// Sum of each row of a [rows x len] byte matrix with contiguous rows; one warp
+// per row, 16-byte loads (len % 16 == 0, base 16-byte aligned).
+__global__ void __launch_bounds__(256) rowsum_u8_kernel(const uint8_t *__restrict__ x,
+                                                        uint32_t *__restrict__ out,
+                                                        int64_t rows, int64_t len) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint4 *p = reinterpret_cast<const uint4 *>(x + row * len);
+  const int64_t nvec = len >> 4;
+  uint32_t s = 0;
+  for (int64_t i = lane; i < nvec; i += 32) {
+    const uint4 v = __ldg(p + i);
+    s = __dp4a(v.x, 0x01010101u, s);
+    s = __dp4a(v.y, 0x01010101u, s);
+    s = __dp4a(v.z, 0x01010101u, s);
+    s = __dp4a(v.w, 0x01010101u, s);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) out[row] = s;
+}
+
+// Sum down the columns of a [rows x cols] byte matrix (cols % 4 == 0, base
+// 4-byte aligned): each thread owns 4 adjacent columns and a slice of the
+// rows; slices are combined with integer atomics into a zeroed output.
+__global__ void __launch_bounds__(256) colsum_u8_kernel(const uint8_t *__restrict__ x,
+                                                        uint32_t *__restrict__ out,
+                                                        int64_t rows, int64_t cols,
+                                                        int64_t rows_per_slice,
+                                                        int64_t batch_stride) {
+  const int64_t c4 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (c4 * 4 >= cols) return;
+  const int b = blockIdx.z;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_slice;
+  const int64_t r1 = min(rows, r0 + rows_per_slice);
+  const uint8_t *base = x + b * batch_stride;
+  uint32_t s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+  for (int64_t r = r0; r < r1; ++r) {
+    const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(base + r * cols) + c4);
+    s0 += w & 0xffu;
+    s1 += (w >> 8) & 0xffu;
+    s2 += (w >> 16) & 0xffu;
+    s3 += w >> 24;
+  }
+  uint32_t *o = out + b * cols + c4 * 4;
+  atomicAdd(o + 0, s0);
+  atomicAdd(o + 1, s1);
+  atomicAdd(o + 2, s2);
+  atomicAdd(o + 3, s3);
+}
+
+// ---- transpose [rows x cols] -> [cols x rows] bytes ------------------------------
+__global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t *__restrict__ in,
+                                                           uint8_t *__restrict__ out,
+                                                           int64_t rows, int64_t cols) {
+  __shared__ uint8_t tile[64][65];
+  const int64_t batch_off = static_cast<int64_t>(blockIdx.z) * rows * cols;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 64, c0 = static_cast<int64_t>(blockIdx.x) * 64;
+  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+    const int r = i >> 6, c = i & 63;
+    tile[r][c] = (r0 + r < rows && c0 + c < cols) ? in[batch_off + (r0 + r) * cols + c0 + c] : 0;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+    const int c = i >> 6, r = i & 63;
+    if (r0 + r < rows && c0 + c < cols) out[batch_off + (c0 + c) * rows + r0 + r] = tile[r][c];
+  }
+}
+
+int launch_rowsum(mb_context *ctx, const uint8_t *x, uint32_t *out, int64_t rows, int64_t len) {
+  rowsum_u8_kernel<<<static_cast<unsigned>(ceil_div64(rows, 8)), 256, 0, ctx->stream>>>(x, out, rows, len);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+int launch_colsum(mb_context *ctx, const uint8_t *x, uint32_t *out, int64_t nb, int64_t rows,
+                  int64_t cols) {
+  MB_CUDA(ctx, cudaMemsetAsync(out, 0, sizeof(uint32_t) * nb * cols, ctx->stream));
+  const int64_t col_blocks = ceil_div64(ceil_div64(cols, 4), 256);
+  int64_t slices = ceil_div64(static_cast<int64_t>(ctx->num_sms) * 2, col_blocks * nb);
+  slices = std::max<int64_t>(1, std::min<int64_t>(slices, ceil_div64(rows, 32)));
+  const int64_t rps = ceil_div64(rows, slices);
+  dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(ceil_div64(rows, rps)),
+            static_cast<unsigned>(nb));
+  colsum_u8_kernel<<<grid, 256, 0, ctx->stream>>>(x, out, rows, cols, rps, rows * cols);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+int launch_transpose(mb_context *ctx, const uint8_t *in, uint8_t *out, int64_t nb, int64_t rows,
+                     int64_t cols) {
+  dim3 grid(static_cast<unsigned>(ceil_div64(cols, 64)), static_cast<unsigned>(ceil_div64(rows, 64)),
+            static_cast<unsigned>(nb));
+  transpose_u8_kernel<<<grid, 256, 0, ctx->stream>>>(in, out, rows, cols);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+int launch_generic(mb_context *ctx, const uint8_t *A, const uint8_t *B, const int32_t *bias,
+                   void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N, int64_t K,
+                   bool a_mn, bool b_mn, int a_batched, int b_batched, int32_t zp_a,
+                   int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c, int bias_per_row) {
+  GenericParams p;
+  p.A = A; p.B = B; p.bias = bias; p.C = C;
+  p.M = M; p.N = N; p.K = K;
+  // A K-major: (m,k) at m*K + k.  A MN-major: (m,k) at k*M + m.
+  p.a_rs = a_mn ? 1 : K; p.a_cs = a_mn ? M : 1;
+  // B MN-major (row-major K x N): (k,n) at k*N + n.  B K-major: n*K + k.
+  p.b_rs = b_mn ? N : 1; p.b_cs = b_mn ? 1 : K;
+  p.a_bs = a_batched ? M * K : 0; p.b_bs = b_batched ? K * N : 0;
+  p.zp_a = zp_a; p.zp_b = zp_b; p.mult = mult; p.shift = shift; p.zp_c = zp_c;
+  p.out_is_int32 = out_is_int32; p.bias_per_row = bias_per_row;
+  const int64_t gx = ceil_div64(N, GT), gy = ceil_div64(M, GT);
+  if (gy > 65535 || batch > 65535)
+    return mb_fail(ctx, MB_UNSUPPORTED, "generic GEMM: M or batch too large for this path");
+  dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy), static_cast<unsigned>(batch));
+  gemm_u8_generic_kernel<<<grid, 256, 0, ctx->stream>>>(p);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+}  // namespace
+
+// Row-major-C GEMM on device operands; a_mn / b_mn as in mb_gemm_u8_tc_launch.
+int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, const int32_t *bias,
+                        void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
+                        int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
+                        int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
+                        int bias_per_row) {
+  const bool aligned16 =
+      ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15u) == 0;
+  bool use_tc = ctx->use_tensor_cores && ctx->encode_tiled != nullptr && aligned16 &&
+                K % 16 == 0 && K <= 33000 && M >= 1 && N >= 1;
+  // How each operand reaches the tensor core: natively in its own major, or
+  // through a K-major copy in scratch.
+  bool a_copy = false, b_copy = false;
+  if (use_tc) {
+    if (a_mn && !(ctx->use_mn_major && M % 16 == 0)) a_copy = true;
+    if (b_mn && !(ctx->use_mn_major && N % 16 == 0)) b_copy = true;
+  }
+  if (!use_tc) {
+    return launch_generic(ctx, A, B, bias, C, out_is_int32, batch, M, N, K, a_mn, b_mn,
+                          a_batched, b_batched, zp_a, zp_b, mult, shift, zp_c, bias_per_row);
+  }
+  const int64_t nb_a = a_batched ? batch : 1, nb_b = b_batched ? batch : 1;
+  const bool need_sum_a = zp_b != 0, need_sum_b = zp_a != 0;
+  size_t off = 0;
+  const size_t off_sum_a = off; off += need_sum_a ? align_up(sizeof(uint32_t) * nb_a * M, 256) : 0;
+  const size_t off_sum_b = off; off += need_sum_b ? align_up(sizeof(uint32_t) * nb_b * N, 256) : 0;
+  const size_t off_at = off; off += a_copy ? align_up(nb_a * M * K, 256) : 0;
+  const size_t off_bt = off; off += b_copy ? align_up(nb_b * N * K, 256) : 0;
+  uint8_t *scratch = nullptr;
+  if (off > 0) MB_RETURN_IF_ERROR(mb_scratch(ctx, off, reinterpret_cast<void **>(&scratch)));
+  uint32_t *sum_a = need_sum_a ? reinterpret_cast<uint32_t *>(scratch + off_sum_a) : nullptr;
+  uint32_t *sum_b = need_sum_b ? reinterpret_cast<uint32_t *>(scratch + off_sum_b) : nullptr;
+  const uint8_t *a_use = A, *b_use = B;
+  bool a_mn_use = a_mn, b_mn_use = b_mn;
+  if (a_copy) {
+    // MN-major A is [K x M]; its transpose [M x K] is K-major.
+    MB_RETURN_IF_ERROR(launch_transpose(ctx, A, scratch + off_at, nb_a, K, M));
+    a_use = scratch + off_at;
+    a_mn_use = false;
+  }
+  if (b_copy) {
+    MB_RETURN_IF_ERROR(launch_transpose(ctx, B, scratch + off_bt, nb_b, K, N));
+    b_use = scratch + off_bt;
+    b_mn_use = false;
+  }
+  if (need_sum_a) {
+    if (a_mn_use) MB_RETURN_IF_ERROR(launch_colsum(ctx, a_use, sum_a, nb_a, K, M));
+    else MB_RETURN_IF_ERROR(launch_rowsum(ctx, a_use, sum_a, nb_a * M, K));
+  }
+  if (need_sum_b) {
+    if (b_mn_use) MB_RETURN_IF_ERROR(launch_colsum(ctx, b_use, sum_b, nb_b, K, N));
+    else MB_RETURN_IF_ERROR(launch_rowsum(ctx, b_use, sum_b, nb_b * N, K));
+  }
+  if (!mb_gemm_u8_tc_supported(ctx, a_use, b_use, M, N, K, a_mn_use, b_mn_use, a_batched,
+                               b_batched)) {
+    return launch_generic(ctx, A, B, bias, C, out_is_int32, batch, M, N, K, a_mn, b_mn,
+                          a_batched, b_batched, zp_a, zp_b, mult, shift, zp_c, bias_per_row);
+  }
+  return mb_gemm_u8_tc_launch(ctx, a_use, b_use, sum_a, sum_b, bias, C, out_is_int32, batch, M,
+                              N, K, a_mn_use, b_mn_use, a_batched, b_batched, zp_a, zp_b, mult,
+                              shift, zp_c, bias_per_row);
+}
+
+extern "C" int mb_gemm_u8(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+                          const int32_t *bias, void *C, int out_is_int32, int64_t batch,
+                          int64_t M, int64_t N, int64_t K, int a_col_major, int b_col_major,
+                          int c_col_major, int a_batched, int b_batched, int32_t zp_a,
+                          int32_t zp_b, int32_t multiplier, int32_t right_shift, int32_t zp_c,
+                          int bias_per_row) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (batch < 0 || M < 0 || N < 0 || K < 0)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemm_u8: negative dimension");
+  if (batch == 0 || M == 0 || N == 0) return MB_SUCCESS;  // empty output
+  if (A == nullptr || B == nullptr || C == nullptr)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemm_u8: null operand");
+  if (!out_is_int32) {
+    // GetOutputMultiplierAndShift (mace/core/quantize.h:116-126) yields a
+    // multiplier in [2^30, 2^31) and a right shift >= 0; RoundingDivideByPOT
+    // is defined for shifts up to 31.
+    if (multiplier <= 0 || right_shift < 0 || right_shift > 31)
+      return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemm_u8: bad multiplier %d / shift %d",
+                     multiplier, right_shift);
+  }
+  if (K == 0) {
+    // Empty depth: the accumulator is zero, the pipeline still applies.
+    return mb_fail(ctx, MB_UNSUPPORTED, "mb_gemm_u8: K == 0");
+  }
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  // A(m,k) is K-major unless a_col_major; B(k,n) is K-major iff b_col_major.
+  if (!c_col_major) {
+    return mb_gemm_u8_rowmajor(ctx, A, B, bias, C, out_is_int32, batch, M, N, K,
+                               a_col_major != 0, b_col_major == 0, a_batched, b_batched, zp_a,
+                               zp_b, multiplier, right_shift, zp_c, bias_per_row);
+  }
+  // Column-major C (M x N) is row-major C^T (N x M) = B^T * A^T: swap the
+  // roles of the operands.  A'(n,k) = B(k,n) is MN-major iff B is; likewise B'.
+  return mb_gemm_u8_rowmajor(ctx, B, A, bias, C, out_is_int32, batch, N, M, K,
+                             /*a_mn=*/b_col_major == 0, /*b_mn=*/a_col_major != 0, b_batched,
+                             a_batched, zp_b, zp_a, multiplier, right_shift, zp_c,
+                             bias != nullptr ? !bias_per_row : 0);
+}

@@ -1,0 +1,124 @@
+// uint8 GEMV with the float requantization rule of MACE's Gemv delegators.
+//
+// Reference behaviour: arm::q8::Gemv<T>::Compute (mace/ops/arm/q8/gemv.cc:36-171):
+//   ret = dot - sum_lhs * zp_rhs - sum_rhs * zp_lhs + K * zp_lhs * zp_rhs (+ bias[h])
+//   uint8: Saturate<uint8_t>(roundf(ret * multiplier_float + zp_out))
+// and ref::q8::Gemv<uint8_t> (mace/ops/ref/q8/gemv.cc:80-122), which omits
+// zp_out.  The product and the sum are rounded separately (no fused
+// multiply-add), as the C++ expression is written.
+//
+// The kernel is bandwidth-bound: one warp streams one row of the matrix with
+// 128-bit loads and integer dot-product instructions, the vector is re-read
+// through L1/L2.  When the matrix is shared by all batch entries (the
+// FullyConnected case) the warp keeps its row and loops over the vectors.
+#include "common.cuh"
+
+namespace {
+
+struct GemvParams {
+  const uint8_t *lhs, *rhs;
+  const int32_t *bias;
+  void *out;
+  int64_t batch, rows, K;
+  int lhs_batched, rhs_batched, out_is_int32, add_zp_out;
+  int32_t zp_lhs, zp_rhs, zp_out;
+  float multiplier;
+};
+
+template <bool VEC>
+__global__ void __launch_bounds__(256) gemv_u8_kernel(const GemvParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  // blockIdx.y walks the batch when every entry has its own matrix; otherwise
+  // one warp serves all batch entries of its row.
+  const int64_t b_begin = p.lhs_batched ? blockIdx.y : 0;
+  const int64_t b_end = p.lhs_batched ? b_begin + 1 : p.batch;
+  for (int64_t b = b_begin; b < b_end; ++b) {
+    const uint8_t *lp = p.lhs + (p.lhs_batched ? b * p.rows * p.K : 0) + row * p.K;
+    const uint8_t *rp = p.rhs + (p.rhs_batched ? b * p.K : 0);
+    uint32_t dot = 0, sum_l = 0, sum_r = 0;
+    if (VEC) {
+      const uint4 *l4 = reinterpret_cast<const uint4 *>(lp);
+      const uint4 *r4 = reinterpret_cast<const uint4 *>(rp);
+      const int64_t nvec = p.K >> 4;
+#pragma unroll 4
+      for (int64_t i = lane; i < nvec; i += 32) {
+        const uint4 l = __ldg(l4 + i);
+        const uint4 r = __ldg(r4 + i);
+        dot = __dp4a(l.x, r.x, dot);
+        dot = __dp4a(l.y, r.y, dot);
+        dot = __dp4a(l.z, r.z, dot);
+        dot = __dp4a(l.w, r.w, dot);
+        sum_l = __dp4a(l.x, 0x01010101u, sum_l);
+        sum_l = __dp4a(l.y, 0x01010101u, sum_l);
+        sum_l = __dp4a(l.z, 0x01010101u, sum_l);
+        sum_l = __dp4a(l.w, 0x01010101u, sum_l);
+        sum_r = __dp4a(r.x, 0x01010101u, sum_r);
+        sum_r = __dp4a(r.y, 0x01010101u, sum_r);
+        sum_r = __dp4a(r.z, 0x01010101u, sum_r);
+        sum_r = __dp4a(r.w, 0x01010101u, sum_r);
+      }
+    } else {
+      for (int64_t i = lane; i < p.K; i += 32) {
+        const uint32_t l = lp[i], r = rp[i];
+        dot += l * r;
+        sum_l += l;
+        sum_r += r;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      sum_l += __shfl_xor_sync(0xffffffffu, sum_l, o);
+      sum_r += __shfl_xor_sync(0xffffffffu, sum_r, o);
+    }
+    if (lane == 0) {
+      const uint32_t zero_point_dot = static_cast<uint32_t>(
+          static_cast<int64_t>(p.zp_lhs) * p.zp_rhs * p.K);
+      int32_t ret = static_cast<int32_t>(dot - sum_l * static_cast<uint32_t>(p.zp_rhs) -
+                                         sum_r * static_cast<uint32_t>(p.zp_lhs) + zero_point_dot);
+      if (p.bias != nullptr) ret += p.bias[row];
+      const int64_t idx = b * p.rows + row;
+      if (p.out_is_int32) {
+        static_cast<int32_t *>(p.out)[idx] = ret;
+      } else {
+        float v = __fmul_rn(static_cast<float>(ret), p.multiplier);
+        if (p.add_zp_out) v = __fadd_rn(v, static_cast<float>(p.zp_out));
+        static_cast<uint8_t *>(p.out)[idx] = static_cast<uint8_t>(mb_saturate_round_u8(v));
+      }
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rhs,
+                          const int32_t *bias, void *out, int out_is_int32, int64_t batch,
+                          int64_t rows, int64_t K, int lhs_batched, int rhs_batched,
+                          int32_t zp_lhs, int32_t zp_rhs, float multiplier, int32_t zp_out,
+                          int add_zp_out) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (batch < 0 || rows < 0 || K < 0)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemv_u8: negative dimension");
+  if (batch == 0 || rows == 0) return MB_SUCCESS;
+  if (lhs == nullptr || rhs == nullptr || out == nullptr)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemv_u8: null operand");
+  if (lhs_batched && batch > 65535)
+    return mb_fail(ctx, MB_UNSUPPORTED, "mb_gemv_u8: batch > 65535 with a batched matrix");
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  GemvParams p;
+  p.lhs = lhs; p.rhs = rhs; p.bias = bias; p.out = out;
+  p.batch = batch; p.rows = rows; p.K = K;
+  p.lhs_batched = lhs_batched; p.rhs_batched = rhs_batched;
+  p.out_is_int32 = out_is_int32; p.add_zp_out = add_zp_out;
+  p.zp_lhs = zp_lhs; p.zp_rhs = zp_rhs; p.zp_out = zp_out; p.multiplier = multiplier;
+  const bool vec = (K % 16 == 0) && K > 0 &&
+                   ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15u) == 0;
+  dim3 grid(static_cast<unsigned>(ceil_div64(rows, 8)), lhs_batched ? static_cast<unsigned>(batch) : 1u);
+  if (vec) gemv_u8_kernel<true><<<grid, 256, 0, ctx->stream>>>(p);
+  else gemv_u8_kernel<false><<<grid, 256, 0, ctx->stream>>>(p);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}

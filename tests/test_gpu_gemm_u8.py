@@ -1,0 +1,184 @@
+"""uint8 GEMM on the GPU against the CPU oracle: bit-exact."""
+import numpy as np
+import pytest
+
+from helpers import gemm_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import mace_b200
+    c = mace_b200.Context(0)
+    yield c
+    c.close()
+
+
+def run_gemm(ctx, orc, case, batch, M, N, K, out_int32=False, c_col_major=False,
+             bias_per_row=False, **kw):
+    A, B, bias = ctx.upload(case["A"]), ctx.upload(case["B"]), None
+    if case["bias"] is not None:
+        bias = ctx.upload(case["bias"])
+    itemsize = 4 if out_int32 else 1
+    out = ctx.alloc(batch * M * N * itemsize + 64)
+    # canary bytes after the output
+    ctx._check(__import__("mace_b200").lib().mb_memset(ctx.h, out.ptr, 0xA5, out.nbytes))
+    ctx.gemm_u8(A, B, bias, out, batch, M, N, K, case["zp_a"], case["zp_b"], case["mult"],
+                case["shift"], case["zp_c"], c_col_major=c_col_major, out_int32=out_int32,
+                bias_per_row=bias_per_row, **kw)
+    got_all = ctx.download(out, (out.nbytes,), np.uint8)
+    assert (got_all[batch * M * N * itemsize:] == 0xA5).all(), "wrote past the output"
+    got = got_all[:batch * M * N * itemsize].view(np.int32 if out_int32 else np.uint8)
+    exp = orc.gemm_u8(case["A"], case["B"], case["bias"], batch, M, N, K, case["zp_a"],
+                      case["zp_b"], case["mult"], case["shift"], case["zp_c"],
+                      c_col_major=c_col_major, out_int32=out_int32, bias_per_row=bias_per_row,
+                      **kw)
+    for b in (A, B, out):
+        b.free()
+    return got, exp
+
+
+def test_config0_1024_matmul(ctx, orc):
+    """M=N=K=1024, zero points 128/120, scales 0.02/0.005, seed 0 (MatMul: no bias)."""
+    case = gemm_case(orc, 0, 1, 1024, 1024, 1024)
+    before = ctx.launches_tensor_core
+    got, exp = run_gemm(ctx, orc, case, 1, 1024, 1024, 1024)
+    assert ctx.launches_tensor_core == before + 1, "tensor-core kernel did not run"
+    assert np.array_equal(got, exp)
+    assert len(np.unique(got)) > 100  # a vacuous all-saturated output would prove nothing
+
+
+def test_config0_1024_with_bias_conv_form(ctx, orc):
+    """The biased GEMM of the same config: bias per output channel (Conv2D 1x1 form)."""
+    case = gemm_case(orc, 0, 1, 1024, 1024, 1024, bias_len=1024)
+    got, exp = run_gemm(ctx, orc, case, 1, 1024, 1024, 1024, bias_per_row=True)
+    assert np.array_equal(got, exp)
+    got, exp = run_gemm(ctx, orc, case, 1, 1024, 1024, 1024, bias_per_row=False)
+    assert np.array_equal(got, exp)
+
+
+@pytest.mark.parametrize("a_cm,b_cm", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("mn_major", [1, 0])
+def test_transpose_combos_tensor_core(ctx, orc, a_cm, b_cm, mn_major):
+    """All four transpose_a/transpose_b combinations (matmul_test.cc:162-254), aligned so
+    that the tensor-core path takes them, with MN-major operands either described to the
+    tensor core directly or transposed in scratch."""
+    ctx.set_option("mn_major", mn_major)
+    try:
+        M, N, K = 256, 384, 512
+        case = gemm_case(orc, 3, 1, M, N, K, a_col_major=a_cm, b_col_major=b_cm)
+        before = ctx.launches_tensor_core
+        got, exp = run_gemm(ctx, orc, case, 1, M, N, K, a_col_major=a_cm, b_col_major=b_cm)
+        assert ctx.launches_tensor_core == before + 1
+        assert np.array_equal(got, exp)
+    finally:
+        ctx.set_option("mn_major", 1)
+
+
+@pytest.mark.parametrize("shape", [(1, 31, 61, 67), (2, 16, 32, 48), (3, 128, 64, 16),
+                                   (1, 1, 256, 30000 // 16 * 16), (1, 200, 136, 144),
+                                   (16, 64, 64, 64), (1, 129, 272, 4096)])
+def test_shapes_and_tails(ctx, orc, shape):
+    batch, M, N, K = shape
+    case = gemm_case(orc, 11, batch, M, N, K)
+    got, exp = run_gemm(ctx, orc, case, batch, M, N, K)
+    assert np.array_equal(got, exp)
+
+
+@pytest.mark.parametrize("a_cm,b_cm", [(False, False), (False, True), (True, False), (True, True)])
+def test_unaligned_generic_path(ctx, orc, a_cm, b_cm):
+    """31 x 61 x 67 (matmul_test.cc): no 16-byte alignment anywhere, CUDA-core kernel."""
+    case = gemm_case(orc, 5, 2, 31, 67, 61, a_col_major=a_cm, b_col_major=b_cm)
+    before = ctx.launches_tensor_core
+    got, exp = run_gemm(ctx, orc, case, 2, 31, 67, 61, a_col_major=a_cm, b_col_major=b_cm)
+    assert ctx.launches_tensor_core == before
+    assert np.array_equal(got, exp)
+
+
+def test_one_side_batched_and_int32_and_colmajor_out(ctx, orc):
+    M, N, K = 96, 160, 208
+    case = gemm_case(orc, 7, 3, M, N, K, b_batched=False)
+    got, exp = run_gemm(ctx, orc, case, 3, M, N, K, b_batched=False)
+    assert np.array_equal(got, exp)
+    case = gemm_case(orc, 8, 3, M, N, K, a_batched=False)
+    got, exp = run_gemm(ctx, orc, case, 3, M, N, K, a_batched=False, out_int32=True)
+    assert np.array_equal(got, exp)
+    case = gemm_case(orc, 9, 1, M, N, K, bias_len=M)
+    got, exp = run_gemm(ctx, orc, case, 1, M, N, K, c_col_major=True, bias_per_row=True)
+    assert np.array_equal(got, exp)
+    got, exp = run_gemm(ctx, orc, case, 1, M, N, K, c_col_major=True, out_int32=True)
+    assert np.array_equal(got, exp)
+
+
+def test_tensor_core_matches_cuda_core_kernel(ctx, orc):
+    M, N, K = 384, 512, 1024
+    case = gemm_case(orc, 21, 1, M, N, K, bias_len=N)
+    got_tc, exp = run_gemm(ctx, orc, case, 1, M, N, K)
+    ctx.set_option("tensor_cores", 0)
+    try:
+        before = ctx.launches_tensor_core
+        got_cc, _ = run_gemm(ctx, orc, case, 1, M, N, K)
+        assert ctx.launches_tensor_core == before
+    finally:
+        ctx.set_option("tensor_cores", 1)
+    assert np.array_equal(got_tc, exp) and np.array_equal(got_cc, exp)
+
+
+def test_extreme_zero_points_and_saturation(ctx, orc):
+    M, N, K = 128, 128, 256
+    for zp_a, zp_b in [(0, 0), (255, 255), (0, 255), (1, 0)]:
+        case = gemm_case(orc, 13, 1, M, N, K, zp_a=zp_a, zp_b=zp_b)
+        got, exp = run_gemm(ctx, orc, case, 1, M, N, K)
+        assert np.array_equal(got, exp)
+    # all-zero and all-255 operands
+    case = gemm_case(orc, 13, 1, M, N, K)
+    case["A"][:] = 255
+    case["B"][:] = 255
+    got, exp = run_gemm(ctx, orc, case, 1, M, N, K, out_int32=True)
+    assert np.array_equal(got, exp)
+
+
+def test_empty_and_bad_arguments(ctx):
+    import mace_b200
+    buf = ctx.alloc(64)
+    # empty output: success, nothing written
+    ctx.gemm_u8(buf, buf, None, buf, 0, 4, 4, 4, 0, 0)
+    ctx.gemm_u8(buf, buf, None, buf, 1, 0, 4, 4, 0, 0)
+    with pytest.raises(mace_b200.MaceB200Error) as e:
+        ctx.gemm_u8(buf, buf, None, buf, 1, -1, 4, 4, 0, 0)
+    assert e.value.code == 1
+    with pytest.raises(mace_b200.MaceB200Error) as e:
+        ctx.gemm_u8(buf, buf, None, buf, 1, 4, 4, 4, 0, 0, mult=0)
+    assert e.value.code == 1
+    with pytest.raises(mace_b200.MaceB200Error) as e:
+        ctx.gemm_u8(buf, buf, None, buf, 1, 4, 4, 4, 0, 0, shift=40)
+    assert e.value.code == 1
+
+
+def test_linearity_at_full_size(ctx, orc):
+    """K = N = 4096, M = 4096 is too large for the scalar oracle in seconds; check raw int32
+    accumulators through properties instead: (a) a random sample of rows against the oracle,
+    (b) additivity over a split of K."""
+    M = N = K = 4096
+    rng = np.random.Generator(np.random.PCG64(4))
+    A = rng.integers(0, 256, size=(M, K), dtype=np.uint8)
+    B = rng.integers(0, 256, size=(K, N), dtype=np.uint8)
+    dA, dB = ctx.upload(A), ctx.upload(B)
+    out = ctx.alloc(M * N * 4)
+    ctx.gemm_u8(dA, dB, None, out, 1, M, N, K, 128, 120, out_int32=True)
+    full = ctx.download(out, (M, N), np.int32)
+    rows = rng.choice(M, size=16, replace=False)
+    exp = orc.gemm_u8(A[rows], B, None, 1, 16, N, K, 128, 120, out_int32=True).reshape(16, N)
+    assert np.array_equal(full[rows], exp)
+    # additivity over K: C(K) = C(first half) + C(second half)
+    A1, A2 = np.ascontiguousarray(A[:, :K // 2]), np.ascontiguousarray(A[:, K // 2:])
+    B1, B2 = np.ascontiguousarray(B[:K // 2]), np.ascontiguousarray(B[K // 2:])
+    parts = []
+    for a, b in ((A1, B1), (A2, B2)):
+        da, db = ctx.upload(a), ctx.upload(b)
+        ctx.gemm_u8(da, db, None, out, 1, M, N, K // 2, 128, 120, out_int32=True)
+        parts.append(ctx.download(out, (M, N), np.int32))
+        da.free()
+        db.free()
+    assert np.array_equal(full, parts[0] + parts[1])

@@ -1,0 +1,192 @@
+"""uint8 GEMV, Conv2D, DepthwiseConv2d and pooling on the GPU against the CPU oracle
+(bit-exact), including the reference's two quantized known-answer tests."""
+import numpy as np
+import pytest
+
+from helpers import conv_quant
+
+pytestmark = pytest.mark.gpu
+
+PAD = {"VALID": 0, "SAME": 1, "FULL": 2}
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import mace_b200
+    c = mace_b200.Context(0)
+    yield c
+    c.close()
+
+
+# ---- known-answer tests through the C ABI ---------------------------------------
+
+def test_conv2d_kat_230(ctx, orc, kats):
+    k = kats["conv2d_u8_3x3"]
+    x = np.array(k["input"], np.uint8).reshape(k["input_nhwc_shape"])
+    f = np.array(k["filter"], np.uint8).reshape(k["filter_ohwi_shape"])
+    bias = orc.get_bias_data(np.array(k["bias"], np.int32), k["bias_scale"], k["input_scale"],
+                             k["filter_scale"], 1)
+    mult, shift = orc.output_multiplier_and_shift(k["filter_scale"], k["input_scale"],
+                                                  k["output_scale"])
+    dx, df, db, do = ctx.upload(x), ctx.upload(f), ctx.upload(bias), ctx.alloc(16)
+    ctx.conv2d_u8(dx, df, db, do, 1, 3, 3, 2, 1, 3, 3, (1, 1), (0, 0), (1, 1), k["input_zp"],
+                  k["filter_zp"], mult, shift, k["output_zp"])
+    assert ctx.download(do, (1,), np.uint8).tolist() == k["expected"]
+
+
+def test_dwconv_kat_255_21(ctx, orc, kats):
+    k = kats["dwconv_u8_3x3"]
+    x = np.array(k["input"], np.uint8).reshape(k["input_nhwc_shape"])
+    f = np.array(k["filter"], np.uint8).reshape(k["filter_hwim_shape"])
+    bias = orc.get_bias_data(np.array(k["bias"], np.int32), k["bias_scale"], k["input_scale"],
+                             k["filter_scale"], 2)
+    mult, shift = orc.output_multiplier_and_shift(k["input_scale"], k["filter_scale"],
+                                                  k["output_scale"])
+    dx, df, db, do = ctx.upload(x), ctx.upload(f), ctx.upload(bias), ctx.alloc(16)
+    ctx.dwconv_u8(dx, df, db, do, 1, 3, 3, 2, 1, 3, 3, (1, 1), (1, 1), (0, 0), (1, 1),
+                  k["input_zp"], k["filter_zp"], mult, shift, k["output_zp"])
+    assert ctx.download(do, (2,), np.uint8).tolist() == k["expected"]
+
+
+# ---- GEMV --------------------------------------------------------------------------
+
+@pytest.mark.parametrize("shape", [(1, 16, 4), (1, 16, 256), (2, 16, 256), (3, 63, 257),
+                                   (1, 4096, 4096), (64, 1000, 1024), (1, 256, 30000)])
+@pytest.mark.parametrize("lhs_batched", [False, True])
+def test_gemv_u8(ctx, orc, shape, lhs_batched):
+    """Shapes of test/ccunit/mace/ops/arm/q8/gemv_test.cc plus the FullyConnected and the
+    M=1 sweep shapes; uint8 (both zero-point formulas) and int32 outputs."""
+    batch, rows, K = shape
+    if lhs_batched and batch * rows * K > (1 << 26):
+        pytest.skip("batched copy of the matrix not needed at this size")
+    rng = np.random.Generator(np.random.PCG64(rows * 7 + K))
+    lhs = rng.integers(0, 256, size=((batch if lhs_batched else 1), rows, K), dtype=np.uint8)
+    rhs = rng.integers(0, 256, size=(batch, K), dtype=np.uint8)
+    bias = np.rint(rng.normal(0, 1000, size=rows)).astype(np.int32)
+    zl, zr = 127, 128
+    mult = np.float32(1.0 / (np.sqrt(K) * 74 * 74 * 3 / 127))
+    dl, dr, db = ctx.upload(lhs), ctx.upload(rhs), ctx.upload(bias)
+    do = ctx.alloc(batch * rows * 4)
+    for add_zp in (True, False):
+        ctx.gemv_u8(dl, dr, db, do, batch, rows, K, zl, zr, mult, 31, add_zp,
+                    lhs_batched=lhs_batched)
+        got = ctx.download(do, (batch * rows,), np.uint8)
+        exp = orc.gemv_u8(lhs, rhs, bias, batch, rows, K, zl, zr, mult, 31, add_zp,
+                          lhs_batched=lhs_batched)
+        assert np.array_equal(got, exp)
+        assert len(np.unique(got)) > 2
+    ctx.gemv_u8(dl, dr, None, do, batch, rows, K, zl, zr, lhs_batched=lhs_batched,
+                out_int32=True)
+    got = ctx.download(do, (batch * rows,), np.int32)
+    exp = orc.gemv_u8(lhs, rhs, None, batch, rows, K, zl, zr, lhs_batched=lhs_batched,
+                      out_int32=True)
+    assert np.array_equal(got, exp)
+    for b in (dl, dr, db, do):
+        b.free()
+
+
+# ---- Conv2D ------------------------------------------------------------------------
+# shapes in the style of conv_2d_test.cc:1348-1397: N, H, W, C, O, KH, KW, stride, padding
+
+def _conv_case(ctx, orc, N, H, W, C, O, KH, KW, stride, padding, seed=0):
+    rng = np.random.Generator(np.random.PCG64(seed + H * 131 + C))
+    x, f, zp_in, zp_f, mult, shift = conv_quant(orc, rng, (N, H, W, C), (O, KH, KW, C),
+                                                C * KH * KW)
+    bias = np.rint(rng.normal(0, 2000, size=O)).astype(np.int32)
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, KH, KW, (1, 1), (stride, stride),
+                                                      PAD[padding])
+    zp_out = int(rng.integers(96, 161))
+    exp = orc.conv2d_u8(x, f, bias, (stride, stride), (ph, pw), (Ho, Wo), zp_in, zp_f, mult,
+                        shift, zp_out)
+    dx, df, db = ctx.upload(x), ctx.upload(f), ctx.upload(bias)
+    do = ctx.alloc(exp.size)
+    ctx.conv2d_u8(dx, df, db, do, N, H, W, C, O, KH, KW, (stride, stride), (ph >> 1, pw >> 1),
+                  (Ho, Wo), zp_in, zp_f, mult, shift, zp_out)
+    got = ctx.download(do, exp.shape, np.uint8)
+    for b in (dx, df, db, do):
+        b.free()
+    assert np.array_equal(got, exp)
+    assert len(np.unique(got)) > min(4, got.size // 2)
+    return got
+
+
+@pytest.mark.parametrize("case", [
+    (1, 2, 3, 3, 1, 1, 1, 1, "VALID"),
+    (1, 16, 16, 64, 64, 1, 1, 1, "VALID"),
+    (9, 7, 9, 32, 128, 1, 1, 1, "SAME"),
+    (1, 32, 32, 3, 32, 3, 3, 2, "SAME"),      # MobileNet stem shape (reduced size)
+    (2, 17, 19, 32, 64, 3, 3, 1, "SAME"),     # patch gather + tensor-core GEMM
+    (1, 31, 33, 16, 24, 3, 3, 2, "VALID"),
+    (1, 15, 17, 8, 16, 5, 5, 1, "FULL"),
+    (1, 12, 12, 64, 96, 3, 3, 3, "SAME"),
+    (1, 9, 11, 5, 7, 1, 5, 1, "SAME"),
+    (1, 9, 11, 5, 7, 5, 1, 2, "VALID"),
+    (1, 20, 20, 16, 17, 7, 7, 2, "SAME"),
+])
+def test_conv2d_u8(ctx, orc, case):
+    _conv_case(ctx, orc, *case)
+
+
+def test_conv2d_u8_pointwise_uses_tensor_core(ctx, orc):
+    before = ctx.launches_tensor_core
+    _conv_case(ctx, orc, 2, 28, 28, 256, 256, 1, 1, 1, "VALID")
+    assert ctx.launches_tensor_core == before + 1
+
+
+# ---- DepthwiseConv2d ---------------------------------------------------------------
+
+@pytest.mark.parametrize("case", [
+    # N, H, W, C, mult, KH, KW, stride, dilation, padding   (depthwise_conv2d_test.cc:464-492)
+    (1, 56, 56, 128, 1, 3, 3, 1, 1, "SAME"),
+    (3, 28, 28, 128, 1, 3, 3, 2, 1, "SAME"),
+    (1, 14, 14, 512, 1, 3, 3, 1, 1, "VALID"),
+    (2, 7, 7, 1024, 1, 3, 3, 1, 1, "SAME"),
+    (1, 33, 31, 32, 1, 3, 3, 2, 1, "SAME"),
+    (1, 9, 5, 36, 1, 3, 3, 1, 1, "FULL"),
+    (1, 13, 14, 12, 2, 3, 3, 1, 1, "SAME"),     # channel multiplier 2 -> general kernel
+    (1, 13, 14, 7, 1, 5, 5, 2, 1, "SAME"),
+    (1, 15, 15, 16, 1, 3, 3, 1, 2, "SAME"),     # dilated -> float-multiplier rule
+])
+def test_dwconv_u8(ctx, orc, case):
+    N, H, W, C, mc, KH, KW, stride, dil, padding = case
+    rng = np.random.Generator(np.random.PCG64(H * 17 + C))
+    x, f, zp_in, zp_f, mult, shift = conv_quant(orc, rng, (N, H, W, C), (KH, KW, C, mc), KH * KW)
+    bias = np.rint(rng.normal(0, 500, size=C * mc)).astype(np.int32)
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, KH, KW, (dil, dil), (stride, stride),
+                                                      PAD[padding])
+    zp_out = int(rng.integers(96, 161))
+    args = (x, f, bias, (stride, stride), (dil, dil), (ph >> 1, pw >> 1), (Ho, Wo), zp_in, zp_f)
+    dx, df, db = ctx.upload(x), ctx.upload(f), ctx.upload(bias)
+    do = ctx.alloc(N * Ho * Wo * C * mc)
+    if dil == 1:
+        exp = orc.dwconv_u8(*args, mult, shift, zp_out)
+        ctx.dwconv_u8(dx, df, db, do, N, H, W, C, mc, KH, KW, (stride, stride), (dil, dil),
+                      (ph >> 1, pw >> 1), (Ho, Wo), zp_in, zp_f, mult, shift, zp_out)
+    else:
+        mf = np.float32(1.0 / (3 * 74 * 74 * 3 / 127))
+        exp = orc.dwconv_u8_general(*args, mf, zp_out)
+        ctx.dwconv_u8(dx, df, db, do, N, H, W, C, mc, KH, KW, (stride, stride), (dil, dil),
+                      (ph >> 1, pw >> 1), (Ho, Wo), zp_in, zp_f, zp_out=zp_out,
+                      float_multiplier=mf)
+    got = ctx.download(do, exp.shape, np.uint8)
+    for b in (dx, df, db, do):
+        b.free()
+    assert np.array_equal(got, exp)
+    assert len(np.unique(got)) > 4
+
+
+# ---- pooling -----------------------------------------------------------------------
+
+@pytest.mark.parametrize("case", [(64, 7, 7, 1024, 7, 7, 1, "VALID"), (2, 9, 11, 24, 3, 3, 2, "SAME"),
+                                  (1, 8, 8, 5, 2, 2, 2, "VALID")])
+def test_avgpool_u8(ctx, orc, case):
+    N, H, W, C, KH, KW, stride, padding = case
+    rng = np.random.Generator(np.random.PCG64(3))
+    x = rng.integers(0, 256, size=(N, H, W, C), dtype=np.uint8)
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, KH, KW, (1, 1), (stride, stride),
+                                                      PAD[padding])
+    exp = orc.avgpool_u8(x, (KH, KW), (stride, stride), (ph >> 1, pw >> 1), (Ho, Wo))
+    dx, do = ctx.upload(x), ctx.alloc(exp.size)
+    ctx.avgpool_u8(dx, do, N, H, W, C, (KH, KW), (stride, stride), (ph >> 1, pw >> 1), (Ho, Wo))
+    got = ctx.download(do, exp.shape, np.uint8)
+    assert np.array_equal(got, exp)
