@@ -61,6 +61,14 @@ int mb_memset(mb_context *ctx, void *dst_dev, int value, size_t bytes);
 int mb_stream_sync(mb_context *ctx);
 /* The cudaStream_t of the context, as an opaque pointer (for event timing). */
 void *mb_stream(mb_context *ctx);
+/* Device-side timing on the context's stream (the per-operator CallStats of
+ * SerialNet::Run, mace/core/net/serial_net.cc:122-180, are filled from these):
+ * create two events, record one before and one after the work, then read the
+ * elapsed milliseconds (waits for the second event). */
+int mb_event_create(mb_context *ctx, void **event);
+int mb_event_record(mb_context *ctx, void *event);
+int mb_event_elapsed_ms(mb_context *ctx, void *start, void *stop, float *ms);
+int mb_event_destroy(mb_context *ctx, void *event);
 /* Number of kernels launched through this context so far; the second form
  * counts only tcgen05 tensor-core GEMM launches. */
 uint64_t mb_launch_count(const mb_context *ctx);

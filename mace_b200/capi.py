@@ -48,6 +48,10 @@ PROTOTYPES = {
     "mb_memset": (_int, [_vp, _vp, _int, _sz]),
     "mb_stream_sync": (_int, [_vp]),
     "mb_stream": (_vp, [_vp]),
+    "mb_event_create": (_int, [_vp, C.POINTER(_vp)]),
+    "mb_event_record": (_int, [_vp, _vp]),
+    "mb_event_elapsed_ms": (_int, [_vp, _vp, _vp, C.POINTER(_f32)]),
+    "mb_event_destroy": (_int, [_vp, _vp]),
     "mb_launch_count": (C.c_uint64, [_vp]),
     "mb_launch_count_tensor_core": (C.c_uint64, [_vp]),
     "mb_set_option": (_int, [_vp, C.c_char_p, _int]),
@@ -113,6 +117,8 @@ class Context:
         if self.h:
             for b in self._bufs:
                 b.free()
+            for p in getattr(self, "_pinned", []):
+                lib().mb_host_free(self.h, p)
             lib().mb_destroy(self.h)
             self.h = None
 
@@ -148,6 +154,35 @@ class Context:
 
     def sync(self):
         self._check(lib().mb_stream_sync(self.h))
+
+    def event(self):
+        e = _vp()
+        self._check(lib().mb_event_create(self.h, C.byref(e)))
+        return e
+
+    def record(self, event):
+        self._check(lib().mb_event_record(self.h, event))
+
+    def elapsed_ms(self, start, stop):
+        ms = _f32()
+        self._check(lib().mb_event_elapsed_ms(self.h, start, stop, C.byref(ms)))
+        return float(ms.value)
+
+    def host_alloc(self, nbytes):
+        """Pinned host memory as a numpy uint8 array (freed with the context)."""
+        import numpy as np
+        p = _vp()
+        self._check(lib().mb_host_alloc(self.h, max(int(nbytes), 1), C.byref(p)))
+        self._pinned = getattr(self, "_pinned", [])
+        self._pinned.append(p.value)
+        return np.ctypeslib.as_array((C.c_uint8 * int(nbytes)).from_address(p.value))
+
+    def h2d(self, buf, arr):
+        """Asynchronous copy of a (pinned) numpy array into a device buffer."""
+        self._check(lib().mb_memcpy_h2d(self.h, buf.ptr, arr.ctypes.data, arr.nbytes))
+
+    def d2h(self, arr, buf):
+        self._check(lib().mb_memcpy_d2h(self.h, arr.ctypes.data, buf.ptr, arr.nbytes))
 
     def set_option(self, name, value):
         self._check(lib().mb_set_option(self.h, name.encode(), int(value)))

@@ -175,6 +175,36 @@ int mb_stream_sync(mb_context *ctx) {
   return MB_SUCCESS;
 }
 
+int mb_event_create(mb_context *ctx, void **event) {
+  if (ctx == nullptr || event == nullptr) return MB_INVALID_ARGS;
+  cudaEvent_t e;
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  MB_CUDA(ctx, cudaEventCreate(&e));
+  *event = e;
+  return MB_SUCCESS;
+}
+
+int mb_event_record(mb_context *ctx, void *event) {
+  if (ctx == nullptr || event == nullptr) return MB_INVALID_ARGS;
+  MB_CUDA(ctx, cudaEventRecord(static_cast<cudaEvent_t>(event), ctx->stream));
+  return MB_SUCCESS;
+}
+
+int mb_event_elapsed_ms(mb_context *ctx, void *start, void *stop, float *ms) {
+  if (ctx == nullptr || start == nullptr || stop == nullptr || ms == nullptr)
+    return MB_INVALID_ARGS;
+  MB_CUDA(ctx, cudaEventSynchronize(static_cast<cudaEvent_t>(stop)));
+  MB_CUDA(ctx, cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start),
+                                    static_cast<cudaEvent_t>(stop)));
+  return MB_SUCCESS;
+}
+
+int mb_event_destroy(mb_context *ctx, void *event) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (event != nullptr) MB_CUDA(ctx, cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  return MB_SUCCESS;
+}
+
 void *mb_stream(mb_context *ctx) { return ctx ? ctx->stream : nullptr; }
 
 uint64_t mb_launch_count(const mb_context *ctx) { return ctx ? ctx->launches : 0; }

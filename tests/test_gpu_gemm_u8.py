@@ -107,7 +107,8 @@ def test_one_side_batched_and_int32_and_colmajor_out(ctx, orc):
     case = gemm_case(orc, 9, 1, M, N, K, bias_len=M)
     got, exp = run_gemm(ctx, orc, case, 1, M, N, K, c_col_major=True, bias_per_row=True)
     assert np.array_equal(got, exp)
-    got, exp = run_gemm(ctx, orc, case, 1, M, N, K, c_col_major=True, out_int32=True)
+    got, exp = run_gemm(ctx, orc, case, 1, M, N, K, c_col_major=True, out_int32=True,
+                        bias_per_row=True)
     assert np.array_equal(got, exp)
 
 
