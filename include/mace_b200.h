@@ -143,6 +143,36 @@ int mb_avgpool_u8_nhwc(mb_context *ctx, const uint8_t *in, uint8_t *out,
                        int64_t KW, int stride_h, int stride_w, int pad_top,
                        int pad_left, int64_t Ho, int64_t Wo);
 
+/* ---- uint8 GEMM without any allocation ------------------------------------
+ * No counterpart in the reference.  For callers that may not allocate device
+ * memory (a real-time loop with a fixed memory budget, a plugin inside an
+ * application that owns all GPU memory, code that can run while another
+ * stream is being captured): the same tensor-core GEMM and epilogue as
+ * mb_gemm_u8, one batch entry, row-major C, but with its scratch (operand
+ * byte sums and the kernel's status word) in a fixed array inside the
+ * library instead of an mb_context arena.  It calls no cudaMalloc / cudaFree
+ * and needs no mb_context; work is enqueued on `stream` (a cudaStream_t, may
+ * be NULL) of the CURRENT device.
+ *  - Limits: M, N <= MB_STATIC_SCRATCH_MAX_DIM; operands 16-byte aligned; K
+ *    and each operand's contiguous dimension a multiple of 16; K <= 33000.
+ *    Anything else is rejected with MB_INVALID_ARGS / MB_UNSUPPORTED and a
+ *    message in error_message (may be NULL).
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress); make that first call before any stream capture.
+ *  - All calls on a device share the one array: calls whose kernels can
+ *    overlap on the GPU (different streams or host threads) race.  Keep them
+ *    on one stream or order them with events.
+ *  - Every GPU that loads the library holds the array (about 130 KB) until
+ *    the process exits. */
+#define MB_STATIC_SCRATCH_MAX_DIM 16384
+int mb_gemm_u8_static_scratch(void *stream, const uint8_t *A, const uint8_t *B,
+                              const int32_t *bias, void *C, int out_is_int32,
+                              int64_t M, int64_t N, int64_t K, int a_col_major,
+                              int b_col_major, int32_t zp_a, int32_t zp_b,
+                              int32_t multiplier, int32_t right_shift,
+                              int32_t zp_c, int bias_per_row,
+                              char *error_message, size_t error_message_len);
+
 #ifdef __cplusplus
 }
 #endif

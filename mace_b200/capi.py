@@ -62,6 +62,8 @@ PROTOTYPES = {
     "mb_dwconv_u8_nhwc": (_int, [_vp] * 5 + [_i64] * 7 + [_int] * 6 + [_i64] * 2 + [_i32] * 5 +
                           [_int, _f32]),
     "mb_avgpool_u8_nhwc": (_int, [_vp] * 3 + [_i64] * 6 + [_int] * 4 + [_i64] * 2),
+    "mb_gemm_u8_static_scratch": (_int, [_vp] * 5 + [_int] + [_i64] * 3 + [_int] * 2 +
+                                  [_i32] * 5 + [_int, C.c_char_p, _sz]),
 }
 
 _lib = None
