@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(256) rowsum_u8_kernel(const uint8_t *__restric
   const uint4 *p = reinterpret_cast<const uint4 *>(x + row * len);
   const int64_t nvec = len >> 4;
   uint32_t s = 0;
+#pragma unroll 4
   for (int64_t i = lane; i < nvec; i += 32) {
     const uint4 v = __ldg(p + i);
     s = __dp4a(v.x, 0x01010101u, s);
@@ -126,33 +127,54 @@ __global__ void __launch_bounds__(256) rowsum_u8_kernel(const uint8_t *__restric
   if (lane == 0) out[row] = s;
 }
 
-// Sum down the columns of a [rows x cols] byte matrix (cols % 4 == 0, base
-// 4-byte aligned): each thread owns 4 adjacent columns and a slice of the
-// rows; slices are combined with integer atomics into a zeroed output.
+// Sum down the columns of a [rows x cols] byte matrix (cols % 16 == 0, base
+// 16-byte aligned).  A block of 32 x 8 threads covers 512 adjacent columns and
+// one slice of rows: each thread owns 16 columns (one 128-bit load per row) and
+// every 8th row of the slice; the 8 partial sums are combined in shared memory
+// and the slice total is added to the zeroed output with integer atomics.
 __global__ void __launch_bounds__(256) colsum_u8_kernel(const uint8_t *__restrict__ x,
                                                         uint32_t *__restrict__ out,
                                                         int64_t rows, int64_t cols,
                                                         int64_t rows_per_slice,
                                                         int64_t batch_stride) {
-  const int64_t c4 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (c4 * 4 >= cols) return;
+  __shared__ uint32_t part[8][32][17];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t c16 = static_cast<int64_t>(blockIdx.x) * 32 + tx;  // 16-column group
+  const bool active = c16 * 16 < cols;
   const int b = blockIdx.z;
   const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_slice;
   const int64_t r1 = min(rows, r0 + rows_per_slice);
   const uint8_t *base = x + b * batch_stride;
-  uint32_t s0 = 0, s1 = 0, s2 = 0, s3 = 0;
-  for (int64_t r = r0; r < r1; ++r) {
-    const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(base + r * cols) + c4);
-    s0 += w & 0xffu;
-    s1 += (w >> 8) & 0xffu;
-    s2 += (w >> 16) & 0xffu;
-    s3 += w >> 24;
+  uint32_t s[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s[i] = 0;
+  if (active) {
+#pragma unroll 4
+    for (int64_t r = r0 + ty; r < r1; r += 8) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(base + r * cols) + c16);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        s[4 * q + 0] += w[q] & 0xffu;
+        s[4 * q + 1] += (w[q] >> 8) & 0xffu;
+        s[4 * q + 2] += (w[q] >> 16) & 0xffu;
+        s[4 * q + 3] += w[q] >> 24;
+      }
+    }
   }
-  uint32_t *o = out + b * cols + c4 * 4;
-  atomicAdd(o + 0, s0);
-  atomicAdd(o + 1, s1);
-  atomicAdd(o + 2, s2);
-  atomicAdd(o + 3, s3);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) part[ty][tx][i] = s[i];
+  __syncthreads();
+  // 512 columns, 256 threads: two columns each
+  for (int c = threadIdx.x; c < 512; c += 256) {
+    const int gx = c >> 4, gi = c & 15;
+    const int64_t col = static_cast<int64_t>(blockIdx.x) * 512 + c;
+    if (col >= cols) continue;
+    uint32_t t = 0;
+#pragma unroll
+    for (int y = 0; y < 8; ++y) t += part[y][gx][gi];
+    atomicAdd(out + b * cols + col, t);
+  }
 }
 
 // ---- transpose [rows x cols] -> [cols x rows] bytes ------------------------------
@@ -183,9 +205,9 @@ int launch_rowsum(mb_context *ctx, const uint8_t *x, uint32_t *out, int64_t rows
 int launch_colsum(mb_context *ctx, const uint8_t *x, uint32_t *out, int64_t nb, int64_t rows,
                   int64_t cols) {
   MB_CUDA(ctx, cudaMemsetAsync(out, 0, sizeof(uint32_t) * nb * cols, ctx->stream));
-  const int64_t col_blocks = ceil_div64(ceil_div64(cols, 4), 256);
-  int64_t slices = ceil_div64(static_cast<int64_t>(ctx->num_sms) * 2, col_blocks * nb);
-  slices = std::max<int64_t>(1, std::min<int64_t>(slices, ceil_div64(rows, 32)));
+  const int64_t col_blocks = ceil_div64(cols, 512);
+  int64_t slices = ceil_div64(static_cast<int64_t>(ctx->num_sms) * 4, col_blocks * nb);
+  slices = std::max<int64_t>(1, std::min<int64_t>(slices, ceil_div64(rows, 64)));
   const int64_t rps = ceil_div64(rows, slices);
   dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(ceil_div64(rows, rps)),
             static_cast<unsigned>(nb));

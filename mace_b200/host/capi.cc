@@ -1,0 +1,267 @@
+#include "capi.h"
+
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "ops.h"
+
+using namespace mace;  // NOLINT
+
+struct mbh_engine {
+  CudaRuntime runtime;
+  Workspace workspace;
+  OpRegistry op_registry;
+  std::unique_ptr<SerialNet> net;
+  OperatorDef pending;
+  bool building = false;
+  std::string last_error;
+};
+
+namespace {
+
+int Fail(mbh_engine *e, const MaceStatus &st) {
+  if (e != nullptr) e->last_error = st.information();
+  return static_cast<int>(st.code());
+}
+
+int Fail(mbh_engine *e, MaceStatus::Code code, const std::string &msg) {
+  if (e != nullptr) e->last_error = msg;
+  return static_cast<int>(code);
+}
+
+#define MBH_TRY(e, expr)                                             \
+  do {                                                               \
+    MaceStatus _st = (expr);                                         \
+    if (_st != MaceStatus::MACE_SUCCESS) return Fail((e), _st);      \
+  } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int mbh_engine_create(int device, mbh_engine **engine) {
+  if (engine == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  *engine = nullptr;
+  mbh_engine *e = new mbh_engine();
+  MaceStatus st = e->runtime.Init(device);
+  if (st != MaceStatus::MACE_SUCCESS) {
+    const int rc = static_cast<int>(st.code());
+    delete e;
+    return rc;
+  }
+  ops::RegisterAllCudaOpDelegators(e->workspace.GetDelegatorRegistry());
+  ops::RegisterAllCudaOps(&e->op_registry);
+  e->net = std::make_unique<SerialNet>(&e->op_registry, &e->workspace, &e->runtime);
+  *engine = e;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_engine_destroy(mbh_engine *engine) {
+  if (engine == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  mb_stream_sync(engine->runtime.ctx());
+  delete engine;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+const char *mbh_last_error(const mbh_engine *engine) {
+  return engine ? engine->last_error.c_str() : "null engine";
+}
+
+void *mbh_engine_context(mbh_engine *engine) { return engine ? engine->runtime.ctx() : nullptr; }
+
+int mbh_add_tensor(mbh_engine *e, const char *name, int data_type, int rank, const int64_t *dims,
+                   const void *host_data, float scale, int32_t zero_point, int is_weight) {
+  if (e == nullptr || name == nullptr || rank < 0 || (rank > 0 && dims == nullptr))
+    return MaceStatus::MACE_INVALID_ARGS;
+  const DataType dt = static_cast<DataType>(data_type);
+  if (GetEnumTypeSize(dt) == 0) return Fail(e, MaceStatus::MACE_INVALID_ARGS, "unsupported data type");
+  std::vector<index_t> shape(dims, dims + rank);
+  for (index_t d : shape)
+    if (d < 0) return Fail(e, MaceStatus::MACE_INVALID_ARGS, "negative dimension");
+  Tensor *t = e->workspace.CreateTensor(name, &e->runtime, dt, is_weight != 0);
+  MBH_TRY(e, t->Resize(shape));
+  t->SetScale(scale);
+  t->SetZeroPoint(zero_point);
+  if (host_data != nullptr && t->raw_size() > 0) {
+    MBH_TRY(e, e->runtime.Status(mb_memcpy_h2d(e->runtime.ctx(), t->mutable_memory<void>(), host_data,
+                                               static_cast<size_t>(t->raw_size()))));
+    MBH_TRY(e, e->runtime.Status(mb_stream_sync(e->runtime.ctx())));
+  }
+  return MaceStatus::MACE_SUCCESS;
+}
+
+static Tensor *FindTensor(mbh_engine *e, const char *name) {
+  if (e == nullptr || name == nullptr) return nullptr;
+  Tensor *t = e->workspace.GetTensor(name);
+  if (t == nullptr) e->last_error = std::string("no tensor named ") + name;
+  return t;
+}
+
+int mbh_set_tensor_quant(mbh_engine *e, const char *name, float scale, int32_t zero_point) {
+  Tensor *t = FindTensor(e, name);
+  if (t == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  t->SetScale(scale);
+  t->SetZeroPoint(zero_point);
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_tensor_rank(mbh_engine *e, const char *name, int *rank) {
+  Tensor *t = FindTensor(e, name);
+  if (t == nullptr || rank == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  *rank = static_cast<int>(t->dim_size());
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_tensor_shape(mbh_engine *e, const char *name, int64_t *dims, int max_rank) {
+  Tensor *t = FindTensor(e, name);
+  if (t == nullptr || dims == nullptr || max_rank < t->dim_size()) return MaceStatus::MACE_INVALID_ARGS;
+  for (index_t i = 0; i < t->dim_size(); ++i) dims[i] = t->dim(static_cast<unsigned>(i));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_tensor_quant(mbh_engine *e, const char *name, float *scale, int32_t *zero_point) {
+  Tensor *t = FindTensor(e, name);
+  if (t == nullptr || scale == nullptr || zero_point == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  *scale = t->scale();
+  *zero_point = t->zero_point();
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_tensor_read(mbh_engine *e, const char *name, void *host_out, size_t bytes) {
+  Tensor *t = FindTensor(e, name);
+  if (t == nullptr || (bytes != 0 && host_out == nullptr)) return MaceStatus::MACE_INVALID_ARGS;
+  if (bytes > static_cast<size_t>(t->raw_size()))
+    return Fail(e, MaceStatus::MACE_INVALID_ARGS, "read larger than the tensor");
+  MBH_TRY(e, e->runtime.Status(mb_memcpy_d2h(e->runtime.ctx(), host_out, t->memory<void>(), bytes)));
+  MBH_TRY(e, e->runtime.Status(mb_stream_sync(e->runtime.ctx())));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_tensor_write(mbh_engine *e, const char *name, const void *host_in, size_t bytes) {
+  Tensor *t = FindTensor(e, name);
+  if (t == nullptr || (bytes != 0 && host_in == nullptr)) return MaceStatus::MACE_INVALID_ARGS;
+  if (bytes > static_cast<size_t>(t->raw_size()))
+    return Fail(e, MaceStatus::MACE_INVALID_ARGS, "write larger than the tensor");
+  MBH_TRY(e, e->runtime.Status(mb_memcpy_h2d(e->runtime.ctx(), t->mutable_memory<void>(), host_in, bytes)));
+  MBH_TRY(e, e->runtime.Status(mb_stream_sync(e->runtime.ctx())));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_op_begin(mbh_engine *e, const char *type, const char *name) {
+  if (e == nullptr || type == nullptr || name == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  e->pending = OperatorDef();
+  e->pending.type = type;
+  e->pending.name = name;
+  e->building = true;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_op_input(mbh_engine *e, const char *tensor_name) {
+  if (e == nullptr || !e->building || tensor_name == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  e->pending.input.push_back(tensor_name);
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_op_output(mbh_engine *e, const char *tensor_name, int data_type, float scale, int32_t zero_point) {
+  if (e == nullptr || !e->building || tensor_name == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  e->pending.output.push_back(tensor_name);
+  if (data_type >= 0) {
+    e->pending.output_type.resize(e->pending.output.size(), DT_INVALID);
+    e->pending.output_type.back() = static_cast<DataType>(data_type);
+  }
+  if (scale > 0.f) {
+    e->pending.quantize_info.resize(e->pending.output.size());
+    e->pending.quantize_info.back().scale = scale;
+    e->pending.quantize_info.back().zero_point = zero_point;
+  }
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_op_arg_int(mbh_engine *e, const char *key, int value) {
+  if (e == nullptr || !e->building || key == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  e->pending.i[key] = value;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_op_arg_ints(mbh_engine *e, const char *key, int count, const int *values) {
+  if (e == nullptr || !e->building || key == nullptr || count < 0 || (count > 0 && values == nullptr))
+    return MaceStatus::MACE_INVALID_ARGS;
+  e->pending.ints[key] = std::vector<int>(values, values + count);
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_op_arg_float(mbh_engine *e, const char *key, float value) {
+  if (e == nullptr || !e->building || key == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  e->pending.f[key] = value;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_op_arg_str(mbh_engine *e, const char *key, const char *value) {
+  if (e == nullptr || !e->building || key == nullptr || value == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  e->pending.s[key] = value;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_op_end(mbh_engine *e) {
+  if (e == nullptr || !e->building) return MaceStatus::MACE_INVALID_ARGS;
+  e->building = false;
+  // an output_type entry left DT_INVALID means "use T"
+  for (auto &dt : e->pending.output_type) {
+    if (dt == DT_INVALID) {
+      auto it = e->pending.i.find("T");
+      dt = it == e->pending.i.end() ? DT_FLOAT : static_cast<DataType>(it->second);
+    }
+  }
+  MBH_TRY(e, e->net->AddOperator(e->pending));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_run(mbh_engine *e) {
+  if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  MBH_TRY(e, e->net->Run(nullptr));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_sync(mbh_engine *e) {
+  if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  MBH_TRY(e, e->runtime.Status(mb_stream_sync(e->runtime.ctx())));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_run_host(mbh_engine *e, const char *input_name, const void *host_in, size_t input_bytes,
+                 const char *output_name, void *host_out, size_t output_bytes) {
+  Tensor *in = FindTensor(e, input_name);
+  if (in == nullptr || host_in == nullptr || host_out == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  if (input_bytes != static_cast<size_t>(in->raw_size()))
+    return Fail(e, MaceStatus::MACE_INVALID_ARGS, "input size does not match the input tensor");
+  MBH_TRY(e, e->runtime.Status(mb_memcpy_h2d(e->runtime.ctx(), in->mutable_memory<void>(), host_in, input_bytes)));
+  MBH_TRY(e, e->net->Run(nullptr));
+  Tensor *out = FindTensor(e, output_name);
+  if (out == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  if (output_bytes != static_cast<size_t>(out->raw_size()))
+    return Fail(e, MaceStatus::MACE_INVALID_ARGS, "output size does not match the output tensor");
+  MBH_TRY(e, e->runtime.Status(mb_memcpy_d2h(e->runtime.ctx(), host_out, out->memory<void>(), output_bytes)));
+  MBH_TRY(e, e->runtime.Status(mb_stream_sync(e->runtime.ctx())));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_run_profiled(mbh_engine *e, float *ms_out, int max_ops, char *names_out, size_t names_len,
+                     int *op_count) {
+  if (e == nullptr || ms_out == nullptr || op_count == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  std::vector<CallStats> stats;
+  MBH_TRY(e, e->net->Run(&stats));
+  *op_count = static_cast<int>(stats.size());
+  std::string names;
+  for (size_t i = 0; i < stats.size(); ++i) {
+    if (static_cast<int>(i) < max_ops) ms_out[i] = stats[i].device_ms;
+    names += stats[i].type + ":" + stats[i].operator_name + "\n";
+  }
+  if (names_out != nullptr && names_len > 0) {
+    std::strncpy(names_out, names.c_str(), names_len - 1);
+    names_out[names_len - 1] = 0;
+  }
+  return MaceStatus::MACE_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,72 @@
+/*
+ * C entry points of the C++ host layer (libmace_b200_host.so), so that the
+ * operators, delegators and the sequential net can be driven from tests and
+ * benchmarks written in another language.  An engine owns one CudaRuntime, a
+ * workspace of named tensors, the delegator and operator registries and a
+ * SerialNet -- the roles of SerialEngine / CpuRefFlow / SerialNet in the
+ * reference (mace/libmace/engines/serial_engine.cc:57-113,
+ * mace/flows/cpu/cpu_ref_flow.cc:32-79, mace/core/net/serial_net.cc:93-228).
+ * Every function returns a MaceStatus::Code integer.
+ */
+#ifndef MACE_B200_HOST_CAPI_H_
+#define MACE_B200_HOST_CAPI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mbh_engine mbh_engine;
+
+int mbh_engine_create(int device, mbh_engine **engine);
+int mbh_engine_destroy(mbh_engine *engine);
+const char *mbh_last_error(const mbh_engine *engine);
+/* The mb_context of the engine's runtime (for event timing / launch counts). */
+void *mbh_engine_context(mbh_engine *engine);
+
+/* Creates (or replaces) a named tensor; data_type is a mace DataType value
+ * (1 float, 2 uint8, 4 int32).  host_data may be NULL (uninitialised). */
+int mbh_add_tensor(mbh_engine *engine, const char *name, int data_type, int rank,
+                   const int64_t *dims, const void *host_data, float scale,
+                   int32_t zero_point, int is_weight);
+int mbh_set_tensor_quant(mbh_engine *engine, const char *name, float scale, int32_t zero_point);
+int mbh_tensor_rank(mbh_engine *engine, const char *name, int *rank);
+int mbh_tensor_shape(mbh_engine *engine, const char *name, int64_t *dims, int max_rank);
+int mbh_tensor_quant(mbh_engine *engine, const char *name, float *scale, int32_t *zero_point);
+/* Synchronous copies between a tensor and host memory. */
+int mbh_tensor_read(mbh_engine *engine, const char *name, void *host_out, size_t bytes);
+int mbh_tensor_write(mbh_engine *engine, const char *name, const void *host_in, size_t bytes);
+
+/* Operator construction, the fields of an OperatorDef (mace/proto/mace.proto:61-95). */
+int mbh_op_begin(mbh_engine *engine, const char *type, const char *name);
+int mbh_op_input(mbh_engine *engine, const char *tensor_name);
+/* data_type < 0: take it from the op's "T" argument; scale <= 0: no quantize_info. */
+int mbh_op_output(mbh_engine *engine, const char *tensor_name, int data_type, float scale,
+                  int32_t zero_point);
+int mbh_op_arg_int(mbh_engine *engine, const char *key, int value);
+int mbh_op_arg_ints(mbh_engine *engine, const char *key, int count, const int *values);
+int mbh_op_arg_float(mbh_engine *engine, const char *key, float value);
+int mbh_op_arg_str(mbh_engine *engine, const char *key, const char *value);
+int mbh_op_end(mbh_engine *engine);
+
+/* Runs all operators once (asynchronously on the engine's stream). */
+int mbh_run(mbh_engine *engine);
+int mbh_sync(mbh_engine *engine);
+/* Host-buffer run, the shape of MaceEngine::Run (mace/libmace/mace_engine.cc:203-212):
+ * copies input_bytes from pinned or pageable host memory into the input
+ * tensor, runs the net, copies the output tensor back and waits. */
+int mbh_run_host(mbh_engine *engine, const char *input_name, const void *host_in,
+                 size_t input_bytes, const char *output_name, void *host_out,
+                 size_t output_bytes);
+/* Per-operator device times of one run; returns the operator count.  names_out
+ * receives "type:name" strings separated by newlines. */
+int mbh_run_profiled(mbh_engine *engine, float *ms_out, int max_ops, char *names_out,
+                     size_t names_len, int *op_count);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MACE_B200_HOST_CAPI_H_ */

@@ -1,0 +1,376 @@
+#include "ops.h"
+
+#include <numeric>
+
+namespace mace {
+
+// ---- Operation ---------------------------------------------------------------
+
+Operation::Operation(OpConstructContext *context) : operator_def_(context->operator_def()) {}
+
+template <>
+int Operation::GetOptionalArg<int>(const std::string &name, const int &default_value) const {
+  auto it = operator_def_->i.find(name);
+  return it == operator_def_->i.end() ? default_value : it->second;
+}
+
+template <>
+bool Operation::GetOptionalArg<bool>(const std::string &name, const bool &default_value) const {
+  auto it = operator_def_->i.find(name);
+  return it == operator_def_->i.end() ? default_value : it->second != 0;
+}
+
+template <>
+float Operation::GetOptionalArg<float>(const std::string &name, const float &default_value) const {
+  auto it = operator_def_->f.find(name);
+  return it == operator_def_->f.end() ? default_value : it->second;
+}
+
+template <>
+std::string Operation::GetOptionalArg<std::string>(const std::string &name,
+                                                   const std::string &default_value) const {
+  auto it = operator_def_->s.find(name);
+  return it == operator_def_->s.end() ? default_value : it->second;
+}
+
+template <>
+std::vector<int> Operation::GetRepeatedArgs<int>(const std::string &name,
+                                                 const std::vector<int> &default_value) const {
+  auto it = operator_def_->ints.find(name);
+  return it == operator_def_->ints.end() ? default_value : it->second;
+}
+
+MaceStatus Operation::Init(OpConstructContext *context) {
+  Workspace *ws = context->workspace();
+  for (const std::string &name : operator_def_->input) {
+    const Tensor *t = ws->GetTensor(name);
+    if (t == nullptr)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS,
+                        "op " + operator_def_->name + ": Input does not exist in workspace: " + name);
+    inputs_.push_back(t);
+  }
+  for (size_t i = 0; i < operator_def_->output.size(); ++i) {
+    const std::string &name = operator_def_->output[i];
+    Tensor *t = ws->GetTensor(name);
+    if (t == nullptr) {
+      DataType dt = static_cast<DataType>(GetOptionalArg<int>("T", static_cast<int>(DT_FLOAT)));
+      if (i < operator_def_->output_type.size()) dt = operator_def_->output_type[i];
+      t = ws->CreateTensor(name, context->runtime(), dt);
+    }
+    // mace/core/workspace.cc:204-222: activation ranges come from quantize_info
+    if (i < operator_def_->quantize_info.size()) {
+      t->SetScale(operator_def_->quantize_info[i].scale);
+      t->SetZeroPoint(operator_def_->quantize_info[i].zero_point);
+    }
+    outputs_.push_back(t);
+  }
+  return MaceStatus::MACE_SUCCESS;
+}
+
+// ---- registry ------------------------------------------------------------------
+
+static std::string OpKey(const std::string &type, RuntimeType rt, DataType dt) {
+  return type + "_" + std::to_string(static_cast<int>(rt)) + "_" + std::to_string(static_cast<int>(dt));
+}
+
+MaceStatus OpRegistry::Register(const std::string &type, RuntimeType rt, DataType dt, OpCreator creator) {
+  registry_[OpKey(type, rt, dt)] = std::move(creator);
+  return MaceStatus::MACE_SUCCESS;
+}
+
+std::unique_ptr<Operation> OpRegistry::CreateOperation(OpConstructContext *context, RuntimeType rt,
+                                                       DataType dt, MaceStatus *status) const {
+  auto it = registry_.find(OpKey(context->operator_def()->type, rt, dt));
+  if (it == registry_.end()) {
+    *status = MaceStatus(MaceStatus::MACE_UNSUPPORTED,
+                         "no operator registered for " + context->operator_def()->type);
+    return nullptr;
+  }
+  *status = MaceStatus::MACE_SUCCESS;
+  return it->second(context);
+}
+
+namespace ops {
+
+// ---- ConvPool2dOpBase (mace/ops/conv_pool_2d_base.h:25-46) -------------------------
+
+class ConvPool2dOpBase : public Operation {
+ public:
+  explicit ConvPool2dOpBase(OpConstructContext *context)
+      : Operation(context),
+        strides_(GetRepeatedArgs<int>("strides")),
+        padding_type_(static_cast<Padding>(GetOptionalArg<int>("padding", static_cast<int>(SAME)))),
+        paddings_(GetRepeatedArgs<int>("padding_values")),
+        dilations_(GetRepeatedArgs<int>("dilations", {1, 1})) {}
+
+ protected:
+  std::vector<int> strides_;
+  Padding padding_type_;
+  std::vector<int> paddings_;
+  std::vector<int> dilations_;
+};
+
+template <RuntimeType D, class T> class Conv2dOp;
+template <RuntimeType D, class T> class DepthwiseConv2dOp;
+template <RuntimeType D, class T> class MatMulOp;
+template <RuntimeType D, class T> class FullyConnectedOp;
+template <RuntimeType D, class T> class PoolingOp;
+
+template <>
+class Conv2dOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
+ public:
+  explicit Conv2dOp(OpConstructContext *context)
+      : ConvPool2dOpBase(context), workspace_(context->workspace()) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0), *filter = Input(1);
+    const Tensor *bias = InputSize() >= 3 ? Input(2) : nullptr;
+    if (strides_.size() != 2) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "strides must have 2 values");
+    if (conv2d_delegator_ == nullptr) {
+      // one CUDA implementation serves every filter shape (tag "general")
+      conv2d_delegator_ = delegator::Conv2d::Create(
+          workspace_, MACE_DELEGATOR_KEY(Conv2d, RuntimeType::RT_CUDA, uint8_t, ImplType::CUDA),
+          delegator::Conv2dParam(strides_, dilations_, paddings_, padding_type_));
+    }
+    conv2d_delegator_->SetBias(bias);
+    return conv2d_delegator_->Compute(context, input, filter, Output(0));
+  }
+
+ private:
+  Workspace *workspace_;
+  std::unique_ptr<delegator::Conv2d> conv2d_delegator_;
+};
+
+template <>
+class DepthwiseConv2dOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
+ public:
+  explicit DepthwiseConv2dOp(OpConstructContext *context)
+      : ConvPool2dOpBase(context), workspace_(context->workspace()) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0), *filter = Input(1);
+    const Tensor *bias = InputSize() >= 3 ? Input(2) : nullptr;
+    if (strides_.size() != 2) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "strides must have 2 values");
+    if (delegator_ == nullptr) {
+      delegator_ = delegator::DepthwiseConv2d::Create(
+          workspace_, MACE_DELEGATOR_KEY(DepthwiseConv2d, RuntimeType::RT_CUDA, uint8_t, ImplType::CUDA),
+          delegator::DepthwiseConv2dParam(strides_, dilations_, paddings_, padding_type_));
+    }
+    delegator_->SetBias(bias);
+    return delegator_->Compute(context, input, filter, Output(0));
+  }
+
+ private:
+  Workspace *workspace_;
+  std::unique_ptr<delegator::DepthwiseConv2d> delegator_;
+};
+
+template <>
+class MatMulOp<RuntimeType::RT_CUDA, uint8_t> : public Operation {
+ public:
+  explicit MatMulOp(OpConstructContext *context)
+      : Operation(context),
+        transpose_a_(GetOptionalArg<bool>("transpose_a", false)),
+        transpose_b_(GetOptionalArg<bool>("transpose_b", false)),
+        gemm_(delegator::Gemm::Create(
+            context->workspace(),
+            MACE_DELEGATOR_KEY(Gemm, RuntimeType::RT_CUDA, uint8_t, ImplType::CUDA),
+            delegator::GemmParam())) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *lhs = Input(0), *rhs = Input(1);
+    Tensor *C = Output(0);
+    const index_t lhs_rank = lhs->dim_size(), rhs_rank = rhs->dim_size();
+    // Validate(), mace/ops/matmul.cc:55-83
+    if (lhs_rank < 2 || rhs_rank < 2)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "rank should be greater than or equal to 2");
+    if (lhs_rank == rhs_rank) {
+      for (index_t i = 0; i < lhs_rank - 2; ++i)
+        if (lhs->dim(i) != rhs->dim(i))
+          return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "batch dimensions are not equal");
+    } else if (lhs_rank != 2 && rhs_rank != 2) {
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS,
+                        "Either lhs or rhs matrix should has rank 2 for non-batched matrix multiplication");
+    }
+    const index_t lhs_rows = lhs->dim(lhs_rank - 2), lhs_cols = lhs->dim(lhs_rank - 1);
+    const index_t rhs_rows = rhs->dim(rhs_rank - 2), rhs_cols = rhs->dim(rhs_rank - 1);
+    const index_t rows = transpose_a_ ? lhs_cols : lhs_rows;
+    const index_t cols = transpose_b_ ? rhs_rows : rhs_cols;
+    const index_t depth = transpose_a_ ? lhs_rows : lhs_cols;
+    const index_t rhs_depth = transpose_b_ ? rhs_cols : rhs_rows;
+    if (depth != rhs_depth)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "the number of A's column must be equal to B's row");
+    const index_t lhs_batch = std::accumulate(lhs->shape().begin(), lhs->shape().end() - 2,
+                                              static_cast<index_t>(1), std::multiplies<index_t>());
+    const index_t rhs_batch = std::accumulate(rhs->shape().begin(), rhs->shape().end() - 2,
+                                              static_cast<index_t>(1), std::multiplies<index_t>());
+    std::vector<index_t> output_shape;
+    index_t batch = 1;
+    if (lhs_rank >= rhs_rank) {
+      output_shape = lhs->shape();
+      output_shape[lhs_rank - 2] = rows;
+      output_shape[lhs_rank - 1] = cols;
+      batch = lhs_batch;
+    } else {
+      output_shape = rhs->shape();
+      output_shape[rhs_rank - 2] = rows;
+      output_shape[rhs_rank - 1] = cols;
+      batch = rhs_batch;
+    }
+    const bool lhs_batched = !(lhs_rank < rhs_rank), rhs_batched = !(rhs_rank < lhs_rank);
+    MACE_RETURN_IF_ERROR(C->Resize(output_shape));
+    // The quantized MatMul reads no bias input (MakeNoBias, matmul.cc:280).
+    return gemm_->Compute(context, lhs, rhs, batch, rows, cols, depth,
+                          transpose_a_ ? ColMajor : RowMajor, transpose_b_ ? ColMajor : RowMajor,
+                          RowMajor, lhs_batched, rhs_batched, C);
+  }
+
+ private:
+  bool transpose_a_, transpose_b_;
+  std::unique_ptr<delegator::Gemm> gemm_;
+};
+
+template <>
+class FullyConnectedOp<RuntimeType::RT_CUDA, uint8_t> : public Operation {
+ public:
+  explicit FullyConnectedOp(OpConstructContext *context)
+      : Operation(context),
+        gemv_(delegator::Gemv::Create(
+            context->workspace(),
+            MACE_DELEGATOR_KEY(Gemv, RuntimeType::RT_CUDA, uint8_t, ImplType::CUDA),
+            DelegatorParam())) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0), *weight = Input(1);
+    const Tensor *bias = InputSize() >= 3 ? Input(2) : nullptr;
+    Tensor *output = Output(0);
+    if (!(input->dim(1) == weight->dim(1) && input->dim(2) == weight->dim(2) &&
+          input->dim(3) == weight->dim(3)))
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "The shape of Input and Weight don't match.");
+    if (bias != nullptr && weight->dim(0) != bias->dim(0))
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "The shape of Weight and Bias don't match.");
+    MACE_RETURN_IF_ERROR(output->Resize({input->dim(0), 1, 1, weight->dim(0)}));
+    const index_t input_size = weight->dim(1) * weight->dim(2) * weight->dim(3);
+    return gemv_->Compute(context, weight, input, bias, output->dim(0), weight->dim(0), input_size,
+                          false, true, output);
+  }
+
+ private:
+  std::unique_ptr<delegator::Gemv> gemv_;
+};
+
+template <>
+class PoolingOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
+ public:
+  explicit PoolingOp(OpConstructContext *context)
+      : ConvPool2dOpBase(context),
+        kernels_(GetRepeatedArgs<int>("kernels")),
+        pooling_type_(static_cast<PoolingType>(GetOptionalArg<int>("pooling_type", static_cast<int>(AVG)))),
+        round_type_(static_cast<RoundType>(GetOptionalArg<int>("round_mode", static_cast<int>(CEIL)))) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0);
+    Tensor *output = Output(0);
+    if (dilations_[0] != 1 || dilations_[1] != 1)
+      return MaceStatus(MaceStatus::MACE_UNSUPPORTED, "Quantized pooling does not support dilation > 1 yet.");
+    if (pooling_type_ != AVG)
+      return MaceStatus(MaceStatus::MACE_UNSUPPORTED, "only AVG pooling is built for the CUDA runtime");
+    if (kernels_.size() != 2 || strides_.size() != 2)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "kernels and strides must have 2 values");
+    // Use the same scale and zero point with input and output (pooling.cc:651-653).
+    output->SetScale(input->scale());
+    output->SetZeroPoint(input->zero_point());
+    index_t out_h = 0, out_w = 0;
+    std::vector<int> paddings(2);
+    if (paddings_.empty()) {
+      MACE_RETURN_IF_ERROR(CalcPaddingAndOutputSize(input->dim(1), input->dim(2), kernels_[0], kernels_[1],
+                                                    dilations_.data(), strides_.data(), padding_type_,
+                                                    &out_h, &out_w, paddings.data()));
+    } else {
+      paddings = paddings_;
+      CalcOutputSize(input->dim(1), input->dim(2), kernels_[0], kernels_[1], paddings.data(),
+                     dilations_.data(), strides_.data(), round_type_, &out_h, &out_w);
+    }
+    MACE_RETURN_IF_ERROR(output->Resize({input->dim(0), out_h, out_w, input->dim(3)}));
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    return rt->Status(mb_avgpool_u8_nhwc(rt->ctx(), input->memory<uint8_t>(),
+                                         output->mutable_memory<uint8_t>(), input->dim(0), input->dim(1),
+                                         input->dim(2), input->dim(3), kernels_[0], kernels_[1],
+                                         strides_[0], strides_[1], paddings[0] / 2, paddings[1] / 2,
+                                         out_h, out_w));
+  }
+
+ private:
+  std::vector<int> kernels_;
+  PoolingType pooling_type_;
+  RoundType round_type_;
+};
+
+#define MACE_REGISTER_OP(registry, op_type, class_name, runtime, dt)                             \
+  registry->Register(op_type, runtime, DataTypeToEnum<dt>::value,                                \
+                     [](OpConstructContext *context) -> std::unique_ptr<Operation> {             \
+                       return std::unique_ptr<Operation>(new class_name<runtime, dt>(context));  \
+                     })
+
+void RegisterAllCudaOps(OpRegistry *registry) {
+  MACE_REGISTER_OP(registry, "Conv2D", Conv2dOp, RuntimeType::RT_CUDA, uint8_t);
+  MACE_REGISTER_OP(registry, "DepthwiseConv2d", DepthwiseConv2dOp, RuntimeType::RT_CUDA, uint8_t);
+  MACE_REGISTER_OP(registry, "MatMul", MatMulOp, RuntimeType::RT_CUDA, uint8_t);
+  MACE_REGISTER_OP(registry, "FullyConnected", FullyConnectedOp, RuntimeType::RT_CUDA, uint8_t);
+  MACE_REGISTER_OP(registry, "Pooling", PoolingOp, RuntimeType::RT_CUDA, uint8_t);
+}
+
+}  // namespace ops
+
+// ---- SerialNet -------------------------------------------------------------------
+
+MaceStatus SerialNet::AddOperator(const OperatorDef &def) {
+  defs_.push_back(std::make_unique<OperatorDef>(def));
+  const OperatorDef *d = defs_.back().get();
+  OpConstructContext cc(ws_, runtime_, d);
+  auto it = d->i.find("T");
+  const DataType dt = it == d->i.end() ? DT_FLOAT : static_cast<DataType>(it->second);
+  MaceStatus st;
+  std::unique_ptr<Operation> op = op_registry_->CreateOperation(&cc, RuntimeType::RT_CUDA, dt, &st);
+  if (op == nullptr) {
+    defs_.pop_back();
+    return st;
+  }
+  st = op->Init(&cc);
+  if (st != MaceStatus::MACE_SUCCESS) {
+    defs_.pop_back();
+    return st;
+  }
+  operators_.push_back(std::move(op));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+MaceStatus SerialNet::Run(std::vector<CallStats> *run_metadata) {
+  OpContext context(runtime_);
+  std::vector<void *> events;
+  if (run_metadata != nullptr) {
+    events.resize(operators_.size() + 1, nullptr);
+    for (auto &e : events) MACE_RETURN_IF_ERROR(runtime_->Status(mb_event_create(runtime_->ctx(), &e)));
+    MACE_RETURN_IF_ERROR(runtime_->Status(mb_event_record(runtime_->ctx(), events[0])));
+  }
+  for (size_t i = 0; i < operators_.size(); ++i) {
+    MACE_RETURN_IF_ERROR(operators_[i]->Run(&context));
+    if (run_metadata != nullptr)
+      MACE_RETURN_IF_ERROR(runtime_->Status(mb_event_record(runtime_->ctx(), events[i + 1])));
+  }
+  if (run_metadata != nullptr) {
+    run_metadata->clear();
+    for (size_t i = 0; i < operators_.size(); ++i) {
+      CallStats cs;
+      cs.operator_name = operators_[i]->debug_def().name;
+      cs.type = operators_[i]->debug_def().type;
+      MACE_RETURN_IF_ERROR(runtime_->Status(
+          mb_event_elapsed_ms(runtime_->ctx(), events[i], events[i + 1], &cs.device_ms)));
+      run_metadata->push_back(cs);
+    }
+    for (auto &e : events) mb_event_destroy(runtime_->ctx(), e);
+  }
+  return MaceStatus::MACE_SUCCESS;
+}
+
+}  // namespace mace

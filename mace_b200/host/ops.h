@@ -1,0 +1,130 @@
+// Operators of the hot path for RuntimeType::RT_CUDA / uint8, with the argument
+// names and Run() behaviour of MACE's CPU operators:
+//   Conv2dOp            mace/ops/conv_2d.cc:190-318     (inputs INPUT, FILTER, BIAS)
+//   DepthwiseConv2dOp   mace/ops/depthwise_conv2d.cc:146-250
+//   MatMulOp            mace/ops/matmul.cc:397-482      (args transpose_a, transpose_b)
+//   FullyConnectedOp    mace/ops/fully_connected.cc:130-179
+//   PoolingOp (AVG)     mace/ops/pooling.cc:638-871     (args kernels, pooling_type, round_mode)
+// plus the sequential executor (SerialNet::Run, mace/core/net/serial_net.cc:93-228)
+// and a small OperatorDef stand-in (mace/proto/mace.proto:61-95: type, inputs,
+// outputs, args, output_type, quantize_info).
+#ifndef MACE_B200_HOST_OPS_H_
+#define MACE_B200_HOST_OPS_H_
+
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "core.h"
+#include "delegators.h"
+
+namespace mace {
+
+struct QuantizeActivationInfo {  // mace.proto:56-59
+  float scale = 0.f;
+  int32_t zero_point = 0;
+};
+
+struct OperatorDef {
+  std::string type;
+  std::string name;
+  std::vector<std::string> input;
+  std::vector<std::string> output;
+  std::map<std::string, std::vector<int>> ints;   // "strides", "dilations", "padding_values", "kernels"
+  std::map<std::string, int> i;                   // "padding", "transpose_a", "T", "pooling_type", ...
+  std::map<std::string, float> f;                 // "max_limit", ...
+  std::map<std::string, std::string> s;           // "activation"
+  std::vector<DataType> output_type;
+  std::vector<QuantizeActivationInfo> quantize_info;
+};
+
+struct CallStats {  // include/mace/public/mace.h:177-180, filled from device events
+  std::string operator_name;
+  std::string type;
+  float device_ms = 0.f;
+};
+
+class OpConstructContext {
+ public:
+  OpConstructContext(Workspace *ws, Runtime *rt, const OperatorDef *def)
+      : workspace_(ws), runtime_(rt), operator_def_(def) {}
+  Workspace *workspace() const { return workspace_; }
+  Runtime *runtime() const { return runtime_; }
+  const OperatorDef *operator_def() const { return operator_def_; }
+
+ private:
+  Workspace *workspace_;
+  Runtime *runtime_;
+  const OperatorDef *operator_def_;
+};
+
+class Operation {
+ public:
+  explicit Operation(OpConstructContext *context);
+  virtual ~Operation() = default;
+
+  template <typename T> T GetOptionalArg(const std::string &name, const T &default_value) const;
+  template <typename T>
+  std::vector<T> GetRepeatedArgs(const std::string &name, const std::vector<T> &default_value = {}) const;
+
+  // Binds input and output tensors by name (Operation::Init, mace/core/ops/operator.cc:26-85):
+  // outputs are created in the workspace with the output type and the
+  // activation range of quantize_info.
+  MaceStatus Init(OpConstructContext *context);
+  virtual MaceStatus Run(OpContext *context) = 0;
+
+  const Tensor *Input(unsigned int idx) const { return inputs_[idx]; }
+  Tensor *Output(unsigned int idx) { return outputs_[idx]; }
+  int InputSize() const { return static_cast<int>(inputs_.size()); }
+  const OperatorDef &debug_def() const { return *operator_def_; }
+
+ protected:
+  const OperatorDef *operator_def_;
+  std::vector<const Tensor *> inputs_;
+  std::vector<Tensor *> outputs_;
+};
+
+typedef std::function<std::unique_ptr<Operation>(OpConstructContext *)> OpCreator;
+
+// Keyed by (type, runtime, data type) like MACE_REGISTER_OP
+// (mace/core/registry/ops_registry.h:73-77).
+class OpRegistry {
+ public:
+  MaceStatus Register(const std::string &type, RuntimeType rt, DataType dt, OpCreator creator);
+  std::unique_ptr<Operation> CreateOperation(OpConstructContext *context, RuntimeType rt, DataType dt,
+                                             MaceStatus *status) const;
+
+ private:
+  std::map<std::string, OpCreator> registry_;
+};
+
+namespace ops {
+// Registers Conv2D, DepthwiseConv2d, MatMul, FullyConnected and Pooling for
+// (RT_CUDA, uint8_t).
+void RegisterAllCudaOps(OpRegistry *registry);
+}  // namespace ops
+
+// Runs a list of operators in order on one CudaRuntime.
+class SerialNet {
+ public:
+  SerialNet(const OpRegistry *op_registry, Workspace *ws, CudaRuntime *runtime)
+      : op_registry_(op_registry), ws_(ws), runtime_(runtime) {}
+  // The OperatorDef is copied; its tensors must exist (inputs) or are created (outputs).
+  MaceStatus AddOperator(const OperatorDef &def);
+  // run_metadata may be null; when given, each operator is bracketed by device
+  // events (mace/core/net/serial_net.cc:122-180).
+  MaceStatus Run(std::vector<CallStats> *run_metadata = nullptr);
+  size_t size() const { return operators_.size(); }
+
+ private:
+  const OpRegistry *op_registry_;
+  Workspace *ws_;
+  CudaRuntime *runtime_;
+  std::vector<std::unique_ptr<OperatorDef>> defs_;
+  std::vector<std::unique_ptr<Operation>> operators_;
+};
+
+}  // namespace mace
+
+#endif  // MACE_B200_HOST_OPS_H_

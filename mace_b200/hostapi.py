@@ -1,0 +1,175 @@
+"""ctypes binding of ``libmace_b200_host.so``: the C entry points of the C++ host layer
+(operators, delegators, sequential net).  Used by the tests and the benchmark to drive the
+host layer the way the reference's OpsTestNet / OpDefBuilder drive MACE's operators
+(test/ccutils/mace/ops/ops_test_util.h:122-316)."""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import capi
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "libmace_b200_host.so")
+
+DT_FLOAT, DT_UINT8, DT_INT32 = 1, 2, 4
+VALID, SAME, FULL = 0, 1, 2
+AVG, MAX = 1, 2
+_NP = {DT_FLOAT: np.float32, DT_UINT8: np.uint8, DT_INT32: np.int32}
+_DT = {np.dtype(np.float32): DT_FLOAT, np.dtype(np.uint8): DT_UINT8, np.dtype(np.int32): DT_INT32}
+
+_vp, _int, _i32, _f32, _sz, _cp = C.c_void_p, C.c_int, C.c_int32, C.c_float, C.c_size_t, C.c_char_p
+_PROTOS = {
+    "mbh_engine_create": [_int, C.POINTER(_vp)],
+    "mbh_engine_destroy": [_vp],
+    "mbh_engine_context": [_vp],
+    "mbh_add_tensor": [_vp, _cp, _int, _int, C.POINTER(C.c_int64), _vp, _f32, _i32, _int],
+    "mbh_set_tensor_quant": [_vp, _cp, _f32, _i32],
+    "mbh_tensor_rank": [_vp, _cp, C.POINTER(_int)],
+    "mbh_tensor_shape": [_vp, _cp, C.POINTER(C.c_int64), _int],
+    "mbh_tensor_quant": [_vp, _cp, C.POINTER(_f32), C.POINTER(_i32)],
+    "mbh_tensor_read": [_vp, _cp, _vp, _sz],
+    "mbh_tensor_write": [_vp, _cp, _vp, _sz],
+    "mbh_op_begin": [_vp, _cp, _cp],
+    "mbh_op_input": [_vp, _cp],
+    "mbh_op_output": [_vp, _cp, _int, _f32, _i32],
+    "mbh_op_arg_int": [_vp, _cp, _int],
+    "mbh_op_arg_ints": [_vp, _cp, _int, C.POINTER(_int)],
+    "mbh_op_arg_float": [_vp, _cp, _f32],
+    "mbh_op_arg_str": [_vp, _cp, _cp],
+    "mbh_op_end": [_vp],
+    "mbh_run": [_vp],
+    "mbh_sync": [_vp],
+    "mbh_run_host": [_vp, _cp, _vp, _sz, _cp, _vp, _sz],
+    "mbh_run_profiled": [_vp, C.POINTER(_f32), _int, C.c_char_p, _sz, C.POINTER(_int)],
+}
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        capi.lib()  # the device library must load first (and must exist)
+        if not os.path.exists(_LIB):
+            raise ImportError("libmace_b200_host.so is missing: build with make -C mace_b200/host")
+        _lib = C.CDLL(_LIB)
+        for name, args in _PROTOS.items():
+            fn = getattr(_lib, name)
+            fn.argtypes = args
+            fn.restype = _int
+        _lib.mbh_last_error.restype = _cp
+        _lib.mbh_last_error.argtypes = [_vp]
+        _lib.mbh_engine_context.restype = _vp
+    return _lib
+
+
+class HostEngine:
+    """One engine: CudaRuntime + workspace + SerialNet on one GPU."""
+
+    def __init__(self, device=0):
+        self.h = _vp()
+        st = lib().mbh_engine_create(int(device), C.byref(self.h))
+        if st != 0:
+            raise capi.MaceB200Error(st, "mbh_engine_create failed (no sm_100a CUDA device?)")
+
+    def _check(self, st):
+        if st != 0:
+            raise capi.MaceB200Error(st, lib().mbh_last_error(self.h).decode())
+
+    def close(self):
+        if self.h:
+            lib().mbh_engine_destroy(self.h)
+            self.h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    @property
+    def context(self):
+        """The raw mb_context pointer of the engine's runtime."""
+        return lib().mbh_engine_context(self.h)
+
+    # -- tensors ------------------------------------------------------------------
+    def add_tensor(self, name, array=None, shape=None, dtype=None, scale=0.0, zero_point=0,
+                   is_weight=False):
+        if array is not None:
+            array = np.ascontiguousarray(array)
+            shape, dt = array.shape, _DT[array.dtype]
+            ptr = array.ctypes.data
+        else:
+            dt, ptr = dtype, None
+        dims = (C.c_int64 * len(shape))(*shape)
+        self._check(lib().mbh_add_tensor(self.h, name.encode(), dt, len(shape), dims, ptr,
+                                         float(scale), int(zero_point), int(is_weight)))
+
+    def set_quant(self, name, scale, zero_point):
+        self._check(lib().mbh_set_tensor_quant(self.h, name.encode(), float(scale), int(zero_point)))
+
+    def shape(self, name):
+        r = _int()
+        self._check(lib().mbh_tensor_rank(self.h, name.encode(), C.byref(r)))
+        dims = (C.c_int64 * max(r.value, 1))()
+        self._check(lib().mbh_tensor_shape(self.h, name.encode(), dims, r.value))
+        return tuple(dims[i] for i in range(r.value))
+
+    def quant(self, name):
+        s, z = _f32(), _i32()
+        self._check(lib().mbh_tensor_quant(self.h, name.encode(), C.byref(s), C.byref(z)))
+        return np.float32(s.value), int(z.value)
+
+    def read(self, name, dtype):
+        out = np.empty(self.shape(name), dtype)
+        self._check(lib().mbh_tensor_read(self.h, name.encode(), out.ctypes.data, out.nbytes))
+        return out
+
+    def write(self, name, array):
+        array = np.ascontiguousarray(array)
+        self._check(lib().mbh_tensor_write(self.h, name.encode(), array.ctypes.data, array.nbytes))
+
+    # -- operators ----------------------------------------------------------------
+    def op(self, type_, name, inputs, outputs, T=DT_UINT8, out_dtype=None, out_quant=None,
+           ints=None, i=None, f=None, s=None):
+        """Adds one operator; the keyword groups are the typed args of an OperatorDef."""
+        L = lib()
+        self._check(L.mbh_op_begin(self.h, type_.encode(), name.encode()))
+        for t in inputs:
+            self._check(L.mbh_op_input(self.h, t.encode()))
+        for k, t in enumerate(outputs):
+            q = out_quant[k] if out_quant else (0.0, 0)
+            self._check(L.mbh_op_output(self.h, t.encode(), -1 if out_dtype is None else out_dtype,
+                                        float(q[0]), int(q[1])))
+        self._check(L.mbh_op_arg_int(self.h, b"T", int(T)))
+        for k, v in (i or {}).items():
+            self._check(L.mbh_op_arg_int(self.h, k.encode(), int(v)))
+        for k, v in (ints or {}).items():
+            arr = (C.c_int * len(v))(*v)
+            self._check(L.mbh_op_arg_ints(self.h, k.encode(), len(v), arr))
+        for k, v in (f or {}).items():
+            self._check(L.mbh_op_arg_float(self.h, k.encode(), float(v)))
+        for k, v in (s or {}).items():
+            self._check(L.mbh_op_arg_str(self.h, k.encode(), v.encode()))
+        self._check(L.mbh_op_end(self.h))
+
+    def run(self, sync=True):
+        self._check(lib().mbh_run(self.h))
+        if sync:
+            self.sync()
+
+    def sync(self):
+        self._check(lib().mbh_sync(self.h))
+
+    def run_host(self, input_name, host_in, output_name, host_out):
+        self._check(lib().mbh_run_host(self.h, input_name.encode(), host_in.ctypes.data,
+                                       host_in.nbytes, output_name.encode(),
+                                       host_out.ctypes.data, host_out.nbytes))
+
+    def run_profiled(self, max_ops=256):
+        ms = (C.c_float * max_ops)()
+        names = C.create_string_buffer(64 * max_ops)
+        n = _int()
+        self._check(lib().mbh_run_profiled(self.h, ms, max_ops, names, len(names), C.byref(n)))
+        labels = names.value.decode().strip().split("\n")
+        return [(labels[k], float(ms[k])) for k in range(min(n.value, max_ops))]

@@ -1,0 +1,172 @@
+"""The C++ host layer (operators -> delegators -> C ABI) on the GPU, driven the way the
+reference's unit tests drive MACE's operators (OpsTestNet + OpDefBuilder): add named input
+tensors with scale / zero point, define the operator with its args, set the output tensor's
+scale / zero point, run, compare.  Expected values: the reference's known-answer literals
+and the CPU oracle, bit-exact."""
+import numpy as np
+import pytest
+
+from helpers import gemm_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def net():
+    from mace_b200 import hostapi
+    e = hostapi.HostEngine(0)
+    yield e
+    e.close()
+
+
+def test_conv2d_quant_simple3x3(net, kats):
+    """TestQuantSimple3x3, test/ccunit/mace/ops/conv_2d_test.cc:1240-1275."""
+    from mace_b200 import hostapi as H
+    k = kats["conv2d_u8_3x3"]
+    net.add_tensor("Filter", np.array(k["filter"], np.uint8).reshape(k["filter_ohwi_shape"]),
+                   scale=k["filter_scale"], zero_point=k["filter_zp"], is_weight=True)
+    net.add_tensor("Input", np.array(k["input"], np.uint8).reshape(k["input_nhwc_shape"]),
+                   scale=k["input_scale"], zero_point=k["input_zp"])
+    net.add_tensor("Bias", np.array(k["bias"], np.int32), scale=k["bias_scale"], zero_point=0,
+                   is_weight=True)
+    net.op("Conv2D", "Conv2dTest", ["Input", "Filter", "Bias"], ["Output"],
+           ints={"strides": [1, 1], "dilations": [1, 1]}, i={"padding": H.VALID})
+    net.set_quant("Output", k["output_scale"], k["output_zp"])
+    net.run()
+    assert net.shape("Output") == (1, 1, 1, 1)
+    assert net.read("Output", np.uint8).ravel().tolist() == k["expected"]
+
+
+def test_depthwise_quant_simple_valid(net, kats):
+    """QuantSimpleValidTest, test/ccunit/mace/ops/depthwise_conv2d_test.cc:333-372."""
+    from mace_b200 import hostapi as H
+    k = kats["dwconv_u8_3x3"]
+    net.add_tensor("Input", np.array(k["input"], np.uint8).reshape(k["input_nhwc_shape"]),
+                   scale=k["input_scale"], zero_point=k["input_zp"])
+    net.add_tensor("Filter", np.array(k["filter"], np.uint8).reshape(k["filter_hwim_shape"]),
+                   scale=k["filter_scale"], zero_point=k["filter_zp"], is_weight=True)
+    net.add_tensor("Bias", np.array(k["bias"], np.int32), scale=k["bias_scale"], zero_point=0,
+                   is_weight=True)
+    net.op("DepthwiseConv2d", "DepthwiseConv2DTest", ["Input", "Filter", "Bias"], ["Output"],
+           ints={"strides": [1, 1], "dilations": [1, 1]}, i={"padding": H.VALID})
+    net.set_quant("Output", k["output_scale"], k["output_zp"])
+    net.run()
+    assert net.read("Output", np.uint8).ravel().tolist() == k["expected"]
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("shape", [((1,), 64, 128, 32), ((2, 3), 31, 61, 67), ((16,), 32, 64, 96)])
+def test_matmul_quant(net, orc, ta, tb, shape):
+    """Quantized MatMul over the transpose / batch combinations of matmul_test.cc:400-426;
+    uint8 and int32 outputs, bit-exact against the oracle."""
+    from mace_b200 import hostapi as H
+    batch_dims, M, K, N = shape
+    batch = int(np.prod(batch_dims))
+    case = gemm_case(orc, 31, batch, M, N, K, a_col_major=ta, b_col_major=tb)
+    a_shape = tuple(batch_dims) + ((K, M) if ta else (M, K))
+    b_shape = tuple(batch_dims) + ((N, K) if tb else (K, N))
+    s_a, s_b = np.float32(0.02), np.float32(0.005)
+    net.add_tensor("A", case["A"].reshape(a_shape), scale=s_a, zero_point=case["zp_a"])
+    net.add_tensor("B", case["B"].reshape(b_shape), scale=s_b, zero_point=case["zp_b"])
+    args = {"transpose_a": int(ta), "transpose_b": int(tb)}
+    net.op("MatMul", "QuantizeMatMulTest", ["A", "B"], ["Output"], i=args,
+           out_quant=[(case["s_c"], case["zp_c"])])
+    net.op("MatMul", "QuantizeMatMulInt32", ["A", "B"], ["Output32"], i=args, out_dtype=H.DT_INT32)
+    net.run()
+    assert net.shape("Output") == tuple(batch_dims) + (M, N)
+    exp = orc.gemm_u8(case["A"], case["B"], None, batch, M, N, K, case["zp_a"], case["zp_b"],
+                      case["mult"], case["shift"], case["zp_c"], a_col_major=ta, b_col_major=tb)
+    assert np.array_equal(net.read("Output", np.uint8).ravel(), exp)
+    exp32 = orc.gemm_u8(case["A"], case["B"], None, batch, M, N, K, case["zp_a"], case["zp_b"],
+                        a_col_major=ta, b_col_major=tb, out_int32=True)
+    assert np.array_equal(net.read("Output32", np.int32).ravel(), exp32)
+    scale, zp = net.quant("Output32")
+    assert abs(scale - s_a * s_b) < 1e-12 and zp == 0  # C.scale = sA * sB, zero point 0
+
+
+def test_matmul_one_side_batched_and_errors(net, orc):
+    import mace_b200
+    case = gemm_case(orc, 32, 3, 16, 32, 48, b_batched=False)
+    net.add_tensor("A", case["A"].reshape(3, 16, 48), scale=0.02, zero_point=case["zp_a"])
+    net.add_tensor("B", case["B"].reshape(48, 32), scale=0.005, zero_point=case["zp_b"])
+    net.op("MatMul", "mm", ["A", "B"], ["Out"], out_quant=[(case["s_c"], case["zp_c"])])
+    net.run()
+    exp = orc.gemm_u8(case["A"], case["B"], None, 3, 16, 32, 48, case["zp_a"], case["zp_b"],
+                      case["mult"], case["shift"], case["zp_c"], b_batched=False)
+    assert np.array_equal(net.read("Out", np.uint8).ravel(), exp)
+    # depth mismatch -> MACE_INVALID_ARGS from Validate()
+    net.add_tensor("Bad", np.zeros((7, 5), np.uint8), scale=0.005, zero_point=0)
+    net.op("MatMul", "bad", ["A", "Bad"], ["OutBad"], out_quant=[(1.0, 0)])
+    with pytest.raises(mace_b200.MaceB200Error) as e:
+        net.run()
+    assert e.value.code == 1
+    # unknown operator type / missing input
+    with pytest.raises(mace_b200.MaceB200Error) as e:
+        net.op("Softmax", "sm", ["A"], ["S"])
+    assert e.value.code == 3
+    with pytest.raises(mace_b200.MaceB200Error) as e:
+        net.op("MatMul", "mm2", ["A", "Nope"], ["S"])
+    assert e.value.code == 1
+
+
+@pytest.mark.parametrize("shape", [(1, 4, 4, 32, 16), (5, 1, 1, 1024, 1000), (2, 7, 7, 64, 33)])
+def test_fully_connected_quant(net, orc, shape):
+    """Quantized FullyConnected (fully_connected_test.cc:210-314 shapes): weight OHWI,
+    input NHWC, float-multiplier Gemv rule with the output zero point added."""
+    n, h, w, c, o = shape
+    rng = np.random.Generator(np.random.PCG64(5))
+    x = rng.integers(0, 256, size=(n, h, w, c), dtype=np.uint8)
+    wt = rng.integers(1, 256, size=(o, h, w, c), dtype=np.uint8)
+    bias = np.rint(rng.normal(0, 500, size=o)).astype(np.int32)
+    s_x, s_w = np.float32(0.03), np.float32(0.004)
+    K = h * w * c
+    s_o = np.float32(s_x * s_w * np.sqrt(K) * 74 * 74 * 3 / 127)
+    net.add_tensor("Input", x, scale=s_x, zero_point=127)
+    net.add_tensor("Weight", wt, scale=s_w, zero_point=128, is_weight=True)
+    net.add_tensor("Bias", bias, scale=s_x * s_w, zero_point=0, is_weight=True)
+    net.op("FullyConnected", "fc", ["Input", "Weight", "Bias"], ["Output"], out_quant=[(s_o, 119)])
+    net.run()
+    assert net.shape("Output") == (n, 1, 1, o)
+    exp = orc.gemv_u8(wt.reshape(1, o, K), x.reshape(n, K), bias, n, o, K, 128, 127,
+                      np.float32(s_w * s_x / s_o), 119, True)
+    got = net.read("Output", np.uint8).ravel()
+    assert np.array_equal(got, exp) and len(np.unique(got)) > 8
+
+
+def test_conv_bias_rescale_and_explicit_paddings(net, orc):
+    """GetBiasData rescales a bias whose scale is not input_scale * filter_scale; explicit
+    `padding_values` take the CalcOutputSize path."""
+    rng = np.random.Generator(np.random.PCG64(9))
+    x = rng.integers(0, 256, size=(2, 9, 10, 16), dtype=np.uint8)
+    f = rng.integers(1, 256, size=(24, 3, 3, 16), dtype=np.uint8)
+    bias = np.rint(rng.normal(0, 50, size=24)).astype(np.int32)
+    s_in, s_f, s_bias = np.float32(0.02), np.float32(0.01), np.float32(0.003)
+    s_out = np.float32(s_in * s_f * 12 * 74 * 74 * 3 / 127)
+    net.add_tensor("Input", x, scale=s_in, zero_point=120)
+    net.add_tensor("Filter", f, scale=s_f, zero_point=131, is_weight=True)
+    net.add_tensor("Bias", bias, scale=s_bias, zero_point=0, is_weight=True)
+    net.op("Conv2D", "conv", ["Input", "Filter", "Bias"], ["Output"], out_quant=[(s_out, 100)],
+           ints={"strides": [2, 1], "dilations": [1, 1], "padding_values": [2, 4]})
+    net.run()
+    bias_adj = orc.get_bias_data(bias, s_bias, s_in, s_f, 24)
+    assert not np.array_equal(bias_adj, bias)
+    ho, wo = (9 + 2 - 3) // 2 + 1, (10 + 4 - 3) // 1 + 1
+    assert net.shape("Output") == (2, ho, wo, 24)
+    m, sh = orc.output_multiplier_and_shift(s_f, s_in, s_out)
+    exp = orc.conv2d_u8(x, f, bias_adj, (2, 1), (2, 4), (ho, wo), 120, 131, m, sh, 100)
+    assert np.array_equal(net.read("Output", np.uint8), exp)
+
+
+def test_pooling_keeps_quantization(net, orc):
+    from mace_b200 import hostapi as H
+    rng = np.random.Generator(np.random.PCG64(2))
+    x = rng.integers(0, 256, size=(3, 7, 7, 96), dtype=np.uint8)
+    net.add_tensor("Input", x, scale=0.0123, zero_point=7)
+    net.op("Pooling", "pool", ["Input"], ["Output"],
+           ints={"kernels": [7, 7], "strides": [1, 1], "dilations": [1, 1]},
+           i={"padding": H.VALID, "pooling_type": H.AVG})
+    net.run()
+    scale, zp = net.quant("Output")
+    assert abs(scale - np.float32(0.0123)) < 1e-9 and zp == 7
+    exp = orc.avgpool_u8(x, (7, 7), (1, 1), (0, 0), (1, 1))
+    assert np.array_equal(net.read("Output", np.uint8), exp)

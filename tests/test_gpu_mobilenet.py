@@ -1,0 +1,89 @@
+"""Quantized MobileNet-v1 (224x224, uint8 NHWC, random weights) through the C++ host
+engine on the GPU against the CPU oracle chain: every layer's activation and the final
+uint8 logits must be bit-exact."""
+import numpy as np
+import pytest
+
+import mobilenet_v1 as mn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def layers(orc):
+    return mn.build(orc, seed=0)
+
+
+def test_mobilenet_chain_every_layer(orc, layers):
+    from mace_b200 import hostapi
+    batch = 3
+    x = mn.random_images(batch, seed=11)
+    exp_logits, exp_acts = mn.oracle_forward(orc, layers, x, keep=True)
+    eng = mn.build_engine(hostapi, layers, batch)
+    try:
+        eng.write("input", x)
+        eng.run()
+        for L, exp in zip(layers, exp_acts):
+            got = eng.read(L["name"], np.uint8)
+            assert np.array_equal(got.reshape(exp.shape), exp), "layer %s differs" % L["name"]
+        assert len(np.unique(exp_logits)) > 50
+    finally:
+        eng.close()
+
+
+def test_mobilenet_layers_in_isolation_full_range(orc, layers):
+    """Each layer alone on fresh uniform [0, 255] input, so that late layers see
+    full-range data (chained activations are ReLU6-skewed)."""
+    from mace_b200 import hostapi
+    rng = np.random.Generator(np.random.PCG64(77))
+    sizes = {"stem": 224}
+    h, c = 112, 32
+    for L in layers:
+        if L["kind"] not in ("conv", "dw"):
+            continue
+        if L["name"] == "stem":
+            hin, cin = 224, 3
+        else:
+            hin, cin = h, c
+        x = rng.integers(0, 256, size=(2, hin, hin, cin), dtype=np.uint8)
+        eng = hostapi.HostEngine(0)
+        try:
+            eng.add_tensor("in", x, scale=L["s_in"], zero_point=0)
+            eng.add_tensor("w", L["w"], scale=L["s_f"], zero_point=L["zp_f"], is_weight=True)
+            eng.add_tensor("b", L["bias"], scale=L["bias_scale"], zero_point=0, is_weight=True)
+            optype = "Conv2D" if L["kind"] == "conv" else "DepthwiseConv2d"
+            eng.op(optype, L["name"], ["in", "w", "b"], ["out"],
+                   out_quant=[(L["s_out"], L["zp_out"])],
+                   ints={"strides": [L["stride"]] * 2, "dilations": [1, 1]},
+                   i={"padding": hostapi.SAME})
+            eng.run()
+            got = eng.read("out", np.uint8)
+        finally:
+            eng.close()
+        one = [dict(L)]
+        exp = mn.oracle_forward(orc, one, x)
+        assert np.array_equal(got, exp), "layer %s differs" % L["name"]
+        if L["name"] != "stem":
+            h, c = exp.shape[1], exp.shape[3]
+
+
+def test_mobilenet_batch64_logits_and_host_buffers(orc, layers):
+    """The benchmark configuration: batch 64, through the host-buffer entry point
+    (H2D + chain + D2H), logits bit-exact against the oracle."""
+    from mace_b200 import hostapi
+    batch = 64
+    x = mn.random_images(batch, seed=0)
+    exp = mn.oracle_forward(orc, layers, x)
+    eng = mn.build_engine(hostapi, layers, batch)
+    try:
+        out = np.empty((batch, 1, 1, mn.NUM_CLASSES), np.uint8)
+        eng.run_host("input", x, "fc", out)
+        assert np.array_equal(out.reshape(batch, -1), exp)
+        # idempotence: a second run on the same input gives the same bytes
+        out2 = np.empty_like(out)
+        eng.run_host("input", x, "fc", out2)
+        assert np.array_equal(out, out2)
+        prof = eng.run_profiled()
+        assert len(prof) == len(layers)
+    finally:
+        eng.close()
