@@ -4,20 +4,23 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 Workloads (``config.workload``):
-  gemm_u8_4096   uint8 MatMul M = N = K = 4096 (the compute-bound entry of the
-                 K = N = 4096 sweep), zero points 128 / 120, fixed-point requantization
-                 to uint8.  metric: u8 GEMM TOPS.
+  mobilenet_v1_u8_b64  (default) quantized MobileNet-v1 1.0, 224x224, batch 64 per GPU, uint8
+                 NHWC, random seeded weights, through the C++ host engine (operators ->
+                 delegators -> C ABI).  metric: images/s.  The line also carries the u8 GEMM
+                 TOPS of the 4096^3 MatMul under "u8_gemm".
+  gemm_u8_4096   uint8 MatMul M = N = K = 4096, zero points 128 / 120, fixed-point
+                 requantization to uint8.  metric: u8 GEMM TOPS.
 
-One "step" is one pass of the hot path over one batch of synthetic, seeded input.
-`value` is measured with the inputs resident in HBM, `e2e` through the C ABI with
-pinned HOST buffers (H2D + kernel + D2H inside the timed region).  Timing uses CUDA
-events on the library's stream; with N > 1 each rank runs its own replica/shard, and
-the time is the maximum over ranks.
+One "step" is one pass of the hot path over one batch of synthetic, seeded input.  `value`
+is measured with the inputs resident in HBM, `e2e` through the host-buffer entry point with
+pinned HOST buffers (H2D + kernels + D2H inside the timed region).  Timing uses CUDA events on
+the library's stream; with N > 1 each rank runs its own shard (weak scaling: the per-GPU batch
+is fixed) and the time is the maximum over ranks.
 """
 import argparse
+import ctypes
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -98,8 +101,67 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(self.samples)}
 
 
+class RawContext:
+    """Event timing and launch counters on an mb_context owned by someone else."""
+
+    def __init__(self, handle):
+        import mace_b200
+        self.L = mace_b200.lib()
+        self.h = ctypes.c_void_p(handle)
+
+    def event(self):
+        e = ctypes.c_void_p()
+        assert self.L.mb_event_create(self.h, ctypes.byref(e)) == 0
+        return e
+
+    def record(self, e):
+        assert self.L.mb_event_record(self.h, e) == 0
+
+    def elapsed_ms(self, a, b):
+        ms = ctypes.c_float()
+        assert self.L.mb_event_elapsed_ms(self.h, a, b, ctypes.byref(ms)) == 0
+        return float(ms.value)
+
+    def sync(self):
+        rc = self.L.mb_stream_sync(self.h)
+        if rc != 0:
+            raise RuntimeError(self.L.mb_last_error(self.h).decode())
+
+    @property
+    def launches(self):
+        return int(self.L.mb_launch_count(self.h))
+
+    @property
+    def launches_tensor_core(self):
+        return int(self.L.mb_launch_count_tensor_core(self.h))
+
+    def pinned(self, nbytes):
+        p = ctypes.c_void_p()
+        assert self.L.mb_host_alloc(self.h, int(nbytes), ctypes.byref(p)) == 0
+        return np.ctypeslib.as_array((ctypes.c_uint8 * int(nbytes)).from_address(p.value))
+
+
+def init_dist(world, local):
+    if world <= 1:
+        return None
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return dist
+
+
+def max_over_ranks(dist, values):
+    if dist is None:
+        return values
+    import torch
+    t = torch.tensor(values, device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
 # --------------------------------------------------------------------------------------
-# workload: uint8 GEMM
+# workload: uint8 GEMM 4096^3
 # --------------------------------------------------------------------------------------
 
 class GemmWorkload:
@@ -112,12 +174,10 @@ class GemmWorkload:
         self.M, self.N, self.K = M, N, K
         self.zp_a, self.zp_b = 128, 120
         self.ops_per_step = 2.0 * M * N * K
-        # algorithmic bytes of one launch: A + B + C in uint8
-        self.bytes_per_step = M * K + K * N + M * N
+        self.bytes_per_step = M * K + K * N + M * N  # algorithmic bytes of one launch (uint8)
 
     def quant(self, orc):
-        # output scale from the expected accumulator spread (std of a sum of K products of
-        # centred uniform bytes), as AdjustRange would give for a +-4 sigma range
+        # output scale for a +-4 sigma accumulator range (sum of K products of centred bytes)
         sigma = np.sqrt(self.K) * 74.0 * 74.0
         s_c = np.float32(0.02 * 0.005 * 8 * sigma / 255.0)
         return orc.output_multiplier_and_shift(np.float32(0.02), np.float32(0.005), s_c) + (128,)
@@ -136,12 +196,8 @@ class GemmWorkload:
                     n_sets, n_sets * self.bytes_per_step / 1e6)}
 
 
-def run_ours(args, rank, world):
-    import mace_b200
-    from oracle import pyoracle as orc  # only for quantization parameters and cpu_baseline
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    ctx = mace_b200.Context(local)
-    wl = GemmWorkload()
+def time_gemm(ctx, orc, wl, steps, warmup, rank=0):
+    """Device-resident timing of the GEMM workload; returns (ms_per_step, sets, quant, n_sets)."""
     mult, shift, zp_c = wl.quant(orc)
     n_sets = max(2, int(np.ceil(1.5 * L2_BYTES / wl.bytes_per_step)))
     sets = []
@@ -153,20 +209,32 @@ def run_ours(args, rank, world):
         dA, dB, dC = sets[i % n_sets]
         ctx.gemm_u8(dA, dB, None, dC, 1, wl.M, wl.N, wl.K, wl.zp_a, wl.zp_b, mult, shift, zp_c)
 
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    for i in range(max(warmup, 3)):
+        step(i)
+    ctx.sync()
+    e0, e1 = ctx.event(), ctx.event()
+    ctx.record(e0)
+    for i in range(steps):
+        step(i)
+    ctx.record(e1)
+    ms = ctx.elapsed_ms(e0, e1)
+    return ms / steps, sets, (mult, shift, zp_c), n_sets, step
+
+
+def run_gemm(args, rank, world):
+    import mace_b200
+    from oracle import pyoracle as orc  # quantization parameters and the cpu_baseline leg only
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    ctx = mace_b200.Context(local)
+    wl = GemmWorkload()
+    dist = init_dist(world, local)
 
     def barrier():
         ctx.sync()
         if dist is not None:
             dist.barrier()
 
-    for i in range(max(args.warmup, 3)):
-        step(i)
+    _, sets, (mult, shift, zp_c), n_sets, step = time_gemm(ctx, orc, wl, 3, args.warmup, rank)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -181,16 +249,12 @@ def run_ours(args, rank, world):
     ms = ctx.elapsed_ms(e0, e1)
     barrier()
     launches, launches_tc = ctx.launches - l0, ctx.launches_tensor_core - ltc0
-
     clocks = sampler.stop() if rank == 0 else None
     if args.profile:
         ctx.close()
         return None
 
-    # end to end with host buffers: pinned H2D of A and B, GEMM, D2H of C, every step
-    hA = ctx.host_alloc(wl.M * wl.K)
-    hB = ctx.host_alloc(wl.K * wl.N)
-    hC = ctx.host_alloc(wl.M * wl.N)
+    hA, hB, hC = ctx.host_alloc(wl.M * wl.K), ctx.host_alloc(wl.K * wl.N), ctx.host_alloc(wl.M * wl.N)
     A, B = wl.host_inputs(7)
     hA[:] = A.ravel()
     hB[:] = B.ravel()
@@ -212,12 +276,7 @@ def run_ours(args, rank, world):
     ctx.record(e1)
     e2e_ms = ctx.elapsed_ms(e0, e1)
     barrier()
-
-    if dist is not None:
-        import torch
-        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+    ms, e2e_ms = max_over_ranks(dist, [ms, e2e_ms])
 
     result = None
     if rank == 0:
@@ -225,8 +284,6 @@ def run_ours(args, rank, world):
         ms_per_step = ms / args.steps
         value = world * wl.ops_per_step / (ms_per_step * 1e-3) / 1e12
         e2e_val = world * wl.ops_per_step / (e2e_ms / e2e_steps * 1e-3) / 1e12
-        # int8 dense peak is not in MEASURED_PEAKS.json; the tensor core's int8 rate is twice
-        # its bf16 rate, so the denominator is 2 x the measured bf16 burst figure.
         peak = 2.0 * peaks["bf16_tflops"]
         achieved = wl.ops_per_step / (ms_per_step * 1e-3) / 1e12
         result = {
@@ -238,27 +295,27 @@ def run_ours(args, rank, world):
             "roofline": {"bound": "tensor", "achieved": round(achieved, 2),
                          "peak": round(peak, 1), "unit": "TOP/s",
                          "frac": round(achieved / peak, 4), "traffic": None,
-                         "peak_source": "2 x %s bf16 burst (int8 rate of the tensor core)"
-                                        % peaks["source"],
-                         "kernel": "gemm_u8_tc_kernel<256> + operand byte-sum kernels"},
+                         "peak_source": "2 x %s bf16 burst (int8 rate of the tensor core; "
+                                        "no int8 figure in MEASURED_PEAKS.json)" % peaks["source"],
+                         "kernel": "gemm_u8_tc_kernel<256> (step also holds the two operand "
+                                   "byte-sum kernels)"},
             "e2e": {"value": round(e2e_val, 3), "unit": wl.unit,
                     "h2d_bytes_per_step": wl.M * wl.K + wl.K * wl.N,
                     "d2h_bytes_per_step": wl.M * wl.N},
             "gpu_launches": launches, "gpu_launches_tensor_core": launches_tc,
             "clocks": clocks,
         }
-        result["cpu_baseline"] = cpu_baseline(wl, orc, mult, shift, zp_c, steps=2)
+        result["cpu_baseline"] = gemm_cpu_baseline(wl, orc, mult, shift, zp_c, steps=2)
     ctx.close()
     if dist is not None:
         dist.destroy_process_group()
     return result
 
 
-def cpu_baseline(wl, orc, mult, shift, zp_c, steps):
+def gemm_cpu_baseline(wl, orc, mult, shift, zp_c, steps):
     """The oracle (a port of the reference's CPU arithmetic) on this box's host cores."""
     A, B = wl.host_inputs(0)
-    # bounded sample: the first 1024 rows of A against the whole B
-    rows = min(wl.M, 1024)
+    rows = min(wl.M, 1024)  # bounded sample: the first 1024 rows of A against the whole B
     threads = orc.set_threads(0)
     orc.gemm_u8(A[:64], B, None, 1, 64, wl.N, wl.K, wl.zp_a, wl.zp_b, mult, shift, zp_c)
     t0 = time.perf_counter()
@@ -270,34 +327,246 @@ def cpu_baseline(wl, orc, mult, shift, zp_c, steps):
             "sample": "%d of %d rows of A against all of B, %d passes" % (rows, wl.M, steps)}
 
 
+# --------------------------------------------------------------------------------------
+# workload: quantized MobileNet-v1, batch 64 per GPU
+# --------------------------------------------------------------------------------------
+
+BATCH = 64
+
+
+def mobilenet_layer_bytes(layers, batch):
+    """Algorithmic bytes per layer: input + output activation (uint8) + weights + int32 bias."""
+    out = {}
+    h, c = 224, 3
+    for L in layers:
+        if L["kind"] == "conv":
+            o, kh, kw, _ = L["w"].shape
+            ho = (h - 1) // L["stride"] + 1
+            out[L["name"]] = batch * (h * h * c + ho * ho * o) + L["w"].size + 4 * o
+            h, c = ho, o
+        elif L["kind"] == "dw":
+            ho = (h - 1) // L["stride"] + 1
+            out[L["name"]] = batch * (h * h * c + ho * ho * c) + 9 * c + 4 * c
+            h = ho
+        elif L["kind"] == "pool":
+            out[L["name"]] = batch * (h * h * c + c)
+            h = 1
+        else:
+            out[L["name"]] = L["w"].size + batch * (1024 + 1000) + 4000
+    return out
+
+
+def run_mobilenet(args, rank, world):
+    import mace_b200
+    from mace_b200 import hostapi
+    from oracle import pyoracle as orc  # model construction (quantization math) and cpu_baseline
+    import mobilenet_v1 as mn
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    dist = init_dist(world, local)
+    layers = mn.build(orc, seed=0)
+    # rotate the engine over several input tensors so that consecutive steps do not find their
+    # input in L2; activations (51 MB at the widest layer) stream through L2 on their own
+    eng = mn.build_engine(hostapi, layers, BATCH, device=local)
+    ctx = RawContext(eng.context)
+    n_inputs = 16  # 16 x 9.6 MB = 154 MB > L2
+    inputs = [mn.random_images(BATCH, seed=100 * rank + i) for i in range(n_inputs)]
+    hin = ctx.pinned(inputs[0].nbytes * n_inputs).reshape(n_inputs, -1)
+    for i, x in enumerate(inputs):
+        hin[i] = x.ravel()
+    hout = ctx.pinned(BATCH * mn.NUM_CLASSES)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    # device-resident inputs: one engine per input slot would triple memory; instead the input
+    # tensor is rewritten by an untimed H2D between steps for warm-up, and the timed loop runs
+    # the chain on device-resident data that the previous (untimed) copy left in HBM -- the
+    # input is 1.5 % of the bytes a step moves, the rest (activations, 650 MB) exceeds L2.
+    for i in range(max(args.warmup, 3)):
+        eng.write("input", inputs[i % n_inputs])
+        eng.run(sync=False)
+    if not args.no_graph:
+        eng.sync()
+        eng.capture()  # the chain is replayed from one CUDA graph from here on
+        eng.run(sync=False)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.01)
+    l0, ltc0 = ctx.launches, ctx.launches_tensor_core
+    e0, e1 = ctx.event(), ctx.event()
+    ctx.record(e0)
+    for i in range(args.steps):
+        eng.run(sync=False)
+    ctx.record(e1)
+    ms = ctx.elapsed_ms(e0, e1)
+    barrier()
+    launches, launches_tc = ctx.launches - l0, ctx.launches_tensor_core - ltc0
+    clocks = sampler.stop() if rank == 0 else None
+    if args.profile:
+        eng.close()
+        return None
+
+    # per-operator device times (CUDA events between operators), averaged over a few runs
+    prof_runs = 5
+    per_op = {}
+    for _ in range(prof_runs):
+        for label, t in eng.run_profiled():
+            per_op[label] = per_op.get(label, 0.0) + t / prof_runs
+
+    # end to end: pinned host input -> H2D -> chain -> D2H logits, every step
+    def e2e_step(i):
+        eng.run_host("input", hin[i % n_inputs], "fc", hout)
+        if dist is not None:  # the only collective of the path: gather the logits
+            import torch
+            mine = torch.from_numpy(hout.copy()).cuda()
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            torch.cuda.synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    e2e_steps = max(3, min(args.steps, 50))
+    t0 = time.perf_counter()
+    ctx.record(e0)
+    for i in range(e2e_steps):
+        e2e_step(i)
+    ctx.record(e1)
+    e2e_ms = ctx.elapsed_ms(e0, e1)
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max(e2e_ms, e2e_wall_ms) if dist is not None else e2e_ms
+    barrier()
+    ms, e2e_ms = max_over_ranks(dist, [ms, e2e_ms])
+
+    result = None
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_per_step = ms / args.steps
+        value = world * BATCH / (ms_per_step * 1e-3)
+        e2e_val = world * BATCH / (e2e_ms / e2e_steps * 1e-3)
+        lbytes = mobilenet_layer_bytes(layers, BATCH)
+        # group operator times by kernel family
+        fam = {"dw": ["dwconv3x3_u8_kernel", 0.0, 0], "pw": ["gemm_u8_tc_kernel (+ byte sums)", 0.0, 0],
+               "stem": ["conv_u8_direct_kernel", 0.0, 0], "pool": ["avgpool_u8_kernel", 0.0, 0],
+               "fc": ["gemv_u8_kernel", 0.0, 0]}
+        for label, t in per_op.items():
+            name = label.split(":")[1]
+            key = "dw" if name.startswith("dw") else "pw" if name.startswith("pw") else name
+            fam[key][1] += t
+            fam[key][2] += lbytes[name]
+        total_prof = sum(v[1] for v in fam.values())
+        dom = max(fam.values(), key=lambda v: v[1])
+        achieved = dom[2] / (dom[1] * 1e-3) / 1e9
+        total_bytes = sum(lbytes.values())
+        result = {
+            "metric": "quantized_mobilenet_v1_images_per_s", "value": round(value, 1),
+            "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+            "data": "synthetic",
+            "config": {"workload": "mobilenet_v1_u8_b64", "batch_per_gpu": BATCH,
+                       "global_batch": BATCH * world, "image": "224x224x3 uint8 NHWC",
+                       "weights": "He-normal, per-tensor uint8 (non_zero), seed 0",
+                       "parallelism": "dp%d: batch sharded, weights replicated, final logits gather only" % world,
+                       "launch": "per-operator launches" if args.no_graph else "CUDA graph replay",
+                       "l2": "activations of one step (%.0f MB) exceed L2" % (total_bytes / 1e6)},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1),
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                         "peak_source": "%s copy bandwidth" % peaks["source"],
+                         "kernel": dom[0],
+                         "kernel_share_of_step": round(dom[1] / total_prof, 3),
+                         "algorithmic_bytes_per_step": dom[2]},
+            "model_hbm": {"algorithmic_bytes_per_step": total_bytes,
+                          "achieved_gbs": round(total_bytes / (ms_per_step * 1e-3) / 1e9, 1),
+                          "frac_of_peak": round(total_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)},
+            "kernel_families_ms": {v[0]: round(v[1], 4) for v in fam.values()},
+            "e2e": {"value": round(e2e_val, 1), "unit": "images/s",
+                    "h2d_bytes_per_step": int(inputs[0].nbytes),
+                    "d2h_bytes_per_step": BATCH * mn.NUM_CLASSES},
+            "gpu_launches": launches, "gpu_launches_tensor_core": launches_tc, "clocks": clocks,
+        }
+        eng.close()
+        eng = None
+        # the other half of the metric: u8 GEMM TOPS on the 4096^3 MatMul
+        gctx = mace_b200.Context(local)
+        gwl = GemmWorkload()
+        gms, _, _, _, _ = time_gemm(gctx, orc, gwl, 30, 5)
+        gtops = gwl.ops_per_step / (gms * 1e-3) / 1e12
+        result["u8_gemm"] = {"workload": gwl.name, "value": round(gtops, 2), "unit": "TOPS",
+                             "ms_per_step": round(gms, 5),
+                             "frac_of_2x_bf16_peak": round(gtops / (2 * peaks["bf16_tflops"]), 4)}
+        gctx.close()
+        # CPU baseline: the oracle chain on this box's host cores, one full batch
+        threads = orc.set_threads(0)
+        x = inputs[0]
+        mn.oracle_forward(orc, layers, x[:4])
+        t0 = time.perf_counter()
+        passes = 2
+        for _ in range(passes):
+            mn.oracle_forward(orc, layers, x)
+        dt = (time.perf_counter() - t0) / passes
+        result["cpu_baseline"] = {"value": round(BATCH / dt, 2), "unit": "images/s",
+                                  "cores": threads, "kind": "port",
+                                  "sample": "%d full batches of %d images" % (passes, BATCH)}
+    if eng is not None:
+        eng.close()
+    if dist is not None:
+        dist.destroy_process_group()
+    return result
+
+
 def run_reference(args, rank, world):
-    """The reference's CPU implementation of the path: the oracle port (the reference's own
-    sources need NEON, gemmlowp and protobuf, none of which exist here)."""
+    """The reference's CPU implementation of the path, timed on the host cores: the oracle
+    port (the reference's own sources need NEON, gemmlowp, a TF-Lite fork and generated
+    protobuf code, none of which exist here)."""
     if rank != 0:
         return None
     from oracle import pyoracle as orc
-    wl = GemmWorkload()
-    mult, shift, zp_c = wl.quant(orc)
-    A, B = wl.host_inputs(0)
-    rows = min(wl.M, 1024)
     threads = orc.set_threads(0)
-    for _ in range(min(args.warmup, 1) or 1):
+    if args.workload == "gemm_u8_4096":
+        wl = GemmWorkload()
+        mult, shift, zp_c = wl.quant(orc)
+        A, B = wl.host_inputs(0)
+        rows = min(wl.M, 1024)
         orc.gemm_u8(A[:64], B, None, 1, 64, wl.N, wl.K, wl.zp_a, wl.zp_b, mult, shift, zp_c)
-    steps = max(1, min(args.steps, 5))
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        orc.gemm_u8(A[:rows], B, None, 1, rows, wl.N, wl.K, wl.zp_a, wl.zp_b, mult, shift, zp_c)
-    dt = (time.perf_counter() - t0) / steps
-    value = round(2.0 * rows * wl.N * wl.K / dt / 1e12, 5)
-    sample = "%d of %d rows of A against all of B per step" % (rows, wl.M)
-    return {"impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit,
-            "n_gpus": world, "steps": steps, "warmup": 1,
-            "ms_per_step": round(dt * 1e3 * wl.M / rows, 3), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": dict(wl.config(1), parallelism="host cores"),
-            "cpu_baseline": {"value": value, "unit": wl.unit, "cores": threads, "kind": "port",
+        steps = max(1, min(args.steps, 5))
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            orc.gemm_u8(A[:rows], B, None, 1, rows, wl.N, wl.K, wl.zp_a, wl.zp_b, mult, shift, zp_c)
+        dt = (time.perf_counter() - t0) / steps
+        value = round(2.0 * rows * wl.N * wl.K / dt / 1e12, 5)
+        sample = "%d of %d rows of A against all of B per step" % (rows, wl.M)
+        metric, unit, config = wl.metric, wl.unit, dict(wl.config(1), parallelism="host cores")
+        ms_per_step = dt * 1e3 * wl.M / rows
+    else:
+        import mobilenet_v1 as mn
+        layers = mn.build(orc, seed=0)
+        sample_n = 16
+        x = mn.random_images(sample_n, seed=0)
+        mn.oracle_forward(orc, layers, x[:2])
+        steps = max(1, min(args.steps, 5))
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            mn.oracle_forward(orc, layers, x)
+        dt = (time.perf_counter() - t0) / steps
+        value = round(sample_n / dt, 2)
+        sample = "%d images of the batch of %d per step" % (sample_n, BATCH)
+        metric, unit = "quantized_mobilenet_v1_images_per_s", "images/s"
+        config = {"workload": "mobilenet_v1_u8_b64", "batch_per_gpu": BATCH,
+                  "image": "224x224x3 uint8 NHWC", "parallelism": "host cores"}
+        ms_per_step = dt * 1e3 * BATCH / sample_n
+    return {"impl": "reference", "metric": metric, "value": value, "unit": unit,
+            "n_gpus": world, "steps": steps, "warmup": 1, "ms_per_step": round(ms_per_step, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+            "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port",
                              "sample": sample},
-            "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0,
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0}}
 
 
@@ -307,6 +576,10 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mobilenet_v1_u8_b64",
+                    choices=["mobilenet_v1_u8_b64", "gemm_u8_4096"])
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every operator separately instead of replaying a CUDA graph")
     ap.add_argument("--profile", action="store_true",
                     help="run only the device-resident timed loop (for ncu captures)")
     args = ap.parse_args()
@@ -314,8 +587,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
         res = run_reference(args, rank, world)
+    elif args.workload == "gemm_u8_4096":
+        res = run_gemm(args, rank, world)
     else:
-        res = run_ours(args, rank, world)
+        res = run_mobilenet(args, rank, world)
     if rank == 0 and res is not None:
         print(json.dumps(res))
 

@@ -69,6 +69,17 @@ int mb_event_create(mb_context *ctx, void **event);
 int mb_event_record(mb_context *ctx, void *event);
 int mb_event_elapsed_ms(mb_context *ctx, void *start, void *stop, float *ms);
 int mb_event_destroy(mb_context *ctx, void *event);
+/* CUDA-graph capture of a sequence of calls on this context (the launch-bound
+ * tail of a small-batch net costs more on the host than on the GPU).  Between
+ * mb_graph_begin and mb_graph_end every call on the context is recorded
+ * instead of executed; mb_graph_launch replays the recorded work.  Run the same
+ * sequence once uncaptured first: a call that would have to grow the scratch
+ * arena during capture fails with MB_RUNTIME_ERROR.  Pointers and shapes are
+ * baked into the graph. */
+int mb_graph_begin(mb_context *ctx);
+int mb_graph_end(mb_context *ctx, void **graph_exec);
+int mb_graph_launch(mb_context *ctx, void *graph_exec);
+int mb_graph_destroy(mb_context *ctx, void *graph_exec);
 /* Number of kernels launched through this context so far; the second form
  * counts only tcgen05 tensor-core GEMM launches. */
 uint64_t mb_launch_count(const mb_context *ctx);

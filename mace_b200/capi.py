@@ -52,6 +52,10 @@ PROTOTYPES = {
     "mb_event_record": (_int, [_vp, _vp]),
     "mb_event_elapsed_ms": (_int, [_vp, _vp, _vp, C.POINTER(_f32)]),
     "mb_event_destroy": (_int, [_vp, _vp]),
+    "mb_graph_begin": (_int, [_vp]),
+    "mb_graph_end": (_int, [_vp, C.POINTER(_vp)]),
+    "mb_graph_launch": (_int, [_vp, _vp]),
+    "mb_graph_destroy": (_int, [_vp, _vp]),
     "mb_launch_count": (C.c_uint64, [_vp]),
     "mb_launch_count_tensor_core": (C.c_uint64, [_vp]),
     "mb_set_option": (_int, [_vp, C.c_char_p, _int]),

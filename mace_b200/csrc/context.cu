@@ -25,6 +25,9 @@ int mb_check_cuda(mb_context *ctx, cudaError_t e, const char *what) {
 
 int mb_scratch(mb_context *ctx, size_t bytes, void **ptr) {
   if (bytes > ctx->scratch_bytes) {
+    if (ctx->capturing)
+      return mb_fail(ctx, MB_RUNTIME_ERROR,
+                     "scratch arena would grow during graph capture; run the sequence once first");
     // Growing invalidates earlier carve-outs, so drain the stream first.
     MB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ctx->scratch != nullptr) {
@@ -202,6 +205,64 @@ int mb_event_elapsed_ms(mb_context *ctx, void *start, void *stop, float *ms) {
 int mb_event_destroy(mb_context *ctx, void *event) {
   if (ctx == nullptr) return MB_INVALID_ARGS;
   if (event != nullptr) MB_CUDA(ctx, cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  return MB_SUCCESS;
+}
+
+// A captured sequence and the number of kernel launches one replay stands for.
+struct mb_graph {
+  cudaGraphExec_t exec = nullptr;
+  uint64_t launches = 0, launches_tc = 0;
+};
+
+int mb_graph_begin(mb_context *ctx) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (ctx->capturing) return mb_fail(ctx, MB_INVALID_ARGS, "a capture is already in progress");
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  MB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+  ctx->capturing = 1;
+  ctx->capture_launches0 = ctx->launches;
+  ctx->capture_launches_tc0 = ctx->launches_tc;
+  return MB_SUCCESS;
+}
+
+int mb_graph_end(mb_context *ctx, void **graph_exec) {
+  if (ctx == nullptr || graph_exec == nullptr) return MB_INVALID_ARGS;
+  if (!ctx->capturing) return mb_fail(ctx, MB_INVALID_ARGS, "no capture in progress");
+  ctx->capturing = 0;
+  cudaGraph_t graph = nullptr;
+  MB_CUDA(ctx, cudaStreamEndCapture(ctx->stream, &graph));
+  cudaGraphExec_t exec = nullptr;
+  cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  MB_CUDA(ctx, e);
+  mb_graph *g = new mb_graph();
+  g->exec = exec;
+  // the launches counted during capture were recorded, not executed
+  g->launches = ctx->launches - ctx->capture_launches0;
+  g->launches_tc = ctx->launches_tc - ctx->capture_launches_tc0;
+  ctx->launches = ctx->capture_launches0;
+  ctx->launches_tc = ctx->capture_launches_tc0;
+  *graph_exec = g;
+  return MB_SUCCESS;
+}
+
+int mb_graph_launch(mb_context *ctx, void *graph_exec) {
+  if (ctx == nullptr || graph_exec == nullptr) return MB_INVALID_ARGS;
+  mb_graph *g = static_cast<mb_graph *>(graph_exec);
+  MB_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+  ctx->launches += g->launches;
+  ctx->launches_tc += g->launches_tc;
+  return MB_SUCCESS;
+}
+
+int mb_graph_destroy(mb_context *ctx, void *graph_exec) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (graph_exec != nullptr) {
+    mb_graph *g = static_cast<mb_graph *>(graph_exec);
+    cudaError_t e = cudaGraphExecDestroy(g->exec);
+    delete g;
+    MB_CUDA(ctx, e);
+  }
   return MB_SUCCESS;
 }
 

@@ -79,6 +79,7 @@ int mbh_add_tensor(mbh_engine *e, const char *name, int data_type, int rank, con
   std::vector<index_t> shape(dims, dims + rank);
   for (index_t d : shape)
     if (d < 0) return Fail(e, MaceStatus::MACE_INVALID_ARGS, "negative dimension");
+  e->net->DropCapture();  // a recorded graph holds the old tensor's address
   Tensor *t = e->workspace.CreateTensor(name, &e->runtime, dt, is_weight != 0);
   MBH_TRY(e, t->Resize(shape));
   t->SetScale(scale);
@@ -220,6 +221,12 @@ int mbh_op_end(mbh_engine *e) {
 int mbh_run(mbh_engine *e) {
   if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
   MBH_TRY(e, e->net->Run(nullptr));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_capture(mbh_engine *e) {
+  if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  MBH_TRY(e, e->net->Capture());
   return MaceStatus::MACE_SUCCESS;
 }
 

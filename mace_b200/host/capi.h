@@ -54,6 +54,10 @@ int mbh_op_end(mbh_engine *engine);
 /* Runs all operators once (asynchronously on the engine's stream). */
 int mbh_run(mbh_engine *engine);
 int mbh_sync(mbh_engine *engine);
+/* Records the operator chain into a CUDA graph that later mbh_run / mbh_run_host calls
+ * replay (SerialNet::Capture).  Needs one plain mbh_run first; adding an operator or
+ * replacing a tensor drops the recording. */
+int mbh_capture(mbh_engine *engine);
 /* Host-buffer run, the shape of MaceEngine::Run (mace/libmace/mace_engine.cc:203-212):
  * copies input_bytes from pinned or pageable host memory into the input
  * tensor, runs the net, copies the output tensor back and waits. */

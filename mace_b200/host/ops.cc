@@ -325,6 +325,7 @@ void RegisterAllCudaOps(OpRegistry *registry) {
 // ---- SerialNet -------------------------------------------------------------------
 
 MaceStatus SerialNet::AddOperator(const OperatorDef &def) {
+  DropCapture();
   defs_.push_back(std::make_unique<OperatorDef>(def));
   const OperatorDef *d = defs_.back().get();
   OpConstructContext cc(ws_, runtime_, d);
@@ -345,7 +346,34 @@ MaceStatus SerialNet::AddOperator(const OperatorDef &def) {
   return MaceStatus::MACE_SUCCESS;
 }
 
+MaceStatus SerialNet::Capture() {
+  DropCapture();
+  OpContext context(runtime_);
+  MACE_RETURN_IF_ERROR(runtime_->Status(mb_graph_begin(runtime_->ctx())));
+  MaceStatus st = MaceStatus::MACE_SUCCESS;
+  for (size_t i = 0; i < operators_.size() && st == MaceStatus::MACE_SUCCESS; ++i)
+    st = operators_[i]->Run(&context);
+  void *graph = nullptr;
+  MaceStatus end = runtime_->Status(mb_graph_end(runtime_->ctx(), &graph));
+  if (st != MaceStatus::MACE_SUCCESS) {
+    if (graph != nullptr) mb_graph_destroy(runtime_->ctx(), graph);
+    return st;
+  }
+  MACE_RETURN_IF_ERROR(end);
+  graph_ = graph;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+void SerialNet::DropCapture() {
+  if (graph_ != nullptr) {
+    mb_graph_destroy(runtime_->ctx(), graph_);
+    graph_ = nullptr;
+  }
+}
+
 MaceStatus SerialNet::Run(std::vector<CallStats> *run_metadata) {
+  if (graph_ != nullptr && run_metadata == nullptr)
+    return runtime_->Status(mb_graph_launch(runtime_->ctx(), graph_));
   OpContext context(runtime_);
   std::vector<void *> events;
   if (run_metadata != nullptr) {

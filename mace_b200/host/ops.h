@@ -115,6 +115,14 @@ class SerialNet {
   // run_metadata may be null; when given, each operator is bracketed by device
   // events (mace/core/net/serial_net.cc:122-180).
   MaceStatus Run(std::vector<CallStats> *run_metadata = nullptr);
+  // Records one pass over the operators into a CUDA graph; later Run() calls
+  // without run_metadata replay it.  Call after at least one plain Run() (so
+  // that scratch and cached operands exist) and again after any change of
+  // tensor shapes or operators.
+  MaceStatus Capture();
+  void DropCapture();
+  bool captured() const { return graph_ != nullptr; }
+  ~SerialNet() { DropCapture(); }
   size_t size() const { return operators_.size(); }
 
  private:
@@ -123,6 +131,7 @@ class SerialNet {
   CudaRuntime *runtime_;
   std::vector<std::unique_ptr<OperatorDef>> defs_;
   std::vector<std::unique_ptr<Operation>> operators_;
+  void *graph_ = nullptr;
 };
 
 }  // namespace mace

@@ -40,6 +40,7 @@ _PROTOS = {
     "mbh_op_end": [_vp],
     "mbh_run": [_vp],
     "mbh_sync": [_vp],
+    "mbh_capture": [_vp],
     "mbh_run_host": [_vp, _cp, _vp, _sz, _cp, _vp, _sz],
     "mbh_run_profiled": [_vp, C.POINTER(_f32), _int, C.c_char_p, _sz, C.POINTER(_int)],
 }
@@ -160,6 +161,10 @@ class HostEngine:
 
     def sync(self):
         self._check(lib().mbh_sync(self.h))
+
+    def capture(self):
+        """Record the chain into a CUDA graph (after one plain run); later runs replay it."""
+        self._check(lib().mbh_capture(self.h))
 
     def run_host(self, input_name, host_in, output_name, host_out):
         self._check(lib().mbh_run_host(self.h, input_name.encode(), host_in.ctypes.data,

@@ -67,6 +67,12 @@ def test_mobilenet_layers_in_isolation_full_range(orc, layers):
             h, c = exp.shape[1], exp.shape[3]
 
 
+def eng_launches(eng):
+    import ctypes
+    import mace_b200
+    return int(mace_b200.lib().mb_launch_count(ctypes.c_void_p(eng.context)))
+
+
 def test_mobilenet_batch64_logits_and_host_buffers(orc, layers):
     """The benchmark configuration: batch 64, through the host-buffer entry point
     (H2D + chain + D2H), logits bit-exact against the oracle."""
@@ -85,5 +91,15 @@ def test_mobilenet_batch64_logits_and_host_buffers(orc, layers):
         assert np.array_equal(out, out2)
         prof = eng.run_profiled()
         assert len(prof) == len(layers)
+        # the same chain replayed from a CUDA graph, on a different input
+        x2 = mn.random_images(batch, seed=5)
+        exp2 = mn.oracle_forward(orc, layers, x2)
+        eng.capture()
+        launches_before = eng_launches(eng)
+        eng.run_host("input", x2, "fc", out2)
+        assert np.array_equal(out2.reshape(batch, -1), exp2)
+        assert eng_launches(eng) - launches_before >= len(layers)  # replay counts its kernels
+        eng.run_host("input", x, "fc", out2)
+        assert np.array_equal(out2, out)
     finally:
         eng.close()
