@@ -89,6 +89,45 @@ __device__ __forceinline__ uint32_t mb_requant(int32_t acc, int32_t mult,
   return static_cast<uint32_t>(min(255, max(0, v)));
 }
 
+// The same arithmetic in about a third of the instructions, for the epilogues
+// that requantize hundreds of millions of values per batch.  With t = acc *
+// mult (64-bit) the two rounding steps collapse into one 64-bit expression:
+//   SRDHM(acc, mult)        = floor((t + 2^30) / 2^31)      (mult > 0: the
+//                             truncating division with the sign-dependent
+//                             nudge equals this floor for every acc)
+//   RDivPOT(x, s), s >= 1   = floor((x + 2^(s-1) - [x < 0]) / 2^s)
+//   floor((floor(a/m) + c) / n) = floor((a + c*m) / (m*n))
+// so  y = (t + 2^30 + 2^(s+30) - [acc < 0] * 2^31) >> (31 + s)   for s >= 1
+// and y = (t + 2^30) >> 31 for s == 0.  ([x < 0] and [acc < 0] differ only for
+// acc = -1, mult = 2^30, where both give y = 0.)  |t| < 2^62 and the constants
+// are below 2^62, so nothing overflows.  tests/test_requant_identity.py checks
+// the identity against the two-step definition.
+struct mb_requant_params {
+  int64_t c64;   // 2^30 (+ 2^(shift+30) when shift >= 1)
+  int32_t mult;  // fixed-point multiplier in [2^30, 2^31)
+  int32_t neg;   // -2^31 when shift >= 1, else 0
+  int32_t sh;    // 31 + shift
+  int32_t zp;    // output zero point, 0..255
+};
+
+static inline mb_requant_params mb_make_requant(int32_t mult, int32_t shift, int32_t zp_out) {
+  mb_requant_params q;
+  q.c64 = (1ll << 30) + (shift >= 1 ? (1ll << (shift + 30)) : 0ll);
+  q.mult = mult;
+  q.neg = shift >= 1 ? static_cast<int32_t>(0x80000000u) : 0;
+  q.sh = 31 + shift;
+  q.zp = zp_out;
+  return q;
+}
+
+__device__ __forceinline__ uint32_t mb_requant_fast(int32_t acc, const mb_requant_params &q) {
+  int64_t t = static_cast<int64_t>(acc) * q.mult + q.c64;
+  t += static_cast<int64_t>(static_cast<int32_t>(static_cast<uint32_t>(acc) >> 31)) * q.neg;
+  const int32_t y = static_cast<int32_t>(t >> q.sh);
+  // clamp(y + zp, 0, 255); y is capped first so that y + zp cannot wrap
+  return static_cast<uint32_t>(__viaddmin_s32_relu(min(y, 255), q.zp, 255));
+}
+
 // Saturate<uint8_t>(roundf(v)) of mace/core/quantize.h:69-83.
 __device__ __forceinline__ uint32_t mb_saturate_round_u8(float v) {
   const int r = static_cast<int>(roundf(v));

@@ -9,8 +9,9 @@
 // Three routes:
 //   1x1 stride 1      -> the NHWC tensor already is the [pixels x C] K-major
 //                        GEMM operand; no copy (conv_2d.cc:279-281)
+//   3x3 on 3 channels -> packed-patch dp4a kernel (MobileNet's 3x3x3 stem)
 //   small depth * O   -> direct kernel, one thread per output pixel, the whole
-//                        filter in shared memory (MobileNet's 3x3x3 stem)
+//                        filter in shared memory
 //   everything else   -> patch gather into scratch (rows padded to 16 bytes)
 //                        + tensor-core GEMM
 #include "common.cuh"
@@ -29,7 +30,8 @@ struct ConvParams {
   uint8_t *out;
   int N, H, W, C, O, KH, KW, stride_h, stride_w, pad_top, pad_left, Ho, Wo;
   int depth, depth_padded;
-  int32_t zp_in, zp_f, mult, shift, zp_out;
+  int32_t zp_in, zp_f;
+  mb_requant_params rq;
 };
 
 // Direct convolution: thread = one output pixel, OT output channels at a time.
@@ -75,7 +77,103 @@ __global__ void __launch_bounds__(128) conv_u8_direct_kernel(const ConvParams p)
 #pragma unroll
     for (int j = 0; j < OT; ++j)
       if (o0 + j < p.O)
-        outp[o0 + j] = static_cast<uint8_t>(mb_requant(acc[j], p.mult, p.shift, p.zp_out));
+        outp[o0 + j] = static_cast<uint8_t>(mb_requant_fast(acc[j], p.rq));
+  }
+}
+
+// First-layer style convolution (few input channels, e.g. 3x3x3): thread = one
+// output pixel, all output channels.  The KH*KW*C patch bytes are packed into
+// DW 32-bit words held in registers and multiplied with the raw filter bytes
+// by dp4a; zero points are applied afterwards:
+//   sum (in - zi)(f - zf) = sum in*f - zf * sum in - zi * sum f + depth * zi * zf
+// with out-of-image taps read as zi (so they contribute zero).  The filter
+// rows (zero-padded to 8 words) and the per-channel constant
+//   bias - zi * sum f + depth * zi * zf
+// live in shared memory and are read as broadcasts.
+template <int KH, int KW, int C>
+__global__ void __launch_bounds__(128) conv_u8_patch_dp4a_kernel(const ConvParams p) {
+  constexpr int DEPTH = KH * KW * C;
+  constexpr int DW = (DEPTH + 3) / 4;
+  constexpr int DWP = (DW + 3) / 4 * 4;  // words per filter row in shared memory
+  extern __shared__ uint32_t smem_w[];   // [O][DWP] filter words, then [O] constants
+  int32_t *cterm = reinterpret_cast<int32_t *>(smem_w + p.O * DWP);
+  for (int i = threadIdx.x; i < p.O * DWP; i += blockDim.x) {
+    const int o = i / DWP, w = i % DWP;
+    uint32_t v = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int d = w * 4 + b;
+      if (d < DEPTH) v |= static_cast<uint32_t>(p.filter[o * DEPTH + d]) << (8 * b);
+    }
+    smem_w[i] = v;
+  }
+  for (int o = threadIdx.x; o < p.O; o += blockDim.x) {
+    int32_t fs = 0;
+    for (int d = 0; d < DEPTH; ++d) fs += p.filter[o * DEPTH + d];
+    cterm[o] = (p.bias != nullptr ? p.bias[o] : 0) - p.zp_in * fs + DEPTH * p.zp_in * p.zp_f;
+  }
+  __syncthreads();
+  const int64_t pix = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t npix = static_cast<int64_t>(p.N) * p.Ho * p.Wo;
+  if (pix >= npix) return;
+  const int wo = static_cast<int>(pix % p.Wo);
+  const int ho = static_cast<int>((pix / p.Wo) % p.Ho);
+  const int n = static_cast<int>(pix / (static_cast<int64_t>(p.Wo) * p.Ho));
+  const int hi0 = ho * p.stride_h - p.pad_top, wi0 = wo * p.stride_w - p.pad_left;
+  const uint8_t *in_n = p.in + static_cast<int64_t>(n) * p.H * p.W * C;
+  uint32_t patch[DW];
+#pragma unroll
+  for (int i = 0; i < DW; ++i) patch[i] = 0;
+  const uint32_t zi = static_cast<uint32_t>(p.zp_in);
+#pragma unroll
+  for (int kh = 0; kh < KH; ++kh) {
+    const int hi = hi0 + kh;
+    const bool row_ok = hi >= 0 && hi < p.H;
+#pragma unroll
+    for (int kw = 0; kw < KW; ++kw) {
+      const int wi = wi0 + kw;
+      const bool ok = row_ok && wi >= 0 && wi < p.W;
+      const uint8_t *ip = in_n + (static_cast<int64_t>(ok ? hi : 0) * p.W + (ok ? wi : 0)) * C;
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const int d = (kh * KW + kw) * C + c;  // compile-time
+        const uint32_t v = ok ? static_cast<uint32_t>(__ldg(ip + c)) : zi;
+        patch[d >> 2] |= v << (8 * (d & 3));
+      }
+    }
+  }
+  uint32_t sum_in = 0;
+#pragma unroll
+  for (int i = 0; i < DW; ++i) sum_in = __dp4a(patch[i], 0x01010101u, sum_in);
+  const int32_t in_term = -p.zp_f * static_cast<int32_t>(sum_in);
+  uint8_t *outp = p.out + pix * p.O;
+  for (int o0 = 0; o0 < p.O; o0 += 4) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int o = o0 + j;
+      if (o < p.O) {
+        const uint4 *wr = reinterpret_cast<const uint4 *>(smem_w + o * DWP);
+        uint32_t dot = 0;
+#pragma unroll
+        for (int q = 0; q < DWP / 4; ++q) {
+          const uint4 w4 = wr[q];
+          if (q * 4 + 0 < DW) dot = __dp4a(patch[q * 4 + 0 < DW ? q * 4 + 0 : 0], w4.x, dot);
+          if (q * 4 + 1 < DW) dot = __dp4a(patch[q * 4 + 1 < DW ? q * 4 + 1 : 0], w4.y, dot);
+          if (q * 4 + 2 < DW) dot = __dp4a(patch[q * 4 + 2 < DW ? q * 4 + 2 : 0], w4.z, dot);
+          if (q * 4 + 3 < DW) dot = __dp4a(patch[q * 4 + 3 < DW ? q * 4 + 3 : 0], w4.w, dot);
+        }
+        const int32_t acc = static_cast<int32_t>(dot) + in_term + cterm[o];
+        packed |= mb_requant_fast(acc, p.rq) << (8 * j);
+      }
+    }
+    if ((p.O & 3) == 0) {
+      *reinterpret_cast<uint32_t *>(outp + o0) = packed;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (o0 + j < p.O) outp[o0 + j] = static_cast<uint8_t>(packed >> (8 * j));
+    }
   }
 }
 
@@ -145,8 +243,8 @@ extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
     return mb_fail(ctx, MB_INVALID_ARGS, "mb_conv2d_u8_nhwc: null operand");
   if (multiplier <= 0 || right_shift < 0 || right_shift > 31)
     return mb_fail(ctx, MB_INVALID_ARGS, "mb_conv2d_u8_nhwc: bad multiplier/shift");
-  if (zp_in < 0 || zp_in > 255)
-    return mb_fail(ctx, MB_INVALID_ARGS, "mb_conv2d_u8_nhwc: input zero point outside uint8");
+  if (zp_in < 0 || zp_in > 255 || zp_out < 0 || zp_out > 255)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_conv2d_u8_nhwc: zero point outside uint8");
   const int64_t depth = C * KH * KW;
   const int64_t pixels = N * Ho * Wo;
   if (depth > (1 << 24) || pixels >= (1ll << 31) || H > (1 << 20) || W > (1 << 20))
@@ -170,8 +268,18 @@ extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
   p.Ho = static_cast<int>(Ho); p.Wo = static_cast<int>(Wo);
   p.depth = static_cast<int>(depth);
   p.depth_padded = static_cast<int>(align_up(static_cast<size_t>(depth), 16));
-  p.zp_in = zp_in; p.zp_f = zp_f; p.mult = multiplier; p.shift = right_shift; p.zp_out = zp_out;
+  p.zp_in = zp_in; p.zp_f = zp_f;
+  p.rq = mb_make_requant(multiplier, right_shift, zp_out);
 
+  if (KH == 3 && KW == 3 && C == 3 && O <= 256 &&
+      (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {
+    const size_t smem = static_cast<size_t>(O) * (8 * 4 + 4);
+    const unsigned blocks = static_cast<unsigned>(ceil_div64(pixels, 128));
+    conv_u8_patch_dp4a_kernel<3, 3, 3><<<blocks, 128, smem, ctx->stream>>>(p);
+    MB_CUDA(ctx, cudaGetLastError());
+    ctx->launches++;
+    return MB_SUCCESS;
+  }
   const size_t direct_smem = static_cast<size_t>(depth) * O * sizeof(int16_t);
   if (direct_smem <= 32 * 1024 && depth <= 256) {
     const unsigned blocks = static_cast<unsigned>(ceil_div64(pixels, 128));

@@ -35,7 +35,8 @@ struct GenericParams {
   int64_t a_rs, a_cs;  // strides of A(m,k): m * a_rs + k * a_cs
   int64_t b_rs, b_cs;  // strides of B(k,n): k * b_rs + n * b_cs
   int64_t a_bs, b_bs;  // batch strides (0 when not batched)
-  int32_t zp_a, zp_b, mult, shift, zp_c;
+  int32_t zp_a, zp_b;
+  mb_requant_params rq;
   int out_is_int32, bias_per_row;
 };
 
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(256) gemm_u8_generic_kernel(const GenericParam
         static_cast<int32_t *>(p.C)[idx] = v;
       } else {
         static_cast<uint8_t *>(p.C)[idx] =
-            static_cast<uint8_t>(mb_requant(v, p.mult, p.shift, p.zp_c));
+            static_cast<uint8_t>(mb_requant_fast(v, p.rq));
       }
     }
   }
@@ -239,7 +240,8 @@ int launch_generic(mb_context *ctx, const uint8_t *A, const uint8_t *B, const in
   // B MN-major (row-major K x N): (k,n) at k*N + n.  B K-major: n*K + k.
   p.b_rs = b_mn ? N : 1; p.b_cs = b_mn ? 1 : K;
   p.a_bs = a_batched ? M * K : 0; p.b_bs = b_batched ? K * N : 0;
-  p.zp_a = zp_a; p.zp_b = zp_b; p.mult = mult; p.shift = shift; p.zp_c = zp_c;
+  p.zp_a = zp_a; p.zp_b = zp_b;
+  p.rq = mb_make_requant(mult, shift, zp_c);
   p.out_is_int32 = out_is_int32; p.bias_per_row = bias_per_row;
   const int64_t gx = ceil_div64(N, GT), gy = ceil_div64(M, GT);
   if (gy > 65535 || batch > 65535)
@@ -335,6 +337,8 @@ extern "C" int mb_gemm_u8(mb_context *ctx, const uint8_t *A, const uint8_t *B,
     if (multiplier <= 0 || right_shift < 0 || right_shift > 31)
       return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemm_u8: bad multiplier %d / shift %d",
                      multiplier, right_shift);
+    if (zp_c < 0 || zp_c > 255)
+      return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemm_u8: output zero point %d outside uint8", zp_c);
   }
   if (K == 0) {
     // Empty depth: the accumulator is zero, the pipeline still applies.

@@ -46,7 +46,8 @@ struct TcParams {
   int a_batched, b_batched;
   const int32_t *bias;
   int bias_per_row;
-  int32_t zp_a, zp_b, mult, shift, zp_c, kzz;
+  int32_t zp_a, zp_b, kzz;
+  mb_requant_params rq;
   void *C;
   int out_is_int32;
   int vec_store_ok;  // rows of C are 16-byte aligned
@@ -283,7 +284,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const int j = 4 * q + e;
                 const int32_t acc = static_cast<int32_t>(r[j]) + row_term +
                                     __shfl_sync(0xffffffffu, col_term, j);
-                w |= mb_requant(acc, p.mult, p.shift, p.zp_c) << (8 * e);
+                w |= mb_requant_fast(acc, p.rq) << (8 * e);
               }
               packed[q] = w;
             }
@@ -418,7 +419,8 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.sum_a_bstride = M; p.sum_b_bstride = N;
   p.a_batched = a_batched; p.b_batched = b_batched;
   p.bias = bias; p.bias_per_row = bias_per_row;
-  p.zp_a = zp_a; p.zp_b = zp_b; p.mult = mult; p.shift = shift; p.zp_c = zp_c;
+  p.zp_a = zp_a; p.zp_b = zp_b;
+  p.rq = mb_make_requant(mult, shift, zp_c);
   p.kzz = static_cast<int32_t>(static_cast<uint32_t>(K) * static_cast<uint32_t>(zp_a) *
                                static_cast<uint32_t>(zp_b));
   p.C = C; p.out_is_int32 = out_is_int32;

@@ -23,6 +23,7 @@ struct GemvParams {
   int lhs_batched, rhs_batched, out_is_int32, add_zp_out;
   int32_t zp_lhs, zp_rhs, zp_out;
   float multiplier;
+  int batch_chunk;
 };
 
 template <bool VEC>
@@ -30,10 +31,10 @@ __global__ void __launch_bounds__(256) gemv_u8_kernel(const GemvParams p) {
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= p.rows) return;
-  // blockIdx.y walks the batch when every entry has its own matrix; otherwise
-  // one warp serves all batch entries of its row.
-  const int64_t b_begin = p.lhs_batched ? blockIdx.y : 0;
-  const int64_t b_end = p.lhs_batched ? b_begin + 1 : p.batch;
+  // blockIdx.y walks the batch: one entry per block when every entry has its
+  // own matrix, otherwise a chunk of entries that share the warp's matrix row.
+  const int64_t b_begin = p.lhs_batched ? blockIdx.y : static_cast<int64_t>(blockIdx.y) * p.batch_chunk;
+  const int64_t b_end = p.lhs_batched ? b_begin + 1 : min(p.batch, b_begin + p.batch_chunk);
   for (int64_t b = b_begin; b < b_end; ++b) {
     const uint8_t *lp = p.lhs + (p.lhs_batched ? b * p.rows * p.K : 0) + row * p.K;
     const uint8_t *rp = p.rhs + (p.rhs_batched ? b * p.K : 0);
@@ -115,7 +116,16 @@ extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rh
   p.zp_lhs = zp_lhs; p.zp_rhs = zp_rhs; p.zp_out = zp_out; p.multiplier = multiplier;
   const bool vec = (K % 16 == 0) && K > 0 &&
                    ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15u) == 0;
-  dim3 grid(static_cast<unsigned>(ceil_div64(rows, 8)), lhs_batched ? static_cast<unsigned>(batch) : 1u);
+  // a shared matrix: split the batch so that at least ~4 blocks per SM exist
+  int64_t chunks = 1;
+  if (!lhs_batched) {
+    chunks = std::min<int64_t>(batch, std::max<int64_t>(1, (4ll * ctx->num_sms) / ceil_div64(rows, 8)));
+    chunks = std::min<int64_t>(chunks, 65535);
+  }
+  p.batch_chunk = static_cast<int>(ceil_div64(batch, chunks));
+  dim3 grid(static_cast<unsigned>(ceil_div64(rows, 8)),
+            lhs_batched ? static_cast<unsigned>(batch)
+                        : static_cast<unsigned>(ceil_div64(batch, p.batch_chunk)));
   if (vec) gemv_u8_kernel<true><<<grid, 256, 0, ctx->stream>>>(p);
   else gemv_u8_kernel<false><<<grid, 256, 0, ctx->stream>>>(p);
   MB_CUDA(ctx, cudaGetLastError());

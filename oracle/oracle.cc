@@ -246,6 +246,10 @@ uint8_t orc_requant_fixed(int32_t acc, int32_t multiplier, int32_t right_shift,
   return requant_fixed(acc, multiplier, right_shift, zp_out);
 }
 
+int32_t orc_rounding_stages(int32_t acc, int32_t multiplier, int32_t right_shift) {
+  return rdivpot(srdhm(acc, multiplier), right_shift);
+}
+
 void orc_get_bias_data(const int32_t *bias, float bias_scale, float input_scale,
                        float filter_scale, int64_t channels, int32_t *out) {
   if (bias == nullptr) {

@@ -57,6 +57,10 @@ int orc_output_multiplier_and_shift(float lhs_scale, float rhs_scale,
 uint8_t orc_requant_fixed(int32_t acc, int32_t multiplier, int32_t right_shift,
                           int32_t zp_out);
 
+/* The same two rounding stages without the offset and the clamp:
+ * RoundingDivideByPOT(SRDHM(acc, multiplier), right_shift). */
+int32_t orc_rounding_stages(int32_t acc, int32_t multiplier, int32_t right_shift);
+
 /* GetBiasData, mace/ops/arm/q8/quantization_util.cc:20-46.  bias may be NULL
  * (zeros are produced). out has `channels` entries. */
 void orc_get_bias_data(const int32_t *bias, float bias_scale,

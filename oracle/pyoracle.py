@@ -43,6 +43,8 @@ def lib():
         _lib = C.CDLL(_LIB_PATH)
         _lib.orc_requant_fixed.restype = C.c_uint8
         _lib.orc_requant_fixed.argtypes = [_i32, _i32, _i32, _i32]
+        _lib.orc_rounding_stages.restype = _i32
+        _lib.orc_rounding_stages.argtypes = [_i32, _i32, _i32]
         _lib.orc_adjust_range_u8.restype = None
         _lib.orc_adjust_range_u8.argtypes = [_f32, _f32, _int, _f32p, _i32p]
         _lib.orc_quantize_u8.restype = None
@@ -114,6 +116,10 @@ def output_multiplier_and_shift(ls, rs, os_):
 
 def requant_fixed(acc, mult, shift, zp):
     return int(lib().orc_requant_fixed(int(acc), int(mult), int(shift), int(zp)))
+
+
+def rounding_stages(acc, mult, shift):
+    return int(lib().orc_rounding_stages(int(acc), int(mult), int(shift)))
 
 
 def get_bias_data(bias, bias_scale, in_scale, f_scale, channels):

@@ -115,6 +115,8 @@ def _conv_case(ctx, orc, N, H, W, C, O, KH, KW, stride, padding, seed=0):
     (1, 16, 16, 64, 64, 1, 1, 1, "VALID"),
     (9, 7, 9, 32, 128, 1, 1, 1, "SAME"),
     (1, 32, 32, 3, 32, 3, 3, 2, "SAME"),      # MobileNet stem shape (reduced size)
+    (2, 17, 19, 3, 10, 3, 3, 1, "VALID"),     # 3-channel input, O not a multiple of 4
+    (1, 9, 9, 3, 7, 3, 3, 3, "SAME"),
     (2, 17, 19, 32, 64, 3, 3, 1, "SAME"),     # patch gather + tensor-core GEMM
     (1, 31, 33, 16, 24, 3, 3, 2, "VALID"),
     (1, 15, 17, 8, 16, 5, 5, 1, "FULL"),

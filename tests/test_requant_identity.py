@@ -1,0 +1,43 @@
+"""The single-expression requantization used by the CUDA epilogues equals the two-step
+gemmlowp definition (SRDHM, then rounding right shift) that the oracle implements.
+
+Device formula (mace_b200/csrc/common.cuh, mb_requant_fast), modelled here with Python
+integers:  y = (acc*mult + 2^30 + [s>=1]*2^(s+30) - [s>=1]*[acc<0]*2^31) >> (31 + s)
+"""
+import numpy as np
+
+
+def device_formula(acc, mult, s):
+    c64 = (1 << 30) + ((1 << (s + 30)) if s >= 1 else 0)
+    neg = -(1 << 31) if s >= 1 else 0
+    t = acc * mult + c64 + (1 if acc < 0 else 0) * neg
+    assert -(1 << 63) <= t < (1 << 63)  # fits the 64-bit register pair
+    return t >> (31 + s)
+
+
+def test_identity_on_edges_ties_and_random_values(orc):
+    rng = np.random.default_rng(0)
+    edges = [0, 1, -1, 2, -2, 3, -3, 5, -5, 2 ** 31 - 1, -2 ** 31, 2 ** 30, -2 ** 30, 2 ** 30 + 1,
+             -2 ** 30 - 1, 65025 * 4096, -65025 * 4096]
+    mults = [2 ** 30, 2 ** 30 + 1, 2 ** 31 - 1, 1374221056, 1392511872]
+    for s in range(0, 32):
+        ms = mults + [int(m) for m in rng.integers(2 ** 30, 2 ** 31, size=3)]
+        for m in ms:
+            accs = edges + [int(a) for a in rng.integers(-2 ** 31, 2 ** 31, size=40)]
+            accs += [int(a) for a in rng.integers(-70000, 70000, size=40)]
+            # exact ties of the second stage: x = k * 2^s + 2^(s-1) needs acc ~ x * 2^31 / m
+            for k in (-3, -1, 0, 1, 2):
+                x = k * (1 << s) + ((1 << s) >> 1)
+                a = (x << 31) // m
+                accs += [a - 1, a, a + 1]
+            for a in accs:
+                if not (-2 ** 31 <= a < 2 ** 31):
+                    continue
+                assert device_formula(a, m, s) == orc.rounding_stages(a, m, s), (a, m, s)
+
+
+def test_identity_exhaustive_small_range(orc):
+    for s in (0, 1, 2, 3, 7):
+        for m in (2 ** 30, 3 * 2 ** 29, 2 ** 31 - 1):
+            for a in range(-3000, 3001):
+                assert device_formula(a, m, s) == orc.rounding_stages(a, m, s), (a, m, s)
