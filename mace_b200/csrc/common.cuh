@@ -40,6 +40,7 @@ struct mb_context {
   uint64_t launches = 0;         // kernels launched through this context
   uint64_t launches_tc = 0;      // of which tcgen05 GEMM launches
   int capturing = 0;             // inside mb_graph_begin / mb_graph_end
+  long long *tc_timeline = nullptr;  // optional device buffer: per-role clock stamps of CTA 0
   uint64_t capture_launches0 = 0, capture_launches_tc0 = 0;
   uint64_t func_attr_mask = 0;   // kernels whose shared-memory limit was raised
   char last_error[512] = {0};

@@ -266,6 +266,15 @@ int mb_graph_destroy(mb_context *ctx, void *graph_exec) {
   return MB_SUCCESS;
 }
 
+// Profiling aid, not part of the public header: give the tensor-core GEMM a
+// device buffer of 32 long longs into which CTA 0 writes clock stamps of its
+// pipeline milestones (null switches it off).
+int mb_internal_set_tc_timeline(mb_context *ctx, long long *device_buffer) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  ctx->tc_timeline = device_buffer;
+  return MB_SUCCESS;
+}
+
 void *mb_stream(mb_context *ctx) { return ctx ? ctx->stream : nullptr; }
 
 uint64_t mb_launch_count(const mb_context *ctx) { return ctx ? ctx->launches : 0; }

@@ -277,7 +277,10 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
                           a_batched, b_batched, zp_a, zp_b, mult, shift, zp_c, bias_per_row);
   }
   const int64_t nb_a = a_batched ? batch : 1, nb_b = b_batched ? batch : 1;
-  const bool need_sum_a = zp_b != 0, need_sum_b = zp_a != 0;
+  // K-major operands with K <= 1024: the tensor-core kernel sums the operand
+  // bytes itself from the tiles it has in shared memory.
+  const bool fused_sums = !(a_mn && !a_copy) && !(b_mn && !b_copy) && K <= 1024;
+  const bool need_sum_a = zp_b != 0 && !fused_sums, need_sum_b = zp_a != 0 && !fused_sums;
   size_t off = 0;
   const size_t off_sum_a = off; off += need_sum_a ? align_up(sizeof(uint32_t) * nb_a * M, 256) : 0;
   const size_t off_sum_b = off; off += need_sum_b ? align_up(sizeof(uint32_t) * nb_b * N, 256) : 0;

@@ -12,13 +12,25 @@
 //   acc = raw - zp_b * rowsum_A[m] - zp_a * colsum_B[n] + K * zp_a * zp_b
 // then + bias, fixed-point requantization, + zp_c, clamp, store.
 //
-// Structure (one persistent CTA per SM, 320 threads):
-//   warp 0      TMA producer: 128-byte-swizzled tiles of A and B into a
-//               multi-stage shared-memory ring (mbarrier full/empty pairs)
-//   warp 1      MMA issuer: one thread issues tcgen05.mma 128 x BN x 32 steps
-//               into one of two TMEM accumulator buffers
-//   warps 2..9  epilogue: tcgen05.ld the finished accumulator, correct,
-//               requantize and store while the next tile is being multiplied
+// Structure (one persistent CTA per SM, 704 threads):
+//   warp 0       TMA producer: 128-byte-swizzled tiles of A and B into a
+//                multi-stage shared-memory ring (mbarrier full/empty pairs)
+//   warp 1       MMA issuer: one thread issues tcgen05.mma 128 x BN x 32 steps
+//                into one of two TMEM accumulator buffers
+//   warps 2..5   preparation: per tile, the row and column terms of the
+//                epilogue (zero-point corrections, bias) into shared memory.
+//                With FUSE_SUMS they also add up the operand bytes of every
+//                stage straight from the tiles in shared memory, so the
+//                correction needs no extra pass over the operands; that mode
+//                serves K-major operands with K <= 1024 (pointwise
+//                convolutions), where the tensor pipe has time to spare.
+//                Large-K GEMMs take their sums from separate kernels, because
+//                the extra shared-memory reads would slow their main loop.
+//   warps 6..21  epilogue: 16 warps, four per TMEM lane quarter, each on its
+//                own 16-column chunks: tcgen05.ld (the next chunk is in flight
+//                while the current one is processed), add the terms,
+//                requantize, pack, store 16-byte row segments, while the next
+//                tile is being multiplied.
 // Every wait is bounded; on a timeout the kernel records a status word, lets
 // outstanding copies land, frees its TMEM and returns.
 #include "common.cuh"
@@ -31,8 +43,11 @@ using namespace sm100;
 constexpr int BM = 128;        // rows of A per tile == TMEM lanes
 constexpr int BK = 128;        // bytes of K per pipeline stage (one swizzle row)
 constexpr int UMMA_K = 32;     // K per tcgen05.mma for 8-bit operands
-constexpr int EPI_WARPS = 8;
-constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
+constexpr int PREP_WARPS = 4;
+constexpr int EPI_WARPS = 16;
+constexpr int FIRST_EPI_WARP = 2 + PREP_WARPS;
+constexpr int NUM_THREADS = (2 + PREP_WARPS + EPI_WARPS) * 32;
+constexpr int CHUNK = 16;      // accumulator columns per tcgen05.ld
 constexpr long long WAIT_BUDGET = 1ll << 31;  // ~1 s of SM clocks per wait
 constexpr uint32_t SWIZZLE_128B = 2;
 
@@ -40,8 +55,8 @@ struct TcParams {
   int64_t M, N, K, batch;
   int tiles_m, tiles_n, k_blocks;
   int64_t total_tiles;
-  const uint32_t *sum_a;  // [batch or 1][M]; may be null when zp_b == 0
-  const uint32_t *sum_b;  // [batch or 1][N]; may be null when zp_a == 0
+  const uint32_t *sum_a;  // [batch or 1][M]; null when fused or zp_b == 0
+  const uint32_t *sum_b;  // [batch or 1][N]; null when fused or zp_a == 0
   int64_t sum_a_bstride, sum_b_bstride;
   int a_batched, b_batched;
   const int32_t *bias;
@@ -52,7 +67,14 @@ struct TcParams {
   int out_is_int32;
   int vec_store_ok;  // rows of C are 16-byte aligned
   int *status;
+  long long *timeline;  // null, or 32 clock stamps written by CTA 0 (profiling aid)
 };
+
+// Clock stamp of a pipeline milestone, CTA 0 only, when a buffer was given.
+#define MB_STAMP(slot)                                                    \
+  do {                                                                    \
+    if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[slot] = clock64(); \
+  } while (0)
 
 template <int BN, bool B_MN>
 struct TileCfg {
@@ -60,11 +82,23 @@ struct TileCfg {
   static constexpr int B_BYTES = B_MN ? ((BN + 127) / 128) * 128 * BK : BN * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  // all 512 TMEM columns as accumulator buffers: 2 for BN = 256, 4 for 128, 8 for 64, so
+  // that narrow tiles (short main loops) keep several tiles in flight
+  static constexpr int NUM_ACC = 512 / BN;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int TERM_BYTES = NUM_ACC * (128 + BN) * 4;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + BAR_BYTES + TERM_BYTES;
 };
 
-template <int BN, bool A_MN, bool B_MN>
+__device__ __forceinline__ uint32_t sum16(const uint4 v, uint32_t s) {
+  s = __dp4a(v.x, 0x01010101u, s);
+  s = __dp4a(v.y, 0x01010101u, s);
+  s = __dp4a(v.z, 0x01010101u, s);
+  return __dp4a(v.w, 0x01010101u, s);
+}
+
+template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const TcParams p) {
@@ -75,26 +109,34 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
   // barrier block after the tile ring
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem_aligned + STAGES * Cfg::STAGE_BYTES);
-  const uint32_t full_bar = smem_u32(bars);                  // [STAGES]
-  const uint32_t empty_bar = full_bar + 8 * STAGES;          // [STAGES]
-  const uint32_t tfull_bar = empty_bar + 8 * STAGES;         // [2]
-  const uint32_t tempty_bar = tfull_bar + 16;                // [2]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+  const uint32_t full_bar = smem_u32(bars);                  // [STAGES] tile landed
+  const uint32_t empty_bar = full_bar + 8 * STAGES;          // [STAGES] tile consumed
+  constexpr int NUM_ACC = Cfg::NUM_ACC;
+  const uint32_t tfull_bar = empty_bar + 8 * STAGES;         // [NUM_ACC] accumulator complete
+  const uint32_t tempty_bar = tfull_bar + 8 * NUM_ACC;       // [NUM_ACC] accumulator drained
+  const uint32_t terms_bar = tempty_bar + 8 * NUM_ACC;       // [NUM_ACC] epilogue terms ready
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 3 * NUM_ACC);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  // per accumulator buffer: row terms [128] and column terms [BN]
+  int32_t *row_term_sm =
+      reinterpret_cast<int32_t *>(smem_aligned + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES);
+  int32_t *col_term_sm = row_term_sm + NUM_ACC * 128;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    MB_STAMP(0);
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar + 8 * s, 1);
-      mbar_init(empty_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, FUSE_SUMS ? 1 + PREP_WARPS : 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < NUM_ACC; ++b) {
       mbar_init(tfull_bar + 8 * b, 1);
       mbar_init(tempty_bar + 8 * b, EPI_WARPS);
+      mbar_init(terms_bar + 8 * b, PREP_WARPS);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -107,12 +149,15 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) MB_STAMP(1);
 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
+    // The whole warp walks the loop (one lane issues) so that the warp reaches
+    // the block-wide barrier at the end of the kernel as one.
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -122,28 +167,32 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
         const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, WAIT_BUDGET)) {
+          if (!mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, WAIT_BUDGET)) {
             *abort_flag = 1;
             atomicCAS(p.status, 0, MB_DEV_TIMEOUT_PRODUCER);
             ok = false;
             break;
           }
-          const uint32_t fb = full_bar + 8 * stage;
-          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
-          const uint32_t sb = sa + Cfg::A_BYTES;
-          mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
-          if (A_MN) {
-            tma_load_3d(sa, &tmap_a, fb, tm * BM, kb * BK, ab);
-          } else {
-            tma_load_3d(sa, &tmap_a, fb, kb * BK, tm * BM, ab);
-          }
-          if (B_MN) {
+          if (lane == 0) {
+            const uint32_t fb = full_bar + 8 * stage;
+            const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+            const uint32_t sb = sa + Cfg::A_BYTES;
+            mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
+            if (A_MN) {
+              tma_load_3d(sa, &tmap_a, fb, tm * BM, kb * BK, ab);
+            } else {
+              tma_load_3d(sa, &tmap_a, fb, kb * BK, tm * BM, ab);
+            }
+            if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < (BN + 127) / 128; ++j)
-              tma_load_3d(sb + j * 128 * BK, &tmap_b, fb, tn * BN + j * 128, kb * BK, bb);
-          } else {
-            tma_load_3d(sb, &tmap_b, fb, kb * BK, tn * BN, bb);
+              for (int j = 0; j < (BN + 127) / 128; ++j)
+                tma_load_3d(sb + j * 128 * BK, &tmap_b, fb, tn * BN + j * 128, kb * BK, bb);
+            } else {
+              tma_load_3d(sb, &tmap_b, fb, kb * BK, tn * BN, bb);
+            }
+            if (tile == 0) MB_STAMP(2 + (kb < 3 ? kb : 3));  // TMA of k-block kb issued
           }
+          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -153,7 +202,8 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // Whole warp in the loop, one lane issues (see the producer).
+    {
       constexpr uint32_t idesc = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, A_MN, B_MN, BM, BN);
       int stage = 0;
       uint32_t phase = 0;
@@ -161,7 +211,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-        if (!mbar_wait(tempty_bar + 8 * acc_buf, acc_phase ^ 1, abort_flag, WAIT_BUDGET)) {
+        if (!mbar_wait_warp(tempty_bar + 8 * acc_buf, acc_phase ^ 1, abort_flag, WAIT_BUDGET)) {
           *abort_flag = 1;
           atomicCAS(p.status, 0, MB_DEV_TIMEOUT_MMA);
           break;
@@ -169,18 +219,20 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc_buf * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, WAIT_BUDGET)) {
+          if (!mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, WAIT_BUDGET)) {
             *abort_flag = 1;
             atomicCAS(p.status, 0, MB_DEV_TIMEOUT_MMA);
             ok = false;
             break;
           }
           tc_fence_after_sync();
+          if (tile == 0) MB_STAMP(6 + (kb < 3 ? kb : 3));  // k-block kb landed
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + Cfg::A_BYTES;
           const int64_t k_left = p.K - static_cast<int64_t>(kb) * BK;
           const int ksteps = k_left >= BK ? BK / UMMA_K
                                           : static_cast<int>((k_left + UMMA_K - 1) / UMMA_K);
+          if (lane == 0) {
 #pragma unroll 4
           for (int j = 0; j < ksteps; ++j) {
             // K-major tile: rows of 128 bytes, 8-row groups 1024 bytes apart;
@@ -197,107 +249,187 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             mma_i8_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || j > 0) ? 1u : 0u);
           }
           mma_commit(empty_bar + 8 * stage);  // frees the stage when the MMAs have read it
+          }
+          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        mma_commit(tfull_bar + 8 * acc_buf);  // accumulator complete
-        acc_buf ^= 1;
-        if (acc_buf == 0) acc_phase ^= 1;
+        if (lane == 0) {
+          mma_commit(tfull_bar + 8 * acc_buf);  // accumulator complete
+          if (tile == 0) MB_STAMP(10);
+        }
+        __syncwarp();
+        if (++acc_buf == NUM_ACC) {
+          acc_buf = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else if (warp < FIRST_EPI_WARP) {
+    // ---------------- preparation: operand sums (fused) and epilogue terms ----------------
+    const int r = (warp - 2) * 32 + lane;  // 0..127: row of the A tile / column slot
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc_buf = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+      const int b = static_cast<int>(tile / tiles_per_batch);
+      const int rem = static_cast<int>(tile % tiles_per_batch);
+      const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
+      uint32_t sa_sum = 0, sb_sum[(BN + 127) / 128];
+#pragma unroll
+      for (int j = 0; j < (BN + 127) / 128; ++j) sb_sum[j] = 0;
+      // global inputs of the terms, requested before the main loop is followed
+      const int64_t m = static_cast<int64_t>(tm) * BM + r;
+      int32_t row_bias = 0, col_bias[(BN + 127) / 128];
+      if (p.bias != nullptr && p.bias_per_row && m < p.M) row_bias = __ldg(p.bias + m);
+      if (!FUSE_SUMS && p.sum_a != nullptr && m < p.M)
+        sa_sum = __ldg(p.sum_a + (p.a_batched ? b : 0) * p.sum_a_bstride + m);
+#pragma unroll
+      for (int j = 0; j < (BN + 127) / 128; ++j) {
+        const int64_t n = static_cast<int64_t>(tn) * BN + j * 128 + r;
+        col_bias[j] = (p.bias != nullptr && !p.bias_per_row && n < p.N) ? __ldg(p.bias + n) : 0;
+        if (!FUSE_SUMS && p.sum_b != nullptr && n < p.N)
+          sb_sum[j] = __ldg(p.sum_b + (p.b_batched ? b : 0) * p.sum_b_bstride + n);
+      }
+      if (FUSE_SUMS) {
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, WAIT_BUDGET)) {
+            *abort_flag = 1;
+            atomicCAS(p.status, 0, MB_DEV_TIMEOUT_EPILOGUE);
+            ok = false;
+            break;
+          }
+          const uint8_t *ta = smem_aligned + stage * Cfg::STAGE_BYTES;
+          const uint8_t *tb = ta + Cfg::A_BYTES;
+          // a row is 128 bytes = 8 chunks of 16; start at chunk (r & 7) so that the
+          // 8 threads of a quarter warp hit 8 different bank groups.  The 128-byte
+          // swizzle only permutes chunks inside a row, which a sum does not see.
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            sa_sum = sum16(*reinterpret_cast<const uint4 *>(ta + r * 128 + ((i + r) & 7) * 16), sa_sum);
+#pragma unroll
+          for (int j = 0; j < (BN + 127) / 128; ++j) {
+            const int row = j * 128 + r;
+            if (row < BN) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                sb_sum[j] = sum16(*reinterpret_cast<const uint4 *>(tb + row * 128 + ((i + r) & 7) * 16),
+                                  sb_sum[j]);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty_bar + 8 * stage);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+      }
+      // terms of this tile (operand sums are zero where no correction is needed)
+      const int32_t row_term = row_bias - p.zp_b * static_cast<int32_t>(sa_sum);
+      int32_t col_term[(BN + 127) / 128];
+#pragma unroll
+      for (int j = 0; j < (BN + 127) / 128; ++j)
+        col_term[j] = p.kzz + col_bias[j] - p.zp_a * static_cast<int32_t>(sb_sum[j]);
+      // the terms of this buffer's previous tile must have been consumed
+      if (!mbar_wait_warp(tempty_bar + 8 * acc_buf, acc_phase ^ 1, abort_flag, WAIT_BUDGET)) {
+        *abort_flag = 1;
+        atomicCAS(p.status, 0, MB_DEV_TIMEOUT_EPILOGUE);
+        break;
+      }
+      row_term_sm[acc_buf * 128 + r] = row_term;
+#pragma unroll
+      for (int j = 0; j < (BN + 127) / 128; ++j)
+        if (j * 128 + r < BN) col_term_sm[acc_buf * BN + j * 128 + r] = col_term[j];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(terms_bar + 8 * acc_buf);
+      if (tile == 0 && warp == 2 && lane == 0) MB_STAMP(11);
+      if (++acc_buf == NUM_ACC) {
+        acc_buf = 0;
+        acc_phase ^= 1;
       }
     }
   } else {
     // ---------------- epilogue ----------------
-    const int ew = warp - 2;
-    const int quarter = warp & 3;          // TMEM lanes [32*quarter, +32) are this warp's
-    const int col_half = ew >> 2;          // two warps share a lane quarter, split columns
-    constexpr int CHUNKS = BN / 32;
-    constexpr int CHUNKS_PER_WARP = CHUNKS >= 2 ? CHUNKS / 2 : 1;
+    const int quarter = warp & 3;                      // TMEM lanes [32*quarter, +32) are this warp's
+    const int col_group = (warp - FIRST_EPI_WARP) >> 2;  // 0..3: which chunks of the tile
+    constexpr int CHUNKS = BN / CHUNK;
+    constexpr int PER_WARP = CHUNKS / 4;               // BN = 64 -> 1, 128 -> 2, 256 -> 4
     int acc_buf = 0;
     uint32_t acc_phase = 0;
     for (int64_t tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
       const int b = static_cast<int>(tile / tiles_per_batch);
       const int rem = static_cast<int>(tile % tiles_per_batch);
       const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
-      if (!mbar_wait(tfull_bar + 8 * acc_buf, acc_phase, abort_flag, WAIT_BUDGET)) {
+      if (!mbar_wait_warp(tfull_bar + 8 * acc_buf, acc_phase, abort_flag, WAIT_BUDGET) ||
+          !mbar_wait_warp(terms_bar + 8 * acc_buf, acc_phase, abort_flag, WAIT_BUDGET)) {
         *abort_flag = 1;
         atomicCAS(p.status, 0, MB_DEV_TIMEOUT_EPILOGUE);
         break;
       }
       tc_fence_after_sync();
+      if (tile == 0 && warp == FIRST_EPI_WARP && lane == 0) MB_STAMP(12);
       const int64_t m = static_cast<int64_t>(tm) * BM + quarter * 32 + lane;
       const bool row_ok = m < p.M;
-      int32_t row_term = 0;
-      if (row_ok) {
-        if (p.sum_a != nullptr)
-          row_term -= p.zp_b * static_cast<int32_t>(
-                                   p.sum_a[(p.a_batched ? b : 0) * p.sum_a_bstride + m]);
-        if (p.bias != nullptr && p.bias_per_row) row_term += p.bias[m];
-      }
-      const uint32_t *sum_b = p.sum_b ? p.sum_b + (p.b_batched ? b : 0) * p.sum_b_bstride : nullptr;
+      const int32_t row_term = row_term_sm[acc_buf * 128 + quarter * 32 + lane];
       uint8_t *c8 = static_cast<uint8_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
       int32_t *c32 = static_cast<int32_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
-      if (CHUNKS >= 2 || col_half == 0) {
-#pragma unroll 1
-        for (int ci = 0; ci < CHUNKS_PER_WARP; ++ci) {
-          const int chunk = col_half * CHUNKS_PER_WARP + ci;
-          const int64_t n0 = static_cast<int64_t>(tn) * BN + chunk * 32;
-          if (n0 >= p.N) break;  // uniform across the warp
-          uint32_t r[32];
-          const uint32_t taddr =
-              tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BN + chunk * 32;
-          tmem_ld_32x32b_x32(taddr, r);
-          // column term of this lane's column, broadcast by shuffle below
-          int32_t col_term = p.kzz;
-          const int64_t nl = n0 + lane;
-          if (nl < p.N) {
-            if (sum_b != nullptr) col_term -= p.zp_a * static_cast<int32_t>(sum_b[nl]);
-            if (p.bias != nullptr && !p.bias_per_row) col_term += p.bias[nl];
+      const uint32_t tbase =
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BN;
+      uint32_t r[2][CHUNK];
+      // chunk indices of this warp: col_group * PER_WARP + i (contiguous columns)
+      tmem_ld_32x32b_x16(tbase + (col_group * PER_WARP) * CHUNK, r[0]);
+#pragma unroll
+      for (int i = 0; i < PER_WARP; ++i) {
+        const int chunk = col_group * PER_WARP + i;
+        const int64_t n0 = static_cast<int64_t>(tn) * BN + chunk * CHUNK;
+        tmem_ld_wait_x16(r[i & 1]);
+        if (i + 1 < PER_WARP) tmem_ld_32x32b_x16(tbase + (chunk + 1) * CHUNK, r[(i + 1) & 1]);
+        if (n0 >= p.N) continue;  // uniform across the warp; the loads above stay aligned
+        const int4 *ct = reinterpret_cast<const int4 *>(col_term_sm + acc_buf * BN + chunk * CHUNK);
+        int32_t v[CHUNK];
+#pragma unroll
+        for (int q = 0; q < CHUNK / 4; ++q) {
+          const int4 t = ct[q];  // broadcast read: all lanes, same address
+          v[4 * q + 0] = static_cast<int32_t>(r[i & 1][4 * q + 0]) + row_term + t.x;
+          v[4 * q + 1] = static_cast<int32_t>(r[i & 1][4 * q + 1]) + row_term + t.y;
+          v[4 * q + 2] = static_cast<int32_t>(r[i & 1][4 * q + 2]) + row_term + t.z;
+          v[4 * q + 3] = static_cast<int32_t>(r[i & 1][4 * q + 3]) + row_term + t.w;
+        }
+        if (p.out_is_int32) {
+          if (row_ok) {
+            if (p.vec_store_ok && n0 + CHUNK <= p.N) {
+              uint4 *dst = reinterpret_cast<uint4 *>(c32 + n0);
+#pragma unroll
+              for (int q = 0; q < CHUNK / 4; ++q)
+                dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < CHUNK; ++j)
+                if (n0 + j < p.N) c32[n0 + j] = v[j];
+            }
           }
-          tmem_ld_wait();
-          if (p.out_is_int32) {
-            int32_t v[32];
+        } else {
+          uint32_t packed[CHUNK / 4];
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              v[j] = static_cast<int32_t>(r[j]) + row_term + __shfl_sync(0xffffffffu, col_term, j);
-            if (row_ok) {
-              if (p.vec_store_ok && n0 + 32 <= p.N) {
-                uint4 *dst = reinterpret_cast<uint4 *>(c32 + n0);
+          for (int q = 0; q < CHUNK / 4; ++q) {
+            packed[q] = mb_requant_fast(v[4 * q], p.rq) | (mb_requant_fast(v[4 * q + 1], p.rq) << 8) |
+                        (mb_requant_fast(v[4 * q + 2], p.rq) << 16) |
+                        (mb_requant_fast(v[4 * q + 3], p.rq) << 24);
+          }
+          if (row_ok) {
+            if (p.vec_store_ok && n0 + CHUNK <= p.N) {
+              *reinterpret_cast<uint4 *>(c8 + n0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            } else {
 #pragma unroll
-                for (int q = 0; q < 8; ++q)
-                  dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (n0 + j < p.N) c32[n0 + j] = v[j];
-              }
-            }
-          } else {
-            uint32_t packed[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              uint32_t w = 0;
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int j = 4 * q + e;
-                const int32_t acc = static_cast<int32_t>(r[j]) + row_term +
-                                    __shfl_sync(0xffffffffu, col_term, j);
-                w |= mb_requant_fast(acc, p.rq) << (8 * e);
-              }
-              packed[q] = w;
-            }
-            if (row_ok) {
-              if (p.vec_store_ok && n0 + 32 <= p.N) {
-                uint4 *dst = reinterpret_cast<uint4 *>(c8 + n0);
-                dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (n0 + j < p.N) c8[n0 + j] = static_cast<uint8_t>(packed[j >> 2] >> (8 * (j & 3)));
-              }
+              for (int j = 0; j < CHUNK; ++j)
+                if (n0 + j < p.N) c8[n0 + j] = static_cast<uint8_t>(packed[j >> 2] >> (8 * (j & 3)));
             }
           }
         }
@@ -305,12 +437,16 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar + 8 * acc_buf);
-      acc_buf ^= 1;
-      if (acc_buf == 0) acc_phase ^= 1;
+      if (warp == FIRST_EPI_WARP && lane == 0) MB_STAMP(tile == 0 ? 13 : 14);
+      if (++acc_buf == NUM_ACC) {
+        acc_buf = 0;
+        acc_phase ^= 1;
+      }
     }
   }
 
   __syncthreads();
+  if (threadIdx.x == 0) MB_STAMP(15);
   if (*abort_flag != 0) {
     // Give copies and MMAs that are still in flight time to land before the
     // shared memory and TMEM they target go away (bounded: about 2 ms).
@@ -345,13 +481,14 @@ int make_map_u8(mb_context *ctx, CUtensorMap *map, const void *base, uint64_t in
   return MB_SUCCESS;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS = false>
 int launch_cfg(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, TcParams &p) {
   using Cfg = TileCfg<BN, B_MN>;
-  auto kern = gemm_u8_tc_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_u8_tc_kernel<BN, A_MN, B_MN, FUSE_SUMS>;
   // The opt-in shared-memory limit is a per-device function attribute; set it
   // once per context.
-  constexpr int cfg_id = (BN == 256 ? 0 : BN == 128 ? 1 : 2) * 4 + (A_MN ? 2 : 0) + (B_MN ? 1 : 0);
+  constexpr int cfg_id = (BN == 256 ? 0 : BN == 128 ? 1 : 2) * 4 + (A_MN ? 2 : 0) + (B_MN ? 1 : 0) +
+                         (FUSE_SUMS ? 12 : 0);
   if (!(ctx->func_attr_mask & (1ull << cfg_id))) {
     MB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg::SMEM_BYTES));
@@ -394,20 +531,32 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
                          int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
                          int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
                          int bias_per_row) {
-  int BN = 256;
+  // Operand sums computed inside the kernel: K-major operands, short K, and the
+  // caller passed no precomputed sums although a zero point needs them.
+  const bool fuse = !a_mn && !b_mn && K <= 8 * BK && sum_a == nullptr && sum_b == nullptr &&
+                    (zp_a != 0 || zp_b != 0);
+  // Tile width.  Long main loops (K > 1024) want the widest tile for operand
+  // reuse.  Short ones are bound by the epilogue, whose cost grows with the
+  // width, plus a fixed cost per tile: pick the width with the fewest rounds
+  // of (width + overhead) over the SMs.
+  int BN = 64;
   {
-    // Prefer the widest tile that still gives every SM a tile.
     const int64_t tm = ceil_div64(M, BM);
     const int widths[3] = {256, 128, 64};
-    BN = 64;
+    int64_t best = -1;
     for (int w : widths) {
-      if (N >= w && batch * tm * ceil_div64(N, w) >= ctx->num_sms) {
+      if (w > 64 && N <= w / 2) continue;  // more than half of the tile would be padding
+      const int64_t rounds = ceil_div64(batch * tm * ceil_div64(N, w), ctx->num_sms);
+      const int64_t cost = rounds * (w + 96);
+      if (K > 1024) {  // widest admissible width wins
         BN = w;
         break;
       }
+      if (best < 0 || cost < best) {
+        best = cost;
+        BN = w;
+      }
     }
-    if (N <= 64) BN = 64;
-    else if (N <= 128 && BN > 128) BN = 128;
   }
   TcParams p;
   p.M = M; p.N = N; p.K = K; p.batch = batch;
@@ -428,6 +577,7 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.vec_store_ok = out_is_int32 ? ((cbase % 16 == 0) && (N % 4 == 0))
                                 : ((cbase % 16 == 0) && (N % 16 == 0));
   p.status = ctx->dev_status;
+  p.timeline = ctx->tc_timeline;
 
   CUtensorMap ta, tb;
   const uint64_t nb_a = a_batched ? batch : 1, nb_b = b_batched ? batch : 1;
@@ -449,6 +599,11 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   } else {                                                                          \
     if (b_mn) return launch_cfg<BN_, false, true>(ctx, ta, tb, p);                  \
     return launch_cfg<BN_, false, false>(ctx, ta, tb, p);                           \
+  }
+  if (fuse) {
+    if (BN == 256) return launch_cfg<256, false, false, true>(ctx, ta, tb, p);
+    if (BN == 128) return launch_cfg<128, false, false, true>(ctx, ta, tb, p);
+    return launch_cfg<64, false, false, true>(ctx, ta, tb, p);
   }
   if (BN == 256) { MB_TC_DISPATCH(256) }
   if (BN == 128) { MB_TC_DISPATCH(128) }

@@ -77,6 +77,37 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   }
 }
 
+// A wait for roles that are far ahead of the pipeline (producer, preparation):
+// sleeps between polls so that the polling does not take issue slots from the
+// warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
+                                                  volatile int *abort_flag, long long budget) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (true) {
+    __nanosleep(64);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - start > budget) return false;
+  }
+}
+
+// The same for a whole warp that waits together: every lane polls, and the
+// warp takes one common decision, so that it stays converged for the
+// warp-aligned instructions that follow (tcgen05.ld, __syncwarp, ...).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
+                                               volatile int *abort_flag, long long budget) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, budget);
+  return __all_sync(0xffffffffu, ok);
+}
+
+__device__ __forceinline__ bool mbar_wait_warp_relaxed(uint32_t bar, uint32_t parity,
+                                                       volatile int *abort_flag,
+                                                       long long budget) {
+  const bool ok = mbar_wait_relaxed(bar, parity, abort_flag, budget);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---- TMA ----------------------------------------------------------------------
 
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
@@ -180,6 +211,30 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
         "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+
+// 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+        "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+        "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Wait for outstanding tcgen05.ld and tie the destination registers to the
+// wait, so that the compiler cannot schedule arithmetic on them above it (the
+// load writes its registers asynchronously; they are valid only after this).
+__device__ __forceinline__ void tmem_ld_wait_x16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]),
+                 "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]),
+                 "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld_wait() {
