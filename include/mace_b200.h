@@ -154,6 +154,67 @@ int mb_avgpool_u8_nhwc(mb_context *ctx, const uint8_t *in, uint8_t *out,
                        int64_t KW, int stride_h, int stride_w, int pad_top,
                        int pad_left, int64_t Ho, int64_t Wo);
 
+/* ---- fp32 path (NCHW activations, OIHW filters) -----------------------------
+ * Activation codes are ops::ActivationType values (mace/ops/common/
+ * activation_type.h:21-31): 0 NOOP, 1 RELU, 2 RELUX (max_limit), 6 LEAKYRELU
+ * (coefficient).  Bias (per output channel, may be NULL) and activation are
+ * fused into the producing kernel; the CPU operator runs them as two extra
+ * passes (mace/ops/conv_2d.cc:171-173, ref/bias_add.cc:74-103,
+ * ref/activation.cc:61-88). */
+
+/* Batched C = A * B in fp32: replaces ref::Gemm<float> / arm::Gemm<float>
+ * (mace/ops/ref/gemm.cc:57-106, mace/ops/arm/base/gemm.cc:520-683).  Any
+ * row/column-major combination; A is M x K, B is K x N, C is M x N. */
+int mb_gemm_f32(mb_context *ctx, const float *A, const float *B, float *C,
+                int64_t batch, int64_t M, int64_t N, int64_t K, int a_col_major,
+                int b_col_major, int c_col_major, int a_batched, int b_batched);
+
+/* out[b,h] = bias[h] + sum_w lhs[h,w] * rhs[b,w]: replaces ref::Gemv<float> /
+ * arm::Gemv<float> (mace/ops/ref/gemv.cc:45-81, mace/ops/arm/fp32/gemv.cc:37). */
+int mb_gemv_f32(mb_context *ctx, const float *lhs, const float *rhs,
+                const float *bias, float *out, int64_t batch, int64_t rows,
+                int64_t K, int lhs_batched, int rhs_batched);
+
+/* General fp32 Conv2D, NCHW x OIHW -> NCHW: replaces ref::Conv2d<float> and the
+ * NEON general / 1x1 delegators (mace/ops/ref/conv_2d.cc:36-122,
+ * mace/ops/arm/base/conv_2d_general.cc:26-197, conv_2d_1x1.cc:27-72).  A 1x1
+ * stride-1 filter is run as a batched GEMM filter[O x C] * input_n[C x H*W]. */
+int mb_conv2d_f32_nchw(mb_context *ctx, const float *in, const float *filter_oihw,
+                       const float *bias, float *out, int64_t N, int64_t C,
+                       int64_t H, int64_t W, int64_t O, int64_t KH, int64_t KW,
+                       int stride_h, int stride_w, int dil_h, int dil_w,
+                       int pad_top, int pad_left, int64_t Ho, int64_t Wo,
+                       int activation, float max_limit, float coefficient);
+
+/* fp32 depthwise conv, NCHW, filter [multiplier, C, kh, kw]: replaces
+ * ref::DepthwiseConv2d<float> (mace/ops/ref/depthwise_conv_2d.cc:36-125). */
+int mb_dwconv_f32_nchw(mb_context *ctx, const float *in, const float *filter,
+                       const float *bias, float *out, int64_t N, int64_t C,
+                       int64_t H, int64_t W, int64_t channel_multiplier,
+                       int64_t KH, int64_t KW, int stride_h, int stride_w,
+                       int dil_h, int dil_w, int pad_top, int pad_left,
+                       int64_t Ho, int64_t Wo, int activation, float max_limit,
+                       float coefficient);
+
+/* fp32 3x3 stride-1 Conv2D by Winograd, NCHW: replaces
+ * arm::Conv2dK3x3Winograd<float> (mace/ops/arm/base/conv_2d_3x3_winograd.cc:
+ * 31-787): F(6x6,3x3) on 8x8 input tiles when H > 16 and W > 16, else
+ * F(2x2,3x3); tile_override 2 or 6 forces a size.  transformed_filter may be
+ * NULL (the filter is transformed into scratch on every call) or a buffer of
+ * (tile+2)^2 * O * C floats that mb_winograd_transform_filter_f32 filled, the
+ * way the CPU delegator caches it for weights (:120-145). */
+int mb_winograd_transform_filter_f32(mb_context *ctx, const float *filter_oihw,
+                                     float *transformed, int64_t C, int64_t O,
+                                     int tile);
+int mb_conv3x3_winograd_f32_nchw(mb_context *ctx, const float *in,
+                                 const float *filter_oihw,
+                                 const float *transformed_filter,
+                                 const float *bias, float *out, int64_t N,
+                                 int64_t C, int64_t H, int64_t W, int64_t O,
+                                 int pad_top, int pad_left, int64_t Ho,
+                                 int64_t Wo, int activation, float max_limit,
+                                 float coefficient, int tile_override);
+
 /* ---- uint8 GEMM without any allocation ------------------------------------
  * No counterpart in the reference.  For callers that may not allocate device
  * memory (a real-time loop with a fixed memory budget, a plugin inside an

@@ -66,6 +66,13 @@ PROTOTYPES = {
     "mb_dwconv_u8_nhwc": (_int, [_vp] * 5 + [_i64] * 7 + [_int] * 6 + [_i64] * 2 + [_i32] * 5 +
                           [_int, _f32]),
     "mb_avgpool_u8_nhwc": (_int, [_vp] * 3 + [_i64] * 6 + [_int] * 4 + [_i64] * 2),
+    "mb_gemm_f32": (_int, [_vp] * 4 + [_i64] * 4 + [_int] * 5),
+    "mb_gemv_f32": (_int, [_vp] * 5 + [_i64] * 3 + [_int] * 2),
+    "mb_conv2d_f32_nchw": (_int, [_vp] * 5 + [_i64] * 7 + [_int] * 6 + [_i64] * 2 + [_int, _f32, _f32]),
+    "mb_dwconv_f32_nchw": (_int, [_vp] * 5 + [_i64] * 7 + [_int] * 6 + [_i64] * 2 + [_int, _f32, _f32]),
+    "mb_winograd_transform_filter_f32": (_int, [_vp] * 3 + [_i64] * 2 + [_int]),
+    "mb_conv3x3_winograd_f32_nchw": (_int, [_vp] * 6 + [_i64] * 5 + [_int] * 2 + [_i64] * 2 +
+                                     [_int, _f32, _f32, _int]),
     "mb_gemm_u8_static_scratch": (_int, [_vp] * 5 + [_int] + [_i64] * 3 + [_int] * 2 +
                                   [_i32] * 5 + [_int, C.c_char_p, _sz]),
 }
@@ -237,6 +244,42 @@ class Context:
             Mc, KH, KW, strides[0], strides[1], dil[0], dil[1], pad_tl[0], pad_tl[1],
             out_hw[0], out_hw[1], zp_in, zp_f, mult, shift, zp_out,
             int(float_multiplier is not None), float(float_multiplier or 0.0)))
+
+    def gemm_f32(self, A, B, Cout, batch, M, N, K, a_col_major=False, b_col_major=False,
+                 c_col_major=False, a_batched=True, b_batched=True):
+        self._check(lib().mb_gemm_f32(self.h, A.ptr, B.ptr, Cout.ptr, batch, M, N, K,
+                                      int(a_col_major), int(b_col_major), int(c_col_major),
+                                      int(a_batched), int(b_batched)))
+
+    def gemv_f32(self, lhs, rhs, bias, out, batch, rows, K, lhs_batched=False, rhs_batched=True):
+        self._check(lib().mb_gemv_f32(self.h, lhs.ptr, rhs.ptr,
+                                      bias.ptr if bias is not None else None, out.ptr, batch,
+                                      rows, K, int(lhs_batched), int(rhs_batched)))
+
+    def conv2d_f32(self, x, f, bias, out, N, Cc, H, W, O, KH, KW, strides, dil, pad_tl, out_hw,
+                   act=0, max_limit=0.0, coef=0.0):
+        self._check(lib().mb_conv2d_f32_nchw(
+            self.h, x.ptr, f.ptr, bias.ptr if bias is not None else None, out.ptr, N, Cc, H, W,
+            O, KH, KW, strides[0], strides[1], dil[0], dil[1], pad_tl[0], pad_tl[1], out_hw[0],
+            out_hw[1], act, max_limit, coef))
+
+    def dwconv_f32(self, x, f, bias, out, N, Cc, H, W, Mc, KH, KW, strides, dil, pad_tl, out_hw,
+                   act=0, max_limit=0.0, coef=0.0):
+        self._check(lib().mb_dwconv_f32_nchw(
+            self.h, x.ptr, f.ptr, bias.ptr if bias is not None else None, out.ptr, N, Cc, H, W,
+            Mc, KH, KW, strides[0], strides[1], dil[0], dil[1], pad_tl[0], pad_tl[1], out_hw[0],
+            out_hw[1], act, max_limit, coef))
+
+    def winograd_f32(self, x, f, bias, out, N, Cc, H, W, O, pad_tl, out_hw, act=0, max_limit=0.0,
+                     coef=0.0, tile=0, transformed=None):
+        self._check(lib().mb_conv3x3_winograd_f32_nchw(
+            self.h, x.ptr, f.ptr if f is not None else None,
+            transformed.ptr if transformed is not None else None,
+            bias.ptr if bias is not None else None, out.ptr, N, Cc, H, W, O, pad_tl[0],
+            pad_tl[1], out_hw[0], out_hw[1], act, max_limit, coef, tile))
+
+    def winograd_transform_filter(self, f, out, Cc, O, tile):
+        self._check(lib().mb_winograd_transform_filter_f32(self.h, f.ptr, out.ptr, Cc, O, tile))
 
     def avgpool_u8(self, x, out, N, H, W, Cc, kernel, strides, pad_tl, out_hw):
         self._check(lib().mb_avgpool_u8_nhwc(

@@ -1,0 +1,321 @@
+// fp32 kernels of the path: batched GEMM, GEMV, general direct Conv2D and
+// depthwise conv in NCHW, with bias and activation fused into the epilogue.
+//
+// Reference behaviour: ref::Gemm / ref::Gemv / ref::Conv2d / ref::DepthwiseConv2d
+// (mace/ops/ref/gemm.cc:57-106, gemv.cc:45-81, conv_2d.cc:36-122,
+// depthwise_conv_2d.cc:36-125), ref::BiasAdd (bias_add.cc:74-103) and
+// ref::Activation (activation.cc:61-88).  The reference accumulates in fp32 in
+// index order; these kernels accumulate in fp32 in a tiled order, so results
+// agree to rounding (tests bound the difference at 1e-4 of the output range).
+#include "common.cuh"
+
+__device__ __forceinline__ float mb_activate(float x, int act, float max_limit, float coef) {
+  switch (act) {
+    case 1: return fmaxf(0.f, x);
+    case 2: return fmaxf(0.f, fminf(max_limit, x));
+    case 6: return fmaxf(x, 0.f) + fminf(x, 0.f) * coef;
+    default: return x;
+  }
+}
+
+namespace {
+
+// ---- GEMM: 64 x 64 tile per 256-thread block, 4 x 4 outputs per thread ----------
+constexpr int FT = 64;
+constexpr int FK = 16;
+
+struct GemmF32Params {
+  const float *A, *B;
+  float *C;
+  const float *bias;  // per row of C (output channel) or null
+  int64_t M, N, K;
+  int64_t a_rs, a_cs, b_rs, b_cs, c_rs, c_cs;  // element strides
+  int64_t a_bs, b_bs, c_bs;                    // batch strides
+  int act;
+  float max_limit, coef;
+};
+
+__global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32Params p) {
+  __shared__ float As[FK][FT + 4];
+  __shared__ float Bs[FK][FT + 4];
+  const int b = blockIdx.z;
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * FT, n0 = static_cast<int64_t>(blockIdx.x) * FT;
+  const float *A = p.A + b * p.a_bs, *B = p.B + b * p.b_bs;
+  float *C = p.C + b * p.c_bs;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  for (int64_t k0 = 0; k0 < p.K; k0 += FK) {
+    for (int i = threadIdx.x; i < FK * FT; i += 256) {
+      int kk, mm;
+      if (p.a_cs == 1) { kk = i % FK; mm = i / FK; } else { mm = i % FT; kk = i / FT; }
+      const int64_t m = m0 + mm, k = k0 + kk;
+      As[kk][mm] = (m < p.M && k < p.K) ? __ldg(A + m * p.a_rs + k * p.a_cs) : 0.f;
+      int nn;
+      if (p.b_cs == 1) { nn = i % FT; kk = i / FT; } else { kk = i % FK; nn = i / FK; }
+      const int64_t n = n0 + nn, kb = k0 + kk;
+      Bs[kk][nn] = (n < p.N && kb < p.K) ? __ldg(B + kb * p.b_rs + n * p.b_cs) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < FK; ++kk) {
+      const float4 a4 = *reinterpret_cast<const float4 *>(&As[kk][ty * 4]);
+      const float4 b4 = *reinterpret_cast<const float4 *>(&Bs[kk][tx * 4]);
+      const float a[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t m = m0 + ty * 4 + i;
+    if (m >= p.M) continue;
+    const float bv = p.bias != nullptr ? p.bias[m] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t n = n0 + tx * 4 + j;
+      if (n >= p.N) continue;
+      float v = acc[i][j];
+      if (p.bias != nullptr) v += bv;
+      C[m * p.c_rs + n * p.c_cs] = mb_activate(v, p.act, p.max_limit, p.coef);
+    }
+  }
+}
+
+// ---- GEMV: one warp per matrix row ------------------------------------------------
+__global__ void __launch_bounds__(256)
+gemv_f32_kernel(const float *__restrict__ lhs, const float *__restrict__ rhs,
+                const float *__restrict__ bias, float *__restrict__ out, int64_t batch,
+                int64_t rows, int64_t K, int lhs_batched, int rhs_batched, int batch_chunk) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int64_t b0 = static_cast<int64_t>(blockIdx.y) * batch_chunk;
+  const int64_t b1 = min(batch, b0 + batch_chunk);
+  for (int64_t b = b0; b < b1; ++b) {
+    const float *lp = lhs + (lhs_batched ? b * rows * K : 0) + row * K;
+    const float *rp = rhs + (rhs_batched ? b * K : 0);
+    float s = 0.f;
+    for (int64_t i = lane; i < K; i += 32) s = fmaf(__ldg(lp + i), __ldg(rp + i), s);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) out[b * rows + row] = s + (bias != nullptr ? bias[row] : 0.f);
+  }
+}
+
+// ---- direct convolutions ------------------------------------------------------------
+struct ConvF32Params {
+  const float *in, *filter, *bias;
+  float *out;
+  int N, C, H, W, O, KH, KW, sh, sw, dh, dw, pad_t, pad_l, Ho, Wo, mult_ch;
+  int act;
+  float max_limit, coef;
+};
+
+// One thread per output value; the loop order (c, kh, kw) is the reference's.
+__global__ void __launch_bounds__(256) conv2d_f32_direct_kernel(const ConvF32Params p) {
+  const int64_t total = static_cast<int64_t>(p.N) * p.O * p.Ho * p.Wo;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (tid >= total) return;
+  const int w = static_cast<int>(tid % p.Wo);
+  int64_t r = tid / p.Wo;
+  const int h = static_cast<int>(r % p.Ho);
+  r /= p.Ho;
+  const int m = static_cast<int>(r % p.O);
+  const int n = static_cast<int>(r / p.O);
+  float sum = 0.f;
+  for (int c = 0; c < p.C; ++c) {
+    const float *ib = p.in + (static_cast<int64_t>(n) * p.C + c) * p.H * p.W;
+    const float *fp = p.filter + (static_cast<int64_t>(m) * p.C + c) * p.KH * p.KW;
+    for (int kh = 0; kh < p.KH; ++kh) {
+      const int ih = -p.pad_t + h * p.sh + kh * p.dh;
+      if (ih < 0 || ih >= p.H) continue;
+      for (int kw = 0; kw < p.KW; ++kw) {
+        const int iw = -p.pad_l + w * p.sw + kw * p.dw;
+        if (iw < 0 || iw >= p.W) continue;
+        sum = fmaf(__ldg(ib + ih * p.W + iw), __ldg(fp + kh * p.KW + kw), sum);
+      }
+    }
+  }
+  if (p.bias != nullptr) sum += p.bias[m];
+  p.out[tid] = mb_activate(sum, p.act, p.max_limit, p.coef);
+}
+
+__global__ void __launch_bounds__(256) dwconv_f32_kernel(const ConvF32Params p) {
+  const int OC = p.C * p.mult_ch;
+  const int64_t total = static_cast<int64_t>(p.N) * OC * p.Ho * p.Wo;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (tid >= total) return;
+  const int w = static_cast<int>(tid % p.Wo);
+  int64_t r = tid / p.Wo;
+  const int h = static_cast<int>(r % p.Ho);
+  r /= p.Ho;
+  const int m = static_cast<int>(r % OC);
+  const int n = static_cast<int>(r / OC);
+  const int c = m / p.mult_ch, o = m % p.mult_ch;
+  const float *ib = p.in + (static_cast<int64_t>(n) * p.C + c) * p.H * p.W;
+  const float *fp = p.filter + (static_cast<int64_t>(o) * p.C + c) * p.KH * p.KW;
+  float sum = 0.f;
+  for (int kh = 0; kh < p.KH; ++kh) {
+    const int ih = -p.pad_t + h * p.sh + kh * p.dh;
+    if (ih < 0 || ih >= p.H) continue;
+    for (int kw = 0; kw < p.KW; ++kw) {
+      const int iw = -p.pad_l + w * p.sw + kw * p.dw;
+      if (iw < 0 || iw >= p.W) continue;
+      sum = fmaf(__ldg(ib + ih * p.W + iw), __ldg(fp + kh * p.KW + kw), sum);
+    }
+  }
+  if (p.bias != nullptr) sum += p.bias[m];
+  p.out[tid] = mb_activate(sum, p.act, p.max_limit, p.coef);
+}
+
+}  // namespace
+
+// Strided batched fp32 GEMM with optional per-row bias and activation; the
+// building block of the 1x1 convolution and of the Winograd batched product.
+int mb_gemm_f32_strided(mb_context *ctx, const float *A, const float *B, float *C,
+                        const float *bias_per_row, int64_t batch, int64_t M, int64_t N, int64_t K,
+                        int64_t a_rs, int64_t a_cs, int64_t a_bs, int64_t b_rs, int64_t b_cs,
+                        int64_t b_bs, int64_t c_rs, int64_t c_cs, int64_t c_bs, int act,
+                        float max_limit, float coef) {
+  if (batch > 65535 || ceil_div64(M, FT) > 65535)
+    return mb_fail(ctx, MB_UNSUPPORTED, "fp32 GEMM: batch or M too large for this kernel");
+  GemmF32Params p;
+  p.A = A; p.B = B; p.C = C; p.bias = bias_per_row;
+  p.M = M; p.N = N; p.K = K;
+  p.a_rs = a_rs; p.a_cs = a_cs; p.b_rs = b_rs; p.b_cs = b_cs; p.c_rs = c_rs; p.c_cs = c_cs;
+  p.a_bs = a_bs; p.b_bs = b_bs; p.c_bs = c_bs;
+  p.act = act; p.max_limit = max_limit; p.coef = coef;
+  dim3 grid(static_cast<unsigned>(ceil_div64(N, FT)), static_cast<unsigned>(ceil_div64(M, FT)),
+            static_cast<unsigned>(batch));
+  gemm_f32_kernel<<<grid, 256, 0, ctx->stream>>>(p);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+extern "C" {
+
+int mb_gemm_f32(mb_context *ctx, const float *A, const float *B, float *C, int64_t batch,
+                int64_t M, int64_t N, int64_t K, int a_col_major, int b_col_major,
+                int c_col_major, int a_batched, int b_batched) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (batch < 0 || M < 0 || N < 0 || K < 0)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemm_f32: negative dimension");
+  if (batch == 0 || M == 0 || N == 0) return MB_SUCCESS;
+  if (A == nullptr || B == nullptr || C == nullptr)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemm_f32: null operand");
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  return mb_gemm_f32_strided(ctx, A, B, C, nullptr, batch, M, N, K, a_col_major ? 1 : K,
+                             a_col_major ? M : 1, a_batched ? M * K : 0, b_col_major ? 1 : N,
+                             b_col_major ? K : 1, b_batched ? K * N : 0, c_col_major ? 1 : N,
+                             c_col_major ? M : 1, M * N, 0, 0.f, 0.f);
+}
+
+int mb_gemv_f32(mb_context *ctx, const float *lhs, const float *rhs, const float *bias,
+                float *out, int64_t batch, int64_t rows, int64_t K, int lhs_batched,
+                int rhs_batched) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (batch < 0 || rows < 0 || K < 0)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemv_f32: negative dimension");
+  if (batch == 0 || rows == 0) return MB_SUCCESS;
+  if (lhs == nullptr || rhs == nullptr || out == nullptr)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemv_f32: null operand");
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  int64_t chunks = std::min<int64_t>(batch, 65535);
+  if (!lhs_batched)
+    chunks = std::min<int64_t>(chunks, std::max<int64_t>(1, (4ll * ctx->num_sms) / ceil_div64(rows, 8)));
+  const int batch_chunk = static_cast<int>(ceil_div64(batch, chunks));
+  dim3 grid(static_cast<unsigned>(ceil_div64(rows, 8)),
+            static_cast<unsigned>(ceil_div64(batch, batch_chunk)));
+  gemv_f32_kernel<<<grid, 256, 0, ctx->stream>>>(lhs, rhs, bias, out, batch, rows, K, lhs_batched,
+                                                 rhs_batched, batch_chunk);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+static int check_conv_f32(mb_context *ctx, const char *who, const float *in, const float *filter,
+                          float *out, int64_t N, int64_t C, int64_t H, int64_t W, int64_t O,
+                          int64_t KH, int64_t KW, int sh, int sw, int dh, int dw, int pt, int pl,
+                          int64_t Ho, int64_t Wo, int act, bool *empty) {
+  *empty = false;
+  if (N < 0 || C < 1 || H < 1 || W < 1 || O < 1 || KH < 1 || KW < 1 || sh < 1 || sw < 1 ||
+      dh < 1 || dw < 1 || pt < 0 || pl < 0 || Ho < 0 || Wo < 0)
+    return mb_fail(ctx, MB_INVALID_ARGS, "%s: bad shape argument", who);
+  if (!(act == 0 || act == 1 || act == 2 || act == 6))
+    return mb_fail(ctx, MB_UNSUPPORTED, "%s: activation %d is not fused here", who, act);
+  if (N == 0 || Ho == 0 || Wo == 0) {
+    *empty = true;
+    return MB_SUCCESS;
+  }
+  if (in == nullptr || filter == nullptr || out == nullptr)
+    return mb_fail(ctx, MB_INVALID_ARGS, "%s: null operand", who);
+  if (N * O * Ho * Wo >= (1ll << 38) || N * C * H * W >= (1ll << 38))
+    return mb_fail(ctx, MB_UNSUPPORTED, "%s: tensor too large", who);
+  return MB_SUCCESS;
+}
+
+int mb_conv2d_f32_nchw(mb_context *ctx, const float *in, const float *filter, const float *bias,
+                       float *out, int64_t N, int64_t C, int64_t H, int64_t W, int64_t O,
+                       int64_t KH, int64_t KW, int stride_h, int stride_w, int dil_h, int dil_w,
+                       int pad_top, int pad_left, int64_t Ho, int64_t Wo, int activation,
+                       float max_limit, float coefficient) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  bool empty;
+  MB_RETURN_IF_ERROR(check_conv_f32(ctx, "mb_conv2d_f32_nchw", in, filter, out, N, C, H, W, O, KH,
+                                    KW, stride_h, stride_w, dil_h, dil_w, pad_top, pad_left, Ho,
+                                    Wo, activation, &empty));
+  if (empty) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (KH == 1 && KW == 1 && stride_h == 1 && stride_w == 1 && pad_top == 0 && pad_left == 0 &&
+      Ho == H && Wo == W) {
+    // out_n[O x HW] = filter[O x C] * in_n[C x HW] for every image n
+    // (arm::Conv2dK1x1, mace/ops/arm/base/conv_2d_1x1.cc:61-68)
+    const int64_t hw = H * W;
+    return mb_gemm_f32_strided(ctx, filter, in, out, bias, N, O, hw, C, C, 1, 0, hw, 1, C * hw, hw,
+                               1, O * hw, activation, max_limit, coefficient);
+  }
+  ConvF32Params p;
+  p.in = in; p.filter = filter; p.bias = bias; p.out = out;
+  p.N = static_cast<int>(N); p.C = static_cast<int>(C); p.H = static_cast<int>(H); p.W = static_cast<int>(W);
+  p.O = static_cast<int>(O); p.KH = static_cast<int>(KH); p.KW = static_cast<int>(KW);
+  p.sh = stride_h; p.sw = stride_w; p.dh = dil_h; p.dw = dil_w; p.pad_t = pad_top; p.pad_l = pad_left;
+  p.Ho = static_cast<int>(Ho); p.Wo = static_cast<int>(Wo); p.mult_ch = 1;
+  p.act = activation; p.max_limit = max_limit; p.coef = coefficient;
+  const int64_t total = N * O * Ho * Wo;
+  conv2d_f32_direct_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, ctx->stream>>>(p);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+int mb_dwconv_f32_nchw(mb_context *ctx, const float *in, const float *filter, const float *bias,
+                       float *out, int64_t N, int64_t C, int64_t H, int64_t W, int64_t mult_ch,
+                       int64_t KH, int64_t KW, int stride_h, int stride_w, int dil_h, int dil_w,
+                       int pad_top, int pad_left, int64_t Ho, int64_t Wo, int activation,
+                       float max_limit, float coefficient) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  bool empty;
+  MB_RETURN_IF_ERROR(check_conv_f32(ctx, "mb_dwconv_f32_nchw", in, filter, out, N, C, H, W,
+                                    mult_ch, KH, KW, stride_h, stride_w, dil_h, dil_w, pad_top,
+                                    pad_left, Ho, Wo, activation, &empty));
+  if (empty) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  ConvF32Params p;
+  p.in = in; p.filter = filter; p.bias = bias; p.out = out;
+  p.N = static_cast<int>(N); p.C = static_cast<int>(C); p.H = static_cast<int>(H); p.W = static_cast<int>(W);
+  p.O = static_cast<int>(C * mult_ch); p.KH = static_cast<int>(KH); p.KW = static_cast<int>(KW);
+  p.sh = stride_h; p.sw = stride_w; p.dh = dil_h; p.dw = dil_w; p.pad_t = pad_top; p.pad_l = pad_left;
+  p.Ho = static_cast<int>(Ho); p.Wo = static_cast<int>(Wo); p.mult_ch = static_cast<int>(mult_ch);
+  p.act = activation; p.max_limit = max_limit; p.coef = coefficient;
+  const int64_t total = N * C * mult_ch * Ho * Wo;
+  dwconv_f32_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, ctx->stream>>>(p);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,163 @@
+"""fp32 kernels (GEMM, GEMV, general / 1x1 / Winograd Conv2D, depthwise) against the CPU
+oracle.  Tolerance: max |got - ref| <= tol * max |ref| with tol = 1e-4 (Winograd: 1e-3
+against the DIRECT fp32 convolution, as the 3x3 Winograd path is specified), plus the
+reference's own literal known-answer cases."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+PAD = {"VALID": 0, "SAME": 1, "FULL": 2}
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import mace_b200
+    c = mace_b200.Context(0)
+    yield c
+    c.close()
+
+
+def rel_err(got, ref):
+    return float(np.abs(got.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+@pytest.mark.parametrize("maj", [(0, 0, 0), (1, 0, 0), (0, 1, 0), (1, 1, 0), (0, 0, 1), (1, 1, 1)])
+@pytest.mark.parametrize("shape", [(1, 5, 5, 5), (2, 47, 61, 33), (3, 64, 128, 96), (1, 1, 300, 700)])
+def test_gemm_f32(ctx, orc, maj, shape):
+    """Major-order combinations of test/ccunit/mace/ops/arm/fp32/gemm_test.cc:28-121."""
+    batch, M, N, K = shape
+    rng = np.random.Generator(np.random.PCG64(M + N))
+    A = rng.standard_normal((batch, M, K)).astype(np.float32)
+    B = rng.standard_normal((batch, K, N)).astype(np.float32)
+    A_st = np.ascontiguousarray(np.swapaxes(A, 1, 2)) if maj[0] else A
+    B_st = np.ascontiguousarray(np.swapaxes(B, 1, 2)) if maj[1] else B
+    dA, dB, dC = ctx.upload(A_st), ctx.upload(B_st), ctx.alloc(batch * M * N * 4)
+    ctx.gemm_f32(dA, dB, dC, batch, M, N, K, bool(maj[0]), bool(maj[1]), bool(maj[2]))
+    got = ctx.download(dC, (batch * M * N,), np.float32)
+    ref = orc.gemm_f32(A_st, B_st, batch, M, N, K, bool(maj[0]), bool(maj[1]), bool(maj[2]))
+    assert rel_err(got, ref) <= 1e-4
+    for b in (dA, dB, dC):
+        b.free()
+
+
+def test_gemm_f32_literals_and_one_side_batched(ctx, orc):
+    a = np.arange(1, 7, dtype=np.float32)  # matmul_test.cc:55-58
+    dA, dC = ctx.upload(a), ctx.alloc(16)
+    ctx.gemm_f32(dA, dA, dC, 1, 2, 2, 3)
+    assert ctx.download(dC, (4,), np.float32).tolist() == [22, 28, 49, 64]
+    rng = np.random.Generator(np.random.PCG64(3))
+    A = rng.standard_normal((1, 24, 40)).astype(np.float32)
+    B = rng.standard_normal((4, 40, 56)).astype(np.float32)
+    dA, dB, dC = ctx.upload(A), ctx.upload(B), ctx.alloc(4 * 24 * 56 * 4)
+    ctx.gemm_f32(dA, dB, dC, 4, 24, 56, 40, a_batched=False)
+    ref = orc.gemm_f32(A, B, 4, 24, 56, 40, a_batched=False)
+    assert rel_err(ctx.download(dC, (4 * 24 * 56,), np.float32), ref) <= 1e-4
+
+
+@pytest.mark.parametrize("shape", [(1, 16, 4), (3, 63, 257), (256, 1000, 2048)])
+def test_gemv_f32(ctx, orc, shape):
+    batch, rows, K = shape
+    rng = np.random.Generator(np.random.PCG64(7))
+    lhs = rng.standard_normal((rows, K)).astype(np.float32)
+    rhs = rng.standard_normal((batch, K)).astype(np.float32)
+    bias = rng.standard_normal(rows).astype(np.float32)
+    dl, dr, db, do = ctx.upload(lhs), ctx.upload(rhs), ctx.upload(bias), ctx.alloc(batch * rows * 4)
+    ctx.gemv_f32(dl, dr, db, do, batch, rows, K)
+    ref = orc.gemv_f32(lhs, rhs, bias, batch, rows, K)
+    assert rel_err(ctx.download(do, (batch * rows,), np.float32), ref) <= 1e-4
+
+
+def _conv_inputs(shape, fshape, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    x = rng.random(shape, dtype=np.float32)
+    fan_in = fshape[1] * fshape[2] * fshape[3]
+    f = (rng.standard_normal(fshape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+    bias = (rng.standard_normal(fshape[0]) * 0.01).astype(np.float32)
+    return x, f, bias
+
+
+@pytest.mark.parametrize("case", [
+    # N, C, H, W, O, KH, KW, stride, dilation, padding, activation
+    (1, 2, 3, 3, 1, 3, 3, 1, 1, "VALID", 0),
+    (2, 16, 14, 14, 32, 1, 1, 1, 1, "VALID", 1),      # 1x1 -> batched GEMM
+    (1, 3, 33, 35, 8, 7, 7, 2, 1, "SAME", 1),         # ResNet-style 7x7 stride-2 stem
+    (2, 8, 15, 15, 16, 1, 1, 2, 1, "SAME", 0),        # 1x1 stride 2
+    (1, 4, 12, 13, 6, 3, 3, 1, 2, "SAME", 2),         # dilated, RELUX
+    (1, 5, 9, 9, 7, 5, 5, 1, 1, "FULL", 6),           # LEAKYRELU
+])
+def test_conv2d_f32(ctx, orc, case):
+    N, C, H, W, O, KH, KW, st, dil, padding, act = case
+    x, f, bias = _conv_inputs((N, C, H, W), (O, C, KH, KW), H * 3 + C)
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, KH, KW, (dil, dil), (st, st), PAD[padding])
+    ref = orc.conv2d_f32(x, f, bias, (st, st), (dil, dil), (ph >> 1, pw >> 1), (Ho, Wo), act, 0.5, 0.1)
+    dx, df, db, do = ctx.upload(x), ctx.upload(f), ctx.upload(bias), ctx.alloc(ref.nbytes)
+    ctx.conv2d_f32(dx, df, db, do, N, C, H, W, O, KH, KW, (st, st), (dil, dil), (ph >> 1, pw >> 1),
+                   (Ho, Wo), act, 0.5, 0.1)
+    assert rel_err(ctx.download(do, ref.shape, np.float32), ref) <= 1e-4
+
+
+def test_conv2d_f32_reference_literals(ctx, kats):
+    """TestNHWCSimple3x3VALID / SAME: all-ones 3x3x2 input and filter, bias 0.1 -> 18.1 ..."""
+    for name in ("conv2d_f32_3x3_valid", "conv2d_f32_3x3_same"):
+        k = kats[name]
+        x = np.ones((1, 2, 3, 3), np.float32)
+        f = np.ones((1, 2, 3, 3), np.float32)
+        bias = np.array(k["bias"], np.float32)
+        same = k["padding"] == "SAME"
+        Ho = 3 if same else 1
+        pad = (1, 1) if same else (0, 0)
+        exp = np.array(k["expected"], np.float32).reshape(1, 1, Ho, Ho)
+        dx, df, db, do = ctx.upload(x), ctx.upload(f), ctx.upload(bias), ctx.alloc(exp.nbytes)
+        ctx.conv2d_f32(dx, df, db, do, 1, 2, 3, 3, 1, 3, 3, (1, 1), (1, 1), pad, (Ho, Ho))
+        np.testing.assert_allclose(ctx.download(do, exp.shape, np.float32), exp, rtol=1e-5)
+        for tile in (2, 6):
+            ctx.winograd_f32(dx, df, db, do, 1, 2, 3, 3, 1, pad, (Ho, Ho), tile=tile)
+            np.testing.assert_allclose(ctx.download(do, exp.shape, np.float32), exp, rtol=1e-4)
+
+
+@pytest.mark.parametrize("case", [
+    # N, C, H, W, O, padding, activation
+    (1, 8, 9, 9, 8, "SAME", 0),        # small input -> F(2,3)
+    (2, 16, 14, 17, 24, "VALID", 1),
+    (1, 8, 20, 20, 16, "SAME", 0),     # larger than 16x16 -> F(6,3)
+    (2, 64, 56, 56, 64, "SAME", 1),    # config-1 shape, reduced batch
+    (1, 32, 31, 29, 40, "VALID", 2),   # tile tails
+])
+def test_winograd_f32(ctx, orc, case):
+    N, C, H, W, O, padding, act = case
+    x, f, bias = _conv_inputs((N, C, H, W), (O, C, 3, 3), H + C)
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, 3, 3, (1, 1), (1, 1), PAD[padding])
+    direct = orc.conv2d_f32(x, f, bias, (1, 1), (1, 1), (ph >> 1, pw >> 1), (Ho, Wo), act, 0.5, 0.0)
+    dx, df, db, do = ctx.upload(x), ctx.upload(f), ctx.upload(bias), ctx.alloc(direct.nbytes)
+    ctx.winograd_f32(dx, df, db, do, N, C, H, W, O, (ph >> 1, pw >> 1), (Ho, Wo), act, 0.5, 0.0)
+    got = ctx.download(do, direct.shape, np.float32)
+    assert rel_err(got, direct) <= 1e-3
+    # against the oracle's Winograd restatement (same algorithm, same tile rule): tighter
+    wino = orc.winograd_f32(x, f, bias, (ph >> 1, pw >> 1), (Ho, Wo), act, 0.5, 0.0)
+    assert rel_err(got, wino) <= 1e-4
+    # cached transformed filter gives the same result
+    tile = 6 if (H > 16 and W > 16) else 2
+    dU = ctx.alloc((tile + 2) ** 2 * O * C * 4)
+    ctx.winograd_transform_filter(df, dU, C, O, tile)
+    ctx.winograd_f32(dx, None, db, do, N, C, H, W, O, (ph >> 1, pw >> 1), (Ho, Wo), act, 0.5, 0.0,
+                     transformed=dU)
+    assert np.array_equal(ctx.download(do, direct.shape, np.float32), got)
+
+
+def test_dwconv_f32(ctx, orc, kats):
+    k = kats["dwconv_f32_2x2_valid"]  # SimpleValidTest, depthwise_conv2d_test.cc:26-84
+    x = np.transpose(np.array(k["input"], np.float32).reshape(1, 3, 3, 2), (0, 3, 1, 2)).copy()
+    f = np.array(k["filter"], np.float32).reshape(1, 2, 2, 2)
+    bias = np.array(k["bias"], np.float32)
+    dx, df, db, do = ctx.upload(x), ctx.upload(f), ctx.upload(bias), ctx.alloc(8 * 4)
+    ctx.dwconv_f32(dx, df, db, do, 1, 2, 3, 3, 1, 2, 2, (1, 1), (1, 1), (0, 0), (2, 2))
+    got = np.transpose(ctx.download(do, (1, 2, 2, 2), np.float32), (0, 2, 3, 1))
+    np.testing.assert_allclose(got.ravel(), np.array(k["expected"], np.float32), rtol=1e-5)
+    rng = np.random.Generator(np.random.PCG64(1))
+    x = rng.standard_normal((2, 12, 17, 15)).astype(np.float32)
+    f = rng.standard_normal((2, 12, 3, 3)).astype(np.float32)
+    bias = rng.standard_normal(24).astype(np.float32)
+    ref = orc.dwconv_f32(x, f, bias, (2, 2), (1, 1), (0, 0), (9, 8), 1)
+    dx, df, db, do = ctx.upload(x), ctx.upload(f), ctx.upload(bias), ctx.alloc(ref.nbytes)
+    ctx.dwconv_f32(dx, df, db, do, 2, 12, 17, 15, 2, 3, 3, (2, 2), (1, 1), (0, 0), (9, 8), 1)
+    assert rel_err(ctx.download(do, ref.shape, np.float32), ref) <= 1e-4
