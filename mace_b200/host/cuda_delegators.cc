@@ -257,6 +257,165 @@ class DepthwiseConv2d : public delegator::DepthwiseConv2d {
 };
 
 }  // namespace q8
+
+namespace fp32 {
+
+// Conv shape bookkeeping shared by the fp32 convolution delegators: NCHW input,
+// OIHW filter (CalcNCHWPaddingAndOutputSize, mace/ops/ref/conv_2d.cc:46-66).
+struct ConvGeometry {
+  index_t out_h = 0, out_w = 0;
+  int pad_top = 0, pad_left = 0;
+};
+
+static MaceStatus Geometry(const Tensor *input, index_t k_h, index_t k_w,
+                           const std::vector<int> &strides, const std::vector<int> &dilations,
+                           const std::vector<int> &paddings_in, Padding padding_type,
+                           ConvGeometry *g) {
+  std::vector<int> paddings(2);
+  if (paddings_in.empty()) {
+    MACE_RETURN_IF_ERROR(CalcPaddingAndOutputSize(input->dim(2), input->dim(3), k_h, k_w,
+                                                  dilations.data(), strides.data(), padding_type,
+                                                  &g->out_h, &g->out_w, paddings.data()));
+  } else {
+    paddings = paddings_in;
+    CalcOutputSize(input->dim(2), input->dim(3), k_h, k_w, paddings.data(), dilations.data(),
+                   strides.data(), FLOOR, &g->out_h, &g->out_w);
+  }
+  g->pad_top = paddings[0] >> 1;
+  g->pad_left = paddings[1] >> 1;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+class Gemm : public delegator::Gemm {
+ public:
+  explicit Gemm(const delegator::GemmParam &param) : delegator::Gemm(param) {}
+  MaceStatus Compute(const OpContext *context, const Tensor *lhs, const Tensor *rhs,
+                     const index_t batch, const index_t rows, const index_t cols,
+                     const index_t depth, const MatrixMajor lhs_major, const MatrixMajor rhs_major,
+                     const MatrixMajor output_major, const bool lhs_batched,
+                     const bool rhs_batched, Tensor *output) override {
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    return rt->Status(mb_gemm_f32(rt->ctx(), lhs->memory<float>(), rhs->memory<float>(),
+                                  output->mutable_memory<float>(), batch, rows, cols, depth,
+                                  lhs_major == ColMajor, rhs_major == ColMajor,
+                                  output_major == ColMajor, lhs_batched, rhs_batched));
+  }
+  MaceStatus Compute(const OpContext *context, const Tensor *lhs, const Tensor *rhs,
+                     const index_t batch, const index_t lhs_rows, const index_t lhs_cols,
+                     const index_t rhs_rows, const index_t rhs_cols, const bool transpose_lhs,
+                     const bool transpose_rhs, const bool transpose_out, const bool lhs_batched,
+                     const bool rhs_batched, Tensor *output) override {
+    const index_t rows = transpose_lhs ? lhs_cols : lhs_rows;
+    const index_t depth = transpose_lhs ? lhs_rows : lhs_cols;
+    const index_t cols = transpose_rhs ? rhs_rows : rhs_cols;
+    MACE_CHECK(depth == (transpose_rhs ? rhs_cols : rhs_rows));
+    return Compute(context, lhs, rhs, batch, rows, cols, depth,
+                   transpose_lhs ? ColMajor : RowMajor, transpose_rhs ? ColMajor : RowMajor,
+                   transpose_out ? ColMajor : RowMajor, lhs_batched, rhs_batched, output);
+  }
+};
+
+class Gemv : public delegator::Gemv {
+ public:
+  explicit Gemv(const DelegatorParam &param) : delegator::Gemv(param) {}
+  MaceStatus Compute(const OpContext *context, const Tensor *lhs, const Tensor *rhs,
+                     const Tensor *bias, const index_t batch, const index_t lhs_height,
+                     const index_t lhs_width, const bool lhs_batched, const bool rhs_batched,
+                     Tensor *output) override {
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    return rt->Status(mb_gemv_f32(rt->ctx(), lhs->memory<float>(), rhs->memory<float>(),
+                                  bias ? bias->memory<float>() : nullptr,
+                                  output->mutable_memory<float>(), batch, lhs_height, lhs_width,
+                                  lhs_batched, rhs_batched));
+  }
+};
+
+// General direct convolution and the 1x1-as-GEMM route (the library picks).
+class Conv2d : public delegator::Conv2d {
+ public:
+  explicit Conv2d(const delegator::Conv2dParam &param) : delegator::Conv2d(param) {}
+  MaceStatus Compute(const OpContext *context, const Tensor *input, const Tensor *filter,
+                     Tensor *output) override {
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    MACE_CHECK(input->dim(1) == filter->dim(1));
+    ConvGeometry g;
+    MACE_RETURN_IF_ERROR(Geometry(input, filter->dim(2), filter->dim(3), strides_, dilations_,
+                                  paddings_, padding_type_, &g));
+    MACE_RETURN_IF_ERROR(output->Resize({input->dim(0), filter->dim(0), g.out_h, g.out_w}));
+    return rt->Status(mb_conv2d_f32_nchw(
+        rt->ctx(), input->memory<float>(), filter->memory<float>(),
+        bias_ ? bias_->memory<float>() : nullptr, output->mutable_memory<float>(), input->dim(0),
+        input->dim(1), input->dim(2), input->dim(3), filter->dim(0), filter->dim(2),
+        filter->dim(3), strides_[0], strides_[1], dilations_[0], dilations_[1], g.pad_top,
+        g.pad_left, g.out_h, g.out_w, activation_, max_limit_, coefficient_));
+  }
+};
+
+// 3x3 stride-1 Winograd; the transformed filter is cached while the filter is a
+// weight, as the CPU delegator does (conv_2d_3x3_winograd.cc:120-145).
+class Conv2dK3x3Winograd : public delegator::Conv2d {
+ public:
+  explicit Conv2dK3x3Winograd(const delegator::Conv2dParam &param) : delegator::Conv2d(param) {}
+  MaceStatus Compute(const OpContext *context, const Tensor *input, const Tensor *filter,
+                     Tensor *output) override {
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    MACE_CHECK(filter->dim(2) == 3 && filter->dim(3) == 3 && strides_[0] == 1 && strides_[1] == 1 &&
+               dilations_[0] == 1 && dilations_[1] == 1);
+    ConvGeometry g;
+    MACE_RETURN_IF_ERROR(Geometry(input, 3, 3, strides_, dilations_, paddings_, padding_type_, &g));
+    MACE_RETURN_IF_ERROR(output->Resize({input->dim(0), filter->dim(0), g.out_h, g.out_w}));
+    const int tile = (input->dim(2) > 16 && input->dim(3) > 16) ? 6 : 2;
+    const float *transformed = nullptr;
+    if (filter->is_weight()) {
+      if (transformed_filter_ == nullptr || tile != out_tile_size_ || src_ != filter) {
+        const index_t t = (tile + 2) * (tile + 2);
+        transformed_filter_ = std::make_unique<Tensor>(
+            rt, DT_FLOAT, std::vector<index_t>{t, filter->dim(0), filter->dim(1)}, true);
+        MACE_RETURN_IF_ERROR(rt->Status(mb_winograd_transform_filter_f32(
+            rt->ctx(), filter->memory<float>(), transformed_filter_->mutable_memory<float>(),
+            filter->dim(1), filter->dim(0), tile)));
+        out_tile_size_ = tile;
+        src_ = filter;
+      }
+      transformed = transformed_filter_->memory<float>();
+    }
+    return rt->Status(mb_conv3x3_winograd_f32_nchw(
+        rt->ctx(), input->memory<float>(), filter->memory<float>(), transformed,
+        bias_ ? bias_->memory<float>() : nullptr, output->mutable_memory<float>(), input->dim(0),
+        input->dim(1), input->dim(2), input->dim(3), filter->dim(0), g.pad_top, g.pad_left,
+        g.out_h, g.out_w, activation_, max_limit_, coefficient_, tile));
+  }
+
+ private:
+  std::unique_ptr<Tensor> transformed_filter_;
+  int out_tile_size_ = 0;
+  const Tensor *src_ = nullptr;
+};
+
+// fp32 depthwise, NCHW, filter [multiplier, C, kh, kw].
+class DepthwiseConv2d : public delegator::DepthwiseConv2d {
+ public:
+  explicit DepthwiseConv2d(const delegator::DepthwiseConv2dParam &param)
+      : delegator::DepthwiseConv2d(param) {}
+  MaceStatus Compute(const OpContext *context, const Tensor *input, const Tensor *filter,
+                     Tensor *output) override {
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    MACE_CHECK(input->dim(1) == filter->dim(1));
+    ConvGeometry g;
+    MACE_RETURN_IF_ERROR(Geometry(input, filter->dim(2), filter->dim(3), strides_, dilations_,
+                                  paddings_, padding_type_, &g));
+    MACE_RETURN_IF_ERROR(
+        output->Resize({input->dim(0), filter->dim(0) * filter->dim(1), g.out_h, g.out_w}));
+    return rt->Status(mb_dwconv_f32_nchw(
+        rt->ctx(), input->memory<float>(), filter->memory<float>(),
+        bias_ ? bias_->memory<float>() : nullptr, output->mutable_memory<float>(), input->dim(0),
+        input->dim(1), input->dim(2), input->dim(3), filter->dim(0), filter->dim(2),
+        filter->dim(3), strides_[0], strides_[1], dilations_[0], dilations_[1], g.pad_top,
+        g.pad_left, g.out_h, g.out_w, activation_, max_limit_, coefficient_));
+  }
+};
+
+}  // namespace fp32
 }  // namespace cuda
 
 void RegisterAllCudaOpDelegators(OpDelegatorRegistry *registry) {
@@ -269,6 +428,21 @@ void RegisterAllCudaOpDelegators(OpDelegatorRegistry *registry) {
   MACE_REGISTER_DELEGATOR(
       registry, cuda::q8::DepthwiseConv2d, delegator::DepthwiseConv2dParam,
       MACE_DELEGATOR_KEY(DepthwiseConv2d, RuntimeType::RT_CUDA, uint8_t, ImplType::CUDA));
+  MACE_REGISTER_DELEGATOR(registry, cuda::fp32::Gemm, delegator::GemmParam,
+                          MACE_DELEGATOR_KEY(Gemm, RuntimeType::RT_CUDA, float, ImplType::CUDA));
+  MACE_REGISTER_DELEGATOR(registry, cuda::fp32::Gemv, DelegatorParam,
+                          MACE_DELEGATOR_KEY(Gemv, RuntimeType::RT_CUDA, float, ImplType::CUDA));
+  MACE_REGISTER_DELEGATOR(registry, cuda::fp32::Conv2d, delegator::Conv2dParam,
+                          MACE_DELEGATOR_KEY(Conv2d, RuntimeType::RT_CUDA, float, ImplType::CUDA));
+  MACE_REGISTER_DELEGATOR(
+      registry, cuda::fp32::Conv2d, delegator::Conv2dParam,
+      MACE_DELEGATOR_KEY_EX(Conv2d, RuntimeType::RT_CUDA, float, ImplType::CUDA, K1x1));
+  MACE_REGISTER_DELEGATOR(
+      registry, cuda::fp32::Conv2dK3x3Winograd, delegator::Conv2dParam,
+      MACE_DELEGATOR_KEY_EX(Conv2d, RuntimeType::RT_CUDA, float, ImplType::CUDA, K3x3Winograd));
+  MACE_REGISTER_DELEGATOR(
+      registry, cuda::fp32::DepthwiseConv2d, delegator::DepthwiseConv2dParam,
+      MACE_DELEGATOR_KEY(DepthwiseConv2d, RuntimeType::RT_CUDA, float, ImplType::CUDA));
 }
 
 }  // namespace ops

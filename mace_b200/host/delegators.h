@@ -19,6 +19,11 @@ namespace ops {
 
 enum ConvType { K1x1, K3x3S1, K3x3S2, K3x3Winograd };
 
+enum ActivationType {  // mace/ops/common/activation_type.h:21-31
+  NOOP = 0, RELU = 1, RELUX = 2, PRELU = 3, TANH = 4, SIGMOID = 5, LEAKYRELU = 6, ELU = 7,
+  HARDSIGMOID = 8,
+};
+
 namespace delegator {
 
 struct GemmParam : public DelegatorParam {
@@ -81,8 +86,15 @@ class Conv2d : public OpDelegator {
                              Tensor *output) = 0;
   // The quantized kernels fuse the int32 bias into the GEMM epilogue (the CPU
   // op passes it to the gemmlowp pipeline, mace/ops/conv_2d.cc:308-310); the
-  // op hands it over before Compute.
+  // op hands it over before Compute.  The fp32 kernels also fuse the bias add
+  // and the activation that the CPU op runs as two more passes
+  // (mace/ops/conv_2d.cc:171-173).
   void SetBias(const Tensor *bias) { bias_ = bias; }
+  void SetActivation(int type, float max_limit, float coefficient) {
+    activation_ = type;
+    max_limit_ = max_limit;
+    coefficient_ = coefficient;
+  }
 
  protected:
   const std::vector<int> strides_;
@@ -90,6 +102,8 @@ class Conv2d : public OpDelegator {
   const std::vector<int> paddings_;
   const Padding padding_type_;
   const Tensor *bias_ = nullptr;
+  int activation_ = 0;  // ops::ActivationType value
+  float max_limit_ = 0.f, coefficient_ = 0.f;
 };
 
 typedef Conv2d DepthwiseConv2d;
@@ -100,6 +114,8 @@ typedef Conv2dParam DepthwiseConv2dParam;
 // Registers the CUDA delegators of this library:
 //   (Gemm, RT_CUDA, uint8_t, CUDA), (Gemv, RT_CUDA, uint8_t, CUDA),
 //   (Conv2d, RT_CUDA, uint8_t, CUDA, general), (DepthwiseConv2d, RT_CUDA, uint8_t, CUDA)
+//   (Gemm | Gemv | DepthwiseConv2d, RT_CUDA, float, CUDA),
+//   (Conv2d, RT_CUDA, float, CUDA, general | K1x1 | K3x3Winograd)
 void RegisterAllCudaOpDelegators(OpDelegatorRegistry *registry);
 
 }  // namespace ops

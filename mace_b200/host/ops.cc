@@ -141,6 +141,185 @@ class Conv2dOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
   std::unique_ptr<delegator::Conv2d> conv2d_delegator_;
 };
 
+static ActivationType StringToActivationType(const std::string &type, MaceStatus *status) {
+  *status = MaceStatus::MACE_SUCCESS;
+  if (type == "NOOP") return NOOP;
+  if (type == "RELU") return RELU;
+  if (type == "RELUX") return RELUX;
+  if (type == "LEAKYRELU") return LEAKYRELU;
+  *status = MaceStatus(MaceStatus::MACE_UNSUPPORTED, "activation not fused by the CUDA runtime: " + type);
+  return NOOP;
+}
+
+// fp32 Conv2D, NCHW: delegator choice as Conv2dOp<RT_CPU,T>::Run makes it on first use
+// (mace/ops/conv_2d.cc:88-169): 1x1 stride 1 -> K1x1; 3x3 stride 1 with at least 8 input and 8
+// output channels -> K3x3Winograd; everything else -> general.  Bias and activation are
+// handed to the delegator, which fuses them.
+template <>
+class Conv2dOp<RuntimeType::RT_CUDA, float> : public ConvPool2dOpBase {
+ public:
+  explicit Conv2dOp(OpConstructContext *context)
+      : ConvPool2dOpBase(context), workspace_(context->workspace()),
+        activation_name_(GetOptionalArg<std::string>("activation", "NOOP")),
+        max_limit_(GetOptionalArg<float>("max_limit", 0.0f)),
+        coefficient_(GetOptionalArg<float>("activation_coefficient", 0.0f)) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0), *filter = Input(1);
+    const Tensor *bias = InputSize() >= 3 ? Input(2) : nullptr;
+    if (strides_.size() != 2) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "strides must have 2 values");
+    MaceStatus st;
+    const ActivationType act = StringToActivationType(activation_name_, &st);
+    MACE_RETURN_IF_ERROR(st);
+    if (conv2d_delegator_ == nullptr) {
+      const index_t filter_h = filter->dim(2), filter_w = filter->dim(3);
+      const index_t in_channels = input->dim(1), out_channels = filter->dim(0);
+      const bool s1d1 = strides_[0] == 1 && strides_[1] == 1 && dilations_[0] == 1 && dilations_[1] == 1;
+      delegator::Conv2dParam param(strides_, dilations_, paddings_, padding_type_);
+      if (filter_h == 1 && filter_w == 1 && s1d1) {
+        conv2d_delegator_ = delegator::Conv2d::Create(
+            workspace_, MACE_DELEGATOR_KEY_EX(Conv2d, RuntimeType::RT_CUDA, float, ImplType::CUDA, K1x1), param);
+      } else if (filter_h == 3 && filter_w == 3 && s1d1 && in_channels >= 8 && out_channels >= 8) {
+        conv2d_delegator_ = delegator::Conv2d::Create(
+            workspace_,
+            MACE_DELEGATOR_KEY_EX(Conv2d, RuntimeType::RT_CUDA, float, ImplType::CUDA, K3x3Winograd), param);
+      } else {
+        conv2d_delegator_ = delegator::Conv2d::Create(
+            workspace_, MACE_DELEGATOR_KEY(Conv2d, RuntimeType::RT_CUDA, float, ImplType::CUDA), param);
+      }
+    }
+    conv2d_delegator_->SetBias(bias);
+    conv2d_delegator_->SetActivation(act, max_limit_, coefficient_);
+    return conv2d_delegator_->Compute(context, input, filter, Output(0));
+  }
+
+ private:
+  Workspace *workspace_;
+  std::string activation_name_;
+  float max_limit_, coefficient_;
+  std::unique_ptr<delegator::Conv2d> conv2d_delegator_;
+};
+
+template <>
+class DepthwiseConv2dOp<RuntimeType::RT_CUDA, float> : public ConvPool2dOpBase {
+ public:
+  explicit DepthwiseConv2dOp(OpConstructContext *context)
+      : ConvPool2dOpBase(context), workspace_(context->workspace()),
+        activation_name_(GetOptionalArg<std::string>("activation", "NOOP")),
+        max_limit_(GetOptionalArg<float>("max_limit", 0.0f)),
+        coefficient_(GetOptionalArg<float>("activation_coefficient", 0.0f)) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0), *filter = Input(1);
+    const Tensor *bias = InputSize() >= 3 ? Input(2) : nullptr;
+    if (strides_.size() != 2) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "strides must have 2 values");
+    MaceStatus st;
+    const ActivationType act = StringToActivationType(activation_name_, &st);
+    MACE_RETURN_IF_ERROR(st);
+    if (delegator_ == nullptr) {
+      delegator_ = delegator::DepthwiseConv2d::Create(
+          workspace_, MACE_DELEGATOR_KEY(DepthwiseConv2d, RuntimeType::RT_CUDA, float, ImplType::CUDA),
+          delegator::DepthwiseConv2dParam(strides_, dilations_, paddings_, padding_type_));
+    }
+    delegator_->SetBias(bias);
+    delegator_->SetActivation(act, max_limit_, coefficient_);
+    return delegator_->Compute(context, input, filter, Output(0));
+  }
+
+ private:
+  Workspace *workspace_;
+  std::string activation_name_;
+  float max_limit_, coefficient_;
+  std::unique_ptr<delegator::DepthwiseConv2d> delegator_;
+};
+
+// fp32 MatMul (mace/ops/matmul.cc:96-225): batched GEMM through the Gemm delegator; a bias
+// input is not supported by this runtime (MACE_UNSUPPORTED).
+template <>
+class MatMulOp<RuntimeType::RT_CUDA, float> : public Operation {
+ public:
+  explicit MatMulOp(OpConstructContext *context)
+      : Operation(context),
+        transpose_a_(GetOptionalArg<bool>("transpose_a", false)),
+        transpose_b_(GetOptionalArg<bool>("transpose_b", false)),
+        gemm_(delegator::Gemm::Create(context->workspace(),
+                                      MACE_DELEGATOR_KEY(Gemm, RuntimeType::RT_CUDA, float, ImplType::CUDA),
+                                      delegator::GemmParam())) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *lhs = Input(0), *rhs = Input(1);
+    if (InputSize() >= 3) return MaceStatus(MaceStatus::MACE_UNSUPPORTED, "MatMul bias input");
+    Tensor *C = Output(0);
+    const index_t lhs_rank = lhs->dim_size(), rhs_rank = rhs->dim_size();
+    if (lhs_rank < 2 || rhs_rank < 2)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "rank should be greater than or equal to 2");
+    if (lhs_rank == rhs_rank) {
+      for (index_t i = 0; i < lhs_rank - 2; ++i)
+        if (lhs->dim(i) != rhs->dim(i))
+          return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "batch dimensions are not equal");
+    } else if (lhs_rank != 2 && rhs_rank != 2) {
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS,
+                        "Either lhs or rhs matrix should has rank 2 for non-batched matrix multiplication");
+    }
+    const index_t lhs_rows = lhs->dim(lhs_rank - 2), lhs_cols = lhs->dim(lhs_rank - 1);
+    const index_t rhs_rows = rhs->dim(rhs_rank - 2), rhs_cols = rhs->dim(rhs_rank - 1);
+    const index_t rows = transpose_a_ ? lhs_cols : lhs_rows;
+    const index_t cols = transpose_b_ ? rhs_rows : rhs_cols;
+    const index_t depth = transpose_a_ ? lhs_rows : lhs_cols;
+    if (depth != (transpose_b_ ? rhs_cols : rhs_rows))
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "the number of A's column must be equal to B's row");
+    const index_t lhs_batch = std::accumulate(lhs->shape().begin(), lhs->shape().end() - 2,
+                                              static_cast<index_t>(1), std::multiplies<index_t>());
+    const index_t rhs_batch = std::accumulate(rhs->shape().begin(), rhs->shape().end() - 2,
+                                              static_cast<index_t>(1), std::multiplies<index_t>());
+    std::vector<index_t> output_shape = lhs_rank >= rhs_rank ? lhs->shape() : rhs->shape();
+    output_shape[output_shape.size() - 2] = rows;
+    output_shape[output_shape.size() - 1] = cols;
+    const index_t batch = lhs_rank >= rhs_rank ? lhs_batch : rhs_batch;
+    MACE_RETURN_IF_ERROR(C->Resize(output_shape));
+    return gemm_->Compute(context, lhs, rhs, batch, rows, cols, depth,
+                          transpose_a_ ? ColMajor : RowMajor, transpose_b_ ? ColMajor : RowMajor,
+                          RowMajor, !(lhs_rank < rhs_rank), !(rhs_rank < lhs_rank), C);
+  }
+
+ private:
+  bool transpose_a_, transpose_b_;
+  std::unique_ptr<delegator::Gemm> gemm_;
+};
+
+// fp32 FullyConnected (mace/ops/fully_connected.cc:61-125): weight OIHW, input NCHW, output
+// [N, O, 1, 1]; Gemv with the weight as the matrix.  Only NOOP activation is supported here.
+template <>
+class FullyConnectedOp<RuntimeType::RT_CUDA, float> : public Operation {
+ public:
+  explicit FullyConnectedOp(OpConstructContext *context)
+      : Operation(context),
+        activation_name_(GetOptionalArg<std::string>("activation", "NOOP")),
+        gemv_(delegator::Gemv::Create(context->workspace(),
+                                      MACE_DELEGATOR_KEY(Gemv, RuntimeType::RT_CUDA, float, ImplType::CUDA),
+                                      DelegatorParam())) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0), *weight = Input(1);
+    const Tensor *bias = InputSize() >= 3 ? Input(2) : nullptr;
+    Tensor *output = Output(0);
+    if (activation_name_ != "NOOP")
+      return MaceStatus(MaceStatus::MACE_UNSUPPORTED, "FullyConnected activation " + activation_name_);
+    if (!(input->dim(1) == weight->dim(1) && input->dim(2) == weight->dim(2) &&
+          input->dim(3) == weight->dim(3)))
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "The shape of Input and Weight don't match.");
+    if (bias != nullptr && weight->dim(0) != bias->dim(0))
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "The shape of Weight and Bias don't match.");
+    MACE_RETURN_IF_ERROR(output->Resize({input->dim(0), weight->dim(0), 1, 1}));
+    return gemv_->Compute(context, weight, input, bias, output->dim(0), weight->dim(0),
+                          weight->dim(1) * weight->dim(2) * weight->dim(3), false, true, output);
+  }
+
+ private:
+  std::string activation_name_;
+  std::unique_ptr<delegator::Gemv> gemv_;
+};
+
 template <>
 class DepthwiseConv2dOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
  public:
@@ -318,6 +497,10 @@ void RegisterAllCudaOps(OpRegistry *registry) {
   MACE_REGISTER_OP(registry, "MatMul", MatMulOp, RuntimeType::RT_CUDA, uint8_t);
   MACE_REGISTER_OP(registry, "FullyConnected", FullyConnectedOp, RuntimeType::RT_CUDA, uint8_t);
   MACE_REGISTER_OP(registry, "Pooling", PoolingOp, RuntimeType::RT_CUDA, uint8_t);
+  MACE_REGISTER_OP(registry, "Conv2D", Conv2dOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "DepthwiseConv2d", DepthwiseConv2dOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "MatMul", MatMulOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "FullyConnected", FullyConnectedOp, RuntimeType::RT_CUDA, float);
 }
 
 }  // namespace ops

@@ -101,7 +101,7 @@ class OpRegistry {
 
 namespace ops {
 // Registers Conv2D, DepthwiseConv2d, MatMul, FullyConnected and Pooling for
-// (RT_CUDA, uint8_t).
+// (RT_CUDA, uint8_t) and Conv2D, DepthwiseConv2d, MatMul, FullyConnected for (RT_CUDA, float).
 void RegisterAllCudaOps(OpRegistry *registry);
 }  // namespace ops
 

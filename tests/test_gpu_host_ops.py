@@ -170,3 +170,79 @@ def test_pooling_keeps_quantization(net, orc):
     assert abs(scale - np.float32(0.0123)) < 1e-9 and zp == 7
     exp = orc.avgpool_u8(x, (7, 7), (1, 1), (0, 0), (1, 1))
     assert np.array_equal(net.read("Output", np.uint8), exp)
+
+
+# ---- fp32 operators -------------------------------------------------------------------
+
+def _rel(got, ref):
+    return float(np.abs(got.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def test_conv2d_float_simple3x3(net, kats):
+    """TestNHWCSimple3x3VALID / SAME (conv_2d_test.cc:35-153) on NCHW tensors: 18.1 ..."""
+    from mace_b200 import hostapi as H
+    for name, pad in (("conv2d_f32_3x3_valid", H.VALID), ("conv2d_f32_3x3_same", H.SAME)):
+        k = kats[name]
+        net.add_tensor("Input" + name, np.ones((1, 2, 3, 3), np.float32))
+        net.add_tensor("Filter" + name, np.ones((1, 2, 3, 3), np.float32), is_weight=True)
+        net.add_tensor("Bias" + name, np.array(k["bias"], np.float32), is_weight=True)
+        net.op("Conv2D", "Conv2dTest" + name, ["Input" + name, "Filter" + name, "Bias" + name],
+               ["Output" + name], T=H.DT_FLOAT, ints={"strides": [1, 1], "dilations": [1, 1]},
+               i={"padding": pad})
+    net.run()
+    for name in ("conv2d_f32_3x3_valid", "conv2d_f32_3x3_same"):
+        k = kats[name]
+        got = net.read("Output" + name, np.float32)
+        np.testing.assert_allclose(got.ravel(), np.array(k["expected"], np.float32), rtol=1e-5)
+
+
+@pytest.mark.parametrize("case", [(2, 16, 20, 20, 24, 3, 1, "RELU"),     # -> K3x3Winograd, F(6,3)
+                                  (1, 8, 12, 12, 8, 3, 1, "NOOP"),       # -> K3x3Winograd, F(2,3)
+                                  (1, 4, 12, 12, 8, 3, 1, "RELUX"),      # C < 8 -> general
+                                  (2, 32, 14, 14, 64, 1, 1, "RELU"),     # -> K1x1
+                                  (1, 3, 30, 30, 16, 7, 2, "LEAKYRELU")])
+def test_conv2d_float_delegator_selection(net, orc, case):
+    from mace_b200 import hostapi as H
+    N, C, Hh, W, O, k, st, act = case
+    rng = np.random.Generator(np.random.PCG64(C + O))
+    x = rng.random((N, C, Hh, W), dtype=np.float32)
+    f = (rng.standard_normal((O, C, k, k)) * np.sqrt(2.0 / (C * k * k))).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.01).astype(np.float32)
+    net.add_tensor("Input", x)
+    net.add_tensor("Filter", f, is_weight=True)
+    net.add_tensor("Bias", bias, is_weight=True)
+    net.op("Conv2D", "conv", ["Input", "Filter", "Bias"], ["Output"], T=H.DT_FLOAT,
+           ints={"strides": [st, st], "dilations": [1, 1]}, i={"padding": H.SAME},
+           s={"activation": act}, f={"max_limit": 0.3, "activation_coefficient": 0.2})
+    net.run()
+    net.run()  # second run reuses the cached transformed filter
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(Hh, W, k, k, (1, 1), (st, st), 1)
+    code = {"NOOP": 0, "RELU": 1, "RELUX": 2, "LEAKYRELU": 6}[act]
+    ref = orc.conv2d_f32(x, f, bias, (st, st), (1, 1), (ph >> 1, pw >> 1), (Ho, Wo), code, 0.3, 0.2)
+    got = net.read("Output", np.float32)
+    assert got.shape == ref.shape
+    assert _rel(got, ref) <= (1e-3 if (k == 3 and C >= 8) else 1e-4)
+
+
+def test_matmul_and_fully_connected_float(net, orc):
+    from mace_b200 import hostapi as H
+    rng = np.random.Generator(np.random.PCG64(12))
+    A = rng.standard_normal((2, 3, 40, 24)).astype(np.float32)
+    B = rng.standard_normal((2, 3, 56, 24)).astype(np.float32)
+    net.add_tensor("A", A)
+    net.add_tensor("B", B)
+    net.op("MatMul", "mm", ["A", "B"], ["C"], T=H.DT_FLOAT, i={"transpose_b": 1})
+    x = rng.standard_normal((5, 32, 2, 2)).astype(np.float32)
+    w = rng.standard_normal((10, 32, 2, 2)).astype(np.float32)
+    b = rng.standard_normal(10).astype(np.float32)
+    net.add_tensor("X", x)
+    net.add_tensor("W", w, is_weight=True)
+    net.add_tensor("Bfc", b, is_weight=True)
+    net.op("FullyConnected", "fc", ["X", "W", "Bfc"], ["Y"], T=H.DT_FLOAT)
+    net.run()
+    ref = orc.gemm_f32(A, B, 6, 40, 56, 24, b_col_major=True)
+    assert net.shape("C") == (2, 3, 40, 56)
+    assert _rel(net.read("C", np.float32).ravel(), ref) <= 1e-4
+    ref = orc.gemv_f32(w.reshape(10, 128), x.reshape(5, 128), b, 5, 10, 128)
+    assert net.shape("Y") == (5, 10, 1, 1)
+    assert _rel(net.read("Y", np.float32).ravel(), ref) <= 1e-4
