@@ -147,6 +147,29 @@ int mb_dwconv_u8_nhwc(mb_context *ctx, const uint8_t *in,
                       int32_t right_shift, int32_t zp_out,
                       int use_float_multiplier, float multiplier_f);
 
+/* The 3x3 / channel-multiplier-1 / undilated / stride 1 or 2 / C % 4 == 0 case runs a
+ * kernel that wants the filter (and bias) rearranged into signed 8-bit tap words per
+ * channel group.  mb_dwconv_u8_nhwc prepares them on every call; a caller whose filter
+ * and bias are constant (filter->is_weight(), as the CPU Winograd delegator caches its
+ * transformed filter, mace/ops/arm/base/conv_2d_3x3_winograd.cc:120-145) prepares them
+ * once into a buffer of mb_dwconv3x3_u8_prepacked_bytes(C) bytes (0: not eligible) and
+ * passes it to mb_dwconv_u8_nhwc_prepacked; zp_in and zp_f must be the values used for
+ * packing.  `prepacked` may be NULL, and is ignored when the call is not that case. */
+size_t mb_dwconv3x3_u8_prepacked_bytes(int64_t C);
+int mb_dwconv3x3_u8_prepack(mb_context *ctx, const uint8_t *filter_hwim,
+                            const int32_t *bias, int64_t C, int32_t zp_in,
+                            int32_t zp_f, void *prepacked);
+int mb_dwconv_u8_nhwc_prepacked(mb_context *ctx, const uint8_t *in,
+                                const uint8_t *filter_hwim, const int32_t *bias,
+                                const void *prepacked, uint8_t *out, int64_t N,
+                                int64_t H, int64_t W, int64_t C,
+                                int64_t channel_multiplier, int64_t KH, int64_t KW,
+                                int stride_h, int stride_w, int dil_h, int dil_w,
+                                int pad_top, int pad_left, int64_t Ho, int64_t Wo,
+                                int32_t zp_in, int32_t zp_f, int32_t multiplier,
+                                int32_t right_shift, int32_t zp_out,
+                                int use_float_multiplier, float multiplier_f);
+
 /* ---- uint8 average pooling, NHWC: replaces PoolingOp<RT_CPU,uint8_t> AVG
  * (mace/ops/pooling.cc:638-871): (sum + n/2) / n over the in-bounds window. */
 int mb_avgpool_u8_nhwc(mb_context *ctx, const uint8_t *in, uint8_t *out,

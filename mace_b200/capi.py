@@ -65,6 +65,10 @@ PROTOTYPES = {
     "mb_conv2d_u8_nhwc": (_int, [_vp] * 5 + [_i64] * 7 + [_int] * 4 + [_i64] * 2 + [_i32] * 5),
     "mb_dwconv_u8_nhwc": (_int, [_vp] * 5 + [_i64] * 7 + [_int] * 6 + [_i64] * 2 + [_i32] * 5 +
                           [_int, _f32]),
+    "mb_dwconv_u8_nhwc_prepacked": (_int, [_vp] * 6 + [_i64] * 7 + [_int] * 6 + [_i64] * 2 +
+                                    [_i32] * 5 + [_int, _f32]),
+    "mb_dwconv3x3_u8_prepacked_bytes": (C.c_size_t, [_i64]),
+    "mb_dwconv3x3_u8_prepack": (_int, [_vp] * 3 + [_i64, _i32, _i32, _vp]),
     "mb_avgpool_u8_nhwc": (_int, [_vp] * 3 + [_i64] * 6 + [_int] * 4 + [_i64] * 2),
     "mb_gemm_f32": (_int, [_vp] * 4 + [_i64] * 4 + [_int] * 5),
     "mb_gemv_f32": (_int, [_vp] * 5 + [_i64] * 3 + [_int] * 2),
@@ -237,8 +241,26 @@ class Context:
             O, KH, KW, strides[0], strides[1], pad_tl[0], pad_tl[1], out_hw[0], out_hw[1],
             zp_in, zp_f, mult, shift, zp_out))
 
+    def dwconv3x3_u8_prepack(self, f, bias, Cc, zp_in, zp_f):
+        """Returns a device buffer with the fast path's tap words for a constant filter."""
+        nbytes = lib().mb_dwconv3x3_u8_prepacked_bytes(Cc)
+        if nbytes == 0:
+            raise ValueError("channel count not eligible for the 3x3 fast path")
+        packed = self.alloc(nbytes)
+        self._check(lib().mb_dwconv3x3_u8_prepack(
+            self.h, f.ptr, bias.ptr if bias is not None else None, Cc, zp_in, zp_f, packed.ptr))
+        return packed
+
     def dwconv_u8(self, x, f, bias, out, N, H, W, Cc, Mc, KH, KW, strides, dil, pad_tl, out_hw,
-                  zp_in, zp_f, mult=1 << 30, shift=0, zp_out=0, float_multiplier=None):
+                  zp_in, zp_f, mult=1 << 30, shift=0, zp_out=0, float_multiplier=None,
+                  prepacked=None):
+        if prepacked is not None:
+            self._check(lib().mb_dwconv_u8_nhwc_prepacked(
+                self.h, x.ptr, f.ptr, bias.ptr if bias is not None else None, prepacked.ptr,
+                out.ptr, N, H, W, Cc, Mc, KH, KW, strides[0], strides[1], dil[0], dil[1],
+                pad_tl[0], pad_tl[1], out_hw[0], out_hw[1], zp_in, zp_f, mult, shift, zp_out,
+                int(float_multiplier is not None), float(float_multiplier or 0.0)))
+            return
         self._check(lib().mb_dwconv_u8_nhwc(
             self.h, x.ptr, f.ptr, bias.ptr if bias is not None else None, out.ptr, N, H, W, Cc,
             Mc, KH, KW, strides[0], strides[1], dil[0], dil[1], pad_tl[0], pad_tl[1],

@@ -129,6 +129,25 @@ __device__ __forceinline__ uint32_t mb_requant_fast(int32_t acc, const mb_requan
   return static_cast<uint32_t>(__viaddmin_s32_relu(min(y, 255), q.zp, 255));
 }
 
+// Compile-time variants of the same expression.  SGE1 (shift >= 1): the total shift is at
+// least 32, so y is the high word of t shifted by (shift - 1) -- one multiply-add and one
+// 32-bit shift.  ZP0 (output zero point 0): a negative accumulator gives y <= 0 with or
+// without the [acc < 0] term and clamps to 0, so the term is dropped.
+template <bool ZP0, bool SGE1>
+__device__ __forceinline__ uint32_t mb_requant_t(int32_t acc, const mb_requant_params &q) {
+  int64_t t = static_cast<int64_t>(acc) * q.mult + q.c64;
+  if (!ZP0 && SGE1)
+    t += static_cast<int64_t>(static_cast<int32_t>(static_cast<uint32_t>(acc) >> 31)) * q.neg;
+  const int32_t y = SGE1 ? (static_cast<int32_t>(t >> 32) >> (q.sh - 32)) : static_cast<int32_t>(t >> 31);
+  if (ZP0) return static_cast<uint32_t>(__vimin_s32_relu(y, 255));
+  return static_cast<uint32_t>(__viaddmin_s32_relu(min(y, 255), q.zp, 255));
+}
+
+// Variant index for kernels that switch on it once per tile or thread: bit 0 = ZP0, bit 1 = SGE1.
+static inline int mb_requant_variant(int32_t shift, int32_t zp_out) {
+  return (zp_out == 0 ? 1 : 0) | (shift >= 1 ? 2 : 0);
+}
+
 // Saturate<uint8_t>(roundf(v)) of mace/core/quantize.h:69-83.
 __device__ __forceinline__ uint32_t mb_saturate_round_u8(float v) {
   const int r = static_cast<int>(roundf(v));

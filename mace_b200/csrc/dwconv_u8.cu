@@ -11,6 +11,8 @@
 // channel bytes of a pixel in one transaction.  Each thread owns 4 adjacent
 // channels (one 32-bit word per tap) and a short strip of output pixels along
 // W; the filter taps of its channels stay in registers for the whole strip.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace {
@@ -36,112 +38,307 @@ __device__ __forceinline__ uint32_t dw_requant(int32_t acc, const DwParams &p) {
   return mb_requant_fast(acc, p.rq);
 }
 
-// dp2a with signed 16-bit halves in `a` and UNSIGNED bytes in `b`:
-//   lo: c + a.lo * b.byte0 + a.hi * b.byte1     hi: c + a.lo * b.byte2 + a.hi * b.byte3
-__device__ __forceinline__ int32_t dp2a_lo_s16_u8(int32_t a, uint32_t b, int32_t c) {
+// ---- fast path: 3x3, channel multiplier 1, dilation 1, stride 1 or 2, C % 4 == 0 -------
+//
+// Arithmetic.  With raw input bytes and w = f - zp_f:
+//   sum (in - zp_in) w = sum in * w - zp_in * sum w,
+// out-of-image taps read as zp_in (they then contribute zero).  dp4a multiplies four
+// unsigned input bytes with four SIGNED 8-bit weights, but w needs 9 bits.  It is split as
+// w = w1 + w2 with w1 = clamp(w, -128, 127): w2 is zero except for the few taps at the far
+// end of the filter's range (none at all when zp_f == 128), and channel groups that have
+// such a tap run a second dp4a with w2.
+//
+// Layout of the work.  A thread owns 4 adjacent channels (one 32-bit word per pixel), 4
+// adjacent output columns and a run of output rows.  Per input row it loads the 6 (stride
+// 1) or 9 (stride 2) pixel words its columns touch and transposes them with byte permutes
+// into per-channel words of 4 horizontally adjacent pixels ("windows"), so that ONE dp4a
+// covers the three taps of a filter row: stride 1 uses window [x-1,x,x+1,x+2] for output x
+// (weights [w0,w1,w2,0]) and for output x+1 (weights [0,w0,w1,w2]).  Every input row is
+// loaded and transposed once and used for the three output rows it belongs to.
+//
+// The prepack kernel turns the HWIM filter (+ bias) into those weight words once per call
+// (or once per weight tensor through mb_dwconv_u8_prepack).
+
+// Per group of 4 channels, as structure of arrays [item][group] of 16-byte items:
+//   0..5   w1[kh][align] : x,y,z,w = channels; bytes = [w0,w1,w2,0] (align 0) / [0,w0,w1,w2]
+//   6..11  w2[kh][align]
+//   12     start[c] = bias[c] - zp_in * sum_t w[t][c]
+//   13     flags: x = group has a non-zero w2
+constexpr int DW_PACK_ITEMS = 14;
+
+__device__ __forceinline__ int32_t dp4a_u8_s8(uint32_t a, uint32_t b, int32_t c) {
   int32_t d;
-  asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-__device__ __forceinline__ int32_t dp2a_hi_s16_u8(int32_t a, uint32_t b, int32_t c) {
-  int32_t d;
-  asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
 
-// Fast path: 3x3, channel multiplier 1, dilation 1, C % 4 == 0.  A thread owns
-// 4 adjacent channels (one 32-bit word per pixel) and STRIP output pixels along
-// W.  One dp2a per tap and channel multiplies the raw input byte with the
-// zero-point-free filter value (f - zp_f, kept as a signed 16-bit half-word;
-// the other half is 0 and masks the neighbouring channel's byte), so nothing is
-// unpacked.  The input zero point is folded into the start value:
-//   sum (in - zp_in)(f - zp_f) = sum in (f - zp_f) - zp_in * sum (f - zp_f)
-// with out-of-image taps read as zp_in, which makes them contribute zero.
-template <int STRIDE, int STRIP>
-__global__ void __launch_bounds__(256) dwconv3x3_u8_kernel(const DwParams p) {
-  const int cgroups = p.C >> 2;
-  const int strips_w = (p.Wo + STRIP - 1) / STRIP;
-  const int64_t total = static_cast<int64_t>(p.N) * p.Ho * strips_w * cgroups;
-  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (tid >= total) return;
-  const int cg = static_cast<int>(tid % cgroups);
-  int64_t r = tid / cgroups;
-  const int sw = static_cast<int>(r % strips_w);
-  r /= strips_w;
-  const int ho = static_cast<int>(r % p.Ho);
-  const int n = static_cast<int>(r / p.Ho);
-  const int c0 = cg * 4;
-  const int wo0 = sw * STRIP;
-
-  int32_t wq[9][4];
-  int32_t fsum[4] = {0, 0, 0, 0};
+__global__ void __launch_bounds__(128)
+dwconv3x3_prepack_kernel(const uint8_t *__restrict__ filter, const int32_t *__restrict__ bias,
+                         uint4 *__restrict__ packed, int C, int32_t zp_in, int32_t zp_f) {
+  const int groups = C >> 2;
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= groups) return;
+  int32_t w[9][4];
 #pragma unroll
   for (int t = 0; t < 9; ++t) {
-    const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(p.filter + t * p.C + c0));
+    const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(filter + t * C + g * 4));
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const int32_t f = static_cast<int32_t>((w >> (8 * c)) & 0xffu) - p.zp_f;
-      fsum[c] += f;
-      wq[t][c] = (c & 1) ? (f << 16) : (f & 0xffff);
-    }
+    for (int c = 0; c < 4; ++c) w[t][c] = static_cast<int32_t>((v >> (8 * c)) & 0xffu) - zp_f;
   }
+  int32_t any_w2 = 0;
+  uint32_t v1[3][2][4], v2[3][2][4];
   int32_t start[4];
-  {
-    int32_t b4[4] = {0, 0, 0, 0};
-    if (p.bias != nullptr) {
-      const int4 bv = __ldg(reinterpret_cast<const int4 *>(p.bias + c0));
-      b4[0] = bv.x; b4[1] = bv.y; b4[2] = bv.z; b4[3] = bv.w;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    int32_t sum = 0;
+#pragma unroll
+    for (int kh = 0; kh < 3; ++kh) {
+      uint32_t p1 = 0, p2 = 0;
+#pragma unroll
+      for (int kw = 0; kw < 3; ++kw) {
+        const int32_t x = w[kh * 3 + kw][c];
+        const int32_t a = min(127, max(-128, x)), b = x - a;
+        sum += x;
+        any_w2 |= b;
+        p1 |= (static_cast<uint32_t>(a) & 0xffu) << (8 * kw);
+        p2 |= (static_cast<uint32_t>(b) & 0xffu) << (8 * kw);
+      }
+      v1[kh][0][c] = p1; v1[kh][1][c] = p1 << 8;
+      v2[kh][0][c] = p2; v2[kh][1][c] = p2 << 8;
     }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) start[c] = b4[c] - p.zp_in * fsum[c];
+    const int32_t bv = bias != nullptr ? __ldg(bias + g * 4 + c) : 0;
+    start[c] = bv - zp_in * sum;
   }
-  int32_t acc[STRIP][4];
 #pragma unroll
-  for (int s = 0; s < STRIP; ++s)
+  for (int kh = 0; kh < 3; ++kh)
 #pragma unroll
-    for (int c = 0; c < 4; ++c) acc[s][c] = start[c];
+    for (int al = 0; al < 2; ++al) {
+      packed[(kh * 2 + al) * groups + g] =
+          make_uint4(v1[kh][al][0], v1[kh][al][1], v1[kh][al][2], v1[kh][al][3]);
+      packed[(6 + kh * 2 + al) * groups + g] =
+          make_uint4(v2[kh][al][0], v2[kh][al][1], v2[kh][al][2], v2[kh][al][3]);
+    }
+  packed[12 * groups + g] = make_uint4(start[0], start[1], start[2], start[3]);
+  packed[13 * groups + g] = make_uint4(any_w2 != 0 ? 1u : 0u, 0u, 0u, 0u);
+}
 
-  constexpr int COLS = (STRIP - 1) * STRIDE + 3;  // input columns the strip touches
-  const int hi0 = ho * STRIDE - p.pad_top;
-  const int wi0 = wo0 * STRIDE - p.pad_left;
-  const uint32_t zi4 = static_cast<uint32_t>(p.zp_in) * 0x01010101u;
-  const uint8_t *in_n = p.in + static_cast<int64_t>(n) * p.H * p.W * p.C + c0;
+// Windows of one input row: win[j][c] holds, for channel c, the 4 horizontally adjacent
+// input bytes that output column j / pair of columns needs (see the kernel).
+template <int STRIDE>
+struct DwRow {
+  // stride 1: win[0] = cols 0..3, win[1] = cols 2..5  (relative to the strip's first column)
+  // stride 2: win[j] = cols 2j .. 2j+3, j = 0..3
+  uint32_t win[STRIDE == 1 ? 2 : 4][4];
+};
+
+template <int STRIDE>
+struct DwRaw {
+  uint32_t q[STRIDE == 1 ? 6 : 9];
+};
+
+// Loads the pixel words of one input row.  Addresses are a uniform base plus an unsigned
+// 32-bit offset (the host keeps the fast path to tensors below 4 GB), which keeps the
+// per-load address arithmetic to one 32-bit addition.
+template <int STRIDE>
+__device__ __forceinline__ void dw_load_raw(DwRaw<STRIDE> &raw, const uint8_t *__restrict__ in,
+                                            uint32_t thread_off, int hi, int H, uint32_t row_stride,
+                                            const uint32_t (&col_off)[STRIDE == 1 ? 6 : 9],
+                                            uint32_t col_ok, uint32_t zi4) {
+  constexpr int COLS = STRIDE == 1 ? 6 : 9;
+  constexpr uint32_t ALL = (1u << COLS) - 1u;
+  if (hi < 0 || hi >= H) {  // a row outside the image reads as the input zero point
+#pragma unroll
+    for (int j = 0; j < COLS; ++j) raw.q[j] = zi4;
+    return;
+  }
+  const uint32_t row_off = thread_off + static_cast<uint32_t>(hi) * row_stride;
+  if (col_ok == ALL) {
+#pragma unroll
+    for (int j = 0; j < COLS; ++j)
+      raw.q[j] = __ldg(reinterpret_cast<const uint32_t *>(in + (row_off + col_off[j])));
+  } else {
+#pragma unroll
+    for (int j = 0; j < COLS; ++j)
+      raw.q[j] = ((col_ok >> j) & 1u) ? __ldg(reinterpret_cast<const uint32_t *>(in + (row_off + col_off[j]))) : zi4;
+  }
+}
+
+template <int STRIDE>
+__device__ __forceinline__ void dw_transpose(const DwRaw<STRIDE> &raw, DwRow<STRIDE> &row) {
+  // pair stage: lo = [a.b0, b.b0, a.b1, b.b1], hi = [a.b2, b.b2, a.b3, b.b3]
+  constexpr int PAIRS = STRIDE == 1 ? 3 : 4;
+  uint32_t lo[PAIRS], hi[PAIRS];
+#pragma unroll
+  for (int k = 0; k < PAIRS; ++k) {
+    lo[k] = __byte_perm(raw.q[2 * k], raw.q[2 * k + 1], 0x5140);
+    hi[k] = __byte_perm(raw.q[2 * k], raw.q[2 * k + 1], 0x7362);
+  }
+  constexpr int FULL = STRIDE == 1 ? 2 : 3;  // windows made of two pairs
+#pragma unroll
+  for (int j = 0; j < FULL; ++j) {
+    row.win[j][0] = __byte_perm(lo[j], lo[j + 1], 0x5410);
+    row.win[j][1] = __byte_perm(lo[j], lo[j + 1], 0x7632);
+    row.win[j][2] = __byte_perm(hi[j], hi[j + 1], 0x5410);
+    row.win[j][3] = __byte_perm(hi[j], hi[j + 1], 0x7632);
+  }
+  if constexpr (STRIDE == 2) {  // last window: cols 6, 7 from the last pair, col 8 from its own word
+    const uint32_t q8 = raw.q[8];
+    row.win[FULL][0] = __byte_perm(lo[PAIRS - 1], q8, 0x4410);
+    row.win[FULL][1] = __byte_perm(lo[PAIRS - 1], q8, 0x5532);
+    row.win[FULL][2] = __byte_perm(hi[PAIRS - 1], q8, 0x6610);
+    row.win[FULL][3] = __byte_perm(hi[PAIRS - 1], q8, 0x7732);
+  }
+}
+
+// acc[j][c] += one filter row (weights wa = [w0,w1,w2,0], wb = [0,w0,w1,w2]) times the row.
+template <int STRIDE>
+__device__ __forceinline__ void dw_mac(int32_t (&acc)[4][4], const DwRow<STRIDE> &row, const uint4 wa,
+                                       const uint4 wb) {
+  const uint32_t a[4] = {wa.x, wa.y, wa.z, wa.w};
+  const uint32_t b[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    if constexpr (STRIDE == 1) {
+      acc[0][c] = dp4a_u8_s8(row.win[0][c], a[c], acc[0][c]);
+      acc[1][c] = dp4a_u8_s8(row.win[0][c], b[c], acc[1][c]);
+      acc[2][c] = dp4a_u8_s8(row.win[1][c], a[c], acc[2][c]);
+      acc[3][c] = dp4a_u8_s8(row.win[1][c], b[c], acc[3][c]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[j][c] = dp4a_u8_s8(row.win[j][c], a[c], acc[j][c]);
+    }
+  }
+}
+
+// VAR: requantization variant (mb_requant_variant): bit 0 = output zero point 0, bit 1 = shift >= 1.
+template <int STRIDE, int VAR>
+__global__ void __launch_bounds__(256, 2)
+dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows_per_thread,
+                    int segments) {
+  constexpr int COLS = STRIDE == 1 ? 6 : 9;
+  const int groups = p.C >> 2;
+  const int strips = (p.Wo + 3) >> 2;
+  const int per_seg = groups * strips;
+  const unsigned per_image = static_cast<unsigned>(per_seg) * segments;
+  const unsigned id = blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned n = id / per_image;
+  if (n >= static_cast<unsigned>(p.N)) return;
+  const int rem_n = id - n * per_image;
+  const int seg = rem_n / per_seg;
+  const int rem = rem_n - seg * per_seg;
+  const int strip = rem / groups;
+  const int g = rem - strip * groups;
+  const int y0 = seg * rows_per_thread;
+  const int y1 = min(p.Ho, y0 + rows_per_thread);
+  if (y0 >= y1) return;
+  const int x0 = strip * 4;
+
+  uint4 w1[3][2];
 #pragma unroll
   for (int kh = 0; kh < 3; ++kh) {
-    const int hi = hi0 + kh;
-    const bool row_ok = hi >= 0 && hi < p.H;
-    const uint8_t *row = in_n + static_cast<int64_t>(row_ok ? hi : 0) * p.W * p.C;
-    uint32_t wv[COLS];
+    w1[kh][0] = __ldg(packed + (kh * 2 + 0) * groups + g);
+    if (STRIDE == 1) w1[kh][1] = __ldg(packed + (kh * 2 + 1) * groups + g);
+    else w1[kh][1] = w1[kh][0];
+  }
+  const uint4 st4 = __ldg(packed + 12 * groups + g);
+  const uint4 flags = __ldg(packed + 13 * groups + g);
+  const int32_t start[4] = {static_cast<int32_t>(st4.x), static_cast<int32_t>(st4.y),
+                            static_cast<int32_t>(st4.z), static_cast<int32_t>(st4.w)};
+  const bool has_w2 = flags.x != 0;
+
+  // columns: byte offsets inside a row and validity bits, fixed for the thread
+  uint32_t col_off[COLS];
+  uint32_t col_ok = 0;
+  const int xi0 = x0 * STRIDE - p.pad_left;
 #pragma unroll
-    for (int j = 0; j < COLS; ++j) {
-      const int wi = wi0 + j;
-      const bool ok = row_ok && wi >= 0 && wi < p.W;
-      wv[j] = ok ? __ldg(reinterpret_cast<const uint32_t *>(row + static_cast<int64_t>(wi) * p.C)) : zi4;
+  for (int j = 0; j < COLS; ++j) {
+    const int xi = xi0 + j;
+    const bool ok = xi >= 0 && xi < p.W;
+    col_off[j] = static_cast<uint32_t>(ok ? xi : 0) * static_cast<uint32_t>(p.C);
+    col_ok |= ok ? (1u << j) : 0u;
+  }
+  const uint32_t zi4 = static_cast<uint32_t>(p.zp_in) * 0x01010101u;
+  const uint32_t row_stride = static_cast<uint32_t>(p.W) * p.C;
+  const uint32_t in_off = n * static_cast<uint32_t>(p.H) * row_stride + g * 4;
+  const uint32_t out_row_stride = static_cast<uint32_t>(p.Wo) * p.C;
+  const uint32_t out_off = n * static_cast<uint32_t>(p.Ho) * out_row_stride + g * 4 +
+                           static_cast<uint32_t>(x0) * p.C;
+  const uint8_t *__restrict__ in = p.in;
+  uint8_t *__restrict__ out = p.out;
+  const int valid_cols = min(4, p.Wo - x0);
+
+  // one output row from three input rows
+  auto emit = [&](int y, const DwRow<STRIDE> &r0, const DwRow<STRIDE> &r1, const DwRow<STRIDE> &r2) {
+    int32_t acc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[j][c] = start[c];
+    dw_mac<STRIDE>(acc, r0, w1[0][0], w1[0][1]);
+    dw_mac<STRIDE>(acc, r1, w1[1][0], w1[1][1]);
+    dw_mac<STRIDE>(acc, r2, w1[2][0], w1[2][1]);
+    if (has_w2) {
+      dw_mac<STRIDE>(acc, r0, __ldg(packed + 6 * groups + g), __ldg(packed + 7 * groups + g));
+      dw_mac<STRIDE>(acc, r1, __ldg(packed + 8 * groups + g), __ldg(packed + 9 * groups + g));
+      dw_mac<STRIDE>(acc, r2, __ldg(packed + 10 * groups + g), __ldg(packed + 11 * groups + g));
     }
+    uint32_t o = out_off + static_cast<uint32_t>(y) * out_row_stride;
 #pragma unroll
-    for (int j = 0; j < COLS; ++j) {
+    for (int j = 0; j < 4; ++j) {
+      uint32_t b[4];
 #pragma unroll
-      for (int s = 0; s < STRIP; ++s) {
-        const int kw = j - s * STRIDE;  // compile-time after unrolling
-        if (kw >= 0 && kw < 3) {
-          const int t = kh * 3 + kw;
-          acc[s][0] = dp2a_lo_s16_u8(wq[t][0], wv[j], acc[s][0]);
-          acc[s][1] = dp2a_lo_s16_u8(wq[t][1], wv[j], acc[s][1]);
-          acc[s][2] = dp2a_hi_s16_u8(wq[t][2], wv[j], acc[s][2]);
-          acc[s][3] = dp2a_hi_s16_u8(wq[t][3], wv[j], acc[s][3]);
-        }
+      for (int c = 0; c < 4; ++c) b[c] = mb_requant_t<(VAR & 1) != 0, (VAR & 2) != 0>(acc[j][c], p.rq);
+      const uint32_t word = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+      if (j < valid_cols) *reinterpret_cast<uint32_t *>(out + o) = word;
+      o += p.C;
+    }
+  };
+
+  DwRaw<STRIDE> raw;
+  DwRow<STRIDE> ra, rb, rc;
+  const int hi0 = y0 * STRIDE - p.pad_top;
+  if constexpr (STRIDE == 1) {
+    // rows hi0, hi0+1 first; then one new input row per output row, requested one output
+    // row ahead of its use so that the load is in flight during the arithmetic
+    dw_load_raw<STRIDE>(raw, in, in_off, hi0, p.H, row_stride, col_off, col_ok, zi4);
+    dw_transpose<STRIDE>(raw, ra);
+    dw_load_raw<STRIDE>(raw, in, in_off, hi0 + 1, p.H, row_stride, col_off, col_ok, zi4);
+    dw_transpose<STRIDE>(raw, rb);
+    dw_load_raw<STRIDE>(raw, in, in_off, hi0 + 2, p.H, row_stride, col_off, col_ok, zi4);
+    for (int y = y0; y < y1; y += 3) {
+      dw_transpose<STRIDE>(raw, rc);
+      dw_load_raw<STRIDE>(raw, in, in_off, y - p.pad_top + 3, p.H, row_stride, col_off, col_ok, zi4);
+      emit(y, ra, rb, rc);
+      if (y + 1 < y1) {
+        dw_transpose<STRIDE>(raw, ra);
+        dw_load_raw<STRIDE>(raw, in, in_off, y - p.pad_top + 4, p.H, row_stride, col_off, col_ok, zi4);
+        emit(y + 1, rb, rc, ra);
+      }
+      if (y + 2 < y1) {
+        dw_transpose<STRIDE>(raw, rb);
+        dw_load_raw<STRIDE>(raw, in, in_off, y - p.pad_top + 5, p.H, row_stride, col_off, col_ok, zi4);
+        emit(y + 2, rc, ra, rb);
       }
     }
-  }
-  uint8_t *out_row = p.out + ((static_cast<int64_t>(n) * p.Ho + ho) * p.Wo) * p.C + c0;
-#pragma unroll
-  for (int s = 0; s < STRIP; ++s) {
-    const int wo = wo0 + s;
-    if (wo >= p.Wo) break;
-    uint32_t w = 0;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) w |= dw_requant(acc[s][c], p) << (8 * c);
-    *reinterpret_cast<uint32_t *>(out_row + static_cast<int64_t>(wo) * p.C) = w;
+  } else {
+    // output row y reads input rows 2y-pad .. 2y-pad+2; the last one is the next row's first
+    dw_load_raw<STRIDE>(raw, in, in_off, hi0, p.H, row_stride, col_off, col_ok, zi4);
+    dw_transpose<STRIDE>(raw, ra);
+    for (int y = y0; y < y1; y += 2) {
+      const int hi = y * 2 - p.pad_top;
+      dw_load_raw<STRIDE>(raw, in, in_off, hi + 1, p.H, row_stride, col_off, col_ok, zi4);
+      dw_transpose<STRIDE>(raw, rb);
+      dw_load_raw<STRIDE>(raw, in, in_off, hi + 2, p.H, row_stride, col_off, col_ok, zi4);
+      dw_transpose<STRIDE>(raw, rc);
+      emit(y, ra, rb, rc);
+      if (y + 1 < y1) {
+        dw_load_raw<STRIDE>(raw, in, in_off, hi + 3, p.H, row_stride, col_off, col_ok, zi4);
+        dw_transpose<STRIDE>(raw, rb);
+        dw_load_raw<STRIDE>(raw, in, in_off, hi + 4, p.H, row_stride, col_off, col_ok, zi4);
+        dw_transpose<STRIDE>(raw, ra);
+        emit(y + 1, rc, rb, ra);
+      }
+    }
   }
 }
 
@@ -177,8 +374,8 @@ __global__ void __launch_bounds__(256) dwconv_u8_general_kernel(const DwParams p
 
 }  // namespace
 
-extern "C" int mb_dwconv_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8_t *filter,
-                                 const int32_t *bias, uint8_t *out, int64_t N, int64_t H,
+static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *filter,
+                                 const int32_t *bias, const void *prepacked, uint8_t *out, int64_t N, int64_t H,
                                  int64_t W, int64_t C, int64_t mult_ch, int64_t KH, int64_t KW,
                                  int stride_h, int stride_w, int dil_h, int dil_w, int pad_top,
                                  int pad_left, int64_t Ho, int64_t Wo, int32_t zp_in,
@@ -210,18 +407,55 @@ extern "C" int mb_dwconv_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
   p.use_float = use_float_multiplier; p.mult_f = multiplier_f;
 
   const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(filter) |
-                         reinterpret_cast<uintptr_t>(out)) & 3u) == 0 &&
-                       (bias == nullptr || (reinterpret_cast<uintptr_t>(bias) & 15u) == 0);
+                         reinterpret_cast<uintptr_t>(out)) & 3u) == 0;
   const bool fast = KH == 3 && KW == 3 && mult_ch == 1 && dil_h == 1 && dil_w == 1 &&
-                    zp_in >= 0 && zp_in <= 255 && !use_float_multiplier &&
+                    zp_in >= 0 && zp_in <= 255 && zp_f >= 0 && zp_f <= 255 && !use_float_multiplier &&
                     stride_h == stride_w && (stride_h == 1 || stride_h == 2) && C % 4 == 0 &&
-                    aligned;
+                    aligned && N * H * W * C < (1ll << 32) && N * Ho * Wo * C < (1ll << 32) &&
+                    (C / 4) * ceil_div64(Wo, 4) * Ho * N < (1ll << 31) - 256;
   if (fast) {
-    constexpr int STRIP = 4;
-    const int64_t total = N * Ho * ceil_div64(Wo, STRIP) * (C / 4);
-    const unsigned blocks = static_cast<unsigned>(ceil_div64(total, 256));
-    if (stride_h == 1) dwconv3x3_u8_kernel<1, STRIP><<<blocks, 256, 0, ctx->stream>>>(p);
-    else dwconv3x3_u8_kernel<2, STRIP><<<blocks, 256, 0, ctx->stream>>>(p);
+    const int64_t groups = C / 4;
+    const uint4 *packed = static_cast<const uint4 *>(prepacked);
+    if (packed == nullptr) {  // no cached copy: prepare the weight words in scratch
+      uint4 *fresh = nullptr;
+      MB_RETURN_IF_ERROR(mb_scratch(ctx, sizeof(uint4) * DW_PACK_ITEMS * groups,
+                                    reinterpret_cast<void **>(&fresh)));
+      dwconv3x3_prepack_kernel<<<static_cast<unsigned>(ceil_div64(groups, 128)), 128, 0, ctx->stream>>>(
+          filter, bias, fresh, static_cast<int>(C), zp_in, zp_f);
+      MB_CUDA(ctx, cudaGetLastError());
+      ctx->launches++;
+      packed = fresh;
+    }
+    // Rows per thread: the longest runs for which all blocks are resident at once (two
+    // 256-thread blocks per SM), so that there is no partial last wave; tensors too large
+    // for that take runs of 16 rows.
+    const int64_t per_seg = groups * ceil_div64(Wo, 4);
+    const int64_t slots = static_cast<int64_t>(ctx->num_sms) * 2 * 256;
+    int64_t segments = slots / (per_seg * N);
+    segments = std::min<int64_t>(segments, ceil_div64(Ho, 2));
+    if (segments < 1) segments = ceil_div64(Ho, 16);
+    const int rows = static_cast<int>(ceil_div64(Ho, segments));
+    segments = ceil_div64(Ho, rows);
+    const unsigned grid = static_cast<unsigned>(ceil_div64(per_seg * segments * N, 256));
+#define MB_DW_LAUNCH(S, V)                                                                   \
+  dwconv3x3_u8_kernel<S, V><<<grid, 256, 0, ctx->stream>>>(p, packed, rows, static_cast<int>(segments))
+    const int var = mb_requant_variant(right_shift, zp_out);
+    if (stride_h == 1) {
+      switch (var) {
+        case 3: MB_DW_LAUNCH(1, 3); break;
+        case 2: MB_DW_LAUNCH(1, 2); break;
+        case 1: MB_DW_LAUNCH(1, 1); break;
+        default: MB_DW_LAUNCH(1, 0); break;
+      }
+    } else {
+      switch (var) {
+        case 3: MB_DW_LAUNCH(2, 3); break;
+        case 2: MB_DW_LAUNCH(2, 2); break;
+        case 1: MB_DW_LAUNCH(2, 1); break;
+        default: MB_DW_LAUNCH(2, 0); break;
+      }
+    }
+#undef MB_DW_LAUNCH
   } else {
     const int64_t total = N * Ho * Wo * C * mult_ch;
     if (ceil_div64(total, 256) > 0x7fffffffll)
@@ -232,3 +466,52 @@ extern "C" int mb_dwconv_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
   ctx->launches++;
   return MB_SUCCESS;
 }
+
+extern "C" {
+
+int mb_dwconv_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8_t *filter, const int32_t *bias,
+                      uint8_t *out, int64_t N, int64_t H, int64_t W, int64_t C, int64_t mult_ch,
+                      int64_t KH, int64_t KW, int stride_h, int stride_w, int dil_h, int dil_w,
+                      int pad_top, int pad_left, int64_t Ho, int64_t Wo, int32_t zp_in, int32_t zp_f,
+                      int32_t multiplier, int32_t right_shift, int32_t zp_out,
+                      int use_float_multiplier, float multiplier_f) {
+  return dwconv_u8_impl(ctx, in, filter, bias, nullptr, out, N, H, W, C, mult_ch, KH, KW, stride_h,
+                        stride_w, dil_h, dil_w, pad_top, pad_left, Ho, Wo, zp_in, zp_f, multiplier,
+                        right_shift, zp_out, use_float_multiplier, multiplier_f);
+}
+
+int mb_dwconv_u8_nhwc_prepacked(mb_context *ctx, const uint8_t *in, const uint8_t *filter,
+                                const int32_t *bias, const void *prepacked, uint8_t *out, int64_t N,
+                                int64_t H, int64_t W, int64_t C, int64_t mult_ch, int64_t KH,
+                                int64_t KW, int stride_h, int stride_w, int dil_h, int dil_w,
+                                int pad_top, int pad_left, int64_t Ho, int64_t Wo, int32_t zp_in,
+                                int32_t zp_f, int32_t multiplier, int32_t right_shift,
+                                int32_t zp_out, int use_float_multiplier, float multiplier_f) {
+  return dwconv_u8_impl(ctx, in, filter, bias, prepacked, out, N, H, W, C, mult_ch, KH, KW, stride_h,
+                        stride_w, dil_h, dil_w, pad_top, pad_left, Ho, Wo, zp_in, zp_f, multiplier,
+                        right_shift, zp_out, use_float_multiplier, multiplier_f);
+}
+
+size_t mb_dwconv3x3_u8_prepacked_bytes(int64_t C) {
+  return C > 0 && C % 4 == 0 ? sizeof(uint4) * DW_PACK_ITEMS * static_cast<size_t>(C / 4) : 0;
+}
+
+int mb_dwconv3x3_u8_prepack(mb_context *ctx, const uint8_t *filter_hwim, const int32_t *bias,
+                            int64_t C, int32_t zp_in, int32_t zp_f, void *prepacked) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (filter_hwim == nullptr || prepacked == nullptr)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_dwconv3x3_u8_prepack: null operand");
+  if (C < 4 || C % 4 != 0 || C > (1 << 24) || zp_in < 0 || zp_in > 255 || zp_f < 0 || zp_f > 255 ||
+      (reinterpret_cast<uintptr_t>(filter_hwim) & 3u) || (reinterpret_cast<uintptr_t>(prepacked) & 15u))
+    return mb_fail(ctx, MB_UNSUPPORTED,
+                   "mb_dwconv3x3_u8_prepack: needs C %% 4 == 0, zero points in 0..255, aligned pointers");
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  const int64_t groups = C / 4;
+  dwconv3x3_prepack_kernel<<<static_cast<unsigned>(ceil_div64(groups, 128)), 128, 0, ctx->stream>>>(
+      filter_hwim, bias, static_cast<uint4 *>(prepacked), static_cast<int>(C), zp_in, zp_f);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+}  // extern "C"

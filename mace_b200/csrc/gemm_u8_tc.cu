@@ -63,6 +63,7 @@ struct TcParams {
   int bias_per_row;
   int32_t zp_a, zp_b, kzz;
   mb_requant_params rq;
+  int rq_variant;  // mb_requant_variant(): bit 0 = output zero point 0, bit 1 = shift >= 1
   void *C;
   int out_is_int32;
   int vec_store_ok;  // rows of C are 16-byte aligned
@@ -96,6 +97,22 @@ __device__ __forceinline__ uint32_t sum16(const uint4 v, uint32_t s) {
   s = __dp4a(v.y, 0x01010101u, s);
   s = __dp4a(v.z, 0x01010101u, s);
   return __dp4a(v.w, 0x01010101u, s);
+}
+
+// Requantizes one 16-column chunk of an accumulator row and packs it into four words.
+template <bool ZP0, bool SGE1>
+__device__ __forceinline__ void requant_chunk(const uint32_t (&raw)[CHUNK], int32_t row_term,
+                                              const int4 *ct, const TcParams &p,
+                                              uint32_t (&packed)[CHUNK / 4]) {
+#pragma unroll
+  for (int q = 0; q < CHUNK / 4; ++q) {
+    const int4 t = ct[q];  // broadcast read: all lanes, same address
+    const uint32_t b0 = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(raw[4 * q + 0]) + row_term + t.x, p.rq);
+    const uint32_t b1 = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(raw[4 * q + 1]) + row_term + t.y, p.rq);
+    const uint32_t b2 = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(raw[4 * q + 2]) + row_term + t.z, p.rq);
+    const uint32_t b3 = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(raw[4 * q + 3]) + row_term + t.w, p.rq);
+    packed[q] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+  }
 }
 
 template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS>
@@ -393,16 +410,16 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (i + 1 < PER_WARP) tmem_ld_32x32b_x16(tbase + (chunk + 1) * CHUNK, r[(i + 1) & 1]);
         if (n0 >= p.N) continue;  // uniform across the warp; the loads above stay aligned
         const int4 *ct = reinterpret_cast<const int4 *>(col_term_sm + acc_buf * BN + chunk * CHUNK);
-        int32_t v[CHUNK];
-#pragma unroll
-        for (int q = 0; q < CHUNK / 4; ++q) {
-          const int4 t = ct[q];  // broadcast read: all lanes, same address
-          v[4 * q + 0] = static_cast<int32_t>(r[i & 1][4 * q + 0]) + row_term + t.x;
-          v[4 * q + 1] = static_cast<int32_t>(r[i & 1][4 * q + 1]) + row_term + t.y;
-          v[4 * q + 2] = static_cast<int32_t>(r[i & 1][4 * q + 2]) + row_term + t.z;
-          v[4 * q + 3] = static_cast<int32_t>(r[i & 1][4 * q + 3]) + row_term + t.w;
-        }
         if (p.out_is_int32) {
+          int32_t v[CHUNK];
+#pragma unroll
+          for (int q = 0; q < CHUNK / 4; ++q) {
+            const int4 t = ct[q];  // broadcast read: all lanes, same address
+            v[4 * q + 0] = static_cast<int32_t>(r[i & 1][4 * q + 0]) + row_term + t.x;
+            v[4 * q + 1] = static_cast<int32_t>(r[i & 1][4 * q + 1]) + row_term + t.y;
+            v[4 * q + 2] = static_cast<int32_t>(r[i & 1][4 * q + 2]) + row_term + t.z;
+            v[4 * q + 3] = static_cast<int32_t>(r[i & 1][4 * q + 3]) + row_term + t.w;
+          }
           if (row_ok) {
             if (p.vec_store_ok && n0 + CHUNK <= p.N) {
               uint4 *dst = reinterpret_cast<uint4 *>(c32 + n0);
@@ -417,11 +434,11 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         } else {
           uint32_t packed[CHUNK / 4];
-#pragma unroll
-          for (int q = 0; q < CHUNK / 4; ++q) {
-            packed[q] = mb_requant_fast(v[4 * q], p.rq) | (mb_requant_fast(v[4 * q + 1], p.rq) << 8) |
-                        (mb_requant_fast(v[4 * q + 2], p.rq) << 16) |
-                        (mb_requant_fast(v[4 * q + 3], p.rq) << 24);
+          switch (p.rq_variant) {
+            case 3: requant_chunk<true, true>(r[i & 1], row_term, ct, p, packed); break;
+            case 2: requant_chunk<false, true>(r[i & 1], row_term, ct, p, packed); break;
+            case 1: requant_chunk<true, false>(r[i & 1], row_term, ct, p, packed); break;
+            default: requant_chunk<false, false>(r[i & 1], row_term, ct, p, packed); break;
           }
           if (row_ok) {
             if (p.vec_store_ok && n0 + CHUNK <= p.N) {
@@ -570,6 +587,7 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.bias = bias; p.bias_per_row = bias_per_row;
   p.zp_a = zp_a; p.zp_b = zp_b;
   p.rq = mb_make_requant(mult, shift, zp_c);
+  p.rq_variant = mb_requant_variant(shift, zp_c);
   p.kzz = static_cast<int32_t>(static_cast<uint32_t>(K) * static_cast<uint32_t>(zp_a) *
                                static_cast<uint32_t>(zp_b));
   p.C = C; p.out_is_int32 = out_is_int32;

@@ -243,8 +243,30 @@ class DepthwiseConv2d : public delegator::DepthwiseConv2d {
       MACE_RETURN_IF_ERROR(GetOutputMultiplierAndShift(input->scale(), filter->scale(),
                                                        output->scale(), &multiplier, &right_shift));
     }
-    return rt->Status(mb_dwconv_u8_nhwc(
-        rt->ctx(), input->memory<uint8_t>(), filter->memory<uint8_t>(), bias_data,
+    // Constant filter and bias: keep the fast path's tap words from call to call, as the CPU
+    // Winograd delegator keeps its transformed filter (conv_2d_3x3_winograd.cc:120-145).
+    const void *prepacked = nullptr;
+    const bool constant = filter->is_weight() && (bias_ == nullptr || bias_->is_weight());
+    const size_t packed_bytes = mb_dwconv3x3_u8_prepacked_bytes(out_channels);
+    if (constant && !dilated && filter->dim(0) == 3 && filter->dim(1) == 3 && filter->dim(3) == 1 &&
+        packed_bytes > 0 && input->zero_point() >= 0 && input->zero_point() <= 255 &&
+        filter->zero_point() >= 0 && filter->zero_point() <= 255) {
+      if (packed_ == nullptr || packed_filter_ != filter || packed_bias_ != bias_data ||
+          packed_zp_in_ != input->zero_point() || packed_zp_f_ != filter->zero_point()) {
+        packed_ = std::make_unique<Tensor>(
+            rt, DT_UINT8, std::vector<index_t>{static_cast<index_t>(packed_bytes)}, true);
+        MACE_RETURN_IF_ERROR(rt->Status(mb_dwconv3x3_u8_prepack(
+            rt->ctx(), filter->memory<uint8_t>(), bias_data, out_channels, input->zero_point(),
+            filter->zero_point(), packed_->mutable_memory<uint8_t>())));
+        packed_filter_ = filter;
+        packed_bias_ = bias_data;
+        packed_zp_in_ = input->zero_point();
+        packed_zp_f_ = filter->zero_point();
+      }
+      prepacked = packed_->memory<uint8_t>();
+    }
+    return rt->Status(mb_dwconv_u8_nhwc_prepacked(
+        rt->ctx(), input->memory<uint8_t>(), filter->memory<uint8_t>(), bias_data, prepacked,
         output->mutable_memory<uint8_t>(), input->dim(0), input->dim(1), input->dim(2),
         input->dim(3), filter->dim(3), filter->dim(0), filter->dim(1), strides_[0], strides_[1],
         dilations_[0], dilations_[1], paddings[0] >> 1, paddings[1] >> 1, out_h, out_w,
@@ -254,6 +276,10 @@ class DepthwiseConv2d : public delegator::DepthwiseConv2d {
 
  private:
   BiasCache bias_cache_;
+  std::unique_ptr<Tensor> packed_;
+  const Tensor *packed_filter_ = nullptr;
+  const int32_t *packed_bias_ = nullptr;
+  int32_t packed_zp_in_ = 0, packed_zp_f_ = 0;
 };
 
 }  // namespace q8

@@ -140,6 +140,30 @@ def test_extreme_zero_points_and_saturation(ctx, orc):
     assert np.array_equal(got, exp)
 
 
+@pytest.mark.parametrize("zp_c", [0, 255, 100])
+@pytest.mark.parametrize("shift", [0, 1, 9, 31])
+def test_requantization_variants(ctx, orc, zp_c, shift):
+    """Every epilogue variant (output zero point 0 or not, shift 0 or not) with
+    accumulators of both signs, ties of the rounding shift and int32 biases near the
+    limits of the range."""
+    M, N, K = 128, 96, 64
+    case = gemm_case(orc, 11 + shift, 1, M, N, K, bias_len=N)
+    case["zp_c"], case["shift"] = zp_c, shift
+    case["mult"] = 1518500250 if shift else 1 << 30
+    bias = case["bias"].astype(np.int64)
+    bias[::7] = 2 ** 31 - 1 - 255 * 255 * K
+    bias[3::7] = -2 ** 31 + 255 * 255 * K
+    if shift >= 1:  # exact ties of the second rounding stage around zero
+        bias[1::5] = (1 << shift) >> 1
+        bias[2::5] = -((1 << shift) >> 1)
+    case["bias"] = bias.astype(np.int32)
+    if shift <= 1:  # keep some accumulators small enough not to saturate
+        case["A"][:, ::2, :] = case["zp_a"]
+        case["A"][:, ::2, :3] += np.arange(3, dtype=np.uint8)
+    got, exp = run_gemm(ctx, orc, case, 1, M, N, K)
+    assert np.array_equal(got, exp)
+
+
 def test_empty_and_bad_arguments(ctx):
     import mace_b200
     buf = ctx.alloc(64)

@@ -177,6 +177,54 @@ def test_dwconv_u8(ctx, orc, case):
     assert len(np.unique(got)) > 4
 
 
+@pytest.mark.parametrize("stride", [1, 2])
+@pytest.mark.parametrize("variant", ["zp_out_0", "shift_0", "shift_0_zp_out_0", "filter_zp_far", "huge_bias",
+                                     "input_zp_0"])
+def test_dwconv_u8_3x3_variants(ctx, orc, stride, variant):
+    """The 3x3 fast path over its requantization variants (output zero point 0, shift 0), a
+    filter zero point far from 128 (weights beyond the signed 8-bit range in most channels),
+    accumulators near the int32 limits, and ragged sizes (W not a multiple of 4, odd H)."""
+    N, H, W, C = 3, 23, 21, 40
+    rng = np.random.Generator(np.random.PCG64(stride * 7 + len(variant)))
+    x = rng.integers(0, 256, size=(N, H, W, C), dtype=np.uint8)
+    f = rng.integers(0, 256, size=(3, 3, C, 1), dtype=np.uint8)
+    zp_in, zp_f, zp_out = 131, 127, 77
+    bias = np.rint(rng.normal(0, 500, size=C)).astype(np.int32)
+    scale = 0.02 * 0.01 * 3 * 74 * 74 * 3 / 127
+    if variant in ("zp_out_0", "shift_0_zp_out_0"):
+        zp_out = 0
+    if variant == "filter_zp_far":
+        zp_f = 40
+    if variant == "input_zp_0":
+        zp_in = 0
+    if variant == "huge_bias":
+        bias = rng.integers(-2 ** 31 + 600000, 2 ** 31 - 600000, size=C, dtype=np.int64).astype(np.int32)
+        bias[::3] = np.rint(rng.normal(0, 500, size=bias[::3].size)).astype(np.int32)
+    mult, shift = orc.output_multiplier_and_shift(np.float32(0.02), np.float32(0.01), np.float32(scale))
+    if variant.startswith("shift_0"):
+        shift = 0
+        x = rng.integers(126, 137, size=(N, H, W, C), dtype=np.uint8)  # small accumulators
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, 3, 3, (1, 1), (stride, stride), PAD["SAME"])
+    exp = orc.dwconv_u8(x, f, bias, (stride, stride), (1, 1), (ph >> 1, pw >> 1), (Ho, Wo), zp_in,
+                        zp_f, mult, shift, zp_out)
+    dx, df, db = ctx.upload(x), ctx.upload(f), ctx.upload(bias)
+    do = ctx.alloc(exp.size)
+    ctx.dwconv_u8(dx, df, db, do, N, H, W, C, 1, 3, 3, (stride, stride), (1, 1), (ph >> 1, pw >> 1),
+                  (Ho, Wo), zp_in, zp_f, mult, shift, zp_out)
+    got = ctx.download(do, exp.shape, np.uint8)
+    # the same through a prepacked filter (what the delegator caches for weights), twice
+    packed = ctx.dwconv3x3_u8_prepack(df, db, C, zp_in, zp_f)
+    for _ in range(2):
+        ctx._check(__import__("mace_b200").lib().mb_memset(ctx.h, do.ptr, 0, do.nbytes))
+        ctx.dwconv_u8(dx, df, db, do, N, H, W, C, 1, 3, 3, (stride, stride), (1, 1),
+                      (ph >> 1, pw >> 1), (Ho, Wo), zp_in, zp_f, mult, shift, zp_out, prepacked=packed)
+        assert np.array_equal(ctx.download(do, exp.shape, np.uint8), exp)
+    for b in (dx, df, db, do, packed):
+        b.free()
+    assert np.array_equal(got, exp)
+    assert len(np.unique(got)) > 4
+
+
 # ---- pooling -----------------------------------------------------------------------
 
 @pytest.mark.parametrize("case", [(64, 7, 7, 1024, 7, 7, 1, "VALID"), (2, 9, 11, 24, 3, 3, 2, "SAME"),

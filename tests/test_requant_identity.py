@@ -41,3 +41,36 @@ def test_identity_exhaustive_small_range(orc):
         for m in (2 ** 30, 3 * 2 ** 29, 2 ** 31 - 1):
             for a in range(-3000, 3001):
                 assert device_formula(a, m, s) == orc.rounding_stages(a, m, s), (a, m, s)
+
+
+def device_formula_variants(acc, mult, s, zp0):
+    """mb_requant_t of common.cuh: for s >= 1 the high word of t, shifted by s - 1; with an
+    output zero point of 0 the [acc < 0] term is dropped."""
+    c64 = (1 << 30) + ((1 << (s + 30)) if s >= 1 else 0)
+    t = acc * mult + c64
+    if s >= 1 and not zp0 and acc < 0:
+        t -= 1 << 31
+    assert -(1 << 63) <= t < (1 << 63)
+    return ((t >> 32) >> (s - 1)) if s >= 1 else (t >> 31)
+
+
+def test_variants_match_two_step_definition(orc):
+    rng = np.random.default_rng(1)
+    for s in range(0, 32):
+        ms = [2 ** 30, 2 ** 30 + 1, 2 ** 31 - 1, 1374221056, 1392511872]
+        ms += [int(m) for m in rng.integers(2 ** 30, 2 ** 31, size=3)]
+        for m in ms:
+            accs = [0, 1, -1, 2, -2, 3, -3, 2 ** 31 - 1, -2 ** 31]
+            accs += [int(a) for a in rng.integers(-2 ** 31, 2 ** 31, size=60)]
+            accs += [int(a) for a in rng.integers(-70000, 70000, size=60)]
+            for k in (-3, -1, 0, 1, 2):
+                x = k * (1 << s) + ((1 << s) >> 1)
+                a = (x << 31) // m
+                accs += [a - 1, a, a + 1]
+            for a in accs:
+                if not (-2 ** 31 <= a < 2 ** 31):
+                    continue
+                ref = orc.rounding_stages(a, m, s)
+                assert device_formula_variants(a, m, s, False) == ref, (a, m, s)
+                z = device_formula_variants(a, m, s, True)
+                assert min(255, max(0, z)) == min(255, max(0, ref)), (a, m, s)
