@@ -26,11 +26,17 @@
 //                convolutions), where the tensor pipe has time to spare.
 //                Large-K GEMMs take their sums from separate kernels, because
 //                the extra shared-memory reads would slow their main loop.
-//   warps 6..21  epilogue: 16 warps, four per TMEM lane quarter, each on its
-//                own 16-column chunks: tcgen05.ld (the next chunk is in flight
-//                while the current one is processed), add the terms,
-//                requantize, pack, store 16-byte row segments, while the next
-//                tile is being multiplied.
+//   warps 6..21  epilogue: sets of four warps (one per TMEM lane quarter), each set on
+//                a 64-column slice of a tile; BN / 64 sets share a tile and the other
+//                sets drain the following tiles from their own accumulator buffers.
+//                Per 16-column chunk: tcgen05.ld (the next chunk is in flight while
+//                the current one is processed), add the terms, requantize (one 64-bit
+//                multiply-add per value), pack; two chunks are staged in shared memory
+//                (32 rows x 32 bytes, 32-byte swizzle) and written by one TMA store,
+//                which also clips the ragged edges of M and N.  Outputs TMA cannot
+//                address (int32, unaligned rows) take plain stores.
+//   K <= 64      K-major operands use 64- or 32-byte rows (64B / 32B swizzle) so that
+//                the TMA boxes of the first pointwise convolutions carry no padding.
 // Every wait is bounded; on a timeout the kernel records a status word, lets
 // outstanding copies land, frees its TMEM and returns.
 #include "common.cuh"
@@ -41,7 +47,8 @@ namespace {
 using namespace sm100;
 
 constexpr int BM = 128;        // rows of A per tile == TMEM lanes
-constexpr int BK = 128;        // bytes of K per pipeline stage (one swizzle row)
+constexpr int BK = 128;        // bytes of K per pipeline stage (one swizzle row); K-major
+                               // operands with K <= 64 use rows of 64 or 32 bytes (template KB)
 constexpr int UMMA_K = 32;     // K per tcgen05.mma for 8-bit operands
 constexpr int PREP_WARPS = 4;
 constexpr int EPI_WARPS = 16;
@@ -55,6 +62,9 @@ struct TcParams {
   int64_t M, N, K, batch;
   int tiles_m, tiles_n, k_blocks;
   int64_t total_tiles;
+  // gridDim.x as (step_b, step_n, step_m) in tile coordinates: advancing a CTA to its next
+  // tile is three additions and two carries instead of 64-bit divisions
+  int step_m, step_n, step_b;
   const uint32_t *sum_a;  // [batch or 1][M]; null when fused or zp_b == 0
   const uint32_t *sum_b;  // [batch or 1][N]; null when fused or zp_a == 0
   int64_t sum_a_bstride, sum_b_bstride;
@@ -66,9 +76,12 @@ struct TcParams {
   int rq_variant;  // mb_requant_variant(): bit 0 = output zero point 0, bit 1 = shift >= 1
   void *C;
   int out_is_int32;
-  int vec_store_ok;  // rows of C are 16-byte aligned
+  int c_tma;  // uint8 C written by TMA stores (base and rows 16-byte aligned)
   int *status;
-  long long *timeline;  // null, or 32 clock stamps written by CTA 0 (profiling aid)
+  // null, or clock stamps written by CTA 0 (profiling aid): 32 milestone slots, then 5
+  // slots for each of its first 16 tiles (TMA issued, tile landed, MMAs committed,
+  // epilogue begins, epilogue ends); the buffer holds 128 values
+  long long *timeline;
 };
 
 // Clock stamp of a pipeline milestone, CTA 0 only, when a buffer was given.
@@ -77,19 +90,32 @@ struct TcParams {
     if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[slot] = clock64(); \
   } while (0)
 
-template <int BN, bool B_MN>
+// Per-tile stamp k (0..4) of CTA 0's n-th tile, first 16 tiles only.
+#define MB_STAMP_TILE(tile, k)                                                       \
+  do {                                                                              \
+    if (p.timeline != nullptr && blockIdx.x == 0 && (tile) < 16)                    \
+      p.timeline[32 + (tile) * 5 + (k)] = clock64();                                \
+  } while (0)
+
+template <int BN, bool B_MN, int KB = BK>
 struct TileCfg {
-  static constexpr int A_BYTES = BM * BK;
-  static constexpr int B_BYTES = B_MN ? ((BN + 127) / 128) * 128 * BK : BN * BK;
+  static_assert(KB == 128 || !B_MN, "short rows are for K-major operands");
+  static constexpr int A_BYTES = BM * KB;
+  static constexpr int B_BYTES = B_MN ? ((BN + 127) / 128) * 128 * KB : BN * KB;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
+  // epilogue staging for the TMA stores: 1 KB (32 rows x 32 bytes) per epilogue warp
+  static constexpr int STAGING_BYTES = EPI_WARPS * 1024;
+  static constexpr int RING_BUDGET = 208 * 1024 - STAGING_BYTES;
+  static constexpr int STAGES = RING_BUDGET / STAGE_BYTES > 8 ? 8 : RING_BUDGET / STAGE_BYTES;
   // all 512 TMEM columns as accumulator buffers: 2 for BN = 256, 4 for 128, 8 for 64, so
   // that narrow tiles (short main loops) keep several tiles in flight
   static constexpr int NUM_ACC = 512 / BN;
   static constexpr int TMEM_COLS = 512;
   static constexpr int BAR_BYTES = 512;
   static constexpr int TERM_BYTES = NUM_ACC * (128 + BN) * 4;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + BAR_BYTES + TERM_BYTES;
+  static constexpr int SMEM_BYTES =
+      STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + BAR_BYTES + TERM_BYTES;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
 __device__ __forceinline__ uint32_t sum16(const uint4 v, uint32_t s) {
@@ -98,6 +124,27 @@ __device__ __forceinline__ uint32_t sum16(const uint4 v, uint32_t s) {
   s = __dp4a(v.z, 0x01010101u, s);
   return __dp4a(v.w, 0x01010101u, s);
 }
+
+// Tile coordinates of a persistent CTA: tile index = (b * tiles_n + tn) * tiles_m + tm,
+// advanced by gridDim.x per step.
+struct TileIter {
+  int tm, tn, b;
+  __device__ __forceinline__ TileIter(const TcParams &p) {
+    const unsigned t = blockIdx.x;  // < tiles of the first wave, one division pair per kernel
+    tm = t % p.tiles_m;
+    const unsigned q = t / p.tiles_m;
+    tn = q % p.tiles_n;
+    b = q / p.tiles_n;
+  }
+  __device__ __forceinline__ bool valid(const TcParams &p) const { return b < p.batch; }
+  __device__ __forceinline__ void next(const TcParams &p) {
+    tm += p.step_m;
+    tn += p.step_n;
+    b += p.step_b;
+    if (tm >= p.tiles_m) { tm -= p.tiles_m; ++tn; }
+    if (tn >= p.tiles_n) { tn -= p.tiles_n; ++b; }
+  }
+};
 
 // Requantizes one 16-column chunk of an accumulator row and packs it into four words.
 template <bool ZP0, bool SGE1>
@@ -115,17 +162,23 @@ __device__ __forceinline__ void requant_chunk(const uint32_t (&raw)[CHUNK], int3
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS>
+template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS, int KB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                  const __grid_constant__ CUtensorMap tmap_b, const TcParams p) {
-  using Cfg = TileCfg<BN, B_MN>;
+                  const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_c, const TcParams p) {
+  using Cfg = TileCfg<BN, B_MN, KB>;
   constexpr int STAGES = Cfg::STAGES;
+  // shared-memory descriptor fields for rows of KB bytes: swizzle mode and the distance
+  // between 8-row groups
+  constexpr uint32_t SWZ = KB == 128 ? 2u : KB == 64 ? 4u : 6u;
+  constexpr uint32_t SBO = 8 * KB;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
   // barrier block after the tile ring
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_aligned + STAGES * Cfg::STAGE_BYTES);
+  uint64_t *bars =
+      reinterpret_cast<uint64_t *>(smem_aligned + STAGES * Cfg::STAGE_BYTES + Cfg::STAGING_BYTES);
   const uint32_t full_bar = smem_u32(bars);                  // [STAGES] tile landed
   const uint32_t empty_bar = full_bar + 8 * STAGES;          // [STAGES] tile consumed
   constexpr int NUM_ACC = Cfg::NUM_ACC;
@@ -136,7 +189,8 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   // per accumulator buffer: row terms [128] and column terms [BN]
   int32_t *row_term_sm =
-      reinterpret_cast<int32_t *>(smem_aligned + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES);
+      reinterpret_cast<int32_t *>(smem_aligned + STAGES * Cfg::STAGE_BYTES + Cfg::STAGING_BYTES +
+                                  Cfg::BAR_BYTES);
   int32_t *col_term_sm = row_term_sm + NUM_ACC * 128;
 
   const int warp = threadIdx.x >> 5;
@@ -146,13 +200,14 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     MB_STAMP(0);
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    if (p.c_tma) prefetch_tensormap(&tmap_c);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, FUSE_SUMS ? 1 + PREP_WARPS : 1);
     }
     for (int b = 0; b < NUM_ACC; ++b) {
       mbar_init(tfull_bar + 8 * b, 1);
-      mbar_init(tempty_bar + 8 * b, EPI_WARPS);
+      mbar_init(tempty_bar + 8 * b, 4 * (BN / 64));
       mbar_init(terms_bar + 8 * b, PREP_WARPS);
     }
     *abort_flag = 0;
@@ -168,7 +223,6 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) MB_STAMP(1);
 
-  const int tiles_per_batch = p.tiles_m * p.tiles_n;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -178,10 +232,9 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-        const int b = static_cast<int>(tile / tiles_per_batch);
-        const int rem = static_cast<int>(tile % tiles_per_batch);
-        const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
+      int local = 0;  // this CTA's tile counter (profiling stamps)
+      for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
+        const int b = it.b, tm = it.tm, tn = it.tn;
         const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, WAIT_BUDGET)) {
@@ -196,18 +249,19 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t sb = sa + Cfg::A_BYTES;
             mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
             if (A_MN) {
-              tma_load_3d(sa, &tmap_a, fb, tm * BM, kb * BK, ab);
+              tma_load_3d(sa, &tmap_a, fb, tm * BM, kb * KB, ab);
             } else {
-              tma_load_3d(sa, &tmap_a, fb, kb * BK, tm * BM, ab);
+              tma_load_3d(sa, &tmap_a, fb, kb * KB, tm * BM, ab);
             }
             if (B_MN) {
 #pragma unroll
               for (int j = 0; j < (BN + 127) / 128; ++j)
-                tma_load_3d(sb + j * 128 * BK, &tmap_b, fb, tn * BN + j * 128, kb * BK, bb);
+                tma_load_3d(sb + j * 128 * KB, &tmap_b, fb, tn * BN + j * 128, kb * KB, bb);
             } else {
-              tma_load_3d(sb, &tmap_b, fb, kb * BK, tn * BN, bb);
+              tma_load_3d(sb, &tmap_b, fb, kb * KB, tn * BN, bb);
             }
-            if (tile == 0) MB_STAMP(2 + (kb < 3 ? kb : 3));  // TMA of k-block kb issued
+            if (local == 0) MB_STAMP(2 + (kb < 3 ? kb : 3));  // TMA of k-block kb issued
+            if (kb == 0) MB_STAMP_TILE(local, 0);
           }
           __syncwarp();
           if (++stage == STAGES) {
@@ -227,7 +281,8 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc_buf = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+      int local = 0;
+      for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
         if (!mbar_wait_warp(tempty_bar + 8 * acc_buf, acc_phase ^ 1, abort_flag, WAIT_BUDGET)) {
           *abort_flag = 1;
           atomicCAS(p.status, 0, MB_DEV_TIMEOUT_MMA);
@@ -243,11 +298,12 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             break;
           }
           tc_fence_after_sync();
-          if (tile == 0) MB_STAMP(6 + (kb < 3 ? kb : 3));  // k-block kb landed
+          if (local == 0) MB_STAMP(6 + (kb < 3 ? kb : 3));  // k-block kb landed
+          if (kb == p.k_blocks - 1 && lane == 0) MB_STAMP_TILE(local, 1);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + Cfg::A_BYTES;
-          const int64_t k_left = p.K - static_cast<int64_t>(kb) * BK;
-          const int ksteps = k_left >= BK ? BK / UMMA_K
+          const int64_t k_left = p.K - static_cast<int64_t>(kb) * KB;
+          const int ksteps = k_left >= KB ? KB / UMMA_K
                                           : static_cast<int>((k_left + UMMA_K - 1) / UMMA_K);
           if (lane == 0) {
 #pragma unroll 4
@@ -258,11 +314,11 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // 8-k-row groups 1024 bytes apart, 128-element atoms 16 KB apart;
             // a K step moves 32 k-rows = 4096 bytes.
             const uint64_t a_desc =
-                A_MN ? make_smem_desc(sa + j * UMMA_K * 128, 128 * BK, 1024, SWIZZLE_128B)
-                     : make_smem_desc(sa + j * UMMA_K, 16, 1024, SWIZZLE_128B);
+                A_MN ? make_smem_desc(sa + j * UMMA_K * 128, 128 * KB, 1024, SWIZZLE_128B)
+                     : make_smem_desc(sa + j * UMMA_K, 16, SBO, SWZ);
             const uint64_t b_desc =
-                B_MN ? make_smem_desc(sb + j * UMMA_K * 128, 128 * BK, 1024, SWIZZLE_128B)
-                     : make_smem_desc(sb + j * UMMA_K, 16, 1024, SWIZZLE_128B);
+                B_MN ? make_smem_desc(sb + j * UMMA_K * 128, 128 * KB, 1024, SWIZZLE_128B)
+                     : make_smem_desc(sb + j * UMMA_K, 16, SBO, SWZ);
             mma_i8_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || j > 0) ? 1u : 0u);
           }
           mma_commit(empty_bar + 8 * stage);  // frees the stage when the MMAs have read it
@@ -276,7 +332,8 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!ok) break;
         if (lane == 0) {
           mma_commit(tfull_bar + 8 * acc_buf);  // accumulator complete
-          if (tile == 0) MB_STAMP(10);
+          if (local == 0) MB_STAMP(10);
+          MB_STAMP_TILE(local, 2);
         }
         __syncwarp();
         if (++acc_buf == NUM_ACC) {
@@ -293,10 +350,9 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc_buf = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int64_t tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-      const int b = static_cast<int>(tile / tiles_per_batch);
-      const int rem = static_cast<int>(tile % tiles_per_batch);
-      const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
+    int local = 0;
+    for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
+      const int b = it.b, tm = it.tm, tn = it.tn;
       uint32_t sa_sum = 0, sb_sum[(BN + 127) / 128];
 #pragma unroll
       for (int j = 0; j < (BN + 127) / 128; ++j) sb_sum[j] = 0;
@@ -323,19 +379,19 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           const uint8_t *ta = smem_aligned + stage * Cfg::STAGE_BYTES;
           const uint8_t *tb = ta + Cfg::A_BYTES;
-          // a row is 128 bytes = 8 chunks of 16; start at chunk (r & 7) so that the
-          // 8 threads of a quarter warp hit 8 different bank groups.  The 128-byte
-          // swizzle only permutes chunks inside a row, which a sum does not see.
+          // a row is KB bytes = KB / 16 chunks of 16; start at chunk (r mod chunks) so that
+          // the threads of a quarter warp spread over the bank groups.  The swizzle only
+          // permutes chunks inside a row, which a sum does not see.
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            sa_sum = sum16(*reinterpret_cast<const uint4 *>(ta + r * 128 + ((i + r) & 7) * 16), sa_sum);
+          for (int i = 0; i < KB / 16; ++i)
+            sa_sum = sum16(*reinterpret_cast<const uint4 *>(ta + r * KB + ((i + r) & (KB / 16 - 1)) * 16), sa_sum);
 #pragma unroll
           for (int j = 0; j < (BN + 127) / 128; ++j) {
             const int row = j * 128 + r;
             if (row < BN) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                sb_sum[j] = sum16(*reinterpret_cast<const uint4 *>(tb + row * 128 + ((i + r) & 7) * 16),
+              for (int i = 0; i < KB / 16; ++i)
+                sb_sum[j] = sum16(*reinterpret_cast<const uint4 *>(tb + row * KB + ((i + r) & (KB / 16 - 1)) * 16),
                                   sb_sum[j]);
             }
           }
@@ -366,7 +422,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (j * 128 + r < BN) col_term_sm[acc_buf * BN + j * 128 + r] = col_term[j];
       __syncwarp();
       if (lane == 0) mbar_arrive(terms_bar + 8 * acc_buf);
-      if (tile == 0 && warp == 2 && lane == 0) MB_STAMP(11);
+      if (local == 0 && warp == 2 && lane == 0) MB_STAMP(11);
       if (++acc_buf == NUM_ACC) {
         acc_buf = 0;
         acc_phase ^= 1;
@@ -374,16 +430,30 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ---------------- epilogue ----------------
+    // Four consecutive warps cover the four TMEM lane quarters of a 64-column slice of a
+    // tile; BN / 64 such sets work on one tile, and the remaining sets on the tiles after
+    // it (GROUPS tiles are drained at the same time, each from its own accumulator
+    // buffer).  Per tile a warp handles 32 rows x 64 columns in four 16-column chunks.
+    constexpr int SETS_PER_TILE = BN / 64;             // 1, 2, 4
+    constexpr int GROUPS = 4 / SETS_PER_TILE;          // 4, 2, 1 tiles in flight
+    constexpr int CHUNKS_PER_WARP = 4;
     const int quarter = warp & 3;                      // TMEM lanes [32*quarter, +32) are this warp's
-    const int col_group = (warp - FIRST_EPI_WARP) >> 2;  // 0..3: which chunks of the tile
-    constexpr int CHUNKS = BN / CHUNK;
-    constexpr int PER_WARP = CHUNKS / 4;               // BN = 64 -> 1, 128 -> 2, 256 -> 4
-    int acc_buf = 0;
-    uint32_t acc_phase = 0;
-    for (int64_t tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
-      const int b = static_cast<int>(tile / tiles_per_batch);
-      const int rem = static_cast<int>(tile % tiles_per_batch);
-      const int tm = rem % p.tiles_m, tn = rem / p.tiles_m;
+    const int set = (warp - FIRST_EPI_WARP) >> 2;      // 0..3
+    const int slice = set % SETS_PER_TILE;             // which 64 columns of the tile
+    const int group = set / SETS_PER_TILE;             // which tiles: local % GROUPS == group
+    // staging for the TMA store: 32 rows x 32 bytes (two chunks), 32-byte swizzle:
+    // 16-byte half h of row r sits at r*32 + ((h ^ (r >> 2)) & 1)*16, which keeps the
+    // quarter-warps' 16-byte writes free of bank conflicts
+    uint8_t *stage_ptr = smem_aligned + STAGES * Cfg::STAGE_BYTES + (warp - FIRST_EPI_WARP) * 1024;
+    const uint32_t stage_addr = smem_u32(stage_ptr);
+    uint4 *stage_row = reinterpret_cast<uint4 *>(stage_ptr + lane * 32);
+    const int swz = (lane >> 2) & 1;
+    int local = 0;
+    for (TileIter it(p); it.valid(p); it.next(p), ++local) {
+      if (local % GROUPS != group) continue;
+      const int b = it.b, tm = it.tm, tn = it.tn;
+      const int acc_buf = local % NUM_ACC;
+      const uint32_t acc_phase = (local / NUM_ACC) & 1;
       if (!mbar_wait_warp(tfull_bar + 8 * acc_buf, acc_phase, abort_flag, WAIT_BUDGET) ||
           !mbar_wait_warp(terms_bar + 8 * acc_buf, acc_phase, abort_flag, WAIT_BUDGET)) {
         *abort_flag = 1;
@@ -391,75 +461,88 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         break;
       }
       tc_fence_after_sync();
-      if (tile == 0 && warp == FIRST_EPI_WARP && lane == 0) MB_STAMP(12);
-      const int64_t m = static_cast<int64_t>(tm) * BM + quarter * 32 + lane;
+      if (local == 0 && warp == FIRST_EPI_WARP && lane == 0) MB_STAMP(12);
+      if (warp == FIRST_EPI_WARP && lane == 0) MB_STAMP_TILE(local, 3);
+      const int m0 = tm * BM + quarter * 32;           // first row of this warp
+      const int64_t m = static_cast<int64_t>(m0) + lane;
       const bool row_ok = m < p.M;
       const int32_t row_term = row_term_sm[acc_buf * 128 + quarter * 32 + lane];
-      uint8_t *c8 = static_cast<uint8_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
-      int32_t *c32 = static_cast<int32_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
-      const uint32_t tbase =
-          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BN;
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BN +
+                             slice * 64;
+      const int32_t *ct_base = col_term_sm + acc_buf * BN + slice * 64;
+      const int64_t n_first = static_cast<int64_t>(tn) * BN + slice * 64;
       uint32_t r[2][CHUNK];
-      // chunk indices of this warp: col_group * PER_WARP + i (contiguous columns)
-      tmem_ld_32x32b_x16(tbase + (col_group * PER_WARP) * CHUNK, r[0]);
+      tmem_ld_32x32b_x16(tbase, r[0]);
+      if (p.c_tma) {
+        // uint8 output through shared memory and TMA stores of 32 rows x 32 bytes
 #pragma unroll
-      for (int i = 0; i < PER_WARP; ++i) {
-        const int chunk = col_group * PER_WARP + i;
-        const int64_t n0 = static_cast<int64_t>(tn) * BN + chunk * CHUNK;
-        tmem_ld_wait_x16(r[i & 1]);
-        if (i + 1 < PER_WARP) tmem_ld_32x32b_x16(tbase + (chunk + 1) * CHUNK, r[(i + 1) & 1]);
-        if (n0 >= p.N) continue;  // uniform across the warp; the loads above stay aligned
-        const int4 *ct = reinterpret_cast<const int4 *>(col_term_sm + acc_buf * BN + chunk * CHUNK);
-        if (p.out_is_int32) {
-          int32_t v[CHUNK];
-#pragma unroll
-          for (int q = 0; q < CHUNK / 4; ++q) {
-            const int4 t = ct[q];  // broadcast read: all lanes, same address
-            v[4 * q + 0] = static_cast<int32_t>(r[i & 1][4 * q + 0]) + row_term + t.x;
-            v[4 * q + 1] = static_cast<int32_t>(r[i & 1][4 * q + 1]) + row_term + t.y;
-            v[4 * q + 2] = static_cast<int32_t>(r[i & 1][4 * q + 2]) + row_term + t.z;
-            v[4 * q + 3] = static_cast<int32_t>(r[i & 1][4 * q + 3]) + row_term + t.w;
+        for (int i = 0; i < CHUNKS_PER_WARP; ++i) {
+          tmem_ld_wait_x16(r[i & 1]);
+          if (i + 1 < CHUNKS_PER_WARP) tmem_ld_32x32b_x16(tbase + (i + 1) * CHUNK, r[(i + 1) & 1]);
+          if (i == CHUNKS_PER_WARP - 1) {
+            // the accumulator is in registers: hand the buffer back to the MMA warp
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar + 8 * acc_buf);
           }
-          if (row_ok) {
-            if (p.vec_store_ok && n0 + CHUNK <= p.N) {
-              uint4 *dst = reinterpret_cast<uint4 *>(c32 + n0);
-#pragma unroll
-              for (int q = 0; q < CHUNK / 4; ++q)
-                dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < CHUNK; ++j)
-                if (n0 + j < p.N) c32[n0 + j] = v[j];
-            }
-          }
-        } else {
           uint32_t packed[CHUNK / 4];
+          const int4 *ct = reinterpret_cast<const int4 *>(ct_base + i * CHUNK);
           switch (p.rq_variant) {
             case 3: requant_chunk<true, true>(r[i & 1], row_term, ct, p, packed); break;
             case 2: requant_chunk<false, true>(r[i & 1], row_term, ct, p, packed); break;
             case 1: requant_chunk<true, false>(r[i & 1], row_term, ct, p, packed); break;
             default: requant_chunk<false, false>(r[i & 1], row_term, ct, p, packed); break;
           }
-          if (row_ok) {
-            if (p.vec_store_ok && n0 + CHUNK <= p.N) {
-              *reinterpret_cast<uint4 *>(c8 + n0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < CHUNK; ++j)
-                if (n0 + j < p.N) c8[n0 + j] = static_cast<uint8_t>(packed[j >> 2] >> (8 * (j & 3)));
+          if ((i & 1) == 0) {
+            // the previous store must have read the staging buffer before it is refilled
+            if (lane == 0) bulk_wait_group_read<0>();
+            __syncwarp();
+          }
+          stage_row[(i & 1) ^ swz] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          if (i & 1) {
+            fence_proxy_async();
+            __syncwarp();
+            const int64_t n0 = n_first + (i - 1) * CHUNK;
+            if (lane == 0 && n0 < p.N && m0 < p.M) {
+              tma_store_3d(&tmap_c, stage_addr, static_cast<int>(n0), m0, b);
+              bulk_commit_group();
             }
           }
         }
+      } else {
+        // direct stores: int32 output, or a uint8 output whose rows TMA cannot address
+        uint8_t *c8 = static_cast<uint8_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
+        int32_t *c32 = static_cast<int32_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
+#pragma unroll 1
+        for (int i = 0; i < CHUNKS_PER_WARP; ++i) {
+          uint32_t v[CHUNK];
+          tmem_ld_wait_x16(r[0]);
+#pragma unroll
+          for (int j = 0; j < CHUNK; ++j) v[j] = r[0][j];
+          if (i + 1 < CHUNKS_PER_WARP) tmem_ld_32x32b_x16(tbase + (i + 1) * CHUNK, r[0]);
+          const int64_t n0 = n_first + i * CHUNK;
+          const int32_t *ct = ct_base + i * CHUNK;
+          if (row_ok && n0 < p.N) {
+#pragma unroll
+            for (int j = 0; j < CHUNK; ++j) {
+              const int32_t acc = static_cast<int32_t>(v[j]) + row_term + ct[j];
+              if (n0 + j < p.N) {
+                if (p.out_is_int32) c32[n0 + j] = acc;
+                else c8[n0 + j] = static_cast<uint8_t>(mb_requant_fast(acc, p.rq));
+              }
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar + 8 * acc_buf);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar + 8 * acc_buf);
-      if (warp == FIRST_EPI_WARP && lane == 0) MB_STAMP(tile == 0 ? 13 : 14);
-      if (++acc_buf == NUM_ACC) {
-        acc_buf = 0;
-        acc_phase ^= 1;
-      }
+      if (warp == FIRST_EPI_WARP && lane == 0) MB_STAMP(local == 0 ? 13 : 14);
+      if (warp == FIRST_EPI_WARP && lane == 0) MB_STAMP_TILE(local, 4);
     }
+    // the staging buffer must outlive the last store's read, and the kernel its writes
+    if (lane == 0) bulk_wait_group<0>();
+    __syncwarp();
   }
 
   __syncthreads();
@@ -481,38 +564,43 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// 3-D uint8 tensor map: dims {inner, rows, batch}, 128-byte swizzle.
+// 3-D uint8 tensor map: dims {inner, rows, batch}; 128-byte swizzle for the operand
+// tiles, 32-byte swizzle for the output staging boxes.
 int make_map_u8(mb_context *ctx, CUtensorMap *map, const void *base, uint64_t inner,
                 uint64_t rows, uint64_t batch, uint64_t batch_stride_bytes, uint32_t box_inner,
-                uint32_t box_rows) {
+                uint32_t box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   const cuuint64_t dims[3] = {inner, rows, batch};
   const cuuint64_t strides[2] = {inner, batch_stride_bytes};
   const cuuint32_t box[3] = {box_inner, box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
       map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, estr,
-      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return mb_fail(ctx, MB_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
   return MB_SUCCESS;
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS = false>
-int launch_cfg(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, TcParams &p) {
-  using Cfg = TileCfg<BN, B_MN>;
-  auto kern = gemm_u8_tc_kernel<BN, A_MN, B_MN, FUSE_SUMS>;
+template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS = false, int KB = BK>
+int launch_cfg(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc,
+               TcParams &p) {
+  using Cfg = TileCfg<BN, B_MN, KB>;
+  auto kern = gemm_u8_tc_kernel<BN, A_MN, B_MN, FUSE_SUMS, KB>;
   // The opt-in shared-memory limit is a per-device function attribute; set it
   // once per context.
   constexpr int cfg_id = (BN == 256 ? 0 : BN == 128 ? 1 : 2) * 4 + (A_MN ? 2 : 0) + (B_MN ? 1 : 0) +
-                         (FUSE_SUMS ? 12 : 0);
+                         (FUSE_SUMS ? 12 : 0) + (KB == 64 ? 3 : KB == 32 ? 6 : 0);
   if (!(ctx->func_attr_mask & (1ull << cfg_id))) {
     MB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg::SMEM_BYTES));
     ctx->func_attr_mask |= (1ull << cfg_id);
   }
   const int grid = static_cast<int>(p.total_tiles < ctx->num_sms ? p.total_tiles : ctx->num_sms);
-  kern<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(ta, tb, p);
+  p.step_m = grid % p.tiles_m;
+  p.step_n = (grid / p.tiles_m) % p.tiles_n;
+  p.step_b = (grid / p.tiles_m) / p.tiles_n;
+  kern<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(ta, tb, tc, p);
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   ctx->launches_tc++;
@@ -550,8 +638,12 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
                          int bias_per_row) {
   // Operand sums computed inside the kernel: K-major operands, short K, and the
   // caller passed no precomputed sums although a zero point needs them.
-  const bool fuse = !a_mn && !b_mn && K <= 8 * BK && sum_a == nullptr && sum_b == nullptr &&
-                    (zp_a != 0 || zp_b != 0);
+  // Rows of 64 or 32 bytes for K-major operands with K <= 64 (the first pointwise
+  // convolutions of a network): the TMA boxes then hold no out-of-range bytes.  These
+  // shapes always take the fused kernel (it also serves zero points of 0).
+  const bool kmajor_free = !a_mn && !b_mn && sum_a == nullptr && sum_b == nullptr;
+  const int KBsel = (kmajor_free && K <= 32) ? 32 : (kmajor_free && K <= 64) ? 64 : BK;
+  const bool fuse = kmajor_free && K <= 8 * BK && (zp_a != 0 || zp_b != 0 || KBsel != BK);
   // Tile width.  Long main loops (K > 1024) want the widest tile for operand
   // reuse.  Short ones are bound by the epilogue, whose cost grows with the
   // width, plus a fixed cost per tile: pick the width with the fewest rounds
@@ -579,7 +671,7 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.M = M; p.N = N; p.K = K; p.batch = batch;
   p.tiles_m = static_cast<int>(ceil_div64(M, BM));
   p.tiles_n = static_cast<int>(ceil_div64(N, BN));
-  p.k_blocks = static_cast<int>(ceil_div64(K, BK));
+  p.k_blocks = static_cast<int>(ceil_div64(K, KBsel));
   p.total_tiles = batch * p.tiles_m * p.tiles_n;
   p.sum_a = sum_a; p.sum_b = sum_b;
   p.sum_a_bstride = M; p.sum_b_bstride = N;
@@ -592,36 +684,48 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
                                static_cast<uint32_t>(zp_b));
   p.C = C; p.out_is_int32 = out_is_int32;
   const uintptr_t cbase = reinterpret_cast<uintptr_t>(C);
-  p.vec_store_ok = out_is_int32 ? ((cbase % 16 == 0) && (N % 4 == 0))
-                                : ((cbase % 16 == 0) && (N % 16 == 0));
+  p.c_tma = (!out_is_int32 && cbase % 16 == 0 && N % 16 == 0 && N >= 32 && M >= 32) ? 1 : 0;
   p.status = ctx->dev_status;
   p.timeline = ctx->tc_timeline;
 
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tc;
+  if (p.c_tma) {
+    MB_RETURN_IF_ERROR(make_map_u8(ctx, &tc, C, N, M, batch, M * N, 32, 32, CU_TENSOR_MAP_SWIZZLE_32B));
+  } else {
+    memset(&tc, 0, sizeof(tc));
+  }
   const uint64_t nb_a = a_batched ? batch : 1, nb_b = b_batched ? batch : 1;
+  const CUtensorMapSwizzle kswz = KBsel == 32   ? CU_TENSOR_MAP_SWIZZLE_32B
+                                  : KBsel == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                : CU_TENSOR_MAP_SWIZZLE_128B;
   if (a_mn) {
     MB_RETURN_IF_ERROR(make_map_u8(ctx, &ta, A, M, K, nb_a, M * K, 128, BK));
   } else {
-    MB_RETURN_IF_ERROR(make_map_u8(ctx, &ta, A, K, M, nb_a, M * K, BK, BM));
+    MB_RETURN_IF_ERROR(make_map_u8(ctx, &ta, A, K, M, nb_a, M * K, KBsel, BM, kswz));
   }
   if (b_mn) {
     MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, N, K, nb_b, N * K, 128, BK));
   } else {
-    MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, K, N, nb_b, N * K, BK, BN));
+    MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, K, N, nb_b, N * K, KBsel, BN, kswz));
   }
 
 #define MB_TC_DISPATCH(BN_)                                                         \
   if (a_mn) {                                                                       \
-    if (b_mn) return launch_cfg<BN_, true, true>(ctx, ta, tb, p);                   \
-    return launch_cfg<BN_, true, false>(ctx, ta, tb, p);                            \
+    if (b_mn) return launch_cfg<BN_, true, true>(ctx, ta, tb, tc, p);                   \
+    return launch_cfg<BN_, true, false>(ctx, ta, tb, tc, p);                            \
   } else {                                                                          \
-    if (b_mn) return launch_cfg<BN_, false, true>(ctx, ta, tb, p);                  \
-    return launch_cfg<BN_, false, false>(ctx, ta, tb, p);                           \
+    if (b_mn) return launch_cfg<BN_, false, true>(ctx, ta, tb, tc, p);                  \
+    return launch_cfg<BN_, false, false>(ctx, ta, tb, tc, p);                           \
   }
   if (fuse) {
-    if (BN == 256) return launch_cfg<256, false, false, true>(ctx, ta, tb, p);
-    if (BN == 128) return launch_cfg<128, false, false, true>(ctx, ta, tb, p);
-    return launch_cfg<64, false, false, true>(ctx, ta, tb, p);
+#define MB_TC_FUSED(KB_)                                                                  \
+  if (BN == 256) return launch_cfg<256, false, false, true, KB_>(ctx, ta, tb, tc, p);     \
+  if (BN == 128) return launch_cfg<128, false, false, true, KB_>(ctx, ta, tb, tc, p);     \
+  return launch_cfg<64, false, false, true, KB_>(ctx, ta, tb, tc, p);
+    if (KBsel == 32) { MB_TC_FUSED(32) }
+    if (KBsel == 64) { MB_TC_FUSED(64) }
+    MB_TC_FUSED(128)
+#undef MB_TC_FUSED
   }
   if (BN == 256) { MB_TC_DISPATCH(256) }
   if (BN == 128) { MB_TC_DISPATCH(128) }

@@ -62,16 +62,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same with a suspend-time hint: the hardware may park the thread for up to `ns`
+// nanoseconds (or until the phase completes), so that a waiting warp does not take issue
+// slots from the warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Wait for the phase with the given parity to complete.  Gives up after
 // `budget` clock cycles or as soon as *abort_flag becomes non-zero; returns
-// false in both cases.
+// false in both cases.  Between polls the thread is parked by the hardware.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int *abort_flag,
                                           long long budget) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
     if (*abort_flag != 0) return false;
     if (clock64() - start > budget) return false;
   }
@@ -127,6 +144,35 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap
       : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0),
         "r"(c1), "r"(c2)
       : "memory");
+}
+
+// 3-D tiled store shared -> global (bulk async-group completion).  Writes outside the
+// tensor's extents are clipped by the hardware.  c0 must keep the store 16-byte aligned,
+// and no coordinate may be negative.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src_smem, int c0,
+                                             int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+      :
+      : "l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// Wait until all but the newest N bulk groups of this thread have finished READING their
+// shared-memory source (the buffer may be overwritten) ...
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+// ... or have completed entirely (their global writes are done).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ---- tcgen05 / TMEM -----------------------------------------------------------
