@@ -153,3 +153,15 @@ __device__ __forceinline__ uint32_t mb_saturate_round_u8(float v) {
   const int r = static_cast<int>(roundf(v));
   return static_cast<uint32_t>(min(255, max(0, r)));
 }
+
+// ---- fp32 epilogue ----------------------------------------------------------
+// ref::Activation (mace/ops/ref/activation.cc:61-88) for the types the fp32 kernels fuse:
+// 0 NOOP, 1 RELU, 2 RELUX (max_limit), 6 LEAKYRELU (coef).
+__device__ __forceinline__ float mb_activate(float x, int act, float max_limit, float coef) {
+  switch (act) {
+    case 1: return fmaxf(0.f, x);
+    case 2: return fmaxf(0.f, fminf(max_limit, x));
+    case 6: return fmaxf(x, 0.f) + fminf(x, 0.f) * coef;
+    default: return x;
+  }
+}

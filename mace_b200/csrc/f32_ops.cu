@@ -9,14 +9,14 @@
 // agree to rounding (tests bound the difference at 1e-4 of the output range).
 #include "common.cuh"
 
-__device__ __forceinline__ float mb_activate(float x, int act, float max_limit, float coef) {
-  switch (act) {
-    case 1: return fmaxf(0.f, x);
-    case 2: return fmaxf(0.f, fminf(max_limit, x));
-    case 6: return fmaxf(x, 0.f) + fminf(x, 0.f) * coef;
-    default: return x;
-  }
-}
+bool mb_gemm_f32_tc_supported(const mb_context *ctx, const float *X, const float *W, int64_t Mdim,
+                              int64_t Ndim, int64_t K, int64_t x_row_stride, int64_t x_batch_stride,
+                              int64_t w_row_stride, int64_t w_batch_stride);
+int mb_gemm_f32_tc_launch(mb_context *ctx, const float *X, const float *W, const float *bias, float *C,
+                          int64_t batch, int64_t Mdim, int64_t Ndim, int64_t K, int64_t x_row_stride,
+                          int64_t x_batch_stride, int64_t w_row_stride, int64_t w_batch_stride,
+                          int64_t c_row_stride, int64_t c_batch_stride, int act, float max_limit,
+                          float coef);
 
 namespace {
 
@@ -180,6 +180,13 @@ int mb_gemm_f32_strided(mb_context *ctx, const float *A, const float *B, float *
                         int64_t a_rs, int64_t a_cs, int64_t a_bs, int64_t b_rs, int64_t b_cs,
                         int64_t b_bs, int64_t c_rs, int64_t c_cs, int64_t c_bs, int act,
                         float max_limit, float coef) {
+  // C = A * B with A [M x K] k-contiguous, B [K x N] n-contiguous and C n-contiguous is the
+  // tensor-core kernel's layout with the roles X = B (pixels x channels side), W = A.
+  if (a_cs == 1 && b_cs == 1 && c_cs == 1 &&
+      mb_gemm_f32_tc_supported(ctx, B, A, N, M, K, b_rs, b_bs, a_rs, a_bs)) {
+    return mb_gemm_f32_tc_launch(ctx, B, A, bias_per_row, C, batch, N, M, K, b_rs, b_bs, a_rs, a_bs,
+                                 c_rs, c_bs, act, max_limit, coef);
+  }
   if (batch > 65535 || ceil_div64(M, FT) > 65535)
     return mb_fail(ctx, MB_UNSUPPORTED, "fp32 GEMM: batch or M too large for this kernel");
   GemmF32Params p;

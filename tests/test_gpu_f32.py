@@ -40,6 +40,26 @@ def test_gemm_f32(ctx, orc, maj, shape):
         b.free()
 
 
+@pytest.mark.parametrize("shape", [(3, 64, 3200, 64), (1, 200, 1000, 40), (2, 24, 132, 260),
+                                   (1, 300, 4100, 512)])
+def test_gemm_f32_tensor_core(ctx, orc, shape):
+    """Row-major A, B and C with 16-byte aligned rows run on the tensor cores (tf32 MMAs on
+    hi/lo split operands); ragged M, N and K tails, with values of mixed magnitude."""
+    batch, M, N, K = shape
+    rng = np.random.Generator(np.random.PCG64(K))
+    A = (rng.standard_normal((batch, M, K)) * np.exp(rng.uniform(-3, 3, (batch, M, K)))).astype(np.float32)
+    B = rng.standard_normal((batch, K, N)).astype(np.float32)
+    dA, dB, dC = ctx.upload(A), ctx.upload(B), ctx.alloc(batch * M * N * 4)
+    before = ctx.launches_tensor_core
+    ctx.gemm_f32(dA, dB, dC, batch, M, N, K)
+    assert ctx.launches_tensor_core == before + 1, "tensor-core kernel did not run"
+    got = ctx.download(dC, (batch * M * N,), np.float32)
+    ref = orc.gemm_f32(A, B, batch, M, N, K)
+    assert rel_err(got, ref) <= 1e-5
+    for b in (dA, dB, dC):
+        b.free()
+
+
 def test_gemm_f32_literals_and_one_side_batched(ctx, orc):
     a = np.arange(1, 7, dtype=np.float32)  # matmul_test.cc:55-58
     dA, dC = ctx.upload(a), ctx.alloc(16)
