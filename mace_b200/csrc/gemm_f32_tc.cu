@@ -55,8 +55,16 @@ struct F32TcParams {
   float max_limit, coef;
   float *C;
   int64_t c_row_stride, c_batch_stride;  // elements between consecutive n / batch entries
+  int c_tma;  // C rows are 16-byte aligned: written by TMA stores from shared memory
   int *status;
+  long long *timeline;  // null, or clock stamps of CTA 0 (profiling aid): 5 per tile from slot 32
 };
+
+#define MBF_STAMP_TILE(tile, k)                                                     \
+  do {                                                                              \
+    if (p.timeline != nullptr && blockIdx.x == 0 && (tile) < 16)                    \
+      p.timeline[32 + (tile) * 5 + (k)] = clock64();                                \
+  } while (0)
 
 template <int BN>
 struct F32Cfg {
@@ -64,11 +72,15 @@ struct F32Cfg {
   static constexpr int W_BYTES = BN * FKB * 4;    // [BN n][32 k]
   static constexpr int HI_BYTES = X_BYTES + W_BYTES;
   static constexpr int STAGE_BYTES = 2 * HI_BYTES;  // hi tiles, then lo tiles
-  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 6 ? 6 : (200 * 1024) / STAGE_BYTES;
+  // epilogue staging for the TMA stores: two buffers of 16 channels x 32 pixels per warp
+  static constexpr int STAGING_BYTES = F_EPI_WARPS * 2 * 16 * 128;
+  static constexpr int RING_BUDGET = 208 * 1024 - STAGING_BYTES;
+  static constexpr int STAGES = RING_BUDGET / STAGE_BYTES > 6 ? 6 : RING_BUDGET / STAGE_BYTES;
+  static_assert(STAGES >= 2, "pipeline needs two stages");
   static constexpr int NUM_ACC = 2;
   static constexpr int TMEM_COLS = 512;
   static constexpr int BAR_BYTES = 512;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 + BAR_BYTES;
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
@@ -98,14 +110,16 @@ namespace {
 template <int BN>
 __global__ void __launch_bounds__(F_THREADS, 1)
 gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                   const __grid_constant__ CUtensorMap tmap_w, const F32TcParams p) {
+                   const __grid_constant__ CUtensorMap tmap_w,
+                   const __grid_constant__ CUtensorMap tmap_c, const F32TcParams p) {
   using Cfg = F32Cfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int NUM_ACC = Cfg::NUM_ACC;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_aligned + STAGES * Cfg::STAGE_BYTES);
+  uint64_t *bars =
+      reinterpret_cast<uint64_t *>(smem_aligned + STAGES * Cfg::STAGE_BYTES + Cfg::STAGING_BYTES);
   const uint32_t full_bar = smem_u32(bars);              // [STAGES] raw tiles landed
   const uint32_t split_bar = full_bar + 8 * STAGES;      // [STAGES] hi/lo tiles ready
   const uint32_t empty_bar = split_bar + 8 * STAGES;     // [STAGES] stage consumed
@@ -120,6 +134,7 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_w);
+    if (p.c_tma) prefetch_tensormap(&tmap_c);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(split_bar + 8 * s, F_SPLIT_WARPS);
@@ -146,7 +161,9 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (FTileIter it(p); ok && it.valid(p); it.next(p)) {
+    int local = 0;
+    if (lane == 0 && p.timeline != nullptr && blockIdx.x == 0) p.timeline[0] = clock64();
+    for (FTileIter it(p); ok && it.valid(p); it.next(p), ++local) {
       const int xb = p.x_batched ? it.b : 0, wb = p.w_batched ? it.b : 0;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, F_WAIT_BUDGET)) {
@@ -164,6 +181,7 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
           for (int j = 0; j < 4; ++j)  // four 32-pixel atoms of the 128-pixel tile
             tma_load_3d(sx + j * (FKB * 128), &tmap_x, fb, it.tm * FBM + j * 32, kb * FKB, xb);
           tma_load_3d(sw, &tmap_w, fb, kb * FKB, it.tn * BN, wb);
+          if (kb == 0) MBF_STAMP_TILE(local, 0);
         }
         __syncwarp();
         if (++stage == STAGES) {
@@ -181,7 +199,8 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
     int acc_buf = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (FTileIter it(p); ok && it.valid(p); it.next(p)) {
+    int local = 0;
+    for (FTileIter it(p); ok && it.valid(p); it.next(p), ++local) {
       if (!mbar_wait_warp(tempty_bar + 8 * acc_buf, acc_phase ^ 1, abort_flag, F_WAIT_BUDGET)) {
         *abort_flag = 1;
         atomicCAS(p.status, 0, MB_DEV_TIMEOUT_MMA);
@@ -197,6 +216,7 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
           break;
         }
         tc_fence_after_sync();
+        if (kb == p.k_blocks - 1 && lane == 0) MBF_STAMP_TILE(local, 1);
         const uint32_t sx = smem_base + stage * Cfg::STAGE_BYTES;
         const uint32_t sw = sx + Cfg::X_BYTES;
         const int64_t k_left = p.K - static_cast<int64_t>(kb) * FKB;
@@ -228,7 +248,10 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
       }
       if (!ok) break;
-      if (lane == 0) mma_commit(tfull_bar + 8 * acc_buf);
+      if (lane == 0) {
+        mma_commit(tfull_bar + 8 * acc_buf);
+        MBF_STAMP_TILE(local, 2);
+      }
       __syncwarp();
       if (++acc_buf == NUM_ACC) {
         acc_buf = 0;
@@ -279,15 +302,27 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int quarter = warp & 3;
     const int set = (warp - F_FIRST_EPI_WARP) >> 2;  // 0, 1: which half of the columns
     constexpr int CHUNKS = BN / 16 / 2;              // 16-column chunks per warp
+    // The activation as clamp + negative-slope term, with the choice made once: a branch
+    // per value costs more than the arithmetic (few warps are there to hide its latency).
+    //   NOOP: [-inf, inf], 0   RELU: [0, inf], 0   RELUX: [0, max_limit], 0   LEAKYRELU: [0, inf], coef
+    const float act_lo = p.act == 0 ? -INFINITY : 0.f;
+    const float act_hi = p.act == 2 ? p.max_limit : INFINITY;
+    const float act_slope = p.act == 6 ? p.coef : 0.f;
+    const bool leaky = p.act == 6;
+    const float *bias = p.bias;
+    const int64_t Ndim = p.Ndim;
+    const int c_tma = p.c_tma;
     int acc_buf = 0;
     uint32_t acc_phase = 0;
-    for (FTileIter it(p); it.valid(p); it.next(p)) {
+    int local = 0;
+    for (FTileIter it(p); it.valid(p); it.next(p), ++local) {
       if (!mbar_wait_warp(tfull_bar + 8 * acc_buf, acc_phase, abort_flag, F_WAIT_BUDGET)) {
         *abort_flag = 1;
         atomicCAS(p.status, 0, MB_DEV_TIMEOUT_EPILOGUE);
         break;
       }
       tc_fence_after_sync();
+      if (warp == F_FIRST_EPI_WARP && lane == 0) MBF_STAMP_TILE(local, 3);
       const int64_t m = static_cast<int64_t>(it.tm) * FBM + quarter * 32 + lane;
       const bool m_ok = m < p.Mdim;
       float *c = p.C + it.b * p.c_batch_stride + m;
@@ -296,6 +331,11 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int64_t n_first = static_cast<int64_t>(it.tn) * BN + set * (BN / 2);
       uint32_t r[2][16];
       tmem_ld_32x32b_x16(tbase, r[0]);
+      // staging: [buffer][channel j][pixel lane]; a lane's 16 writes of a chunk go to 16
+      // different rows, the warp's write of one row covers all 32 banks
+      float *stage_f = reinterpret_cast<float *>(smem_aligned + STAGES * Cfg::STAGE_BYTES +
+                                                 (warp - F_FIRST_EPI_WARP) * (2 * 16 * 128));
+      const int m0 = it.tm * FBM + quarter * 32;
 #pragma unroll
       for (int i = 0; i < CHUNKS; ++i) {
         tmem_ld_wait_x16(r[i & 1]);
@@ -306,25 +346,45 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (lane == 0) mbar_arrive(tempty_bar + 8 * acc_buf);
         }
         const int64_t n0 = n_first + i * 16;
+        float v[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const int64_t n = n0 + j;
-          if (n < p.Ndim) {  // uniform across the warp
-            float v = __uint_as_float(r[i & 1][j]);
-            if (p.bias != nullptr) v += __ldg(p.bias + n);
-            v = mb_activate(v, p.act, p.max_limit, p.coef);
-            if (m_ok) c[n * p.c_row_stride] = v;
+          const float bj = (bias != nullptr && n0 + j < Ndim) ? __ldg(bias + n0 + j) : 0.f;
+          const float x = __uint_as_float(r[i & 1][j]) + bj;
+          const float neg = leaky ? fminf(x, 0.f) * act_slope : 0.f;
+          v[j] = fminf(fmaxf(x, act_lo), act_hi) + neg;
+        }
+        if (c_tma) {
+          float *buf = stage_f + (i & 1) * (16 * 32);
+          // the store that last used this buffer (two chunks ago) must have read it
+          if (lane == 0) bulk_wait_group_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) buf[j * 32 + lane] = v[j];
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && n0 < p.Ndim && m0 < p.Mdim) {
+            tma_store_3d(&tmap_c, smem_u32(buf), m0, static_cast<int>(n0), it.b);
+            bulk_commit_group();
           }
+        } else if (m_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (n0 + j < p.Ndim) c[(n0 + j) * p.c_row_stride] = v[j];
         }
       }
+      if (warp == F_FIRST_EPI_WARP && lane == 0) MBF_STAMP_TILE(local, 4);
       if (++acc_buf == NUM_ACC) {
         acc_buf = 0;
         acc_phase ^= 1;
       }
     }
+    if (lane == 0) bulk_wait_group<0>();  // staging must outlive the stores' reads
+    __syncwarp();
   }
 
   __syncthreads();
+  if (threadIdx.x == 0 && p.timeline != nullptr && blockIdx.x == 0) p.timeline[15] = clock64();
   if (*abort_flag != 0) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
@@ -359,7 +419,8 @@ int make_map_f32(mb_context *ctx, CUtensorMap *map, const void *base, uint64_t i
 }
 
 template <int BN>
-int launch_f32(mb_context *ctx, const CUtensorMap &tx, const CUtensorMap &tw, F32TcParams &p, int cfg_bit) {
+int launch_f32(mb_context *ctx, const CUtensorMap &tx, const CUtensorMap &tw, const CUtensorMap &tc,
+               F32TcParams &p, int cfg_bit) {
   using Cfg = F32Cfg<BN>;
   auto kern = gemm_f32_tc_kernel<BN>;
   if (!(ctx->func_attr_mask & (1ull << cfg_bit))) {
@@ -371,7 +432,7 @@ int launch_f32(mb_context *ctx, const CUtensorMap &tx, const CUtensorMap &tw, F3
   p.step_m = grid % p.tiles_m;
   p.step_n = (grid / p.tiles_m) % p.tiles_n;
   p.step_b = (grid / p.tiles_m) / p.tiles_n;
-  kern<<<grid, F_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tx, tw, p);
+  kern<<<grid, F_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tx, tw, tc, p);
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   ctx->launches_tc++;
@@ -399,7 +460,7 @@ int mb_gemm_f32_tc_launch(mb_context *ctx, const float *X, const float *W, const
                           int64_t x_batch_stride, int64_t w_row_stride, int64_t w_batch_stride,
                           int64_t c_row_stride, int64_t c_batch_stride, int act, float max_limit,
                           float coef) {
-  int BN = Ndim > 128 ? 256 : Ndim > 64 ? 128 : 64;
+  const int BN = Ndim > 64 ? 128 : 64;
   F32TcParams p;
   p.Mdim = Mdim; p.Ndim = Ndim; p.K = K; p.batch = batch;
   p.tiles_m = static_cast<int>(ceil_div64(Mdim, FBM));
@@ -409,13 +470,23 @@ int mb_gemm_f32_tc_launch(mb_context *ctx, const float *X, const float *W, const
   p.bias = bias; p.act = act; p.max_limit = max_limit; p.coef = coef;
   p.C = C; p.c_row_stride = c_row_stride; p.c_batch_stride = c_batch_stride;
   p.status = ctx->dev_status;
+  p.timeline = ctx->tc_timeline;
   CUtensorMap tx, tw;
   MB_RETURN_IF_ERROR(make_map_f32(ctx, &tx, X, Mdim, K, p.x_batched ? batch : 1, x_row_stride,
                                   p.x_batched ? x_batch_stride : Mdim * K, 32, FKB,
                                   CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
   MB_RETURN_IF_ERROR(make_map_f32(ctx, &tw, W, K, Ndim, p.w_batched ? batch : 1, w_row_stride,
                                   p.w_batched ? w_batch_stride : Ndim * K, FKB, BN));
-  if (BN == 256) return launch_f32<256>(ctx, tx, tw, p, 40);
-  if (BN == 128) return launch_f32<128>(ctx, tx, tw, p, 41);
-  return launch_f32<64>(ctx, tx, tw, p, 42);
+  CUtensorMap tc;
+  p.c_tma = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && c_row_stride % 4 == 0 &&
+             c_batch_stride % 4 == 0 && Ndim >= 16) ? 1 : 0;
+  if (p.c_tma) {
+    MB_RETURN_IF_ERROR(make_map_f32(ctx, &tc, C, Mdim, Ndim, batch, c_row_stride,
+                                    batch > 1 ? c_batch_stride : Mdim * Ndim, 32, 16,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE));
+  } else {
+    memset(&tc, 0, sizeof(tc));
+  }
+  if (BN == 128) return launch_f32<128>(ctx, tx, tw, tc, p, 41);
+  return launch_f32<64>(ctx, tx, tw, tc, p, 42);
 }

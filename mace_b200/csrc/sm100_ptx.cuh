@@ -81,14 +81,16 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 
 // Wait for the phase with the given parity to complete.  Gives up after
 // `budget` clock cycles or as soon as *abort_flag becomes non-zero; returns
-// false in both cases.  Between polls the thread is parked by the hardware.
+// false in both cases.  (mbarrier.try_wait itself parks the thread for a short,
+// implementation-defined time per poll; a longer suspend-time hint made wake-ups late.)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int *abort_flag,
                                           long long budget) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   while (true) {
-    if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
+    __nanosleep(20);
+    if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag != 0) return false;
     if (clock64() - start > budget) return false;
   }
