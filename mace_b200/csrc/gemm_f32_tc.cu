@@ -60,11 +60,15 @@ struct F32TcParams {
   long long *timeline;  // null, or clock stamps of CTA 0 (profiling aid): 5 per tile from slot 32
 };
 
+#ifdef MB_TC_TIMELINE
 #define MBF_STAMP_TILE(tile, k)                                                     \
   do {                                                                              \
     if (p.timeline != nullptr && blockIdx.x == 0 && (tile) < 16)                    \
       p.timeline[32 + (tile) * 5 + (k)] = clock64();                                \
   } while (0)
+#else
+#define MBF_STAMP_TILE(tile, k) do { (void)(tile); } while (0)
+#endif
 
 template <int BN>
 struct F32Cfg {
@@ -162,7 +166,9 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
     uint32_t phase = 0;
     bool ok = true;
     int local = 0;
+#ifdef MB_TC_TIMELINE
     if (lane == 0 && p.timeline != nullptr && blockIdx.x == 0) p.timeline[0] = clock64();
+#endif
     for (FTileIter it(p); ok && it.valid(p); it.next(p), ++local) {
       const int xb = p.x_batched ? it.b : 0, wb = p.w_batched ? it.b : 0;
       for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -384,7 +390,9 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
   }
 
   __syncthreads();
+#ifdef MB_TC_TIMELINE
   if (threadIdx.x == 0 && p.timeline != nullptr && blockIdx.x == 0) p.timeline[15] = clock64();
+#endif
   if (*abort_flag != 0) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();

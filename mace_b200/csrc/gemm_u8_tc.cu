@@ -84,18 +84,27 @@ struct TcParams {
   long long *timeline;
 };
 
-// Clock stamp of a pipeline milestone, CTA 0 only, when a buffer was given.
+// Clock stamp of a pipeline milestone, CTA 0 only, when a buffer was given.  Compiled in
+// only with -DMB_TC_TIMELINE: the checks sit on the single-thread roles' critical path.
+#ifdef MB_TC_TIMELINE
 #define MB_STAMP(slot)                                                    \
   do {                                                                    \
     if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[slot] = clock64(); \
   } while (0)
+#else
+#define MB_STAMP(slot) do { } while (0)
+#endif
 
 // Per-tile stamp k (0..4) of CTA 0's n-th tile, first 16 tiles only.
+#ifndef MB_TC_TIMELINE
+#define MB_STAMP_TILE(tile, k) do { (void)(tile); } while (0)
+#else
 #define MB_STAMP_TILE(tile, k)                                                       \
   do {                                                                              \
     if (p.timeline != nullptr && blockIdx.x == 0 && (tile) < 16)                    \
       p.timeline[32 + (tile) * 5 + (k)] = clock64();                                \
   } while (0)
+#endif
 
 template <int BN, bool B_MN, int KB = BK>
 struct TileCfg {
@@ -159,6 +168,58 @@ __device__ __forceinline__ void requant_chunk(const uint32_t (&raw)[CHUNK], int3
     const uint32_t b2 = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(raw[4 * q + 2]) + row_term + t.z, p.rq);
     const uint32_t b3 = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(raw[4 * q + 3]) + row_term + t.w, p.rq);
     packed[q] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+  }
+}
+
+// What an epilogue warp needs for one tile on the TMA-store path.
+struct EpiTile {
+  uint32_t tbase;          // TMEM address of the warp's 32 lanes x 64 columns
+  int32_t row_term;
+  const int32_t *ct_base;  // column terms of the 64 columns (shared memory)
+  uint32_t tempty;         // barrier that returns the accumulator buffer
+  uint4 *stage_row;        // this lane's 32-byte row of the staging buffer
+  int swz;
+  uint32_t stage_addr;
+  int64_t n_first;
+  int m0, b, lane;
+};
+
+// 32 rows x 64 columns of one tile: four 16-column chunks from TMEM (the next one in flight
+// while the current one is requantized), staged two chunks at a time for a TMA store of
+// 32 rows x 32 bytes.
+template <bool ZP0, bool SGE1>
+__device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap &tmap_c,
+                                             const TcParams &p) {
+  uint32_t r[2][CHUNK];
+  tmem_ld_32x32b_x16(e.tbase, r[0]);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    tmem_ld_wait_x16(r[i & 1]);
+    if (i + 1 < 4) tmem_ld_32x32b_x16(e.tbase + (i + 1) * CHUNK, r[(i + 1) & 1]);
+    if (i == 3) {
+      // the accumulator is in registers: hand the buffer back to the MMA warp
+      tc_fence_before_sync();
+      __syncwarp();
+      if (e.lane == 0) mbar_arrive(e.tempty);
+    }
+    uint32_t packed[CHUNK / 4];
+    requant_chunk<ZP0, SGE1>(r[i & 1], e.row_term, reinterpret_cast<const int4 *>(e.ct_base + i * CHUNK),
+                             p, packed);
+    if ((i & 1) == 0) {
+      // the previous store must have read the staging buffer before it is refilled
+      if (e.lane == 0) bulk_wait_group_read<0>();
+      __syncwarp();
+    }
+    e.stage_row[(i & 1) ^ e.swz] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    if (i & 1) {
+      fence_proxy_async();
+      __syncwarp();
+      const int64_t n0 = e.n_first + (i - 1) * CHUNK;
+      if (e.lane == 0 && n0 < p.N && e.m0 < p.M) {
+        tma_store_3d(&tmap_c, e.stage_addr, static_cast<int>(n0), e.m0, e.b);
+        bulk_commit_group();
+      }
+    }
   }
 }
 
@@ -471,48 +532,23 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                              slice * 64;
       const int32_t *ct_base = col_term_sm + acc_buf * BN + slice * 64;
       const int64_t n_first = static_cast<int64_t>(tn) * BN + slice * 64;
-      uint32_t r[2][CHUNK];
-      tmem_ld_32x32b_x16(tbase, r[0]);
       if (p.c_tma) {
-        // uint8 output through shared memory and TMA stores of 32 rows x 32 bytes
-#pragma unroll
-        for (int i = 0; i < CHUNKS_PER_WARP; ++i) {
-          tmem_ld_wait_x16(r[i & 1]);
-          if (i + 1 < CHUNKS_PER_WARP) tmem_ld_32x32b_x16(tbase + (i + 1) * CHUNK, r[(i + 1) & 1]);
-          if (i == CHUNKS_PER_WARP - 1) {
-            // the accumulator is in registers: hand the buffer back to the MMA warp
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar + 8 * acc_buf);
-          }
-          uint32_t packed[CHUNK / 4];
-          const int4 *ct = reinterpret_cast<const int4 *>(ct_base + i * CHUNK);
-          switch (p.rq_variant) {
-            case 3: requant_chunk<true, true>(r[i & 1], row_term, ct, p, packed); break;
-            case 2: requant_chunk<false, true>(r[i & 1], row_term, ct, p, packed); break;
-            case 1: requant_chunk<true, false>(r[i & 1], row_term, ct, p, packed); break;
-            default: requant_chunk<false, false>(r[i & 1], row_term, ct, p, packed); break;
-          }
-          if ((i & 1) == 0) {
-            // the previous store must have read the staging buffer before it is refilled
-            if (lane == 0) bulk_wait_group_read<0>();
-            __syncwarp();
-          }
-          stage_row[(i & 1) ^ swz] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          if (i & 1) {
-            fence_proxy_async();
-            __syncwarp();
-            const int64_t n0 = n_first + (i - 1) * CHUNK;
-            if (lane == 0 && n0 < p.N && m0 < p.M) {
-              tma_store_3d(&tmap_c, stage_addr, static_cast<int>(n0), m0, b);
-              bulk_commit_group();
-            }
-          }
+        // one decision per tile (not per chunk or value: with so few warps per scheduler
+        // a branch's latency is not hidden)
+        const EpiTile e{tbase, row_term, ct_base, tempty_bar + 8 * acc_buf, stage_row, swz, stage_addr,
+                        n_first, m0, b, lane};
+        switch (p.rq_variant) {
+          case 3: epi_tma_tile<true, true>(e, tmap_c, p); break;
+          case 2: epi_tma_tile<false, true>(e, tmap_c, p); break;
+          case 1: epi_tma_tile<true, false>(e, tmap_c, p); break;
+          default: epi_tma_tile<false, false>(e, tmap_c, p); break;
         }
       } else {
         // direct stores: int32 output, or a uint8 output whose rows TMA cannot address
         uint8_t *c8 = static_cast<uint8_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
         int32_t *c32 = static_cast<int32_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
+        uint32_t r[1][CHUNK];
+        tmem_ld_32x32b_x16(tbase, r[0]);
 #pragma unroll 1
         for (int i = 0; i < CHUNKS_PER_WARP; ++i) {
           uint32_t v[CHUNK];
