@@ -10,6 +10,10 @@ Workloads (``config.workload``):
                  TOPS of the 4096^3 MatMul under "u8_gemm".
   gemm_u8_4096   uint8 MatMul M = N = K = 4096, zero points 128 / 120, fixed-point
                  requantization to uint8.  metric: u8 GEMM TOPS.
+  winograd_f32_cfg1  fp32 3x3 Conv2D, input [32,64,56,56], filter [64,64,3,3], SAME, through the
+                 Winograd entry point (cached transformed filter).  metric: direct-equivalent TFLOP/s.
+  gemm_u8_sweep  uint8 GEMM with K = N = 4096 and M in {1, 16, 128, 4096}, the batched
+                 64 x 512^3 MatMul and the 4096 x 4096 GEMV; one row per case under "cases".
 
 One "step" is one pass of the hot path over one batch of synthetic, seeded input.  `value`
 is measured with the inputs resident in HBM, `e2e` through the host-buffer entry point with
@@ -421,11 +425,8 @@ def run_mobilenet(args, rank, world):
     def e2e_step(i):
         eng.run_host("input", hin[i % n_inputs], "fc", hout)
         if dist is not None:  # the only collective of the path: gather the logits
-            import torch
-            mine = torch.from_numpy(hout.copy()).cuda()
-            parts = [torch.empty_like(mine) for _ in range(world)]
-            dist.all_gather(parts, mine)
-            torch.cuda.synchronize()
+            from mace_b200.sharding import gather_rows
+            gather_rows(dist, hout.reshape(BATCH, mn.NUM_CLASSES), BATCH * world, device="cuda")
 
     for i in range(3):
         e2e_step(i)
@@ -520,6 +521,193 @@ def run_mobilenet(args, rank, world):
     return result
 
 
+# --------------------------------------------------------------------------------------
+# workload: fp32 3x3 Conv2D by Winograd (input [32,64,56,56], filter [64,64,3,3], SAME)
+# --------------------------------------------------------------------------------------
+
+def run_winograd(args, rank, world):
+    import mace_b200
+    from oracle import pyoracle as orc  # cpu_baseline leg only
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    ctx = mace_b200.Context(local)
+    dist = init_dist(world, local)
+    N, C, H, W, O = 32, 64, 56, 56, 64
+    rng = np.random.Generator(np.random.PCG64(rank))
+    f = (rng.standard_normal((O, C, 3, 3)) * np.sqrt(2.0 / (9 * C))).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.01).astype(np.float32)
+    n_sets = 6  # 6 x (25.7 MB in + 25.7 MB out) = 308 MB > L2
+    xs = [rng.random((N, C, H, W), dtype=np.float32) for _ in range(n_sets)]
+    dxs = [ctx.upload(x) for x in xs]
+    dos = [ctx.alloc(N * O * H * W * 4) for _ in range(n_sets)]
+    df, db = ctx.upload(f), ctx.upload(bias)
+    dU = ctx.alloc(64 * O * C * 4)
+    ctx.winograd_transform_filter(df, dU, C, O, 6)  # cached per weight, as the delegator does
+
+    def step(i):
+        ctx.winograd_f32(dxs[i % n_sets], df, db, dos[i % n_sets], N, C, H, W, O, (1, 1), (H, W),
+                         transformed=dU)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.01)
+    l0, ltc0 = ctx.launches, ctx.launches_tensor_core
+    e0, e1 = ctx.event(), ctx.event()
+    ctx.record(e0)
+    for i in range(args.steps):
+        step(i)
+    ctx.record(e1)
+    ms = ctx.elapsed_ms(e0, e1)
+    barrier()
+    launches, launches_tc = ctx.launches - l0, ctx.launches_tensor_core - ltc0
+    clocks = sampler.stop() if rank == 0 else None
+    if args.profile:
+        ctx.close()
+        return None
+    hx, ho = ctx.host_alloc(xs[0].nbytes), ctx.host_alloc(N * O * H * W * 4)
+    hx[:] = xs[0].view(np.uint8).ravel()
+
+    def e2e_step():
+        ctx.h2d(dxs[0], hx)
+        step(0)
+        ctx.d2h(ho, dos[0])
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 20))
+    ctx.record(e0)
+    for _ in range(e2e_steps):
+        e2e_step()
+    ctx.record(e1)
+    e2e_ms = ctx.elapsed_ms(e0, e1)
+    barrier()
+    ms, e2e_ms = max_over_ranks(dist, [ms, e2e_ms])
+    result = None
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_per_step = ms / args.steps
+        direct_flops = 2.0 * N * O * C * 9 * H * W
+        alg_bytes = 4 * (N * C * H * W + N * O * H * W + O * C * 9 + O)
+        value = world * direct_flops / (ms_per_step * 1e-3) / 1e12
+        achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9
+        result = {
+            "metric": "fp32_conv3x3_winograd_direct_equivalent_tflops", "value": round(value, 2),
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "winograd_f32_cfg1", "input": [N, C, H, W], "filter": [O, C, 3, 3],
+                       "padding": "SAME", "tile": "F(6x6,3x3)", "executed_gemm_flops": 2.0 * 64 * O * C * N * 100,
+                       "l2": "rotating %d input/output sets (%.0f MB > L2)" % (n_sets, n_sets * 51.4),
+                       "parallelism": "dp%d: batch sharded, filter replicated" % world},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                         "peak_source": "%s copy bandwidth" % peaks["source"],
+                         "kernel": "whole call: wino_input_kernel + gemm_f32_tc_kernel + wino_output_kernel",
+                         "algorithmic_bytes_per_step": alg_bytes},
+            "e2e": {"value": round(world * direct_flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, 2),
+                    "unit": "TFLOP/s", "h2d_bytes_per_step": int(xs[0].nbytes),
+                    "d2h_bytes_per_step": N * O * H * W * 4},
+            "gpu_launches": launches, "gpu_launches_tensor_core": launches_tc, "clocks": clocks,
+        }
+        threads = orc.set_threads(0)
+        sample_n = 4
+        orc.winograd_f32(xs[0][:1], f, bias, (1, 1), (H, W), 0, 0.0, 0.0)
+        t0 = time.perf_counter()
+        orc.winograd_f32(xs[0][:sample_n], f, bias, (1, 1), (H, W), 0, 0.0, 0.0)
+        dt = time.perf_counter() - t0
+        result["cpu_baseline"] = {"value": round(direct_flops * sample_n / N / dt / 1e12, 4),
+                                  "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                  "sample": "%d of %d images, one pass" % (sample_n, N)}
+    ctx.close()
+    if dist is not None:
+        dist.destroy_process_group()
+    return result
+
+
+# --------------------------------------------------------------------------------------
+# workload: uint8 GEMM / GEMV sweep, K = N = 4096, M in {1, 16, 128, 4096}, batched 64 x 512^3
+# --------------------------------------------------------------------------------------
+
+def run_sweep(args, rank, world):
+    import mace_b200
+    from oracle import pyoracle as orc
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    ctx = mace_b200.Context(local)
+    dist = init_dist(world, local)
+    peaks = measured_peaks()
+    rows = []
+
+    def timed(fn, n):
+        for i in range(max(args.warmup, 3)):
+            fn(i)
+        ctx.sync()
+        e0, e1 = ctx.event(), ctx.event()
+        ctx.record(e0)
+        for i in range(n):
+            fn(i)
+        ctx.record(e1)
+        return ctx.elapsed_ms(e0, e1) / n
+
+    K = Nn = 4096
+    n_sets = 10  # 10 x 16.8 MB of B > L2
+    rng = np.random.Generator(np.random.PCG64(rank))
+    Bs = [ctx.upload(rng.integers(0, 256, size=(K, Nn), dtype=np.uint8)) for _ in range(n_sets)]
+    for M in (1, 16, 128, 4096):
+        wl = GemmWorkload(M, Nn, K)
+        mult, shift, zp_c = wl.quant(orc)
+        dA = ctx.upload(rng.integers(0, 256, size=(M, K), dtype=np.uint8))
+        dC = ctx.alloc(M * Nn)
+        ms = timed(lambda i: ctx.gemm_u8(dA, Bs[i % n_sets], None, dC, 1, M, Nn, K, wl.zp_a, wl.zp_b,
+                                         mult, shift, zp_c), args.steps)
+        byts = M * K + K * Nn + M * Nn
+        rows.append({"case": "M=%d" % M, "ms": round(ms, 5), "tops": round(2.0 * M * Nn * K / ms / 1e9, 2),
+                     "gbs": round(byts / ms / 1e6, 1),
+                     "frac_hbm": round(byts / ms / 1e6 / peaks["hbm_gbs"], 4),
+                     "frac_2x_bf16": round(2.0 * M * Nn * K / ms / 1e9 / (2 * peaks["bf16_tflops"]), 4)})
+    # batched MatMul 64 x 512^3
+    bA = [ctx.upload(rng.integers(0, 256, size=(64, 512, 512), dtype=np.uint8)) for _ in range(5)]
+    bB = [ctx.upload(rng.integers(0, 256, size=(64, 512, 512), dtype=np.uint8)) for _ in range(5)]
+    bC = ctx.alloc(64 * 512 * 512)
+    wl = GemmWorkload(512, 512, 512)
+    mult, shift, zp_c = wl.quant(orc)
+    ms = timed(lambda i: ctx.gemm_u8(bA[i % 5], bB[i % 5], None, bC, 64, 512, 512, 512, wl.zp_a, wl.zp_b,
+                                     mult, shift, zp_c), args.steps)
+    rows.append({"case": "batch64_512^3", "ms": round(ms, 5), "tops": round(2.0 * 64 * 512 ** 3 / ms / 1e9, 2),
+                 "gbs": round(3 * 64 * 512 * 512 / ms / 1e6, 1),
+                 "frac_2x_bf16": round(2.0 * 64 * 512 ** 3 / ms / 1e9 / (2 * peaks["bf16_tflops"]), 4)})
+    # GEMV with the FullyConnected rule: weights [4096 x 4096], one vector
+    Ws = [ctx.upload(rng.integers(0, 256, size=(1, 4096, 4096), dtype=np.uint8)) for _ in range(n_sets)]
+    dx, dout = ctx.upload(rng.integers(0, 256, size=(1, 4096), dtype=np.uint8)), ctx.alloc(4096)
+    ms = timed(lambda i: ctx.gemv_u8(Ws[i % n_sets], dx, None, dout, 1, 4096, 4096, 120, 128,
+                                     np.float32(1e-5), 30, True), args.steps)
+    gemv_gbs = 4096 * 4096 / ms / 1e6
+    rows.append({"case": "gemv_4096x4096", "ms": round(ms, 5), "gbs": round(gemv_gbs, 1),
+                 "frac_hbm": round(gemv_gbs / peaks["hbm_gbs"], 4)})
+    ctx.close()
+    if dist is not None:
+        dist.destroy_process_group()
+    if rank != 0:
+        return None
+    big = [r for r in rows if r["case"] == "M=4096"][0]
+    return {"metric": "u8_gemm_tops", "value": big["tops"], "unit": "TOPS", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": big["ms"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+            "data": "synthetic",
+            "config": {"workload": "gemm_u8_sweep", "K": K, "N": Nn,
+                       "l2": "rotating %d B matrices (%.0f MB > L2)" % (n_sets, n_sets * 16.8),
+                       "parallelism": "replicas only (dp%d)" % world},
+            "cases": rows}
+
+
 def run_reference(args, rank, world):
     """The reference's CPU implementation of the path, timed on the host cores: the oracle
     port (the reference's own sources need NEON, gemmlowp, a TF-Lite fork and generated
@@ -577,7 +765,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mobilenet_v1_u8_b64",
-                    choices=["mobilenet_v1_u8_b64", "gemm_u8_4096"])
+                    choices=["mobilenet_v1_u8_b64", "gemm_u8_4096", "winograd_f32_cfg1", "gemm_u8_sweep"])
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every operator separately instead of replaying a CUDA graph")
     ap.add_argument("--profile", action="store_true",
@@ -589,6 +777,10 @@ def main():
         res = run_reference(args, rank, world)
     elif args.workload == "gemm_u8_4096":
         res = run_gemm(args, rank, world)
+    elif args.workload == "winograd_f32_cfg1":
+        res = run_winograd(args, rank, world)
+    elif args.workload == "gemm_u8_sweep":
+        res = run_sweep(args, rank, world)
     else:
         res = run_mobilenet(args, rank, world)
     if rank == 0 and res is not None:
