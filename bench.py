@@ -148,6 +148,10 @@ class RawContext:
 def init_dist(world, local):
     if world <= 1:
         return None
+    # NCCL prints its version banner on stdout at INFO / VERSION level; the bench prints one
+    # JSON line there and nothing else
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "INFO"):
+        os.environ["NCCL_DEBUG"] = "WARN"
     import torch
     import torch.distributed as dist
     torch.cuda.set_device(local)

@@ -96,6 +96,7 @@ int mb_destroy(mb_context *ctx) {
   cudaSetDevice(ctx->device);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->skinny_ws) cudaFree(ctx->skinny_ws);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
   if (ctx->host_status) cudaFreeHost(ctx->host_status);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);

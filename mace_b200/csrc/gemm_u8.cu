@@ -255,12 +255,22 @@ int launch_generic(mb_context *ctx, const uint8_t *A, const uint8_t *B, const in
 
 }  // namespace
 
+bool mb_gemm_u8_skinny_supported(int64_t batch, int64_t M, int64_t N, int64_t K, bool a_mn, bool b_mn,
+                                 const void *A, const void *B);
+int mb_gemm_u8_skinny_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B, const int32_t *bias,
+                             void *C, int out_is_int32, int64_t M, int64_t N, int64_t K, int32_t zp_a,
+                             int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c, int bias_per_row);
+
 // Row-major-C GEMM on device operands; a_mn / b_mn as in mb_gemm_u8_tc_launch.
 int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, const int32_t *bias,
                         void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
                         int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
                         int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
                         int bias_per_row) {
+  // A few rows against a large row-major B: stream B once over all SMs.
+  if (ctx->use_tensor_cores && mb_gemm_u8_skinny_supported(batch, M, N, K, a_mn, b_mn, A, B))
+    return mb_gemm_u8_skinny_launch(ctx, A, B, bias, C, out_is_int32, M, N, K, zp_a, zp_b, mult, shift,
+                                    zp_c, bias_per_row);
   const bool aligned16 =
       ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15u) == 0;
   bool use_tc = ctx->use_tensor_cores && ctx->encode_tiled != nullptr && aligned16 &&

@@ -8,9 +8,8 @@
 // multiply-add), as the C++ expression is written.
 //
 // The kernel is bandwidth-bound: one warp streams one row of the matrix with
-// 128-bit loads and integer dot-product instructions, the vector is re-read
-// through L1/L2.  When the matrix is shared by all batch entries (the
-// FullyConnected case) the warp keeps its row and loops over the vectors.
+// 128-bit loads and integer dot-product instructions.  When the matrix is shared by all
+// batch entries (the FullyConnected case) the warp keeps its row and loops over the vectors.
 #include "common.cuh"
 
 namespace {
@@ -26,39 +25,77 @@ struct GemvParams {
   int batch_chunk;
 };
 
+// One warp per matrix row.  The first 4 KB of the row are requested before anything else (8
+// independent 128-bit loads per lane in flight); the vector's bytes and their sum are the
+// same for every row of the block, so they are staged in shared memory once per block and
+// batch entry.  A matrix shared by the batch is loaded once and kept in registers.
 template <bool VEC>
 __global__ void __launch_bounds__(256) gemv_u8_kernel(const GemvParams p) {
+  extern __shared__ uint4 xs[];  // VEC: the vector, K / 16 words
+  __shared__ uint32_t sum_r_sm;
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (row >= p.rows) return;
+  const bool row_ok = row < p.rows;
   // blockIdx.y walks the batch: one entry per block when every entry has its
   // own matrix, otherwise a chunk of entries that share the warp's matrix row.
   const int64_t b_begin = p.lhs_batched ? blockIdx.y : static_cast<int64_t>(blockIdx.y) * p.batch_chunk;
   const int64_t b_end = p.lhs_batched ? b_begin + 1 : min(p.batch, b_begin + p.batch_chunk);
+  uint4 l[8];
   for (int64_t b = b_begin; b < b_end; ++b) {
-    const uint8_t *lp = p.lhs + (p.lhs_batched ? b * p.rows * p.K : 0) + row * p.K;
+    const uint8_t *lp = p.lhs + (p.lhs_batched ? b * p.rows * p.K : 0) + (row_ok ? row : 0) * p.K;
     const uint8_t *rp = p.rhs + (p.rhs_batched ? b * p.K : 0);
     uint32_t dot = 0, sum_l = 0, sum_r = 0;
     if (VEC) {
+      const int nvec = static_cast<int>(p.K >> 4);
       const uint4 *l4 = reinterpret_cast<const uint4 *>(lp);
       const uint4 *r4 = reinterpret_cast<const uint4 *>(rp);
-      const int64_t nvec = p.K >> 4;
-#pragma unroll 4
-      for (int64_t i = lane; i < nvec; i += 32) {
-        const uint4 l = __ldg(l4 + i);
+      // the matrix row first: its loads are the long-latency ones
+      const int pre = min(8, (nvec - lane + 31) / 32);
+      if (b == b_begin || p.lhs_batched) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (i < pre) l[i] = __ldg(l4 + lane + 32 * i);
+      }
+      __syncthreads();  // previous batch entry's readers are done with xs
+      uint32_t part = 0;
+      for (int i = threadIdx.x; i < nvec; i += 256) {
         const uint4 r = __ldg(r4 + i);
-        dot = __dp4a(l.x, r.x, dot);
-        dot = __dp4a(l.y, r.y, dot);
-        dot = __dp4a(l.z, r.z, dot);
-        dot = __dp4a(l.w, r.w, dot);
-        sum_l = __dp4a(l.x, 0x01010101u, sum_l);
-        sum_l = __dp4a(l.y, 0x01010101u, sum_l);
-        sum_l = __dp4a(l.z, 0x01010101u, sum_l);
-        sum_l = __dp4a(l.w, 0x01010101u, sum_l);
-        sum_r = __dp4a(r.x, 0x01010101u, sum_r);
-        sum_r = __dp4a(r.y, 0x01010101u, sum_r);
-        sum_r = __dp4a(r.z, 0x01010101u, sum_r);
-        sum_r = __dp4a(r.w, 0x01010101u, sum_r);
+        xs[i] = r;
+        part = __dp4a(r.x, 0x01010101u, part);
+        part = __dp4a(r.y, 0x01010101u, part);
+        part = __dp4a(r.z, 0x01010101u, part);
+        part = __dp4a(r.w, 0x01010101u, part);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      if (threadIdx.x == 0) sum_r_sm = 0;
+      __syncthreads();
+      if (lane == 0) atomicAdd(&sum_r_sm, part);
+      __syncthreads();
+      sum_r = sum_r_sm;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (i < pre) {
+          const uint4 r = xs[lane + 32 * i];
+          dot = __dp4a(l[i].x, r.x, dot); dot = __dp4a(l[i].y, r.y, dot);
+          dot = __dp4a(l[i].z, r.z, dot); dot = __dp4a(l[i].w, r.w, dot);
+          sum_l = __dp4a(l[i].x, 0x01010101u, sum_l); sum_l = __dp4a(l[i].y, 0x01010101u, sum_l);
+          sum_l = __dp4a(l[i].z, 0x01010101u, sum_l); sum_l = __dp4a(l[i].w, 0x01010101u, sum_l);
+        }
+      }
+#pragma unroll 4
+      for (int i = lane + 256; i < nvec; i += 32) {
+        const uint4 lv = __ldg(l4 + i);
+        const uint4 r = xs[i];
+        dot = __dp4a(lv.x, r.x, dot); dot = __dp4a(lv.y, r.y, dot);
+        dot = __dp4a(lv.z, r.z, dot); dot = __dp4a(lv.w, r.w, dot);
+        sum_l = __dp4a(lv.x, 0x01010101u, sum_l); sum_l = __dp4a(lv.y, 0x01010101u, sum_l);
+        sum_l = __dp4a(lv.z, 0x01010101u, sum_l); sum_l = __dp4a(lv.w, 0x01010101u, sum_l);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        sum_l += __shfl_xor_sync(0xffffffffu, sum_l, o);
       }
     } else {
       for (int64_t i = lane; i < p.K; i += 32) {
@@ -67,14 +104,14 @@ __global__ void __launch_bounds__(256) gemv_u8_kernel(const GemvParams p) {
         sum_l += l;
         sum_r += r;
       }
-    }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      sum_l += __shfl_xor_sync(0xffffffffu, sum_l, o);
-      sum_r += __shfl_xor_sync(0xffffffffu, sum_r, o);
+      for (int o = 16; o > 0; o >>= 1) {
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        sum_l += __shfl_xor_sync(0xffffffffu, sum_l, o);
+        sum_r += __shfl_xor_sync(0xffffffffu, sum_r, o);
+      }
     }
-    if (lane == 0) {
+    if (lane == 0 && row_ok) {
       const uint32_t zero_point_dot = static_cast<uint32_t>(
           static_cast<int64_t>(p.zp_lhs) * p.zp_rhs * p.K);
       int32_t ret = static_cast<int32_t>(dot - sum_l * static_cast<uint32_t>(p.zp_rhs) -
@@ -114,7 +151,7 @@ extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rh
   p.lhs_batched = lhs_batched; p.rhs_batched = rhs_batched;
   p.out_is_int32 = out_is_int32; p.add_zp_out = add_zp_out;
   p.zp_lhs = zp_lhs; p.zp_rhs = zp_rhs; p.zp_out = zp_out; p.multiplier = multiplier;
-  const bool vec = (K % 16 == 0) && K > 0 &&
+  const bool vec = (K % 16 == 0) && K > 0 && K <= 32768 &&
                    ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15u) == 0;
   // a shared matrix: split the batch so that at least ~4 blocks per SM exist
   int64_t chunks = 1;
@@ -126,7 +163,7 @@ extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rh
   dim3 grid(static_cast<unsigned>(ceil_div64(rows, 8)),
             lhs_batched ? static_cast<unsigned>(batch)
                         : static_cast<unsigned>(ceil_div64(batch, p.batch_chunk)));
-  if (vec) gemv_u8_kernel<true><<<grid, 256, 0, ctx->stream>>>(p);
+  if (vec) gemv_u8_kernel<true><<<grid, 256, static_cast<size_t>(K), ctx->stream>>>(p);
   else gemv_u8_kernel<false><<<grid, 256, 0, ctx->stream>>>(p);
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;

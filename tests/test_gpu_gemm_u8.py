@@ -164,6 +164,29 @@ def test_requantization_variants(ctx, orc, zp_c, shift):
     assert np.array_equal(got, exp)
 
 
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 4096, 4096), (3, 640, 260), (7, 516, 1000),
+                                   (9, 2048, 512)])
+@pytest.mark.parametrize("out_int32", [False, True])
+def test_few_rows_against_row_major_b(ctx, orc, shape, out_int32):
+    """M <= 16 with a row-major B (the M = 1 / M = 16 cases of the K = N = 4096 sweep): the
+    split-K streaming kernel, twice in a row (its workspace must come back zeroed), with a
+    bias, ragged N and K, and interleaved with a differently shaped call."""
+    M, N, K = shape
+    case = gemm_case(orc, M + N, 1, M, N, K, bias_len=N)
+    before = ctx.launches_tensor_core
+    for _ in range(2):
+        got, exp = run_gemm(ctx, orc, case, 1, M, N, K, out_int32=out_int32)
+        assert np.array_equal(got, exp)
+    assert ctx.launches_tensor_core == before, "expected the CUDA-core streaming kernel"
+    other = gemm_case(orc, 5, 1, 2, 512, 256, bias_len=2)
+    got, exp = run_gemm(ctx, orc, other, 1, 2, 512, 256, bias_per_row=True)
+    assert np.array_equal(got, exp)
+    got, exp = run_gemm(ctx, orc, case, 1, M, N, K, out_int32=out_int32)
+    assert np.array_equal(got, exp)
+    if not out_int32:
+        assert len(np.unique(got)) > 16
+
+
 def test_empty_and_bad_arguments(ctx):
     import mace_b200
     buf = ctx.alloc(64)
