@@ -32,6 +32,7 @@ struct ConvParams {
   int depth, depth_padded;
   int32_t zp_in, zp_f;
   mb_requant_params rq;
+  int rq_variant;  // mb_requant_variant()
 };
 
 // Direct convolution: thread = one output pixel, OT output channels at a time.
@@ -90,6 +91,33 @@ __global__ void __launch_bounds__(128) conv_u8_direct_kernel(const ConvParams p)
 // rows (zero-padded to 8 words) and the per-channel constant
 //   bias - zi * sum f + depth * zi * zf
 // live in shared memory and are read as broadcasts.
+// All output channels of one pixel from its packed patch: four channels per step, filter
+// rows read as 128-bit broadcasts.
+template <int DW, int DWP, bool ZP0, bool SGE1>
+__device__ __forceinline__ void patch_outputs(const uint32_t (&patch)[DW], const uint32_t *smem_w,
+                                              const int32_t *cterm, int32_t in_term,
+                                              const ConvParams &p, uint8_t *outp) {
+  for (int o0 = 0; o0 < p.O; o0 += 4) {
+    uint32_t b[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 *wr = reinterpret_cast<const uint4 *>(smem_w + (o0 + j) * DWP);
+      uint32_t dot = 0;
+#pragma unroll
+      for (int q = 0; q < DWP / 4; ++q) {
+        const uint4 w4 = wr[q];
+        if (q * 4 + 0 < DW) dot = __dp4a(patch[q * 4 + 0 < DW ? q * 4 + 0 : 0], w4.x, dot);
+        if (q * 4 + 1 < DW) dot = __dp4a(patch[q * 4 + 1 < DW ? q * 4 + 1 : 0], w4.y, dot);
+        if (q * 4 + 2 < DW) dot = __dp4a(patch[q * 4 + 2 < DW ? q * 4 + 2 : 0], w4.z, dot);
+        if (q * 4 + 3 < DW) dot = __dp4a(patch[q * 4 + 3 < DW ? q * 4 + 3 : 0], w4.w, dot);
+      }
+      b[j] = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(dot) + in_term + cterm[o0 + j], p.rq);
+    }
+    *reinterpret_cast<uint32_t *>(outp + o0) =
+        __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+  }
+}
+
 template <int KH, int KW, int C>
 __global__ void __launch_bounds__(128) conv_u8_patch_dp4a_kernel(const ConvParams p) {
   constexpr int DEPTH = KH * KW * C;
@@ -147,33 +175,24 @@ __global__ void __launch_bounds__(128) conv_u8_patch_dp4a_kernel(const ConvParam
   for (int i = 0; i < DW; ++i) sum_in = __dp4a(patch[i], 0x01010101u, sum_in);
   const int32_t in_term = -p.zp_f * static_cast<int32_t>(sum_in);
   uint8_t *outp = p.out + pix * p.O;
-  for (int o0 = 0; o0 < p.O; o0 += 4) {
-    uint32_t packed = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int o = o0 + j;
-      if (o < p.O) {
-        const uint4 *wr = reinterpret_cast<const uint4 *>(smem_w + o * DWP);
-        uint32_t dot = 0;
-#pragma unroll
-        for (int q = 0; q < DWP / 4; ++q) {
-          const uint4 w4 = wr[q];
-          if (q * 4 + 0 < DW) dot = __dp4a(patch[q * 4 + 0 < DW ? q * 4 + 0 : 0], w4.x, dot);
-          if (q * 4 + 1 < DW) dot = __dp4a(patch[q * 4 + 1 < DW ? q * 4 + 1 : 0], w4.y, dot);
-          if (q * 4 + 2 < DW) dot = __dp4a(patch[q * 4 + 2 < DW ? q * 4 + 2 : 0], w4.z, dot);
-          if (q * 4 + 3 < DW) dot = __dp4a(patch[q * 4 + 3 < DW ? q * 4 + 3 : 0], w4.w, dot);
-        }
-        const int32_t acc = static_cast<int32_t>(dot) + in_term + cterm[o];
-        packed |= mb_requant_fast(acc, p.rq) << (8 * j);
-      }
+  // The requantization variant is chosen once per thread, and output channels are handled four
+  // at a time without per-channel checks when O is a multiple of four: in a loop this short a
+  // branch per value costs more than the arithmetic.
+  if ((p.O & 3) == 0) {
+    switch (p.rq_variant) {
+      case 3: patch_outputs<DW, DWP, true, true>(patch, smem_w, cterm, in_term, p, outp); break;
+      case 2: patch_outputs<DW, DWP, false, true>(patch, smem_w, cterm, in_term, p, outp); break;
+      case 1: patch_outputs<DW, DWP, true, false>(patch, smem_w, cterm, in_term, p, outp); break;
+      default: patch_outputs<DW, DWP, false, false>(patch, smem_w, cterm, in_term, p, outp); break;
     }
-    if ((p.O & 3) == 0) {
-      *reinterpret_cast<uint32_t *>(outp + o0) = packed;
-    } else {
+    return;
+  }
+  for (int o = 0; o < p.O; ++o) {
+    const uint32_t *wr = smem_w + o * DWP;
+    uint32_t dot = 0;
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (o0 + j < p.O) outp[o0 + j] = static_cast<uint8_t>(packed >> (8 * j));
-    }
+    for (int q = 0; q < DW; ++q) dot = __dp4a(patch[q], wr[q], dot);
+    outp[o] = static_cast<uint8_t>(mb_requant_fast(static_cast<int32_t>(dot) + in_term + cterm[o], p.rq));
   }
 }
 
@@ -270,6 +289,7 @@ extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
   p.depth_padded = static_cast<int>(align_up(static_cast<size_t>(depth), 16));
   p.zp_in = zp_in; p.zp_f = zp_f;
   p.rq = mb_make_requant(multiplier, right_shift, zp_out);
+  p.rq_variant = mb_requant_variant(right_shift, zp_out);
 
   if (KH == 3 && KW == 3 && C == 3 && O <= 256 &&
       (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {

@@ -73,7 +73,9 @@ struct TcParams {
   int bias_per_row;
   int32_t zp_a, zp_b, kzz;
   mb_requant_params rq;
-  int rq_variant;  // mb_requant_variant(): bit 0 = output zero point 0, bit 1 = shift >= 1
+  int rq_variant;  // mb_requant_variant(): bit 0 = output zero point 0, bit 1 = shift >= 1;
+                   // 4 = the Gemv delegators' float rule (mult_f, zp_f)
+  float mult_f, zp_f;
   void *C;
   int out_is_int32;
   int c_tma;  // uint8 C written by TMA stores (base and rows 16-byte aligned)
@@ -171,6 +173,14 @@ __device__ __forceinline__ void requant_chunk(const uint32_t (&raw)[CHUNK], int3
   }
 }
 
+// The float rule of the Gemv delegators (mace/ops/arm/q8/gemv.cc:151-164):
+// Saturate<uint8_t>(roundf(acc * multiplier [+ zp_out])), product and sum rounded separately
+// (zp_f is 0 for the REF delegator's formula, which omits the zero point).
+__device__ __forceinline__ uint32_t requant_float_rule(int32_t acc, float mult_f, float zp_f) {
+  const float v = __fadd_rn(__fmul_rn(static_cast<float>(acc), mult_f), zp_f);
+  return mb_saturate_round_u8(v);
+}
+
 // What an epilogue warp needs for one tile on the TMA-store path.
 struct EpiTile {
   uint32_t tbase;          // TMEM address of the warp's 32 lanes x 64 columns
@@ -187,7 +197,7 @@ struct EpiTile {
 // 32 rows x 64 columns of one tile: four 16-column chunks from TMEM (the next one in flight
 // while the current one is requantized), staged two chunks at a time for a TMA store of
 // 32 rows x 32 bytes.
-template <bool ZP0, bool SGE1>
+template <bool ZP0, bool SGE1, bool FLOAT_RULE = false>
 __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap &tmap_c,
                                              const TcParams &p) {
   uint32_t r[2][CHUNK];
@@ -203,8 +213,21 @@ __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap
       if (e.lane == 0) mbar_arrive(e.tempty);
     }
     uint32_t packed[CHUNK / 4];
-    requant_chunk<ZP0, SGE1>(r[i & 1], e.row_term, reinterpret_cast<const int4 *>(e.ct_base + i * CHUNK),
-                             p, packed);
+    if (FLOAT_RULE) {
+      const int4 *ct = reinterpret_cast<const int4 *>(e.ct_base + i * CHUNK);
+#pragma unroll
+      for (int q = 0; q < CHUNK / 4; ++q) {
+        const int4 t = ct[q];
+        const uint32_t b0 = requant_float_rule(static_cast<int32_t>(r[i & 1][4 * q + 0]) + e.row_term + t.x, p.mult_f, p.zp_f);
+        const uint32_t b1 = requant_float_rule(static_cast<int32_t>(r[i & 1][4 * q + 1]) + e.row_term + t.y, p.mult_f, p.zp_f);
+        const uint32_t b2 = requant_float_rule(static_cast<int32_t>(r[i & 1][4 * q + 2]) + e.row_term + t.z, p.mult_f, p.zp_f);
+        const uint32_t b3 = requant_float_rule(static_cast<int32_t>(r[i & 1][4 * q + 3]) + e.row_term + t.w, p.mult_f, p.zp_f);
+        packed[q] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+      }
+    } else {
+      requant_chunk<ZP0, SGE1>(r[i & 1], e.row_term, reinterpret_cast<const int4 *>(e.ct_base + i * CHUNK),
+                               p, packed);
+    }
     if ((i & 1) == 0) {
       // the previous store must have read the staging buffer before it is refilled
       if (e.lane == 0) bulk_wait_group_read<0>();
@@ -538,6 +561,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const EpiTile e{tbase, row_term, ct_base, tempty_bar + 8 * acc_buf, stage_row, swz, stage_addr,
                         n_first, m0, b, lane};
         switch (p.rq_variant) {
+          case 4: epi_tma_tile<false, false, true>(e, tmap_c, p); break;
           case 3: epi_tma_tile<true, true>(e, tmap_c, p); break;
           case 2: epi_tma_tile<false, true>(e, tmap_c, p); break;
           case 1: epi_tma_tile<true, false>(e, tmap_c, p); break;
@@ -564,7 +588,8 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const int32_t acc = static_cast<int32_t>(v[j]) + row_term + ct[j];
               if (n0 + j < p.N) {
                 if (p.out_is_int32) c32[n0 + j] = acc;
-                else c8[n0 + j] = static_cast<uint8_t>(mb_requant_fast(acc, p.rq));
+                else c8[n0 + j] = static_cast<uint8_t>(p.rq_variant == 4 ? requant_float_rule(acc, p.mult_f, p.zp_f)
+                                                                         : mb_requant_fast(acc, p.rq));
               }
             }
           }
@@ -666,12 +691,12 @@ bool mb_gemm_u8_tc_supported(const mb_context *ctx, const void *A, const void *B
 // [K x M] MN-major; B^T is [N x K] K-major (b_mn = false) or B is [K x N]
 // MN-major.  C is row-major M x N.  sum_a / sum_b are the per-row byte sums of
 // the operands (may be null when the other zero point is 0).
-int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
-                         const uint32_t *sum_a, const uint32_t *sum_b, const int32_t *bias,
-                         void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
-                         int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
-                         int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
-                         int bias_per_row) {
+static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+                          const uint32_t *sum_a, const uint32_t *sum_b, const int32_t *bias,
+                          void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
+                          int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
+                          int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
+                          int bias_per_row, int float_rule, float mult_f, int add_zp) {
   // Operand sums computed inside the kernel: K-major operands, short K, and the
   // caller passed no precomputed sums although a zero point needs them.
   // Rows of 64 or 32 bytes for K-major operands with K <= 64 (the first pointwise
@@ -715,7 +740,9 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.bias = bias; p.bias_per_row = bias_per_row;
   p.zp_a = zp_a; p.zp_b = zp_b;
   p.rq = mb_make_requant(mult, shift, zp_c);
-  p.rq_variant = mb_requant_variant(shift, zp_c);
+  p.rq_variant = float_rule ? 4 : mb_requant_variant(shift, zp_c);
+  p.mult_f = mult_f;
+  p.zp_f = add_zp ? static_cast<float>(zp_c) : 0.f;
   p.kzz = static_cast<int32_t>(static_cast<uint32_t>(K) * static_cast<uint32_t>(zp_a) *
                                static_cast<uint32_t>(zp_b));
   p.C = C; p.out_is_int32 = out_is_int32;
@@ -767,4 +794,24 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   if (BN == 128) { MB_TC_DISPATCH(128) }
   MB_TC_DISPATCH(64)
 #undef MB_TC_DISPATCH
+}
+
+int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+                         const uint32_t *sum_a, const uint32_t *sum_b, const int32_t *bias,
+                         void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
+                         int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
+                         int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
+                         int bias_per_row) {
+  return tc_launch_impl(ctx, A, B, sum_a, sum_b, bias, C, out_is_int32, batch, M, N, K, a_mn, b_mn,
+                        a_batched, b_batched, zp_a, zp_b, mult, shift, zp_c, bias_per_row, 0, 0.f, 0);
+}
+
+// The same product with the Gemv delegators' float requantization rule (see
+// requant_float_rule): K-major operands, operand sums taken inside the kernel.
+int mb_gemm_u8_tc_launch_float_rule(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+                                    const int32_t *bias, void *C, int out_is_int32, int64_t M,
+                                    int64_t N, int64_t K, int32_t zp_a, int32_t zp_b, float mult_f,
+                                    int32_t zp_c, int add_zp) {
+  return tc_launch_impl(ctx, A, B, nullptr, nullptr, bias, C, out_is_int32, 1, M, N, K, false, false, 0,
+                        0, zp_a, zp_b, 1 << 30, 0, zp_c, 0, 1, mult_f, add_zp);
 }

@@ -131,6 +131,14 @@ __global__ void __launch_bounds__(256) gemv_u8_kernel(const GemvParams p) {
 
 }  // namespace
 
+bool mb_gemm_u8_tc_supported(const mb_context *ctx, const void *A, const void *B, int64_t M,
+                             int64_t N, int64_t K, bool a_mn, bool b_mn, int a_batched,
+                             int b_batched);
+int mb_gemm_u8_tc_launch_float_rule(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+                                    const int32_t *bias, void *C, int out_is_int32, int64_t M,
+                                    int64_t N, int64_t K, int32_t zp_a, int32_t zp_b, float mult_f,
+                                    int32_t zp_c, int add_zp);
+
 extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rhs,
                           const int32_t *bias, void *out, int out_is_int32, int64_t batch,
                           int64_t rows, int64_t K, int lhs_batched, int rhs_batched,
@@ -145,6 +153,14 @@ extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rh
   if (lhs_batched && batch > 65535)
     return mb_fail(ctx, MB_UNSUPPORTED, "mb_gemv_u8: batch > 65535 with a batched matrix");
   MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  // Many vectors against one matrix (FullyConnected on a batch) is a GEMM
+  // out[batch x rows] = rhs[batch x K] * lhs[rows x K]^T: the tensor-core kernel with the float
+  // requantization rule in its epilogue reads the matrix once instead of once per vector.
+  if (!lhs_batched && rhs_batched && batch >= 16 && K % 16 == 0 && K <= 1024 && ctx->use_tensor_cores &&
+      mb_gemm_u8_tc_supported(ctx, rhs, lhs, batch, rows, K, false, false, 0, 0)) {
+    return mb_gemm_u8_tc_launch_float_rule(ctx, rhs, lhs, bias, out, out_is_int32, batch, rows, K, zp_rhs,
+                                           zp_lhs, multiplier, zp_out, add_zp_out);
+  }
   GemvParams p;
   p.lhs = lhs; p.rhs = rhs; p.bias = bias; p.out = out;
   p.batch = batch; p.rows = rows; p.K = K;
