@@ -37,6 +37,16 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 L2_BYTES = 126 * 1024 * 1024
 
+# dram__bytes_read.sum + dram__bytes_write.sum from the ncu captures summarised under profiles/
+# (bytes per step of the kernel family, resp. per launch); outputs that are still in L2 when a
+# kernel's capture ends are not in these sums.
+NCU_TRAFFIC = {
+    "mobilenet_dw": 196.4e6,   # 13 depthwise launches, profiles/mobilenet_v1_u8_b64_launches.md
+    "mobilenet_pw": 129.0e6,   # 13 pointwise + FC GEMM launches, same file
+    "gemm_u8_4096": 33.76e6,   # gemm_u8_tc_kernel<256>, profiles/gemm_u8_tc_kernel_4096.md
+    "winograd_f32_cfg1": 144.2e6,  # three kernels of one convolution, caches flushed between them
+}
+
 
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -302,7 +312,7 @@ def run_gemm(args, rank, world):
             "config": dict(wl.config(n_sets), parallelism="replicas only (dp%d)" % world),
             "roofline": {"bound": "tensor", "achieved": round(achieved, 2),
                          "peak": round(peak, 1), "unit": "TOP/s",
-                         "frac": round(achieved / peak, 4), "traffic": None,
+                         "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC["gemm_u8_4096"],
                          "peak_source": "2 x %s bf16 burst (int8 rate of the tensor core; "
                                         "no int8 figure in MEASURED_PEAKS.json)" % peaks["source"],
                          "kernel": "gemm_u8_tc_kernel<256> (step also holds the two operand "
@@ -455,9 +465,9 @@ def run_mobilenet(args, rank, world):
         e2e_val = world * BATCH / (e2e_ms / e2e_steps * 1e-3)
         lbytes = mobilenet_layer_bytes(layers, BATCH)
         # group operator times by kernel family
-        fam = {"dw": ["dwconv3x3_u8_kernel", 0.0, 0], "pw": ["gemm_u8_tc_kernel (+ byte sums)", 0.0, 0],
-               "stem": ["conv_u8_direct_kernel", 0.0, 0], "pool": ["avgpool_u8_kernel", 0.0, 0],
-               "fc": ["gemv_u8_kernel", 0.0, 0]}
+        fam = {"dw": ["dwconv3x3_u8_kernel", 0.0, 0], "pw": ["gemm_u8_tc_kernel (pointwise)", 0.0, 0],
+               "stem": ["conv_u8_patch_dp4a_kernel", 0.0, 0], "pool": ["avgpool_u8_c4_kernel", 0.0, 0],
+               "fc": ["gemm_u8_tc_kernel (FullyConnected, float rule)", 0.0, 0]}
         for label, t in per_op.items():
             name = label.split(":")[1]
             key = "dw" if name.startswith("dw") else "pw" if name.startswith("pw") else name
@@ -481,7 +491,9 @@ def run_mobilenet(args, rank, world):
                        "l2": "activations of one step (%.0f MB) exceed L2" % (total_bytes / 1e6)},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                         "frac": round(achieved / peaks["hbm_gbs"], 4),
+                         "traffic": NCU_TRAFFIC["mobilenet_dw" if dom is fam["dw"] else "mobilenet_pw"]
+                         if dom in (fam["dw"], fam["pw"]) else None,
                          "peak_source": "%s copy bandwidth" % peaks["source"],
                          "kernel": dom[0],
                          "kernel_share_of_step": round(dom[1] / total_prof, 3),
@@ -613,7 +625,8 @@ def run_winograd(args, rank, world):
                        "l2": "rotating %d input/output sets (%.0f MB > L2)" % (n_sets, n_sets * 51.4),
                        "parallelism": "dp%d: batch sharded, filter replicated" % world},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
-                         "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                         "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                         "traffic": NCU_TRAFFIC["winograd_f32_cfg1"],
                          "peak_source": "%s copy bandwidth" % peaks["source"],
                          "kernel": "whole call: wino_input_kernel + gemm_f32_tc_kernel + wino_output_kernel",
                          "algorithmic_bytes_per_step": alg_bytes},
