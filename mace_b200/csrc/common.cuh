@@ -43,6 +43,8 @@ struct mb_context {
   long long *tc_timeline = nullptr;  // optional device buffer: per-role clock stamps of CTA 0
   uint64_t capture_launches0 = 0, capture_launches_tc0 = 0;
   uint64_t func_attr_mask = 0;   // kernels whose shared-memory limit was raised
+  int pdl_next_gemm = 0;         // the next tensor-core GEMM may start before its predecessor (the
+                                 // operand-sum kernel) ends; it waits for it where it reads the sums
   void *skinny_ws = nullptr;     // arrival counters of the few-row GEMM (zero between calls)
   size_t skinny_ws_bytes = 0;
   char last_error[512] = {0};

@@ -109,6 +109,8 @@ __global__ void __launch_bounds__(256) gemm_u8_generic_kernel(const GenericParam
 __global__ void __launch_bounds__(256) rowsum_u8_kernel(const uint8_t *__restrict__ x,
                                                         uint32_t *__restrict__ out,
                                                         int64_t rows, int64_t len) {
+  // let a dependent GEMM launch now: it waits for this grid only where it reads the sums
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -139,6 +141,7 @@ __global__ void __launch_bounds__(256) colsum_u8_kernel(const uint8_t *__restric
                                                         int64_t rows_per_slice,
                                                         int64_t batch_stride) {
   __shared__ uint32_t part[8][32][17];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int64_t c16 = static_cast<int64_t>(blockIdx.x) * 32 + tx;  // 16-column group
   const bool active = c16 * 16 < cols;
@@ -326,6 +329,9 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
     return launch_generic(ctx, A, B, bias, C, out_is_int32, batch, M, N, K, a_mn, b_mn,
                           a_batched, b_batched, zp_a, zp_b, mult, shift, zp_c, bias_per_row);
   }
+  // The operand-sum kernel was the last launch: the GEMM may overlap it (programmatic
+  // dependent launch); its operands were complete before that kernel started.
+  ctx->pdl_next_gemm = (need_sum_a || need_sum_b) && !ctx->capturing ? 1 : 0;
   return mb_gemm_u8_tc_launch(ctx, a_use, b_use, sum_a, sum_b, bias, C, out_is_int32, batch, M,
                               N, K, a_mn_use, b_mn_use, a_batched, b_batched, zp_a, zp_b, mult,
                               shift, zp_c, bias_per_row);

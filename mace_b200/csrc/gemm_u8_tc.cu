@@ -428,6 +428,10 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp < FIRST_EPI_WARP) {
     // ---------------- preparation: operand sums (fused) and epilogue terms ----------------
+    // Precomputed sums come from the kernel launched just before this one, which this grid
+    // may have overtaken (programmatic dependent launch): wait for it here, and only here.
+    if (!FUSE_SUMS && (p.sum_a != nullptr || p.sum_b != nullptr))
+      asm volatile("griddepcontrol.wait;" ::: "memory");
     const int r = (warp - 2) * 32 + lane;  // 0..127: row of the A tile / column slot
     int stage = 0;
     uint32_t phase = 0;
@@ -661,7 +665,22 @@ int launch_cfg(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, co
   p.step_m = grid % p.tiles_m;
   p.step_n = (grid / p.tiles_m) % p.tiles_n;
   p.step_b = (grid / p.tiles_m) / p.tiles_n;
-  kern<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(ta, tb, tc, p);
+  if (ctx->pdl_next_gemm) {
+    ctx->pdl_next_gemm = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p));
+  } else {
+    kern<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(ta, tb, tc, p);
+  }
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   ctx->launches_tc++;
