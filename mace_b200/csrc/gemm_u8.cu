@@ -108,11 +108,11 @@ __global__ void __launch_bounds__(256) gemm_u8_generic_kernel(const GenericParam
 // per row, 16-byte loads (len % 16 == 0, base 16-byte aligned).
 __global__ void __launch_bounds__(256) rowsum_u8_kernel(const uint8_t *__restrict__ x,
                                                         uint32_t *__restrict__ out,
-                                                        int64_t rows, int64_t len) {
+                                                        int64_t rows, int64_t len, int wait_at_end) {
   // let a dependent GEMM launch now: it waits for this grid only where it reads the sums
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
+  if (row >= rows) return;  // (block 0 always has a live warp 0 for the wait below)
   const int lane = threadIdx.x & 31;
   const uint4 *p = reinterpret_cast<const uint4 *>(x + row * len);
   const int64_t nvec = len >> 4;
@@ -128,6 +128,9 @@ __global__ void __launch_bounds__(256) rowsum_u8_kernel(const uint8_t *__restric
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   if (lane == 0) out[row] = s;
+  // Launched ahead of the kernel before it: do not let this grid END before that one has,
+  // so that whoever waits for this grid has waited for both.
+  if (wait_at_end && threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // Sum down the columns of a [rows x cols] byte matrix (cols % 16 == 0, base
@@ -139,7 +142,7 @@ __global__ void __launch_bounds__(256) colsum_u8_kernel(const uint8_t *__restric
                                                         uint32_t *__restrict__ out,
                                                         int64_t rows, int64_t cols,
                                                         int64_t rows_per_slice,
-                                                        int64_t batch_stride) {
+                                                        int64_t batch_stride, int wait_at_end) {
   __shared__ uint32_t part[8][32][17];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -179,6 +182,7 @@ __global__ void __launch_bounds__(256) colsum_u8_kernel(const uint8_t *__restric
     for (int y = 0; y < 8; ++y) t += part[y][gx][gi];
     atomicAdd(out + b * cols + col, t);
   }
+  if (wait_at_end && threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // ---- transpose [rows x cols] -> [cols x rows] bytes ------------------------------
@@ -199,26 +203,43 @@ __global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t *__rest
   }
 }
 
-int launch_rowsum(mb_context *ctx, const uint8_t *x, uint32_t *out, int64_t rows, int64_t len) {
-  rowsum_u8_kernel<<<static_cast<unsigned>(ceil_div64(rows, 8)), 256, 0, ctx->stream>>>(x, out, rows, len);
-  MB_CUDA(ctx, cudaGetLastError());
+// pdl: launch with programmatic stream serialization, i.e. allowed to start before the kernel
+// launched just before it has ended (that kernel must be the other operand-sum kernel, whose
+// data this one does not touch); the kernel then holds its own end back until that one's.
+template <typename... Args>
+int launch_maybe_pdl(mb_context *ctx, void (*kern)(Args...), dim3 grid, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  MB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, args...));
   ctx->launches++;
   return MB_SUCCESS;
 }
 
+int launch_rowsum(mb_context *ctx, const uint8_t *x, uint32_t *out, int64_t rows, int64_t len,
+                  bool pdl = false) {
+  return launch_maybe_pdl(ctx, rowsum_u8_kernel, dim3(static_cast<unsigned>(ceil_div64(rows, 8))), pdl, x,
+                          out, rows, len, pdl ? 1 : 0);
+}
+
+// `out` must be zero (mb_zero_colsum); kept apart so that the zeroing can precede BOTH sum kernels.
 int launch_colsum(mb_context *ctx, const uint8_t *x, uint32_t *out, int64_t nb, int64_t rows,
-                  int64_t cols) {
-  MB_CUDA(ctx, cudaMemsetAsync(out, 0, sizeof(uint32_t) * nb * cols, ctx->stream));
+                  int64_t cols, bool pdl = false) {
   const int64_t col_blocks = ceil_div64(cols, 512);
   int64_t slices = ceil_div64(static_cast<int64_t>(ctx->num_sms) * 4, col_blocks * nb);
   slices = std::max<int64_t>(1, std::min<int64_t>(slices, ceil_div64(rows, 64)));
   const int64_t rps = ceil_div64(rows, slices);
   dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(ceil_div64(rows, rps)),
             static_cast<unsigned>(nb));
-  colsum_u8_kernel<<<grid, 256, 0, ctx->stream>>>(x, out, rows, cols, rps, rows * cols);
-  MB_CUDA(ctx, cudaGetLastError());
-  ctx->launches++;
-  return MB_SUCCESS;
+  return launch_maybe_pdl(ctx, colsum_u8_kernel, grid, pdl, x, out, rows, cols, rps, rows * cols,
+                          pdl ? 1 : 0);
 }
 
 int launch_transpose(mb_context *ctx, const uint8_t *in, uint8_t *out, int64_t nb, int64_t rows,
@@ -316,13 +337,18 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
     b_use = scratch + off_bt;
     b_mn_use = false;
   }
+  // column-type sums accumulate with atomics into zeroed outputs: zero them before either kernel
+  if (need_sum_a && a_mn_use) MB_CUDA(ctx, cudaMemsetAsync(sum_a, 0, sizeof(uint32_t) * nb_a * M, ctx->stream));
+  if (need_sum_b && b_mn_use) MB_CUDA(ctx, cudaMemsetAsync(sum_b, 0, sizeof(uint32_t) * nb_b * N, ctx->stream));
   if (need_sum_a) {
     if (a_mn_use) MB_RETURN_IF_ERROR(launch_colsum(ctx, a_use, sum_a, nb_a, K, M));
     else MB_RETURN_IF_ERROR(launch_rowsum(ctx, a_use, sum_a, nb_a * M, K));
   }
   if (need_sum_b) {
-    if (b_mn_use) MB_RETURN_IF_ERROR(launch_colsum(ctx, b_use, sum_b, nb_b, K, N));
-    else MB_RETURN_IF_ERROR(launch_rowsum(ctx, b_use, sum_b, nb_b * N, K));
+    // the second sum kernel may run alongside the first (see launch_maybe_pdl)
+    const bool pdl = need_sum_a && !ctx->capturing;
+    if (b_mn_use) MB_RETURN_IF_ERROR(launch_colsum(ctx, b_use, sum_b, nb_b, K, N, pdl));
+    else MB_RETURN_IF_ERROR(launch_rowsum(ctx, b_use, sum_b, nb_b * N, K, pdl));
   }
   if (!mb_gemm_u8_tc_supported(ctx, a_use, b_use, M, N, K, a_mn_use, b_mn_use, a_batched,
                                b_batched)) {
