@@ -115,7 +115,9 @@ struct TileCfg {
   static constexpr int B_BYTES = B_MN ? ((BN + 127) / 128) * 128 * KB : BN * KB;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   // epilogue staging for the TMA stores: 1 KB (32 rows x 32 bytes) per epilogue warp
-  static constexpr int STAGING_BYTES = EPI_WARPS * 1024;
+  // ... 2 KB (32 rows x 64 bytes: one store per warp and tile) where the ring leaves room
+  static constexpr int STG_CHUNKS = BN == 256 ? 2 : 4;   // 16-byte chunks per staged row
+  static constexpr int STAGING_BYTES = EPI_WARPS * 32 * STG_CHUNKS * 16;
   static constexpr int RING_BUDGET = 208 * 1024 - STAGING_BYTES;
   static constexpr int STAGES = RING_BUDGET / STAGE_BYTES > 8 ? 8 : RING_BUDGET / STAGE_BYTES;
   // all 512 TMEM columns as accumulator buffers: 2 for BN = 256, 4 for 128, 8 for 64, so
@@ -187,7 +189,7 @@ struct EpiTile {
   int32_t row_term;
   const int32_t *ct_base;  // column terms of the 64 columns (shared memory)
   uint32_t tempty;         // barrier that returns the accumulator buffer
-  uint4 *stage_row;        // this lane's 32-byte row of the staging buffer
+  uint4 *stage_row;        // this lane's row of the staging buffer (STG chunks of 16 bytes)
   int swz;
   uint32_t stage_addr;
   int64_t n_first;
@@ -195,9 +197,9 @@ struct EpiTile {
 };
 
 // 32 rows x 64 columns of one tile: four 16-column chunks from TMEM (the next one in flight
-// while the current one is requantized), staged two chunks at a time for a TMA store of
-// 32 rows x 32 bytes.
-template <bool ZP0, bool SGE1, bool FLOAT_RULE = false>
+// while the current one is requantized), staged STG chunks at a time for a TMA store of
+// 32 rows x 16*STG bytes.
+template <int STG, bool ZP0, bool SGE1, bool FLOAT_RULE = false>
 __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap &tmap_c,
                                              const TcParams &p) {
   uint32_t r[2][CHUNK];
@@ -228,16 +230,16 @@ __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap
       requant_chunk<ZP0, SGE1>(r[i & 1], e.row_term, reinterpret_cast<const int4 *>(e.ct_base + i * CHUNK),
                                p, packed);
     }
-    if ((i & 1) == 0) {
+    if ((i & (STG - 1)) == 0) {
       // the previous store must have read the staging buffer before it is refilled
       if (e.lane == 0) bulk_wait_group_read<0>();
       __syncwarp();
     }
-    e.stage_row[(i & 1) ^ e.swz] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    if (i & 1) {
+    e.stage_row[(i & (STG - 1)) ^ e.swz] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    if ((i & (STG - 1)) == STG - 1) {
       fence_proxy_async();
       __syncwarp();
-      const int64_t n0 = e.n_first + (i - 1) * CHUNK;
+      const int64_t n0 = e.n_first + (i - (STG - 1)) * CHUNK;
       if (e.lane == 0 && n0 < p.N && e.m0 < p.M) {
         tma_store_3d(&tmap_c, e.stage_addr, static_cast<int>(n0), e.m0, e.b);
         bulk_commit_group();
@@ -532,10 +534,13 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // staging for the TMA store: 32 rows x 32 bytes (two chunks), 32-byte swizzle:
     // 16-byte half h of row r sits at r*32 + ((h ^ (r >> 2)) & 1)*16, which keeps the
     // quarter-warps' 16-byte writes free of bank conflicts
-    uint8_t *stage_ptr = smem_aligned + STAGES * Cfg::STAGE_BYTES + (warp - FIRST_EPI_WARP) * 1024;
+    constexpr int STG = Cfg::STG_CHUNKS;
+    uint8_t *stage_ptr = smem_aligned + STAGES * Cfg::STAGE_BYTES + (warp - FIRST_EPI_WARP) * (32 * STG * 16);
     const uint32_t stage_addr = smem_u32(stage_ptr);
-    uint4 *stage_row = reinterpret_cast<uint4 *>(stage_ptr + lane * 32);
-    const int swz = (lane >> 2) & 1;
+    uint4 *stage_row = reinterpret_cast<uint4 *>(stage_ptr + lane * (STG * 16));
+    // 32-byte rows, 32-byte swizzle: half h of row r at ((h ^ (r >> 2)) & 1); 64-byte rows,
+    // 64-byte swizzle: chunk c of row r at (c ^ (r >> 1)) & 3
+    const int swz = STG == 2 ? ((lane >> 2) & 1) : ((lane >> 1) & 3);
     int local = 0;
     for (TileIter it(p); it.valid(p); it.next(p), ++local) {
       if (local % GROUPS != group) continue;
@@ -565,11 +570,11 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const EpiTile e{tbase, row_term, ct_base, tempty_bar + 8 * acc_buf, stage_row, swz, stage_addr,
                         n_first, m0, b, lane};
         switch (p.rq_variant) {
-          case 4: epi_tma_tile<false, false, true>(e, tmap_c, p); break;
-          case 3: epi_tma_tile<true, true>(e, tmap_c, p); break;
-          case 2: epi_tma_tile<false, true>(e, tmap_c, p); break;
-          case 1: epi_tma_tile<true, false>(e, tmap_c, p); break;
-          default: epi_tma_tile<false, false>(e, tmap_c, p); break;
+          case 4: epi_tma_tile<STG, false, false, true>(e, tmap_c, p); break;
+          case 3: epi_tma_tile<STG, true, true>(e, tmap_c, p); break;
+          case 2: epi_tma_tile<STG, false, true>(e, tmap_c, p); break;
+          case 1: epi_tma_tile<STG, true, false>(e, tmap_c, p); break;
+          default: epi_tma_tile<STG, false, false>(e, tmap_c, p); break;
         }
       } else {
         // direct stores: int32 output, or a uint8 output whose rows TMA cannot address
@@ -766,13 +771,18 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
                                static_cast<uint32_t>(zp_b));
   p.C = C; p.out_is_int32 = out_is_int32;
   const uintptr_t cbase = reinterpret_cast<uintptr_t>(C);
-  p.c_tma = (!out_is_int32 && cbase % 16 == 0 && N % 16 == 0 && N >= 32 && M >= 32) ? 1 : 0;
+  p.c_tma = (!out_is_int32 && cbase % 16 == 0 && N % 16 == 0 && N >= 64 && M >= 32) ? 1 : 0;
   p.status = ctx->dev_status;
   p.timeline = ctx->tc_timeline;
 
   CUtensorMap ta, tb, tc;
   if (p.c_tma) {
-    MB_RETURN_IF_ERROR(make_map_u8(ctx, &tc, C, N, M, batch, M * N, 32, 32, CU_TENSOR_MAP_SWIZZLE_32B));
+    // the staged box is 32 bytes wide for 256-wide tiles, else 64 (TileCfg::STG_CHUNKS)
+    if (BN == 256) {
+      MB_RETURN_IF_ERROR(make_map_u8(ctx, &tc, C, N, M, batch, M * N, 32, 32, CU_TENSOR_MAP_SWIZZLE_32B));
+    } else {
+      MB_RETURN_IF_ERROR(make_map_u8(ctx, &tc, C, N, M, batch, M * N, 64, 32, CU_TENSOR_MAP_SWIZZLE_64B));
+    }
   } else {
     memset(&tc, 0, sizeof(tc));
   }
