@@ -109,6 +109,7 @@ __device__ __forceinline__ uint32_t mb_requant(int32_t acc, int32_t mult,
 // the identity against the two-step definition.
 struct mb_requant_params {
   int64_t c64;   // 2^30 (+ 2^(shift+30) when shift >= 1)
+  int64_t c64z;  // c64 + (zp << sh): the output zero point folded into the rounding constant
   int32_t mult;  // fixed-point multiplier in [2^30, 2^31)
   int32_t neg;   // -2^31 when shift >= 1, else 0
   int32_t sh;    // 31 + shift
@@ -122,6 +123,7 @@ static inline mb_requant_params mb_make_requant(int32_t mult, int32_t shift, int
   q.neg = shift >= 1 ? static_cast<int32_t>(0x80000000u) : 0;
   q.sh = 31 + shift;
   q.zp = zp_out;
+  q.c64z = q.c64 + (q.sh <= 50 ? (static_cast<int64_t>(zp_out) << q.sh) : 0ll);
   return q;
 }
 
@@ -147,8 +149,36 @@ __device__ __forceinline__ uint32_t mb_requant_t(int32_t acc, const mb_requant_p
   return static_cast<uint32_t>(__viaddmin_s32_relu(min(y, 255), q.zp, 255));
 }
 
-// Variant index for kernels that switch on it once per tile or thread: bit 0 = ZP0, bit 1 = SGE1.
+// Four values at once for 1 <= shift <= 19: the zero point rides in the rounding constant
+// (c64z), so y + zp comes straight out of the shift, and cvt.pack saturates two values to
+// [0, 255] AND packs them in one instruction: 2.5 instructions per value instead of 3.75.
+// (shift 0 is excluded because y + zp could wrap int32 there; shift > 19 because zp << sh
+// would not fit.)
+__device__ __forceinline__ uint32_t mb_pack4_sat_u8(int32_t v0, int32_t v1, int32_t v2, int32_t v3) {
+  uint32_t hi, d;
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(v3), "r"(v2), "r"(0));
+  asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(v1), "r"(v0), "r"(hi));
+  return d;
+}
+
+template <bool ZP0>
+__device__ __forceinline__ int32_t mb_requant_unclamped(int32_t acc, const mb_requant_params &q) {
+  int64_t t = static_cast<int64_t>(acc) * q.mult + q.c64z;
+  if (!ZP0) t += static_cast<int64_t>(static_cast<int32_t>(static_cast<uint32_t>(acc) >> 31)) * q.neg;
+  return static_cast<int32_t>(t >> 32) >> (q.sh - 32);
+}
+
+template <bool ZP0>
+__device__ __forceinline__ uint32_t mb_requant_pack4(int32_t a0, int32_t a1, int32_t a2, int32_t a3,
+                                                     const mb_requant_params &q) {
+  return mb_pack4_sat_u8(mb_requant_unclamped<ZP0>(a0, q), mb_requant_unclamped<ZP0>(a1, q),
+                         mb_requant_unclamped<ZP0>(a2, q), mb_requant_unclamped<ZP0>(a3, q));
+}
+
+// Variant index for kernels that switch on it once per tile or thread:
+//   0..3: bit 0 = ZP0, bit 1 = SGE1 (mb_requant_t);  4 / 5: packed form, zero point != 0 / == 0.
 static inline int mb_requant_variant(int32_t shift, int32_t zp_out) {
+  if (shift >= 1 && shift <= 19) return zp_out == 0 ? 5 : 4;
   return (zp_out == 0 ? 1 : 0) | (shift >= 1 ? 2 : 0);
 }
 

@@ -93,12 +93,12 @@ __global__ void __launch_bounds__(128) conv_u8_direct_kernel(const ConvParams p)
 // live in shared memory and are read as broadcasts.
 // All output channels of one pixel from its packed patch: four channels per step, filter
 // rows read as 128-bit broadcasts.
-template <int DW, int DWP, bool ZP0, bool SGE1>
+template <int DW, int DWP, int VAR>
 __device__ __forceinline__ void patch_outputs(const uint32_t (&patch)[DW], const uint32_t *smem_w,
                                               const int32_t *cterm, int32_t in_term,
                                               const ConvParams &p, uint8_t *outp) {
   for (int o0 = 0; o0 < p.O; o0 += 4) {
-    uint32_t b[4];
+    int32_t a[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const uint4 *wr = reinterpret_cast<const uint4 *>(smem_w + (o0 + j) * DWP);
@@ -111,10 +111,18 @@ __device__ __forceinline__ void patch_outputs(const uint32_t (&patch)[DW], const
         if (q * 4 + 2 < DW) dot = __dp4a(patch[q * 4 + 2 < DW ? q * 4 + 2 : 0], w4.z, dot);
         if (q * 4 + 3 < DW) dot = __dp4a(patch[q * 4 + 3 < DW ? q * 4 + 3 : 0], w4.w, dot);
       }
-      b[j] = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(dot) + in_term + cterm[o0 + j], p.rq);
+      a[j] = static_cast<int32_t>(dot) + in_term + cterm[o0 + j];
     }
-    *reinterpret_cast<uint32_t *>(outp + o0) =
-        __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+    uint32_t word;
+    if (VAR >= 4) {
+      word = mb_requant_pack4<VAR == 5>(a[0], a[1], a[2], a[3], p.rq);
+    } else {
+      uint32_t b[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = mb_requant_t<(VAR & 1) != 0, (VAR & 2) != 0>(a[j], p.rq);
+      word = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+    }
+    *reinterpret_cast<uint32_t *>(outp + o0) = word;
   }
 }
 
@@ -180,10 +188,12 @@ __global__ void __launch_bounds__(128) conv_u8_patch_dp4a_kernel(const ConvParam
   // branch per value costs more than the arithmetic.
   if ((p.O & 3) == 0) {
     switch (p.rq_variant) {
-      case 3: patch_outputs<DW, DWP, true, true>(patch, smem_w, cterm, in_term, p, outp); break;
-      case 2: patch_outputs<DW, DWP, false, true>(patch, smem_w, cterm, in_term, p, outp); break;
-      case 1: patch_outputs<DW, DWP, true, false>(patch, smem_w, cterm, in_term, p, outp); break;
-      default: patch_outputs<DW, DWP, false, false>(patch, smem_w, cterm, in_term, p, outp); break;
+      case 5: patch_outputs<DW, DWP, 5>(patch, smem_w, cterm, in_term, p, outp); break;
+      case 4: patch_outputs<DW, DWP, 4>(patch, smem_w, cterm, in_term, p, outp); break;
+      case 3: patch_outputs<DW, DWP, 3>(patch, smem_w, cterm, in_term, p, outp); break;
+      case 2: patch_outputs<DW, DWP, 2>(patch, smem_w, cterm, in_term, p, outp); break;
+      case 1: patch_outputs<DW, DWP, 1>(patch, smem_w, cterm, in_term, p, outp); break;
+      default: patch_outputs<DW, DWP, 0>(patch, smem_w, cterm, in_term, p, outp); break;
     }
     return;
   }

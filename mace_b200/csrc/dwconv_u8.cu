@@ -210,7 +210,7 @@ __device__ __forceinline__ void dw_mac(int32_t (&acc)[4][4], const DwRow<STRIDE>
   }
 }
 
-// VAR: requantization variant (mb_requant_variant): bit 0 = output zero point 0, bit 1 = shift >= 1.
+// VAR: requantization variant (mb_requant_variant): 0..3 = mb_requant_t, 4 / 5 = packed form.
 template <int STRIDE, int VAR>
 __global__ void __launch_bounds__(256, 2)
 dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows_per_thread,
@@ -285,10 +285,15 @@ dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows
     uint32_t o = out_off + static_cast<uint32_t>(y) * out_row_stride;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      uint32_t b[4];
+      uint32_t word;
+      if (VAR >= 4) {
+        word = mb_requant_pack4<VAR == 5>(acc[j][0], acc[j][1], acc[j][2], acc[j][3], p.rq);
+      } else {
+        uint32_t b[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) b[c] = mb_requant_t<(VAR & 1) != 0, (VAR & 2) != 0>(acc[j][c], p.rq);
-      const uint32_t word = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+        for (int c = 0; c < 4; ++c) b[c] = mb_requant_t<(VAR & 1) != 0, (VAR & 2) != 0>(acc[j][c], p.rq);
+        word = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+      }
       if (j < valid_cols) *reinterpret_cast<uint32_t *>(out + o) = word;
       o += p.C;
     }
@@ -442,6 +447,8 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
     const int var = mb_requant_variant(right_shift, zp_out);
     if (stride_h == 1) {
       switch (var) {
+        case 5: MB_DW_LAUNCH(1, 5); break;
+        case 4: MB_DW_LAUNCH(1, 4); break;
         case 3: MB_DW_LAUNCH(1, 3); break;
         case 2: MB_DW_LAUNCH(1, 2); break;
         case 1: MB_DW_LAUNCH(1, 1); break;
@@ -449,6 +456,8 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
       }
     } else {
       switch (var) {
+        case 5: MB_DW_LAUNCH(2, 5); break;
+        case 4: MB_DW_LAUNCH(2, 4); break;
         case 3: MB_DW_LAUNCH(2, 3); break;
         case 2: MB_DW_LAUNCH(2, 2); break;
         case 1: MB_DW_LAUNCH(2, 1); break;

@@ -73,8 +73,8 @@ struct TcParams {
   int bias_per_row;
   int32_t zp_a, zp_b, kzz;
   mb_requant_params rq;
-  int rq_variant;  // mb_requant_variant(): bit 0 = output zero point 0, bit 1 = shift >= 1;
-                   // 4 = the Gemv delegators' float rule (mult_f, zp_f)
+  int rq_variant;  // mb_requant_variant() (0..5), or 8 = the Gemv delegators' float rule
+                   // (mult_f, zp_f)
   float mult_f, zp_f;
   void *C;
   int out_is_int32;
@@ -160,20 +160,12 @@ struct TileIter {
 };
 
 // Requantizes one 16-column chunk of an accumulator row and packs it into four words.
-template <bool ZP0, bool SGE1>
+// MODE: 0..3 = mb_requant_t<ZP0 = bit 0, SGE1 = bit 1>; 4 / 5 = packed saturating form
+// (zero point != 0 / == 0); 8 = the Gemv delegators' float rule.
+template <int MODE>
 __device__ __forceinline__ void requant_chunk(const uint32_t (&raw)[CHUNK], int32_t row_term,
                                               const int4 *ct, const TcParams &p,
-                                              uint32_t (&packed)[CHUNK / 4]) {
-#pragma unroll
-  for (int q = 0; q < CHUNK / 4; ++q) {
-    const int4 t = ct[q];  // broadcast read: all lanes, same address
-    const uint32_t b0 = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(raw[4 * q + 0]) + row_term + t.x, p.rq);
-    const uint32_t b1 = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(raw[4 * q + 1]) + row_term + t.y, p.rq);
-    const uint32_t b2 = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(raw[4 * q + 2]) + row_term + t.z, p.rq);
-    const uint32_t b3 = mb_requant_t<ZP0, SGE1>(static_cast<int32_t>(raw[4 * q + 3]) + row_term + t.w, p.rq);
-    packed[q] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
-  }
-}
+                                              uint32_t (&packed)[CHUNK / 4]);
 
 // The float rule of the Gemv delegators (mace/ops/arm/q8/gemv.cc:151-164):
 // Saturate<uint8_t>(roundf(acc * multiplier [+ zp_out])), product and sum rounded separately
@@ -181,6 +173,35 @@ __device__ __forceinline__ void requant_chunk(const uint32_t (&raw)[CHUNK], int3
 __device__ __forceinline__ uint32_t requant_float_rule(int32_t acc, float mult_f, float zp_f) {
   const float v = __fadd_rn(__fmul_rn(static_cast<float>(acc), mult_f), zp_f);
   return mb_saturate_round_u8(v);
+}
+
+template <int MODE>
+__device__ __forceinline__ void requant_chunk(const uint32_t (&raw)[CHUNK], int32_t row_term,
+                                              const int4 *ct, const TcParams &p,
+                                              uint32_t (&packed)[CHUNK / 4]) {
+#pragma unroll
+  for (int q = 0; q < CHUNK / 4; ++q) {
+    const int4 t = ct[q];  // broadcast read: all lanes, same address
+    const int32_t a0 = static_cast<int32_t>(raw[4 * q + 0]) + row_term + t.x;
+    const int32_t a1 = static_cast<int32_t>(raw[4 * q + 1]) + row_term + t.y;
+    const int32_t a2 = static_cast<int32_t>(raw[4 * q + 2]) + row_term + t.z;
+    const int32_t a3 = static_cast<int32_t>(raw[4 * q + 3]) + row_term + t.w;
+    if (MODE == 4 || MODE == 5) {
+      packed[q] = mb_requant_pack4<MODE == 5>(a0, a1, a2, a3, p.rq);
+    } else {
+      uint32_t b0, b1, b2, b3;
+      if (MODE == 8) {
+        b0 = requant_float_rule(a0, p.mult_f, p.zp_f); b1 = requant_float_rule(a1, p.mult_f, p.zp_f);
+        b2 = requant_float_rule(a2, p.mult_f, p.zp_f); b3 = requant_float_rule(a3, p.mult_f, p.zp_f);
+      } else {
+        b0 = mb_requant_t<(MODE & 1) != 0, (MODE & 2) != 0>(a0, p.rq);
+        b1 = mb_requant_t<(MODE & 1) != 0, (MODE & 2) != 0>(a1, p.rq);
+        b2 = mb_requant_t<(MODE & 1) != 0, (MODE & 2) != 0>(a2, p.rq);
+        b3 = mb_requant_t<(MODE & 1) != 0, (MODE & 2) != 0>(a3, p.rq);
+      }
+      packed[q] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+    }
+  }
 }
 
 // What an epilogue warp needs for one tile on the TMA-store path.
@@ -199,7 +220,7 @@ struct EpiTile {
 // 32 rows x 64 columns of one tile: four 16-column chunks from TMEM (the next one in flight
 // while the current one is requantized), staged STG chunks at a time for a TMA store of
 // 32 rows x 16*STG bytes.
-template <int STG, bool ZP0, bool SGE1, bool FLOAT_RULE = false>
+template <int STG, int MODE>
 __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap &tmap_c,
                                              const TcParams &p) {
   uint32_t r[2][CHUNK];
@@ -215,21 +236,7 @@ __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap
       if (e.lane == 0) mbar_arrive(e.tempty);
     }
     uint32_t packed[CHUNK / 4];
-    if (FLOAT_RULE) {
-      const int4 *ct = reinterpret_cast<const int4 *>(e.ct_base + i * CHUNK);
-#pragma unroll
-      for (int q = 0; q < CHUNK / 4; ++q) {
-        const int4 t = ct[q];
-        const uint32_t b0 = requant_float_rule(static_cast<int32_t>(r[i & 1][4 * q + 0]) + e.row_term + t.x, p.mult_f, p.zp_f);
-        const uint32_t b1 = requant_float_rule(static_cast<int32_t>(r[i & 1][4 * q + 1]) + e.row_term + t.y, p.mult_f, p.zp_f);
-        const uint32_t b2 = requant_float_rule(static_cast<int32_t>(r[i & 1][4 * q + 2]) + e.row_term + t.z, p.mult_f, p.zp_f);
-        const uint32_t b3 = requant_float_rule(static_cast<int32_t>(r[i & 1][4 * q + 3]) + e.row_term + t.w, p.mult_f, p.zp_f);
-        packed[q] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
-      }
-    } else {
-      requant_chunk<ZP0, SGE1>(r[i & 1], e.row_term, reinterpret_cast<const int4 *>(e.ct_base + i * CHUNK),
-                               p, packed);
-    }
+    requant_chunk<MODE>(r[i & 1], e.row_term, reinterpret_cast<const int4 *>(e.ct_base + i * CHUNK), p, packed);
     if ((i & (STG - 1)) == 0) {
       // the previous store must have read the staging buffer before it is refilled
       if (e.lane == 0) bulk_wait_group_read<0>();
@@ -570,11 +577,13 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const EpiTile e{tbase, row_term, ct_base, tempty_bar + 8 * acc_buf, stage_row, swz, stage_addr,
                         n_first, m0, b, lane};
         switch (p.rq_variant) {
-          case 4: epi_tma_tile<STG, false, false, true>(e, tmap_c, p); break;
-          case 3: epi_tma_tile<STG, true, true>(e, tmap_c, p); break;
-          case 2: epi_tma_tile<STG, false, true>(e, tmap_c, p); break;
-          case 1: epi_tma_tile<STG, true, false>(e, tmap_c, p); break;
-          default: epi_tma_tile<STG, false, false>(e, tmap_c, p); break;
+          case 8: epi_tma_tile<STG, 8>(e, tmap_c, p); break;
+          case 5: epi_tma_tile<STG, 5>(e, tmap_c, p); break;
+          case 4: epi_tma_tile<STG, 4>(e, tmap_c, p); break;
+          case 3: epi_tma_tile<STG, 3>(e, tmap_c, p); break;
+          case 2: epi_tma_tile<STG, 2>(e, tmap_c, p); break;
+          case 1: epi_tma_tile<STG, 1>(e, tmap_c, p); break;
+          default: epi_tma_tile<STG, 0>(e, tmap_c, p); break;
         }
       } else {
         // direct stores: int32 output, or a uint8 output whose rows TMA cannot address
@@ -597,7 +606,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const int32_t acc = static_cast<int32_t>(v[j]) + row_term + ct[j];
               if (n0 + j < p.N) {
                 if (p.out_is_int32) c32[n0 + j] = acc;
-                else c8[n0 + j] = static_cast<uint8_t>(p.rq_variant == 4 ? requant_float_rule(acc, p.mult_f, p.zp_f)
+                else c8[n0 + j] = static_cast<uint8_t>(p.rq_variant == 8 ? requant_float_rule(acc, p.mult_f, p.zp_f)
                                                                          : mb_requant_fast(acc, p.rq));
               }
             }
@@ -764,7 +773,7 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.bias = bias; p.bias_per_row = bias_per_row;
   p.zp_a = zp_a; p.zp_b = zp_b;
   p.rq = mb_make_requant(mult, shift, zp_c);
-  p.rq_variant = float_rule ? 4 : mb_requant_variant(shift, zp_c);
+  p.rq_variant = float_rule ? 8 : mb_requant_variant(shift, zp_c);
   p.mult_f = mult_f;
   p.zp_f = add_zp ? static_cast<float>(zp_c) : 0.f;
   p.kzz = static_cast<int32_t>(static_cast<uint32_t>(K) * static_cast<uint32_t>(zp_a) *

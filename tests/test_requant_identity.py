@@ -74,3 +74,37 @@ def test_variants_match_two_step_definition(orc):
                 assert device_formula_variants(a, m, s, False) == ref, (a, m, s)
                 z = device_formula_variants(a, m, s, True)
                 assert min(255, max(0, z)) == min(255, max(0, ref)), (a, m, s)
+
+
+def device_formula_packed(acc, mult, s, zp):
+    """mb_requant_pack4 of common.cuh (1 <= s <= 19): the output zero point rides in the rounding
+    constant, the saturation to [0, 255] is done by the packing instruction."""
+    assert 1 <= s <= 19 and 0 <= zp <= 255
+    sh = 31 + s
+    t = acc * mult + (1 << 30) + (1 << (s + 30)) + (zp << sh)
+    if zp != 0 and acc < 0:  # the zero-point-0 variant drops the sign term
+        t -= 1 << 31
+    assert -(1 << 63) <= t < (1 << 63)
+    y = (t >> 32) >> (sh - 32)
+    assert -(1 << 31) <= y < (1 << 31)
+    return min(255, max(0, y))
+
+
+def test_packed_form_matches_two_step_definition(orc):
+    rng = np.random.default_rng(2)
+    for s in range(1, 20):
+        ms = [2 ** 30, 2 ** 30 + 1, 2 ** 31 - 1, 1374221056] + [int(m) for m in rng.integers(2 ** 30, 2 ** 31, size=3)]
+        for m in ms:
+            accs = [0, 1, -1, 2, -2, 2 ** 31 - 1, -2 ** 31]
+            accs += [int(a) for a in rng.integers(-2 ** 31, 2 ** 31, size=40)]
+            accs += [int(a) for a in rng.integers(-300 * (1 << s), 300 * (1 << s), size=60)]
+            for k in (-3, -1, 0, 1, 2, 254, 255):
+                x = k * (1 << s) + ((1 << s) >> 1)
+                a = (x << 31) // m
+                accs += [a - 1, a, a + 1]
+            for a in accs:
+                if not (-2 ** 31 <= a < 2 ** 31):
+                    continue
+                ref = orc.rounding_stages(a, m, s)
+                for zp in (0, 1, 77, 128, 255):
+                    assert device_formula_packed(a, m, s, zp) == min(255, max(0, ref + zp)), (a, m, s, zp)
