@@ -65,6 +65,10 @@ __device__ __forceinline__ uint32_t dw_requant(int32_t acc, const DwParams &p) {
 //   12     start[c] = bias[c] - zp_in * sum_t w[t][c]
 //   13     flags: x = group has a non-zero w2
 constexpr int DW_PACK_ITEMS = 14;
+#ifndef DW_THREADS
+#define DW_THREADS 256
+#define DW_BLOCKS_PER_SM 2
+#endif
 
 __device__ __forceinline__ int32_t dp4a_u8_s8(uint32_t a, uint32_t b, int32_t c) {
   int32_t d;
@@ -212,7 +216,7 @@ __device__ __forceinline__ void dw_mac(int32_t (&acc)[4][4], const DwRow<STRIDE>
 
 // VAR: requantization variant (mb_requant_variant): 0..3 = mb_requant_t, 4 / 5 = packed form.
 template <int STRIDE, int VAR>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(DW_THREADS, DW_BLOCKS_PER_SM)
 dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows_per_thread,
                     int segments) {
   constexpr int COLS = STRIDE == 1 ? 6 : 9;
@@ -435,15 +439,15 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
     // 256-thread blocks per SM), so that there is no partial last wave; tensors too large
     // for that take runs of 16 rows.
     const int64_t per_seg = groups * ceil_div64(Wo, 4);
-    const int64_t slots = static_cast<int64_t>(ctx->num_sms) * 2 * 256;
+    const int64_t slots = static_cast<int64_t>(ctx->num_sms) * DW_BLOCKS_PER_SM * DW_THREADS;
     int64_t segments = slots / (per_seg * N);
     segments = std::min<int64_t>(segments, ceil_div64(Ho, 2));
     if (segments < 1) segments = ceil_div64(Ho, 16);
     const int rows = static_cast<int>(ceil_div64(Ho, segments));
     segments = ceil_div64(Ho, rows);
-    const unsigned grid = static_cast<unsigned>(ceil_div64(per_seg * segments * N, 256));
+    const unsigned grid = static_cast<unsigned>(ceil_div64(per_seg * segments * N, DW_THREADS));
 #define MB_DW_LAUNCH(S, V)                                                                   \
-  dwconv3x3_u8_kernel<S, V><<<grid, 256, 0, ctx->stream>>>(p, packed, rows, static_cast<int>(segments))
+  dwconv3x3_u8_kernel<S, V><<<grid, DW_THREADS, 0, ctx->stream>>>(p, packed, rows, static_cast<int>(segments))
     const int var = mb_requant_variant(right_shift, zp_out);
     if (stride_h == 1) {
       switch (var) {

@@ -229,14 +229,16 @@ __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap
   for (int i = 0; i < 4; ++i) {
     tmem_ld_wait_x16(r[i & 1]);
     if (i + 1 < 4) tmem_ld_32x32b_x16(e.tbase + (i + 1) * CHUNK, r[(i + 1) & 1]);
+    uint32_t packed[CHUNK / 4];
+    requant_chunk<MODE>(r[i & 1], e.row_term, reinterpret_cast<const int4 *>(e.ct_base + i * CHUNK), p, packed);
     if (i == 3) {
-      // the accumulator is in registers: hand the buffer back to the MMA warp
+      // The accumulator is in registers and the tile's terms have been read: hand the buffer
+      // (TMEM columns and term slots; the preparation warps refill the latter on the same
+      // barrier) back before the staging and the store.
       tc_fence_before_sync();
       __syncwarp();
       if (e.lane == 0) mbar_arrive(e.tempty);
     }
-    uint32_t packed[CHUNK / 4];
-    requant_chunk<MODE>(r[i & 1], e.row_term, reinterpret_cast<const int4 *>(e.ct_base + i * CHUNK), p, packed);
     if ((i & (STG - 1)) == 0) {
       // the previous store must have read the staging buffer before it is refilled
       if (e.lane == 0) bulk_wait_group_read<0>();

@@ -181,3 +181,25 @@ def test_dwconv_f32(ctx, orc, kats):
     dx, df, db, do = ctx.upload(x), ctx.upload(f), ctx.upload(bias), ctx.alloc(ref.nbytes)
     ctx.dwconv_f32(dx, df, db, do, 2, 12, 17, 15, 2, 3, 3, (2, 2), (1, 1), (0, 0), (9, 8), 1)
     assert rel_err(ctx.download(do, ref.shape, np.float32), ref) <= 1e-4
+
+
+def test_winograd_config1_full_size(ctx, orc):
+    """Input [32,64,56,56], filter [64,64,3,3], SAME: too slow for the scalar oracle as a whole,
+    so two images are checked against the oracle's direct convolution, and every image of the
+    batch-32 call against the same image run alone (the batch entries are independent)."""
+    N, C, H, W, O = 32, 64, 56, 56, 64
+    rng = np.random.Generator(np.random.PCG64(0))
+    x = rng.random((N, C, H, W), dtype=np.float32)
+    f = (rng.standard_normal((O, C, 3, 3)) * np.sqrt(2.0 / (9 * C))).astype(np.float32)
+    bias = (rng.standard_normal(O) * 0.01).astype(np.float32)
+    dx, df, db = ctx.upload(x), ctx.upload(f), ctx.upload(bias)
+    do = ctx.alloc(N * O * H * W * 4)
+    ctx.winograd_f32(dx, df, db, do, N, C, H, W, O, (1, 1), (H, W))
+    got = ctx.download(do, (N, O, H, W), np.float32)
+    for n in (0, 31):
+        ref = orc.conv2d_f32(x[n:n + 1], f, bias, (1, 1), (1, 1), (1, 1), (H, W), 0, 0.0, 0.0)
+        assert rel_err(got[n:n + 1], ref) <= 1e-3
+    d1, o1 = ctx.upload(x[17:18]), ctx.alloc(O * H * W * 4)
+    ctx.winograd_f32(d1, df, db, o1, 1, C, H, W, O, (1, 1), (H, W))
+    alone = ctx.download(o1, (1, O, H, W), np.float32)
+    assert np.array_equal(alone[0], got[17])

@@ -230,3 +230,21 @@ def test_linearity_at_full_size(ctx, orc):
         da.free()
         db.free()
     assert np.array_equal(full, parts[0] + parts[1])
+    # the requantized uint8 output of the same product (tensor-core kernel, TMA-store epilogue):
+    # sampled rows against the oracle, and every output byte as a function of the int32 result
+    case = gemm_case(orc, 0, 1, 64, 64, 64)  # only for plausible multiplier / shift / zero point
+    mult, shift, zp_c = case["mult"], 9, 128
+    out8 = ctx.alloc(M * N)
+    before = ctx.launches_tensor_core
+    ctx.gemm_u8(dA, dB, None, out8, 1, M, N, K, 128, 120, mult, shift, zp_c)
+    assert ctx.launches_tensor_core == before + 1
+    got8 = ctx.download(out8, (M, N), np.uint8)
+    exp8 = orc.gemm_u8(A[rows], B, None, 1, 16, N, K, 128, 120, mult, shift, zp_c).reshape(16, N)
+    assert np.array_equal(got8[rows], exp8)
+    requant = np.array([min(255, max(0, orc.rounding_stages(int(v), mult, shift) + zp_c))
+                        for v in np.unique(full)[::4001]], dtype=np.uint8)
+    lut = dict(zip(np.unique(full)[::4001].tolist(), requant.tolist()))
+    flat_full, flat8 = full.ravel(), got8.ravel()
+    for v, q in list(lut.items())[:200]:
+        assert (flat8[flat_full == v] == q).all()
+    assert len(np.unique(got8)) > 100
