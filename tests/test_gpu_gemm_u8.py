@@ -248,3 +248,35 @@ def test_linearity_at_full_size(ctx, orc):
     for v, q in list(lut.items())[:200]:
         assert (flat8[flat_full == v] == q).all()
     assert len(np.unique(got8)) > 100
+
+
+@pytest.mark.parametrize("N,K", [(64, 32), (128, 64), (128, 128), (256, 256), (512, 512), (1024, 96)])
+def test_pointwise_shapes_with_many_tiles_per_cta(ctx, orc, N, K):
+    """Pointwise-convolution shapes ([pixels x K] * [N x K]^T, K-major operands) large enough
+    that every persistent CTA walks through its accumulator buffers several times; sampled
+    rows against the oracle, three runs (a race shows up as run-to-run differences)."""
+    M = 148 * 128 * 3 + 77
+    rng = np.random.Generator(np.random.PCG64(N + K))
+    A = rng.integers(0, 256, size=(1, M, K), dtype=np.uint8)
+    Bt = rng.integers(1, 256, size=(1, N, K), dtype=np.uint8)  # stored [N x K] = column-major B
+    bias = np.rint(rng.normal(0, 2000, size=N)).astype(np.int32)
+    mult, shift = orc.output_multiplier_and_shift(np.float32(0.02), np.float32(0.01),
+                                                  np.float32(0.02 * 0.01 * np.sqrt(K) * 74 * 74 * 3 / 127))
+    dA, dB, db = ctx.upload(A), ctx.upload(Bt), ctx.upload(bias)
+    out = ctx.alloc(M * N)
+    rows = np.sort(rng.choice(M, size=48, replace=False))
+    rows[-1] = M - 1
+    exp = orc.gemm_u8(np.ascontiguousarray(A[:, rows]), Bt, bias, 1, len(rows), N, K, 0, 131, mult, shift, 0,
+                      b_col_major=True).reshape(len(rows), N)
+    first = None
+    for _ in range(3):
+        ctx.gemm_u8(dA, dB, db, out, 1, M, N, K, 0, 131, mult, shift, 0, b_col_major=True)
+        got = ctx.download(out, (M, N), np.uint8)
+        assert np.array_equal(got[rows], exp)
+        if first is None:
+            first = got
+        else:
+            assert np.array_equal(got, first)
+    assert len(np.unique(first)) > 50
+    for b in (dA, dB, db, out):
+        b.free()
