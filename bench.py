@@ -14,6 +14,10 @@ Workloads (``config.workload``):
                  Winograd entry point (cached transformed filter).  metric: direct-equivalent TFLOP/s.
   gemm_u8_sweep  uint8 GEMM with K = N = 4096 and M in {1, 16, 128, 4096}, the batched
                  64 x 512^3 MatMul and the 4096 x 4096 GEMV; one row per case under "cases".
+  resnet50_f32_b256  ResNet-50 v1, fp32 NCHW, 224x224, batch 256 per GPU (--batch changes it),
+                 He-normal seeded weights, through the C++ host engine: 3x3 convolutions by
+                 Winograd, 1x1 by GEMM, stem and stride-2 1x1 by im2col + GEMM, pooling, residual
+                 sums and activations on the device.  metric: images/s.
 
 One "step" is one pass of the hot path over one batch of synthetic, seeded input.  `value`
 is measured with the inputs resident in HBM, `e2e` through the host-buffer entry point with
@@ -651,6 +655,145 @@ def run_winograd(args, rank, world):
 
 
 # --------------------------------------------------------------------------------------
+# workload: ResNet-50 v1, fp32 NCHW, batch 256 per GPU
+# --------------------------------------------------------------------------------------
+
+def resnet_kind(node):
+    if node["op"] == "conv":
+        if node["k"] == 7:
+            return "stem 7x7 s2 (im2col + gemm_f32_tc_kernel)"
+        if node["k"] == 3:
+            return "3x3 s1 (Winograd: wino_input + gemm_f32_tc_kernel + wino_output)"
+        if node["stride"] == 2:
+            return "1x1 s2 (im2col + gemm_f32_tc_kernel)"
+        return "1x1 s1 (gemm_f32_tc_kernel)"
+    return {"maxpool": "max pool", "avgpool": "avg pool", "add": "eltwise sum", "relu": "activation",
+            "fc": "fully connected"}[node["op"]]
+
+
+def run_resnet(args, rank, world):
+    import mace_b200  # noqa: F401  (fails loudly when the device library is missing)
+    from mace_b200 import hostapi
+    from oracle import pyoracle as orc  # cpu_baseline leg only
+    import resnet50 as rn
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    dist = init_dist(world, local)
+    batch = args.batch or 256
+    nodes, weights = rn.build(seed=0)
+    eng = rn.build_engine(hostapi, nodes, weights, batch, device=local)
+    ctx = RawContext(eng.context)
+    x = rn.random_images(batch, seed=100 + rank)
+    hin = ctx.pinned(x.nbytes)
+    hin[:] = x.view(np.uint8).ravel()
+    hout = ctx.pinned(batch * rn.NUM_CLASSES * 4)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    eng.write("input", x)
+    for i in range(max(args.warmup, 3)):
+        eng.run(sync=False)
+    if not args.no_graph:
+        eng.sync()
+        eng.capture()
+        eng.run(sync=False)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.01)
+    l0, ltc0 = ctx.launches, ctx.launches_tensor_core
+    e0, e1 = ctx.event(), ctx.event()
+    ctx.record(e0)
+    for i in range(args.steps):
+        eng.run(sync=False)
+    ctx.record(e1)
+    ms = ctx.elapsed_ms(e0, e1)
+    barrier()
+    launches, launches_tc = ctx.launches - l0, ctx.launches_tensor_core - ltc0
+    clocks = sampler.stop() if rank == 0 else None
+    if args.profile:
+        eng.close()
+        return None
+    kinds = {n["name"]: resnet_kind(n) for n in nodes}
+    fam = {}
+    prof_runs = 3
+    for _ in range(prof_runs):
+        for label, t in eng.run_profiled(max_ops=512):
+            k = kinds.get(label.split(":", 1)[-1], label)
+            fam[k] = fam.get(k, 0.0) + t / prof_runs
+
+    def e2e_step():
+        eng.run_host("input", hin, "fc", hout)
+        if dist is not None:
+            from mace_b200.sharding import gather_rows
+            gather_rows(dist, hout.view(np.float32).reshape(batch, rn.NUM_CLASSES), batch * world, device="cuda")
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    ctx.record(e0)
+    for _ in range(e2e_steps):
+        e2e_step()
+    ctx.record(e1)
+    e2e_ms = ctx.elapsed_ms(e0, e1)
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max(e2e_ms, e2e_wall_ms) if dist is not None else e2e_ms
+    barrier()
+    ms, e2e_ms = max_over_ranks(dist, [ms, e2e_ms])
+    result = None
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_per_step = ms / args.steps
+        macs = rn.macs_per_image(nodes)
+        value = world * batch / (ms_per_step * 1e-3)
+        tflops = 2.0 * macs * batch / (ms_per_step * 1e-3) / 1e12
+        tf32_peak = peaks["bf16_tflops"] / 2.0
+        alg_bytes = rn.activation_bytes(nodes, batch)
+        result = {
+            "metric": "fp32_resnet50_images_per_s", "value": round(value, 1), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "resnet50_f32_b256", "batch_per_gpu": batch, "global_batch": batch * world,
+                       "image": "224x224x3 fp32 NCHW", "weights": "He-normal, seed 0",
+                       "macs_per_image": macs,
+                       "parallelism": "dp%d: batch sharded, weights replicated, final logits gather only" % world,
+                       "launch": "operator by operator" if args.no_graph else "CUDA graph replay",
+                       "l2": "activations of one step (%.1f GB) exceed L2" % (alg_bytes / 1e9)},
+            "roofline": {"bound": "tensor", "achieved": round(tflops, 2), "peak": round(tf32_peak, 1),
+                         "unit": "TFLOP/s", "frac": round(tflops / tf32_peak, 4), "traffic": None,
+                         "peak_source": "half the %s bf16 GEMM rate (dense tf32); the fp32 GEMMs run three "
+                                        "tf32 MMAs per product (hi/lo split), so a third of it is the ceiling "
+                                        "for direct-equivalent flops outside Winograd" % peaks["source"],
+                         "kernel": "whole step (gemm_f32_tc_kernel dominates)",
+                         "direct_equivalent_flops_per_step": 2.0 * macs * batch},
+            "model_hbm": {"algorithmic_bytes_per_step": alg_bytes,
+                          "achieved_gbs": round(alg_bytes / (ms_per_step * 1e-3) / 1e9, 1),
+                          "frac_of_peak": round(alg_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)},
+            "operator_kinds_ms": {k: round(v, 4) for k, v in sorted(fam.items(), key=lambda kv: -kv[1])},
+            "e2e": {"value": round(world * batch / (e2e_ms / e2e_steps * 1e-3), 1), "unit": "images/s",
+                    "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": batch * rn.NUM_CLASSES * 4},
+            "gpu_launches": launches, "gpu_launches_tensor_core": launches_tc, "clocks": clocks,
+        }
+        threads = orc.set_threads(0)
+        sample_n = 2
+        t0 = time.perf_counter()
+        rn.oracle_forward(orc, nodes, weights, x[:sample_n])
+        dt = time.perf_counter() - t0
+        result["cpu_baseline"] = {"value": round(sample_n / dt, 3), "unit": "images/s", "cores": threads,
+                                  "kind": "port", "sample": "%d images, one pass (direct fp32 convolutions)" % sample_n}
+    eng.close()
+    if dist is not None:
+        dist.destroy_process_group()
+    return result
+
+
+# --------------------------------------------------------------------------------------
 # workload: uint8 GEMM / GEMV sweep, K = N = 4096, M in {1, 16, 128, 4096}, batched 64 x 512^3
 # --------------------------------------------------------------------------------------
 
@@ -782,7 +925,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mobilenet_v1_u8_b64",
-                    choices=["mobilenet_v1_u8_b64", "gemm_u8_4096", "winograd_f32_cfg1", "gemm_u8_sweep"])
+                    choices=["mobilenet_v1_u8_b64", "gemm_u8_4096", "winograd_f32_cfg1", "gemm_u8_sweep",
+                             "resnet50_f32_b256"])
+    ap.add_argument("--batch", type=int, default=0, help="images per GPU for resnet50_f32_b256 (default 256)")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every operator separately instead of replaying a CUDA graph")
     ap.add_argument("--profile", action="store_true",
@@ -798,6 +943,8 @@ def main():
         res = run_winograd(args, rank, world)
     elif args.workload == "gemm_u8_sweep":
         res = run_sweep(args, rank, world)
+    elif args.workload == "resnet50_f32_b256":
+        res = run_resnet(args, rank, world)
     else:
         res = run_mobilenet(args, rank, world)
     if rank == 0 and res is not None:

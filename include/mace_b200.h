@@ -84,9 +84,12 @@ int mb_graph_destroy(mb_context *ctx, void *graph_exec);
  * counts only tcgen05 tensor-core GEMM launches. */
 uint64_t mb_launch_count(const mb_context *ctx);
 uint64_t mb_launch_count_tensor_core(const mb_context *ctx);
-/* Options for A/B tests: "tensor_cores" (1 default; 0 forces the CUDA-core
- * GEMM), "mn_major" (1 default; 0 transposes MN-major operands to K-major
- * in scratch instead of describing them to the tensor core directly). */
+/* Options: "tensor_cores" (1 default; 0 forces the CUDA-core GEMM, for A/B
+ * tests), "mn_major" (1 default; 0 transposes MN-major operands to K-major
+ * in scratch instead of describing them to the tensor core directly),
+ * "col_budget_mb" (1024 default: the fp32 general convolution gathers the
+ * im2col columns of as many images at a time as fit into this many MiB of
+ * scratch). */
 int mb_set_option(mb_context *ctx, const char *name, int value);
 
 /* ---- uint8 GEMM: replaces the gemmlowp calls of MatMulOp<RT_CPU,uint8_t>
@@ -237,6 +240,46 @@ int mb_conv3x3_winograd_f32_nchw(mb_context *ctx, const float *in,
                                  int pad_top, int pad_left, int64_t Ho,
                                  int64_t Wo, int activation, float max_limit,
                                  float coefficient, int tile_override);
+
+/* ---- fp32 operators between the convolutions of a float network -----------
+ * They keep activations on the device from the first convolution to the
+ * logits. */
+
+/* MAX / AVG pooling, NCHW: replaces PoolingOp<RT_CPU,float>::MaxPooling /
+ * AvgPooling (mace/ops/pooling.cc:128-240).  pooling_type is ops::PoolingType
+ * (mace/ops/common/pooling_type.h:20-23): 1 AVG, 2 MAX.  Taps outside the
+ * image are skipped; AVG divides by the number of in-bounds taps. */
+int mb_pooling_f32_nchw(mb_context *ctx, const float *in, float *out, int64_t N,
+                        int64_t C, int64_t H, int64_t W, int64_t KH, int64_t KW,
+                        int stride_h, int stride_w, int dil_h, int dil_w,
+                        int pad_top, int pad_left, int64_t Ho, int64_t Wo,
+                        int pooling_type);
+
+/* Element-wise op on two tensors of the same shape, or (in1 == NULL) on a
+ * tensor and scalar_input: replaces TensorEltwise / TensorScalarEltwise
+ * (mace/ops/eltwise.cc:419-700).  type is ops::EltwiseType (mace/ops/common/
+ * eltwise_type.h:21-38); built here: SUM 0 (has_coeff: in0 * coeff0 + in1 *
+ * coeff1), SUB 1, PROD 2, DIV 3, MIN 4, MAX 5, NEG 6, ABS 7, SQR_DIFF 8,
+ * CLIP 12 (coeff0 <= x <= coeff1); other types return MB_UNSUPPORTED.
+ * swapped has the operator's meaning: the caller exchanged the operands, so
+ * SUB and DIV compute in1 - in0 and in1 / in0 and SUM exchanges its
+ * coefficients. */
+int mb_eltwise_f32(mb_context *ctx, const float *in0, const float *in1,
+                   float *out, int64_t size, int type, float scalar_input,
+                   int has_coeff, float coeff0, float coeff1, int swapped);
+
+/* Standalone activation: replaces ref::Activation / arm::Activation
+ * (mace/ops/ref/activation.cc:61-88) for the activation codes listed above.
+ * in == out is allowed. */
+int mb_activation_f32(mb_context *ctx, const float *in, float *out, int64_t size,
+                      int activation, float max_limit, float coefficient);
+
+/* Softmax over the middle dimension of [outer, classes, inner]: replaces
+ * SoftmaxOp<RT_CPU,float> (mace/ops/softmax.cc:76-290): NCHW over channels is
+ * (N, C, H*W); a 2-D or NHWC tensor is (rows, classes, 1).  use_log gives
+ * log(softmax). */
+int mb_softmax_f32(mb_context *ctx, const float *in, float *out, int64_t outer,
+                   int64_t classes, int64_t inner, int use_log);
 
 /* ---- uint8 GEMM without any allocation ------------------------------------
  * No counterpart in the reference.  For callers that may not allocate device

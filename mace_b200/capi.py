@@ -77,6 +77,10 @@ PROTOTYPES = {
     "mb_winograd_transform_filter_f32": (_int, [_vp] * 3 + [_i64] * 2 + [_int]),
     "mb_conv3x3_winograd_f32_nchw": (_int, [_vp] * 6 + [_i64] * 5 + [_int] * 2 + [_i64] * 2 +
                                      [_int, _f32, _f32, _int]),
+    "mb_pooling_f32_nchw": (_int, [_vp] * 3 + [_i64] * 6 + [_int] * 6 + [_i64] * 2 + [_int]),
+    "mb_eltwise_f32": (_int, [_vp] * 4 + [_i64, _int, _f32, _int, _f32, _f32, _int]),
+    "mb_activation_f32": (_int, [_vp] * 3 + [_i64, _int, _f32, _f32]),
+    "mb_softmax_f32": (_int, [_vp] * 3 + [_i64] * 3 + [_int]),
     "mb_gemm_u8_static_scratch": (_int, [_vp] * 5 + [_int] + [_i64] * 3 + [_int] * 2 +
                                   [_i32] * 5 + [_int, C.c_char_p, _sz]),
 }
@@ -302,6 +306,24 @@ class Context:
 
     def winograd_transform_filter(self, f, out, Cc, O, tile):
         self._check(lib().mb_winograd_transform_filter_f32(self.h, f.ptr, out.ptr, Cc, O, tile))
+
+    def pooling_f32(self, x, out, N, Cc, H, W, kernel, strides, dil, pad_tl, out_hw, pooling_type):
+        self._check(lib().mb_pooling_f32_nchw(
+            self.h, x.ptr, out.ptr, N, Cc, H, W, kernel[0], kernel[1], strides[0], strides[1],
+            dil[0], dil[1], pad_tl[0], pad_tl[1], out_hw[0], out_hw[1], pooling_type))
+
+    def eltwise_f32(self, a, b, out, size, type_, coeff=None, swapped=False, scalar=1.0):
+        c = coeff if coeff else (0.0, 0.0)
+        self._check(lib().mb_eltwise_f32(
+            self.h, a.ptr, b.ptr if b is not None else None, out.ptr, size, type_, scalar,
+            1 if coeff else 0, c[0], c[1], 1 if swapped else 0))
+
+    def activation_f32(self, x, out, size, act, max_limit=0.0, coef=0.0):
+        self._check(lib().mb_activation_f32(self.h, x.ptr, out.ptr, size, act, max_limit, coef))
+
+    def softmax_f32(self, x, out, outer, classes, inner, use_log=False):
+        self._check(lib().mb_softmax_f32(self.h, x.ptr, out.ptr, outer, classes, inner,
+                                         1 if use_log else 0))
 
     def avgpool_u8(self, x, out, N, H, W, Cc, kernel, strides, pad_tl, out_hw):
         self._check(lib().mb_avgpool_u8_nhwc(

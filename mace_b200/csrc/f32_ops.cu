@@ -171,6 +171,53 @@ __global__ void __launch_bounds__(256) dwconv_f32_kernel(const ConvF32Params p) 
   p.out[tid] = mb_activate(sum, p.act, p.max_limit, p.coef);
 }
 
+// ---- im2col for the tensor-core route of the general convolution --------------------------
+// col[k][...] with k = (c * KH + kh) * KW + kw, the order of an OIHW filter row.  Two layouts:
+// per image (col_ns = K * col_rs: image n owns a [K x positions] matrix) and merged
+// (col_ns = positions per image: the images of a chunk lie side by side in one
+// [K x images * positions] matrix, which keeps 128-position tiles full when an image has few).
+struct ColF32Params {
+  const float *in;  // first image of the chunk
+  float *col;
+  int C, H, W, KH, KW, sh, sw, dh, dw, pad_t, pad_l, Ho, Wo, hw;
+  int64_t col_rs, col_ns;
+};
+
+__global__ void __launch_bounds__(256) im2col_f32_kernel(const ColF32Params p) {
+  const int pos = blockIdx.x * 256 + threadIdx.x;
+  if (pos >= p.hw) return;
+  const int k = blockIdx.y, n = blockIdx.z;
+  const int kw = k % p.KW, kh = (k / p.KW) % p.KH, c = k / (p.KW * p.KH);
+  const int h = pos / p.Wo, w = pos - h * p.Wo;
+  const int ih = h * p.sh - p.pad_t + kh * p.dh, iw = w * p.sw - p.pad_l + kw * p.dw;
+  float v = 0.f;
+  if (ih >= 0 && ih < p.H && iw >= 0 && iw < p.W)
+    v = __ldg(p.in + ((static_cast<int64_t>(n) * p.C + c) * p.H + ih) * p.W + iw);
+  p.col[k * p.col_rs + n * p.col_ns + pos] = v;
+}
+
+// rows of K floats -> rows of Kp floats (a 16-byte multiple, which a tensor map's strides need)
+__global__ void __launch_bounds__(256)
+repack_rows_f32_kernel(const float *__restrict__ src, float *__restrict__ dst, int64_t rows, int K, int Kp) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= rows * Kp) return;
+  const int k = static_cast<int>(i % Kp);
+  dst[i] = k < K ? __ldg(src + (i / Kp) * K + k) : 0.f;
+}
+
+// merged product [O][images * hw] (row stride src_rs) -> NCHW images
+__global__ void __launch_bounds__(256)
+unmerge_f32_kernel(const float *__restrict__ src, float *__restrict__ dst, int64_t total, int O, int hw,
+                   int64_t src_rs) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= total) return;
+  const int pos = static_cast<int>(i % hw);
+  const int64_t r = i / hw;
+  const int o = static_cast<int>(r % O);
+  const int64_t n = r / O;
+  dst[i] = __ldg(src + o * src_rs + n * hw + pos);
+}
+
 }  // namespace
 
 // Strided batched fp32 GEMM with optional per-row bias and activation; the
@@ -200,6 +247,74 @@ int mb_gemm_f32_strided(mb_context *ctx, const float *A, const float *B, float *
   gemm_f32_kernel<<<grid, 256, 0, ctx->stream>>>(p);
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
+  return MB_SUCCESS;
+}
+
+// General convolution as im2col + GEMM (the tensor-core kernel when the shapes allow it).
+// Images are processed in chunks so that the column matrix stays below the context's budget
+// (1 GiB unless the option col_budget_mb changes it).
+static int conv2d_f32_im2col(mb_context *ctx, const float *in, const float *filter, const float *bias,
+                             float *out, int64_t N, int64_t C, int64_t H, int64_t W, int64_t O,
+                             int64_t KH, int64_t KW, int sh, int sw, int dh, int dw, int pad_t,
+                             int pad_l, int64_t Ho, int64_t Wo, int act, float max_limit, float coef) {
+  const int64_t K = C * KH * KW, hw = Ho * Wo;
+  const int64_t Kp = (K + 3) / 4 * 4;
+  const bool merged = (hw % 4 != 0) || hw < 128;
+  const int64_t hwp = (hw + 3) / 4 * 4;
+  const int64_t per_image = K * (merged ? hw : hwp) * 4;
+  int64_t chunk = std::max<int64_t>(1, std::min<int64_t>(N, ctx->col_budget_bytes / std::max<int64_t>(per_image, 1)));
+  chunk = std::min<int64_t>(chunk, 65535);
+  const bool repack = (K % 4 != 0) || (reinterpret_cast<uintptr_t>(filter) & 15u);
+  const int64_t merged_rs = (chunk * hw + 3) / 4 * 4;
+  size_t off = 0;
+  const size_t off_f = off; off += repack ? align_up(sizeof(float) * O * Kp, 256) : 0;
+  const size_t off_col = off; off += align_up(sizeof(float) * K * (merged ? merged_rs : chunk * hwp), 256);
+  const size_t off_c2 = off; off += merged ? align_up(sizeof(float) * O * merged_rs, 256) : 0;
+  uint8_t *scratch = nullptr;
+  MB_RETURN_IF_ERROR(mb_scratch(ctx, off, reinterpret_cast<void **>(&scratch)));
+  const float *wmat = filter;
+  int64_t w_rs = K;
+  if (repack) {
+    float *wf = reinterpret_cast<float *>(scratch + off_f);
+    repack_rows_f32_kernel<<<static_cast<unsigned>(ceil_div64(O * Kp, 256)), 256, 0, ctx->stream>>>(
+        filter, wf, O, static_cast<int>(K), static_cast<int>(Kp));
+    MB_CUDA(ctx, cudaGetLastError());
+    ctx->launches++;
+    wmat = wf;
+    w_rs = Kp;
+  }
+  float *col = reinterpret_cast<float *>(scratch + off_col);
+  float *c2 = reinterpret_cast<float *>(scratch + off_c2);
+  ColF32Params p;
+  p.col = col;
+  p.C = static_cast<int>(C); p.H = static_cast<int>(H); p.W = static_cast<int>(W);
+  p.KH = static_cast<int>(KH); p.KW = static_cast<int>(KW);
+  p.sh = sh; p.sw = sw; p.dh = dh; p.dw = dw; p.pad_t = pad_t; p.pad_l = pad_l;
+  p.Ho = static_cast<int>(Ho); p.Wo = static_cast<int>(Wo); p.hw = static_cast<int>(hw);
+  for (int64_t n0 = 0; n0 < N; n0 += chunk) {
+    const int64_t nc = std::min(chunk, N - n0);
+    p.in = in + n0 * C * H * W;
+    p.col_rs = merged ? merged_rs : hwp;
+    p.col_ns = merged ? hw : K * hwp;
+    dim3 grid(static_cast<unsigned>(ceil_div64(hw, 256)), static_cast<unsigned>(K), static_cast<unsigned>(nc));
+    im2col_f32_kernel<<<grid, 256, 0, ctx->stream>>>(p);
+    MB_CUDA(ctx, cudaGetLastError());
+    ctx->launches++;
+    float *dst = out + n0 * O * hw;
+    if (!merged) {
+      // out_n [O x hw] = filter [O x K] * col_n [K x hw]
+      MB_RETURN_IF_ERROR(mb_gemm_f32_strided(ctx, wmat, col, dst, bias, nc, O, hw, K, w_rs, 1, 0, hwp, 1,
+                                             K * hwp, hw, 1, O * hw, act, max_limit, coef));
+    } else {
+      MB_RETURN_IF_ERROR(mb_gemm_f32_strided(ctx, wmat, col, c2, bias, 1, O, nc * hw, K, w_rs, 1, 0,
+                                             merged_rs, 1, 0, merged_rs, 1, 0, act, max_limit, coef));
+      const int64_t total = nc * O * hw;
+      unmerge_f32_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, ctx->stream>>>(
+          c2, dst, total, static_cast<int>(O), static_cast<int>(hw), merged_rs);
+      MB_CUDA(ctx, cudaGetLastError());
+      ctx->launches++;
+    }
+  }
   return MB_SUCCESS;
 }
 
@@ -278,12 +393,19 @@ int mb_conv2d_f32_nchw(mb_context *ctx, const float *in, const float *filter, co
   if (empty) return MB_SUCCESS;
   MB_CUDA(ctx, cudaSetDevice(ctx->device));
   if (KH == 1 && KW == 1 && stride_h == 1 && stride_w == 1 && pad_top == 0 && pad_left == 0 &&
-      Ho == H && Wo == W) {
+      Ho == H && Wo == W && ((H * W) % 4 == 0 && H * W >= 128 || !ctx->use_tensor_cores)) {
     // out_n[O x HW] = filter[O x C] * in_n[C x HW] for every image n
     // (arm::Conv2dK1x1, mace/ops/arm/base/conv_2d_1x1.cc:61-68)
     const int64_t hw = H * W;
     return mb_gemm_f32_strided(ctx, filter, in, out, bias, N, O, hw, C, C, 1, 0, hw, 1, C * hw, hw,
                                1, O * hw, activation, max_limit, coefficient);
+  }
+  // enough work to fill tensor-core tiles: gather columns and multiply; tiny problems stay on
+  // the one-thread-per-output kernel
+  if (N * O * Ho * Wo * C * KH * KW >= (1ll << 18) && Ho * Wo * N >= 32 && C * KH * KW <= 65535 &&
+      Ho * Wo < (1ll << 30)) {
+    return conv2d_f32_im2col(ctx, in, filter, bias, out, N, C, H, W, O, KH, KW, stride_h, stride_w, dil_h,
+                             dil_w, pad_top, pad_left, Ho, Wo, activation, max_limit, coefficient);
   }
   ConvF32Params p;
   p.in = in; p.filter = filter; p.bias = bias; p.out = out;

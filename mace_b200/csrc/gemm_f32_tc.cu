@@ -409,6 +409,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // 3-D fp32 tensor map: dims {inner, rows, batch} in elements, 128-byte swizzle, zero fill.
+// Every stride must be a multiple of 16 bytes, that of a batch dimension of extent 1 too:
+// callers pass row stride x rows there.
 int make_map_f32(mb_context *ctx, CUtensorMap *map, const void *base, uint64_t inner, uint64_t rows,
                  uint64_t batch, uint64_t row_stride_elems, uint64_t batch_stride_elems,
                  uint32_t box_inner, uint32_t box_rows,
@@ -481,16 +483,16 @@ int mb_gemm_f32_tc_launch(mb_context *ctx, const float *X, const float *W, const
   p.timeline = ctx->tc_timeline;
   CUtensorMap tx, tw;
   MB_RETURN_IF_ERROR(make_map_f32(ctx, &tx, X, Mdim, K, p.x_batched ? batch : 1, x_row_stride,
-                                  p.x_batched ? x_batch_stride : Mdim * K, 32, FKB,
+                                  p.x_batched ? x_batch_stride : x_row_stride * K, 32, FKB,
                                   CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
   MB_RETURN_IF_ERROR(make_map_f32(ctx, &tw, W, K, Ndim, p.w_batched ? batch : 1, w_row_stride,
-                                  p.w_batched ? w_batch_stride : Ndim * K, FKB, BN));
+                                  p.w_batched ? w_batch_stride : w_row_stride * Ndim, FKB, BN));
   CUtensorMap tc;
   p.c_tma = ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && c_row_stride % 4 == 0 &&
              c_batch_stride % 4 == 0 && Ndim >= 16) ? 1 : 0;
   if (p.c_tma) {
     MB_RETURN_IF_ERROR(make_map_f32(ctx, &tc, C, Mdim, Ndim, batch, c_row_stride,
-                                    batch > 1 ? c_batch_stride : Mdim * Ndim, 32, 16,
+                                    batch > 1 ? c_batch_stride : c_row_stride * Ndim, 32, 16,
                                     CU_TENSOR_MAP_SWIZZLE_NONE));
   } else {
     memset(&tc, 0, sizeof(tc));

@@ -192,6 +192,13 @@ int mbh_op_arg_ints(mbh_engine *e, const char *key, int count, const int *values
   return MaceStatus::MACE_SUCCESS;
 }
 
+int mbh_op_arg_floats(mbh_engine *e, const char *key, int count, const float *values) {
+  if (e == nullptr || !e->building || key == nullptr || count < 0 || (count > 0 && values == nullptr))
+    return MaceStatus::MACE_INVALID_ARGS;
+  e->pending.floats[key] = std::vector<float>(values, values + count);
+  return MaceStatus::MACE_SUCCESS;
+}
+
 int mbh_op_arg_float(mbh_engine *e, const char *key, float value) {
   if (e == nullptr || !e->building || key == nullptr) return MaceStatus::MACE_INVALID_ARGS;
   e->pending.f[key] = value;

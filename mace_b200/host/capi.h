@@ -47,6 +47,7 @@ int mbh_op_output(mbh_engine *engine, const char *tensor_name, int data_type, fl
                   int32_t zero_point);
 int mbh_op_arg_int(mbh_engine *engine, const char *key, int value);
 int mbh_op_arg_ints(mbh_engine *engine, const char *key, int count, const int *values);
+int mbh_op_arg_floats(mbh_engine *engine, const char *key, int count, const float *values);
 int mbh_op_arg_float(mbh_engine *engine, const char *key, float value);
 int mbh_op_arg_str(mbh_engine *engine, const char *key, const char *value);
 int mbh_op_end(mbh_engine *engine);

@@ -40,6 +40,13 @@ std::vector<int> Operation::GetRepeatedArgs<int>(const std::string &name,
   return it == operator_def_->ints.end() ? default_value : it->second;
 }
 
+template <>
+std::vector<float> Operation::GetRepeatedArgs<float>(const std::string &name,
+                                                     const std::vector<float> &default_value) const {
+  auto it = operator_def_->floats.find(name);
+  return it == operator_def_->floats.end() ? default_value : it->second;
+}
+
 MaceStatus Operation::Init(OpConstructContext *context) {
   Workspace *ws = context->workspace();
   for (const std::string &name : operator_def_->input) {
@@ -115,6 +122,9 @@ template <RuntimeType D, class T> class DepthwiseConv2dOp;
 template <RuntimeType D, class T> class MatMulOp;
 template <RuntimeType D, class T> class FullyConnectedOp;
 template <RuntimeType D, class T> class PoolingOp;
+template <RuntimeType D, class T> class EltwiseOp;
+template <RuntimeType D, class T> class ActivationOp;
+template <RuntimeType D, class T> class SoftmaxOp;
 
 template <>
 class Conv2dOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
@@ -485,6 +495,164 @@ class PoolingOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
   RoundType round_type_;
 };
 
+// fp32 Pooling, NCHW (mace/ops/pooling.cc:46-126): MAX and AVG, output size from the padding
+// type or from explicit paddings with round_mode (CEIL unless the arg says FLOOR).
+template <>
+class PoolingOp<RuntimeType::RT_CUDA, float> : public ConvPool2dOpBase {
+ public:
+  explicit PoolingOp(OpConstructContext *context)
+      : ConvPool2dOpBase(context),
+        kernels_(GetRepeatedArgs<int>("kernels")),
+        pooling_type_(static_cast<PoolingType>(GetOptionalArg<int>("pooling_type", static_cast<int>(AVG)))),
+        round_type_(static_cast<RoundType>(GetOptionalArg<int>("round_mode", static_cast<int>(CEIL)))) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0);
+    Tensor *output = Output(0);
+    if (input->dim_size() != 4) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Pooling input must be NCHW");
+    if (kernels_.size() != 2 || strides_.size() != 2)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "kernels and strides must have 2 values");
+    if (pooling_type_ != AVG && pooling_type_ != MAX)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "unknown pooling type");
+    index_t out_h = 0, out_w = 0;
+    std::vector<int> paddings(2);
+    if (paddings_.empty()) {
+      MACE_RETURN_IF_ERROR(CalcPaddingAndOutputSize(input->dim(2), input->dim(3), kernels_[0], kernels_[1],
+                                                    dilations_.data(), strides_.data(), padding_type_,
+                                                    &out_h, &out_w, paddings.data()));
+    } else {
+      paddings = paddings_;
+      CalcOutputSize(input->dim(2), input->dim(3), kernels_[0], kernels_[1], paddings.data(),
+                     dilations_.data(), strides_.data(), round_type_, &out_h, &out_w);
+    }
+    MACE_RETURN_IF_ERROR(output->Resize({input->dim(0), input->dim(1), out_h, out_w}));
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    // pad_hw = paddings / 2 (pooling.cc:104-105)
+    return rt->Status(mb_pooling_f32_nchw(rt->ctx(), input->memory<float>(), output->mutable_memory<float>(),
+                                          input->dim(0), input->dim(1), input->dim(2), input->dim(3),
+                                          kernels_[0], kernels_[1], strides_[0], strides_[1], dilations_[0],
+                                          dilations_[1], paddings[0] / 2, paddings[1] / 2, out_h, out_w,
+                                          static_cast<int>(pooling_type_)));
+  }
+
+ private:
+  std::vector<int> kernels_;
+  PoolingType pooling_type_;
+  RoundType round_type_;
+};
+
+// fp32 Eltwise (mace/ops/eltwise.cc:949-1144) for the two forms a float network's residual
+// adds and scalings use: two inputs of the same size, or one input and the scalar_input arg.
+// Broadcasting between different shapes returns MACE_UNSUPPORTED.
+template <>
+class EltwiseOp<RuntimeType::RT_CUDA, float> : public Operation {
+ public:
+  explicit EltwiseOp(OpConstructContext *context)
+      : Operation(context),
+        type_(GetOptionalArg<int>("type", 14 /* NONE */)),
+        coeff_(GetRepeatedArgs<float>("coeff")),
+        scalar_input_(GetOptionalArg<float>("scalar_input", 1.0f)),
+        scalar_input_index_(GetOptionalArg<int>("scalar_input_index", 1)) {}
+
+  MaceStatus Run(OpContext *context) override {
+    if (InputSize() >= 3)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Element-Wise does not support 3 or higher inputs");
+    const Tensor *input0 = Input(0);
+    const Tensor *input1 = InputSize() == 2 ? Input(1) : nullptr;
+    if (type_ == 12 /* CLIP */ && !(coeff_.size() == 2 && coeff_[0] < coeff_[1]))
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Clip's min/max values are not correct.");
+    if (!coeff_.empty() && coeff_.size() != 2)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "coeff must have 2 values");
+    bool swapped = false;
+    if (input1 != nullptr) {
+      // the larger operand leads (eltwise.cc:1004-1010)
+      if (input0->dim_size() < input1->dim_size() ||
+          (input0->dim_size() == input1->dim_size() && input0->size() < input1->size())) {
+        std::swap(input0, input1);
+        swapped = true;
+      }
+      if (input0->size() != input1->size())
+        return MaceStatus(MaceStatus::MACE_UNSUPPORTED, "Eltwise broadcasting is not built for the CUDA runtime");
+    }
+    if (scalar_input_index_ == 0) swapped = !swapped;
+    Tensor *output = Output(0);
+    MACE_RETURN_IF_ERROR(output->Resize(input0->shape()));
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    return rt->Status(mb_eltwise_f32(rt->ctx(), input0->memory<float>(),
+                                     input1 != nullptr ? input1->memory<float>() : nullptr,
+                                     output->mutable_memory<float>(), input0->size(), type_, scalar_input_,
+                                     coeff_.empty() ? 0 : 1, coeff_.empty() ? 0.f : coeff_[0],
+                                     coeff_.empty() ? 0.f : coeff_[1], swapped ? 1 : 0));
+  }
+
+ private:
+  int type_;
+  std::vector<float> coeff_;
+  float scalar_input_;
+  int scalar_input_index_;
+};
+
+// fp32 Activation (mace/ops/activation.cc:36-79); PRELU (an alpha input) is not built.
+template <>
+class ActivationOp<RuntimeType::RT_CUDA, float> : public Operation {
+ public:
+  explicit ActivationOp(OpConstructContext *context)
+      : Operation(context),
+        activation_name_(GetOptionalArg<std::string>("activation", "NOOP")),
+        max_limit_(GetOptionalArg<float>("max_limit", 0.0f)),
+        coefficient_(GetOptionalArg<float>("activation_coefficient", 0.0f)) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0);
+    Tensor *output = Output(0);
+    MaceStatus st;
+    const ActivationType act = StringToActivationType(activation_name_, &st);
+    MACE_RETURN_IF_ERROR(st);
+    MACE_RETURN_IF_ERROR(output->Resize(input->shape()));
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    return rt->Status(mb_activation_f32(rt->ctx(), input->memory<float>(), output->mutable_memory<float>(),
+                                        input->size(), static_cast<int>(act), max_limit_, coefficient_));
+  }
+
+ private:
+  std::string activation_name_;
+  float max_limit_, coefficient_;
+};
+
+// fp32 Softmax (mace/ops/softmax.cc:249-290): over the channels of an NCHW tensor when the
+// op has a data format and axis 1, otherwise over the last dimension.
+template <>
+class SoftmaxOp<RuntimeType::RT_CUDA, float> : public Operation {
+ public:
+  explicit SoftmaxOp(OpConstructContext *context)
+      : Operation(context),
+        use_log_(GetOptionalArg<bool>("use_log", false)),
+        has_df_(GetOptionalArg<int>("has_data_format", 0) != 0),
+        axis_(GetOptionalArg<int>("axis", 1)) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0);
+    Tensor *output = Output(0);
+    if (input->dim_size() < 2) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "The input->dim_size() >= 2 failed.");
+    MACE_RETURN_IF_ERROR(output->Resize(input->shape()));
+    index_t outer, classes, inner;
+    if (input->dim_size() == 4 && has_df_ && axis_ == 1) {
+      outer = input->dim(0); classes = input->dim(1); inner = input->dim(2) * input->dim(3);
+    } else {
+      classes = input->dim(input->dim_size() - 1);
+      outer = classes > 0 ? input->size() / classes : 0;
+      inner = 1;
+    }
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    return rt->Status(mb_softmax_f32(rt->ctx(), input->memory<float>(), output->mutable_memory<float>(), outer,
+                                     classes, inner, use_log_ ? 1 : 0));
+  }
+
+ private:
+  bool use_log_, has_df_;
+  int axis_;
+};
+
 #define MACE_REGISTER_OP(registry, op_type, class_name, runtime, dt)                             \
   registry->Register(op_type, runtime, DataTypeToEnum<dt>::value,                                \
                      [](OpConstructContext *context) -> std::unique_ptr<Operation> {             \
@@ -501,6 +669,10 @@ void RegisterAllCudaOps(OpRegistry *registry) {
   MACE_REGISTER_OP(registry, "DepthwiseConv2d", DepthwiseConv2dOp, RuntimeType::RT_CUDA, float);
   MACE_REGISTER_OP(registry, "MatMul", MatMulOp, RuntimeType::RT_CUDA, float);
   MACE_REGISTER_OP(registry, "FullyConnected", FullyConnectedOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "Pooling", PoolingOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "Eltwise", EltwiseOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "Activation", ActivationOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "Softmax", SoftmaxOp, RuntimeType::RT_CUDA, float);
 }
 
 }  // namespace ops

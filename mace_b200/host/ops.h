@@ -34,6 +34,7 @@ struct OperatorDef {
   std::map<std::string, std::vector<int>> ints;   // "strides", "dilations", "padding_values", "kernels"
   std::map<std::string, int> i;                   // "padding", "transpose_a", "T", "pooling_type", ...
   std::map<std::string, float> f;                 // "max_limit", ...
+  std::map<std::string, std::vector<float>> floats;  // "coeff"
   std::map<std::string, std::string> s;           // "activation"
   std::vector<DataType> output_type;
   std::vector<QuantizeActivationInfo> quantize_info;

@@ -35,6 +35,7 @@ _PROTOS = {
     "mbh_op_output": [_vp, _cp, _int, _f32, _i32],
     "mbh_op_arg_int": [_vp, _cp, _int],
     "mbh_op_arg_ints": [_vp, _cp, _int, C.POINTER(_int)],
+    "mbh_op_arg_floats": [_vp, _cp, _int, C.POINTER(C.c_float)],
     "mbh_op_arg_float": [_vp, _cp, _f32],
     "mbh_op_arg_str": [_vp, _cp, _cp],
     "mbh_op_end": [_vp],
@@ -132,7 +133,7 @@ class HostEngine:
 
     # -- operators ----------------------------------------------------------------
     def op(self, type_, name, inputs, outputs, T=DT_UINT8, out_dtype=None, out_quant=None,
-           ints=None, i=None, f=None, s=None):
+           ints=None, i=None, f=None, s=None, floats=None):
         """Adds one operator; the keyword groups are the typed args of an OperatorDef."""
         L = lib()
         self._check(L.mbh_op_begin(self.h, type_.encode(), name.encode()))
@@ -148,6 +149,9 @@ class HostEngine:
         for k, v in (ints or {}).items():
             arr = (C.c_int * len(v))(*v)
             self._check(L.mbh_op_arg_ints(self.h, k.encode(), len(v), arr))
+        for k, v in (floats or {}).items():
+            arr = (C.c_float * len(v))(*v)
+            self._check(L.mbh_op_arg_floats(self.h, k.encode(), len(v), arr))
         for k, v in (f or {}).items():
             self._check(L.mbh_op_arg_float(self.h, k.encode(), float(v)))
         for k, v in (s or {}).items():

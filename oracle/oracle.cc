@@ -890,4 +890,98 @@ int orc_conv3x3_winograd_f32_nchw(const float *in, const float *filter,
   return 0;
 }
 
+int orc_pooling_f32_nchw(const float *in, float *out, int64_t N, int64_t C, int64_t H, int64_t W,
+                         int64_t KH, int64_t KW, int stride_h, int stride_w, int dil_h, int dil_w,
+                         int pad_top, int pad_left, int64_t Ho, int64_t Wo, int pooling_type) {
+  if (pooling_type != 1 && pooling_type != 2) return 1;
+  parallel_for(N * C, [&](int64_t pb, int64_t pe) {
+    for (int64_t pl = pb; pl < pe; ++pl) {
+      const float *ip = in + pl * H * W;
+      float *op = out + pl * Ho * Wo;
+      for (int64_t h = 0; h < Ho; ++h)
+        for (int64_t w = 0; w < Wo; ++w) {
+          // MaxPooling: res = lowest(), max over in-bounds taps (pooling.cc:150-170);
+          // AvgPooling: sum over in-bounds taps / their count (pooling.cc:213-236)
+          float res = pooling_type == 2 ? std::numeric_limits<float>::lowest() : 0.f;
+          int block_size = 0;
+          for (int64_t fh = 0; fh < KH; ++fh)
+            for (int64_t fw = 0; fw < KW; ++fw) {
+              const int64_t inh = h * stride_h + dil_h * fh - pad_top;
+              const int64_t inw = w * stride_w + dil_w * fw - pad_left;
+              if (inh < 0 || inh >= H || inw < 0 || inw >= W) continue;
+              const float v = ip[inh * W + inw];
+              if (pooling_type == 2) res = std::max(res, v);
+              else res += v;
+              ++block_size;
+            }
+          if (pooling_type == 1) res = block_size > 0 ? res / block_size : 0.f;
+          op[h * Wo + w] = res;
+        }
+    }
+  });
+  return 0;
+}
+
+int orc_eltwise_f32(const float *in0, const float *in1, float *out, int64_t size, int type,
+                    float scalar_input, int has_coeff, float coeff0, float coeff1, int swapped) {
+  // TensorEltwise / TensorScalarEltwise (mace/ops/eltwise.cc:419-700); in1 == NULL is the
+  // tensor-scalar form.
+  float c0 = coeff0, c1 = coeff1;
+  if (swapped && type == 0) std::swap(c0, c1);
+  for (int64_t i = 0; i < size; ++i) {
+    const float a = in0[i], b = in1 != nullptr ? in1[i] : scalar_input;
+    float r;
+    switch (type) {
+      case 0: {
+        if (has_coeff) {
+          volatile float p0 = a * c0, p1 = b * c1;  // two rounded products, then the sum
+          r = p0 + p1;
+        } else {
+          r = a + b;
+        }
+        break;
+      }
+      case 1: r = swapped ? b - a : a - b; break;
+      case 2: r = a * b; break;
+      case 3: r = swapped ? b / a : a / b; break;
+      case 4: r = std::min(a, b); break;
+      case 5: r = std::max(a, b); break;
+      case 6: r = -a; break;
+      case 7: r = std::fabs(a); break;
+      case 8: r = std::pow(a - b, 2.f); break;
+      case 12: r = std::fmax(coeff0, std::fmin(coeff1, a)); break;
+      default: return 1;
+    }
+    out[i] = r;
+  }
+  return 0;
+}
+
+int orc_activation_f32(const float *in, float *out, int64_t size, int act, float max_limit, float coef) {
+  for (int64_t i = 0; i < size; ++i) out[i] = activate(in[i], act, max_limit, coef);
+  return 0;
+}
+
+int orc_softmax_f32(const float *in, float *out, int64_t outer, int64_t classes, int64_t inner, int use_log) {
+  // SoftmaxOp<RT_CPU,float> (mace/ops/softmax.cc:76-290): per position the maximum over the
+  // classes, exp(x - max), the sum in class order, the division, then log if asked.
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      const float *ip = in + o * classes * inner + i;
+      float *op = out + o * classes * inner + i;
+      float mx = std::numeric_limits<float>::lowest();
+      for (int64_t c = 0; c < classes; ++c) mx = std::max(mx, ip[c * inner]);
+      float sum = 0.f;
+      for (int64_t c = 0; c < classes; ++c) {
+        op[c * inner] = std::exp(ip[c * inner] - mx);
+        sum += op[c * inner];
+      }
+      for (int64_t c = 0; c < classes; ++c) {
+        op[c * inner] /= sum;
+        if (use_log) op[c * inner] = std::log(op[c * inner]);
+      }
+    }
+  return 0;
+}
+
 }  // extern "C"

@@ -198,6 +198,23 @@ int orc_conv3x3_winograd_f32_nchw(const float *in, const float *filter,
                                   int64_t Wo, int act, float max_limit,
                                   float coef, int tile_override);
 
+/* PoolingOp<RT_CPU,float>::MaxPooling / AvgPooling (mace/ops/pooling.cc:128-240), NCHW;
+ * pooling_type 1 AVG, 2 MAX (mace/ops/common/pooling_type.h:20-23). */
+int orc_pooling_f32_nchw(const float *in, float *out, int64_t N, int64_t C, int64_t H, int64_t W,
+                         int64_t KH, int64_t KW, int stride_h, int stride_w, int dil_h, int dil_w,
+                         int pad_top, int pad_left, int64_t Ho, int64_t Wo, int pooling_type);
+
+/* TensorEltwise / TensorScalarEltwise (mace/ops/eltwise.cc:419-700); in1 NULL = scalar form. */
+int orc_eltwise_f32(const float *in0, const float *in1, float *out, int64_t size, int type,
+                    float scalar_input, int has_coeff, float coeff0, float coeff1, int swapped);
+
+/* ref::Activation (mace/ops/ref/activation.cc:61-88). */
+int orc_activation_f32(const float *in, float *out, int64_t size, int act, float max_limit, float coef);
+
+/* SoftmaxOp<RT_CPU,float> (mace/ops/softmax.cc:76-290) over the middle dimension of
+ * [outer, classes, inner]. */
+int orc_softmax_f32(const float *in, float *out, int64_t outer, int64_t classes, int64_t inner, int use_log);
+
 #ifdef __cplusplus
 }
 #endif

@@ -73,6 +73,10 @@ def lib():
         _lib.orc_gemv_f32.argtypes = [_vp] * 4 + [_i64] * 3 + [_int] * 2
         _lib.orc_conv3x3_winograd_f32_nchw.argtypes = (
             [_vp] * 4 + [_i64] * 5 + [_int] * 2 + [_i64] * 2 + [_int, _f32, _f32, _int])
+        _lib.orc_pooling_f32_nchw.argtypes = [_vp] * 2 + [_i64] * 6 + [_int] * 6 + [_i64] * 2 + [_int]
+        _lib.orc_eltwise_f32.argtypes = [_vp] * 3 + [_i64, _int, _f32, _int, _f32, _f32, _int]
+        _lib.orc_activation_f32.argtypes = [_vp] * 2 + [_i64, _int, _f32, _f32]
+        _lib.orc_softmax_f32.argtypes = [_vp] * 2 + [_i64] * 3 + [_int]
     return _lib
 
 
@@ -273,5 +277,46 @@ def winograd_f32(x, f, bias, pad_tl, out_hw, act=0, max_limit=0.0, coef=0.0, til
     st = lib().orc_conv3x3_winograd_f32_nchw(_p(x), _p(f), _p(bias), _p(out), N, Cc, H, W, O,
                                              pad_tl[0], pad_tl[1], Ho, Wo, act, max_limit,
                                              coef, tile)
+    assert st == 0
+    return out
+
+
+def pooling_f32(x, kernel, strides, dil, pad_tl, out_hw, pooling_type):
+    """x NCHW; pooling_type 1 AVG, 2 MAX."""
+    x = _c(x, np.float32)
+    N, Cc, H, W = x.shape
+    Ho, Wo = out_hw
+    out = np.empty((N, Cc, Ho, Wo), np.float32)
+    st = lib().orc_pooling_f32_nchw(_p(x), _p(out), N, Cc, H, W, kernel[0], kernel[1], strides[0],
+                                    strides[1], dil[0], dil[1], pad_tl[0], pad_tl[1], Ho, Wo,
+                                    pooling_type)
+    assert st == 0
+    return out
+
+
+def eltwise_f32(a, b, type_, coeff=None, swapped=False, scalar=1.0):
+    """b None: the tensor-scalar form with `scalar` as second operand."""
+    a = _c(a, np.float32)
+    b = _c(b, np.float32) if b is not None else None
+    out = np.empty_like(a)
+    c = coeff if coeff else (0.0, 0.0)
+    st = lib().orc_eltwise_f32(_p(a), _p(b) if b is not None else None, _p(out), a.size, type_,
+                               scalar, 1 if coeff else 0, c[0], c[1], 1 if swapped else 0)
+    assert st == 0
+    return out
+
+
+def activation_f32(x, act, max_limit=0.0, coef=0.0):
+    x = _c(x, np.float32)
+    out = np.empty_like(x)
+    st = lib().orc_activation_f32(_p(x), _p(out), x.size, act, max_limit, coef)
+    assert st == 0
+    return out
+
+
+def softmax_f32(x, outer, classes, inner, use_log=False):
+    x = _c(x, np.float32)
+    out = np.empty_like(x)
+    st = lib().orc_softmax_f32(_p(x), _p(out), outer, classes, inner, 1 if use_log else 0)
     assert st == 0
     return out

@@ -203,3 +203,131 @@ def test_winograd_config1_full_size(ctx, orc):
     ctx.winograd_f32(d1, df, db, o1, 1, C, H, W, O, (1, 1), (H, W))
     alone = ctx.download(o1, (1, O, H, W), np.float32)
     assert np.array_equal(alone[0], got[17])
+
+
+@pytest.mark.parametrize("case", [
+    # N, C, H, W, O, KH, KW, stride, dilation, padding, activation
+    (3, 3, 64, 64, 64, 7, 7, 2, 1, "SAME", 1),     # stem shape: K = 147 (filter rows repacked), 1024 positions
+    (2, 64, 30, 30, 48, 1, 1, 2, 1, "SAME", 0),    # 1x1 stride 2: 225 positions -> images merged
+    (5, 96, 7, 7, 40, 1, 1, 1, 1, "VALID", 1),     # 1x1 stride 1 with 49 positions -> images merged
+    (2, 32, 20, 24, 24, 3, 3, 2, 1, "SAME", 6),    # 3x3 stride 2: 120 positions -> merged
+    (2, 16, 40, 40, 32, 3, 3, 1, 2, "SAME", 2),    # dilated 3x3, 1600 positions per image
+    (1, 8, 33, 47, 16, 5, 3, 1, 1, "FULL", 0),     # ragged everything
+])
+@pytest.mark.parametrize("budget_mb", [1024, 1])
+def test_conv2d_f32_column_route(ctx, orc, case, budget_mb):
+    """General convolutions large enough for the im2col + tensor-core GEMM route, with the
+    column matrix in one piece and split into chunks of images (1 MiB budget)."""
+    N, C, H, W, O, KH, KW, st, dil, padding, act = case
+    x, f, bias = _conv_inputs((N, C, H, W), (O, C, KH, KW), H * 5 + C)
+    x = x * 2 - 1
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, KH, KW, (dil, dil), (st, st), PAD[padding])
+    ref = orc.conv2d_f32(x, f, bias, (st, st), (dil, dil), (ph >> 1, pw >> 1), (Ho, Wo), act, 0.5, 0.1)
+    dx, df, db, do = ctx.upload(x), ctx.upload(f), ctx.upload(bias), ctx.alloc(ref.nbytes)
+    ctx.set_option("col_budget_mb", budget_mb)
+    before = ctx.launches_tensor_core
+    try:
+        ctx.conv2d_f32(dx, df, db, do, N, C, H, W, O, KH, KW, (st, st), (dil, dil), (ph >> 1, pw >> 1),
+                       (Ho, Wo), act, 0.5, 0.1)
+    finally:
+        ctx.set_option("col_budget_mb", 1024)
+    assert ctx.launches_tensor_core > before, "tensor-core GEMM did not run"
+    assert rel_err(ctx.download(do, ref.shape, np.float32), ref) <= 1e-4
+    for b in (dx, df, db, do):
+        b.free()
+
+
+@pytest.mark.parametrize("case", [
+    # N, C, H, W, kernel, stride, dilation, padding
+    (2, 5, 17, 19, 3, 2, 1, "SAME"),      # ResNet's 3x3 stride-2 max pool
+    (1, 3, 8, 8, 2, 2, 1, "VALID"),
+    (2, 16, 7, 7, 7, 1, 1, "VALID"),      # global pooling
+    (1, 4, 13, 11, 3, 1, 2, "SAME"),      # dilated
+    (2, 3, 10, 10, 5, 3, 1, "FULL"),      # windows that overlap the border by more than half
+])
+@pytest.mark.parametrize("ptype", [1, 2])
+def test_pooling_f32(ctx, orc, case, ptype):
+    N, C, H, W, k, st, dil, padding = case
+    rng = np.random.Generator(np.random.PCG64(H + ptype))
+    x = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, k, k, (dil, dil), (st, st), PAD[padding])
+    ref = orc.pooling_f32(x, (k, k), (st, st), (dil, dil), (ph >> 1, pw >> 1), (Ho, Wo), ptype)
+    dx, do = ctx.upload(x), ctx.alloc(ref.nbytes)
+    ctx.pooling_f32(dx, do, N, C, H, W, (k, k), (st, st), (dil, dil), (ph >> 1, pw >> 1), (Ho, Wo), ptype)
+    got = ctx.download(do, ref.shape, np.float32)
+    if ptype == 2:
+        assert np.array_equal(got, ref)          # a maximum has no rounding
+    else:
+        assert rel_err(got, ref) <= 1e-6
+    dx.free(); do.free()
+
+
+def test_pooling_f32_reference_literals(ctx):
+    """PoolingOpTest.MAX_VALID / AVG_VALID (test/ccunit/mace/ops/pooling_test.cc:27-61, 301-336)."""
+    x = np.ascontiguousarray(np.arange(32, dtype=np.float32).reshape(1, 2, 4, 4))
+    dx, do = ctx.upload(x), ctx.alloc(8 * 4)
+    ctx.pooling_f32(dx, do, 1, 2, 4, 4, (2, 2), (2, 2), (1, 1), (0, 0), (2, 2), 2)
+    assert ctx.download(do, (8,), np.float32).tolist() == [5, 7, 13, 15, 21, 23, 29, 31]
+    ctx.pooling_f32(dx, do, 1, 2, 4, 4, (2, 2), (2, 2), (1, 1), (0, 0), (2, 2), 1)
+    assert ctx.download(do, (8,), np.float32).tolist() == [2.5, 4.5, 10.5, 12.5, 18.5, 20.5, 26.5, 28.5]
+
+
+@pytest.mark.parametrize("size", [1, 6, 1000, 4099, 1 << 20])
+def test_eltwise_f32(ctx, orc, size):
+    """Same-shape and tensor-scalar forms; the results are single IEEE operations (or two
+    products and a sum), so they must be bit-identical to the CPU's."""
+    rng = np.random.Generator(np.random.PCG64(size))
+    a = rng.standard_normal(size).astype(np.float32)
+    b = (rng.standard_normal(size) + 2.5).astype(np.float32)
+    da, db, do = ctx.upload(a), ctx.upload(b), ctx.alloc(size * 4)
+    for type_ in (0, 1, 2, 3, 4, 5, 6, 7, 8):
+        for swapped in (False, True):
+            ctx.eltwise_f32(da, db, do, size, type_, swapped=swapped)
+            assert np.array_equal(ctx.download(do, (size,), np.float32),
+                                  orc.eltwise_f32(a, b, type_, swapped=swapped)), (type_, swapped)
+            ctx.eltwise_f32(da, None, do, size, type_, swapped=swapped, scalar=0.75)
+            assert np.array_equal(ctx.download(do, (size,), np.float32),
+                                  orc.eltwise_f32(a, None, type_, swapped=swapped, scalar=0.75)), type_
+    for swapped in (False, True):
+        ctx.eltwise_f32(da, db, do, size, 0, coeff=(0.3, -1.7), swapped=swapped)
+        assert np.array_equal(ctx.download(do, (size,), np.float32),
+                              orc.eltwise_f32(a, b, 0, coeff=(0.3, -1.7), swapped=swapped))
+    ctx.eltwise_f32(da, None, do, size, 12, coeff=(-0.5, 0.25))
+    assert np.array_equal(ctx.download(do, (size,), np.float32), orc.eltwise_f32(a, None, 12, coeff=(-0.5, 0.25)))
+    import mace_b200
+    with pytest.raises(mace_b200.MaceB200Error):
+        ctx.eltwise_f32(da, db, do, size, 9)           # POW is not built
+    with pytest.raises(mace_b200.MaceB200Error):
+        ctx.eltwise_f32(da, None, do, size, 12, coeff=(1.0, 0.0))   # Clip needs min < max
+    for buf in (da, db, do):
+        buf.free()
+
+
+@pytest.mark.parametrize("act", [0, 1, 2, 6])
+def test_activation_f32(ctx, orc, act):
+    rng = np.random.Generator(np.random.PCG64(act))
+    x = (rng.standard_normal(100003) * 3).astype(np.float32)
+    dx, do = ctx.upload(x), ctx.alloc(x.nbytes)
+    ctx.activation_f32(dx, do, x.size, act, 2.0, 0.1)
+    assert rel_err(ctx.download(do, x.shape, np.float32), orc.activation_f32(x, act, 2.0, 0.1)) <= 1e-7
+    ctx.activation_f32(dx, dx, x.size, act, 2.0, 0.1)   # in place
+    assert rel_err(ctx.download(dx, x.shape, np.float32), orc.activation_f32(x, act, 2.0, 0.1)) <= 1e-7
+    dx.free(); do.free()
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 1), (3, 1001, 1), (64, 1000, 1), (2, 21, 35), (1, 3, 1000)])
+@pytest.mark.parametrize("use_log", [False, True])
+def test_softmax_f32(ctx, orc, shape, use_log):
+    outer, classes, inner = shape
+    rng = np.random.Generator(np.random.PCG64(classes))
+    x = (rng.standard_normal(shape) * 4).astype(np.float32)
+    if shape == (2, 4, 1):
+        x = np.array([1, 1, 1, 1, 1, 2, 3, 4], np.float32).reshape(shape)  # softmax_test.cc:37-38
+    dx, do = ctx.upload(x), ctx.alloc(x.nbytes)
+    ctx.softmax_f32(dx, do, outer, classes, inner, use_log)
+    got = ctx.download(do, shape, np.float32)
+    ref = orc.softmax_f32(x, outer, classes, inner, use_log).reshape(shape)
+    # the reference's own softmax tests compare at 1e-5 (softmax_test.cc:96); expf on the
+    # device and std::exp on the host differ by a few ulps
+    assert np.abs(got - ref).max() <= (1e-4 if use_log else 1e-5)
+    dx.free(); do.free()

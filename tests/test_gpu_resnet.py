@@ -1,0 +1,124 @@
+"""The float operators between the convolutions (Pooling, Eltwise, Activation, Softmax) through
+the C++ host layer, and a ResNet-50-shaped graph end to end on the device against the CPU
+oracle's direct fp32 convolutions.  Tolerance for the chain: 1e-3 of each activation's range
+(the bound the 3x3 Winograd path is specified with); the observed error is far smaller."""
+import numpy as np
+import pytest
+
+import resnet50 as rn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def net():
+    from mace_b200 import hostapi
+    e = hostapi.HostEngine(0)
+    yield e
+    e.close()
+
+
+def test_pooling_op_literals(net):
+    """PoolingOpTest.MAX_VALID, AVG_VALID, MAX_SAME, MAX_VALID_DILATION
+    (test/ccunit/mace/ops/pooling_test.cc:27-128, 301-336) through PoolingOp<RT_CUDA,float>."""
+    from mace_b200 import hostapi as H
+    x = np.arange(32, dtype=np.float32).reshape(1, 2, 4, 4)
+    net.add_tensor("Input", x)
+    common = {"kernels": [2, 2], "strides": [2, 2], "dilations": [1, 1]}
+    net.op("Pooling", "max", ["Input"], ["OutMax"], T=H.DT_FLOAT, ints=common,
+           i={"padding": H.VALID, "pooling_type": H.MAX})
+    net.op("Pooling", "avg", ["Input"], ["OutAvg"], T=H.DT_FLOAT, ints=common,
+           i={"padding": H.VALID, "pooling_type": H.AVG})
+    net.add_tensor("In3", np.arange(9, dtype=np.float32).reshape(1, 1, 3, 3))
+    net.op("Pooling", "same", ["In3"], ["OutSame"], T=H.DT_FLOAT, ints=common,
+           i={"padding": H.SAME, "pooling_type": H.MAX})
+    net.add_tensor("In4", np.arange(16, dtype=np.float32).reshape(1, 1, 4, 4))
+    net.op("Pooling", "dil", ["In4"], ["OutDil"], T=H.DT_FLOAT,
+           ints={"kernels": [2, 2], "strides": [1, 1], "dilations": [2, 2]},
+           i={"padding": H.VALID, "pooling_type": H.MAX})
+    net.run()
+    assert net.shape("OutMax") == (1, 2, 2, 2)
+    assert net.read("OutMax", np.float32).ravel().tolist() == [5, 7, 13, 15, 21, 23, 29, 31]
+    assert net.read("OutAvg", np.float32).ravel().tolist() == [2.5, 4.5, 10.5, 12.5, 18.5, 20.5, 26.5, 28.5]
+    assert net.shape("OutSame") == (1, 1, 2, 2)
+    assert net.read("OutSame", np.float32).ravel().tolist() == [4, 5, 7, 8]
+    assert net.read("OutDil", np.float32).ravel().tolist() == [10, 11, 14, 15]
+
+
+def test_eltwise_activation_softmax_ops(net):
+    """EltwiseOpTest.CPUSimpleTensorTensor / CPUSimpleTensorScalar literals
+    (test/ccunit/mace/ops/eltwise_test.cc:253-294, 476-491), SoftmaxOpTest.CPUSimple
+    (softmax_test.cc:32-97) and a ReLU, through the operators of the CUDA runtime."""
+    from mace_b200 import hostapi as H
+    a = np.arange(1, 7, dtype=np.float32).reshape(1, 1, 2, 3)
+    net.add_tensor("A", a)
+    net.add_tensor("B", a.copy())
+    F = H.DT_FLOAT
+    net.op("Eltwise", "sum", ["A", "B"], ["Sum"], T=F, i={"type": 0})
+    net.op("Eltwise", "wsum", ["A", "B"], ["WSum"], T=F, i={"type": 0}, floats={"coeff": [0.1, 0.1]})
+    net.op("Eltwise", "prod", ["A", "B"], ["Prod"], T=F, i={"type": 2})
+    net.op("Eltwise", "subs", ["A"], ["SubS"], T=F, i={"type": 1}, f={"scalar_input": 1.0})
+    net.op("Eltwise", "rsub", ["A"], ["RSub"], T=F, i={"type": 1, "scalar_input_index": 0},
+           f={"scalar_input": 1.0})
+    net.op("Eltwise", "maxs", ["A"], ["MaxS"], T=F, i={"type": 5}, f={"scalar_input": 3.0})
+    net.op("Eltwise", "neg", ["A"], ["Neg"], T=F, i={"type": 6})
+    net.op("Activation", "relu", ["RSub"], ["Relu"], T=F, s={"activation": "RELU"})
+    net.add_tensor("Logits", np.array([1, 1, 1, 1, 1, 2, 3, 4], np.float32).reshape(2, 4))
+    net.op("Softmax", "sm", ["Logits"], ["Prob"], T=F)
+    net.op("Softmax", "lsm", ["Logits"], ["LogProb"], T=F, i={"use_log": 1})
+    net.run()
+    assert net.read("Sum", np.float32).ravel().tolist() == [2, 4, 6, 8, 10, 12]
+    assert np.allclose(net.read("WSum", np.float32).ravel(), [0.2, 0.4, 0.6, 0.8, 1, 1.2], atol=1e-5)
+    assert net.read("Prod", np.float32).ravel().tolist() == [1, 4, 9, 16, 25, 36]
+    assert net.read("SubS", np.float32).ravel().tolist() == [0, 1, 2, 3, 4, 5]
+    assert net.read("RSub", np.float32).ravel().tolist() == [0, -1, -2, -3, -4, -5]
+    assert net.read("MaxS", np.float32).ravel().tolist() == [3, 3, 3, 4, 5, 6]
+    assert net.read("Neg", np.float32).ravel().tolist() == [-1, -2, -3, -4, -5, -6]
+    assert net.read("Relu", np.float32).ravel().tolist() == [0] * 6
+    assert np.allclose(net.read("Prob", np.float32).ravel(),
+                       [0.25, 0.25, 0.25, 0.25, 0.0320586, 0.08714432, 0.23688282, 0.6439142], atol=1e-5)
+    assert np.allclose(net.read("LogProb", np.float32).ravel(),
+                       [-1.3862944] * 4 + [-3.4401896, -2.4401896, -1.4401897, -0.44018975], atol=1e-5)
+
+
+def test_eltwise_rejects_what_is_not_built(net):
+    from mace_b200 import hostapi as H
+    net.add_tensor("A", np.ones((1, 4, 2, 2), np.float32))
+    net.add_tensor("V", np.ones((1, 4, 1, 1), np.float32))
+    net.op("Eltwise", "bcast", ["A", "V"], ["Out"], T=H.DT_FLOAT, i={"type": 0})
+    from mace_b200 import MaceB200Error
+    with pytest.raises(MaceB200Error) as e:
+        net.run()
+    assert "broadcast" in str(e.value)
+
+
+@pytest.mark.parametrize("cfg", [
+    {"batch": 2, "image": 64, "width_div": 4},     # every layer kind, small enough for the oracle
+    {"batch": 3, "image": 96, "width_div": 8},     # odd batch, 3x3 convs above and below the F(6,3) limit
+])
+def test_resnet50_graph_against_oracle(orc, cfg):
+    from mace_b200 import hostapi
+    nodes, weights = rn.build(seed=0, image=cfg["image"], width_div=cfg["width_div"])
+    x = rn.random_images(cfg["batch"], 1, cfg["image"])
+    ref_logits, ref = rn.oracle_forward(orc, nodes, weights, x, keep=True)
+    eng = rn.build_engine(hostapi, nodes, weights, cfg["batch"], image=cfg["image"])
+    try:
+        eng.write("input", x)
+        eng.run()
+        worst = 0.0
+        for n in nodes:
+            got = eng.read(n["name"], np.float32)
+            want = ref[n["name"]]
+            assert got.shape == want.shape, n["name"]
+            err = float(np.abs(got.astype(np.float64) - want).max() / max(np.abs(want).max(), 1e-30))
+            worst = max(worst, err)
+            assert err <= 1e-3, (n["name"], err)
+        assert worst <= 1e-4, worst        # what the kernels actually deliver
+        assert np.array_equal(eng.read("fc", np.float32).argmax(1).ravel(), ref_logits.argmax(1).ravel())
+        # a second run through a captured CUDA graph gives the same bytes
+        first = eng.read("fc", np.float32)
+        eng.capture()
+        eng.run()
+        assert np.array_equal(eng.read("fc", np.float32), first)
+    finally:
+        eng.close()

@@ -129,3 +129,81 @@ def test_padding_rules(orc):
     assert orc.calc_padding_and_output_size(112, 112, 3, 3, (1, 1), (1, 1), 1) == (112, 112, 2, 2)
     assert orc.calc_padding_and_output_size(5, 5, 3, 3, (1, 1), (1, 1), 2) == (7, 7, 4, 4)
     assert orc.calc_padding_and_output_size(7, 7, 3, 3, (2, 2), (1, 1), 0) == (3, 3, 0, 0)
+
+
+def _flat_nhwc_to_nchw(values, shape):
+    return np.ascontiguousarray(np.asarray(values, np.float32).reshape(shape).transpose(0, 3, 1, 2))
+
+
+def _nchw_to_flat_nhwc(t):
+    return t.transpose(0, 2, 3, 1).ravel().tolist()
+
+
+def test_pooling_f32_known_answers(orc):
+    # PoolingOpTest.MAX_VALID / AVG_VALID (test/ccunit/mace/ops/pooling_test.cc:27-61, 301-336):
+    # NHWC [1,4,4,2] whose two channels count 0..15 and 16..31, 2x2 window, stride 2, VALID
+    x = _flat_nhwc_to_nchw([v for i in range(16) for v in (i, 16 + i)], (1, 4, 4, 2))
+    out = orc.pooling_f32(x, (2, 2), (2, 2), (1, 1), (0, 0), (2, 2), 2)
+    assert _nchw_to_flat_nhwc(out) == [5, 21, 7, 23, 13, 29, 15, 31]
+    out = orc.pooling_f32(x, (2, 2), (2, 2), (1, 1), (0, 0), (2, 2), 1)
+    assert _nchw_to_flat_nhwc(out) == [2.5, 18.5, 4.5, 20.5, 10.5, 26.5, 12.5, 28.5]
+    # MAX_SAME (:63-94): 3x3 counting from 0, 2x2 stride 2 SAME -> pad 0 before, 1 after
+    x = _flat_nhwc_to_nchw(range(9), (1, 3, 3, 1))
+    ho, wo, ph, pw = orc.calc_padding_and_output_size(3, 3, 2, 2, (1, 1), (2, 2), 1)
+    out = orc.pooling_f32(x, (2, 2), (2, 2), (1, 1), (ph // 2, pw // 2), (ho, wo), 2)
+    assert _nchw_to_flat_nhwc(out) == [4, 5, 7, 8]
+    # MAX_VALID_DILATION (:96-128): 4x4 counting from 0, 2x2 window, dilation 2
+    x = _flat_nhwc_to_nchw(range(16), (1, 4, 4, 1))
+    out = orc.pooling_f32(x, (2, 2), (1, 1), (2, 2), (0, 0), (2, 2), 2)
+    assert _nchw_to_flat_nhwc(out) == [10, 11, 14, 15]
+    # MAX_k2x2s2x2 (:130-162): [1,2,9,1] counting from 0, SAME -> the last window is cut
+    x = _flat_nhwc_to_nchw(range(18), (1, 2, 9, 1))
+    ho, wo, ph, pw = orc.calc_padding_and_output_size(2, 9, 2, 2, (1, 1), (2, 2), 1)
+    out = orc.pooling_f32(x, (2, 2), (2, 2), (1, 1), (ph // 2, pw // 2), (ho, wo), 2)
+    assert (ho, wo) == (1, 5) and _nchw_to_flat_nhwc(out) == [10, 12, 14, 16, 17]
+    # SimpleAvgPoolingTest (:338-366): [1,2,8,1] counting from 0, 2x2 stride 2 SAME
+    x = _flat_nhwc_to_nchw(range(16), (1, 2, 8, 1))
+    out = orc.pooling_f32(x, (2, 2), (2, 2), (1, 1), (0, 0), (1, 4), 1)
+    assert _nchw_to_flat_nhwc(out) == [4.5, 6.5, 8.5, 10.5]
+
+
+def test_eltwise_f32_known_answers(orc):
+    # EltwiseOpTest.CPUSimpleTensorScalar (test/ccunit/mace/ops/eltwise_test.cc:253-294)
+    one_to_six = np.arange(1, 7, dtype=np.float32)
+    SUM, SUB, PROD, DIV, MIN, MAX, NEG, ABS, SQR_DIFF = range(9)
+    assert orc.eltwise_f32(np.ones(1, np.float32), None, SUM, scalar=1.0).tolist() == [2]
+    assert orc.eltwise_f32(one_to_six, None, SUB, scalar=1.0).tolist() == [0, 1, 2, 3, 4, 5]
+    assert orc.eltwise_f32(one_to_six, None, PROD, scalar=2.0).tolist() == [2, 4, 6, 8, 10, 12]
+    assert orc.eltwise_f32(2 * one_to_six, None, DIV, scalar=2.0).tolist() == [1, 2, 3, 4, 5, 6]
+    assert orc.eltwise_f32(one_to_six, None, MIN, scalar=1.0).tolist() == [1] * 6
+    assert orc.eltwise_f32(one_to_six, None, MAX, scalar=3.0).tolist() == [3, 3, 3, 4, 5, 6]
+    assert orc.eltwise_f32(one_to_six, None, NEG, scalar=3.0).tolist() == [-1, -2, -3, -4, -5, -6]
+    assert orc.eltwise_f32(-one_to_six, None, ABS, scalar=3.0).tolist() == [1, 2, 3, 4, 5, 6]
+    assert orc.eltwise_f32(one_to_six, None, SQR_DIFF, scalar=1.0).tolist() == [0, 1, 4, 9, 16, 25]
+    # CPUSimpleTensorTensor (:476-491): same-shape operands, with and without coeff
+    a = np.arange(1, 7, dtype=np.float32)
+    assert orc.eltwise_f32(a, a, SUM).tolist() == [2, 4, 6, 8, 10, 12]
+    assert np.allclose(orc.eltwise_f32(a, a, SUM, coeff=(0.1, 0.1)), [0.2, 0.4, 0.6, 0.8, 1, 1.2], atol=1e-5)
+    assert orc.eltwise_f32(a, a, SUB).tolist() == [0] * 6
+    assert orc.eltwise_f32(a, a, PROD).tolist() == [1, 4, 9, 16, 25, 36]
+    assert orc.eltwise_f32(a, a, DIV).tolist() == [1] * 6
+    # swapped operands: SUB and DIV are computed the other way round, SUM swaps its coefficients
+    b = np.array([6, 5, 4, 3, 2, 1], np.float32)
+    assert orc.eltwise_f32(a, b, SUB, swapped=True).tolist() == [5, 3, 1, -1, -3, -5]
+    assert orc.eltwise_f32(a, b, SUM, coeff=(1.0, 2.0), swapped=True).tolist() == [8, 9, 10, 11, 12, 13]
+
+
+def test_softmax_f32_known_answers(orc):
+    # SoftmaxOpTest.CPUSimple / LogSoftmaxOpTest.CPUSimple (test/ccunit/mace/ops/softmax_test.cc:
+    # 32-97): rows (1,1,1,1) and (1,2,3,4), as NHWC [1,1,2,4] and as a 2-D tensor [2,4]
+    x = np.array([1, 1, 1, 1, 1, 2, 3, 4], np.float32)
+    want = [0.25, 0.25, 0.25, 0.25, 0.0320586, 0.08714432, 0.23688282, 0.6439142]
+    got = orc.softmax_f32(x, 2, 4, 1)
+    assert np.allclose(got, want, atol=1e-5)
+    want_log = [-1.3862944, -1.3862944, -1.3862944, -1.3862944, -3.4401896, -2.4401896,
+                -1.4401897, -0.44018975]
+    assert np.allclose(orc.softmax_f32(x, 2, 4, 1, use_log=True), want_log, atol=1e-5)
+    # the same rows as the channels of an NCHW tensor [1,4,2,1]: softmax over C at each pixel
+    nchw = np.ascontiguousarray(x.reshape(2, 4).T).reshape(1, 4, 2, 1)
+    got = orc.softmax_f32(nchw, 1, 4, 2).reshape(4, 2).T.ravel()
+    assert np.allclose(got, want, atol=1e-5)
