@@ -4,8 +4,8 @@
 // What it serves: the batched product of the Winograd convolution
 // (arm::Conv2dK3x3Winograd, mace/ops/arm/base/conv_2d_3x3_winograd.cc:147-170, which calls
 // arm::Gemm per image), the 1x1 convolution (arm::Conv2dK1x1,
-// mace/ops/arm/base/conv_2d_1x1.cc:61-68) and MatMul/Gemm (mace/ops/arm/base/gemm.cc:520-683)
-// in the layout all three share:
+// mace/ops/arm/base/conv_2d_1x1.cc:61-68), the im2col form of the general convolution and
+// MatMul/Gemm (mace/ops/arm/base/gemm.cc:520-683) in the layout all of them share:
 //     C[b][n][m] = act(bias[n] + sum_k X[b][k][m] * W[b][n][k])
 // X is [K x Mdim] with m contiguous (an activation matrix: channels x pixels), W is
 // [Ndim x K] with k contiguous (a filter matrix: output channels x channels), C is
@@ -14,19 +14,31 @@
 // consecutive pixels.
 //
 // Precision.  kind::tf32 reads only the upper 19 bits of each fp32 operand.  Every operand
-// tile is therefore split in shared memory into hi = x with the low 13 mantissa bits
-// cleared and lo = x - hi (exact), and each K step issues three MMAs,
-//     hi*hi + lo*hi + hi*lo,
+// is therefore split into hi = x with the low 13 mantissa bits cleared and lo = x - hi
+// (exact), and each K step issues three MMAs,
+//     lo*hi + hi*lo + hi*hi,
 // into the fp32 accumulator; the dropped lo*lo term is below 2^-22 of the product, so the
 // result matches an fp32 FMA loop to a few ulps (tests bound it at 1e-4 of the output range).
 //
-// Structure (one persistent CTA per SM, 448 threads):
-//   warp 0        TMA producer: X as four [32 k x 32 m] boxes and W as one [BN x 32 k] box per
-//                 stage, 128-byte swizzle, mbarrier ring
-//   warp 1        MMA issuer (one thread)
-//   warps 2..5    split: hi/lo tiles of the landed stage, then release it to the MMA warp
-//   warps 6..13   epilogue: two sets of four warps (one per TMEM lane quarter), each on half
-//                 of the tile's columns: tcgen05.ld, bias, activation, coalesced stores
+// Where the split operands live.  The X operand (the MMA's A, 128 pixels = 128 TMEM lanes)
+// goes to TENSOR MEMORY: a warp per lane quarter reads its pixels' 32 k-values of the landed
+// tile from shared memory (one word per lane and k: conflict-free), splits them in registers
+// and writes hi and lo with tcgen05.st into a ring of TMEM columns; the MMA takes A from
+// there.  Only W (the MMA's B) is split in shared memory, in place.  Against splitting both
+// operands in shared memory this halves the shared-memory bytes a K step moves (the MMA no
+// longer reads A from it, and X is never written back) and shrinks a pipeline stage from
+// 64 KB to 48 KB, so four stages fit instead of two; the loads then run far enough ahead to
+// hide the memory latency, which had bounded the two-stage version.
+//
+// Structure (one persistent CTA per SM, 576 threads):
+//   warp 0        TMA producer: X as one [32 k x 128 m] box (no swizzle) and W as one
+//                 [BN x 32 k] box (128-byte swizzle) per stage, mbarrier ring
+//   warp 1        MMA issuer (one thread): A from TMEM, B from shared memory
+//   warps 2..5    X split: shared memory -> registers -> hi/lo in TMEM
+//   warps 6..9    W split: hi/lo tiles in shared memory
+//   warps 10..17  epilogue: two sets of four warps (one per TMEM lane quarter), each on half
+//                 of the tile's columns: tcgen05.ld, bias, activation, TMA stores
+// TMEM columns: two accumulators of BN columns, then STAGES x 64 columns of A (hi 32, lo 32).
 // Every wait is bounded; on a timeout the kernel records a status word, lets outstanding
 // copies land, frees its TMEM and returns.
 #include "common.cuh"
@@ -39,10 +51,14 @@ using namespace sm100;
 constexpr int FBM = 128;       // pixels (m) per tile == TMEM lanes
 constexpr int FKB = 32;        // k per pipeline stage (32 fp32 = one 128-byte swizzle row of W)
 constexpr int FUMMA_K = 8;     // k per tcgen05.mma for tf32
-constexpr int F_SPLIT_WARPS = 4;
+constexpr int F_XSPLIT_WARPS = 4;   // one per TMEM lane quarter
+constexpr int F_WSPLIT_WARPS = 4;
+constexpr int F_SPLIT_WARPS = F_XSPLIT_WARPS + F_WSPLIT_WARPS;
+constexpr int F_FIRST_WSPLIT_WARP = 2 + F_XSPLIT_WARPS;
 constexpr int F_EPI_WARPS = 8;
 constexpr int F_FIRST_EPI_WARP = 2 + F_SPLIT_WARPS;
 constexpr int F_THREADS = (2 + F_SPLIT_WARPS + F_EPI_WARPS) * 32;
+constexpr int F_A_COLS = 2 * FKB;   // TMEM columns of one stage's A operand: hi, then lo
 constexpr long long F_WAIT_BUDGET = 1ll << 31;
 
 struct F32TcParams {
@@ -66,26 +82,37 @@ struct F32TcParams {
     if (p.timeline != nullptr && blockIdx.x == 0 && (tile) < 16)                    \
       p.timeline[32 + (tile) * 5 + (k)] = clock64();                                \
   } while (0)
+// per K step of CTA 0 (first 64 steps): role 0 producer issue, 1 tile landed, 2 X split done,
+// 3 MMA sees both splits, 4 MMAs issued, 5 W split done; slots from 128
+#define MBF_STAMP_K(role, idx)                                                      \
+  do {                                                                              \
+    if (p.timeline != nullptr && blockIdx.x == 0 && (idx) < 64)                     \
+      p.timeline[128 + (role) * 64 + (idx)] = clock64();                            \
+  } while (0)
 #else
 #define MBF_STAMP_TILE(tile, k) do { (void)(tile); } while (0)
+#define MBF_STAMP_K(role, idx) do { (void)(idx); } while (0)
 #endif
 
 template <int BN>
 struct F32Cfg {
-  static constexpr int X_BYTES = FBM * FKB * 4;   // 16 KB: four [32 k][32 m] sub-tiles of 4 KB
+  static constexpr int X_BYTES = FBM * FKB * 4;   // 16 KB: [32 k][128 m]
   static constexpr int W_BYTES = BN * FKB * 4;    // [BN n][32 k]
-  static constexpr int HI_BYTES = X_BYTES + W_BYTES;
-  static constexpr int STAGE_BYTES = 2 * HI_BYTES;  // hi tiles, then lo tiles
-  // epilogue staging for the TMA stores: two buffers of 16 channels x 32 pixels per warp
-  static constexpr int STAGING_BYTES = F_EPI_WARPS * 2 * 16 * 128;
-  static constexpr int RING_BUDGET = 208 * 1024 - STAGING_BYTES;
-  static constexpr int STAGES = RING_BUDGET / STAGE_BYTES > 6 ? 6 : RING_BUDGET / STAGE_BYTES;
-  static_assert(STAGES >= 2, "pipeline needs two stages");
+  static constexpr int STAGE_BYTES = X_BYTES + 2 * W_BYTES;  // raw X, W hi (lands raw), W lo
+  // epilogue staging for the TMA stores: two buffers of 16 channels x 128 pixels per warp set
+  static constexpr int STAGING_BYTES = 2 * 2 * 16 * FBM * 4;
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int RING_BUDGET = 227 * 1024 - STAGING_BYTES - 1024 - BAR_BYTES;
   static constexpr int NUM_ACC = 2;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int BAR_BYTES = 512;
+  static constexpr int A_COL0 = NUM_ACC * BN;     // first TMEM column of the A ring
+  static constexpr int MAX_TMEM_STAGES = (TMEM_COLS - A_COL0) / F_A_COLS;
+  static constexpr int SMEM_STAGES = RING_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = SMEM_STAGES < MAX_TMEM_STAGES ? SMEM_STAGES : MAX_TMEM_STAGES;
+  static_assert(STAGES >= 2, "pipeline needs two stages");
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 + BAR_BYTES;
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+  static_assert(3 * STAGES * 8 + 2 * NUM_ACC * 8 + 16 <= BAR_BYTES, "barrier area");
 };
 
 struct FTileIter {
@@ -166,6 +193,7 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
     uint32_t phase = 0;
     bool ok = true;
     int local = 0;
+    int kstep = 0;
 #ifdef MB_TC_TIMELINE
     if (lane == 0 && p.timeline != nullptr && blockIdx.x == 0) p.timeline[0] = clock64();
 #endif
@@ -182,13 +210,13 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
           const uint32_t fb = full_bar + 8 * stage;
           const uint32_t sx = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sw = sx + Cfg::X_BYTES;
-          mbar_arrive_expect_tx(fb, Cfg::HI_BYTES);
-#pragma unroll
-          for (int j = 0; j < 4; ++j)  // four 32-pixel atoms of the 128-pixel tile
-            tma_load_3d(sx + j * (FKB * 128), &tmap_x, fb, it.tm * FBM + j * 32, kb * FKB, xb);
+          MBF_STAMP_K(0, kstep);
+          mbar_arrive_expect_tx(fb, Cfg::X_BYTES + Cfg::W_BYTES);
+          tma_load_3d(sx, &tmap_x, fb, it.tm * FBM, kb * FKB, xb);  // [32 k][128 m], 512-byte rows
           tma_load_3d(sw, &tmap_w, fb, kb * FKB, it.tn * BN, wb);
           if (kb == 0) MBF_STAMP_TILE(local, 0);
         }
+        ++kstep;
         __syncwarp();
         if (++stage == STAGES) {
           stage = 0;
@@ -198,78 +226,89 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    constexpr uint32_t idesc = make_idesc(/*c f32*/ 1, /*a tf32*/ 2, /*b tf32*/ 2, /*a mn*/ true,
-                                          /*b mn*/ false, FBM, BN);
-    int stage = 0;
-    uint32_t phase = 0;
-    int acc_buf = 0;
-    uint32_t acc_phase = 0;
-    bool ok = true;
-    int local = 0;
-    for (FTileIter it(p); ok && it.valid(p); it.next(p), ++local) {
-      if (!mbar_wait_warp(tempty_bar + 8 * acc_buf, acc_phase ^ 1, abort_flag, F_WAIT_BUDGET)) {
-        *abort_flag = 1;
-        atomicCAS(p.status, 0, MB_DEV_TIMEOUT_MMA);
-        break;
-      }
-      tc_fence_after_sync();
-      const uint32_t d_tmem = tmem_base + acc_buf * BN;
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
-        if (!mbar_wait_warp(split_bar + 8 * stage, phase, abort_flag, F_WAIT_BUDGET)) {
+    // One thread runs the whole role.  The tensor pipe queues only a few MMAs, so everything
+    // between the last MMA of one K step and the first of the next (commit, barrier poll,
+    // descriptor arithmetic) has to fit into the time those queued MMAs take to execute, or
+    // the pipe idles: the descriptors are one add per K step, the common four-step case is
+    // unrolled, and nothing in the loop is warp-collective.
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(/*c f32*/ 1, /*a tf32*/ 2, /*b tf32*/ 2, /*a mn*/ false,
+                                            /*b mn*/ false, FBM, BN);
+      // W (K-major): rows of 128 bytes (32 k), 8-row groups 1024 bytes apart; a K step of 8
+      // moves 32 bytes inside the swizzled row (+2 in the descriptor's address field).
+      const uint64_t wdesc = make_smem_desc(0, 16, 1024, 2);
+      const int last_ksteps =
+          static_cast<int>((p.K - static_cast<int64_t>(p.k_blocks - 1) * FKB + FUMMA_K - 1) / FUMMA_K);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc_buf = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      int local = 0;
+      int kstep = 0;
+      for (FTileIter it(p); ok && it.valid(p); it.next(p), ++local) {
+        if (!mbar_wait(tempty_bar + 8 * acc_buf, acc_phase ^ 1, abort_flag, F_WAIT_BUDGET)) {
           *abort_flag = 1;
           atomicCAS(p.status, 0, MB_DEV_TIMEOUT_MMA);
-          ok = false;
           break;
         }
         tc_fence_after_sync();
-        if (kb == p.k_blocks - 1 && lane == 0) MBF_STAMP_TILE(local, 1);
-        const uint32_t sx = smem_base + stage * Cfg::STAGE_BYTES;
-        const uint32_t sw = sx + Cfg::X_BYTES;
-        const int64_t k_left = p.K - static_cast<int64_t>(kb) * FKB;
-        const int ksteps = k_left >= FKB ? FKB / FUMMA_K
-                                         : static_cast<int>((k_left + FUMMA_K - 1) / FUMMA_K);
-        if (lane == 0) {
-          for (int j = 0; j < ksteps; ++j) {
-            // X (MN-major tf32): k-rows of 128 bytes (32 pixels) in the "128-byte swizzle
-            // with 32-byte atoms" layout (descriptor layout type 1; the TMA map uses
-            // SWIZZLE_128B_ATOM_32B), whose pattern repeats every 4 k-rows: 4-row groups are
-            // 512 bytes apart (SBO), 32-pixel atoms FKB * 128 bytes apart (LBO); a K step of 8
-            // covers two groups = 1024 bytes.  The plain 128-byte swizzle gives zeros here.
-            // W (K-major): rows of 128 bytes (32 k), 8-row groups 1024 bytes apart; a K step
-            // moves 32 bytes inside the swizzled row.
-            const uint64_t x_hi = make_smem_desc(sx + j * 1024, FKB * 128, 512, 1);
-            const uint64_t x_lo = make_smem_desc(sx + Cfg::HI_BYTES + j * 1024, FKB * 128, 512, 1);
-            const uint64_t w_hi = make_smem_desc(sw + j * 32, 16, 1024, 2);
-            const uint64_t w_lo = make_smem_desc(sw + Cfg::HI_BYTES + j * 32, 16, 1024, 2);
-            mma_tf32_ss(d_tmem, x_lo, w_hi, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-            mma_tf32_ss(d_tmem, x_hi, w_lo, idesc, 1u);
-            mma_tf32_ss(d_tmem, x_hi, w_hi, idesc, 1u);
+        const uint32_t d_tmem = tmem_base + acc_buf * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++kstep) {
+          if (!mbar_wait(split_bar + 8 * stage, phase, abort_flag, F_WAIT_BUDGET)) {
+            *abort_flag = 1;
+            atomicCAS(p.status, 0, MB_DEV_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          if (kb == p.k_blocks - 1) MBF_STAMP_TILE(local, 1);
+          MBF_STAMP_K(3, kstep);
+          const uint32_t sw = smem_base + stage * Cfg::STAGE_BYTES + Cfg::X_BYTES;
+          // A (TMEM): lane = pixel, one column per k; a K step of 8 is 8 columns; hi in the
+          // first 32 columns of the stage's slot, lo in the next 32.
+          const uint32_t a_hi = tmem_base + Cfg::A_COL0 + stage * F_A_COLS, a_lo = a_hi + FKB;
+          const uint64_t w_hi = wdesc | static_cast<uint64_t>((sw >> 4) & 0x3FFFu);
+          const uint64_t w_lo = wdesc | static_cast<uint64_t>(((sw + Cfg::W_BYTES) >> 4) & 0x3FFFu);
+          if (kb + 1 < p.k_blocks || last_ksteps == FKB / FUMMA_K) {
+#pragma unroll
+            for (int j = 0; j < FKB / FUMMA_K; ++j) {
+              mma_tf32_ts(d_tmem, a_lo + j * FUMMA_K, w_hi + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+              mma_tf32_ts(d_tmem, a_hi + j * FUMMA_K, w_lo + 2 * j, idesc, 1u);
+              mma_tf32_ts(d_tmem, a_hi + j * FUMMA_K, w_hi + 2 * j, idesc, 1u);
+            }
+          } else {
+            for (int j = 0; j < last_ksteps; ++j) {
+              mma_tf32_ts(d_tmem, a_lo + j * FUMMA_K, w_hi + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+              mma_tf32_ts(d_tmem, a_hi + j * FUMMA_K, w_lo + 2 * j, idesc, 1u);
+              mma_tf32_ts(d_tmem, a_hi + j * FUMMA_K, w_hi + 2 * j, idesc, 1u);
+            }
           }
           mma_commit(empty_bar + 8 * stage);
+          MBF_STAMP_K(4, kstep);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
         }
-        __syncwarp();
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1;
-        }
-      }
-      if (!ok) break;
-      if (lane == 0) {
+        if (!ok) break;
         mma_commit(tfull_bar + 8 * acc_buf);
         MBF_STAMP_TILE(local, 2);
-      }
-      __syncwarp();
-      if (++acc_buf == NUM_ACC) {
-        acc_buf = 0;
-        acc_phase ^= 1;
+        if (++acc_buf == NUM_ACC) {
+          acc_buf = 0;
+          acc_phase ^= 1;
+        }
       }
     }
-  } else if (warp < F_FIRST_EPI_WARP) {
-    // ---------------- split: hi / lo tiles ----------------
-    const int t = (warp - 2) * 32 + lane;  // 0..127
+    __syncwarp();
+  } else if (warp < F_FIRST_WSPLIT_WARP) {
+    // ---------------- X split: shared memory -> hi / lo in tensor memory ----------------
+    const int quarter = warp & 3;  // the TMEM lanes this warp may touch: 32 * (warp % 4) ...
+    const uint32_t a_lane = static_cast<uint32_t>(quarter * 32) << 16;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    int kstep = 0;
     for (FTileIter it(p); ok && it.valid(p); it.next(p)) {
       for (int kb = 0; kb < p.k_blocks; ++kb) {
         if (!mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, F_WAIT_BUDGET)) {
@@ -278,12 +317,58 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
           ok = false;
           break;
         }
-        uint4 *hi = reinterpret_cast<uint4 *>(smem_aligned + stage * Cfg::STAGE_BYTES);
-        uint4 *lo = reinterpret_cast<uint4 *>(smem_aligned + stage * Cfg::STAGE_BYTES + Cfg::HI_BYTES);
+        if (warp == 2 && lane == 0) MBF_STAMP_K(1, kstep);
+        // The slot's previous contents are dead: the producer refilled this stage only after
+        // the MMAs that read the slot had completed.
+        tc_fence_after_sync();
+        const float *xs = reinterpret_cast<const float *>(smem_aligned + stage * Cfg::STAGE_BYTES) +
+                          quarter * 32 + lane;
+        const uint32_t a_col = tmem_base + a_lane + Cfg::A_COL0 + stage * F_A_COLS;
+#pragma unroll
+        for (int h = 0; h < FKB / 16; ++h) {
+          uint32_t hi[16], lo[16];
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const uint32_t v = __float_as_uint(xs[(h * 16 + k) * FBM]);
+            hi[k] = v & 0xffffe000u;
+            lo[k] = __float_as_uint(__uint_as_float(v) - __uint_as_float(hi[k]));
+          }
+          tmem_st_32x32b_x16(a_col + h * 16, hi);
+          tmem_st_32x32b_x16(a_col + FKB + h * 16, lo);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(split_bar + 8 * stage);
+        if (warp == 2 && lane == 0) MBF_STAMP_K(2, kstep);
+        ++kstep;
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp < F_FIRST_EPI_WARP) {
+    // ---------------- W split: hi / lo tiles in shared memory ----------------
+    const int t = (warp - F_FIRST_WSPLIT_WARP) * 32 + lane;  // 0..127
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int kstep = 0;
+    for (FTileIter it(p); ok && it.valid(p); it.next(p)) {
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (!mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, F_WAIT_BUDGET)) {
+          *abort_flag = 1;
+          atomicCAS(p.status, 0, MB_DEV_TIMEOUT_EPILOGUE);
+          ok = false;
+          break;
+        }
+        uint4 *hi = reinterpret_cast<uint4 *>(smem_aligned + stage * Cfg::STAGE_BYTES + Cfg::X_BYTES);
+        uint4 *lo = hi + Cfg::W_BYTES / 16;
         // the split is element-wise, so the swizzled placement does not matter
-#pragma unroll 4
-        for (int i = t; i < Cfg::HI_BYTES / 16; i += F_SPLIT_WARPS * 32) {
-          const uint4 v = hi[i];
+#pragma unroll
+        for (int i = 0; i < Cfg::W_BYTES / 16 / (F_WSPLIT_WARPS * 32); ++i) {
+          const uint4 v = hi[t + i * (F_WSPLIT_WARPS * 32)];
           uint4 h, l;
           h.x = v.x & 0xffffe000u; h.y = v.y & 0xffffe000u;
           h.z = v.z & 0xffffe000u; h.w = v.w & 0xffffe000u;
@@ -291,12 +376,14 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
           l.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(h.y));
           l.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(h.z));
           l.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(h.w));
-          hi[i] = h;
-          lo[i] = l;
+          hi[t + i * (F_WSPLIT_WARPS * 32)] = h;
+          lo[t + i * (F_WSPLIT_WARPS * 32)] = l;
         }
         fence_proxy_async();  // the MMA reads these tiles through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(split_bar + 8 * stage);
+        if (t == 0) MBF_STAMP_K(5, kstep);
+        ++kstep;
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
@@ -307,6 +394,7 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;
     const int set = (warp - F_FIRST_EPI_WARP) >> 2;  // 0, 1: which half of the columns
+    const int my_turn = (warp - F_FIRST_EPI_WARP) & 3;  // which of the set's stores this warp issues
     constexpr int CHUNKS = BN / 16 / 2;              // 16-column chunks per warp
     // The activation as clamp + negative-slope term, with the choice made once: a branch
     // per value costs more than the arithmetic (few warps are there to hide its latency).
@@ -315,7 +403,8 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const float act_hi = p.act == 2 ? p.max_limit : INFINITY;
     const float act_slope = p.act == 6 ? p.coef : 0.f;
     const bool leaky = p.act == 6;
-    const float *bias = p.bias;
+    const float *__restrict__ bias = p.bias;
+    const bool has_bias = bias != nullptr;
     const int64_t Ndim = p.Ndim;
     const int c_tma = p.c_tma;
     int acc_buf = 0;
@@ -337,11 +426,18 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int64_t n_first = static_cast<int64_t>(it.tn) * BN + set * (BN / 2);
       uint32_t r[2][16];
       tmem_ld_32x32b_x16(tbase, r[0]);
-      // staging: [buffer][channel j][pixel lane]; a lane's 16 writes of a chunk go to 16
-      // different rows, the warp's write of one row covers all 32 banks
-      float *stage_f = reinterpret_cast<float *>(smem_aligned + STAGES * Cfg::STAGE_BYTES +
-                                                 (warp - F_FIRST_EPI_WARP) * (2 * 16 * 128));
-      const int m0 = it.tm * FBM + quarter * 32;
+      // Bias: lane j of a warp fetches the value of the chunk's channel j one chunk ahead and
+      // the chunk broadcasts it with shuffles.  (A load per value needs a bounds branch per
+      // value, and with eight warps nothing hides a branch: that form took 750 cycles a chunk.)
+      float b_next = 0.f;
+      if (has_bias) b_next = bias[min(n_first + (lane & 15), Ndim - 1)];
+      // staging, per set of four warps: [buffer][channel j][128 pixels]; a lane's 16 writes of
+      // a chunk go to 16 different rows, a warp's write of one row covers all 32 banks.  The
+      // four warps fill one [16 x 128] tile together and one thread stores it with a single
+      // TMA store of 512-byte rows (stores of 128-byte rows, one per warp, ran at half the rate).
+      float *stage_f = reinterpret_cast<float *>(smem_aligned + STAGES * Cfg::STAGE_BYTES) +
+                       set * (2 * 16 * FBM);
+      const int m0 = it.tm * FBM;
 #pragma unroll
       for (int i = 0; i < CHUNKS; ++i) {
         tmem_ld_wait_x16(r[i & 1]);
@@ -352,24 +448,29 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (lane == 0) mbar_arrive(tempty_bar + 8 * acc_buf);
         }
         const int64_t n0 = n_first + i * 16;
+        const float b_cur = b_next;
+        if (has_bias && i + 1 < CHUNKS) b_next = bias[min(n0 + 16 + (lane & 15), Ndim - 1)];
         float v[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const float bj = (bias != nullptr && n0 + j < Ndim) ? __ldg(bias + n0 + j) : 0.f;
+          const float bj = __shfl_sync(0xffffffffu, b_cur, j);
           const float x = __uint_as_float(r[i & 1][j]) + bj;
           const float neg = leaky ? fminf(x, 0.f) * act_slope : 0.f;
           v[j] = fminf(fmaxf(x, act_lo), act_hi) + neg;
         }
         if (c_tma) {
-          float *buf = stage_f + (i & 1) * (16 * 32);
-          // the store that last used this buffer (two chunks ago) must have read it
-          if (lane == 0) bulk_wait_group_read<1>();
-          __syncwarp();
+          float *buf = stage_f + (i & 1) * (16 * FBM);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) buf[j * 32 + lane] = v[j];
+          for (int j = 0; j < 16; ++j) buf[j * FBM + quarter * 32 + lane] = v[j];
           fence_proxy_async();
-          __syncwarp();
-          if (lane == 0 && n0 < p.Ndim && m0 < p.Mdim) {
+          // The four warps of a set take turns at issuing the stores (an issue costs its thread
+          // some 200 cycles; on one fixed thread that would be on every chunk's critical path).
+          // Before the barrier the thread that issued the previous store makes sure that it has
+          // read its buffer: after the barrier this buffer is complete AND the other one is free.
+          const int turn = (local * CHUNKS + i) & 3;
+          if (lane == 0 && my_turn == ((turn + 3) & 3)) bulk_wait_group_read<0>();
+          named_bar_sync(1 + set, 128);
+          if (lane == 0 && my_turn == turn && n0 < p.Ndim) {
             tma_store_3d(&tmap_c, smem_u32(buf), m0, static_cast<int>(n0), it.b);
             bulk_commit_group();
           }
@@ -483,8 +584,8 @@ int mb_gemm_f32_tc_launch(mb_context *ctx, const float *X, const float *W, const
   p.timeline = ctx->tc_timeline;
   CUtensorMap tx, tw;
   MB_RETURN_IF_ERROR(make_map_f32(ctx, &tx, X, Mdim, K, p.x_batched ? batch : 1, x_row_stride,
-                                  p.x_batched ? x_batch_stride : x_row_stride * K, 32, FKB,
-                                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
+                                  p.x_batched ? x_batch_stride : x_row_stride * K, FBM, FKB,
+                                  CU_TENSOR_MAP_SWIZZLE_NONE));
   MB_RETURN_IF_ERROR(make_map_f32(ctx, &tw, W, K, Ndim, p.w_batched ? batch : 1, w_row_stride,
                                   p.w_batched ? w_batch_stride : w_row_stride * Ndim, FKB, BN));
   CUtensorMap tc;
@@ -492,7 +593,7 @@ int mb_gemm_f32_tc_launch(mb_context *ctx, const float *X, const float *W, const
              c_batch_stride % 4 == 0 && Ndim >= 16) ? 1 : 0;
   if (p.c_tma) {
     MB_RETURN_IF_ERROR(make_map_f32(ctx, &tc, C, Mdim, Ndim, batch, c_row_stride,
-                                    batch > 1 ? c_batch_stride : c_row_stride * Ndim, 32, 16,
+                                    batch > 1 ? c_batch_stride : c_row_stride * Ndim, FBM, 16,
                                     CU_TENSOR_MAP_SWIZZLE_NONE));
   } else {
     memset(&tc, 0, sizeof(tc));
