@@ -183,17 +183,27 @@ struct ColF32Params {
   int64_t col_rs, col_ns;
 };
 
-__global__ void __launch_bounds__(256) im2col_f32_kernel(const ColF32Params p) {
-  const int pos = blockIdx.x * 256 + threadIdx.x;
-  if (pos >= p.hw) return;
-  const int k = blockIdx.y, n = blockIdx.z;
-  const int kw = k % p.KW, kh = (k / p.KW) % p.KH, c = k / (p.KW * p.KH);
-  const int h = pos / p.Wo, w = pos - h * p.Wo;
-  const int ih = h * p.sh - p.pad_t + kh * p.dh, iw = w * p.sw - p.pad_l + kw * p.dw;
-  float v = 0.f;
-  if (ih >= 0 && ih < p.H && iw >= 0 && iw < p.W)
-    v = __ldg(p.in + ((static_cast<int64_t>(n) * p.C + c) * p.H + ih) * p.W + iw);
-  p.col[k * p.col_rs + n * p.col_ns + pos] = v;
+// One block per (group of output rows, channel and filter row, image): threadIdx.x walks along
+// an output row and threadIdx.y picks the row, so no thread divides by anything, the KW taps
+// of a pixel re-read the same input row from L1, and every store is a contiguous run.
+__global__ void __launch_bounds__(128) im2col_f32_kernel(const ColF32Params p, int rows_per_block) {
+  const int h = blockIdx.x * blockDim.y + threadIdx.y, n = blockIdx.z;
+  if (h >= p.Ho) return;
+  const int y_end = min((static_cast<int>(blockIdx.y) + 1) * rows_per_block, p.C * p.KH);
+  for (int y = blockIdx.y * rows_per_block; y < y_end; ++y) {  // y = c * KH + kh
+    const int c = y / p.KH, kh = y - c * p.KH;
+    const int ih = h * p.sh - p.pad_t + kh * p.dh;
+    const bool row_ok = ih >= 0 && ih < p.H;
+    const float *src = p.in + ((static_cast<int64_t>(n) * p.C + c) * p.H + (row_ok ? ih : 0)) * p.W;
+    float *dst = p.col + static_cast<int64_t>(y) * p.KW * p.col_rs + n * p.col_ns + h * p.Wo;
+    for (int w = threadIdx.x; w < p.Wo; w += blockDim.x) {
+      const int iw0 = w * p.sw - p.pad_l;
+      for (int kw = 0; kw < p.KW; ++kw) {
+        const int iw = iw0 + kw * p.dw;
+        dst[kw * p.col_rs + w] = (row_ok && iw >= 0 && iw < p.W) ? __ldg(src + iw) : 0.f;
+      }
+    }
+  }
 }
 
 // rows of K floats -> rows of Kp floats (a 16-byte multiple, which a tensor map's strides need)
@@ -296,8 +306,15 @@ static int conv2d_f32_im2col(mb_context *ctx, const float *in, const float *filt
     p.in = in + n0 * C * H * W;
     p.col_rs = merged ? merged_rs : hwp;
     p.col_ns = merged ? hw : K * hwp;
-    dim3 grid(static_cast<unsigned>(ceil_div64(hw, 256)), static_cast<unsigned>(K), static_cast<unsigned>(nc));
-    im2col_f32_kernel<<<grid, 256, 0, ctx->stream>>>(p);
+    int bw = 8;  // threads along a row: the power of two that covers Wo, at most 128
+    while (bw < Wo && bw < 128) bw *= 2;
+    dim3 block(bw, 128 / bw);
+    // a block of few useful threads (narrow or single-tap rows) takes several (channel,
+    // filter row) pairs, so that its launch cost is spread over more than a handful of values
+    const int rows_per_block = (C * KH >= 64 && Wo * KW < 512) ? 8 : 1;
+    dim3 grid(static_cast<unsigned>(ceil_div64(Ho, block.y)),
+              static_cast<unsigned>(ceil_div64(C * KH, rows_per_block)), static_cast<unsigned>(nc));
+    im2col_f32_kernel<<<grid, block, 0, ctx->stream>>>(p, rows_per_block);
     MB_CUDA(ctx, cudaGetLastError());
     ctx->launches++;
     float *dst = out + n0 * O * hw;
@@ -402,7 +419,7 @@ int mb_conv2d_f32_nchw(mb_context *ctx, const float *in, const float *filter, co
   }
   // enough work to fill tensor-core tiles: gather columns and multiply; tiny problems stay on
   // the one-thread-per-output kernel
-  if (N * O * Ho * Wo * C * KH * KW >= (1ll << 18) && Ho * Wo * N >= 32 && C * KH * KW <= 65535 &&
+  if (N * O * Ho * Wo * C * KH * KW >= (1ll << 18) && Ho * Wo * N >= 32 && C * KH <= 65535 &&
       Ho * Wo < (1ll << 30)) {
     return conv2d_f32_im2col(ctx, in, filter, bias, out, N, C, H, W, O, KH, KW, stride_h, stride_w, dil_h,
                              dil_w, pad_top, pad_left, Ho, Wo, activation, max_limit, coefficient);
