@@ -281,6 +281,21 @@ int mb_activation_f32(mb_context *ctx, const float *in, float *out, int64_t size
 int mb_softmax_f32(mb_context *ctx, const float *in, float *out, int64_t outer,
                    int64_t classes, int64_t inner, int use_log);
 
+/* ---- Quantize / Dequantize: replace QuantizeUtil<float, uint8_t> as the
+ * Quantize and Dequantize operators use it (mace/core/quantize.h:128-215,
+ * mace/ops/quantize.cc:31-115).
+ *   q = Saturate<uint8_t>(roundf(zero_point + (1 / scale) * x))
+ *   x = scale * (q - zero_point)          (q uint8, or int32 with in_is_int32)
+ * mb_minmax_f32 is FindMinMax (quantize.h:90-102); it waits for the stream and
+ * returns the two values in HOST memory, for AdjustRange to derive scale and
+ * zero point from.  It cannot be captured into a graph. */
+int mb_quantize_f32_u8(mb_context *ctx, const float *in, uint8_t *out,
+                       int64_t size, float scale, int32_t zero_point);
+int mb_dequantize_f32(mb_context *ctx, const void *in, int in_is_int32,
+                      float *out, int64_t size, float scale, int32_t zero_point);
+int mb_minmax_f32(mb_context *ctx, const float *in, int64_t size,
+                  float *host_min, float *host_max);
+
 /* ---- uint8 GEMM without any allocation ------------------------------------
  * No counterpart in the reference.  For callers that may not allocate device
  * memory (a real-time loop with a fixed memory budget, a plugin inside an

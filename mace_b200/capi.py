@@ -81,6 +81,9 @@ PROTOTYPES = {
     "mb_eltwise_f32": (_int, [_vp] * 4 + [_i64, _int, _f32, _int, _f32, _f32, _int]),
     "mb_activation_f32": (_int, [_vp] * 3 + [_i64, _int, _f32, _f32]),
     "mb_softmax_f32": (_int, [_vp] * 3 + [_i64] * 3 + [_int]),
+    "mb_quantize_f32_u8": (_int, [_vp] * 3 + [_i64, _f32, _i32]),
+    "mb_dequantize_f32": (_int, [_vp, _vp, _int, _vp, _i64, _f32, _i32]),
+    "mb_minmax_f32": (_int, [_vp, _vp, _i64, C.POINTER(_f32), C.POINTER(_f32)]),
     "mb_gemm_u8_static_scratch": (_int, [_vp] * 5 + [_int] + [_i64] * 3 + [_int] * 2 +
                                   [_i32] * 5 + [_int, C.c_char_p, _sz]),
 }
@@ -324,6 +327,18 @@ class Context:
     def softmax_f32(self, x, out, outer, classes, inner, use_log=False):
         self._check(lib().mb_softmax_f32(self.h, x.ptr, out.ptr, outer, classes, inner,
                                          1 if use_log else 0))
+
+    def quantize_f32_u8(self, x, out, size, scale, zero_point):
+        self._check(lib().mb_quantize_f32_u8(self.h, x.ptr, out.ptr, size, scale, zero_point))
+
+    def dequantize_f32(self, q, out, size, scale, zero_point, int32=False):
+        self._check(lib().mb_dequantize_f32(self.h, q.ptr, 1 if int32 else 0, out.ptr, size, scale,
+                                            zero_point))
+
+    def minmax_f32(self, x, size):
+        mn, mx = _f32(), _f32()
+        self._check(lib().mb_minmax_f32(self.h, x.ptr, size, C.byref(mn), C.byref(mx)))
+        return mn.value, mx.value
 
     def avgpool_u8(self, x, out, N, H, W, Cc, kernel, strides, pad_tl, out_hw):
         self._check(lib().mb_avgpool_u8_nhwc(

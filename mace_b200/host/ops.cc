@@ -125,6 +125,8 @@ template <RuntimeType D, class T> class PoolingOp;
 template <RuntimeType D, class T> class EltwiseOp;
 template <RuntimeType D, class T> class ActivationOp;
 template <RuntimeType D, class T> class SoftmaxOp;
+template <RuntimeType D, class T> class QuantizeOp;
+template <RuntimeType D, class T> class DequantizeOp;
 
 template <>
 class Conv2dOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
@@ -653,6 +655,57 @@ class SoftmaxOp<RuntimeType::RT_CUDA, float> : public Operation {
   int axis_;
 };
 
+// Quantize (mace/ops/quantize.cc:31-74): float -> uint8 with the output tensor's scale and
+// zero point, or, when the output has no scale yet (or find_range_every_time), with the
+// range of the data; that path reads min and max back to the host and cannot be captured.
+template <>
+class QuantizeOp<RuntimeType::RT_CUDA, uint8_t> : public Operation {
+ public:
+  explicit QuantizeOp(OpConstructContext *context)
+      : Operation(context),
+        non_zero_(GetOptionalArg<int>("non_zero", 0) != 0),
+        find_range_every_time_(GetOptionalArg<bool>("find_range_every_time", false)) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0);
+    Tensor *output = Output(0);
+    if (input->dtype() != DT_FLOAT) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Quantize input must be float");
+    MACE_RETURN_IF_ERROR(output->Resize(input->shape()));
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    if (find_range_every_time_ || !(output->scale() > 0.f)) {
+      float mn = 0.f, mx = 0.f, scale = 0.f;
+      int32_t zero_point = 0;
+      MACE_RETURN_IF_ERROR(rt->Status(mb_minmax_f32(rt->ctx(), input->memory<float>(), input->size(), &mn, &mx)));
+      AdjustRangeU8(mn, mx, non_zero_, &scale, &zero_point);
+      output->SetScale(scale);
+      output->SetZeroPoint(zero_point);
+    }
+    return rt->Status(mb_quantize_f32_u8(rt->ctx(), input->memory<float>(), output->mutable_memory<uint8_t>(),
+                                         input->size(), output->scale(), output->zero_point()));
+  }
+
+ private:
+  bool non_zero_, find_range_every_time_;
+};
+
+// Dequantize (mace/ops/quantize.cc:79-104): uint8 or int32 -> float with the input's scale
+// and zero point.
+template <class T>
+class DequantizeOp<RuntimeType::RT_CUDA, T> : public Operation {
+ public:
+  explicit DequantizeOp(OpConstructContext *context) : Operation(context) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0);
+    Tensor *output = Output(0);
+    MACE_RETURN_IF_ERROR(output->Resize(input->shape()));
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    return rt->Status(mb_dequantize_f32(rt->ctx(), input->memory<T>(), std::is_same<T, int32_t>::value ? 1 : 0,
+                                        output->mutable_memory<float>(), input->size(), input->scale(),
+                                        input->zero_point()));
+  }
+};
+
 #define MACE_REGISTER_OP(registry, op_type, class_name, runtime, dt)                             \
   registry->Register(op_type, runtime, DataTypeToEnum<dt>::value,                                \
                      [](OpConstructContext *context) -> std::unique_ptr<Operation> {             \
@@ -673,6 +726,9 @@ void RegisterAllCudaOps(OpRegistry *registry) {
   MACE_REGISTER_OP(registry, "Eltwise", EltwiseOp, RuntimeType::RT_CUDA, float);
   MACE_REGISTER_OP(registry, "Activation", ActivationOp, RuntimeType::RT_CUDA, float);
   MACE_REGISTER_OP(registry, "Softmax", SoftmaxOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "Quantize", QuantizeOp, RuntimeType::RT_CUDA, uint8_t);
+  MACE_REGISTER_OP(registry, "Dequantize", DequantizeOp, RuntimeType::RT_CUDA, uint8_t);
+  MACE_REGISTER_OP(registry, "Dequantize", DequantizeOp, RuntimeType::RT_CUDA, int32_t);
 }
 
 }  // namespace ops

@@ -24,6 +24,29 @@ enum MatrixMajor { RowMajor, ColMajor };
 }  // namespace ops
 
 // multiplier in [0.5, 1) * 2^31 and a binary exponent, from a double.
+// AdjustRange<uint8_t> (mace/core/quantize.h:28-66): the range is widened to contain 0, which
+// must quantize to an integer; non_zero nudges the minimum so that it quantizes to >= 1.
+inline void AdjustRangeU8(const float in_min_data, const float in_max_data, const bool non_zero,
+                          float *scale, int32_t *zero_point) {
+  const int quantized_min = 0, quantized_max = 255;
+  float out_max = std::max(0.f, in_max_data);
+  float out_min = std::min(0.f, in_min_data);
+  if (non_zero)
+    out_min = std::min(out_min, in_min_data - (out_max - in_min_data) / (quantized_max - quantized_min - 1));
+  *scale = (out_max - out_min) / (quantized_max - quantized_min);
+  const float kEps = 1e-6;
+  if (out_min < -kEps && out_max > kEps) {
+    const float quantized_zero = -out_min / *scale;
+    const int32_t near_int = static_cast<int32_t>(roundf(quantized_zero));
+    *zero_point = near_int;
+    if (fabs(quantized_zero - near_int) > kEps && non_zero) *zero_point = static_cast<int32_t>(std::ceil(quantized_zero));
+  } else if (out_min > -kEps) {
+    *zero_point = quantized_min;
+  } else {
+    *zero_point = quantized_max;
+  }
+}
+
 inline void QuantizeMultiplier(double multiplier, int32_t *output_multiplier, int32_t *shift) {
   int exponent = 0;
   const double mantissa = std::frexp(multiplier, &exponent);

@@ -984,4 +984,13 @@ int orc_softmax_f32(const float *in, float *out, int64_t outer, int64_t classes,
   return 0;
 }
 
+void orc_dequantize_u8(const uint8_t *in, int64_t n, float scale, int32_t zero_point, float *out) {
+  // QuantizeUtil::Dequantize (mace/core/quantize.h:187-197)
+  for (int64_t i = 0; i < n; ++i) out[i] = scale * (in[i] - zero_point);
+}
+
+void orc_dequantize_i32(const int32_t *in, int64_t n, float scale, int32_t zero_point, float *out) {
+  for (int64_t i = 0; i < n; ++i) out[i] = scale * (in[i] - zero_point);
+}
+
 }  // extern "C"

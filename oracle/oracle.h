@@ -215,6 +215,10 @@ int orc_activation_f32(const float *in, float *out, int64_t size, int act, float
  * [outer, classes, inner]. */
 int orc_softmax_f32(const float *in, float *out, int64_t outer, int64_t classes, int64_t inner, int use_log);
 
+/* QuantizeUtil::Dequantize (mace/core/quantize.h:187-197): scale * (q - zero_point). */
+void orc_dequantize_u8(const uint8_t *in, int64_t n, float scale, int32_t zero_point, float *out);
+void orc_dequantize_i32(const int32_t *in, int64_t n, float scale, int32_t zero_point, float *out);
+
 #ifdef __cplusplus
 }
 #endif

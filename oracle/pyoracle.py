@@ -77,6 +77,10 @@ def lib():
         _lib.orc_eltwise_f32.argtypes = [_vp] * 3 + [_i64, _int, _f32, _int, _f32, _f32, _int]
         _lib.orc_activation_f32.argtypes = [_vp] * 2 + [_i64, _int, _f32, _f32]
         _lib.orc_softmax_f32.argtypes = [_vp] * 2 + [_i64] * 3 + [_int]
+        _lib.orc_dequantize_u8.restype = None
+        _lib.orc_dequantize_u8.argtypes = [_vp, _i64, _f32, _i32, _vp]
+        _lib.orc_dequantize_i32.restype = None
+        _lib.orc_dequantize_i32.argtypes = [_vp, _i64, _f32, _i32, _vp]
     return _lib
 
 
@@ -320,3 +324,21 @@ def softmax_f32(x, outer, classes, inner, use_log=False):
     st = lib().orc_softmax_f32(_p(x), _p(out), outer, classes, inner, 1 if use_log else 0)
     assert st == 0
     return out
+
+
+def dequantize(q, scale, zp):
+    """uint8 or int32 -> float32: scale * (q - zp)."""
+    q = np.ascontiguousarray(q)
+    out = np.empty(q.shape, np.float32)
+    if q.dtype == np.uint8:
+        lib().orc_dequantize_u8(_p(q), q.size, scale, zp, _p(out))
+    else:
+        q = _c(q, np.int32)
+        lib().orc_dequantize_i32(_p(q), q.size, scale, zp, _p(out))
+    return out
+
+
+def find_min_max(x):
+    """FindMinMax (mace/core/quantize.h:90-102)."""
+    x = np.asarray(x, np.float32)
+    return float(x.min()), float(x.max())

@@ -246,3 +246,49 @@ def test_matmul_and_fully_connected_float(net, orc):
     ref = orc.gemv_f32(w.reshape(10, 128), x.reshape(5, 128), b, 5, 10, 128)
     assert net.shape("Y") == (5, 10, 1, 1)
     assert _rel(net.read("Y", np.float32).ravel(), ref) <= 1e-4
+
+
+@pytest.mark.parametrize("values", [[-2, -1, 0, 1, 2, 3, 4], [0, 1, 2, 3, 4], [2, 3, 4, 5, 6], [2, 4, 6, 8],
+                                    [-2, -4, -6, -8]])
+@pytest.mark.parametrize("non_zero", [0, 1])
+def test_quantize_dequantize_ops(net, orc, values, non_zero):
+    """QuantizeTest.TestQuantize (test/ccunit/mace/ops/quantize_test.cc:22-77) through
+    QuantizeOp / DequantizeOp of the CUDA runtime: the range comes from the data."""
+    from mace_b200 import hostapi as H
+    x = np.array(values, np.float32)
+    net.add_tensor("Input", x)
+    net.op("Quantize", "QuantizeTest", ["Input"], ["QuantizeOutput"], T=H.DT_UINT8, out_dtype=H.DT_UINT8,
+           i={"non_zero": non_zero})
+    net.op("Dequantize", "DeQuantizeTest", ["QuantizeOutput"], ["Output"], T=H.DT_UINT8, out_dtype=H.DT_FLOAT)
+    net.run()
+    q = net.read("QuantizeOutput", np.uint8)
+    scale, zp = net.quant("QuantizeOutput")
+    assert (scale, zp) == orc.adjust_range(*orc.find_min_max(x), bool(non_zero))
+    assert np.array_equal(q, orc.quantize(x, scale, zp))
+    if non_zero:
+        assert (q > 0).all()
+    out = net.read("Output", np.float32)
+    assert np.array_equal(out, orc.dequantize(q, scale, zp))
+    assert np.abs(out - x).max() <= 0.1
+
+
+def test_quantize_with_given_range_then_conv(net, orc):
+    """A float input quantized with the output tensor's preset scale (the converter's
+    quantize_info), fed to a quantized 1x1 convolution and dequantized again."""
+    from mace_b200 import hostapi as H
+    rng = np.random.Generator(np.random.PCG64(5))
+    x = rng.random((2, 9, 9, 16), dtype=np.float32) * 4 - 1
+    w = rng.integers(0, 256, (8, 1, 1, 16), dtype=np.uint8)
+    net.add_tensor("Input", x)
+    net.add_tensor("W", w, scale=0.01, zero_point=120, is_weight=True)
+    net.op("Quantize", "q", ["Input"], ["Xq"], T=H.DT_UINT8, out_dtype=H.DT_UINT8, out_quant=[(4 / 255.0, 64)])
+    net.op("Conv2D", "conv", ["Xq", "W"], ["Yq"], out_quant=[(0.05, 100)],
+           ints={"strides": [1, 1], "dilations": [1, 1]}, i={"padding": H.VALID})
+    net.op("Dequantize", "dq", ["Yq"], ["Y"], T=H.DT_UINT8, out_dtype=H.DT_FLOAT)
+    net.run()
+    xq = orc.quantize(x, np.float32(4 / 255.0), 64)
+    assert np.array_equal(net.read("Xq", np.uint8), xq)
+    m, sh = orc.output_multiplier_and_shift(np.float32(4 / 255.0), np.float32(0.01), np.float32(0.05))
+    yq = orc.conv2d_u8(xq, w, None, (1, 1), (0, 0), (9, 9), 64, 120, m, sh, 100)
+    assert np.array_equal(net.read("Yq", np.uint8), yq)
+    assert np.array_equal(net.read("Y", np.float32), orc.dequantize(yq, np.float32(0.05), 100))

@@ -240,3 +240,26 @@ def test_avgpool_u8(ctx, orc, case):
     ctx.avgpool_u8(dx, do, N, H, W, C, (KH, KW), (stride, stride), (ph >> 1, pw >> 1), (Ho, Wo))
     got = ctx.download(do, exp.shape, np.uint8)
     assert np.array_equal(got, exp)
+
+
+@pytest.mark.parametrize("size", [1, 7, 4096, 1000003])
+def test_quantize_dequantize_minmax(ctx, orc, size):
+    """Quantize / Dequantize / FindMinMax on the device, bit-exact against the oracle, with
+    values that hit both saturation ends and exact rounding ties."""
+    rng = np.random.Generator(np.random.PCG64(size))
+    x = (rng.standard_normal(size) * 3).astype(np.float32)
+    x[:: max(1, size // 50)] = 0.5 * 0.0625 * np.arange(len(x[:: max(1, size // 50)]))  # ties at scale 1/16
+    dx, dq, dy = ctx.upload(x), ctx.alloc(size), ctx.alloc(size * 4)
+    assert ctx.minmax_f32(dx, size) == orc.find_min_max(x)
+    for scale, zp in ((0.0625, 128), (0.02, 3), (0.11, 250)):
+        ctx.quantize_f32_u8(dx, dq, size, scale, zp)
+        q = ctx.download(dq, (size,), np.uint8)
+        assert np.array_equal(q, orc.quantize(x, scale, zp))
+        ctx.dequantize_f32(dq, dy, size, scale, zp)
+        assert np.array_equal(ctx.download(dy, (size,), np.float32), orc.dequantize(q, scale, zp))
+    acc = rng.integers(-2 ** 20, 2 ** 20, size=size, dtype=np.int32)
+    da = ctx.upload(acc)
+    ctx.dequantize_f32(da, dy, size, 3.7e-4, 0, int32=True)
+    assert np.array_equal(ctx.download(dy, (size,), np.float32), orc.dequantize(acc, 3.7e-4, 0))
+    for b in (dx, dq, dy, da):
+        b.free()

@@ -4,6 +4,7 @@ These literals come from the reference's unit tests (tests/golden/reference_kats
 cites file:line for each); they are what pins the oracle.
 """
 import numpy as np
+import pytest
 
 PAD = {"VALID": 0, "SAME": 1, "FULL": 2}
 
@@ -207,3 +208,23 @@ def test_softmax_f32_known_answers(orc):
     nchw = np.ascontiguousarray(x.reshape(2, 4).T).reshape(1, 4, 2, 1)
     got = orc.softmax_f32(nchw, 1, 4, 2).reshape(4, 2).T.ravel()
     assert np.allclose(got, want, atol=1e-5)
+
+
+QUANT_CASES = [[-2, -1, 0, 1, 2, 3, 4], [0, 1, 2, 3, 4], [2, 3, 4, 5, 6], [2, 4, 6, 8], [-2, -4, -6, -8]]
+
+
+@pytest.mark.parametrize("values", QUANT_CASES)
+@pytest.mark.parametrize("non_zero", [False, True])
+def test_quantize_dequantize_known_answers(orc, values, non_zero):
+    """QuantizeTest.TestQuantize (test/ccunit/mace/ops/quantize_test.cc:22-77): the range is
+    found from the data, a round trip stays within 0.1, non_zero leaves no 0 in the output."""
+    x = np.array(values, np.float32)
+    mn, mx = orc.find_min_max(x)
+    scale, zp = orc.adjust_range(mn, mx, non_zero)
+    q = orc.quantize(x, scale, zp)
+    if non_zero:
+        assert (q > 0).all()
+    assert np.abs(orc.dequantize(q, scale, zp) - x).max() <= 0.1
+    assert 0 <= zp <= 255
+    # zero is exactly representable
+    assert orc.dequantize(np.array([zp], np.uint8), scale, zp)[0] == 0.0
