@@ -681,6 +681,7 @@ def run_resnet(args, rank, world):
     batch = args.batch or 256
     nodes, weights = rn.build(seed=0)
     eng = rn.build_engine(hostapi, nodes, weights, batch, device=local)
+    merged = 0 if args.no_fuse else eng.fuse_activations()  # residual sum + ReLU in one pass
     ctx = RawContext(eng.context)
     x = rn.random_images(batch, seed=100 + rank)
     hin = ctx.pinned(x.nbytes)
@@ -764,6 +765,7 @@ def run_resnet(args, rank, world):
                        "macs_per_image": macs,
                        "parallelism": "dp%d: batch sharded, weights replicated, final logits gather only" % world,
                        "launch": "operator by operator" if args.no_graph else "CUDA graph replay",
+                       "merged_sum_relu_pairs": merged,
                        "l2": "activations of one step (%.1f GB) exceed L2" % (alg_bytes / 1e9)},
             "roofline": {"bound": "tensor", "achieved": round(tflops, 2), "peak": round(tf32_peak, 1),
                          "unit": "TFLOP/s", "frac": round(tflops / tf32_peak, 4), "traffic": None,
@@ -930,6 +932,8 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="images per GPU for resnet50_f32_b256 (default 256)")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every operator separately instead of replaying a CUDA graph")
+    ap.add_argument("--no-fuse", action="store_true",
+                    help="resnet50_f32_b256: keep residual sums and their ReLUs as separate operators")
     ap.add_argument("--profile", action="store_true",
                     help="run only the device-resident timed loop (for ncu captures)")
     args = ap.parse_args()

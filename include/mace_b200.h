@@ -89,7 +89,8 @@ uint64_t mb_launch_count_tensor_core(const mb_context *ctx);
  * in scratch instead of describing them to the tensor core directly),
  * "col_budget_mb" (1024 default: the fp32 general convolution gathers the
  * im2col columns of as many images at a time as fit into this many MiB of
- * scratch). */
+ * scratch), "wino_plane" (1 default; 0 takes the one-thread-per-tile Winograd
+ * output transform instead of the plane-at-a-time one, for A/B tests). */
 int mb_set_option(mb_context *ctx, const char *name, int value);
 
 /* ---- uint8 GEMM: replaces the gemmlowp calls of MatMulOp<RT_CPU,uint8_t>
@@ -267,6 +268,15 @@ int mb_pooling_f32_nchw(mb_context *ctx, const float *in, float *out, int64_t N,
 int mb_eltwise_f32(mb_context *ctx, const float *in0, const float *in1,
                    float *out, int64_t size, int type, float scalar_input,
                    int has_coeff, float coeff0, float coeff1, int swapped);
+
+/* The same followed by an activation (codes as above) in one pass: what a net
+ * runs when it has merged an Eltwise with the Activation operator that
+ * consumes it (a residual sum and its ReLU).  No counterpart in the CPU
+ * runtime, which runs the two operators one after the other. */
+int mb_eltwise_act_f32(mb_context *ctx, const float *in0, const float *in1,
+                       float *out, int64_t size, int type, float scalar_input,
+                       int has_coeff, float coeff0, float coeff1, int swapped,
+                       int activation, float max_limit, float coefficient);
 
 /* Standalone activation: replaces ref::Activation / arm::Activation
  * (mace/ops/ref/activation.cc:61-88) for the activation codes listed above.

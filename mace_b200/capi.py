@@ -79,6 +79,7 @@ PROTOTYPES = {
                                      [_int, _f32, _f32, _int]),
     "mb_pooling_f32_nchw": (_int, [_vp] * 3 + [_i64] * 6 + [_int] * 6 + [_i64] * 2 + [_int]),
     "mb_eltwise_f32": (_int, [_vp] * 4 + [_i64, _int, _f32, _int, _f32, _f32, _int]),
+    "mb_eltwise_act_f32": (_int, [_vp] * 4 + [_i64, _int, _f32, _int, _f32, _f32, _int, _int, _f32, _f32]),
     "mb_activation_f32": (_int, [_vp] * 3 + [_i64, _int, _f32, _f32]),
     "mb_softmax_f32": (_int, [_vp] * 3 + [_i64] * 3 + [_int]),
     "mb_quantize_f32_u8": (_int, [_vp] * 3 + [_i64, _f32, _i32]),
@@ -315,11 +316,12 @@ class Context:
             self.h, x.ptr, out.ptr, N, Cc, H, W, kernel[0], kernel[1], strides[0], strides[1],
             dil[0], dil[1], pad_tl[0], pad_tl[1], out_hw[0], out_hw[1], pooling_type))
 
-    def eltwise_f32(self, a, b, out, size, type_, coeff=None, swapped=False, scalar=1.0):
+    def eltwise_f32(self, a, b, out, size, type_, coeff=None, swapped=False, scalar=1.0, act=0,
+                    max_limit=0.0, coef=0.0):
         c = coeff if coeff else (0.0, 0.0)
-        self._check(lib().mb_eltwise_f32(
+        self._check(lib().mb_eltwise_act_f32(
             self.h, a.ptr, b.ptr if b is not None else None, out.ptr, size, type_, scalar,
-            1 if coeff else 0, c[0], c[1], 1 if swapped else 0))
+            1 if coeff else 0, c[0], c[1], 1 if swapped else 0, act, max_limit, coef))
 
     def activation_f32(self, x, out, size, act, max_limit=0.0, coef=0.0):
         self._check(lib().mb_activation_f32(self.h, x.ptr, out.ptr, size, act, max_limit, coef))

@@ -47,6 +47,7 @@ struct mb_context {
                                  // operand-sum kernel) ends; it waits for it where it reads the sums
   void *skinny_ws = nullptr;     // arrival counters of the few-row GEMM (zero between calls)
   size_t skinny_ws_bytes = 0;
+  int wino_plane = 1;            // plane-at-a-time Winograd output transform (0: per-tile kernel)
   int64_t col_budget_bytes = 1ll << 30;  // im2col column matrix of the fp32 general convolution:
                                          // images are processed in chunks that stay below this
   char last_error[512] = {0};

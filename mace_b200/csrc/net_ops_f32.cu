@@ -63,10 +63,12 @@ struct EltParams {
   int64_t size;
   float scalar, c0, c1;
   int has_coeff, swapped;
+  int act;  // activation applied to the result (0: none)
+  float max_limit, coef;
 };
 
 template <int TYPE>
-__device__ __forceinline__ float elt_apply(float a, float b, const EltParams &p) {
+__device__ __forceinline__ float elt_op(float a, float b, const EltParams &p) {
   switch (TYPE) {
     case ELT_SUM:
       // products and sum rounded separately, as the C++ expression a * c0 + b * c1 is
@@ -82,6 +84,11 @@ __device__ __forceinline__ float elt_apply(float a, float b, const EltParams &p)
     case ELT_CLIP: return fmaxf(p.c0, fminf(p.c1, a));
     default: return a;
   }
+}
+
+template <int TYPE>
+__device__ __forceinline__ float elt_apply(float a, float b, const EltParams &p) {
+  return mb_activate(elt_op<TYPE>(a, b, p), p.act, p.max_limit, p.coef);
 }
 
 template <int TYPE>
@@ -199,10 +206,13 @@ int mb_pooling_f32_nchw(mb_context *ctx, const float *in, float *out, int64_t N,
   return MB_SUCCESS;
 }
 
-int mb_eltwise_f32(mb_context *ctx, const float *in0, const float *in1, float *out, int64_t size, int type,
-                   float scalar_input, int has_coeff, float coeff0, float coeff1, int swapped) {
+int mb_eltwise_act_f32(mb_context *ctx, const float *in0, const float *in1, float *out, int64_t size, int type,
+                       float scalar_input, int has_coeff, float coeff0, float coeff1, int swapped,
+                       int activation, float max_limit, float coefficient) {
   if (ctx == nullptr) return MB_INVALID_ARGS;
   if (size < 0) return mb_fail(ctx, MB_INVALID_ARGS, "mb_eltwise_f32: negative size");
+  if (!(activation == 0 || activation == 1 || activation == 2 || activation == 6))
+    return mb_fail(ctx, MB_UNSUPPORTED, "mb_eltwise_act_f32: activation %d is not built for this runtime", activation);
   if (size == 0) return MB_SUCCESS;
   if (in0 == nullptr || out == nullptr) return mb_fail(ctx, MB_INVALID_ARGS, "mb_eltwise_f32: null operand");
   if (type == ELT_CLIP && !(has_coeff && coeff0 < coeff1))
@@ -214,6 +224,7 @@ int mb_eltwise_f32(mb_context *ctx, const float *in0, const float *in1, float *o
   p.c0 = (swapped && type == ELT_SUM) ? coeff1 : coeff0;
   p.c1 = (swapped && type == ELT_SUM) ? coeff0 : coeff1;
   p.has_coeff = has_coeff; p.swapped = swapped;
+  p.act = activation; p.max_limit = max_limit; p.coef = coefficient;
   const uintptr_t bits = reinterpret_cast<uintptr_t>(in0) | reinterpret_cast<uintptr_t>(in1) |
                          reinterpret_cast<uintptr_t>(out);
   const int vec4 = (bits & 15u) == 0;
@@ -233,6 +244,12 @@ int mb_eltwise_f32(mb_context *ctx, const float *in0, const float *in1, float *o
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   return MB_SUCCESS;
+}
+
+int mb_eltwise_f32(mb_context *ctx, const float *in0, const float *in1, float *out, int64_t size, int type,
+                   float scalar_input, int has_coeff, float coeff0, float coeff1, int swapped) {
+  return mb_eltwise_act_f32(ctx, in0, in1, out, size, type, scalar_input, has_coeff, coeff0, coeff1, swapped, 0,
+                            0.f, 0.f);
 }
 
 int mb_activation_f32(mb_context *ctx, const float *in, float *out, int64_t size, int activation,

@@ -231,6 +231,13 @@ int mbh_run(mbh_engine *e) {
   return MaceStatus::MACE_SUCCESS;
 }
 
+int mbh_fuse_activations(mbh_engine *e, int *merged) {
+  if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  const int n = e->net->FuseActivations();
+  if (merged != nullptr) *merged = n;
+  return MaceStatus::MACE_SUCCESS;
+}
+
 int mbh_capture(mbh_engine *e) {
   if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
   MBH_TRY(e, e->net->Capture());

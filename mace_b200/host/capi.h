@@ -52,6 +52,12 @@ int mbh_op_arg_float(mbh_engine *engine, const char *key, float value);
 int mbh_op_arg_str(mbh_engine *engine, const char *key, const char *value);
 int mbh_op_end(mbh_engine *engine);
 
+/* Merges each Activation operator into the operator producing its input where that operator
+ * can apply the activation itself (the float Eltwise) and nothing else reads the tensor in
+ * between, which is then no longer written.  *merged (may be NULL) receives the number of
+ * merged pairs. */
+int mbh_fuse_activations(mbh_engine *engine, int *merged);
+
 /* Runs all operators once (asynchronously on the engine's stream). */
 int mbh_run(mbh_engine *engine);
 int mbh_sync(mbh_engine *engine);

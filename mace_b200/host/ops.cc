@@ -580,14 +580,31 @@ class EltwiseOp<RuntimeType::RT_CUDA, float> : public Operation {
     Tensor *output = Output(0);
     MACE_RETURN_IF_ERROR(output->Resize(input0->shape()));
     CudaRuntime *rt = CudaRuntimeOf(context);
-    return rt->Status(mb_eltwise_f32(rt->ctx(), input0->memory<float>(),
-                                     input1 != nullptr ? input1->memory<float>() : nullptr,
-                                     output->mutable_memory<float>(), input0->size(), type_, scalar_input_,
-                                     coeff_.empty() ? 0 : 1, coeff_.empty() ? 0.f : coeff_[0],
-                                     coeff_.empty() ? 0.f : coeff_[1], swapped ? 1 : 0));
+    return rt->Status(mb_eltwise_act_f32(rt->ctx(), input0->memory<float>(),
+                                         input1 != nullptr ? input1->memory<float>() : nullptr,
+                                         output->mutable_memory<float>(), input0->size(), type_, scalar_input_,
+                                         coeff_.empty() ? 0 : 1, coeff_.empty() ? 0.f : coeff_[0],
+                                         coeff_.empty() ? 0.f : coeff_[1], swapped ? 1 : 0,
+                                         static_cast<int>(fused_act_), fused_max_limit_, fused_coefficient_));
+  }
+
+  bool AbsorbActivation(const OperatorDef &def, Tensor *activation_output) override {
+    if (fused_act_ != NOOP || def.input.size() != 1) return false;  // PRELU has an alpha input
+    auto name = def.s.find("activation");
+    MaceStatus st;
+    const ActivationType act = StringToActivationType(name == def.s.end() ? "NOOP" : name->second, &st);
+    if (st != MaceStatus::MACE_SUCCESS) return false;
+    auto limit = def.f.find("max_limit"), coef = def.f.find("activation_coefficient");
+    fused_act_ = act;
+    fused_max_limit_ = limit == def.f.end() ? 0.f : limit->second;
+    fused_coefficient_ = coef == def.f.end() ? 0.f : coef->second;
+    outputs_[0] = activation_output;
+    return true;
   }
 
  private:
+  ActivationType fused_act_ = NOOP;
+  float fused_max_limit_ = 0.f, fused_coefficient_ = 0.f;
   int type_;
   std::vector<float> coeff_;
   float scalar_input_;
@@ -754,7 +771,30 @@ MaceStatus SerialNet::AddOperator(const OperatorDef &def) {
     return st;
   }
   operators_.push_back(std::move(op));
+  skipped_.push_back(0);
   return MaceStatus::MACE_SUCCESS;
+}
+
+int SerialNet::FuseActivations() {
+  DropCapture();
+  std::map<std::string, int> readers;
+  for (const auto &d : defs_)
+    for (const std::string &in : d->input) ++readers[in];
+  int merged = 0;
+  for (size_t a = 0; a < defs_.size(); ++a) {
+    if (skipped_[a] || defs_[a]->type != "Activation" || defs_[a]->input.empty()) continue;
+    const std::string &mid = defs_[a]->input[0];
+    if (readers[mid] != 1) continue;
+    for (size_t pr = 0; pr < a; ++pr) {
+      if (skipped_[pr] || defs_[pr]->output.size() != 1 || defs_[pr]->output[0] != mid) continue;
+      if (operators_[pr]->AbsorbActivation(*defs_[a], operators_[a]->Output(0))) {
+        skipped_[a] = 1;
+        ++merged;
+      }
+      break;
+    }
+  }
+  return merged;
 }
 
 MaceStatus SerialNet::Capture() {
@@ -763,7 +803,7 @@ MaceStatus SerialNet::Capture() {
   MACE_RETURN_IF_ERROR(runtime_->Status(mb_graph_begin(runtime_->ctx())));
   MaceStatus st = MaceStatus::MACE_SUCCESS;
   for (size_t i = 0; i < operators_.size() && st == MaceStatus::MACE_SUCCESS; ++i)
-    st = operators_[i]->Run(&context);
+    if (!skipped_[i]) st = operators_[i]->Run(&context);
   void *graph = nullptr;
   MaceStatus end = runtime_->Status(mb_graph_end(runtime_->ctx(), &graph));
   if (st != MaceStatus::MACE_SUCCESS) {
@@ -793,7 +833,7 @@ MaceStatus SerialNet::Run(std::vector<CallStats> *run_metadata) {
     MACE_RETURN_IF_ERROR(runtime_->Status(mb_event_record(runtime_->ctx(), events[0])));
   }
   for (size_t i = 0; i < operators_.size(); ++i) {
-    MACE_RETURN_IF_ERROR(operators_[i]->Run(&context));
+    if (!skipped_[i]) MACE_RETURN_IF_ERROR(operators_[i]->Run(&context));
     if (run_metadata != nullptr)
       MACE_RETURN_IF_ERROR(runtime_->Status(mb_event_record(runtime_->ctx(), events[i + 1])));
   }

@@ -80,6 +80,15 @@ class Operation {
   int InputSize() const { return static_cast<int>(inputs_.size()); }
   const OperatorDef &debug_def() const { return *operator_def_; }
 
+  // Net-level merging of this operator with the Activation operator that consumes its only
+  // output: an operator that can apply the activation itself takes it over, writes into
+  // `activation_output` from then on and returns true; the net then skips the Activation.
+  virtual bool AbsorbActivation(const OperatorDef &activation_def, Tensor *activation_output) {
+    (void)activation_def;
+    (void)activation_output;
+    return false;
+  }
+
  protected:
   const OperatorDef *operator_def_;
   std::vector<const Tensor *> inputs_;
@@ -122,6 +131,12 @@ class SerialNet {
   // tensor shapes or operators.
   MaceStatus Capture();
   void DropCapture();
+  // Merges every Activation operator into the operator that produces its input when that
+  // operator can absorb it (the float Eltwise: a residual sum and its ReLU become one pass)
+  // and nothing else reads the intermediate tensor, which is then no longer written.
+  // Returns the number of merged pairs.  Off unless called: operator by operator the net
+  // behaves like the CPU runtime's.
+  int FuseActivations();
   bool captured() const { return graph_ != nullptr; }
   ~SerialNet() { DropCapture(); }
   size_t size() const { return operators_.size(); }
@@ -132,6 +147,7 @@ class SerialNet {
   CudaRuntime *runtime_;
   std::vector<std::unique_ptr<OperatorDef>> defs_;
   std::vector<std::unique_ptr<Operation>> operators_;
+  std::vector<char> skipped_;  // operators merged into their producer
   void *graph_ = nullptr;
 };
 

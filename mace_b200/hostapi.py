@@ -42,6 +42,7 @@ _PROTOS = {
     "mbh_run": [_vp],
     "mbh_sync": [_vp],
     "mbh_capture": [_vp],
+    "mbh_fuse_activations": [_vp, C.POINTER(_int)],
     "mbh_run_host": [_vp, _cp, _vp, _sz, _cp, _vp, _sz],
     "mbh_run_profiled": [_vp, C.POINTER(_f32), _int, C.c_char_p, _sz, C.POINTER(_int)],
 }
@@ -165,6 +166,12 @@ class HostEngine:
 
     def sync(self):
         self._check(lib().mbh_sync(self.h))
+
+    def fuse_activations(self):
+        """Merge Activation operators into the Eltwise that feeds them; returns how many."""
+        n = _int()
+        self._check(lib().mbh_fuse_activations(self.h, C.byref(n)))
+        return n.value
 
     def capture(self):
         """Record the chain into a CUDA graph (after one plain run); later runs replay it."""

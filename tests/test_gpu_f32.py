@@ -162,6 +162,13 @@ def test_winograd_f32(ctx, orc, case):
     ctx.winograd_f32(dx, None, db, do, N, C, H, W, O, (ph >> 1, pw >> 1), (Ho, Wo), act, 0.5, 0.0,
                      transformed=dU)
     assert np.array_equal(ctx.download(do, direct.shape, np.float32), got)
+    # the one-thread-per-tile output transform computes the same values as the plane-at-a-time one
+    ctx.set_option("wino_plane", 0)
+    try:
+        ctx.winograd_f32(dx, df, db, do, N, C, H, W, O, (ph >> 1, pw >> 1), (Ho, Wo), act, 0.5, 0.0)
+    finally:
+        ctx.set_option("wino_plane", 1)
+    assert np.array_equal(ctx.download(do, direct.shape, np.float32), got)
 
 
 def test_dwconv_f32(ctx, orc, kats):

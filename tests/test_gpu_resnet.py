@@ -120,5 +120,35 @@ def test_resnet50_graph_against_oracle(orc, cfg):
         eng.capture()
         eng.run()
         assert np.array_equal(eng.read("fc", np.float32), first)
+        # residual sums merged with their ReLUs: one merged pair per bottleneck block, the same
+        # bytes in every tensor that is still written
+        kept = {n["name"]: eng.read(n["name"], np.float32) for n in nodes if n["op"] != "add"}
+        assert eng.fuse_activations() == sum(1 for n in nodes if n["op"] == "add") == 16
+        eng.write("input", x)
+        eng.run()
+        for name, want in kept.items():
+            assert np.array_equal(eng.read(name, np.float32), want), name
+        eng.capture()
+        eng.run()
+        assert np.array_equal(eng.read("fc", np.float32), first)
     finally:
         eng.close()
+
+
+def test_activation_is_not_merged_when_the_sum_has_another_reader(net):
+    from mace_b200 import hostapi as H
+    a = np.arange(-3, 3, dtype=np.float32).reshape(1, 1, 2, 3)
+    net.add_tensor("A", a)
+    net.add_tensor("B", np.ones_like(a))
+    F = H.DT_FLOAT
+    net.op("Eltwise", "sum", ["A", "B"], ["Sum"], T=F, i={"type": 0})
+    net.op("Activation", "relu", ["Sum"], ["Relu"], T=F, s={"activation": "RELU"})
+    net.op("Eltwise", "neg", ["Sum"], ["Neg"], T=F, i={"type": 6})          # second reader of Sum
+    net.op("Eltwise", "sum2", ["A", "A"], ["Sum2"], T=F, i={"type": 0})
+    net.op("Activation", "relux", ["Sum2"], ["Relux"], T=F, s={"activation": "RELUX"}, f={"max_limit": 3.0})
+    assert net.fuse_activations() == 1       # only sum2 + relux
+    net.run()
+    assert net.read("Sum", np.float32).ravel().tolist() == [-2, -1, 0, 1, 2, 3]
+    assert net.read("Relu", np.float32).ravel().tolist() == [0, 0, 0, 1, 2, 3]
+    assert net.read("Neg", np.float32).ravel().tolist() == [2, 1, 0, -1, -2, -3]
+    assert net.read("Relux", np.float32).ravel().tolist() == [0, 0, 0, 0, 2, 3]
