@@ -368,9 +368,22 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    // Whole warp in the loop, one lane issues (see the producer).
-    {
+    // One thread runs the whole role; the other lanes go straight to the warp barrier below.
+    // What the thread does between two MMAs has to fit into the time the tensor pipe's short
+    // queue keeps it busy, and for tiles of one K step it is on the critical path outright:
+    // the descriptors are one add per step and nothing in the loop is warp-collective.
+    if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, A_MN, B_MN, BM, BN);
+      // K-major tile: rows of KB bytes, 8-row groups SBO bytes apart; a K step moves 32 bytes
+      // inside the swizzled row.  MN-major tile: k-rows of 128 bytes (128 elements of M or N),
+      // 8-k-row groups 1024 bytes apart, 128-element atoms 128 * KB bytes apart; a K step moves
+      // 32 k-rows = 4096 bytes.  The address field counts 16-byte units.
+      const uint64_t a_base = A_MN ? make_smem_desc(0, 128 * KB, 1024, SWIZZLE_128B) : make_smem_desc(0, 16, SBO, SWZ);
+      const uint64_t b_base = B_MN ? make_smem_desc(0, 128 * KB, 1024, SWIZZLE_128B) : make_smem_desc(0, 16, SBO, SWZ);
+      constexpr uint32_t a_step = (A_MN ? UMMA_K * 128 : UMMA_K) >> 4;
+      constexpr uint32_t b_step = (B_MN ? UMMA_K * 128 : UMMA_K) >> 4;
+      const int last_ksteps =
+          static_cast<int>((p.K - static_cast<int64_t>(p.k_blocks - 1) * KB + UMMA_K - 1) / UMMA_K);
       int stage = 0;
       uint32_t phase = 0;
       int acc_buf = 0;
@@ -378,7 +391,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       int local = 0;
       for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
-        if (!mbar_wait_warp(tempty_bar + 8 * acc_buf, acc_phase ^ 1, abort_flag, WAIT_BUDGET)) {
+        if (!mbar_wait(tempty_bar + 8 * acc_buf, acc_phase ^ 1, abort_flag, WAIT_BUDGET)) {
           *abort_flag = 1;
           atomicCAS(p.status, 0, MB_DEV_TIMEOUT_MMA);
           break;
@@ -386,7 +399,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc_buf * BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, WAIT_BUDGET)) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, WAIT_BUDGET)) {
             *abort_flag = 1;
             atomicCAS(p.status, 0, MB_DEV_TIMEOUT_MMA);
             ok = false;
@@ -394,49 +407,35 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           tc_fence_after_sync();
           if (local == 0) MB_STAMP(6 + (kb < 3 ? kb : 3));  // k-block kb landed
-          if (kb == p.k_blocks - 1 && lane == 0) MB_STAMP_TILE(local, 1);
+          if (kb == p.k_blocks - 1) MB_STAMP_TILE(local, 1);
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
-          const uint32_t sb = sa + Cfg::A_BYTES;
-          const int64_t k_left = p.K - static_cast<int64_t>(kb) * KB;
-          const int ksteps = k_left >= KB ? KB / UMMA_K
-                                          : static_cast<int>((k_left + UMMA_K - 1) / UMMA_K);
-          if (lane == 0) {
-#pragma unroll 4
-          for (int j = 0; j < ksteps; ++j) {
-            // K-major tile: rows of 128 bytes, 8-row groups 1024 bytes apart;
-            // a K step moves 32 bytes inside the swizzled row.
-            // MN-major tile: k-rows of 128 bytes (128 elements of M or N),
-            // 8-k-row groups 1024 bytes apart, 128-element atoms 16 KB apart;
-            // a K step moves 32 k-rows = 4096 bytes.
-            const uint64_t a_desc =
-                A_MN ? make_smem_desc(sa + j * UMMA_K * 128, 128 * KB, 1024, SWIZZLE_128B)
-                     : make_smem_desc(sa + j * UMMA_K, 16, SBO, SWZ);
-            const uint64_t b_desc =
-                B_MN ? make_smem_desc(sb + j * UMMA_K * 128, 128 * KB, 1024, SWIZZLE_128B)
-                     : make_smem_desc(sb + j * UMMA_K, 16, SBO, SWZ);
-            mma_i8_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          const uint64_t a_desc = a_base | static_cast<uint64_t>((sa >> 4) & 0x3FFFu);
+          const uint64_t b_desc = b_base | static_cast<uint64_t>(((sa + Cfg::A_BYTES) >> 4) & 0x3FFFu);
+          if (kb + 1 < p.k_blocks || last_ksteps == KB / UMMA_K) {
+#pragma unroll
+            for (int j = 0; j < KB / UMMA_K; ++j)
+              mma_i8_ss(d_tmem, a_desc + j * a_step, b_desc + j * b_step, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          } else {
+            for (int j = 0; j < last_ksteps; ++j)
+              mma_i8_ss(d_tmem, a_desc + j * a_step, b_desc + j * b_step, idesc, (kb > 0 || j > 0) ? 1u : 0u);
           }
           mma_commit(empty_bar + 8 * stage);  // frees the stage when the MMAs have read it
-          }
-          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        if (lane == 0) {
-          mma_commit(tfull_bar + 8 * acc_buf);  // accumulator complete
-          if (local == 0) MB_STAMP(10);
-          MB_STAMP_TILE(local, 2);
-        }
-        __syncwarp();
+        mma_commit(tfull_bar + 8 * acc_buf);  // accumulator complete
+        if (local == 0) MB_STAMP(10);
+        MB_STAMP_TILE(local, 2);
         if (++acc_buf == NUM_ACC) {
           acc_buf = 0;
           acc_phase ^= 1;
         }
       }
     }
+    __syncwarp();
   } else if (warp < FIRST_EPI_WARP) {
     // ---------------- preparation: operand sums (fused) and epilogue terms ----------------
     // Precomputed sums come from the kernel launched just before this one, which this grid
