@@ -189,24 +189,25 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    int local = 0;
-    int kstep = 0;
+    // One thread runs the role (see the MMA issuer); the other lanes wait at the warp barrier.
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      int kstep = 0;
 #ifdef MB_TC_TIMELINE
-    if (lane == 0 && p.timeline != nullptr && blockIdx.x == 0) p.timeline[0] = clock64();
+      if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[0] = clock64();
 #endif
-    for (FTileIter it(p); ok && it.valid(p); it.next(p), ++local) {
-      const int xb = p.x_batched ? it.b : 0, wb = p.w_batched ? it.b : 0;
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
-        if (!mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, F_WAIT_BUDGET)) {
-          *abort_flag = 1;
-          atomicCAS(p.status, 0, MB_DEV_TIMEOUT_PRODUCER);
-          ok = false;
-          break;
-        }
-        if (lane == 0) {
+      for (FTileIter it(p); ok && it.valid(p); it.next(p), ++local) {
+        const int xb = p.x_batched ? it.b : 0, wb = p.w_batched ? it.b : 0;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++kstep) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, F_WAIT_BUDGET)) {
+            *abort_flag = 1;
+            atomicCAS(p.status, 0, MB_DEV_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
           const uint32_t fb = full_bar + 8 * stage;
           const uint32_t sx = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sw = sx + Cfg::X_BYTES;
@@ -215,15 +216,14 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
           tma_load_3d(sx, &tmap_x, fb, it.tm * FBM, kb * FKB, xb);  // [32 k][128 m], 512-byte rows
           tma_load_3d(sw, &tmap_w, fb, kb * FKB, it.tn * BN, wb);
           if (kb == 0) MBF_STAMP_TILE(local, 0);
-        }
-        ++kstep;
-        __syncwarp();
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
         }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     // One thread runs the whole role.  The tensor pipe queues only a few MMAs, so everything

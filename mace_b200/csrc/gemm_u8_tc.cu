@@ -321,9 +321,8 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    // The whole warp walks the loop (one lane issues) so that the warp reaches
-    // the block-wide barrier at the end of the kernel as one.
-    {
+    // One thread runs the role (see the MMA issuer); the other lanes wait at the warp barrier.
+    if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -332,33 +331,30 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int b = it.b, tm = it.tm, tn = it.tn;
         const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait_warp(empty_bar + 8 * stage, phase ^ 1, abort_flag, WAIT_BUDGET)) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, WAIT_BUDGET)) {
             *abort_flag = 1;
             atomicCAS(p.status, 0, MB_DEV_TIMEOUT_PRODUCER);
             ok = false;
             break;
           }
-          if (lane == 0) {
-            const uint32_t fb = full_bar + 8 * stage;
-            const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
-            const uint32_t sb = sa + Cfg::A_BYTES;
-            mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
-            if (A_MN) {
-              tma_load_3d(sa, &tmap_a, fb, tm * BM, kb * KB, ab);
-            } else {
-              tma_load_3d(sa, &tmap_a, fb, kb * KB, tm * BM, ab);
-            }
-            if (B_MN) {
-#pragma unroll
-              for (int j = 0; j < (BN + 127) / 128; ++j)
-                tma_load_3d(sb + j * 128 * KB, &tmap_b, fb, tn * BN + j * 128, kb * KB, bb);
-            } else {
-              tma_load_3d(sb, &tmap_b, fb, kb * KB, tn * BN, bb);
-            }
-            if (local == 0) MB_STAMP(2 + (kb < 3 ? kb : 3));  // TMA of k-block kb issued
-            if (kb == 0) MB_STAMP_TILE(local, 0);
+          const uint32_t fb = full_bar + 8 * stage;
+          const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sb = sa + Cfg::A_BYTES;
+          mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
+          if (A_MN) {
+            tma_load_3d(sa, &tmap_a, fb, tm * BM, kb * KB, ab);
+          } else {
+            tma_load_3d(sa, &tmap_a, fb, kb * KB, tm * BM, ab);
           }
-          __syncwarp();
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < (BN + 127) / 128; ++j)
+              tma_load_3d(sb + j * 128 * KB, &tmap_b, fb, tn * BN + j * 128, kb * KB, bb);
+          } else {
+            tma_load_3d(sb, &tmap_b, fb, kb * KB, tn * BN, bb);
+          }
+          if (local == 0) MB_STAMP(2 + (kb < 3 ? kb : 3));  // TMA of k-block kb issued
+          if (kb == 0) MB_STAMP_TILE(local, 0);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -366,6 +362,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     // One thread runs the whole role; the other lanes go straight to the warp barrier below.
