@@ -327,6 +327,11 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;  // this CTA's tile counter (profiling stamps)
+      // When every tile of the launch reads the same B tile (one column of tiles, one K step,
+      // B shared by the batch: a pointwise convolution with few channels), each stage's copy
+      // of B is loaded once, on the first pass through the ring, and then left in place: TMA
+      // handles short rows one by one, and the B rows would be a third to a half of them.
+      const bool b_once = p.tiles_n == 1 && p.k_blocks == 1 && !p.b_batched;
       for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
         const int b = it.b, tm = it.tm, tn = it.tn;
         const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
@@ -340,13 +345,16 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t fb = full_bar + 8 * stage;
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + Cfg::A_BYTES;
-          mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
+          const bool skip_b = b_once && local >= STAGES;
+          mbar_arrive_expect_tx(fb, skip_b ? Cfg::A_BYTES : Cfg::STAGE_BYTES);
           if (A_MN) {
             tma_load_3d(sa, &tmap_a, fb, tm * BM, kb * KB, ab);
           } else {
             tma_load_3d(sa, &tmap_a, fb, kb * KB, tm * BM, ab);
           }
-          if (B_MN) {
+          if (skip_b) {
+            // B of this stage is already in place
+          } else if (B_MN) {
 #pragma unroll
             for (int j = 0; j < (BN + 127) / 128; ++j)
               tma_load_3d(sb + j * 128 * KB, &tmap_b, fb, tn * BN + j * 128, kb * KB, bb);
