@@ -47,6 +47,9 @@ struct mb_context {
                                  // operand-sum kernel) ends; it waits for it where it reads the sums
   void *skinny_ws = nullptr;     // arrival counters of the few-row GEMM (zero between calls)
   size_t skinny_ws_bytes = 0;
+  int pdl_chain = 1;             // kernels of an operator chain launched with programmatic stream
+                                 // serialization (each waits for its predecessor where it first
+                                 // touches global memory); 0: plain stream order
   int wino_plane = 1;            // plane-at-a-time Winograd output transform (0: per-tile kernel)
   int64_t col_budget_bytes = 1ll << 30;  // im2col column matrix of the fp32 general convolution:
                                          // images are processed in chunks that stay below this
@@ -58,6 +61,35 @@ int mb_check_cuda(mb_context *ctx, cudaError_t e, const char *what);
 // Returns a device pointer to at least `bytes` of scratch (256-byte aligned),
 // growing the arena if needed.  offset allows several carve-outs per call.
 int mb_scratch(mb_context *ctx, size_t bytes, void **ptr);
+
+// ---- programmatic dependent launch ------------------------------------------------------------
+// A kernel launched through mb_launch_chained may be started before the kernel in front of it in
+// the stream has finished: its CTAs run their prologue (barrier setup, tensor-memory
+// allocation, descriptor prefetch) on SMs the predecessor has already left, and every thread
+// calls mb_grid_dep_wait() before its first access to global memory, which returns when the
+// predecessor has completed and its writes are visible.  mb_grid_dep_launch(), called at the top
+// of a kernel, lets the kernel BEHIND it do the same.  Kernels launched the ordinary way are
+// full barriers in the stream, so the two kinds mix freely.
+__device__ __forceinline__ void mb_grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void mb_grid_dep_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t mb_launch_chained(mb_context *ctx, void (*kern)(KArgs...), dim3 grid, dim3 block,
+                                            size_t smem, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl_chain ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 #define MB_RETURN_IF_ERROR(expr)        \
   do {                                  \

@@ -290,6 +290,8 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
     ctx->use_tensor_cores = value;
   } else if (strcmp(name, "mn_major") == 0) {
     ctx->use_mn_major = value;
+  } else if (strcmp(name, "pdl") == 0) {
+    ctx->pdl_chain = value;
   } else if (strcmp(name, "wino_plane") == 0) {
     ctx->wino_plane = value;
   } else if (strcmp(name, "col_budget_mb") == 0) {

@@ -133,6 +133,8 @@ __global__ void __launch_bounds__(128) conv_u8_patch_dp4a_kernel(const ConvParam
   constexpr int DWP = (DW + 3) / 4 * 4;  // words per filter row in shared memory
   extern __shared__ uint32_t smem_w[];   // [O][DWP] filter words, then [O] constants
   int32_t *cterm = reinterpret_cast<int32_t *>(smem_w + p.O * DWP);
+  mb_grid_dep_launch();
+  mb_grid_dep_wait();
   for (int i = threadIdx.x; i < p.O * DWP; i += blockDim.x) {
     const int o = i / DWP, w = i % DWP;
     uint32_t v = 0;
@@ -305,7 +307,7 @@ extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
       (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {
     const size_t smem = static_cast<size_t>(O) * (8 * 4 + 4);
     const unsigned blocks = static_cast<unsigned>(ceil_div64(pixels, 128));
-    conv_u8_patch_dp4a_kernel<3, 3, 3><<<blocks, 128, smem, ctx->stream>>>(p);
+    MB_CUDA(ctx, mb_launch_chained(ctx, conv_u8_patch_dp4a_kernel<3, 3, 3>, dim3(blocks), dim3(128), smem, p));
     MB_CUDA(ctx, cudaGetLastError());
     ctx->launches++;
     return MB_SUCCESS;

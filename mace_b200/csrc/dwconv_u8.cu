@@ -220,6 +220,8 @@ __global__ void __launch_bounds__(DW_THREADS, DW_BLOCKS_PER_SM)
 dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows_per_thread,
                     int segments) {
   constexpr int COLS = STRIDE == 1 ? 6 : 9;
+  mb_grid_dep_launch();
+  mb_grid_dep_wait();  // the input is the previous kernel's output
   const int groups = p.C >> 2;
   const int strips = (p.Wo + 3) >> 2;
   const int per_seg = groups * strips;
@@ -447,7 +449,8 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
     segments = ceil_div64(Ho, rows);
     const unsigned grid = static_cast<unsigned>(ceil_div64(per_seg * segments * N, DW_THREADS));
 #define MB_DW_LAUNCH(S, V)                                                                   \
-  dwconv3x3_u8_kernel<S, V><<<grid, DW_THREADS, 0, ctx->stream>>>(p, packed, rows, static_cast<int>(segments))
+  MB_CUDA(ctx, mb_launch_chained(ctx, dwconv3x3_u8_kernel<S, V>, dim3(grid), dim3(DW_THREADS), 0, p, packed, rows, \
+                                 static_cast<int>(segments)))
     const int var = mb_requant_variant(right_shift, zp_out);
     if (stride_h == 1) {
       switch (var) {

@@ -290,6 +290,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  mb_grid_dep_launch();  // the kernel behind this one may start its own prologue
 
   if (threadIdx.x == 0) {
     MB_STAMP(0);
@@ -317,6 +318,11 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) MB_STAMP(1);
+  // Everything above touched only this CTA's shared and tensor memory (and the kernel's
+  // parameters); from here on the roles read and write global memory, which the kernel in
+  // front of this one in the stream may still be producing.
+  mb_grid_dep_wait();
+
 
 
   if (warp == 0) {
@@ -443,10 +449,6 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __syncwarp();
   } else if (warp < FIRST_EPI_WARP) {
     // ---------------- preparation: operand sums (fused) and epilogue terms ----------------
-    // Precomputed sums come from the kernel launched just before this one, which this grid
-    // may have overtaken (programmatic dependent launch): wait for it here, and only here.
-    if (!FUSE_SUMS && (p.sum_a != nullptr || p.sum_b != nullptr))
-      asm volatile("griddepcontrol.wait;" ::: "memory");
     const int r = (warp - 2) * 32 + lane;  // 0..127: row of the A tile / column slot
     int stage = 0;
     uint32_t phase = 0;
@@ -685,22 +687,8 @@ int launch_cfg(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, co
   p.step_m = grid % p.tiles_m;
   p.step_n = (grid / p.tiles_m) % p.tiles_n;
   p.step_b = (grid / p.tiles_m) / p.tiles_n;
-  if (ctx->pdl_next_gemm) {
-    ctx->pdl_next_gemm = 0;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    MB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p));
-  } else {
-    kern<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(ta, tb, tc, p);
-  }
+  ctx->pdl_next_gemm = 0;
+  MB_CUDA(ctx, mb_launch_chained(ctx, kern, dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, ta, tb, tc, p));
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   ctx->launches_tc++;

@@ -37,6 +37,8 @@ avgpool_u8_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int
 __global__ void __launch_bounds__(128)
 avgpool_u8_c4_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int N, int H, int W,
                      int C, int KH, int KW, int sh, int sw, int pad_top, int pad_left, int Ho, int Wo) {
+  mb_grid_dep_launch();
+  mb_grid_dep_wait();
   const int groups = C >> 2;
   const unsigned total = static_cast<unsigned>(N) * Ho * Wo * groups;
   const unsigned tid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -108,10 +110,11 @@ extern "C" int mb_avgpool_u8_nhwc(mb_context *ctx, const uint8_t *in, uint8_t *o
   MB_CUDA(ctx, cudaSetDevice(ctx->device));
   if (C % 4 == 0 && total / 4 < (1ll << 31) &&
       ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 3u) == 0) {
-    avgpool_u8_c4_kernel<<<static_cast<unsigned>(ceil_div64(total / 4, 128)), 128, 0, ctx->stream>>>(
-        in, out, static_cast<int>(N), static_cast<int>(H), static_cast<int>(W), static_cast<int>(C),
-        static_cast<int>(KH), static_cast<int>(KW), stride_h, stride_w, pad_top, pad_left,
-        static_cast<int>(Ho), static_cast<int>(Wo));
+    MB_CUDA(ctx, mb_launch_chained(ctx, avgpool_u8_c4_kernel, dim3(static_cast<unsigned>(ceil_div64(total / 4, 128))),
+                                   dim3(128), 0, in, out, static_cast<int>(N), static_cast<int>(H),
+                                   static_cast<int>(W), static_cast<int>(C), static_cast<int>(KH),
+                                   static_cast<int>(KW), stride_h, stride_w, pad_top, pad_left,
+                                   static_cast<int>(Ho), static_cast<int>(Wo)));
     MB_CUDA(ctx, cudaGetLastError());
     ctx->launches++;
     return MB_SUCCESS;
