@@ -46,9 +46,9 @@ L2_BYTES = 126 * 1024 * 1024
 # kernel's capture ends are not in these sums.
 NCU_TRAFFIC = {
     "mobilenet_dw": 196.4e6,   # 13 depthwise launches, profiles/mobilenet_v1_u8_b64_launches.md
-    "mobilenet_pw": 129.0e6,   # 13 pointwise + FC GEMM launches, same file
-    "gemm_u8_4096": 33.76e6,   # gemm_u8_tc_kernel<256>, profiles/gemm_u8_tc_kernel_4096.md
-    "winograd_f32_cfg1": 144.2e6,  # three kernels of one convolution, caches flushed between them
+    "mobilenet_pw": 130.3e6,   # 13 pointwise + FC GEMM launches, same file
+    "gemm_u8_4096": 33.78e6,   # gemm_u8_tc_kernel<256>, profiles/gemm_u8_tc_kernel_4096.md
+    "winograd_f32_cfg1": 134.6e6,  # three kernels of one convolution, caches flushed between them
 }
 
 

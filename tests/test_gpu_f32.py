@@ -74,7 +74,7 @@ def test_gemm_f32_literals_and_one_side_batched(ctx, orc):
     assert rel_err(ctx.download(dC, (4 * 24 * 56,), np.float32), ref) <= 1e-4
 
 
-@pytest.mark.parametrize("shape", [(1, 16, 4), (3, 63, 257), (256, 1000, 2048)])
+@pytest.mark.parametrize("shape", [(1, 16, 4), (3, 63, 257), (17, 65, 100), (256, 1000, 2048)])
 def test_gemv_f32(ctx, orc, shape):
     batch, rows, K = shape
     rng = np.random.Generator(np.random.PCG64(7))
