@@ -162,10 +162,8 @@ class RawContext:
 def init_dist(world, local):
     if world <= 1:
         return None
-    # NCCL prints its version banner on stdout at INFO / VERSION level; the bench prints one
-    # JSON line there and nothing else
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION", "INFO"):
-        os.environ["NCCL_DEBUG"] = "WARN"
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO"):
+        os.environ["NCCL_DEBUG"] = "WARN"  # keep the logs short (they go to stderr, see main)
     import torch
     import torch.distributed as dist
     torch.cuda.set_device(local)
@@ -939,6 +937,11 @@ def main():
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
+    # stdout carries the one JSON line and nothing else: whatever libraries print there (NCCL's
+    # version banner, for one) is sent to stderr for the duration of the run
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         res = run_reference(args, rank, world)
     elif args.workload == "gemm_u8_4096":
@@ -951,8 +954,10 @@ def main():
         res = run_resnet(args, rank, world)
     else:
         res = run_mobilenet(args, rank, world)
+    sys.stdout.flush()
     if rank == 0 and res is not None:
-        print(json.dumps(res))
+        os.write(json_fd, (json.dumps(res) + "\n").encode())
+    os.close(json_fd)
 
 
 if __name__ == "__main__":
