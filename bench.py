@@ -692,6 +692,10 @@ def run_resnet(args, rank, world):
             dist.barrier()
 
     eng.write("input", x)
+    eng.run()
+    mem = None
+    if not args.no_plan:  # activation memory shared between tensors with disjoint lifetimes
+        mem = eng.plan_memory()
     for i in range(max(args.warmup, 3)):
         eng.run(sync=False)
     if not args.no_graph:
@@ -764,6 +768,8 @@ def run_resnet(args, rank, world):
                        "parallelism": "dp%d: batch sharded, weights replicated, final logits gather only" % world,
                        "launch": "operator by operator" if args.no_graph else "CUDA graph replay",
                        "merged_sum_relu_pairs": merged,
+                       "activation_memory_gb": None if mem is None else
+                       {"one_buffer_per_tensor": round(mem[0] / 1e9, 2), "planned": round(mem[1] / 1e9, 2)},
                        "l2": "activations of one step (%.1f GB) exceed L2" % (alg_bytes / 1e9)},
             "roofline": {"bound": "tensor", "achieved": round(tflops, 2), "peak": round(tf32_peak, 1),
                          "unit": "TFLOP/s", "frac": round(tflops / tf32_peak, 4), "traffic": None,
@@ -932,6 +938,8 @@ def main():
                     help="launch every operator separately instead of replaying a CUDA graph")
     ap.add_argument("--no-fuse", action="store_true",
                     help="resnet50_f32_b256: keep residual sums and their ReLUs as separate operators")
+    ap.add_argument("--no-plan", action="store_true",
+                    help="resnet50_f32_b256: every activation tensor keeps its own buffer")
     ap.add_argument("--profile", action="store_true",
                     help="run only the device-resident timed loop (for ncu captures)")
     args = ap.parse_args()

@@ -90,7 +90,11 @@ uint64_t mb_launch_count_tensor_core(const mb_context *ctx);
  * "col_budget_mb" (1024 default: the fp32 general convolution gathers the
  * im2col columns of as many images at a time as fit into this many MiB of
  * scratch), "wino_plane" (1 default; 0 takes the one-thread-per-tile Winograd
- * output transform instead of the plane-at-a-time one, for A/B tests). */
+ * output transform instead of the plane-at-a-time one, for A/B tests), "pdl"
+ * (1 default; 0 launches the kernels of the uint8 operator chain in plain
+ * stream order instead of with programmatic stream serialization),
+ * "dw_waves" (1 default: the 3x3 depthwise grid is sized so that all blocks
+ * are resident at once; n sizes it for n such rounds with shorter row runs). */
 int mb_set_option(mb_context *ctx, const char *name, int value);
 
 /* ---- uint8 GEMM: replaces the gemmlowp calls of MatMulOp<RT_CPU,uint8_t>

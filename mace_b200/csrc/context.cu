@@ -290,6 +290,9 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
     ctx->use_tensor_cores = value;
   } else if (strcmp(name, "mn_major") == 0) {
     ctx->use_mn_major = value;
+  } else if (strcmp(name, "dw_waves") == 0) {
+    if (value < 1) return mb_fail(ctx, MB_INVALID_ARGS, "dw_waves must be at least 1");
+    ctx->dw_waves = value;
   } else if (strcmp(name, "pdl") == 0) {
     ctx->pdl_chain = value;
   } else if (strcmp(name, "wino_plane") == 0) {

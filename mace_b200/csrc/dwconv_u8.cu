@@ -441,7 +441,7 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
     // 256-thread blocks per SM), so that there is no partial last wave; tensors too large
     // for that take runs of 16 rows.
     const int64_t per_seg = groups * ceil_div64(Wo, 4);
-    const int64_t slots = static_cast<int64_t>(ctx->num_sms) * DW_BLOCKS_PER_SM * DW_THREADS;
+    const int64_t slots = static_cast<int64_t>(ctx->num_sms) * DW_BLOCKS_PER_SM * DW_THREADS * ctx->dw_waves;
     int64_t segments = slots / (per_seg * N);
     segments = std::min<int64_t>(segments, ceil_div64(Ho, 2));
     if (segments < 1) segments = ceil_div64(Ho, 16);

@@ -238,6 +238,12 @@ int mbh_fuse_activations(mbh_engine *e, int *merged) {
   return MaceStatus::MACE_SUCCESS;
 }
 
+int mbh_plan_memory(mbh_engine *e, size_t *separate_bytes, size_t *shared_bytes) {
+  if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  MBH_TRY(e, e->net->PlanMemory(separate_bytes, shared_bytes));
+  return MaceStatus::MACE_SUCCESS;
+}
+
 int mbh_capture(mbh_engine *e) {
   if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
   MBH_TRY(e, e->net->Capture());

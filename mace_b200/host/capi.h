@@ -58,6 +58,11 @@ int mbh_op_end(mbh_engine *engine);
  * merged pairs. */
 int mbh_fuse_activations(mbh_engine *engine, int *merged);
 
+/* Shares activation memory between tensors whose lifetimes do not overlap (MACE's SERIAL_OPT
+ * allocation strategy).  Call after one run; intermediate tensors cannot be read back afterwards.
+ * The two sizes (may be NULL) are the activation bytes before and after. */
+int mbh_plan_memory(mbh_engine *engine, size_t *separate_bytes, size_t *shared_bytes);
+
 /* Runs all operators once (asynchronously on the engine's stream). */
 int mbh_run(mbh_engine *engine);
 int mbh_sync(mbh_engine *engine);

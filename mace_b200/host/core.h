@@ -163,7 +163,7 @@ class Tensor {
     if (!shape.empty()) Resize(shape);
   }
   ~Tensor() {
-    if (buffer_ != nullptr) runtime_->Delete(buffer_);
+    if (buffer_ != nullptr && owns_buffer_) runtime_->Delete(buffer_);
   }
   Tensor(const Tensor &) = delete;
   Tensor &operator=(const Tensor &) = delete;
@@ -196,14 +196,27 @@ class Tensor {
     shape_ = shape;
     const size_t need = static_cast<size_t>(raw_size());
     if (need > capacity_) {
-      if (buffer_ != nullptr) runtime_->Delete(buffer_);
+      // (a tensor that outgrows a shared buffer leaves it and owns its memory again)
+      if (buffer_ != nullptr && owns_buffer_) runtime_->Delete(buffer_);
       buffer_ = nullptr;
       capacity_ = 0;
       MACE_RETURN_IF_ERROR(runtime_->New(need, &buffer_));
       capacity_ = need;
+      owns_buffer_ = true;
     }
     return MaceStatus::MACE_SUCCESS;
   }
+
+  // Memory planning (the RENT_SHARE buffers of mace/core/net/allocate_opt_strategy.cc:157-178):
+  // the tensor gives up its own allocation and lives in `buffer`, which the net owns and
+  // shares among tensors whose lifetimes do not overlap.  The contents are not kept.
+  void BindShared(void *buffer, size_t capacity) {
+    if (buffer_ != nullptr && owns_buffer_) runtime_->Delete(buffer_);
+    buffer_ = buffer;
+    capacity_ = capacity;
+    owns_buffer_ = false;
+  }
+  bool owns_buffer() const { return owns_buffer_; }
 
  private:
   Runtime *runtime_;
@@ -211,6 +224,7 @@ class Tensor {
   std::vector<index_t> shape_;
   void *buffer_ = nullptr;
   size_t capacity_ = 0;
+  bool owns_buffer_ = true;
   bool is_weight_;
   float scale_ = 0.f;
   int32_t zero_point_ = 0;

@@ -797,6 +797,93 @@ int SerialNet::FuseActivations() {
   return merged;
 }
 
+SerialNet::~SerialNet() {
+  DropCapture();
+  operators_.clear();  // delegators may hold device memory; tensors are the workspace's
+  for (void *b : shared_buffers_) runtime_->Delete(b);
+}
+
+MaceStatus SerialNet::PlanMemory(size_t *separate_bytes, size_t *shared_bytes) {
+  DropCapture();
+  struct Ref {
+    Tensor *tensor;
+    int refs = 0;
+    int buffer = -1;
+    bool produced = false;
+  };
+  std::map<std::string, Ref> refs;
+  // readers of every activation tensor
+  for (size_t i = 0; i < operators_.size(); ++i) {
+    if (skipped_[i]) continue;
+    for (int k = 0; k < operators_[i]->InputSize(); ++k) {
+      const Tensor *t = operators_[i]->Input(k);
+      if (t->is_weight()) continue;
+      Ref &r = refs[t->name()];
+      r.tensor = const_cast<Tensor *>(t);
+      r.refs++;
+    }
+  }
+  struct Buf {
+    size_t bytes;
+    bool free;
+  };
+  std::vector<Buf> bufs;
+  size_t separate = 0;
+  for (size_t i = 0; i < operators_.size(); ++i) {
+    if (skipped_[i]) continue;
+    const OperatorDef &def = operators_[i]->debug_def();
+    for (size_t k = 0; k < def.output.size(); ++k) {
+      Tensor *t = operators_[i]->Output(static_cast<unsigned>(k));
+      auto it = refs.find(t->name());
+      if (it == refs.end()) continue;  // nobody reads it: an output of the net, keeps its memory
+      Ref &r = it->second;
+      if (r.produced) continue;        // written by two operators: first placement stands
+      r.produced = true;
+      const size_t need = static_cast<size_t>(t->raw_size());
+      if (need == 0)
+        return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "PlanMemory: run the net once first (tensor " +
+                                                             t->name() + " has no shape)");
+      separate += need;
+      // best fit: the smallest free buffer that is large enough, else the largest free one, grown
+      int best = -1;
+      for (size_t b = 0; b < bufs.size(); ++b) {
+        if (!bufs[b].free) continue;
+        if (best < 0) { best = static_cast<int>(b); continue; }
+        const bool fits = bufs[b].bytes >= need, best_fits = bufs[best].bytes >= need;
+        if (fits && (!best_fits || bufs[b].bytes < bufs[best].bytes)) best = static_cast<int>(b);
+        else if (!fits && !best_fits && bufs[b].bytes > bufs[best].bytes) best = static_cast<int>(b);
+      }
+      if (best < 0) {
+        bufs.push_back({need, false});
+        best = static_cast<int>(bufs.size()) - 1;
+      } else {
+        bufs[best].free = false;
+        bufs[best].bytes = std::max(bufs[best].bytes, need);
+      }
+      r.buffer = best;
+    }
+    for (int k = 0; k < operators_[i]->InputSize(); ++k) {
+      const Tensor *t = operators_[i]->Input(k);
+      if (t->is_weight()) continue;
+      Ref &r = refs[t->name()];
+      if (--r.refs == 0 && r.buffer >= 0) bufs[r.buffer].free = true;  // (net inputs have no buffer)
+    }
+  }
+  // allocate the shared buffers and move the tensors in
+  std::vector<void *> mem(bufs.size(), nullptr);
+  size_t shared = 0;
+  for (size_t b = 0; b < bufs.size(); ++b) {
+    MACE_RETURN_IF_ERROR(runtime_->New(bufs[b].bytes, &mem[b]));
+    shared_buffers_.push_back(mem[b]);
+    shared += bufs[b].bytes;
+  }
+  for (auto &kv : refs)
+    if (kv.second.buffer >= 0) kv.second.tensor->BindShared(mem[kv.second.buffer], bufs[kv.second.buffer].bytes);
+  if (separate_bytes != nullptr) *separate_bytes = separate;
+  if (shared_bytes != nullptr) *shared_bytes = shared;
+  return MaceStatus::MACE_SUCCESS;
+}
+
 MaceStatus SerialNet::Capture() {
   DropCapture();
   OpContext context(runtime_);

@@ -137,8 +137,19 @@ class SerialNet {
   // Returns the number of merged pairs.  Off unless called: operator by operator the net
   // behaves like the CPU runtime's.
   int FuseActivations();
+  // Shares activation memory between tensors whose lifetimes do not overlap, the way
+  // AllocateTensorMemory<SERIAL_OPT> does (mace/core/net/allocate_opt_strategy.cc:181-285): the
+  // net is walked once; every operator's outputs take the best-fitting free buffer (the
+  // smallest that is large enough, else the largest one, grown) BEFORE the operator's inputs
+  // are released, so an output never aliases an input of its own operator; a tensor's buffer
+  // returns to the free list after its last reader.  Weights, tensors no operator of the net
+  // produces (the net's inputs) and tensors no operator reads (its outputs) keep their own
+  // memory.  Call after one plain Run(): the sizes are the ones that run produced.  Intermediate
+  // tensors can no longer be read back afterwards.  separate_bytes / shared_bytes (may be null)
+  // receive the activation memory before and after.
+  MaceStatus PlanMemory(size_t *separate_bytes, size_t *shared_bytes);
   bool captured() const { return graph_ != nullptr; }
-  ~SerialNet() { DropCapture(); }
+  ~SerialNet();
   size_t size() const { return operators_.size(); }
 
  private:
@@ -148,6 +159,7 @@ class SerialNet {
   std::vector<std::unique_ptr<OperatorDef>> defs_;
   std::vector<std::unique_ptr<Operation>> operators_;
   std::vector<char> skipped_;  // operators merged into their producer
+  std::vector<void *> shared_buffers_;  // activation memory handed out by PlanMemory
   void *graph_ = nullptr;
 };
 

@@ -43,6 +43,7 @@ _PROTOS = {
     "mbh_sync": [_vp],
     "mbh_capture": [_vp],
     "mbh_fuse_activations": [_vp, C.POINTER(_int)],
+    "mbh_plan_memory": [_vp, C.POINTER(_sz), C.POINTER(_sz)],
     "mbh_run_host": [_vp, _cp, _vp, _sz, _cp, _vp, _sz],
     "mbh_run_profiled": [_vp, C.POINTER(_f32), _int, C.c_char_p, _sz, C.POINTER(_int)],
 }
@@ -172,6 +173,13 @@ class HostEngine:
         n = _int()
         self._check(lib().mbh_fuse_activations(self.h, C.byref(n)))
         return n.value
+
+    def plan_memory(self):
+        """Share activation memory between tensors with disjoint lifetimes (after one run);
+        returns (bytes before, bytes after)."""
+        a, b = _sz(), _sz()
+        self._check(lib().mbh_plan_memory(self.h, C.byref(a), C.byref(b)))
+        return a.value, b.value
 
     def capture(self):
         """Record the chain into a CUDA graph (after one plain run); later runs replay it."""

@@ -27,6 +27,16 @@ def test_mobilenet_chain_every_layer(orc, layers):
             got = eng.read(L["name"], np.uint8)
             assert np.array_equal(got.reshape(exp.shape), exp), "layer %s differs" % L["name"]
         assert len(np.unique(exp_logits)) > 50
+        # a linear chain needs two activation buffers (plus the logits, which nobody reads):
+        # planned memory is the two largest consecutive activations, and the logits stay exact
+        separate, shared = eng.plan_memory()
+        assert shared < separate / 2, (separate, shared)
+        eng.write("input", x)
+        eng.run()
+        assert np.array_equal(eng.read("fc", np.uint8).reshape(exp_logits.shape), exp_logits)
+        eng.capture()
+        eng.run()
+        assert np.array_equal(eng.read("fc", np.uint8).reshape(exp_logits.shape), exp_logits)
     finally:
         eng.close()
 

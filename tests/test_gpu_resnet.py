@@ -131,6 +131,19 @@ def test_resnet50_graph_against_oracle(orc, cfg):
         eng.capture()
         eng.run()
         assert np.array_equal(eng.read("fc", np.float32), first)
+        # activation memory shared between tensors with disjoint lifetimes: same logits from
+        # less than a third of the memory, also through a re-captured graph and for new inputs
+        separate, shared = eng.plan_memory()
+        assert 0 < shared < separate / 3, (separate, shared)
+        eng.run()
+        assert np.array_equal(eng.read("fc", np.float32), first)
+        eng.capture()
+        x2 = rn.random_images(cfg["batch"], 7, cfg["image"])
+        eng.write("input", x2)
+        eng.run()
+        ref2 = rn.oracle_forward(orc, nodes, weights, x2)
+        got2 = eng.read("fc", np.float32)
+        assert float(np.abs(got2 - ref2).max() / np.abs(ref2).max()) <= 1e-4
     finally:
         eng.close()
 
