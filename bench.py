@@ -494,7 +494,9 @@ def run_mobilenet(args, rank, world):
                        "weights": "He-normal, per-tensor uint8 (non_zero), seed 0",
                        "parallelism": "dp%d: batch sharded, weights replicated, final logits gather only" % world,
                        "launch": "per-operator launches" if args.no_graph else "CUDA graph replay",
-                       "l2": "activations of one step (%.0f MB) exceed L2" % (total_bytes / 1e6)},
+                       "l2": ("activations of one step (%.0f MB) exceed L2" % (total_bytes / 1e6)) if mem is None else
+                       ("activations of one step (%.0f MB) pass through shared buffers of %.0f MB in total"
+                        % (total_bytes / 1e6, mem[1] / 1e6))},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / peaks["hbm_gbs"], 4),
