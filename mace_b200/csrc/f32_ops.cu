@@ -189,18 +189,51 @@ struct ColF32Params {
 __global__ void __launch_bounds__(128) im2col_f32_kernel(const ColF32Params p, int rows_per_block) {
   const int h = blockIdx.x * blockDim.y + threadIdx.y, n = blockIdx.z;
   if (h >= p.Ho) return;
+  const float *__restrict__ in = p.in;
+  float *__restrict__ col = p.col;
   const int y_end = min((static_cast<int>(blockIdx.y) + 1) * rows_per_block, p.C * p.KH);
+  // Up to eight values are loaded before the first is stored: a store waits for the load that
+  // feeds it, a warp issues in order, and the compiler may not move a load above a store to
+  // memory it cannot tell apart.
+  if (p.KW == 1) {
+    for (int w = threadIdx.x; w < p.Wo; w += blockDim.x) {
+      const int iw = w * p.sw - p.pad_l;
+      const bool col_ok = iw >= 0 && iw < p.W;
+      for (int y0 = blockIdx.y * rows_per_block; y0 < y_end; y0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int y = y0 + j;
+          const int c = y / p.KH, kh = y - c * p.KH;
+          const int ih = h * p.sh - p.pad_t + kh * p.dh;
+          const bool ok = y < y_end && col_ok && ih >= 0 && ih < p.H;
+          v[j] = ok ? __ldg(in + ((static_cast<int64_t>(n) * p.C + c) * p.H + ih) * p.W + iw) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (y0 + j < y_end) col[static_cast<int64_t>(y0 + j) * p.col_rs + n * p.col_ns + h * p.Wo + w] = v[j];
+      }
+    }
+    return;
+  }
   for (int y = blockIdx.y * rows_per_block; y < y_end; ++y) {  // y = c * KH + kh
     const int c = y / p.KH, kh = y - c * p.KH;
     const int ih = h * p.sh - p.pad_t + kh * p.dh;
     const bool row_ok = ih >= 0 && ih < p.H;
-    const float *src = p.in + ((static_cast<int64_t>(n) * p.C + c) * p.H + (row_ok ? ih : 0)) * p.W;
-    float *dst = p.col + static_cast<int64_t>(y) * p.KW * p.col_rs + n * p.col_ns + h * p.Wo;
+    const float *src = in + ((static_cast<int64_t>(n) * p.C + c) * p.H + (row_ok ? ih : 0)) * p.W;
+    float *dst = col + static_cast<int64_t>(y) * p.KW * p.col_rs + n * p.col_ns + h * p.Wo;
     for (int w = threadIdx.x; w < p.Wo; w += blockDim.x) {
       const int iw0 = w * p.sw - p.pad_l;
-      for (int kw = 0; kw < p.KW; ++kw) {
-        const int iw = iw0 + kw * p.dw;
-        dst[kw * p.col_rs + w] = (row_ok && iw >= 0 && iw < p.W) ? __ldg(src + iw) : 0.f;
+      for (int kw0 = 0; kw0 < p.KW; kw0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int iw = iw0 + (kw0 + j) * p.dw;
+          v[j] = (kw0 + j < p.KW && row_ok && iw >= 0 && iw < p.W) ? __ldg(src + iw) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (kw0 + j < p.KW) dst[(kw0 + j) * p.col_rs + w] = v[j];
       }
     }
   }
