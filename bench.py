@@ -441,25 +441,35 @@ def run_mobilenet(args, rank, world):
         for label, t in eng.run_profiled():
             per_op[label] = per_op.get(label, 0.0) + t / prof_runs
 
-    # end to end: pinned host input -> H2D -> chain -> D2H logits, every step
-    def e2e_step(i):
-        eng.run_host("input", hin[i % n_inputs], "fc", hout)
-        if dist is not None:  # the only collective of the path: gather the logits
-            from mace_b200.sharding import gather_rows
-            gather_rows(dist, hout.reshape(BATCH, mn.NUM_CLASSES), BATCH * world, device="cuda")
+    # end to end: pinned host input -> H2D -> chain -> D2H logits, every step.  The calls are
+    # pipelined: the upload of step i + 1 (upload stream, two staging buffers) overlaps the
+    # chain of step i; every step's images are copied in and its logits copied out inside the
+    # timed region, and the region ends when the last logits are in host memory.
+    houts = [hout, ctx.pinned(BATCH * mn.NUM_CLASSES)]
 
-    for i in range(3):
-        e2e_step(i)
+    def gather(call):  # the only collective of the path: gather the logits of a finished step
+        slot, buf = call
+        eng.wait_slot(slot)
+        from mace_b200.sharding import gather_rows
+        gather_rows(dist, houts[buf].reshape(BATCH, mn.NUM_CLASSES), BATCH * world, device="cuda")
+
+    def e2e_loop(n, first):
+        prev = None
+        for i in range(first, first + n):
+            slot = eng.run_host_pipelined("input", hin[i % n_inputs], "fc", houts[i & 1])
+            if dist is not None and prev is not None:
+                gather(prev)
+            prev = (slot, i & 1)
+        if dist is not None:
+            gather(prev)
+        eng.sync()
+
+    e2e_loop(4, 0)
     barrier()
-    e2e_steps = max(3, min(args.steps, 50))
+    e2e_steps = max(4, min(args.steps, 50))
     t0 = time.perf_counter()
-    ctx.record(e0)
-    for i in range(e2e_steps):
-        e2e_step(i)
-    ctx.record(e1)
-    e2e_ms = ctx.elapsed_ms(e0, e1)
-    e2e_wall_ms = (time.perf_counter() - t0) * 1e3
-    e2e_ms = max(e2e_ms, e2e_wall_ms) if dist is not None else e2e_ms
+    e2e_loop(e2e_steps, 4)
+    e2e_ms = (time.perf_counter() - t0) * 1e3  # host clock around enqueue ... last logits on the host
     barrier()
     ms, e2e_ms = max_over_ranks(dist, [ms, e2e_ms])
 
@@ -734,24 +744,36 @@ def run_resnet(args, rank, world):
             k = kinds.get(label.split(":", 1)[-1], label)
             fam[k] = fam.get(k, 0.0) + t / prof_runs
 
-    def e2e_step():
-        eng.run_host("input", hin, "fc", hout)
-        if dist is not None:
-            from mace_b200.sharding import gather_rows
-            gather_rows(dist, hout.view(np.float32).reshape(batch, rn.NUM_CLASSES), batch * world, device="cuda")
+    # pipelined end-to-end calls (see run_mobilenet): the next batch's upload overlaps this
+    # batch's run; two pinned host input and output buffers rotate
+    hins = [hin, ctx.pinned(x.nbytes)]
+    hins[1][:] = rn.random_images(batch, seed=200 + rank).view(np.uint8).ravel()
+    houts = [hout, ctx.pinned(batch * rn.NUM_CLASSES * 4)]
 
-    for _ in range(2):
-        e2e_step()
+    def gather(call):
+        slot, buf = call
+        eng.wait_slot(slot)
+        from mace_b200.sharding import gather_rows
+        gather_rows(dist, houts[buf].view(np.float32).reshape(batch, rn.NUM_CLASSES), batch * world,
+                    device="cuda")
+
+    def e2e_loop(n):
+        prev = None
+        for i in range(n):
+            slot = eng.run_host_pipelined("input", hins[i & 1], "fc", houts[i & 1])
+            if dist is not None and prev is not None:
+                gather(prev)
+            prev = (slot, i & 1)
+        if dist is not None:
+            gather(prev)
+        eng.sync()
+
+    e2e_loop(2)
     barrier()
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(4, min(args.steps, 10))
     t0 = time.perf_counter()
-    ctx.record(e0)
-    for _ in range(e2e_steps):
-        e2e_step()
-    ctx.record(e1)
-    e2e_ms = ctx.elapsed_ms(e0, e1)
-    e2e_wall_ms = (time.perf_counter() - t0) * 1e3
-    e2e_ms = max(e2e_ms, e2e_wall_ms) if dist is not None else e2e_ms
+    e2e_loop(e2e_steps)
+    e2e_ms = (time.perf_counter() - t0) * 1e3
     barrier()
     ms, e2e_ms = max_over_ranks(dist, [ms, e2e_ms])
     result = None

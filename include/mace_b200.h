@@ -58,6 +58,18 @@ int mb_host_free(mb_context *ctx, void *hptr);
 int mb_memcpy_h2d(mb_context *ctx, void *dst_dev, const void *src_host, size_t bytes);
 int mb_memcpy_d2h(mb_context *ctx, void *dst_host, const void *src_dev, size_t bytes);
 int mb_memset(mb_context *ctx, void *dst_dev, int value, size_t bytes);
+int mb_memcpy_d2d(mb_context *ctx, void *dst_dev, const void *src_dev, size_t bytes);
+/* Uploads that overlap the compute stream's work (double-buffered inputs): the
+ * context owns a second stream for them.
+ *   mb_upload_h2d         asynchronous copy from PINNED host memory on the upload stream
+ *   mb_upload_wait_event  the upload stream waits for an event recorded with mb_event_record
+ *                         (i.e. on the compute stream), e.g. "the staging buffer has been
+ *                         consumed", before later uploads overwrite it
+ *   mb_upload_signal      the compute stream waits for every upload enqueued so far
+ * None of them may be called between mb_graph_begin and mb_graph_end. */
+int mb_upload_h2d(mb_context *ctx, void *dst_dev, const void *src_host, size_t bytes);
+int mb_upload_wait_event(mb_context *ctx, void *event);
+int mb_upload_signal(mb_context *ctx);
 int mb_stream_sync(mb_context *ctx);
 /* The cudaStream_t of the context, as an opaque pointer (for event timing). */
 void *mb_stream(mb_context *ctx);
@@ -69,6 +81,8 @@ int mb_event_create(mb_context *ctx, void **event);
 int mb_event_record(mb_context *ctx, void *event);
 int mb_event_elapsed_ms(mb_context *ctx, void *start, void *stop, float *ms);
 int mb_event_destroy(mb_context *ctx, void *event);
+/* Blocks the calling host thread until the event has happened. */
+int mb_event_sync(mb_context *ctx, void *event);
 /* CUDA-graph capture of a sequence of calls on this context (the launch-bound
  * tail of a small-batch net costs more on the host than on the GPU).  Between
  * mb_graph_begin and mb_graph_end every call on the context is recorded

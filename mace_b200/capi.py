@@ -46,6 +46,11 @@ PROTOTYPES = {
     "mb_memcpy_h2d": (_int, [_vp, _vp, _vp, _sz]),
     "mb_memcpy_d2h": (_int, [_vp, _vp, _vp, _sz]),
     "mb_memset": (_int, [_vp, _vp, _int, _sz]),
+    "mb_memcpy_d2d": (_int, [_vp, _vp, _vp, _sz]),
+    "mb_upload_h2d": (_int, [_vp, _vp, _vp, _sz]),
+    "mb_upload_wait_event": (_int, [_vp, _vp]),
+    "mb_upload_signal": (_int, [_vp]),
+    "mb_event_sync": (_int, [_vp, _vp]),
     "mb_stream_sync": (_int, [_vp]),
     "mb_stream": (_vp, [_vp]),
     "mb_event_create": (_int, [_vp, C.POINTER(_vp)]),

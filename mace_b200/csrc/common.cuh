@@ -27,6 +27,8 @@ struct mb_context {
   int num_sms = 0;
   int max_smem_optin = 0;
   cudaStream_t stream = nullptr;
+  cudaStream_t upload_stream = nullptr;  // created on first use: uploads that overlap the compute stream
+  cudaEvent_t upload_event = nullptr;    // last mb_upload_signal
   // Scratch arena, the analogue of the runtime's RENT_SCRATCH buffers
   // (mace/core/runtime/runtime.cc:153-182): one growable device block that a
   // call carves from the start; contents do not survive the call.

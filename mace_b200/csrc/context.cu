@@ -95,6 +95,11 @@ int mb_destroy(mb_context *ctx) {
   if (ctx == nullptr) return MB_INVALID_ARGS;
   cudaSetDevice(ctx->device);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  if (ctx->upload_stream) {
+    cudaStreamSynchronize(ctx->upload_stream);
+    cudaEventDestroy(ctx->upload_event);
+    cudaStreamDestroy(ctx->upload_stream);
+  }
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->skinny_ws) cudaFree(ctx->skinny_ws);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
@@ -154,6 +159,53 @@ int mb_memcpy_d2h(mb_context *ctx, void *dst, const void *src, size_t bytes) {
   if (bytes == 0) return MB_SUCCESS;
   MB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost,
                                ctx->stream));
+  return MB_SUCCESS;
+}
+
+int mb_memcpy_d2d(mb_context *ctx, void *dst, const void *src, size_t bytes) {
+  if (ctx == nullptr || (bytes && (!dst || !src))) return MB_INVALID_ARGS;
+  if (bytes == 0) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return MB_SUCCESS;
+}
+
+static int upload_stream_ready(mb_context *ctx) {
+  if (ctx->upload_stream == nullptr) {
+    MB_CUDA(ctx, cudaSetDevice(ctx->device));
+    MB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->upload_stream, cudaStreamNonBlocking));
+    MB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->upload_event, cudaEventDisableTiming));
+  }
+  return MB_SUCCESS;
+}
+
+int mb_upload_h2d(mb_context *ctx, void *dst, const void *src, size_t bytes) {
+  if (ctx == nullptr || (bytes && (!dst || !src))) return MB_INVALID_ARGS;
+  if (ctx->capturing) return mb_fail(ctx, MB_INVALID_ARGS, "mb_upload_h2d: not inside a graph capture");
+  MB_RETURN_IF_ERROR(upload_stream_ready(ctx));
+  if (bytes == 0) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->upload_stream));
+  return MB_SUCCESS;
+}
+
+int mb_upload_wait_event(mb_context *ctx, void *event) {
+  if (ctx == nullptr || event == nullptr) return MB_INVALID_ARGS;
+  MB_RETURN_IF_ERROR(upload_stream_ready(ctx));
+  MB_CUDA(ctx, cudaStreamWaitEvent(ctx->upload_stream, static_cast<cudaEvent_t>(event), 0));
+  return MB_SUCCESS;
+}
+
+int mb_upload_signal(mb_context *ctx) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (ctx->capturing) return mb_fail(ctx, MB_INVALID_ARGS, "mb_upload_signal: not inside a graph capture");
+  MB_RETURN_IF_ERROR(upload_stream_ready(ctx));
+  MB_CUDA(ctx, cudaEventRecord(ctx->upload_event, ctx->upload_stream));
+  MB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->upload_event, 0));
+  return MB_SUCCESS;
+}
+
+int mb_event_sync(mb_context *ctx, void *event) {
+  if (ctx == nullptr || event == nullptr) return MB_INVALID_ARGS;
+  MB_CUDA(ctx, cudaEventSynchronize(static_cast<cudaEvent_t>(event)));
   return MB_SUCCESS;
 }
 

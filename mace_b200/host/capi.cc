@@ -16,6 +16,13 @@ struct mbh_engine {
   OperatorDef pending;
   bool building = false;
   std::string last_error;
+  // mbh_run_host_pipelined: two staging copies of the input, per slot an event "staging
+  // consumed" and an event "output in host memory"
+  void *staging[2] = {nullptr, nullptr};
+  size_t staging_bytes = 0;
+  void *consumed[2] = {nullptr, nullptr};
+  void *done[2] = {nullptr, nullptr};
+  uint64_t pipelined_calls = 0;
 };
 
 namespace {
@@ -60,6 +67,11 @@ int mbh_engine_create(int device, mbh_engine **engine) {
 int mbh_engine_destroy(mbh_engine *engine) {
   if (engine == nullptr) return MaceStatus::MACE_INVALID_ARGS;
   mb_stream_sync(engine->runtime.ctx());
+  for (int i = 0; i < 2; ++i) {
+    if (engine->staging[i] != nullptr) mb_free(engine->runtime.ctx(), engine->staging[i]);
+    if (engine->consumed[i] != nullptr) mb_event_destroy(engine->runtime.ctx(), engine->consumed[i]);
+    if (engine->done[i] != nullptr) mb_event_destroy(engine->runtime.ctx(), engine->done[i]);
+  }
   delete engine;
   return MaceStatus::MACE_SUCCESS;
 }
@@ -270,6 +282,50 @@ int mbh_run_host(mbh_engine *e, const char *input_name, const void *host_in, siz
     return Fail(e, MaceStatus::MACE_INVALID_ARGS, "output size does not match the output tensor");
   MBH_TRY(e, e->runtime.Status(mb_memcpy_d2h(e->runtime.ctx(), host_out, out->memory<void>(), output_bytes)));
   MBH_TRY(e, e->runtime.Status(mb_stream_sync(e->runtime.ctx())));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_run_host_pipelined(mbh_engine *e, const char *input_name, const void *host_in, size_t input_bytes,
+                           const char *output_name, void *host_out, size_t output_bytes, int *slot_out) {
+  Tensor *in = FindTensor(e, input_name);
+  Tensor *out = FindTensor(e, output_name);
+  if (in == nullptr || out == nullptr || host_in == nullptr || host_out == nullptr)
+    return MaceStatus::MACE_INVALID_ARGS;
+  if (input_bytes != static_cast<size_t>(in->raw_size()))
+    return Fail(e, MaceStatus::MACE_INVALID_ARGS, "input size does not match the input tensor");
+  if (output_bytes != static_cast<size_t>(out->raw_size()))
+    return Fail(e, MaceStatus::MACE_INVALID_ARGS, "output size does not match the output tensor (run the net once first)");
+  mb_context *ctx = e->runtime.ctx();
+  if (e->staging_bytes < input_bytes) {
+    for (int i = 0; i < 2; ++i) {
+      if (e->staging[i] != nullptr) MBH_TRY(e, e->runtime.Status(mb_free(ctx, e->staging[i])));
+      MBH_TRY(e, e->runtime.Status(mb_malloc(ctx, input_bytes, &e->staging[i])));
+      if (e->consumed[i] == nullptr) MBH_TRY(e, e->runtime.Status(mb_event_create(ctx, &e->consumed[i])));
+      if (e->done[i] == nullptr) MBH_TRY(e, e->runtime.Status(mb_event_create(ctx, &e->done[i])));
+    }
+    e->staging_bytes = input_bytes;
+    e->pipelined_calls = 0;
+  }
+  const int slot = static_cast<int>(e->pipelined_calls & 1);
+  // upload stream: wait until the copy out of this staging buffer two calls ago has run, then
+  // fill it; compute stream: wait for the upload, move it into the input tensor (a copy inside
+  // device memory: microseconds), run the net, bring the output back
+  if (e->pipelined_calls >= 2) MBH_TRY(e, e->runtime.Status(mb_upload_wait_event(ctx, e->consumed[slot])));
+  MBH_TRY(e, e->runtime.Status(mb_upload_h2d(ctx, e->staging[slot], host_in, input_bytes)));
+  MBH_TRY(e, e->runtime.Status(mb_upload_signal(ctx)));
+  MBH_TRY(e, e->runtime.Status(mb_memcpy_d2d(ctx, in->mutable_memory<void>(), e->staging[slot], input_bytes)));
+  MBH_TRY(e, e->runtime.Status(mb_event_record(ctx, e->consumed[slot])));
+  MBH_TRY(e, e->net->Run(nullptr));
+  MBH_TRY(e, e->runtime.Status(mb_memcpy_d2h(ctx, host_out, out->memory<void>(), output_bytes)));
+  MBH_TRY(e, e->runtime.Status(mb_event_record(ctx, e->done[slot])));
+  e->pipelined_calls++;
+  if (slot_out != nullptr) *slot_out = slot;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_wait_slot(mbh_engine *e, int slot) {
+  if (e == nullptr || slot < 0 || slot > 1 || e->done[slot] == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  MBH_TRY(e, e->runtime.Status(mb_event_sync(e->runtime.ctx(), e->done[slot])));
   return MaceStatus::MACE_SUCCESS;
 }
 

@@ -45,6 +45,8 @@ _PROTOS = {
     "mbh_fuse_activations": [_vp, C.POINTER(_int)],
     "mbh_plan_memory": [_vp, C.POINTER(_sz), C.POINTER(_sz)],
     "mbh_run_host": [_vp, _cp, _vp, _sz, _cp, _vp, _sz],
+    "mbh_run_host_pipelined": [_vp, _cp, _vp, _sz, _cp, _vp, _sz, C.POINTER(_int)],
+    "mbh_wait_slot": [_vp, _int],
     "mbh_run_profiled": [_vp, C.POINTER(_f32), _int, C.c_char_p, _sz, C.POINTER(_int)],
 }
 _lib = None
@@ -189,6 +191,18 @@ class HostEngine:
         self._check(lib().mbh_run_host(self.h, input_name.encode(), host_in.ctypes.data,
                                        host_in.nbytes, output_name.encode(),
                                        host_out.ctypes.data, host_out.nbytes))
+
+    def run_host_pipelined(self, input_name, host_in, output_name, host_out):
+        """Enqueue upload + run + download without waiting (pinned host arrays); returns the slot
+        to pass to wait_slot().  The upload overlaps the previous call's run."""
+        slot = _int()
+        self._check(lib().mbh_run_host_pipelined(self.h, input_name.encode(), host_in.ctypes.data,
+                                                 host_in.nbytes, output_name.encode(),
+                                                 host_out.ctypes.data, host_out.nbytes, C.byref(slot)))
+        return slot.value
+
+    def wait_slot(self, slot):
+        self._check(lib().mbh_wait_slot(self.h, int(slot)))
 
     def run_profiled(self, max_ops=256):
         ms = (C.c_float * max_ops)()

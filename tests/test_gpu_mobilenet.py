@@ -113,3 +113,34 @@ def test_mobilenet_batch64_logits_and_host_buffers(orc, layers):
         assert np.array_equal(out2, out)
     finally:
         eng.close()
+
+
+def test_mobilenet_pipelined_host_runs(orc, layers):
+    """mbh_run_host_pipelined: uploads overlap the previous call's chain through two staging
+    buffers; every call's logits, read after wait_slot, are those of ITS input."""
+    from mace_b200 import hostapi
+    batch = 4
+    xs = [mn.random_images(batch, seed=20 + i) for i in range(6)]
+    exps = [mn.oracle_forward(orc, layers, x) for x in xs]
+    eng = mn.build_engine(hostapi, layers, batch)
+    try:
+        eng.write("input", xs[0])
+        eng.run()
+        eng.capture()
+        outs = [np.zeros((batch, mn.NUM_CLASSES), np.uint8) for _ in range(2)]
+        prev = None
+        for i, x in enumerate(xs):
+            slot = eng.run_host_pipelined("input", x, "fc", outs[i & 1])
+            if prev is not None:
+                eng.wait_slot(prev[0])
+                assert np.array_equal(outs[prev[1]], exps[prev[2]]), "call %d" % prev[2]
+            prev = (slot, i & 1, i)
+        eng.wait_slot(prev[0])
+        assert np.array_equal(outs[prev[1]], exps[prev[2]])
+        eng.sync()
+        # the ordinary entry point still works afterwards
+        out = np.empty((batch, mn.NUM_CLASSES), np.uint8)
+        eng.run_host("input", xs[2], "fc", out)
+        assert np.array_equal(out, exps[2])
+    finally:
+        eng.close()
