@@ -1,13 +1,18 @@
-// Operators of the hot path for RuntimeType::RT_CUDA / uint8, with the argument
-// names and Run() behaviour of MACE's CPU operators:
-//   Conv2dOp            mace/ops/conv_2d.cc:190-318     (inputs INPUT, FILTER, BIAS)
-//   DepthwiseConv2dOp   mace/ops/depthwise_conv2d.cc:146-250
-//   MatMulOp            mace/ops/matmul.cc:397-482      (args transpose_a, transpose_b)
-//   FullyConnectedOp    mace/ops/fully_connected.cc:130-179
-//   PoolingOp (AVG)     mace/ops/pooling.cc:638-871     (args kernels, pooling_type, round_mode)
-// plus the sequential executor (SerialNet::Run, mace/core/net/serial_net.cc:93-228)
-// and a small OperatorDef stand-in (mace/proto/mace.proto:61-95: type, inputs,
-// outputs, args, output_type, quantize_info).
+// Operators for RuntimeType::RT_CUDA with the argument names and Run() behaviour of MACE's CPU
+// operators:
+//   uint8   Conv2dOp            mace/ops/conv_2d.cc:190-318     (inputs INPUT, FILTER, BIAS)
+//           DepthwiseConv2dOp   mace/ops/depthwise_conv2d.cc:146-250
+//           MatMulOp            mace/ops/matmul.cc:397-482      (args transpose_a, transpose_b)
+//           FullyConnectedOp    mace/ops/fully_connected.cc:130-179
+//           PoolingOp (AVG)     mace/ops/pooling.cc:638-871     (args kernels, pooling_type, round_mode)
+//           QuantizeOp, DequantizeOp   mace/ops/quantize.cc:31-115
+//   float   Conv2dOp (mace/ops/conv_2d.cc:82-176), DepthwiseConv2dOp, MatMulOp, FullyConnectedOp,
+//           PoolingOp (mace/ops/pooling.cc:46-240), EltwiseOp (mace/ops/eltwise.cc:949-1144),
+//           ActivationOp (mace/ops/activation.cc:36-79), SoftmaxOp (mace/ops/softmax.cc:249-290)
+// plus the sequential executor (SerialNet::Run, mace/core/net/serial_net.cc:93-228) with
+// activation merging and MACE's shared activation memory
+// (mace/core/net/allocate_opt_strategy.cc:181-285), and a small OperatorDef stand-in
+// (mace/proto/mace.proto:61-95: type, inputs, outputs, args, output_type, quantize_info).
 #ifndef MACE_B200_HOST_OPS_H_
 #define MACE_B200_HOST_OPS_H_
 
@@ -110,8 +115,7 @@ class OpRegistry {
 };
 
 namespace ops {
-// Registers Conv2D, DepthwiseConv2d, MatMul, FullyConnected and Pooling for
-// (RT_CUDA, uint8_t) and Conv2D, DepthwiseConv2d, MatMul, FullyConnected for (RT_CUDA, float).
+// Registers the operators listed at the top of this file.
 void RegisterAllCudaOps(OpRegistry *registry);
 }  // namespace ops
 
