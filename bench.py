@@ -709,6 +709,7 @@ def run_resnet(args, rank, world):
 
     eng.write("input", x)
     eng.run()
+    merged_conv = 0 if args.no_fuse else eng.fuse_residual_sums()  # ... and into the 1x1 conv before it
     mem = None
     if not args.no_plan:  # activation memory shared between tensors with disjoint lifetimes
         mem = eng.plan_memory()
@@ -795,7 +796,7 @@ def run_resnet(args, rank, world):
                        "macs_per_image": macs,
                        "parallelism": "dp%d: batch sharded, weights replicated, final logits gather only" % world,
                        "launch": "operator by operator" if args.no_graph else "CUDA graph replay",
-                       "merged_sum_relu_pairs": merged,
+                       "merged_sum_relu_pairs": merged, "sums_merged_into_convolutions": merged_conv,
                        "activation_memory_gb": None if mem is None else
                        {"one_buffer_per_tensor": round(mem[0] / 1e9, 2), "planned": round(mem[1] / 1e9, 2)},
                        "l2": "activations of one step (%.1f GB) exceed L2" % (alg_bytes / 1e9)},

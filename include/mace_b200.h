@@ -231,6 +231,24 @@ int mb_conv2d_f32_nchw(mb_context *ctx, const float *in, const float *filter_oih
                        int pad_top, int pad_left, int64_t Ho, int64_t Wo,
                        int activation, float max_limit, float coefficient);
 
+/* The same convolution with a residual: out = act(conv(in) + bias + residual),
+ * residual shaped like out.  What a net runs after merging a convolution with
+ * the Eltwise SUM (and its Activation) that consumes it — a bottleneck block's
+ * last 1x1 convolution and its shortcut; for 1x1 stride-1 convolutions the sum
+ * and the activation run in the GEMM's epilogue, other shapes run the
+ * convolution and then one sum + activation pass in place.  The values are
+ * those of the separate operators: (acc + bias) + residual, then the
+ * activation.  residual == NULL is mb_conv2d_f32_nchw. */
+int mb_conv2d_f32_nchw_residual(mb_context *ctx, const float *in,
+                                const float *filter_oihw, const float *bias,
+                                const float *residual, float *out, int64_t N,
+                                int64_t C, int64_t H, int64_t W, int64_t O,
+                                int64_t KH, int64_t KW, int stride_h,
+                                int stride_w, int dil_h, int dil_w, int pad_top,
+                                int pad_left, int64_t Ho, int64_t Wo,
+                                int activation, float max_limit,
+                                float coefficient);
+
 /* fp32 depthwise conv, NCHW, filter [multiplier, C, kh, kw]: replaces
  * ref::DepthwiseConv2d<float> (mace/ops/ref/depthwise_conv_2d.cc:36-125). */
 int mb_dwconv_f32_nchw(mb_context *ctx, const float *in, const float *filter,

@@ -78,6 +78,7 @@ PROTOTYPES = {
     "mb_gemm_f32": (_int, [_vp] * 4 + [_i64] * 4 + [_int] * 5),
     "mb_gemv_f32": (_int, [_vp] * 5 + [_i64] * 3 + [_int] * 2),
     "mb_conv2d_f32_nchw": (_int, [_vp] * 5 + [_i64] * 7 + [_int] * 6 + [_i64] * 2 + [_int, _f32, _f32]),
+    "mb_conv2d_f32_nchw_residual": (_int, [_vp] * 6 + [_i64] * 7 + [_int] * 6 + [_i64] * 2 + [_int, _f32, _f32]),
     "mb_dwconv_f32_nchw": (_int, [_vp] * 5 + [_i64] * 7 + [_int] * 6 + [_i64] * 2 + [_int, _f32, _f32]),
     "mb_winograd_transform_filter_f32": (_int, [_vp] * 3 + [_i64] * 2 + [_int]),
     "mb_conv3x3_winograd_f32_nchw": (_int, [_vp] * 6 + [_i64] * 5 + [_int] * 2 + [_i64] * 2 +
@@ -296,6 +297,13 @@ class Context:
         self._check(lib().mb_conv2d_f32_nchw(
             self.h, x.ptr, f.ptr, bias.ptr if bias is not None else None, out.ptr, N, Cc, H, W,
             O, KH, KW, strides[0], strides[1], dil[0], dil[1], pad_tl[0], pad_tl[1], out_hw[0],
+            out_hw[1], act, max_limit, coef))
+
+    def conv2d_f32_residual(self, x, f, bias, residual, out, N, Cc, H, W, O, KH, KW, strides, dil, pad_tl,
+                            out_hw, act=0, max_limit=0.0, coef=0.0):
+        self._check(lib().mb_conv2d_f32_nchw_residual(
+            self.h, x.ptr, f.ptr, bias.ptr if bias is not None else None, residual.ptr, out.ptr, N, Cc, H,
+            W, O, KH, KW, strides[0], strides[1], dil[0], dil[1], pad_tl[0], pad_tl[1], out_hw[0],
             out_hw[1], act, max_limit, coef))
 
     def dwconv_f32(self, x, f, bias, out, N, Cc, H, W, Mc, KH, KW, strides, dil, pad_tl, out_hw,

@@ -16,7 +16,7 @@ int mb_gemm_f32_tc_launch(mb_context *ctx, const float *X, const float *W, const
                           int64_t batch, int64_t Mdim, int64_t Ndim, int64_t K, int64_t x_row_stride,
                           int64_t x_batch_stride, int64_t w_row_stride, int64_t w_batch_stride,
                           int64_t c_row_stride, int64_t c_batch_stride, int act, float max_limit,
-                          float coef);
+                          float coef, const float *residual);
 
 namespace {
 
@@ -275,7 +275,7 @@ int mb_gemm_f32_strided(mb_context *ctx, const float *A, const float *B, float *
   if (a_cs == 1 && b_cs == 1 && c_cs == 1 &&
       mb_gemm_f32_tc_supported(ctx, B, A, N, M, K, b_rs, b_bs, a_rs, a_bs)) {
     return mb_gemm_f32_tc_launch(ctx, B, A, bias_per_row, C, batch, N, M, K, b_rs, b_bs, a_rs, a_bs,
-                                 c_rs, c_bs, act, max_limit, coef);
+                                 c_rs, c_bs, act, max_limit, coef, nullptr);
   }
   if (batch > 65535 || ceil_div64(M, FT) > 65535)
     return mb_fail(ctx, MB_UNSUPPORTED, "fp32 GEMM: batch or M too large for this kernel");
@@ -469,6 +469,37 @@ int mb_conv2d_f32_nchw(mb_context *ctx, const float *in, const float *filter, co
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   return MB_SUCCESS;
+}
+
+int mb_conv2d_f32_nchw_residual(mb_context *ctx, const float *in, const float *filter, const float *bias,
+                                const float *residual, float *out, int64_t N, int64_t C, int64_t H,
+                                int64_t W, int64_t O, int64_t KH, int64_t KW, int stride_h, int stride_w,
+                                int dil_h, int dil_w, int pad_top, int pad_left, int64_t Ho, int64_t Wo,
+                                int activation, float max_limit, float coefficient) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (residual == nullptr)
+    return mb_conv2d_f32_nchw(ctx, in, filter, bias, out, N, C, H, W, O, KH, KW, stride_h, stride_w, dil_h,
+                              dil_w, pad_top, pad_left, Ho, Wo, activation, max_limit, coefficient);
+  bool empty;
+  MB_RETURN_IF_ERROR(check_conv_f32(ctx, "mb_conv2d_f32_nchw_residual", in, filter, out, N, C, H, W, O, KH,
+                                    KW, stride_h, stride_w, dil_h, dil_w, pad_top, pad_left, Ho, Wo,
+                                    activation, &empty));
+  if (empty) return MB_SUCCESS;
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  const int64_t hw = H * W;
+  // 1x1 stride 1 on the tensor cores: the sum and the activation ride in the GEMM's epilogue
+  if (KH == 1 && KW == 1 && stride_h == 1 && stride_w == 1 && pad_top == 0 && pad_left == 0 && Ho == H &&
+      Wo == W && hw % 4 == 0 && hw >= 128 &&
+      mb_gemm_f32_tc_supported(ctx, in, filter, hw, O, C, hw, C * hw, C, 0) &&
+      (reinterpret_cast<uintptr_t>(residual) & 3u) == 0) {
+    return mb_gemm_f32_tc_launch(ctx, in, filter, bias, out, N, hw, O, C, hw, C * hw, C, 0, hw, O * hw,
+                                 activation, max_limit, coefficient, residual);
+  }
+  // every other shape: the convolution without activation, then sum + activation in place
+  MB_RETURN_IF_ERROR(mb_conv2d_f32_nchw(ctx, in, filter, bias, out, N, C, H, W, O, KH, KW, stride_h, stride_w,
+                                        dil_h, dil_w, pad_top, pad_left, Ho, Wo, 0, 0.f, 0.f));
+  return mb_eltwise_act_f32(ctx, out, residual, out, N * O * Ho * Wo, 0, 0.f, 0, 0.f, 0.f, 0, activation,
+                            max_limit, coefficient);
 }
 
 int mb_dwconv_f32_nchw(mb_context *ctx, const float *in, const float *filter, const float *bias,

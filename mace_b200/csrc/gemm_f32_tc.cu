@@ -6,7 +6,7 @@
 // arm::Gemm per image), the 1x1 convolution (arm::Conv2dK1x1,
 // mace/ops/arm/base/conv_2d_1x1.cc:61-68), the im2col form of the general convolution and
 // MatMul/Gemm (mace/ops/arm/base/gemm.cc:520-683) in the layout all of them share:
-//     C[b][n][m] = act(bias[n] + sum_k X[b][k][m] * W[b][n][k])
+//     C[b][n][m] = act(bias[n] + sum_k X[b][k][m] * W[b][n][k] [+ R[b][n][m]])
 // X is [K x Mdim] with m contiguous (an activation matrix: channels x pixels), W is
 // [Ndim x K] with k contiguous (a filter matrix: output channels x channels), C is
 // [Ndim x Mdim] with m contiguous (output channels x pixels).  The long pixel dimension is
@@ -67,6 +67,7 @@ struct F32TcParams {
   int step_m, step_n, step_b;
   int x_batched, w_batched;
   const float *bias;  // per n, or null
+  const float *residual;  // null, or a tensor laid out like C that is added before the activation
   int act;
   float max_limit, coef;
   float *C;
@@ -405,6 +406,7 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const bool leaky = p.act == 6;
     const float *__restrict__ bias = p.bias;
     const bool has_bias = bias != nullptr;
+    const float *__restrict__ residual = p.residual;
     const int64_t Ndim = p.Ndim;
     const int c_tma = p.c_tma;
     int acc_buf = 0;
@@ -431,6 +433,32 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
       // value, and with eight warps nothing hides a branch: that form took 750 cycles a chunk.)
       float b_next = 0.f;
       if (has_bias) b_next = bias[min(n_first + (lane & 15), Ndim - 1)];
+      // Residual (a tensor laid out like C, e.g. a bottleneck block's shortcut): the 16 values
+      // of a chunk are requested one chunk ahead, from addresses clamped into the tensor
+      // instead of guarded by branches; a lane's loads of one channel are 128 contiguous bytes
+      // across the warp.
+      const float *res = residual != nullptr
+                             ? residual + it.b * p.c_batch_stride + min(m, p.Mdim - 1)
+                             : nullptr;
+      float r_next[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) r_next[j] = 0.f;
+      if (res != nullptr) {
+        // ask L2 for the NEXT tile's residual rows now (lane j: the 128-byte piece of channel j
+        // of each chunk), a whole tile ahead of the loads that will want them
+        FTileIter nit = it;
+        nit.next(p);
+        if (nit.valid(p) && lane < 16) {
+          const float *nres = residual + nit.b * p.c_batch_stride +
+                              min(static_cast<int64_t>(nit.tm) * FBM + quarter * 32, p.Mdim - 1);
+          const int64_t nn = static_cast<int64_t>(nit.tn) * BN + set * (BN / 2) + lane;
+#pragma unroll
+          for (int c = 0; c < CHUNKS; ++c)
+            prefetch_l2(nres + min(nn + c * 16, Ndim - 1) * p.c_row_stride);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r_next[j] = __ldg(res + min(n_first + j, Ndim - 1) * p.c_row_stride);
+      }
       // staging, per set of four warps: [buffer][channel j][128 pixels]; a lane's 16 writes of
       // a chunk go to 16 different rows, a warp's write of one row covers all 32 banks.  The
       // four warps fill one [16 x 128] tile together and one thread stores it with a single
@@ -450,11 +478,19 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int64_t n0 = n_first + i * 16;
         const float b_cur = b_next;
         if (has_bias && i + 1 < CHUNKS) b_next = bias[min(n0 + 16 + (lane & 15), Ndim - 1)];
+        float r_cur[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r_cur[j] = r_next[j];
+        if (res != nullptr && i + 1 < CHUNKS) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r_next[j] = __ldg(res + min(n0 + 16 + j, Ndim - 1) * p.c_row_stride);
+        }
         float v[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const float bj = __shfl_sync(0xffffffffu, b_cur, j);
-          const float x = __uint_as_float(r[i & 1][j]) + bj;
+          // (acc + bias) + residual: the rounding order of a convolution followed by a sum
+          const float x = (__uint_as_float(r[i & 1][j]) + bj) + r_cur[j];
           const float neg = leaky ? fminf(x, 0.f) * act_slope : 0.f;
           v[j] = fminf(fmaxf(x, act_lo), act_hi) + neg;
         }
@@ -570,7 +606,7 @@ int mb_gemm_f32_tc_launch(mb_context *ctx, const float *X, const float *W, const
                           int64_t batch, int64_t Mdim, int64_t Ndim, int64_t K, int64_t x_row_stride,
                           int64_t x_batch_stride, int64_t w_row_stride, int64_t w_batch_stride,
                           int64_t c_row_stride, int64_t c_batch_stride, int act, float max_limit,
-                          float coef) {
+                          float coef, const float *residual) {
   const int BN = Ndim > 64 ? 128 : 64;
   F32TcParams p;
   p.Mdim = Mdim; p.Ndim = Ndim; p.K = K; p.batch = batch;
@@ -578,7 +614,7 @@ int mb_gemm_f32_tc_launch(mb_context *ctx, const float *X, const float *W, const
   p.tiles_n = static_cast<int>(ceil_div64(Ndim, BN));
   p.k_blocks = static_cast<int>(ceil_div64(K, FKB));
   p.x_batched = x_batch_stride != 0; p.w_batched = w_batch_stride != 0;
-  p.bias = bias; p.act = act; p.max_limit = max_limit; p.coef = coef;
+  p.bias = bias; p.residual = residual; p.act = act; p.max_limit = max_limit; p.coef = coef;
   p.C = C; p.c_row_stride = c_row_stride; p.c_batch_stride = c_batch_stride;
   p.status = ctx->dev_status;
   p.timeline = ctx->tc_timeline;

@@ -133,6 +133,11 @@ __device__ __forceinline__ bool mbar_wait_warp_relaxed(uint32_t bar, uint32_t pa
   return __all_sync(0xffffffffu, ok);
 }
 
+// Ask for the 128-byte line that holds `p` to be brought into L2.
+__device__ __forceinline__ void prefetch_l2(const void *p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 // Barrier among `threads` threads (a multiple of 32) of the CTA; id 0 is __syncthreads'.
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

@@ -58,6 +58,12 @@ int mbh_op_end(mbh_engine *engine);
  * merged pairs. */
 int mbh_fuse_activations(mbh_engine *engine, int *merged);
 
+/* After one run and after mbh_fuse_activations: merges each element-wise SUM of two tensors
+ * (with the activation it has absorbed) into the float Conv2D that produces one of them, when
+ * nothing else reads that tensor and the other one exists before the convolution runs: the
+ * convolution then writes activation(conv + residual) into the sum's output. */
+int mbh_fuse_residual_sums(mbh_engine *engine, int *merged);
+
 /* Shares activation memory between tensors whose lifetimes do not overlap (MACE's SERIAL_OPT
  * allocation strategy).  Call after one run; intermediate tensors cannot be read back afterwards.
  * The two sizes (may be NULL) are the activation bytes before and after. */

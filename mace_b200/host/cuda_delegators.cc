@@ -368,13 +368,22 @@ class Conv2d : public delegator::Conv2d {
     MACE_RETURN_IF_ERROR(Geometry(input, filter->dim(2), filter->dim(3), strides_, dilations_,
                                   paddings_, padding_type_, &g));
     MACE_RETURN_IF_ERROR(output->Resize({input->dim(0), filter->dim(0), g.out_h, g.out_w}));
-    return rt->Status(mb_conv2d_f32_nchw(
+    if (residual_ != nullptr && residual_->size() != output->size())
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "residual and convolution output differ in size");
+    return rt->Status(mb_conv2d_f32_nchw_residual(
         rt->ctx(), input->memory<float>(), filter->memory<float>(),
-        bias_ ? bias_->memory<float>() : nullptr, output->mutable_memory<float>(), input->dim(0),
-        input->dim(1), input->dim(2), input->dim(3), filter->dim(0), filter->dim(2),
-        filter->dim(3), strides_[0], strides_[1], dilations_[0], dilations_[1], g.pad_top,
-        g.pad_left, g.out_h, g.out_w, activation_, max_limit_, coefficient_));
+        bias_ ? bias_->memory<float>() : nullptr, residual_ ? residual_->memory<float>() : nullptr,
+        output->mutable_memory<float>(), input->dim(0), input->dim(1), input->dim(2), input->dim(3),
+        filter->dim(0), filter->dim(2), filter->dim(3), strides_[0], strides_[1], dilations_[0],
+        dilations_[1], g.pad_top, g.pad_left, g.out_h, g.out_w, activation_, max_limit_, coefficient_));
   }
+  bool SetResidual(const Tensor *residual) override {
+    residual_ = residual;
+    return true;
+  }
+
+ private:
+  const Tensor *residual_ = nullptr;
 };
 
 // 3x3 stride-1 Winograd; the transformed filter is cached while the filter is a

@@ -95,6 +95,13 @@ class Conv2d : public OpDelegator {
     max_limit_ = max_limit;
     coefficient_ = coefficient;
   }
+  // A tensor shaped like the output that is added before the activation (a residual sum merged
+  // into the convolution by the net); delegators that cannot fuse it ignore the setter's
+  // return value at their peril, so it says whether the delegator will apply it.
+  virtual bool SetResidual(const Tensor *residual) {
+    (void)residual;
+    return false;
+  }
 
  protected:
   const std::vector<int> strides_;

@@ -178,7 +178,9 @@ class Conv2dOp<RuntimeType::RT_CUDA, float> : public ConvPool2dOpBase {
 
   MaceStatus Run(OpContext *context) override {
     const Tensor *input = Input(0), *filter = Input(1);
-    const Tensor *bias = InputSize() >= 3 ? Input(2) : nullptr;
+    // (an absorbed residual is appended to the inputs, so that the net sees its last reader)
+    const int own_inputs = InputSize() - (residual_ != nullptr ? 1 : 0);
+    const Tensor *bias = own_inputs >= 3 ? Input(2) : nullptr;
     if (strides_.size() != 2) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "strides must have 2 values");
     MaceStatus st;
     const ActivationType act = StringToActivationType(activation_name_, &st);
@@ -201,8 +203,23 @@ class Conv2dOp<RuntimeType::RT_CUDA, float> : public ConvPool2dOpBase {
       }
     }
     conv2d_delegator_->SetBias(bias);
-    conv2d_delegator_->SetActivation(act, max_limit_, coefficient_);
+    if (residual_ != nullptr) {
+      conv2d_delegator_->SetActivation(sum_.activation, sum_.max_limit, sum_.coefficient);
+    } else {
+      conv2d_delegator_->SetActivation(act, max_limit_, coefficient_);
+    }
     return conv2d_delegator_->Compute(context, input, filter, Output(0));
+  }
+
+  // Needs the delegator, i.e. one Run() before the net merges operators.
+  bool AbsorbResidualSum(const Tensor *residual, const ResidualSum &sum, Tensor *sum_output) override {
+    if (residual_ != nullptr || conv2d_delegator_ == nullptr || activation_name_ != "NOOP") return false;
+    if (!conv2d_delegator_->SetResidual(residual)) return false;
+    residual_ = residual;
+    sum_ = sum;
+    inputs_.push_back(residual);
+    outputs_[0] = sum_output;
+    return true;
   }
 
  private:
@@ -210,6 +227,8 @@ class Conv2dOp<RuntimeType::RT_CUDA, float> : public ConvPool2dOpBase {
   std::string activation_name_;
   float max_limit_, coefficient_;
   std::unique_ptr<delegator::Conv2d> conv2d_delegator_;
+  const Tensor *residual_ = nullptr;
+  ResidualSum sum_;
 };
 
 template <>
@@ -588,6 +607,15 @@ class EltwiseOp<RuntimeType::RT_CUDA, float> : public Operation {
                                          static_cast<int>(fused_act_), fused_max_limit_, fused_coefficient_));
   }
 
+  bool DescribeResidualSum(ResidualSum *sum) const override {
+    if (type_ != 0 /* SUM */ || !coeff_.empty() || InputSize() != 2) return false;
+    if (Input(0)->size() != Input(1)->size()) return false;
+    sum->activation = static_cast<int>(fused_act_);
+    sum->max_limit = fused_max_limit_;
+    sum->coefficient = fused_coefficient_;
+    return true;
+  }
+
   bool AbsorbActivation(const OperatorDef &def, Tensor *activation_output) override {
     if (fused_act_ != NOOP || def.input.size() != 1) return false;  // PRELU has an alpha input
     auto name = def.s.find("activation");
@@ -792,6 +820,40 @@ int SerialNet::FuseActivations() {
         ++merged;
       }
       break;
+    }
+  }
+  return merged;
+}
+
+int SerialNet::FuseResidualSums() {
+  DropCapture();
+  std::map<std::string, int> readers;
+  std::map<std::string, size_t> producer;
+  for (size_t i = 0; i < defs_.size(); ++i) {
+    if (skipped_[i]) continue;
+    for (const std::string &in : defs_[i]->input) ++readers[in];
+    // the tensor an operator really writes (it may have taken over a later operator's output)
+    for (size_t k = 0; k < defs_[i]->output.size(); ++k)
+      producer[operators_[i]->Output(static_cast<unsigned>(k))->name()] = i;
+  }
+  int merged = 0;
+  for (size_t e = 0; e < defs_.size(); ++e) {
+    if (skipped_[e]) continue;
+    Operation::ResidualSum sum;
+    if (!operators_[e]->DescribeResidualSum(&sum)) continue;
+    for (int side = 0; side < 2; ++side) {
+      const Tensor *conv_out = operators_[e]->Input(side), *residual = operators_[e]->Input(1 - side);
+      auto pc = producer.find(conv_out->name());
+      if (pc == producer.end() || pc->second >= e || readers[conv_out->name()] != 1) continue;
+      if (defs_[pc->second]->type != "Conv2D") continue;
+      // the residual must exist when the convolution runs: a net input, a weight, or produced earlier
+      auto pr = producer.find(residual->name());
+      if (pr != producer.end() && pr->second >= pc->second) continue;
+      if (operators_[pc->second]->AbsorbResidualSum(residual, sum, operators_[e]->Output(0))) {
+        skipped_[e] = 1;
+        ++merged;
+        break;
+      }
     }
   }
   return merged;

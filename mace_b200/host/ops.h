@@ -93,6 +93,25 @@ class Operation {
     (void)activation_output;
     return false;
   }
+  // An operator that is a plain sum of two tensors of equal size (no coefficients, no scalar)
+  // describes itself here, with the activation it may already have absorbed, so that the
+  // operator producing one of its inputs can take the whole thing over (AbsorbResidualSum).
+  struct ResidualSum {
+    int activation = 0;  // ops::ActivationType value
+    float max_limit = 0.f, coefficient = 0.f;
+  };
+  virtual bool DescribeResidualSum(ResidualSum *sum) const {
+    (void)sum;
+    return false;
+  }
+  // out = activation(this operator's result + residual), written to `sum_output`: a convolution
+  // that can add a residual in its own kernel returns true and does that from then on.
+  virtual bool AbsorbResidualSum(const Tensor *residual, const ResidualSum &sum, Tensor *sum_output) {
+    (void)residual;
+    (void)sum;
+    (void)sum_output;
+    return false;
+  }
 
  protected:
   const OperatorDef *operator_def_;
@@ -141,6 +160,11 @@ class SerialNet {
   // Returns the number of merged pairs.  Off unless called: operator by operator the net
   // behaves like the CPU runtime's.
   int FuseActivations();
+  // After FuseActivations: merges each (Eltwise SUM [+ absorbed Activation]) into the float
+  // Conv2D that produces one of its two inputs, when nothing else reads that input and the
+  // other input (the residual) is produced earlier in the net; the convolution then writes
+  // activation(conv + residual) straight into the sum's output.  Returns the number of merges.
+  int FuseResidualSums();
   // Shares activation memory between tensors whose lifetimes do not overlap, the way
   // AllocateTensorMemory<SERIAL_OPT> does (mace/core/net/allocate_opt_strategy.cc:181-285): the
   // net is walked once; every operator's outputs take the best-fitting free buffer (the

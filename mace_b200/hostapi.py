@@ -44,6 +44,7 @@ _PROTOS = {
     "mbh_capture": [_vp],
     "mbh_fuse_activations": [_vp, C.POINTER(_int)],
     "mbh_plan_memory": [_vp, C.POINTER(_sz), C.POINTER(_sz)],
+    "mbh_fuse_residual_sums": [_vp, C.POINTER(_int)],
     "mbh_run_host": [_vp, _cp, _vp, _sz, _cp, _vp, _sz],
     "mbh_run_host_pipelined": [_vp, _cp, _vp, _sz, _cp, _vp, _sz, C.POINTER(_int)],
     "mbh_wait_slot": [_vp, _int],
@@ -174,6 +175,13 @@ class HostEngine:
         """Merge Activation operators into the Eltwise that feeds them; returns how many."""
         n = _int()
         self._check(lib().mbh_fuse_activations(self.h, C.byref(n)))
+        return n.value
+
+    def fuse_residual_sums(self):
+        """After one run and fuse_activations(): merge residual sums into the 1x1 convolutions
+        that feed them; returns how many."""
+        n = _int()
+        self._check(lib().mbh_fuse_residual_sums(self.h, C.byref(n)))
         return n.value
 
     def plan_memory(self):

@@ -338,3 +338,30 @@ def test_softmax_f32(ctx, orc, shape, use_log):
     # device and std::exp on the host differ by a few ulps
     assert np.abs(got - ref).max() <= (1e-4 if use_log else 1e-5)
     dx.free(); do.free()
+
+
+@pytest.mark.parametrize("case", [
+    # N, C, H, W, O, KH, stride, activation
+    (3, 64, 16, 16, 160, 1, 1, 1),     # 1x1 stride 1, 256 pixels: sum + ReLU in the GEMM's epilogue, ragged N tile
+    (2, 32, 12, 11, 48, 1, 1, 6),      # 132 pixels (a multiple of 4), LEAKYRELU
+    (4, 40, 7, 7, 72, 1, 1, 1),        # 49 pixels: images merged, then one in-place sum + ReLU pass
+    (2, 16, 14, 14, 24, 3, 1, 2),      # 3x3: convolution, then the in-place pass
+    (1, 8, 9, 9, 8, 1, 2, 0),          # tiny: direct kernel, then the in-place pass
+])
+def test_conv2d_f32_residual(ctx, orc, case):
+    """out = act((conv + bias) + residual) equals Conv2D (no activation), Eltwise SUM and
+    Activation run one after the other."""
+    N, C, H, W, O, k, st, act = case
+    x, f, bias = _conv_inputs((N, C, H, W), (O, C, k, k), H * 7 + O)
+    x = x * 2 - 1
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, k, k, (1, 1), (st, st), PAD["SAME"])
+    rng = np.random.Generator(np.random.PCG64(O))
+    res = rng.standard_normal((N, O, Ho, Wo)).astype(np.float32)
+    conv = orc.conv2d_f32(x, f, bias, (st, st), (1, 1), (ph >> 1, pw >> 1), (Ho, Wo), 0)
+    ref = orc.activation_f32(orc.eltwise_f32(conv, res, 0), act, 0.5, 0.1)
+    dx, df, db, dr, do = ctx.upload(x), ctx.upload(f), ctx.upload(bias), ctx.upload(res), ctx.alloc(ref.nbytes)
+    ctx.conv2d_f32_residual(dx, df, db, dr, do, N, C, H, W, O, k, k, (st, st), (1, 1), (ph >> 1, pw >> 1),
+                            (Ho, Wo), act, 0.5, 0.1)
+    assert rel_err(ctx.download(do, ref.shape, np.float32), ref) <= 1e-4
+    for b in (dx, df, db, dr, do):
+        b.free()

@@ -131,12 +131,21 @@ def test_resnet50_graph_against_oracle(orc, cfg):
         eng.capture()
         eng.run()
         assert np.array_equal(eng.read("fc", np.float32), first)
+        # residual sums merged into the 1x1 convolutions that feed them: the sum and the ReLU
+        # run in the GEMM's epilogue (for the 7x7-pixel stage: one in-place pass after it)
+        before = {n["name"]: eng.read(n["name"], np.float32) for n in nodes if n["op"] in ("relu", "fc", "maxpool")}
+        assert eng.fuse_residual_sums() == 16
+        eng.run()
+        for name, want in before.items():
+            got = eng.read(name, np.float32)
+            assert float(np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)) <= 1e-6, name
         # activation memory shared between tensors with disjoint lifetimes: same logits from
         # less than a third of the memory, also through a re-captured graph and for new inputs
+        fused_logits = eng.read("fc", np.float32)
         separate, shared = eng.plan_memory()
         assert 0 < shared < separate / 3, (separate, shared)
         eng.run()
-        assert np.array_equal(eng.read("fc", np.float32), first)
+        assert np.array_equal(eng.read("fc", np.float32), fused_logits)
         eng.capture()
         x2 = rn.random_images(cfg["batch"], 7, cfg["image"])
         eng.write("input", x2)
