@@ -596,6 +596,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       } else {
         // direct stores: int32 output, or a uint8 output whose rows TMA cannot address
         uint8_t *c8 = static_cast<uint8_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
+        const bool words_ok = !p.out_is_int32 && (p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 3u) == 0;
         int32_t *c32 = static_cast<int32_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
         uint32_t r[1][CHUNK];
         tmem_ld_32x32b_x16(tbase, r[0]);
@@ -608,7 +609,27 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (i + 1 < CHUNKS_PER_WARP) tmem_ld_32x32b_x16(tbase + (i + 1) * CHUNK, r[0]);
           const int64_t n0 = n_first + i * CHUNK;
           const int32_t *ct = ct_base + i * CHUNK;
-          if (row_ok && n0 < p.N) {
+          if (words_ok && n0 + CHUNK <= p.N) {
+            // a whole chunk of a uint8 row whose words are 4-byte aligned (N % 4 == 0, e.g. the
+            // 1000 logits of a classifier, which TMA cannot address): requantize without a
+            // branch per value and store four words instead of sixteen bytes
+            uint32_t packed[CHUNK / 4];
+            const int4 *ct4 = reinterpret_cast<const int4 *>(ct);
+            switch (p.rq_variant) {
+              case 8: requant_chunk<8>(v, row_term, ct4, p, packed); break;
+              case 5: requant_chunk<5>(v, row_term, ct4, p, packed); break;
+              case 4: requant_chunk<4>(v, row_term, ct4, p, packed); break;
+              case 3: requant_chunk<3>(v, row_term, ct4, p, packed); break;
+              case 2: requant_chunk<2>(v, row_term, ct4, p, packed); break;
+              case 1: requant_chunk<1>(v, row_term, ct4, p, packed); break;
+              default: requant_chunk<0>(v, row_term, ct4, p, packed); break;
+            }
+            if (row_ok) {
+              uint32_t *cw = reinterpret_cast<uint32_t *>(c8 + n0);
+#pragma unroll
+              for (int q = 0; q < CHUNK / 4; ++q) cw[q] = packed[q];
+            }
+          } else if (row_ok && n0 < p.N) {
 #pragma unroll
             for (int j = 0; j < CHUNK; ++j) {
               const int32_t acc = static_cast<int32_t>(v[j]) + row_term + ct[j];
