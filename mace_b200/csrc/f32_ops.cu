@@ -261,6 +261,19 @@ unmerge_f32_kernel(const float *__restrict__ src, float *__restrict__ dst, int64
   dst[i] = __ldg(src + o * src_rs + n * hw + pos);
 }
 
+// out[c][r] = in[r][c] for a [rows x cols] matrix, through a 32 x 33 shared-memory tile.
+__global__ void __launch_bounds__(256)
+transpose_f32_kernel(const float *__restrict__ in, float *__restrict__ out, int rows, int cols) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int i = ty; i < 32; i += 8)
+    if (r0 + i < rows && c0 + tx < cols) tile[i][tx] = __ldg(in + static_cast<int64_t>(r0 + i) * cols + c0 + tx);
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8)
+    if (c0 + i < cols && r0 + tx < rows) out[static_cast<int64_t>(c0 + i) * rows + r0 + tx] = tile[tx][i];
+}
+
 }  // namespace
 
 // Strided batched fp32 GEMM with optional per-row bias and activation; the
@@ -396,6 +409,28 @@ int mb_gemv_f32(mb_context *ctx, const float *lhs, const float *rhs, const float
   if (lhs == nullptr || rhs == nullptr || out == nullptr)
     return mb_fail(ctx, MB_INVALID_ARGS, "mb_gemv_f32: null operand");
   MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  // Many vectors against one matrix (FullyConnected on a batch) on the tensor cores: the
+  // vectors are transposed to [K x batch] (the kernel's activation operand has the long
+  // dimension contiguous), the product comes out as [rows x batch] and is transposed back.
+  if (!lhs_batched && rhs_batched && batch >= 32 && batch % 4 == 0 && K % 4 == 0 && rows >= 16 &&
+      batch < (1 << 30) && K < (1 << 30) && rows < (1 << 30)) {
+    float *scratch = nullptr;
+    const size_t xt_bytes = align_up(sizeof(float) * K * batch, 256);
+    MB_RETURN_IF_ERROR(mb_scratch(ctx, xt_bytes + sizeof(float) * rows * batch, reinterpret_cast<void **>(&scratch)));
+    float *xt = scratch, *ct = scratch + xt_bytes / sizeof(float);
+    if (mb_gemm_f32_tc_supported(ctx, xt, lhs, batch, rows, K, batch, 0, K, 0)) {
+      dim3 g1(static_cast<unsigned>(ceil_div64(K, 32)), static_cast<unsigned>(ceil_div64(batch, 32)));
+      transpose_f32_kernel<<<g1, 256, 0, ctx->stream>>>(rhs, xt, static_cast<int>(batch), static_cast<int>(K));
+      MB_CUDA(ctx, cudaGetLastError());
+      MB_RETURN_IF_ERROR(mb_gemm_f32_tc_launch(ctx, xt, lhs, bias, ct, 1, batch, rows, K, batch, 0, K, 0, batch, 0,
+                                               0, 0.f, 0.f, nullptr));
+      dim3 g2(static_cast<unsigned>(ceil_div64(batch, 32)), static_cast<unsigned>(ceil_div64(rows, 32)));
+      transpose_f32_kernel<<<g2, 256, 0, ctx->stream>>>(ct, out, static_cast<int>(rows), static_cast<int>(batch));
+      MB_CUDA(ctx, cudaGetLastError());
+      ctx->launches += 2;
+      return MB_SUCCESS;
+    }
+  }
   int64_t chunks = std::min<int64_t>(batch, 65535);
   if (!lhs_batched)
     chunks = std::min<int64_t>(chunks, std::max<int64_t>(1, (4ll * ctx->num_sms) / ceil_div64(rows, 8)));

@@ -74,7 +74,7 @@ def test_gemm_f32_literals_and_one_side_batched(ctx, orc):
     assert rel_err(ctx.download(dC, (4 * 24 * 56,), np.float32), ref) <= 1e-4
 
 
-@pytest.mark.parametrize("shape", [(1, 16, 4), (3, 63, 257), (17, 65, 100), (256, 1000, 2048)])
+@pytest.mark.parametrize("shape", [(1, 16, 4), (3, 63, 257), (17, 65, 100), (36, 50, 260), (256, 1000, 2048)])
 def test_gemv_f32(ctx, orc, shape):
     batch, rows, K = shape
     rng = np.random.Generator(np.random.PCG64(7))
@@ -251,6 +251,9 @@ def test_conv2d_f32_column_route(ctx, orc, case, budget_mb):
     (2, 16, 7, 7, 7, 1, 1, "VALID"),      # global pooling
     (1, 4, 13, 11, 3, 1, 2, "SAME"),      # dilated
     (2, 3, 10, 10, 5, 3, 1, "FULL"),      # windows that overlap the border by more than half
+    (2, 6, 16, 24, 3, 2, 1, "SAME"),      # rows of a multiple of 4: four outputs per thread, 128-bit accesses
+    (1, 3, 20, 20, 3, 2, 1, "VALID"),     # ... with an output width that is not a multiple of 4
+    (2, 4, 112, 112, 3, 2, 1, "SAME"),    # ResNet's pooling layer at full size
 ])
 @pytest.mark.parametrize("ptype", [1, 2])
 def test_pooling_f32(ctx, orc, case, ptype):
