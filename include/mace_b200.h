@@ -342,6 +342,17 @@ int mb_dequantize_f32(mb_context *ctx, const void *in, int in_is_int32,
 int mb_minmax_f32(mb_context *ctx, const float *in, int64_t size,
                   float *host_min, float *host_max);
 
+/* ---- Layout conversion at the edge of a network: replaces ops::Transpose as
+ * BaseFlow::TransposeInput / TransposeOutput call it for NHWC <-> NCHW
+ * (mace/core/flow/base_flow.cc:131-204, mace/flows/cpu/cpu_ref_flow.cc:81-101)
+ * and the Transpose operator for those permutations (mace/ops/transpose.cc).
+ *   out[b][c][r] = in[b][r][c],  in [batch, rows, cols], out [batch, cols, rows]
+ * NHWC -> NCHW: rows = H * W, cols = C; NCHW -> NHWC: rows = C, cols = H * W.
+ * elem_bytes is 1 or 4; in and out must not overlap. */
+int mb_transpose2d_batched(mb_context *ctx, const void *in, void *out,
+                           int64_t batch, int64_t rows, int64_t cols,
+                           int elem_bytes);
+
 /* ---- uint8 GEMM without any allocation ------------------------------------
  * No counterpart in the reference.  For callers that may not allocate device
  * memory (a real-time loop with a fixed memory budget, a plugin inside an

@@ -91,6 +91,7 @@ PROTOTYPES = {
     "mb_quantize_f32_u8": (_int, [_vp] * 3 + [_i64, _f32, _i32]),
     "mb_dequantize_f32": (_int, [_vp, _vp, _int, _vp, _i64, _f32, _i32]),
     "mb_minmax_f32": (_int, [_vp, _vp, _i64, C.POINTER(_f32), C.POINTER(_f32)]),
+    "mb_transpose2d_batched": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int]),
     "mb_gemm_u8_static_scratch": (_int, [_vp] * 5 + [_int] + [_i64] * 3 + [_int] * 2 +
                                   [_i32] * 5 + [_int, C.c_char_p, _sz]),
 }
@@ -354,6 +355,10 @@ class Context:
         mn, mx = _f32(), _f32()
         self._check(lib().mb_minmax_f32(self.h, x.ptr, size, C.byref(mn), C.byref(mx)))
         return mn.value, mx.value
+
+    def transpose2d_batched(self, x, out, batch, rows, cols, elem_bytes):
+        """out[b][c][r] = x[b][r][c]; NHWC -> NCHW is rows = H * W, cols = C."""
+        self._check(lib().mb_transpose2d_batched(self.h, x.ptr, out.ptr, batch, rows, cols, elem_bytes))
 
     def avgpool_u8(self, x, out, N, H, W, Cc, kernel, strides, pad_tl, out_hw):
         self._check(lib().mb_avgpool_u8_nhwc(

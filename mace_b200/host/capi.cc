@@ -1,9 +1,13 @@
 #include "capi.h"
 
+#include <algorithm>
 #include <cstring>
+#include <map>
+#include <memory>
 #include <string>
 #include <vector>
 
+#include "mace_engine.h"
 #include "ops.h"
 
 using namespace mace;  // NOLINT
@@ -350,6 +354,94 @@ int mbh_run_profiled(mbh_engine *e, float *ms_out, int max_ops, char *names_out,
   if (names_out != nullptr && names_len > 0) {
     std::strncpy(names_out, names.c_str(), names_len - 1);
     names_out[names_len - 1] = 0;
+  }
+  return MaceStatus::MACE_SUCCESS;
+}
+
+// ---- model files -------------------------------------------------------------------------
+
+struct mbh_model {
+  std::shared_ptr<MaceEngine> engine;
+  std::string last_error;
+};
+
+int mbh_netdef_describe(const void *graph, size_t graph_len, char *json_out, size_t capacity, size_t *needed) {
+  proto::NetDef net_def;
+  MaceStatus st = ParseNetDef(graph, graph_len, &net_def);
+  const std::string text = st == MaceStatus::MACE_SUCCESS ? DescribeNetDef(net_def) : st.information();
+  if (needed != nullptr) *needed = text.size() + 1;
+  if (json_out != nullptr && capacity > 0) {
+    const size_t n = std::min(capacity - 1, text.size());
+    std::memcpy(json_out, text.data(), n);
+    json_out[n] = 0;
+  }
+  return static_cast<int>(st.code());
+}
+
+int mbh_model_create(int device, const void *graph, size_t graph_len, const void *weights, size_t weights_len,
+                     int fuse, int plan_memory, int cuda_graph, mbh_model **model, char *error, size_t error_len) {
+  if (model == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  *model = nullptr;
+  MaceEngineConfig config;
+  config.device = device;
+  config.fuse = fuse != 0;
+  config.plan_memory = plan_memory != 0;
+  config.cuda_graph = cuda_graph != 0;
+  auto m = std::make_unique<mbh_model>();
+  MaceStatus st = CreateMaceEngineFromProto(static_cast<const unsigned char *>(graph), graph_len,
+                                            static_cast<const unsigned char *>(weights), weights_len, {}, {}, config,
+                                            &m->engine);
+  if (st != MaceStatus::MACE_SUCCESS) {
+    if (error != nullptr && error_len > 0) {
+      std::strncpy(error, st.information().c_str(), error_len - 1);
+      error[error_len - 1] = 0;
+    }
+    return static_cast<int>(st.code());
+  }
+  *model = m.release();
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_model_destroy(mbh_model *model) {
+  if (model == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  delete model;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+const char *mbh_model_last_error(const mbh_model *model) { return model ? model->last_error.c_str() : "null model"; }
+
+void *mbh_model_context(mbh_model *model) { return model ? model->engine->runtime()->ctx() : nullptr; }
+
+int mbh_model_captured(mbh_model *model) { return model != nullptr && model->engine->net()->captured() ? 1 : 0; }
+
+int mbh_model_run(mbh_model *model, int n_inputs, const mbh_io_tensor *inputs, int n_outputs, mbh_io_tensor *outputs) {
+  if (model == nullptr || n_inputs < 0 || n_outputs < 0 || (n_inputs > 0 && inputs == nullptr) ||
+      (n_outputs > 0 && outputs == nullptr))
+    return MaceStatus::MACE_INVALID_ARGS;
+  auto no_delete = [](void *) {};
+  std::map<std::string, MaceTensor> in, out;
+  for (int i = 0; i < n_inputs; ++i) {
+    const mbh_io_tensor &t = inputs[i];
+    if (t.name == nullptr || t.rank < 0 || t.rank > 8) return MaceStatus::MACE_INVALID_ARGS;
+    in[t.name] = MaceTensor(std::vector<int64_t>(t.shape, t.shape + t.rank), std::shared_ptr<void>(t.data, no_delete),
+                            static_cast<DataFormat>(t.data_format), static_cast<IDataType>(t.data_type));
+  }
+  for (int i = 0; i < n_outputs; ++i) {
+    const mbh_io_tensor &t = outputs[i];
+    if (t.name == nullptr || t.rank < 0 || t.rank > 8) return MaceStatus::MACE_INVALID_ARGS;
+    out[t.name] = MaceTensor(std::vector<int64_t>(t.shape, t.shape + t.rank), std::shared_ptr<void>(t.data, no_delete),
+                             static_cast<DataFormat>(t.data_format), static_cast<IDataType>(t.data_type));
+  }
+  MaceStatus st = model->engine->Run(in, &out);
+  if (st != MaceStatus::MACE_SUCCESS) {
+    model->last_error = st.information();
+    return static_cast<int>(st.code());
+  }
+  for (int i = 0; i < n_outputs; ++i) {
+    const std::vector<int64_t> &shape = out[outputs[i].name].shape();
+    if (shape.size() > 8) return MaceStatus::MACE_INVALID_ARGS;
+    outputs[i].rank = static_cast<int>(shape.size());
+    for (size_t k = 0; k < shape.size(); ++k) outputs[i].shape[k] = shape[k];
   }
   return MaceStatus::MACE_SUCCESS;
 }

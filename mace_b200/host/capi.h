@@ -96,6 +96,43 @@ int mbh_run_host(mbh_engine *engine, const char *input_name, const void *host_in
 int mbh_run_profiled(mbh_engine *engine, float *ms_out, int max_ops, char *names_out,
                      size_t names_len, int *op_count);
 
+/* ---- Model files: the serialized NetDef of a converted model (mace/proto/mace.proto) and its
+ * weights blob, loaded and run the way CreateMaceEngineFromProto / MaceEngine::Run do
+ * (include/mace/public/mace.h:553-655). ---- */
+
+/* Parses a serialized NetDef and writes a JSON rendering of every field into json_out (always
+ * NUL-terminated, truncated to capacity); *needed (may be NULL) receives the full length
+ * including the terminator.  Needs no GPU.  MACE_INVALID_ARGS for a malformed message, with
+ * the reason in json_out. */
+int mbh_netdef_describe(const void *graph, size_t graph_len, char *json_out, size_t capacity, size_t *needed);
+
+typedef struct mbh_model mbh_model;
+
+/* One input or output in host memory, the fields of a MaceTensor: data_format 0 none, 1 NHWC,
+ * 2 NCHW; data_type 1 float, 2 uint8, 4 int32.  For an output, shape/rank state the buffer's
+ * capacity going in and the actual shape coming out. */
+typedef struct mbh_io_tensor {
+  const char *name;
+  void *data;
+  int64_t shape[8];
+  int rank;
+  int data_format;
+  int data_type;
+} mbh_io_tensor;
+
+/* fuse / plan_memory / cuda_graph: the MaceEngineConfig switches of this runtime (merge
+ * activations and residual sums, share activation memory, replay a CUDA graph), applied after
+ * the first run.  On failure the reason is copied into error (may be NULL). */
+int mbh_model_create(int device, const void *graph, size_t graph_len, const void *weights, size_t weights_len,
+                     int fuse, int plan_memory, int cuda_graph, mbh_model **model, char *error, size_t error_len);
+int mbh_model_destroy(mbh_model *model);
+const char *mbh_model_last_error(const mbh_model *model);
+void *mbh_model_context(mbh_model *model);
+/* 1 when the operator chain is currently recorded in a CUDA graph. */
+int mbh_model_captured(mbh_model *model);
+int mbh_model_run(mbh_model *model, int n_inputs, const mbh_io_tensor *inputs, int n_outputs,
+                  mbh_io_tensor *outputs);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,9 @@
 #include "ops.h"
 
+#include <algorithm>
 #include <numeric>
+#include <set>
+#include <type_traits>
 
 namespace mace {
 
@@ -127,6 +130,9 @@ template <RuntimeType D, class T> class ActivationOp;
 template <RuntimeType D, class T> class SoftmaxOp;
 template <RuntimeType D, class T> class QuantizeOp;
 template <RuntimeType D, class T> class DequantizeOp;
+template <RuntimeType D, class T> class TransposeOp;
+template <RuntimeType D, class T> class SqueezeOp;
+template <RuntimeType D, class T> class ReshapeOp;
 
 template <>
 class Conv2dOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
@@ -751,6 +757,162 @@ class DequantizeOp<RuntimeType::RT_CUDA, T> : public Operation {
   }
 };
 
+// Transpose (mace/ops/transpose.cc:34-73) for the permutations that move one block of
+// adjacent axes behind the axes that follow it: {0,3,1,2}, {0,2,3,1}, {1,0}, {0,2,1}, ... --
+// each a batched 2-D transpose.  Other permutations return MACE_UNSUPPORTED.
+template <RuntimeType D, class T>
+class TransposeOp : public Operation {
+ public:
+  explicit TransposeOp(OpConstructContext *context) : Operation(context), dims_(GetRepeatedArgs<int>("dims")) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0);
+    Tensor *output = Output(0);
+    const std::vector<index_t> &in_shape = input->shape();
+    const size_t rank = in_shape.size();
+    if (dims_.size() != rank || rank < 2 || rank > 4)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "rank should be 2, 3 or 4");
+    std::vector<index_t> out_shape;
+    for (int d : dims_) {
+      if (d < 0 || static_cast<size_t>(d) >= rank) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "bad dims");
+      out_shape.push_back(in_shape[d]);
+    }
+    MACE_RETURN_IF_ERROR(output->Resize(out_shape));
+    output->SetScale(input->scale());
+    output->SetZeroPoint(input->zero_point());
+    // dims_ = (0 .. b-1) (b+k .. rank-1) (b .. b+k-1)
+    size_t b = 0;
+    while (b < rank && dims_[b] == static_cast<int>(b)) ++b;
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    if (b == rank)
+      return rt->Status(mb_memcpy_d2d(rt->ctx(), output->mutable_memory<void>(), input->memory<void>(),
+                                      static_cast<size_t>(input->raw_size())));
+    const size_t first = static_cast<size_t>(dims_[b]);  // = b + k
+    bool rotation = first > b;
+    for (size_t i = b; i < rank && rotation; ++i) {
+      const size_t want = i - b < rank - first ? first + (i - b) : b + (i - b) - (rank - first);
+      rotation = static_cast<size_t>(dims_[i]) == want;
+    }
+    if (!rotation) return MaceStatus(MaceStatus::MACE_UNSUPPORTED, "Transpose: permutation is not a batched 2-D transpose");
+    index_t batch = 1, rows = 1, cols = 1;
+    for (size_t i = 0; i < b; ++i) batch *= in_shape[i];
+    for (size_t i = b; i < first; ++i) rows *= in_shape[i];
+    for (size_t i = first; i < rank; ++i) cols *= in_shape[i];
+    return rt->Status(mb_transpose2d_batched(rt->ctx(), input->memory<void>(), output->mutable_memory<void>(), batch,
+                                             rows, cols, static_cast<int>(sizeof(T))));
+  }
+
+ private:
+  std::vector<int> dims_;
+};
+
+// Squeeze (mace/ops/squeeze.cc:25-84) and Reshape (mace/ops/reshape.cc:27-133).  The CPU
+// operators let the output reuse the input's buffer; here the output keeps memory of its own
+// and the bytes are copied on the device, so that the shared-memory plan, which frees a buffer
+// after its tensor's last reader, never sees two tensors in one buffer.
+template <RuntimeType D, class T>
+class SqueezeOp : public Operation {
+ public:
+  explicit SqueezeOp(OpConstructContext *context)
+      : Operation(context), axis_(GetRepeatedArgs<int>("axis", {})), checked_(false) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0);
+    Tensor *output = Output(0);
+    if (!checked_ && !std::is_same<T, uint8_t>::value) {
+      // float tensors of this runtime are NCHW like the CPU runtime's: axes given for NHWC move
+      if (GetOptionalArg<int>("has_data_format", 0) != 0 && input->dim_size() == 4 && axis_.size() == 2 &&
+          axis_[0] == 1 && axis_[1] == 2) {
+        axis_[0] = 2;
+        axis_[1] = 3;
+      }
+      checked_ = true;
+    }
+    std::vector<index_t> out_shape;
+    for (index_t i = 0; i < input->dim_size(); ++i) {
+      const bool listed = std::find(axis_.begin(), axis_.end(), static_cast<int>(i)) != axis_.end();
+      if (input->dim(static_cast<unsigned>(i)) > 1 || (!axis_.empty() && !listed))
+        out_shape.push_back(input->dim(static_cast<unsigned>(i)));
+    }
+    MACE_RETURN_IF_ERROR(output->Resize(out_shape));
+    output->SetScale(input->scale());
+    output->SetZeroPoint(input->zero_point());
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    return rt->Status(mb_memcpy_d2d(rt->ctx(), output->mutable_memory<void>(), input->memory<void>(),
+                                    static_cast<size_t>(input->raw_size())));
+  }
+
+ private:
+  std::vector<int> axis_;
+  bool checked_;
+};
+
+template <RuntimeType D, class T>
+class ReshapeOp : public Operation {
+ public:
+  explicit ReshapeOp(OpConstructContext *context)
+      : Operation(context), dim_(GetRepeatedArgs<int>("dim", {})),
+        has_df_(GetOptionalArg<int>("has_data_format", 0) != 0) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0);
+    Tensor *output = Output(0);
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    if (dim_.empty()) {
+      // the shape tensor (int32, a constant of the model) is read back once
+      if (InputSize() < 2) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Reshape needs a dim argument or a shape input");
+      const Tensor *shape = Input(1);
+      if (shape->dtype() != DT_INT32) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Reshape: the shape input must be int32");
+      std::vector<int32_t> host(static_cast<size_t>(shape->size()));
+      MACE_RETURN_IF_ERROR(rt->Status(mb_memcpy_d2h(rt->ctx(), host.data(), shape->memory<void>(),
+                                                    static_cast<size_t>(shape->raw_size()))));
+      MACE_RETURN_IF_ERROR(rt->Status(mb_stream_sync(rt->ctx())));
+      dim_.assign(host.begin(), host.end());
+    }
+    std::vector<int> target = dim_;
+    if (has_df_ && !std::is_same<T, uint8_t>::value && target.size() == 4)
+      target = {target[0], target[3], target[1], target[2]};  // NHWC -> NCHW
+    // GetOutputShape (reshape.cc:27-69): one -1 is inferred, 0 keeps the input's extent
+    std::vector<index_t> out_shape(target.size());
+    index_t product = 1;
+    int unknown = -1;
+    for (size_t i = 0; i < target.size(); ++i) {
+      if (target[i] == -1) {
+        if (unknown != -1) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Only one input size may be -1");
+        unknown = static_cast<int>(i);
+        out_shape[i] = 1;
+      } else if (target[i] == 0) {
+        if (static_cast<index_t>(i) >= input->dim_size())
+          return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "dims:0 out of input dims' range.");
+        out_shape[i] = input->dim(static_cast<unsigned>(i));
+        product *= out_shape[i];
+      } else {
+        if (target[i] < 0) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Shape must be non-negative");
+        out_shape[i] = target[i];
+        product *= target[i];
+      }
+    }
+    if (unknown != -1) {
+      if (product == 0) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Cannot infer shape if there is zero shape size.");
+      const index_t missing = input->size() / product;
+      if (missing * product != input->size())
+        return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Input size not match reshaped tensor size");
+      out_shape[static_cast<size_t>(unknown)] = missing;
+      product *= missing;
+    }
+    if (product != input->size()) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Input size not match reshaped tensor size");
+    MACE_RETURN_IF_ERROR(output->Resize(out_shape));
+    output->SetScale(input->scale());
+    output->SetZeroPoint(input->zero_point());
+    return rt->Status(mb_memcpy_d2d(rt->ctx(), output->mutable_memory<void>(), input->memory<void>(),
+                                    static_cast<size_t>(input->raw_size())));
+  }
+
+ private:
+  std::vector<int> dim_;
+  bool has_df_;
+};
+
 #define MACE_REGISTER_OP(registry, op_type, class_name, runtime, dt)                             \
   registry->Register(op_type, runtime, DataTypeToEnum<dt>::value,                                \
                      [](OpConstructContext *context) -> std::unique_ptr<Operation> {             \
@@ -774,6 +936,12 @@ void RegisterAllCudaOps(OpRegistry *registry) {
   MACE_REGISTER_OP(registry, "Quantize", QuantizeOp, RuntimeType::RT_CUDA, uint8_t);
   MACE_REGISTER_OP(registry, "Dequantize", DequantizeOp, RuntimeType::RT_CUDA, uint8_t);
   MACE_REGISTER_OP(registry, "Dequantize", DequantizeOp, RuntimeType::RT_CUDA, int32_t);
+  MACE_REGISTER_OP(registry, "Transpose", TransposeOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "Transpose", TransposeOp, RuntimeType::RT_CUDA, uint8_t);
+  MACE_REGISTER_OP(registry, "Squeeze", SqueezeOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "Squeeze", SqueezeOp, RuntimeType::RT_CUDA, uint8_t);
+  MACE_REGISTER_OP(registry, "Reshape", ReshapeOp, RuntimeType::RT_CUDA, float);
+  MACE_REGISTER_OP(registry, "Reshape", ReshapeOp, RuntimeType::RT_CUDA, uint8_t);
 }
 
 }  // namespace ops
@@ -803,7 +971,7 @@ MaceStatus SerialNet::AddOperator(const OperatorDef &def) {
   return MaceStatus::MACE_SUCCESS;
 }
 
-int SerialNet::FuseActivations() {
+int SerialNet::FuseActivations(const std::set<std::string> *keep) {
   DropCapture();
   std::map<std::string, int> readers;
   for (const auto &d : defs_)
@@ -812,7 +980,7 @@ int SerialNet::FuseActivations() {
   for (size_t a = 0; a < defs_.size(); ++a) {
     if (skipped_[a] || defs_[a]->type != "Activation" || defs_[a]->input.empty()) continue;
     const std::string &mid = defs_[a]->input[0];
-    if (readers[mid] != 1) continue;
+    if (readers[mid] != 1 || (keep != nullptr && keep->count(mid) != 0)) continue;
     for (size_t pr = 0; pr < a; ++pr) {
       if (skipped_[pr] || defs_[pr]->output.size() != 1 || defs_[pr]->output[0] != mid) continue;
       if (operators_[pr]->AbsorbActivation(*defs_[a], operators_[a]->Output(0))) {
@@ -825,7 +993,7 @@ int SerialNet::FuseActivations() {
   return merged;
 }
 
-int SerialNet::FuseResidualSums() {
+int SerialNet::FuseResidualSums(const std::set<std::string> *keep) {
   DropCapture();
   std::map<std::string, int> readers;
   std::map<std::string, size_t> producer;
@@ -845,6 +1013,7 @@ int SerialNet::FuseResidualSums() {
       const Tensor *conv_out = operators_[e]->Input(side), *residual = operators_[e]->Input(1 - side);
       auto pc = producer.find(conv_out->name());
       if (pc == producer.end() || pc->second >= e || readers[conv_out->name()] != 1) continue;
+      if (keep != nullptr && keep->count(conv_out->name()) != 0) continue;
       if (defs_[pc->second]->type != "Conv2D") continue;
       // the residual must exist when the convolution runs: a net input, a weight, or produced earlier
       auto pr = producer.find(residual->name());
@@ -865,7 +1034,7 @@ SerialNet::~SerialNet() {
   for (void *b : shared_buffers_) runtime_->Delete(b);
 }
 
-MaceStatus SerialNet::PlanMemory(size_t *separate_bytes, size_t *shared_bytes) {
+MaceStatus SerialNet::PlanMemory(size_t *separate_bytes, size_t *shared_bytes, const std::set<std::string> *keep) {
   DropCapture();
   struct Ref {
     Tensor *tensor;
@@ -898,6 +1067,7 @@ MaceStatus SerialNet::PlanMemory(size_t *separate_bytes, size_t *shared_bytes) {
       Tensor *t = operators_[i]->Output(static_cast<unsigned>(k));
       auto it = refs.find(t->name());
       if (it == refs.end()) continue;  // nobody reads it: an output of the net, keeps its memory
+      if (keep != nullptr && keep->count(t->name()) != 0) continue;  // a named output that is also read
       Ref &r = it->second;
       if (r.produced) continue;        // written by two operators: first placement stands
       r.produced = true;

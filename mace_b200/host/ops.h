@@ -18,6 +18,7 @@
 
 #include <map>
 #include <memory>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -159,12 +160,13 @@ class SerialNet {
   // and nothing else reads the intermediate tensor, which is then no longer written.
   // Returns the number of merged pairs.  Off unless called: operator by operator the net
   // behaves like the CPU runtime's.
-  int FuseActivations();
+  // Tensors named in keep (a model's declared outputs) are always written.
+  int FuseActivations(const std::set<std::string> *keep = nullptr);
   // After FuseActivations: merges each (Eltwise SUM [+ absorbed Activation]) into the float
   // Conv2D that produces one of its two inputs, when nothing else reads that input and the
   // other input (the residual) is produced earlier in the net; the convolution then writes
   // activation(conv + residual) straight into the sum's output.  Returns the number of merges.
-  int FuseResidualSums();
+  int FuseResidualSums(const std::set<std::string> *keep = nullptr);
   // Shares activation memory between tensors whose lifetimes do not overlap, the way
   // AllocateTensorMemory<SERIAL_OPT> does (mace/core/net/allocate_opt_strategy.cc:181-285): the
   // net is walked once; every operator's outputs take the best-fitting free buffer (the
@@ -174,8 +176,9 @@ class SerialNet {
   // produces (the net's inputs) and tensors no operator reads (its outputs) keep their own
   // memory.  Call after one plain Run(): the sizes are the ones that run produced.  Intermediate
   // tensors can no longer be read back afterwards.  separate_bytes / shared_bytes (may be null)
-  // receive the activation memory before and after.
-  MaceStatus PlanMemory(size_t *separate_bytes, size_t *shared_bytes);
+  // receive the activation memory before and after.  Tensors named in keep (a model's declared
+  // outputs, which some operator may read as well) stay out of the plan.
+  MaceStatus PlanMemory(size_t *separate_bytes, size_t *shared_bytes, const std::set<std::string> *keep = nullptr);
   bool captured() const { return graph_ != nullptr; }
   ~SerialNet();
   size_t size() const { return operators_.size(); }

@@ -49,6 +49,9 @@ _PROTOS = {
     "mbh_run_host_pipelined": [_vp, _cp, _vp, _sz, _cp, _vp, _sz, C.POINTER(_int)],
     "mbh_wait_slot": [_vp, _int],
     "mbh_run_profiled": [_vp, C.POINTER(_f32), _int, C.c_char_p, _sz, C.POINTER(_int)],
+    "mbh_netdef_describe": [_vp, _sz, C.c_char_p, _sz, C.POINTER(_sz)],
+    "mbh_model_destroy": [_vp],
+    "mbh_model_captured": [_vp],
 }
 _lib = None
 
@@ -67,7 +70,98 @@ def lib():
         _lib.mbh_last_error.restype = _cp
         _lib.mbh_last_error.argtypes = [_vp]
         _lib.mbh_engine_context.restype = _vp
+        _lib.mbh_model_create.restype = _int
+        _lib.mbh_model_create.argtypes = [_int, _vp, _sz, _vp, _sz, _int, _int, _int, C.POINTER(_vp), C.c_char_p, _sz]
+        _lib.mbh_model_run.restype = _int
+        _lib.mbh_model_run.argtypes = [_vp, _int, C.POINTER(IoTensor), _int, C.POINTER(IoTensor)]
+        _lib.mbh_model_last_error.restype = _cp
+        _lib.mbh_model_last_error.argtypes = [_vp]
+        _lib.mbh_model_context.restype = _vp
+        _lib.mbh_model_context.argtypes = [_vp]
     return _lib
+
+
+DF_NONE, DF_NHWC, DF_NCHW = 0, 1, 2
+
+
+class IoTensor(C.Structure):
+    """mbh_io_tensor: one input or output of a model in host memory."""
+    _fields_ = [("name", _cp), ("data", _vp), ("shape", C.c_int64 * 8), ("rank", _int), ("data_format", _int),
+                ("data_type", _int)]
+
+
+def describe_netdef(graph):
+    """Parses a serialized NetDef (bytes) and returns its JSON rendering; needs no GPU."""
+    need = _sz()
+    L = lib()
+    L.mbh_netdef_describe(graph, len(graph), None, 0, C.byref(need))
+    buf = C.create_string_buffer(need.value)
+    st = L.mbh_netdef_describe(graph, len(graph), buf, need.value, None)
+    if st != 0:
+        raise capi.MaceB200Error(st, buf.value.decode())
+    return buf.value.decode()
+
+
+class Model:
+    """A converted model (serialized NetDef + weights blob) on one GPU: the C++ MaceEngine of
+    mace_b200/host/mace_engine.h, i.e. CreateMaceEngineFromProto + MaceEngine::Run."""
+
+    def __init__(self, graph, weights, device=0, fuse=False, plan_memory=False, cuda_graph=False):
+        self.h = _vp()
+        err = C.create_string_buffer(1024)
+        st = lib().mbh_model_create(int(device), graph, len(graph), weights, len(weights), int(fuse),
+                                    int(plan_memory), int(cuda_graph), C.byref(self.h), err, len(err))
+        if st != 0:
+            self.h = None
+            raise capi.MaceB200Error(st, err.value.decode())
+
+    def close(self):
+        if self.h:
+            lib().mbh_model_destroy(self.h)
+            self.h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    @property
+    def context(self):
+        return lib().mbh_model_context(self.h)
+
+    @property
+    def captured(self):
+        return bool(lib().mbh_model_captured(self.h))
+
+    def run(self, inputs, outputs):
+        """inputs: {name: (array, data_format)}; outputs: {name: (array sized for the largest result,
+        data_format)}.  Returns {name: view of the output array with the actual shape}."""
+        ins = (IoTensor * max(1, len(inputs)))()
+        keep = []
+        for k, (name, (a, fmt)) in enumerate(inputs.items()):
+            a = np.ascontiguousarray(a)
+            keep.append(a)
+            ins[k].name, ins[k].data, ins[k].rank = name.encode(), a.ctypes.data, a.ndim
+            ins[k].data_format, ins[k].data_type = fmt, _DT[a.dtype]
+            for d in range(a.ndim):
+                ins[k].shape[d] = a.shape[d]
+        outs = (IoTensor * max(1, len(outputs)))()
+        for k, (name, (a, fmt)) in enumerate(outputs.items()):
+            assert a.flags["C_CONTIGUOUS"]
+            outs[k].name, outs[k].data, outs[k].rank = name.encode(), a.ctypes.data, a.ndim
+            outs[k].data_format, outs[k].data_type = fmt, _DT[a.dtype]
+            for d in range(a.ndim):
+                outs[k].shape[d] = a.shape[d]
+        st = lib().mbh_model_run(self.h, len(inputs), ins, len(outputs), outs)
+        if st != 0:
+            raise capi.MaceB200Error(st, lib().mbh_model_last_error(self.h).decode())
+        result = {}
+        for k, (name, (a, fmt)) in enumerate(outputs.items()):
+            shape = tuple(outs[k].shape[d] for d in range(outs[k].rank))
+            n = int(np.prod(shape)) if shape else 1
+            result[name] = a.reshape(-1)[:n].reshape(shape)
+        return result
 
 
 class HostEngine:
