@@ -91,7 +91,7 @@ def _mobilenet_model(orc, image):
     layers = mn.build(orc, seed=0, calib_images=1, image=image)
     w = W.NetDefWriter(quantized=True, name="mobilenet_v1_u8")
     mn.build_engine(W.WriterModule(hostapi, w), layers, 1, image=image)
-    w.add_output("fc", (1, 1000), data_type=W.DT_UINT8, data_format=W.DF_NONE)
+    w.add_output("fc", (1, 1, 1, 1000), data_type=W.DT_UINT8)
     return layers, w.netdef(), w.weights()
 
 
@@ -101,22 +101,22 @@ def test_quantized_mobilenet_model_file_is_bit_exact(orc):
     layers, graph, weights = _mobilenet_model(orc, image)
     x = mn.random_images(batch, seed=21, image=image)
     want = mn.oracle_forward(orc, layers, x)
-    out = np.zeros((batch, 1000), np.uint8)
+    out = np.zeros((batch, 1, 1, 1000), np.uint8)   # the quantized FullyConnected writes [N, 1, 1, O]
     for cfg in ({}, {"plan_memory": True, "cuda_graph": True}):
         with H.Model(graph, weights, **cfg) as m:
             # the model was written for batch 1: the engine follows the input's actual shape
-            got = m.run({"input": (x, H.DF_NHWC)}, {"fc": (out, H.DF_NONE)})["fc"]
-            assert got.shape == want.shape and np.array_equal(got, want)
+            got = m.run({"input": (x, H.DF_NHWC)}, {"fc": (out, H.DF_NHWC)})["fc"]
+            assert got.shape == (batch, 1, 1, 1000) and np.array_equal(got.reshape(want.shape), want)
             # a quantized model runs NHWC: an NCHW input is transposed on the way in
-            got = m.run({"input": (x.transpose(0, 3, 1, 2), H.DF_NCHW)}, {"fc": (out, H.DF_NONE)})["fc"]
-            assert np.array_equal(got, want)
+            got = m.run({"input": (x.transpose(0, 3, 1, 2), H.DF_NCHW)}, {"fc": (out, H.DF_NHWC)})["fc"]
+            assert np.array_equal(got.reshape(want.shape), want)
             for _ in range(2):
-                got = m.run({"input": (x, H.DF_NHWC)}, {"fc": (out, H.DF_NONE)})["fc"]
-                assert np.array_equal(got, want)
+                got = m.run({"input": (x, H.DF_NHWC)}, {"fc": (out, H.DF_NHWC)})["fc"]
+                assert np.array_equal(got.reshape(want.shape), want)
             assert m.captured == bool(cfg.get("cuda_graph"))
             # another batch size drops the recording and still gives the oracle's bytes
-            got = m.run({"input": (x[:2], H.DF_NHWC)}, {"fc": (out, H.DF_NONE)})["fc"]
-            assert got.shape == (2, 1000) and np.array_equal(got, want[:2])
+            got = m.run({"input": (x[:2], H.DF_NHWC)}, {"fc": (out, H.DF_NHWC)})["fc"]
+            assert got.shape == (2, 1, 1, 1000) and np.array_equal(got.reshape(2, 1000), want[:2])
 
 
 def _resnet_model(image, width_div, tail=True):
