@@ -9,6 +9,8 @@
 //   float   Conv2dOp (mace/ops/conv_2d.cc:82-176), DepthwiseConv2dOp, MatMulOp, FullyConnectedOp,
 //           PoolingOp (mace/ops/pooling.cc:46-240), EltwiseOp (mace/ops/eltwise.cc:949-1144),
 //           ActivationOp (mace/ops/activation.cc:36-79), SoftmaxOp (mace/ops/softmax.cc:249-290)
+//   both    TransposeOp (mace/ops/transpose.cc:34-73), SqueezeOp (mace/ops/squeeze.cc:25-84),
+//           ReshapeOp (mace/ops/reshape.cc:27-133)
 // plus the sequential executor (SerialNet::Run, mace/core/net/serial_net.cc:93-228) with
 // activation merging and MACE's shared activation memory
 // (mace/core/net/allocate_opt_strategy.cc:181-285), and a small OperatorDef stand-in
