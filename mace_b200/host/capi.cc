@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <exception>
 #include <map>
 #include <memory>
 #include <string>
@@ -378,6 +379,12 @@ int mbh_netdef_describe(const void *graph, size_t graph_len, char *json_out, siz
   return static_cast<int>(st.code());
 }
 
+int mbh_half_to_float(const uint16_t *in, float *out, size_t count) {
+  if ((in == nullptr || out == nullptr) && count != 0) return MaceStatus::MACE_INVALID_ARGS;
+  for (size_t i = 0; i < count; ++i) out[i] = HalfToFloat(in[i]);
+  return MaceStatus::MACE_SUCCESS;
+}
+
 int mbh_model_create(int device, const void *graph, size_t graph_len, const void *weights, size_t weights_len,
                      int fuse, int plan_memory, int cuda_graph, mbh_model **model, char *error, size_t error_len) {
   if (model == nullptr) return MaceStatus::MACE_INVALID_ARGS;
@@ -388,9 +395,13 @@ int mbh_model_create(int device, const void *graph, size_t graph_len, const void
   config.plan_memory = plan_memory != 0;
   config.cuda_graph = cuda_graph != 0;
   auto m = std::make_unique<mbh_model>();
-  MaceStatus st = CreateMaceEngineFromProto(static_cast<const unsigned char *>(graph), graph_len,
-                                            static_cast<const unsigned char *>(weights), weights_len, {}, {}, config,
-                                            &m->engine);
+  MaceStatus st;
+  try {  // no exception may cross the C boundary
+    st = CreateMaceEngineFromProto(static_cast<const unsigned char *>(graph), graph_len,
+                                   static_cast<const unsigned char *>(weights), weights_len, {}, {}, config, &m->engine);
+  } catch (const std::exception &ex) {
+    st = MaceStatus(MaceStatus::MACE_OUT_OF_RESOURCES, std::string("exception while loading the model: ") + ex.what());
+  }
   if (st != MaceStatus::MACE_SUCCESS) {
     if (error != nullptr && error_len > 0) {
       std::strncpy(error, st.information().c_str(), error_len - 1);
@@ -432,7 +443,12 @@ int mbh_model_run(mbh_model *model, int n_inputs, const mbh_io_tensor *inputs, i
     out[t.name] = MaceTensor(std::vector<int64_t>(t.shape, t.shape + t.rank), std::shared_ptr<void>(t.data, no_delete),
                              static_cast<DataFormat>(t.data_format), static_cast<IDataType>(t.data_type));
   }
-  MaceStatus st = model->engine->Run(in, &out);
+  MaceStatus st;
+  try {
+    st = model->engine->Run(in, &out);
+  } catch (const std::exception &ex) {
+    st = MaceStatus(MaceStatus::MACE_OUT_OF_RESOURCES, std::string("exception while running the model: ") + ex.what());
+  }
   if (st != MaceStatus::MACE_SUCCESS) {
     model->last_error = st.information();
     return static_cast<int>(st.code());

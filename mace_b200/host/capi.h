@@ -106,6 +106,10 @@ int mbh_run_profiled(mbh_engine *engine, float *ms_out, int max_ops, char *names
  * the reason in json_out. */
 int mbh_netdef_describe(const void *graph, size_t graph_len, char *json_out, size_t capacity, size_t *needed);
 
+/* The widening applied to DT_HALF weights when a model is loaded (IEEE binary16 -> binary32,
+ * subnormals, infinities and NaN payloads included).  Needs no GPU. */
+int mbh_half_to_float(const uint16_t *in, float *out, size_t count);
+
 typedef struct mbh_model mbh_model;
 
 /* One input or output in host memory, the fields of a MaceTensor: data_format 0 none, 1 NHWC,

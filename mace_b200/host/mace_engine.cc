@@ -62,10 +62,13 @@ MaceStatus MaceEngine::LoadModelTensors(const unsigned char *model_data, int64_t
     index_t count = 1;
     for (index_t d : dims) {
       if (d < 0) return Invalid("tensor " + ct.name + ": negative dimension");
+      // (sizes come from a file: no product may leave the range of the blob's size)
+      if (d != 0 && count > model_data_size / d) return Invalid("tensor " + ct.name + ": larger than the weights data");
       count *= d;
     }
     if (ct.offset < 0 || ct.data_size < 0) return Invalid("tensor " + ct.name + ": negative offset or size");
     if (count != ct.data_size) return Invalid("tensor " + ct.name + ": data_size not equal with the shape");
+    if (ct.offset > model_data_size) return Invalid("tensor " + ct.name + ": offset beyond the weights data");
     const int64_t tensor_end = ct.offset + count * static_cast<int64_t>(elem);
     if (tensor_end > model_data_size)
       return Invalid("tensor " + ct.name + ": tensor_end (" + std::to_string(tensor_end) + ") should <= " +
@@ -176,6 +179,8 @@ MaceStatus MaceEngine::Run(const std::map<std::string, MaceTensor> &inputs, std:
     if (static_cast<int>(mt.data_type_) != static_cast<int>(t->dtype()))
       return Invalid("input " + in.first + ": data type does not match the model's");
     std::vector<index_t> shape(mt.shape_.begin(), mt.shape_.end());
+    for (index_t d : shape)
+      if (d < 0) return Invalid("input " + in.first + ": negative dimension");
     bool to_nchw = false, to_nhwc = false;
     if (info.data_format != static_cast<int>(DataFormat::NONE) && shape.size() == 4) {
       to_nchw = !quantized_ && mt.format_ == DataFormat::NHWC;

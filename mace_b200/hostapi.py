@@ -50,6 +50,7 @@ _PROTOS = {
     "mbh_wait_slot": [_vp, _int],
     "mbh_run_profiled": [_vp, C.POINTER(_f32), _int, C.c_char_p, _sz, C.POINTER(_int)],
     "mbh_netdef_describe": [_vp, _sz, C.c_char_p, _sz, C.POINTER(_sz)],
+    "mbh_half_to_float": [_vp, _vp, _sz],
     "mbh_model_destroy": [_vp],
     "mbh_model_captured": [_vp],
 }
@@ -100,6 +101,16 @@ def describe_netdef(graph):
     if st != 0:
         raise capi.MaceB200Error(st, buf.value.decode())
     return buf.value.decode()
+
+
+def half_to_float(h):
+    """uint16 bit patterns of IEEE halves -> float32, by the loader's own routine; needs no GPU."""
+    h = np.ascontiguousarray(h, np.uint16)
+    out = np.empty(h.shape, np.float32)
+    st = lib().mbh_half_to_float(h.ctypes.data, out.ctypes.data, h.size)
+    if st != 0:
+        raise capi.MaceB200Error(st, "mbh_half_to_float")
+    return out
 
 
 class Model:

@@ -133,3 +133,10 @@ def test_encoder_used_by_the_gpu_tests_round_trips_through_the_reader():
     info = got["input_info"][0]
     assert info["name"] == "input" and info["dims"] == [2, 8, 8, 3] and info["data_type"] == 2
     assert got["output_info"][0]["name"] == "conv" and got["output_info"][0]["data_type"] == 2
+
+
+def test_half_weights_widen_exactly_for_every_bit_pattern():
+    bits = np.arange(65536, dtype=np.uint16)
+    got = hostapi.half_to_float(bits).view(np.uint32)
+    want = bits.view(np.float16).astype(np.float32).view(np.uint32)
+    assert np.array_equal(got, want)  # normals, subnormals, zeros, infinities, NaN payloads
