@@ -536,6 +536,33 @@ def run_mobilenet(args, rank, world):
                              "ms_per_step": round(gms, 5),
                              "frac_of_2x_bf16_peak": round(gtops / (2 * peaks["bf16_tflops"]), 4)}
         gctx.close()
+        # the same network as a converted-model file through the model-level API (NetDef bytes +
+        # weights blob -> CreateMaceEngineFromProto; one synchronous MaceEngine::Run per step on
+        # pinned host buffers: upload, graph replay, download, wait)
+        if world == 1:
+            import netdef_wire
+            writer = netdef_wire.NetDefWriter(quantized=True, name="mobilenet_v1_u8")
+            mn.build_engine(netdef_wire.WriterModule(hostapi, writer), layers, BATCH)
+            writer.add_output("fc", (BATCH, 1, 1, mn.NUM_CLASSES), data_type=netdef_wire.DT_UINT8)
+            model = hostapi.Model(writer.netdef(), writer.weights(), device=local, plan_memory=True, cuda_graph=True)
+            mctx = RawContext(model.context)
+            mout = mctx.pinned(BATCH * mn.NUM_CLASSES).reshape(BATCH, 1, 1, mn.NUM_CLASSES)
+            shaped = hin.reshape((n_inputs,) + inputs[0].shape)
+
+            def model_step(i):
+                return model.run({"input": (shaped[i % n_inputs], hostapi.DF_NHWC)}, {"fc": (mout, hostapi.DF_NHWC)})
+
+            for i in range(4):
+                model_step(i)
+            msteps = max(4, min(args.steps, 50))
+            t0 = time.perf_counter()
+            for i in range(msteps):
+                model_step(4 + i)
+            mms = (time.perf_counter() - t0) * 1e3 / msteps
+            result["e2e_model_api"] = {"value": round(BATCH / (mms * 1e-3), 1), "unit": "images/s",
+                                       "ms_per_step": round(mms, 4), "graph": model.captured,
+                                       "call": "MaceEngine::Run on a model file, synchronous, pinned host buffers"}
+            model.close()
         # CPU baseline: the oracle chain on this box's host cores, one full batch
         threads = orc.set_threads(0)
         x = inputs[0]
