@@ -119,6 +119,29 @@ def test_quantized_mobilenet_model_file_is_bit_exact(orc):
             assert got.shape == (2, 1, 1, 1000) and np.array_equal(got.reshape(2, 1000), want[:2])
 
 
+def test_full_size_mobilenet_model_file_equals_the_operator_chain(orc):
+    """224 x 224 at batch 8: the model-file path must give the bytes of the operator-by-operator
+    engine (which test_gpu_mobilenet.py holds against the oracle at this size)."""
+    from mace_b200 import hostapi as H
+    batch = 8
+    layers, graph, weights = _mobilenet_model(orc, 224)
+    x = mn.random_images(batch, seed=5)
+    eng = mn.build_engine(H, layers, batch)
+    try:
+        eng.write("input", x)
+        eng.run()
+        want = eng.read("fc", np.uint8).reshape(batch, 1000)
+    finally:
+        eng.close()
+    out = np.zeros((batch, 1, 1, 1000), np.uint8)
+    with H.Model(graph, weights, plan_memory=True, cuda_graph=True) as m:
+        for _ in range(3):
+            got = m.run({"input": (x, H.DF_NHWC)}, {"fc": (out, H.DF_NHWC)})["fc"]
+            assert np.array_equal(got.reshape(batch, 1000), want)
+        assert m.captured
+    assert len(np.unique(want)) > 50
+
+
 def _resnet_model(image, width_div, tail=True):
     from mace_b200 import hostapi
     nodes, weights = rn.build(seed=0, image=image, width_div=width_div)
@@ -243,6 +266,31 @@ def test_float_in_float_out_quantized_model(orc):
         got = m.run({"input": (x, H.DF_NHWC)}, {"y": (out, H.DF_NCHW)})["y"]
     assert got.shape == (2, 16, 10, 12)
     assert np.array_equal(got, want.transpose(0, 3, 1, 2))
+
+
+def test_two_inputs_in_different_layouts():
+    """Each input is transposed (or not) by its own MaceTensor's layout; 2-D tensors never are."""
+    from mace_b200 import hostapi as H
+    rng = np.random.Generator(np.random.PCG64(17))
+    a = rng.standard_normal((2, 5, 6, 3)).astype(np.float32)      # NHWC
+    b = rng.standard_normal((2, 5, 6, 3)).astype(np.float32)
+    v = rng.standard_normal((4, 9)).astype(np.float32)
+    w = W.NetDefWriter(name="two_inputs")
+    w.add_tensor("a", shape=a.shape, dtype=W.DT_FLOAT)
+    w.add_tensor("b", shape=b.shape, dtype=W.DT_FLOAT)
+    w.add_tensor("v", shape=v.shape, dtype=W.DT_FLOAT, data_format=W.DF_NONE)
+    w.op("Eltwise", "sum", ["a", "b"], ["s"], T=W.DT_FLOAT, i={"type": 0})
+    w.op("Eltwise", "prod", ["s", "a"], ["p"], T=W.DT_FLOAT, i={"type": 2})
+    w.op("Activation", "relu", ["v"], ["r"], T=W.DT_FLOAT, s={"activation": "RELU"})
+    w.add_output("p", a.shape)
+    w.add_output("r", v.shape, data_format=W.DF_NONE)
+    out = np.zeros(a.shape, np.float32)
+    r = np.zeros(v.shape, np.float32)
+    with H.Model(w.netdef(), b"") as m:
+        got = m.run({"a": (a, H.DF_NHWC), "b": (b.transpose(0, 3, 1, 2), H.DF_NCHW), "v": (v, H.DF_NONE)},
+                    {"p": (out, H.DF_NHWC), "r": (r, H.DF_NHWC)})
+        assert np.array_equal(got["p"], (a + b) * a)
+        assert np.array_equal(got["r"], np.maximum(v, 0))
 
 
 def test_model_errors():
