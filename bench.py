@@ -706,7 +706,7 @@ def resnet_kind(node):
         if node["k"] == 3:
             return "3x3 s1 (Winograd: wino_input + gemm_f32_tc_kernel + wino_output)"
         if node["stride"] == 2:
-            return "1x1 s2 (im2col + gemm_f32_tc_kernel)"
+            return "1x1 s2 (pixel gather + gemm_f32_tc_kernel)"
         return "1x1 s1 (gemm_f32_tc_kernel)"
     return {"maxpool": "max pool", "avgpool": "avg pool", "add": "eltwise sum", "relu": "activation",
             "fc": "fully connected"}[node["op"]]
@@ -722,6 +722,8 @@ def run_resnet(args, rank, world):
     batch = args.batch or 256
     nodes, weights = rn.build(seed=0)
     eng = rn.build_engine(hostapi, nodes, weights, batch, device=local)
+    # one gather for the two stride-2 1x1 convolutions that open a stage (shortcut and branch2a)
+    shared = 0 if args.no_fuse else eng.share_subsampled_inputs()
     merged = 0 if args.no_fuse else eng.fuse_activations()  # residual sum + ReLU in one pass
     ctx = RawContext(eng.context)
     x = rn.random_images(batch, seed=100 + rank)
@@ -770,6 +772,8 @@ def run_resnet(args, rank, world):
     for _ in range(prof_runs):
         for label, t in eng.run_profiled(max_ops=512):
             k = kinds.get(label.split(":", 1)[-1], label)
+            if label.startswith("Subsample:"):
+                k = "1x1 s2 (pixel gather + gemm_f32_tc_kernel)"
             fam[k] = fam.get(k, 0.0) + t / prof_runs
 
     # pipelined end-to-end calls (see run_mobilenet): the next batch's upload overlaps this
@@ -824,6 +828,7 @@ def run_resnet(args, rank, world):
                        "parallelism": "dp%d: batch sharded, weights replicated, final logits gather only" % world,
                        "launch": "operator by operator" if args.no_graph else "CUDA graph replay",
                        "merged_sum_relu_pairs": merged, "sums_merged_into_convolutions": merged_conv,
+                       "shared_stride2_gathers": shared,
                        "activation_memory_gb": None if mem is None else
                        {"one_buffer_per_tensor": round(mem[0] / 1e9, 2), "planned": round(mem[1] / 1e9, 2)},
                        "l2": "activations of one step (%.1f GB) exceed L2" % (alg_bytes / 1e9)},

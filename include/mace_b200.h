@@ -342,6 +342,17 @@ int mb_dequantize_f32(mb_context *ctx, const void *in, int in_is_int32,
 int mb_minmax_f32(mb_context *ctx, const float *in, int64_t size,
                   float *host_min, float *host_max);
 
+/* ---- The pixels a strided 1x1 convolution reads, gathered once.  No operator
+ * of its own in the reference: arm::Conv2dGeneral / ref::Conv2d index the input
+ * with the stride (mace/ops/ref/conv_2d.cc:36-122).  A 1x1 convolution with
+ * strides (sh, sw) and no padding equals a 1x1 stride-1 convolution of
+ *   out[p][ho][wo] = in[p][ho * sh][wo * sw],  ho < ceil(H / sh), wo < ceil(W / sw)
+ * over the N * C planes; two such convolutions of one tensor (a residual block's
+ * shortcut and its first convolution) then share one gather. */
+int mb_subsample_f32_nchw(mb_context *ctx, const float *in, float *out,
+                          int64_t planes, int64_t H, int64_t W,
+                          int stride_h, int stride_w);
+
 /* ---- Layout conversion at the edge of a network: replaces ops::Transpose as
  * BaseFlow::TransposeInput / TransposeOutput call it for NHWC <-> NCHW
  * (mace/core/flow/base_flow.cc:131-204, mace/flows/cpu/cpu_ref_flow.cc:81-101)

@@ -92,6 +92,7 @@ PROTOTYPES = {
     "mb_dequantize_f32": (_int, [_vp, _vp, _int, _vp, _i64, _f32, _i32]),
     "mb_minmax_f32": (_int, [_vp, _vp, _i64, C.POINTER(_f32), C.POINTER(_f32)]),
     "mb_transpose2d_batched": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int]),
+    "mb_subsample_f32_nchw": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int]),
     "mb_gemm_u8_static_scratch": (_int, [_vp] * 5 + [_int] + [_i64] * 3 + [_int] * 2 +
                                   [_i32] * 5 + [_int, C.c_char_p, _sz]),
 }
@@ -355,6 +356,10 @@ class Context:
         mn, mx = _f32(), _f32()
         self._check(lib().mb_minmax_f32(self.h, x.ptr, size, C.byref(mn), C.byref(mx)))
         return mn.value, mx.value
+
+    def subsample_f32(self, x, out, planes, H, W, strides):
+        """out[p][ho][wo] = x[p][ho * sh][wo * sw]."""
+        self._check(lib().mb_subsample_f32_nchw(self.h, x.ptr, out.ptr, planes, H, W, strides[0], strides[1]))
 
     def transpose2d_batched(self, x, out, batch, rows, cols, elem_bytes):
         """out[b][c][r] = x[b][r][c]; NHWC -> NCHW is rows = H * W, cols = C."""

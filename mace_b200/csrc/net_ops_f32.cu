@@ -217,6 +217,23 @@ static void launch_eltwise(mb_context *ctx, const EltParams &p, int vec4) {
   eltwise_f32_kernel<TYPE><<<stream_grid(ctx, vec4 ? p.size / 4 + 1 : p.size), 256, 0, ctx->stream>>>(p, vec4);
 }
 
+// out[p][ho][wo] = in[p][ho * sh][wo * sw] over N * C planes: the pixels a 1x1 convolution with
+// strides (sh, sw) reads, gathered once so that several such convolutions of one tensor (a
+// residual block's shortcut and its first convolution) can run as plain 1x1 convolutions on
+// the compact copy.  One thread per output value, grid-stride; writes are contiguous.
+__global__ void __launch_bounds__(256)
+subsample_f32_kernel(const float *__restrict__ in, float *__restrict__ out, int64_t total, int H, int W, int sh,
+                     int sw, int Ho, int Wo) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t plane_out = static_cast<int64_t>(Ho) * Wo, plane_in = static_cast<int64_t>(H) * W;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t pl = i / plane_out;
+    const int rem = static_cast<int>(i - pl * plane_out);
+    const int ho = rem / Wo, wo = rem - ho * Wo;
+    out[i] = __ldg(in + pl * plane_in + static_cast<int64_t>(ho) * sh * W + wo * sw);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -333,6 +350,25 @@ int mb_softmax_f32(mb_context *ctx, const float *in, float *out, int64_t outer, 
   MB_CUDA(ctx, cudaSetDevice(ctx->device));
   softmax_f32_kernel<<<static_cast<unsigned>(ceil_div64(positions, 8)), 256, 0, ctx->stream>>>(
       in, out, positions, classes, inner, use_log);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+int mb_subsample_f32_nchw(mb_context *ctx, const float *in, float *out, int64_t planes, int64_t H, int64_t W,
+                          int stride_h, int stride_w) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (planes < 0 || H < 0 || W < 0 || stride_h < 1 || stride_w < 1 || H > INT32_MAX || W > INT32_MAX)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_subsample_f32_nchw: bad extents or strides");
+  const int64_t Ho = ceil_div64(H, stride_h), Wo = ceil_div64(W, stride_w);
+  const int64_t total = planes * Ho * Wo;
+  if (total == 0) return MB_SUCCESS;
+  if (in == nullptr || out == nullptr || in == out)
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_subsample_f32_nchw: null or aliased buffers");
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  subsample_f32_kernel<<<stream_grid(ctx, total), 256, 0, ctx->stream>>>(in, out, total, static_cast<int>(H),
+                                                                         static_cast<int>(W), stride_h, stride_w,
+                                                                         static_cast<int>(Ho), static_cast<int>(Wo));
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   return MB_SUCCESS;

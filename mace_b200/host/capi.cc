@@ -262,6 +262,13 @@ int mbh_fuse_residual_sums(mbh_engine *e, int *merged) {
   return MaceStatus::MACE_SUCCESS;
 }
 
+int mbh_share_subsampled_inputs(mbh_engine *e, int *groups) {
+  if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  const int n = e->net->ShareSubsampledInputs();
+  if (groups != nullptr) *groups = n;
+  return MaceStatus::MACE_SUCCESS;
+}
+
 int mbh_plan_memory(mbh_engine *e, size_t *separate_bytes, size_t *shared_bytes) {
   if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
   MBH_TRY(e, e->net->PlanMemory(separate_bytes, shared_bytes));

@@ -64,6 +64,12 @@ int mbh_fuse_activations(mbh_engine *engine, int *merged);
  * convolution then writes activation(conv + residual) into the sum's output. */
 int mbh_fuse_residual_sums(mbh_engine *engine, int *merged);
 
+/* Where several strided 1x1 float convolutions read one tensor with the same strides, gathers
+ * the pixels they read once (a Subsample operator in front of the first) and runs them as
+ * stride-1 convolutions of that copy.  Call before the first run or before the merging passes
+ * above.  *groups (may be NULL) receives the number of shared gathers. */
+int mbh_share_subsampled_inputs(mbh_engine *engine, int *groups);
+
 /* Shares activation memory between tensors whose lifetimes do not overlap (MACE's SERIAL_OPT
  * allocation strategy).  Call after one run; intermediate tensors cannot be read back afterwards.
  * The two sizes (may be NULL) are the activation bytes before and after. */

@@ -157,6 +157,7 @@ MaceStatus MaceEngine::Init(const proto::NetDef *net_def, const std::vector<std:
   }
   for (const auto &kv : output_info_)
     if (!workspace_.HasTensor(kv.first)) return Invalid("no operator produces the model output " + kv.first);
+  if (config_.fuse) net_->ShareSubsampledInputs();
   initialised_ = true;
   return MaceStatus::MACE_SUCCESS;
 }

@@ -133,6 +133,7 @@ template <RuntimeType D, class T> class DequantizeOp;
 template <RuntimeType D, class T> class TransposeOp;
 template <RuntimeType D, class T> class SqueezeOp;
 template <RuntimeType D, class T> class ReshapeOp;
+template <RuntimeType D, class T> class SubsampleOp;
 
 template <>
 class Conv2dOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
@@ -215,6 +216,27 @@ class Conv2dOp<RuntimeType::RT_CUDA, float> : public ConvPool2dOpBase {
       conv2d_delegator_->SetActivation(act, max_limit_, coefficient_);
     }
     return conv2d_delegator_->Compute(context, input, filter, Output(0));
+  }
+
+  bool DescribeStridedPointwise(int *stride_h, int *stride_w) const override {
+    const Tensor *filter = Input(1);
+    if (residual_ != nullptr || strides_.size() != 2 || filter->dim_size() != 4) return false;
+    if (filter->dim(2) != 1 || filter->dim(3) != 1 || (strides_[0] == 1 && strides_[1] == 1)) return false;
+    if (strides_[0] < 1 || strides_[1] < 1 || dilations_.size() != 2 || dilations_[0] != 1 || dilations_[1] != 1)
+      return false;
+    // SAME and VALID both pad a 1x1 filter by nothing; explicit padding values must be zero
+    for (int pad : paddings_)
+      if (pad != 0) return false;
+    if (paddings_.empty() && padding_type_ != SAME && padding_type_ != VALID) return false;
+    *stride_h = strides_[0];
+    *stride_w = strides_[1];
+    return true;
+  }
+
+  void TakeSubsampledInput(const Tensor *subsampled) override {
+    inputs_[0] = subsampled;
+    strides_ = {1, 1};
+    conv2d_delegator_.reset();  // the next Run() picks the 1x1 delegator
   }
 
   // Needs the delegator, i.e. one Run() before the net merges operators.
@@ -913,6 +935,31 @@ class ReshapeOp : public Operation {
   bool has_df_;
 };
 
+// Internal to this runtime (no MACE operator of this name): the pixels a strided 1x1
+// convolution reads, see SerialNet::ShareSubsampledInputs.  Argument "strides".
+template <RuntimeType D, class T>
+class SubsampleOp : public Operation {
+ public:
+  explicit SubsampleOp(OpConstructContext *context)
+      : Operation(context), strides_(GetRepeatedArgs<int>("strides", {1, 1})) {}
+
+  MaceStatus Run(OpContext *context) override {
+    const Tensor *input = Input(0);
+    Tensor *output = Output(0);
+    if (input->dim_size() != 4 || strides_.size() != 2 || strides_[0] < 1 || strides_[1] < 1)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "Subsample needs a 4-D input and two strides");
+    const index_t H = input->dim(2), W = input->dim(3);
+    MACE_RETURN_IF_ERROR(output->Resize({input->dim(0), input->dim(1), (H + strides_[0] - 1) / strides_[0],
+                                         (W + strides_[1] - 1) / strides_[1]}));
+    CudaRuntime *rt = CudaRuntimeOf(context);
+    return rt->Status(mb_subsample_f32_nchw(rt->ctx(), input->memory<float>(), output->mutable_memory<float>(),
+                                            input->dim(0) * input->dim(1), H, W, strides_[0], strides_[1]));
+  }
+
+ private:
+  std::vector<int> strides_;
+};
+
 #define MACE_REGISTER_OP(registry, op_type, class_name, runtime, dt)                             \
   registry->Register(op_type, runtime, DataTypeToEnum<dt>::value,                                \
                      [](OpConstructContext *context) -> std::unique_ptr<Operation> {             \
@@ -942,6 +989,7 @@ void RegisterAllCudaOps(OpRegistry *registry) {
   MACE_REGISTER_OP(registry, "Squeeze", SqueezeOp, RuntimeType::RT_CUDA, uint8_t);
   MACE_REGISTER_OP(registry, "Reshape", ReshapeOp, RuntimeType::RT_CUDA, float);
   MACE_REGISTER_OP(registry, "Reshape", ReshapeOp, RuntimeType::RT_CUDA, uint8_t);
+  MACE_REGISTER_OP(registry, "Subsample", SubsampleOp, RuntimeType::RT_CUDA, float);
 }
 
 }  // namespace ops
@@ -1026,6 +1074,59 @@ int SerialNet::FuseResidualSums(const std::set<std::string> *keep) {
     }
   }
   return merged;
+}
+
+int SerialNet::ShareSubsampledInputs() {
+  DropCapture();
+  // members of each (input tensor, strides) group, in net order
+  std::map<std::string, std::vector<size_t>> groups;
+  std::map<std::string, std::pair<int, int>> group_strides;
+  for (size_t i = 0; i < operators_.size(); ++i) {
+    int sh = 0, sw = 0;
+    if (skipped_[i] || defs_[i]->input.empty() || !operators_[i]->DescribeStridedPointwise(&sh, &sw)) continue;
+    const std::string key = defs_[i]->input[0] + "/subsampled_" + std::to_string(sh) + "x" + std::to_string(sw);
+    groups[key].push_back(i);
+    group_strides[key] = {sh, sw};
+  }
+  std::vector<Operation *> member_ops(operators_.size());
+  std::vector<OperatorDef *> member_defs(operators_.size());
+  for (size_t i = 0; i < operators_.size(); ++i) {
+    member_ops[i] = operators_[i].get();
+    member_defs[i] = defs_[i].get();
+  }
+  // the new operators are inserted from the back of the net, so that earlier positions stay valid
+  std::vector<std::pair<size_t, std::string>> order;
+  for (const auto &kv : groups)
+    if (kv.second.size() >= 2) order.emplace_back(kv.second.front(), kv.first);
+  std::sort(order.begin(), order.end(), [](const auto &a, const auto &b) { return a.first > b.first; });
+  int shared = 0;
+  for (const auto &entry : order) {
+    // (pointers, not indices: an insertion further back has moved the members behind it)
+    std::vector<std::pair<Operation *, OperatorDef *>> members;
+    for (size_t m : groups[entry.second]) members.emplace_back(member_ops[m], member_defs[m]);
+    auto def = std::make_unique<OperatorDef>();
+    def->type = "Subsample";
+    def->name = entry.second;
+    def->input = {members.front().second->input[0]};
+    def->output = {entry.second};
+    def->ints["strides"] = {group_strides[entry.second].first, group_strides[entry.second].second};
+    def->i["T"] = static_cast<int>(DT_FLOAT);
+    OpConstructContext cc(ws_, runtime_, def.get());
+    MaceStatus st;
+    std::unique_ptr<Operation> op = op_registry_->CreateOperation(&cc, RuntimeType::RT_CUDA, DT_FLOAT, &st);
+    if (op == nullptr || op->Init(&cc) != MaceStatus::MACE_SUCCESS) continue;
+    for (const auto &m : members) {
+      m.first->TakeSubsampledInput(op->Output(0));
+      m.second->input[0] = entry.second;
+      m.second->ints["strides"] = {1, 1};
+    }
+    const auto at = static_cast<std::ptrdiff_t>(entry.first);
+    defs_.insert(defs_.begin() + at, std::move(def));
+    operators_.insert(operators_.begin() + at, std::move(op));
+    skipped_.insert(skipped_.begin() + at, 0);
+    ++shared;
+  }
+  return shared;
 }
 
 SerialNet::~SerialNet() {

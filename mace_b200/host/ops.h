@@ -109,6 +109,16 @@ class Operation {
   }
   // out = activation(this operator's result + residual), written to `sum_output`: a convolution
   // that can add a residual in its own kernel returns true and does that from then on.
+  // A float 1x1 convolution with a stride above 1, no dilation and no padding reads every
+  // stride-th pixel only: it names its strides here, and TakeSubsampledInput() turns it into a
+  // stride-1 convolution of `subsampled` (that tensor holds exactly those pixels), so that several
+  // such convolutions of one tensor share one gather (SerialNet::ShareSubsampledInputs).
+  virtual bool DescribeStridedPointwise(int *stride_h, int *stride_w) const {
+    (void)stride_h;
+    (void)stride_w;
+    return false;
+  }
+  virtual void TakeSubsampledInput(const Tensor *subsampled) { (void)subsampled; }
   virtual bool AbsorbResidualSum(const Tensor *residual, const ResidualSum &sum, Tensor *sum_output) {
     (void)residual;
     (void)sum;
@@ -169,6 +179,12 @@ class SerialNet {
   // other input (the residual) is produced earlier in the net; the convolution then writes
   // activation(conv + residual) straight into the sum's output.  Returns the number of merges.
   int FuseResidualSums(const std::set<std::string> *keep = nullptr);
+  // Where two or more strided 1x1 float convolutions read the same tensor with the same strides
+  // (a ResNet block's shortcut and its first convolution), a Subsample operator is put in front of
+  // the first of them and they become stride-1 convolutions of its output: one gather of the
+  // pixels instead of one per convolution.  Call before the first Run() or before the other
+  // merging passes (the convolutions pick their delegators again).  Returns the number of groups.
+  int ShareSubsampledInputs();
   // Shares activation memory between tensors whose lifetimes do not overlap, the way
   // AllocateTensorMemory<SERIAL_OPT> does (mace/core/net/allocate_opt_strategy.cc:181-285): the
   // net is walked once; every operator's outputs take the best-fitting free buffer (the

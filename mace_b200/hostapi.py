@@ -45,6 +45,7 @@ _PROTOS = {
     "mbh_fuse_activations": [_vp, C.POINTER(_int)],
     "mbh_plan_memory": [_vp, C.POINTER(_sz), C.POINTER(_sz)],
     "mbh_fuse_residual_sums": [_vp, C.POINTER(_int)],
+    "mbh_share_subsampled_inputs": [_vp, C.POINTER(_int)],
     "mbh_run_host": [_vp, _cp, _vp, _sz, _cp, _vp, _sz],
     "mbh_run_host_pipelined": [_vp, _cp, _vp, _sz, _cp, _vp, _sz, C.POINTER(_int)],
     "mbh_wait_slot": [_vp, _int],
@@ -287,6 +288,13 @@ class HostEngine:
         that feed them; returns how many."""
         n = _int()
         self._check(lib().mbh_fuse_residual_sums(self.h, C.byref(n)))
+        return n.value
+
+    def share_subsampled_inputs(self):
+        """One gather for the strided 1x1 convolutions that read the same tensor; returns the
+        number of shared gathers.  Call before the first run."""
+        n = _int()
+        self._check(lib().mbh_share_subsampled_inputs(self.h, C.byref(n)))
         return n.value
 
     def plan_memory(self):

@@ -157,6 +157,84 @@ def test_resnet50_graph_against_oracle(orc, cfg):
         eng.close()
 
 
+def test_strided_pointwise_convolutions_share_one_gather(orc):
+    """ShareSubsampledInputs: the two stride-2 1x1 convolutions that open a ResNet stage read the
+    same pixels; with the pass every tensor of the graph still matches the oracle, before and
+    after the merging passes, memory planning and graph capture."""
+    from mace_b200 import hostapi
+    cfg = {"batch": 3, "image": 64, "width_div": 4}
+    nodes, weights = rn.build(seed=0, image=cfg["image"], width_div=cfg["width_div"])
+    x = rn.random_images(cfg["batch"], 2, cfg["image"])
+    ref_logits, ref = rn.oracle_forward(orc, nodes, weights, x, keep=True)
+    eng = rn.build_engine(hostapi, nodes, weights, cfg["batch"], image=cfg["image"])
+    try:
+        assert eng.share_subsampled_inputs() == 3          # res3a, res4a, res5a
+        assert eng.share_subsampled_inputs() == 0          # nothing strided is left
+        eng.write("input", x)
+        eng.run()
+        for n in nodes:
+            got, want = eng.read(n["name"], np.float32), ref[n["name"]]
+            assert got.shape == want.shape, n["name"]
+            assert float(np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)) <= 1e-4, n["name"]
+        # the gathered tensor holds exactly every second pixel of the stage's input
+        sub = eng.read("res2c/subsampled_2x2", np.float32)
+        assert np.array_equal(sub, eng.read("res2c", np.float32)[:, :, ::2, ::2])
+        assert eng.fuse_activations() == 16 and eng.fuse_residual_sums() == 16
+        eng.run()
+        eng.plan_memory()
+        eng.run()
+        eng.capture()
+        eng.run()
+        got = eng.read("fc", np.float32)
+        assert float(np.abs(got - ref_logits).max() / np.abs(ref_logits).max()) <= 1e-4
+    finally:
+        eng.close()
+
+
+def test_subsample_kernel_and_its_limits():
+    import mace_b200
+    ctx = mace_b200.Context(0)
+    try:
+        rng = np.random.Generator(np.random.PCG64(3))
+        for planes, H, W, sh, sw in [(6, 56, 56, 2, 2), (5, 7, 9, 2, 3), (3, 1, 1, 2, 2), (2, 13, 4, 1, 2), (4, 8, 8, 3, 1)]:
+            x = rng.standard_normal((planes, H, W)).astype(np.float32)
+            want = x[:, ::sh, ::sw]
+            dx, do = ctx.upload(x), ctx.alloc(want.size * 4)
+            ctx.subsample_f32(dx, do, planes, H, W, (sh, sw))
+            assert np.array_equal(ctx.download(do, want.shape, np.float32), want)
+        with pytest.raises(mace_b200.MaceB200Error):
+            ctx.subsample_f32(dx, do, 1, 4, 4, (0, 1))
+        with pytest.raises(mace_b200.MaceB200Error):
+            ctx.subsample_f32(dx, dx, 1, 4, 4, (2, 2))
+    finally:
+        ctx.close()
+
+
+def test_a_single_strided_convolution_or_a_padded_one_is_left_alone(net):
+    from mace_b200 import hostapi as H
+    rng = np.random.Generator(np.random.PCG64(4))
+    F = H.DT_FLOAT
+    net.add_tensor("X", rng.standard_normal((1, 8, 10, 10)).astype(np.float32))
+    net.add_tensor("Y", rng.standard_normal((1, 8, 10, 10)).astype(np.float32))
+    for name in ("w1", "w2", "w3", "w4"):
+        net.add_tensor(name, rng.standard_normal((8, 8, 1, 1)).astype(np.float32), is_weight=True)
+    net.add_tensor("w5", rng.standard_normal((8, 8, 3, 3)).astype(np.float32), is_weight=True)
+    s2 = {"strides": [2, 2], "dilations": [1, 1]}
+    net.op("Conv2D", "a", ["X", "w1"], ["A"], T=F, ints=s2, i={"padding": H.SAME})      # alone on X
+    net.op("Conv2D", "b", ["Y", "w2"], ["B"], T=F, ints=s2, i={"padding": H.VALID})     # pair on Y ...
+    net.op("Conv2D", "c", ["Y", "w3"], ["C"], T=F, ints=s2, i={"padding": H.SAME})
+    net.op("Conv2D", "d", ["Y", "w4"], ["D"], T=F, ints={"strides": [2, 1], "dilations": [1, 1]},
+           i={"padding": H.SAME})                                                        # ... other strides
+    net.op("Conv2D", "e", ["Y", "w5"], ["E"], T=F, ints=s2, i={"padding": H.SAME})      # 3x3: not pointwise
+    net.run()
+    before = {k: net.read(k, np.float32) for k in "ABCDE"}
+    assert net.share_subsampled_inputs() == 1
+    net.run()
+    for k, want in before.items():
+        got = net.read(k, np.float32)
+        assert got.shape == want.shape and np.abs(got - want).max() <= 1e-5 * np.abs(want).max(), k
+
+
 def test_activation_is_not_merged_when_the_sum_has_another_reader(net):
     from mace_b200 import hostapi as H
     a = np.arange(-3, 3, dtype=np.float32).reshape(1, 1, 2, 3)
