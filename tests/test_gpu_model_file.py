@@ -36,6 +36,24 @@ def test_transpose2d_batched_moves_every_element(ctx, batch, rows, cols, dtype):
     assert np.array_equal(got, x.transpose(0, 2, 1))
 
 
+def test_transpose2d_batched_round_trip_at_full_size(ctx):
+    """The input of the benchmarked networks (64 x 224 x 224 x 3 uint8, 256 x 3 x 224 x 224 fp32):
+    NHWC -> NCHW -> NHWC gives the bytes back, and the middle tensor is the numpy transpose of a
+    sample of images."""
+    rng = np.random.Generator(np.random.PCG64(99))
+    for batch, dtype in ((64, np.uint8), (256, np.float32)):
+        x = rng.integers(0, 256, size=(batch, 224 * 224, 3)).astype(dtype)
+        dx, dm, db = ctx.upload(x), ctx.alloc(x.nbytes), ctx.alloc(x.nbytes)
+        ctx.transpose2d_batched(dx, dm, batch, 224 * 224, 3, x.dtype.itemsize)
+        ctx.transpose2d_batched(dm, db, batch, 3, 224 * 224, x.dtype.itemsize)
+        assert np.array_equal(ctx.download(db, x.shape, dtype), x)
+        mid = ctx.download(dm, (batch, 3, 224 * 224), dtype)
+        for n in (0, batch // 2, batch - 1):
+            assert np.array_equal(mid[n], x[n].T)
+        for b in (dx, dm, db):
+            b.free()
+
+
 def test_transpose2d_batched_edge_cases(ctx):
     from mace_b200 import MaceB200Error
     d = ctx.alloc(64)
