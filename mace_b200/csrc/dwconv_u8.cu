@@ -218,10 +218,12 @@ __device__ __forceinline__ void dw_mac(int32_t (&acc)[4][4], const DwRow<STRIDE>
 template <int STRIDE, int VAR>
 __global__ void __launch_bounds__(DW_THREADS, DW_BLOCKS_PER_SM)
 dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows_per_thread,
-                    int segments) {
+                    int segments, int weights_cached) {
   constexpr int COLS = STRIDE == 1 ? 6 : 9;
   mb_grid_dep_launch();
-  mb_grid_dep_wait();  // the input is the previous kernel's output
+  // (packed weights cached by the caller were written long ago: they are fetched before the
+  // wait for the previous kernel, whose output is this kernel's input)
+  if (!weights_cached) mb_grid_dep_wait();
   const int groups = p.C >> 2;
   const int strips = (p.Wo + 3) >> 2;
   const int per_seg = groups * strips;
@@ -251,6 +253,7 @@ dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows
   const int32_t start[4] = {static_cast<int32_t>(st4.x), static_cast<int32_t>(st4.y),
                             static_cast<int32_t>(st4.z), static_cast<int32_t>(st4.w)};
   const bool has_w2 = flags.x != 0;
+  if (weights_cached) mb_grid_dep_wait();
 
   // columns: byte offsets inside a row and validity bits, fixed for the thread
   uint32_t col_off[COLS];
@@ -427,6 +430,7 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
   if (fast) {
     const int64_t groups = C / 4;
     const uint4 *packed = static_cast<const uint4 *>(prepacked);
+    const int weights_cached = packed != nullptr ? 1 : 0;
     if (packed == nullptr) {  // no cached copy: prepare the weight words in scratch
       uint4 *fresh = nullptr;
       MB_RETURN_IF_ERROR(mb_scratch(ctx, sizeof(uint4) * DW_PACK_ITEMS * groups,
@@ -450,7 +454,7 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
     const unsigned grid = static_cast<unsigned>(ceil_div64(per_seg * segments * N, DW_THREADS));
 #define MB_DW_LAUNCH(S, V)                                                                   \
   MB_CUDA(ctx, mb_launch_chained(ctx, dwconv3x3_u8_kernel<S, V>, dim3(grid), dim3(DW_THREADS), 0, p, packed, rows, \
-                                 static_cast<int>(segments)))
+                                 static_cast<int>(segments), weights_cached))
     const int var = mb_requant_variant(right_shift, zp_out);
     if (stride_h == 1) {
       switch (var) {
