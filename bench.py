@@ -37,7 +37,6 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 L2_BYTES = 126 * 1024 * 1024
 
@@ -62,6 +61,72 @@ def measured_peaks():
                 "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
             "source": "fallback"}
+
+
+def library_tensor_peaks(device_index, seconds=2.0):
+    """int8 and tf32 tensor-core yardsticks measured on this GPU with library GEMMs, the way
+    MEASURED_PEAKS.json's bf16 figure is made: 8192^3, best of 10 launches (burst) and back to
+    back for `seconds` (sustained), CUDA events, SM clocks sampled meanwhile.  torch._int_mm is
+    cuBLASLt's int8 x int8 -> int32 GEMM, torch.matmul with TF32 allowed its tf32 GEMM.  These
+    are denominators only; nothing of the measured path calls them."""
+    import torch
+    out = {}
+    dev = torch.device("cuda", device_index)
+    n = 8192
+    ops = 2.0 * n ** 3
+    with torch.cuda.device(dev):
+        a8 = torch.randint(-128, 127, (n, n), dtype=torch.int8, device=dev)
+        b8 = torch.randint(-128, 127, (n, n), dtype=torch.int8, device=dev)
+        a32 = torch.randn((n, n), dtype=torch.float32, device=dev)
+        b32 = torch.randn((n, n), dtype=torch.float32, device=dev)
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        try:
+            for key, fn in (("int8", lambda: torch._int_mm(a8, b8)), ("tf32", lambda: torch.matmul(a32, b32))):
+                try:
+                    for _ in range(3):
+                        fn()
+                    torch.cuda.synchronize()
+                    best = float("inf")
+                    for _ in range(10):
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                        fn()
+                        e1.record()
+                        e1.synchronize()
+                        best = min(best, e0.elapsed_time(e1))
+                    sampler = ClockSampler(device_index)
+                    sampler.start()
+                    reps = max(10, int(seconds * 1e3 / best))
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(reps):
+                        fn()
+                    e1.record()
+                    e1.synchronize()
+                    clocks = sampler.stop()
+                    out[key] = {"burst": round(ops / (best * 1e-3) / 1e12, 1),
+                                "sustained": round(ops * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12, 1),
+                                "unit": "TOP/s" if key == "int8" else "TFLOP/s", "shape": "8192^3",
+                                "sm_mhz_sustained": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")}
+                except Exception as e:  # the yardstick is missing: say so, keep the run
+                    out[key] = {"error": str(e)[:200]}
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+        del a8, b8, a32, b32
+        torch.cuda.empty_cache()
+    return out
+
+
+def tensor_peak(peaks, lib_peaks, kind):
+    """(peak, source) for a tensor-bound fraction: the measured library GEMM of that type where
+    it could be measured, else the multiple of the measured bf16 GEMM that the tensor core's
+    relative rates imply (int8 2 x, tf32 1/2 x)."""
+    m = (lib_peaks or {}).get(kind, {})
+    if "burst" in m:
+        return m["burst"], "measured %s library GEMM 8192^3, burst (sustained %.0f)" % (kind, m["sustained"])
+    factor = 2.0 if kind == "int8" else 0.5
+    return factor * peaks["bf16_tflops"], "%g x %s bf16 burst (no %s yardstick)" % (factor, peaks["source"], kind)
 
 
 class ClockSampler:
@@ -162,8 +227,6 @@ class RawContext:
 def init_dist(world, local):
     if world <= 1:
         return None
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO"):
-        os.environ["NCCL_DEBUG"] = "WARN"  # keep the logs short (they go to stderr, see main)
     import torch
     import torch.distributed as dist
     torch.cuda.set_device(local)
@@ -246,7 +309,10 @@ def run_gemm(args, rank, world):
     from oracle import pyoracle as orc  # quantization parameters and the cpu_baseline leg only
     local = int(os.environ.get("LOCAL_RANK", rank))
     ctx = mace_b200.Context(local)
-    wl = GemmWorkload()
+    size = int(getattr(args, "gemm_size", 4096) or 4096)
+    wl = GemmWorkload(size, size, size)
+    if size != 4096:
+        wl.name = "gemm_u8_%d" % size
     dist = init_dist(world, local)
 
     def barrier():
@@ -304,7 +370,7 @@ def run_gemm(args, rank, world):
         ms_per_step = ms / args.steps
         value = world * wl.ops_per_step / (ms_per_step * 1e-3) / 1e12
         e2e_val = world * wl.ops_per_step / (e2e_ms / e2e_steps * 1e-3) / 1e12
-        peak = 2.0 * peaks["bf16_tflops"]
+        peak, peak_src = tensor_peak(peaks, lib_peaks(local), "int8")
         achieved = wl.ops_per_step / (ms_per_step * 1e-3) / 1e12
         result = {
             "metric": wl.metric, "value": round(value, 3), "unit": wl.unit, "n_gpus": world,
@@ -314,9 +380,10 @@ def run_gemm(args, rank, world):
             "config": dict(wl.config(n_sets), parallelism="replicas only (dp%d)" % world),
             "roofline": {"bound": "tensor", "achieved": round(achieved, 2),
                          "peak": round(peak, 1), "unit": "TOP/s",
-                         "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC["gemm_u8_4096"],
-                         "peak_source": "2 x %s bf16 burst (int8 rate of the tensor core; "
-                                        "no int8 figure in MEASURED_PEAKS.json)" % peaks["source"],
+                         "frac": round(achieved / peak, 4),
+                         "traffic": NCU_TRAFFIC["gemm_u8_4096"] if size == 4096 else None,
+                         "peak_source": peak_src,
+                         "frac_of_2x_bf16_burst": round(achieved / (2.0 * peaks["bf16_tflops"]), 4),
                          "kernel": "gemm_u8_tc_kernel<256> (step also holds the two operand "
                                    "byte-sum kernels)"},
             "e2e": {"value": round(e2e_val, 3), "unit": wl.unit,
@@ -376,102 +443,188 @@ def mobilenet_layer_bytes(layers, batch):
     return out
 
 
+LIB_PEAKS = None  # library_tensor_peaks() of this process, once measured
+
+
+def lib_peaks(local):
+    global LIB_PEAKS
+    if LIB_PEAKS is None:
+        LIB_PEAKS = library_tensor_peaks(local)
+    return LIB_PEAKS
+
+
+class MobilenetRig:
+    """One engine of the quantized MobileNet at a given per-GPU batch, with rotating pinned host
+    inputs, and the two timed loops of the benchmark."""
+
+    def __init__(self, mn, hostapi, layers, batch, local, rank, n_inputs=16):
+        self.mn, self.batch, self.n_inputs = mn, batch, n_inputs
+        self.eng = mn.build_engine(hostapi, layers, batch, device=local)
+        self.ctx = RawContext(self.eng.context)
+        # rotate the engine over several input tensors so that consecutive steps do not find
+        # their input in L2; activations (51 MB at the widest layer of batch 64) stream through
+        # L2 on their own
+        self.inputs = [mn.random_images(batch, seed=100 * rank + i) for i in range(n_inputs)]
+        self.hin = self.ctx.pinned(self.inputs[0].nbytes * n_inputs).reshape(n_inputs, -1)
+        for i, x in enumerate(self.inputs):
+            self.hin[i] = x.ravel()
+        self.houts = [self.ctx.pinned(batch * mn.NUM_CLASSES) for _ in range(2)]
+
+    def warm_and_capture(self, warmup, graph=True, plan=False):
+        mem = None
+        for i in range(max(warmup, 3)):
+            self.eng.write("input", self.inputs[i % self.n_inputs])
+            self.eng.run(sync=False)
+            if i == 0 and plan:
+                self.eng.sync()
+                mem = self.eng.plan_memory()
+        if graph:
+            self.eng.sync()
+            self.eng.capture()  # the chain is replayed from one CUDA graph from here on
+            self.eng.run(sync=False)
+        return mem
+
+    def timed_resident(self, steps):
+        """Device-timed replays on the input the last (untimed) copy left in HBM: the input is
+        1.5 % of the bytes a step moves, the rest (activations) exceeds L2 at batch 64."""
+        ctx = self.ctx
+        e0, e1 = ctx.event(), ctx.event()
+        ctx.record(e0)
+        for _ in range(steps):
+            self.eng.run(sync=False)
+        ctx.record(e1)
+        return ctx.elapsed_ms(e0, e1)
+
+    def e2e_loop(self, n, first, gather):
+        """Pinned host input -> H2D -> chain -> D2H logits, every step, pipelined two deep: the
+        upload of step i + 1 (upload stream, two staging buffers) overlaps the chain of step i,
+        and the host takes delivery of step i - 1's logits (waits for their copy) after it has
+        enqueued step i.  With several ranks the gather of the logits is enqueued behind every
+        step (AsyncRowGather: a side stream, no host wait).  The region ends when the last logits
+        -- and the last gather -- are in host memory."""
+        prev = None
+        for i in range(first, first + n):
+            slot = self.eng.run_host_pipelined("input", self.hin[i % self.n_inputs], "fc", self.houts[i & 1])
+            if gather is not None:
+                gather.enqueue()
+            if prev is not None:
+                self.eng.wait_slot(prev)
+            prev = slot
+        self.eng.wait_slot(prev)
+        if gather is not None:
+            gather.wait()
+        self.eng.sync()
+
+    def make_gather(self, dist, world):
+        if dist is None:
+            return None
+        from mace_b200.sharding import AsyncRowGather, torch_view
+        import mace_b200
+        ptr, nbytes = self.eng.device_ptr("fc")
+        assert nbytes == self.batch * self.mn.NUM_CLASSES
+        rows = torch_view(ptr, (self.batch, self.mn.NUM_CLASSES))
+        stream = mace_b200.lib().mb_stream(ctypes.c_void_p(self.eng.context))
+        return AsyncRowGather(dist, self.batch * world, rows, stream)
+
+    def close(self):
+        self.eng.close()
+
+
+def h2d_rate(ctx, src_row, dist):
+    """GB/s of this rank's uploads from pinned host memory with every rank copying at once
+    (the slowest rank's figure): what the host's PCIe / memory path gives each GPU."""
+    L = ctx.L
+    nbytes = int(src_row.nbytes)
+    dst = ctypes.c_void_p()
+    assert L.mb_malloc(ctx.h, nbytes, ctypes.byref(dst)) == 0
+    src = ctypes.c_void_p(src_row.ctypes.data)
+    for _ in range(3):
+        L.mb_memcpy_h2d(ctx.h, dst, src, nbytes)
+    ctx.sync()
+    if dist is not None:
+        dist.barrier()
+    reps = 20
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        L.mb_memcpy_h2d(ctx.h, dst, src, nbytes)
+    ctx.sync()
+    dt = time.perf_counter() - t0
+    dt = max_over_ranks(dist, [dt])[0]
+    L.mb_free(ctx.h, dst)
+    return reps * nbytes / dt / 1e9
+
+
 def run_mobilenet(args, rank, world):
     import mace_b200
     from mace_b200 import hostapi
     from oracle import pyoracle as orc  # model construction (quantization math) and cpu_baseline
-    import mobilenet_v1 as mn
+    from mace_b200.harness import mobilenet_v1 as mn
     local = int(os.environ.get("LOCAL_RANK", rank))
     dist = init_dist(world, local)
     layers = mn.build(orc, seed=0)
-    # rotate the engine over several input tensors so that consecutive steps do not find their
-    # input in L2; activations (51 MB at the widest layer) stream through L2 on their own
-    eng = mn.build_engine(hostapi, layers, BATCH, device=local)
-    ctx = RawContext(eng.context)
-    n_inputs = 16  # 16 x 9.6 MB = 154 MB > L2
-    inputs = [mn.random_images(BATCH, seed=100 * rank + i) for i in range(n_inputs)]
-    hin = ctx.pinned(inputs[0].nbytes * n_inputs).reshape(n_inputs, -1)
-    for i, x in enumerate(inputs):
-        hin[i] = x.ravel()
-    hout = ctx.pinned(BATCH * mn.NUM_CLASSES)
+    rig = MobilenetRig(mn, hostapi, layers, BATCH, local, rank)
+    eng, ctx = rig.eng, rig.ctx
 
     def barrier():
         ctx.sync()
         if dist is not None:
             dist.barrier()
 
-    # device-resident inputs: one engine per input slot would triple memory; instead the input
-    # tensor is rewritten by an untimed H2D between steps for warm-up, and the timed loop runs
-    # the chain on device-resident data that the previous (untimed) copy left in HBM -- the
-    # input is 1.5 % of the bytes a step moves, the rest (activations, 650 MB) exceeds L2.
-    mem = None
-    for i in range(max(args.warmup, 3)):
-        eng.write("input", inputs[i % n_inputs])
-        eng.run(sync=False)
-        if i == 0 and args.plan:
-            eng.sync()
-            mem = eng.plan_memory()
-    if not args.no_graph:
-        eng.sync()
-        eng.capture()  # the chain is replayed from one CUDA graph from here on
-        eng.run(sync=False)
+    mem = rig.warm_and_capture(args.warmup, graph=not args.no_graph, plan=args.plan)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.01)
     l0, ltc0 = ctx.launches, ctx.launches_tensor_core
-    e0, e1 = ctx.event(), ctx.event()
-    ctx.record(e0)
-    for i in range(args.steps):
-        eng.run(sync=False)
-    ctx.record(e1)
-    ms = ctx.elapsed_ms(e0, e1)
+    ms = rig.timed_resident(args.steps)
     barrier()
     launches, launches_tc = ctx.launches - l0, ctx.launches_tensor_core - ltc0
     clocks = sampler.stop() if rank == 0 else None
     if args.profile:
-        eng.close()
+        rig.close()
         return None
 
-    # per-operator device times (CUDA events between operators), averaged over a few runs
-    prof_runs = 5
-    per_op = {}
-    for _ in range(prof_runs):
-        for label, t in eng.run_profiled():
-            per_op[label] = per_op.get(label, 0.0) + t / prof_runs
+    # per-operator device times inside a graph replay (event nodes between the operators of a
+    # second recorded graph): they add up to the replayed step
+    per_op = dict(eng.run_profiled_graph(replays=5))
 
-    # end to end: pinned host input -> H2D -> chain -> D2H logits, every step.  The calls are
-    # pipelined: the upload of step i + 1 (upload stream, two staging buffers) overlaps the
-    # chain of step i; every step's images are copied in and its logits copied out inside the
-    # timed region, and the region ends when the last logits are in host memory.
-    houts = [hout, ctx.pinned(BATCH * mn.NUM_CLASSES)]
-
-    def gather(call):  # the only collective of the path: gather the logits of a finished step
-        slot, buf = call
-        eng.wait_slot(slot)
-        from mace_b200.sharding import gather_rows
-        gather_rows(dist, houts[buf].reshape(BATCH, mn.NUM_CLASSES), BATCH * world, device="cuda")
-
-    def e2e_loop(n, first):
-        prev = None
-        for i in range(first, first + n):
-            slot = eng.run_host_pipelined("input", hin[i % n_inputs], "fc", houts[i & 1])
-            if dist is not None and prev is not None:
-                gather(prev)
-            prev = (slot, i & 1)
-        if dist is not None:
-            gather(prev)
-        eng.sync()
-
-    e2e_loop(4, 0)
+    gather = rig.make_gather(dist, world)
+    rig.e2e_loop(4, 0, gather)
     barrier()
     e2e_steps = max(4, min(args.steps, 50))
     t0 = time.perf_counter()
-    e2e_loop(e2e_steps, 4)
+    rig.e2e_loop(e2e_steps, 4, gather)
     e2e_ms = (time.perf_counter() - t0) * 1e3  # host clock around enqueue ... last logits on the host
     barrier()
+    gathered_ok = None
+    if gather is not None and rank == 0:  # the gathered rows of the last step: rank 0's own rows must be in place
+        full = gather.wait().numpy()
+        gathered_ok = bool(np.array_equal(full[:BATCH].ravel(), rig.houts[(4 + e2e_steps - 1) & 1]))
+    h2d_gbs = h2d_rate(ctx, rig.hin[0], dist)
     ms, e2e_ms = max_over_ranks(dist, [ms, e2e_ms])
+
+    # strong scaling: the configuration's own batch of 64 split over the ranks
+    strong = None
+    if world > 1 and BATCH % world == 0:
+        srig = MobilenetRig(mn, hostapi, layers, BATCH // world, local, rank)
+        srig.warm_and_capture(args.warmup, graph=not args.no_graph)
+        barrier()
+        s_ms = srig.timed_resident(args.steps)
+        barrier()
+        sg = srig.make_gather(dist, world)
+        srig.e2e_loop(4, 0, sg)
+        barrier()
+        t0 = time.perf_counter()
+        srig.e2e_loop(e2e_steps, 4, sg)
+        s_e2e = (time.perf_counter() - t0) * 1e3
+        barrier()
+        s_ms, s_e2e = max_over_ranks(dist, [s_ms, s_e2e])
+        strong = {"global_batch": BATCH, "batch_per_gpu": BATCH // world,
+                  "value": round(BATCH / (s_ms / args.steps * 1e-3), 1), "unit": "images/s",
+                  "ms_per_step": round(s_ms / args.steps, 4),
+                  "e2e": {"value": round(BATCH / (s_e2e / e2e_steps * 1e-3), 1), "unit": "images/s"}}
+        srig.close()
 
     result = None
     if rank == 0:
@@ -519,38 +672,56 @@ def run_mobilenet(args, rank, world):
             "model_hbm": {"algorithmic_bytes_per_step": total_bytes,
                           "achieved_gbs": round(total_bytes / (ms_per_step * 1e-3) / 1e9, 1),
                           "frac_of_peak": round(total_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)},
-            "kernel_families_ms": {v[0]: round(v[1], 4) for v in fam.values()},
+            "kernel_families_ms": dict({v[0]: round(v[1], 4) for v in fam.values()},
+                                       how="event nodes between the operators of a replayed graph; sum %.4f ms"
+                                           % total_prof),
             "e2e": {"value": round(e2e_val, 1), "unit": "images/s",
-                    "h2d_bytes_per_step": int(inputs[0].nbytes),
+                    "h2d_bytes_per_step": int(rig.inputs[0].nbytes),
                     "d2h_bytes_per_step": BATCH * mn.NUM_CLASSES},
+            "h2d_gbs_per_rank": round(h2d_gbs, 2),
             "gpu_launches": launches, "gpu_launches_tensor_core": launches_tc, "clocks": clocks,
         }
-        eng.close()
-        eng = None
+        if dist is not None:
+            result["gather"] = {"kind": "all_gather_into_tensor on a side stream, one per step, rank 0 copies "
+                                        "the rows to pinned host memory", "rows_in_place": gathered_ok}
+        if strong is not None:
+            result["strong_scaling"] = strong
+        elif world == 1:
+            result["strong_scaling"] = {"global_batch": BATCH, "batch_per_gpu": BATCH, "value": round(value, 1),
+                                        "unit": "images/s", "ms_per_step": round(ms_per_step, 4),
+                                        "e2e": {"value": round(e2e_val, 1), "unit": "images/s"}}
+    rig.close()
+    if rank == 0:
+        lp = lib_peaks(local)
+        result["tensor_peaks_measured"] = lp
         # the other half of the metric: u8 GEMM TOPS on the 4096^3 MatMul
         gctx = mace_b200.Context(local)
         gwl = GemmWorkload()
         gms, _, _, _, _ = time_gemm(gctx, orc, gwl, 30, 5)
         gtops = gwl.ops_per_step / (gms * 1e-3) / 1e12
+        ipeak, isrc = tensor_peak(peaks, lp, "int8")
         result["u8_gemm"] = {"workload": gwl.name, "value": round(gtops, 2), "unit": "TOPS",
                              "ms_per_step": round(gms, 5),
+                             "frac_of_int8_peak": round(gtops / ipeak, 4), "int8_peak": ipeak, "peak_source": isrc,
                              "frac_of_2x_bf16_peak": round(gtops / (2 * peaks["bf16_tflops"]), 4)}
         gctx.close()
         # the same network as a converted-model file through the model-level API (NetDef bytes +
         # weights blob -> CreateMaceEngineFromProto; one synchronous MaceEngine::Run per step on
         # pinned host buffers: upload, graph replay, download, wait)
         if world == 1:
-            import netdef_wire
+            from mace_b200.harness import netdef_wire
             writer = netdef_wire.NetDefWriter(quantized=True, name="mobilenet_v1_u8")
             mn.build_engine(netdef_wire.WriterModule(hostapi, writer), layers, BATCH)
             writer.add_output("fc", (BATCH, 1, 1, mn.NUM_CLASSES), data_type=netdef_wire.DT_UINT8)
             model = hostapi.Model(writer.netdef(), writer.weights(), device=local, plan_memory=True, cuda_graph=True)
             mctx = RawContext(model.context)
             mout = mctx.pinned(BATCH * mn.NUM_CLASSES).reshape(BATCH, 1, 1, mn.NUM_CLASSES)
-            shaped = hin.reshape((n_inputs,) + inputs[0].shape)
+            minp = mctx.pinned(rig.inputs[0].nbytes * 4).reshape((4,) + rig.inputs[0].shape)
+            for i in range(4):
+                minp[i] = rig.inputs[i]
 
             def model_step(i):
-                return model.run({"input": (shaped[i % n_inputs], hostapi.DF_NHWC)}, {"fc": (mout, hostapi.DF_NHWC)})
+                return model.run({"input": (minp[i % 4], hostapi.DF_NHWC)}, {"fc": (mout, hostapi.DF_NHWC)})
 
             for i in range(4):
                 model_step(i)
@@ -563,9 +734,9 @@ def run_mobilenet(args, rank, world):
                                        "ms_per_step": round(mms, 4), "graph": model.captured,
                                        "call": "MaceEngine::Run on a model file, synchronous, pinned host buffers"}
             model.close()
-        # CPU baseline: the oracle chain on this box's host cores, one full batch
+        # CPU baseline: the oracle chain on this box's host cores, full batches
         threads = orc.set_threads(0)
-        x = inputs[0]
+        x = rig.inputs[0]
         mn.oracle_forward(orc, layers, x[:4])
         t0 = time.perf_counter()
         passes = 2
@@ -575,11 +746,53 @@ def run_mobilenet(args, rank, world):
         result["cpu_baseline"] = {"value": round(BATCH / dt, 2), "unit": "images/s",
                                   "cores": threads, "kind": "port",
                                   "sample": "%d full batches of %d images" % (passes, BATCH)}
-    if eng is not None:
-        eng.close()
+        if world == 1 and not args.no_extras:
+            result["configs"] = other_config_records(args, rank)
     if dist is not None:
         dist.destroy_process_group()
     return result
+
+
+def other_config_records(args, rank):
+    """Compact records of the other benchmark configurations (the 1024^3 MatMul, the Winograd
+    convolution, the K = N = 4096 sweep with the batched MatMul and the GEMV, ResNet-50 at batch
+    256), each timed with its own CUDA events over >= 20 steps, for the default line."""
+    import copy
+    sub = copy.copy(args)
+    sub.steps, sub.warmup, sub.profile = max(20, min(args.steps, 50)), max(args.warmup, 3), False
+    out = {}
+
+    def pick(res, keys):
+        return {k: res[k] for k in keys if k in res}
+
+    try:
+        sub.gemm_size = 1024
+        r = run_gemm(sub, rank, 1)
+        out["gemm_u8_1024"] = dict(pick(r, ("value", "unit", "ms_per_step")), frac=r["roofline"]["frac"],
+                                   peak=r["roofline"]["peak"], e2e=r["e2e"]["value"],
+                                   cpu_baseline=r["cpu_baseline"]["value"])
+    except Exception as e:
+        out["gemm_u8_1024"] = {"error": str(e)[:200]}
+    sub.gemm_size = 4096
+    try:
+        r = run_winograd(sub, rank, 1)
+        out["winograd_f32_cfg1"] = dict(pick(r, ("value", "unit", "ms_per_step")), hbm_frac=r["roofline"]["frac"],
+                                        e2e=r["e2e"]["value"], cpu_baseline=r["cpu_baseline"]["value"])
+    except Exception as e:
+        out["winograd_f32_cfg1"] = {"error": str(e)[:200]}
+    try:
+        r = run_sweep(sub, rank, 1)
+        out["gemm_u8_sweep"] = r["cases"]
+    except Exception as e:
+        out["gemm_u8_sweep"] = {"error": str(e)[:200]}
+    try:
+        r = run_resnet(sub, rank, 1)
+        out["resnet50_f32_b256"] = dict(pick(r, ("value", "unit", "ms_per_step")), tensor_frac=r["roofline"]["frac"],
+                                        tflops=r["roofline"]["achieved"], e2e=r["e2e"]["value"],
+                                        cpu_baseline=r["cpu_baseline"]["value"])
+    except Exception as e:
+        out["resnet50_f32_b256"] = {"error": str(e)[:200]}
+    return out
 
 
 # --------------------------------------------------------------------------------------
@@ -716,7 +929,7 @@ def run_resnet(args, rank, world):
     import mace_b200  # noqa: F401  (fails loudly when the device library is missing)
     from mace_b200 import hostapi
     from oracle import pyoracle as orc  # cpu_baseline leg only
-    import resnet50 as rn
+    from mace_b200.harness import resnet50 as rn
     local = int(os.environ.get("LOCAL_RANK", rank))
     dist = init_dist(world, local)
     batch = args.batch or 256
@@ -815,7 +1028,7 @@ def run_resnet(args, rank, world):
         macs = rn.macs_per_image(nodes)
         value = world * batch / (ms_per_step * 1e-3)
         tflops = 2.0 * macs * batch / (ms_per_step * 1e-3) / 1e12
-        tf32_peak = peaks["bf16_tflops"] / 2.0
+        tf32_peak, tf32_src = tensor_peak(peaks, lib_peaks(local), "tf32")
         alg_bytes = rn.activation_bytes(nodes, batch)
         result = {
             "metric": "fp32_resnet50_images_per_s", "value": round(value, 1), "unit": "images/s",
@@ -834,9 +1047,9 @@ def run_resnet(args, rank, world):
                        "l2": "activations of one step (%.1f GB) exceed L2" % (alg_bytes / 1e9)},
             "roofline": {"bound": "tensor", "achieved": round(tflops, 2), "peak": round(tf32_peak, 1),
                          "unit": "TFLOP/s", "frac": round(tflops / tf32_peak, 4), "traffic": None,
-                         "peak_source": "half the %s bf16 GEMM rate (dense tf32); the fp32 GEMMs run three "
-                                        "tf32 MMAs per product (hi/lo split), so a third of it is the ceiling "
-                                        "for direct-equivalent flops outside Winograd" % peaks["source"],
+                         "peak_source": tf32_src + "; the fp32 GEMMs run three tf32 MMAs per product (hi/lo "
+                                        "split), so a third of it is the ceiling for direct-equivalent flops "
+                                        "outside Winograd",
                          "kernel": "whole step (gemm_f32_tc_kernel dominates)",
                          "direct_equivalent_flops_per_step": 2.0 * macs * batch},
             "model_hbm": {"algorithmic_bytes_per_step": alg_bytes,
@@ -871,6 +1084,7 @@ def run_sweep(args, rank, world):
     ctx = mace_b200.Context(local)
     dist = init_dist(world, local)
     peaks = measured_peaks()
+    int8_peak, int8_src = tensor_peak(peaks, lib_peaks(local) if rank == 0 else None, "int8")
     rows = []
 
     def timed(fn, n):
@@ -899,6 +1113,7 @@ def run_sweep(args, rank, world):
         rows.append({"case": "M=%d" % M, "ms": round(ms, 5), "tops": round(2.0 * M * Nn * K / ms / 1e9, 2),
                      "gbs": round(byts / ms / 1e6, 1),
                      "frac_hbm": round(byts / ms / 1e6 / peaks["hbm_gbs"], 4),
+                     "frac_int8_peak": round(2.0 * M * Nn * K / ms / 1e9 / int8_peak, 4),
                      "frac_2x_bf16": round(2.0 * M * Nn * K / ms / 1e9 / (2 * peaks["bf16_tflops"]), 4)})
     # batched MatMul 64 x 512^3
     bA = [ctx.upload(rng.integers(0, 256, size=(64, 512, 512), dtype=np.uint8)) for _ in range(5)]
@@ -910,6 +1125,7 @@ def run_sweep(args, rank, world):
                                      mult, shift, zp_c), args.steps)
     rows.append({"case": "batch64_512^3", "ms": round(ms, 5), "tops": round(2.0 * 64 * 512 ** 3 / ms / 1e9, 2),
                  "gbs": round(3 * 64 * 512 * 512 / ms / 1e6, 1),
+                 "frac_int8_peak": round(2.0 * 64 * 512 ** 3 / ms / 1e9 / int8_peak, 4),
                  "frac_2x_bf16": round(2.0 * 64 * 512 ** 3 / ms / 1e9 / (2 * peaks["bf16_tflops"]), 4)})
     # GEMV with the FullyConnected rule: weights [4096 x 4096], one vector
     Ws = [ctx.upload(rng.integers(0, 256, size=(1, 4096, 4096), dtype=np.uint8)) for _ in range(n_sets)]
@@ -931,6 +1147,7 @@ def run_sweep(args, rank, world):
             "data": "synthetic",
             "config": {"workload": "gemm_u8_sweep", "K": K, "N": Nn,
                        "l2": "rotating %d B matrices (%.0f MB > L2)" % (n_sets, n_sets * 16.8),
+                       "int8_peak": int8_peak, "int8_peak_source": int8_src,
                        "parallelism": "replicas only (dp%d)" % world},
             "cases": rows}
 
@@ -959,9 +1176,9 @@ def run_reference(args, rank, world):
         metric, unit, config = wl.metric, wl.unit, dict(wl.config(1), parallelism="host cores")
         ms_per_step = dt * 1e3 * wl.M / rows
     else:
-        import mobilenet_v1 as mn
+        from mace_b200.harness import mobilenet_v1 as mn
         layers = mn.build(orc, seed=0)
-        sample_n = 16
+        sample_n = BATCH  # the whole batch of the configuration, every step
         x = mn.random_images(sample_n, seed=0)
         mn.oracle_forward(orc, layers, x[:2])
         steps = max(1, min(args.steps, 5))
@@ -970,10 +1187,12 @@ def run_reference(args, rank, world):
             mn.oracle_forward(orc, layers, x)
         dt = (time.perf_counter() - t0) / steps
         value = round(sample_n / dt, 2)
-        sample = "%d images of the batch of %d per step" % (sample_n, BATCH)
+        sample = "the full batch of %d images per step" % BATCH
         metric, unit = "quantized_mobilenet_v1_images_per_s", "images/s"
-        config = {"workload": "mobilenet_v1_u8_b64", "batch_per_gpu": BATCH,
-                  "image": "224x224x3 uint8 NHWC", "parallelism": "host cores"}
+        config = {"workload": "mobilenet_v1_u8_b64", "batch_per_gpu": BATCH, "global_batch": BATCH,
+                  "image": "224x224x3 uint8 NHWC",
+                  "weights": "He-normal, per-tensor uint8 (non_zero), seed 0",
+                  "parallelism": "host cores (%d threads), one process" % threads, "sample": sample}
         ms_per_step = dt * 1e3 * BATCH / sample_n
     return {"impl": "reference", "metric": metric, "value": value, "unit": unit,
             "n_gpus": world, "steps": steps, "warmup": 1, "ms_per_step": round(ms_per_step, 3),
@@ -1003,6 +1222,9 @@ def main():
                     help="mobilenet_v1_u8_b64: share activation memory between layers (two buffers)")
     ap.add_argument("--no-plan", action="store_true",
                     help="resnet50_f32_b256: every activation tensor keeps its own buffer")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="mobilenet_v1_u8_b64: skip the records of the other configurations")
+    ap.add_argument("--gemm-size", type=int, default=4096, help="gemm_u8_4096: M = N = K (1024: config 0)")
     ap.add_argument("--profile", action="store_true",
                     help="run only the device-resident timed loop (for ncu captures)")
     args = ap.parse_args()

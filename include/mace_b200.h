@@ -71,6 +71,28 @@ int mb_upload_h2d(mb_context *ctx, void *dst_dev, const void *src_host, size_t b
 int mb_upload_wait_event(mb_context *ctx, void *event);
 int mb_upload_signal(mb_context *ctx);
 int mb_stream_sync(mb_context *ctx);
+
+/* ---- Failure paths ---------------------------------------------------------
+ * mb_set_runtime_failure_ratio / mb_should_mock_runtime_failure: the reference's
+ * allocator fault injection (ShouldMockRuntimeFailure,
+ * mace/core/runtime_failure_mock.cc:25-53, env MACE_RUNTIME_FAILURE_RATIO, checked
+ * at the top of every allocator's New()).  With a ratio r in (0, 1] every mb_malloc
+ * fails with MACE_OUT_OF_RESOURCES with probability r.  The ratio is process-wide;
+ * it is read from the environment at the first allocation unless set here.
+ *
+ * mb_wait_timeout_selftest: runs the bounded mbarrier wait that the tensor-core
+ * kernels use on a barrier nobody arrives at, with a budget of `budget_cycles` SM
+ * clocks (1 .. 2^31), so that it runs out: the kernel records the timeout in the
+ * context's status word and returns; the next mb_stream_sync then fails with
+ * MACE_RUNTIME_ERROR ("a kernel gave up a bounded wait") and clears the word, and
+ * the context stays usable.  No counterpart in the reference (its kernels do not
+ * wait on one another); it mirrors how an error code travels up through
+ * MACE_RETURN_IF_ERROR (include/mace/utils/logging.h:86-95).  host_waited_cycles
+ * (may be NULL) receives the clocks the wait took. */
+int mb_set_runtime_failure_ratio(float ratio);
+int mb_should_mock_runtime_failure(void);
+int mb_wait_timeout_selftest(mb_context *ctx, long long budget_cycles,
+                             long long *host_waited_cycles);
 /* The cudaStream_t of the context, as an opaque pointer (for event timing). */
 void *mb_stream(mb_context *ctx);
 /* Device-side timing on the context's stream (the per-operator CallStats of
@@ -176,7 +198,12 @@ int mb_dwconv_u8_nhwc(mb_context *ctx, const uint8_t *in,
  * transformed filter, mace/ops/arm/base/conv_2d_3x3_winograd.cc:120-145) prepares them
  * once into a buffer of mb_dwconv3x3_u8_prepacked_bytes(C) bytes (0: not eligible) and
  * passes it to mb_dwconv_u8_nhwc_prepacked; zp_in and zp_f must be the values used for
- * packing.  `prepacked` may be NULL, and is ignored when the call is not that case. */
+ * packing.  `prepacked` may be NULL, and is ignored when the call is not that case.
+ * Precondition: the buffer must be filled by mb_dwconv3x3_u8_prepack on the SAME context
+ * (or by a copy on its stream) -- the depthwise kernel reads the tap words before it has
+ * waited for the kernel in front of it, unless that kernel is this context's prepack
+ * kernel, which the context tracks.  A buffer written by a kernel on another stream must
+ * be complete (event or sync) before the call. */
 size_t mb_dwconv3x3_u8_prepacked_bytes(int64_t C);
 int mb_dwconv3x3_u8_prepack(mb_context *ctx, const uint8_t *filter_hwim,
                             const int32_t *bias, int64_t C, int32_t zp_in,
@@ -341,6 +368,13 @@ int mb_dequantize_f32(mb_context *ctx, const void *in, int in_is_int32,
                       float *out, int64_t size, float scale, int32_t zero_point);
 int mb_minmax_f32(mb_context *ctx, const float *in, int64_t size,
                   float *host_min, float *host_max);
+/* The bin counts SerialNet::Run logs for an operator that carries a quantize_info range
+ * when MACE_LOG_TENSOR_RANGE is on (mace/core/net/serial_net.cc:200-221):
+ *   bin_v = (max_v - min_v) / bins;  counts[clamp(int((x - min_v) / bin_v), 0, bins - 1)]++
+ * into `bins` (<= 8192) int32 counters in HOST memory.  Waits for the stream; cannot be
+ * captured into a graph. */
+int mb_histogram_f32(mb_context *ctx, const float *in, int64_t size, float min_v,
+                     float max_v, int bins, int32_t *host_counts);
 
 /* ---- The pixels a strided 1x1 convolution reads, gathered once.  No operator
  * of its own in the reference: arm::Conv2dGeneral / ref::Conv2d index the input
@@ -375,7 +409,8 @@ int mb_transpose2d_batched(mb_context *ctx, const void *in, void *out,
  * and needs no mb_context; work is enqueued on `stream` (a cudaStream_t, may
  * be NULL) of the CURRENT device.
  *  - Limits: M, N <= MB_STATIC_SCRATCH_MAX_DIM; operands 16-byte aligned; K
- *    and each operand's contiguous dimension a multiple of 16; K <= 33000.
+ *    and each operand's contiguous dimension a multiple of 16; K <= 33000;
+ *    zero points in 0..255.
  *    Anything else is rejected with MB_INVALID_ARGS / MB_UNSUPPORTED and a
  *    message in error_message (may be NULL).
  *  - The first call on each device looks up the array's device address
@@ -393,6 +428,17 @@ int mb_gemm_u8_static_scratch(void *stream, const uint8_t *A, const uint8_t *B,
                               int32_t multiplier, int32_t right_shift,
                               int32_t zp_c, int bias_per_row,
                               char *error_message, size_t error_message_len);
+
+/* No counterpart in the reference.  The kernel behind mb_gemm_u8_static_scratch
+ * bounds its waits; if one runs out it records a non-zero code in a status word
+ * of the static array and stops early, leaving C incomplete.  That call itself
+ * still returns MB_SUCCESS (the kernel runs later), so a caller that wants to
+ * know asks here: the status word of the last call on the current device is
+ * copied into *host_status by an asynchronous copy enqueued on `stream` (no
+ * allocation).  Synchronize the stream, then read: 0 = the last GEMM ran to
+ * completion; 1 / 2 / 3 = its TMA producer / MMA issuer / epilogue gave up
+ * waiting.  The next mb_gemm_u8_static_scratch call clears the word. */
+int mb_gemm_u8_static_scratch_status(void *stream, int *host_status);
 
 #ifdef __cplusplus
 }

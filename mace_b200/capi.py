@@ -95,6 +95,11 @@ PROTOTYPES = {
     "mb_subsample_f32_nchw": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int]),
     "mb_gemm_u8_static_scratch": (_int, [_vp] * 5 + [_int] + [_i64] * 3 + [_int] * 2 +
                                   [_i32] * 5 + [_int, C.c_char_p, _sz]),
+    "mb_gemm_u8_static_scratch_status": (_int, [_vp, C.POINTER(_int)]),
+    "mb_histogram_f32": (_int, [_vp, _vp, _i64, _f32, _f32, _int, C.POINTER(_i32)]),
+    "mb_set_runtime_failure_ratio": (_int, [_f32]),
+    "mb_should_mock_runtime_failure": (_int, []),
+    "mb_wait_timeout_selftest": (_int, [_vp, C.c_longlong, C.POINTER(C.c_longlong)]),
 }
 
 _lib = None

@@ -52,6 +52,10 @@ struct mb_context {
   int pdl_chain = 1;             // kernels of an operator chain launched with programmatic stream
                                  // serialization (each waits for its predecessor where it first
                                  // touches global memory); 0: plain stream order
+  uint64_t dw_prepack_mark = ~0ull;  // value of `launches` right after the last depthwise prepack
+                                 // kernel: while they are equal that kernel is the newest one in
+                                 // the stream and the depthwise kernel may not read the tap words
+                                 // before it has waited for its predecessor
   int dw_waves = 1;              // depthwise 3x3: rounds of resident blocks the grid is sized for
   int wino_plane = 1;            // plane-at-a-time Winograd output transform (0: per-tile kernel)
   int64_t col_budget_bytes = 1ll << 30;  // im2col column matrix of the fp32 general convolution:

@@ -2,7 +2,9 @@
 // stream copies and synchronisation.  It plays the role that CpuRuntime and
 // its allocator play for the CPU path (mace/runtimes/cpu/cpu_runtime.cc:28-109)
 // for a CUDA device.
+#include <atomic>
 #include <cstdarg>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -113,10 +115,52 @@ const char *mb_last_error(const mb_context *ctx) {
   return ctx ? ctx->last_error : "null context";
 }
 
+// ---- allocator fault injection ------------------------------------------------------------
+// The reference's allocators fail at random when MACE_RUNTIME_FAILURE_RATIO is set
+// (ShouldMockRuntimeFailure, mace/core/runtime_failure_mock.cc:25-53, called at the top of every
+// allocator's New(), e.g. mace/runtimes/cpu/cpu_ref_allocator.cc:33), so that callers' handling
+// of MACE_OUT_OF_RESOURCES can be exercised.  The same switch here: the ratio comes from the
+// environment variable, read once, unless mb_set_runtime_failure_ratio has set it.
+namespace {
+std::atomic<float> g_failure_ratio{-1.f};   // < 0: not decided yet (read the environment)
+std::atomic<uint64_t> g_failure_draws{0x9e3779b97f4a7c15ull};
+
+float failure_ratio() {
+  float r = g_failure_ratio.load();
+  if (r < 0.f) {
+    const char *env = getenv("MACE_RUNTIME_FAILURE_RATIO");
+    r = env != nullptr ? static_cast<float>(atof(env)) : 0.f;
+    if (!(r >= 0.f)) r = 0.f;
+    g_failure_ratio.store(r);
+  }
+  return r;
+}
+}  // namespace
+
+int mb_set_runtime_failure_ratio(float ratio) {
+  if (!(ratio >= 0.f && ratio <= 1.f)) return MB_INVALID_ARGS;
+  g_failure_ratio.store(ratio);
+  return MB_SUCCESS;
+}
+
+int mb_should_mock_runtime_failure(void) {
+  const float ratio = failure_ratio();
+  if (!(ratio > 1e-6f)) return 0;
+  // one draw of a 64-bit mixing generator per call; thread-safe through the atomic counter
+  uint64_t z = g_failure_draws.fetch_add(0x9e3779b97f4a7c15ull);
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  z ^= z >> 31;
+  const float u = static_cast<float>(z >> 40) * (1.0f / 16777216.0f);  // [0, 1)
+  return u < ratio ? 1 : 0;
+}
+
 int mb_malloc(mb_context *ctx, size_t bytes, void **dptr) {
   if (ctx == nullptr || dptr == nullptr) return MB_INVALID_ARGS;
   *dptr = nullptr;
   if (bytes == 0) return MB_SUCCESS;
+  if (mb_should_mock_runtime_failure())
+    return mb_fail(ctx, MB_OUT_OF_RESOURCES, "mb_malloc: mock runtime failure (MACE_RUNTIME_FAILURE_RATIO)");
   MB_CUDA(ctx, cudaSetDevice(ctx->device));
   MB_CUDA(ctx, cudaMalloc(dptr, bytes));
   return MB_SUCCESS;
@@ -242,7 +286,11 @@ int mb_event_create(mb_context *ctx, void **event) {
 
 int mb_event_record(mb_context *ctx, void *event) {
   if (ctx == nullptr || event == nullptr) return MB_INVALID_ARGS;
-  MB_CUDA(ctx, cudaEventRecord(static_cast<cudaEvent_t>(event), ctx->stream));
+  // Inside a graph capture the record becomes an event-record NODE of the graph (the "external"
+  // flag), so that replays of the graph stamp the event and the time between two such nodes can
+  // be read after a replay has finished.
+  MB_CUDA(ctx, cudaEventRecordWithFlags(static_cast<cudaEvent_t>(event), ctx->stream,
+                                        ctx->capturing ? cudaEventRecordExternal : cudaEventRecordDefault));
   return MB_SUCCESS;
 }
 

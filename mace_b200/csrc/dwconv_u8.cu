@@ -221,8 +221,10 @@ dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows
                     int segments, int weights_cached) {
   constexpr int COLS = STRIDE == 1 ? 6 : 9;
   mb_grid_dep_launch();
-  // (packed weights cached by the caller were written long ago: they are fetched before the
-  // wait for the previous kernel, whose output is this kernel's input)
+  // weights_cached: the tap words were complete before the kernel in front of this one started
+  // (the host checks that the prepack kernel is not that kernel), so they may be fetched before
+  // the wait for the previous kernel, whose output is this kernel's input.  Otherwise only the
+  // wait makes the predecessor's writes visible.
   if (!weights_cached) mb_grid_dep_wait();
   const int groups = p.C >> 2;
   const int strips = (p.Wo + 3) >> 2;
@@ -430,7 +432,11 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
   if (fast) {
     const int64_t groups = C / 4;
     const uint4 *packed = static_cast<const uint4 *>(prepacked);
-    const int weights_cached = packed != nullptr ? 1 : 0;
+    // A caller's tap words may be read ahead of the wait for the previous kernel only when the
+    // kernel that wrote them is not that previous kernel: after a (re)pack through this context
+    // at least one other kernel must have been launched.  (A copy into the buffer is a full
+    // barrier in the stream and needs no care.)
+    const int weights_cached = (packed != nullptr && ctx->launches != ctx->dw_prepack_mark) ? 1 : 0;
     if (packed == nullptr) {  // no cached copy: prepare the weight words in scratch
       uint4 *fresh = nullptr;
       MB_RETURN_IF_ERROR(mb_scratch(ctx, sizeof(uint4) * DW_PACK_ITEMS * groups,
@@ -531,6 +537,7 @@ int mb_dwconv3x3_u8_prepack(mb_context *ctx, const uint8_t *filter_hwim, const i
       filter_hwim, bias, static_cast<uint4 *>(prepacked), static_cast<int>(C), zp_in, zp_f);
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
+  ctx->dw_prepack_mark = ctx->launches;
   return MB_SUCCESS;
 }
 

@@ -45,6 +45,10 @@ constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
 uint32_t *g_scratch_addr[kMaxDevices] = {nullptr};  // device address per GPU
 int g_num_sms[kMaxDevices] = {0};
+// kernels whose shared-memory limit was already raised on each GPU (the launcher sets the
+// attribute once per device and kernel variant and records it in its context; the per-call
+// context view below carries this mask in and out so that later calls skip the attribute call)
+uint64_t g_func_attr_mask[kMaxDevices] = {0};
 void *g_encode_tiled = nullptr;
 
 // Sum of each row of a [rows x len] byte matrix (len % 16 == 0): one warp per
@@ -156,6 +160,14 @@ extern "C" int mb_gemm_u8_static_scratch(void *stream, const uint8_t *A, const u
     snprintf(err, err_len, "bad multiplier %d / shift %d", multiplier, right_shift);
     return MB_INVALID_ARGS;
   }
+  if (!out_is_int32 && (zp_c < 0 || zp_c > 255)) {
+    snprintf(err, err_len, "output zero point %d outside uint8", zp_c);
+    return MB_INVALID_ARGS;
+  }
+  if (zp_a < 0 || zp_a > 255 || zp_b < 0 || zp_b > 255) {
+    snprintf(err, err_len, "operand zero points %d / %d outside uint8", zp_a, zp_b);
+    return MB_INVALID_ARGS;
+  }
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
     snprintf(err, err_len, "no current CUDA device");
@@ -173,6 +185,10 @@ extern "C" int mb_gemm_u8_static_scratch(void *stream, const uint8_t *A, const u
   view.stream = static_cast<cudaStream_t>(stream);
   view.encode_tiled = g_encode_tiled;
   view.dev_status = reinterpret_cast<int *>(scratch + 2 * kMaxDim);
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    view.func_attr_mask = g_func_attr_mask[device];
+  }
 
   const bool a_mn = a_col_major != 0, b_mn = b_col_major == 0;
   if (!mb_gemm_u8_tc_supported(&view, A, B, M, N, K, a_mn, b_mn, 0, 0) || K % 16 != 0) {
@@ -212,5 +228,34 @@ extern "C" int mb_gemm_u8_static_scratch(void *stream, const uint8_t *A, const u
                             N, K, a_mn, b_mn, 0, 0, zp_a, zp_b, multiplier, right_shift, zp_c,
                             bias_per_row);
   if (st != MB_SUCCESS) snprintf(err, err_len, "%s", view.last_error);
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    g_func_attr_mask[device] |= view.func_attr_mask;
+  }
   return st;
+}
+
+// The GEMM kernel bounds every wait on a barrier; when one runs out it writes a non-zero code
+// into its status word, stops, and leaves C partly written.  mb_gemm_u8 reports that through
+// mb_stream_sync; this entry point has no context to sync, so the caller asks here: the word
+// of the LAST call on the current device is copied into *host_status by an asynchronous copy
+// on `stream` (no allocation; pinned memory makes it truly asynchronous).  After the stream
+// has been synchronized, 0 means the last call ran to completion.
+extern "C" int mb_gemm_u8_static_scratch_status(void *stream, int *host_status) {
+  if (host_status == nullptr) return MB_INVALID_ARGS;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices)
+    return MB_RUNTIME_ERROR;
+  const uint32_t *scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    scratch = g_scratch_addr[device];
+  }
+  if (scratch == nullptr) {  // no call has run on this device yet
+    *host_status = 0;
+    return MB_SUCCESS;
+  }
+  const cudaError_t e = cudaMemcpyAsync(host_status, scratch + 2 * kMaxDim, sizeof(int),
+                                        cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? MB_SUCCESS : MB_RUNTIME_ERROR;
 }

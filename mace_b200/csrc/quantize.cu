@@ -72,6 +72,26 @@ minmax_f32_kernel(const float *__restrict__ in, int64_t size, int32_t *__restric
   }
 }
 
+// counts[clamp(int((x - min_v) / bin_v), 0, bins - 1)]++ with the division and subtraction
+// rounded as the host's float arithmetic rounds them; a block collects in shared memory first.
+__global__ void __launch_bounds__(256) histogram_f32_kernel(const float *__restrict__ in, int64_t size,
+                                                            float min_v, float bin_v, int bins,
+                                                            int32_t *__restrict__ counts) {
+  extern __shared__ int32_t local[];
+  for (int i = threadIdx.x; i < bins; i += blockDim.x) local[i] = 0;
+  __syncthreads();
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < size; i += stride) {
+    const float q = __fdiv_rn(__fsub_rn(__ldg(in + i), min_v), bin_v);
+    int index = q >= static_cast<float>(bins) ? bins - 1 : static_cast<int>(q);  // NaN -> 0
+    index = min(bins - 1, max(0, index));
+    atomicAdd(local + index, 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < bins; i += blockDim.x)
+    if (local[i] != 0) atomicAdd(counts + i, local[i]);
+}
+
 static unsigned stream_grid(const mb_context *ctx, int64_t work_items) {
   const int64_t blocks = ceil_div64(work_items, 256);
   return static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>(blocks, 16ll * ctx->num_sms)));
@@ -147,6 +167,31 @@ int mb_minmax_f32(mb_context *ctx, const float *in, int64_t size, float *host_mi
   MB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   *host_min = ordered_to_float(host[0]);
   *host_max = ordered_to_float(host[1]);
+  return MB_SUCCESS;
+}
+
+int mb_histogram_f32(mb_context *ctx, const float *in, int64_t size, float min_v, float max_v, int bins,
+                     int32_t *host_counts) {
+  if (ctx == nullptr) return MB_INVALID_ARGS;
+  if (size < 0 || bins < 1 || bins > 8192 || host_counts == nullptr || !(max_v > min_v))
+    return mb_fail(ctx, MB_INVALID_ARGS, "mb_histogram_f32: bad argument");
+  if (size >= (1ll << 31)) return mb_fail(ctx, MB_UNSUPPORTED, "mb_histogram_f32: more than 2^31 - 1 values");
+  memset(host_counts, 0, sizeof(int32_t) * bins);
+  if (size == 0) return MB_SUCCESS;
+  if (in == nullptr) return mb_fail(ctx, MB_INVALID_ARGS, "mb_histogram_f32: null operand");
+  if (ctx->capturing)
+    return mb_fail(ctx, MB_RUNTIME_ERROR, "mb_histogram_f32 reads its result on the host: not inside a graph capture");
+  MB_CUDA(ctx, cudaSetDevice(ctx->device));
+  int32_t *counts = nullptr;
+  MB_RETURN_IF_ERROR(mb_scratch(ctx, sizeof(int32_t) * bins, reinterpret_cast<void **>(&counts)));
+  MB_CUDA(ctx, cudaMemsetAsync(counts, 0, sizeof(int32_t) * bins, ctx->stream));
+  const float bin_v = (max_v - min_v) / static_cast<float>(bins);
+  histogram_f32_kernel<<<stream_grid(ctx, size), 256, sizeof(int32_t) * bins, ctx->stream>>>(in, size, min_v, bin_v,
+                                                                                            bins, counts);
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  MB_CUDA(ctx, cudaMemcpyAsync(host_counts, counts, sizeof(int32_t) * bins, cudaMemcpyDeviceToHost, ctx->stream));
+  MB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return MB_SUCCESS;
 }
 

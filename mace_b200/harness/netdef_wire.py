@@ -151,7 +151,10 @@ class NetDefWriter:
         if out_dtype is not None:
             od["output_type"] = [int(out_dtype)] * len(outputs)
         if out_quant:
-            od["quantize_info"] = [{"scale": float(q[0]), "zero_point": int(q[1])} for q in out_quant]
+            # (scale, zero_point) or (scale, zero_point, minval, maxval)
+            od["quantize_info"] = [dict({"scale": float(q[0]), "zero_point": int(q[1])},
+                                        **({"minval": float(q[2]), "maxval": float(q[3])} if len(q) == 4 else {}))
+                                   for q in out_quant]
         self.net["op"].append(od)
 
     # -- model outputs --

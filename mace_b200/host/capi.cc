@@ -5,10 +5,13 @@
 #include <exception>
 #include <map>
 #include <memory>
+#include <sstream>
 #include <string>
 #include <vector>
 
+#include "logging.h"
 #include "mace_engine.h"
+#include "multi_gpu.h"
 #include "ops.h"
 
 using namespace mace;  // NOLINT
@@ -153,6 +156,14 @@ int mbh_tensor_read(mbh_engine *e, const char *name, void *host_out, size_t byte
     return Fail(e, MaceStatus::MACE_INVALID_ARGS, "read larger than the tensor");
   MBH_TRY(e, e->runtime.Status(mb_memcpy_d2h(e->runtime.ctx(), host_out, t->memory<void>(), bytes)));
   MBH_TRY(e, e->runtime.Status(mb_stream_sync(e->runtime.ctx())));
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_tensor_device_ptr(mbh_engine *e, const char *name, void **device_ptr, size_t *bytes) {
+  Tensor *t = FindTensor(e, name);
+  if (t == nullptr || device_ptr == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  *device_ptr = t->mutable_memory<void>();
+  if (bytes != nullptr) *bytes = static_cast<size_t>(t->raw_size());
   return MaceStatus::MACE_SUCCESS;
 }
 
@@ -351,8 +362,28 @@ int mbh_wait_slot(mbh_engine *e, int slot) {
 int mbh_run_profiled(mbh_engine *e, float *ms_out, int max_ops, char *names_out, size_t names_len,
                      int *op_count) {
   if (e == nullptr || ms_out == nullptr || op_count == nullptr) return MaceStatus::MACE_INVALID_ARGS;
-  std::vector<CallStats> stats;
-  MBH_TRY(e, e->net->Run(&stats));
+  RunMetadata metadata;
+  MBH_TRY(e, e->net->Run(&metadata));
+  const std::vector<OperatorStats> &stats = metadata.op_stats;
+  *op_count = static_cast<int>(stats.size());
+  std::string names;
+  for (size_t i = 0; i < stats.size(); ++i) {
+    if (static_cast<int>(i) < max_ops) ms_out[i] = stats[i].device_ms;
+    names += stats[i].type + ":" + stats[i].operator_name + "\n";
+  }
+  if (names_out != nullptr && names_len > 0) {
+    std::strncpy(names_out, names.c_str(), names_len - 1);
+    names_out[names_len - 1] = 0;
+  }
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_run_profiled_graph(mbh_engine *e, int replays, float *ms_out, int max_ops, char *names_out,
+                           size_t names_len, int *op_count) {
+  if (e == nullptr || ms_out == nullptr || op_count == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  RunMetadata metadata;
+  MBH_TRY(e, e->net->RunProfiledGraph(&metadata, replays));
+  const std::vector<OperatorStats> &stats = metadata.op_stats;
   *op_count = static_cast<int>(stats.size());
   std::string names;
   for (size_t i = 0; i < stats.size(); ++i) {
@@ -397,10 +428,10 @@ int mbh_model_create(int device, const void *graph, size_t graph_len, const void
   if (model == nullptr) return MaceStatus::MACE_INVALID_ARGS;
   *model = nullptr;
   MaceEngineConfig config;
-  config.device = device;
-  config.fuse = fuse != 0;
-  config.plan_memory = plan_memory != 0;
-  config.cuda_graph = cuda_graph != 0;
+  config.SetRuntimeType(RuntimeType::RT_CUDA);
+  MaceStatus cfg = config.SetCudaDevice(device);
+  if (cfg != MaceStatus::MACE_SUCCESS) return static_cast<int>(cfg.code());
+  config.SetCudaNetOptimizations(fuse != 0, plan_memory != 0, cuda_graph != 0);
   auto m = std::make_unique<mbh_model>();
   MaceStatus st;
   try {  // no exception may cross the C boundary
@@ -465,6 +496,160 @@ int mbh_model_run(mbh_model *model, int n_inputs, const mbh_io_tensor *inputs, i
     if (shape.size() > 8) return MaceStatus::MACE_INVALID_ARGS;
     outputs[i].rank = static_cast<int>(shape.size());
     for (size_t k = 0; k < shape.size(); ++k) outputs[i].shape[k] = shape[k];
+  }
+  return MaceStatus::MACE_SUCCESS;
+}
+
+// ---- several GPUs ------------------------------------------------------------------------
+
+struct mbh_multi {
+  std::unique_ptr<MultiGpuRunner> runner;
+  std::string last_error;
+};
+
+int mbh_shard_bounds(int64_t total, int parts, int index, int64_t *begin, int64_t *end) {
+  if (begin == nullptr || end == nullptr || parts < 1 || index < 0 || index >= parts || total < 0)
+    return MaceStatus::MACE_INVALID_ARGS;
+  ShardBounds(total, parts, index, begin, end);
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_multi_create(int n_shards, const int *devices, const void *graph, size_t graph_len, const void *weights,
+                     size_t weights_len, int fuse, int plan_memory, int cuda_graph, mbh_multi **runner, char *error,
+                     size_t error_len) {
+  if (runner == nullptr || n_shards < 1 || devices == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  *runner = nullptr;
+  MaceEngineConfig config(RuntimeType::RT_CUDA);
+  config.SetCudaNetOptimizations(fuse != 0, plan_memory != 0, cuda_graph != 0);
+  auto m = std::make_unique<mbh_multi>();
+  MaceStatus st;
+  try {
+    st = MultiGpuRunner::Create(std::vector<int>(devices, devices + n_shards),
+                                static_cast<const unsigned char *>(graph), graph_len,
+                                static_cast<const unsigned char *>(weights), weights_len, config, &m->runner);
+  } catch (const std::exception &ex) {
+    st = MaceStatus(MaceStatus::MACE_OUT_OF_RESOURCES, std::string("exception while loading the model: ") + ex.what());
+  }
+  if (st != MaceStatus::MACE_SUCCESS) {
+    if (error != nullptr && error_len > 0) {
+      std::strncpy(error, st.information().c_str(), error_len - 1);
+      error[error_len - 1] = 0;
+    }
+    return static_cast<int>(st.code());
+  }
+  *runner = m.release();
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_multi_destroy(mbh_multi *runner) {
+  if (runner == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  delete runner;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+const char *mbh_multi_last_error(const mbh_multi *runner) { return runner ? runner->last_error.c_str() : "null runner"; }
+
+int mbh_multi_shards(const mbh_multi *runner) { return runner ? runner->runner->shards() : 0; }
+
+int mbh_multi_run(mbh_multi *runner, int n_inputs, const mbh_io_tensor *inputs, int n_outputs,
+                  mbh_io_tensor *outputs) {
+  if (runner == nullptr || n_inputs < 1 || n_outputs < 1 || inputs == nullptr || outputs == nullptr)
+    return MaceStatus::MACE_INVALID_ARGS;
+  auto no_delete = [](void *) {};
+  std::map<std::string, MaceTensor> in, out;
+  for (int i = 0; i < n_inputs; ++i) {
+    const mbh_io_tensor &t = inputs[i];
+    if (t.name == nullptr || t.rank < 1 || t.rank > 8) return MaceStatus::MACE_INVALID_ARGS;
+    in[t.name] = MaceTensor(std::vector<int64_t>(t.shape, t.shape + t.rank), std::shared_ptr<void>(t.data, no_delete),
+                            static_cast<DataFormat>(t.data_format), static_cast<IDataType>(t.data_type));
+  }
+  for (int i = 0; i < n_outputs; ++i) {
+    const mbh_io_tensor &t = outputs[i];
+    if (t.name == nullptr || t.rank < 1 || t.rank > 8) return MaceStatus::MACE_INVALID_ARGS;
+    out[t.name] = MaceTensor(std::vector<int64_t>(t.shape, t.shape + t.rank), std::shared_ptr<void>(t.data, no_delete),
+                             static_cast<DataFormat>(t.data_format), static_cast<IDataType>(t.data_type));
+  }
+  MaceStatus st;
+  try {
+    st = runner->runner->Run(in, &out);
+  } catch (const std::exception &ex) {
+    st = MaceStatus(MaceStatus::MACE_OUT_OF_RESOURCES, std::string("exception while running the model: ") + ex.what());
+  }
+  if (st != MaceStatus::MACE_SUCCESS) {
+    runner->last_error = st.information();
+    return static_cast<int>(st.code());
+  }
+  for (int i = 0; i < n_outputs; ++i) {
+    const std::vector<int64_t> &shape = out[outputs[i].name].shape();
+    if (shape.size() > 8) return MaceStatus::MACE_INVALID_ARGS;
+    outputs[i].rank = static_cast<int>(shape.size());
+    for (size_t k = 0; k < shape.size(); ++k) outputs[i].shape[k] = shape[k];
+  }
+  return MaceStatus::MACE_SUCCESS;
+}
+
+// ---- logging -----------------------------------------------------------------------------
+
+int mbh_set_log_sink(mbh_log_sink sink) {
+  SetLogSink(sink);
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_set_vlog_level(int level) {
+  SetVLogLevelForTest(level);
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_vlog_is_on(int level) { return ShouldGenerateVLogMessage(level) ? 1 : 0; }
+
+int mbh_log(int severity, const char *message) {
+  if (message == nullptr || severity < INFO || severity > ERROR) return MaceStatus::MACE_INVALID_ARGS;
+  Logger(__FILE__, __LINE__, static_cast<LogLevel>(severity)) << message;
+  return MaceStatus::MACE_SUCCESS;
+}
+
+int mbh_model_run_metadata(mbh_model *model, char *json_out, size_t capacity, size_t *needed) {
+  if (model == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  RunMetadata md;
+  MaceStatus st = model->engine->net()->Run(&md);
+  if (st == MaceStatus::MACE_SUCCESS) st = model->engine->runtime()->Status(mb_stream_sync(model->engine->runtime()->ctx()));
+  if (st != MaceStatus::MACE_SUCCESS) {
+    model->last_error = st.information();
+    return static_cast<int>(st.code());
+  }
+  std::ostringstream ss;
+  auto list = [&ss](const auto &v) {
+    ss << "[";
+    for (size_t i = 0; i < v.size(); ++i) ss << (i ? "," : "") << v[i];
+    ss << "]";
+  };
+  ss << "[";
+  for (size_t i = 0; i < md.op_stats.size(); ++i) {
+    const OperatorStats &o = md.op_stats[i];
+    ss << (i ? "," : "") << "{\"name\":\"" << o.operator_name << "\",\"type\":\"" << o.type
+       << "\",\"device_ms\":" << o.device_ms << ",\"start_micros\":" << o.stats.start_micros
+       << ",\"end_micros\":" << o.stats.end_micros << ",\"output_shape\":[";
+    for (size_t k = 0; k < o.output_shape.size(); ++k) {
+      ss << (k ? "," : "");
+      list(o.output_shape[k]);
+    }
+    ss << "],\"strides\":";
+    list(o.args.strides);
+    ss << ",\"padding_type\":" << o.args.padding_type << ",\"paddings\":";
+    list(o.args.paddings);
+    ss << ",\"dilations\":";
+    list(o.args.dilations);
+    ss << ",\"kernels\":";
+    list(o.args.kernels);
+    ss << "}";
+  }
+  ss << "]";
+  const std::string text = ss.str();
+  if (needed != nullptr) *needed = text.size() + 1;
+  if (json_out != nullptr && capacity > 0) {
+    const size_t n = std::min(capacity - 1, text.size());
+    std::memcpy(json_out, text.data(), n);
+    json_out[n] = 0;
   }
   return MaceStatus::MACE_SUCCESS;
 }

@@ -38,6 +38,10 @@ int mbh_tensor_quant(mbh_engine *engine, const char *name, float *scale, int32_t
 /* Synchronous copies between a tensor and host memory. */
 int mbh_tensor_read(mbh_engine *engine, const char *name, void *host_out, size_t bytes);
 int mbh_tensor_write(mbh_engine *engine, const char *name, const void *host_in, size_t bytes);
+/* The tensor's device address and size after the last run (Tensor::memory<T>(),
+ * mace/core/memory/buffer.h:41-59), for a caller that hands it to another library on the same
+ * stream -- the final gather of the output rows, for one.  Valid until the tensor is resized. */
+int mbh_tensor_device_ptr(mbh_engine *engine, const char *name, void **device_ptr, size_t *bytes);
 
 /* Operator construction, the fields of an OperatorDef (mace/proto/mace.proto:61-95). */
 int mbh_op_begin(mbh_engine *engine, const char *type, const char *name);
@@ -102,6 +106,12 @@ int mbh_run_host(mbh_engine *engine, const char *input_name, const void *host_in
 int mbh_run_profiled(mbh_engine *engine, float *ms_out, int max_ops, char *names_out,
                      size_t names_len, int *op_count);
 
+/* The same inside a graph replay (SerialNet::RunProfiledGraph): the operators are recorded into
+ * a graph with an event node behind each and the graph is replayed `replays` times; the times
+ * add up to the graph's duration. */
+int mbh_run_profiled_graph(mbh_engine *engine, int replays, float *ms_out, int max_ops, char *names_out,
+                           size_t names_len, int *op_count);
+
 /* ---- Model files: the serialized NetDef of a converted model (mace/proto/mace.proto) and its
  * weights blob, loaded and run the way CreateMaceEngineFromProto / MaceEngine::Run do
  * (include/mace/public/mace.h:553-655). ---- */
@@ -142,6 +152,49 @@ void *mbh_model_context(mbh_model *model);
 int mbh_model_captured(mbh_model *model);
 int mbh_model_run(mbh_model *model, int n_inputs, const mbh_io_tensor *inputs, int n_outputs,
                   mbh_io_tensor *outputs);
+
+/* ---- Several GPUs: one engine, stream and host thread per shard (MultiGpuRunner); the batch
+ * (first dimension of every input and output) is split into contiguous shards, each shard's
+ * output rows are copied device-to-host straight into its slice of the caller's buffer.  The
+ * reference runs one net on one device (mace/core/net/serial_net.cc:103-124) and allows several
+ * engines in parallel threads (test/ccunit/mace/libmace/mace_api_mt_test.cc:100-110). ---- */
+
+/* Shard `index` of `parts` over `total` items (contiguous, the first total % parts shards one
+ * longer).  Needs no GPU. */
+int mbh_shard_bounds(int64_t total, int parts, int index, int64_t *begin, int64_t *end);
+
+typedef struct mbh_multi mbh_multi;
+
+/* devices[i]: CUDA ordinal of shard i (ordinals may repeat).  The other arguments as for
+ * mbh_model_create. */
+int mbh_multi_create(int n_shards, const int *devices, const void *graph, size_t graph_len, const void *weights,
+                     size_t weights_len, int fuse, int plan_memory, int cuda_graph, mbh_multi **runner, char *error,
+                     size_t error_len);
+int mbh_multi_destroy(mbh_multi *runner);
+const char *mbh_multi_last_error(const mbh_multi *runner);
+int mbh_multi_shards(const mbh_multi *runner);
+/* As mbh_model_run, on the whole batch. */
+int mbh_multi_run(mbh_multi *runner, int n_inputs, const mbh_io_tensor *inputs, int n_outputs,
+                  mbh_io_tensor *outputs);
+
+/* ---- Logging (MACE_CPP_MIN_LOG_LEVEL, MACE_CPP_MIN_VLOG_LEVEL: include/mace/port/logger.h:40-58).
+ * Lines go to stderr unless a sink is installed (NULL restores stderr); the sink is called from
+ * whichever thread logs.  mbh_set_vlog_level overrides the environment's VLOG level
+ * (INT_MIN: back to the environment).  mbh_log writes one line at `severity` (1 INFO, 2 WARNING,
+ * 3 ERROR) through the same path; mbh_vlog_is_on answers what VLOG(level) would do.  No GPU
+ * needed. ---- */
+typedef void (*mbh_log_sink)(int severity, const char *line);
+int mbh_set_log_sink(mbh_log_sink sink);
+int mbh_set_vlog_level(int level);
+int mbh_vlog_is_on(int level);
+int mbh_log(int severity, const char *message);
+
+/* Per-operator statistics of one run of a model (RunMetadata, include/mace/public/mace.h:177-201)
+ * as JSON: [{"name":..,"type":..,"device_ms":..,"start_micros":..,"end_micros":..,
+ * "output_shape":[[..]],"strides":[..],"padding_type":..,"paddings":[..],"dilations":[..],
+ * "kernels":[..]}, ...].  The inputs already on the device from the last mbh_model_run are
+ * used.  json_out is always NUL-terminated; *needed (may be NULL) receives the full length. */
+int mbh_model_run_metadata(mbh_model *model, char *json_out, size_t capacity, size_t *needed);
 
 #ifdef __cplusplus
 }

@@ -109,6 +109,14 @@ class MaceStatus {
     }                                                                             \
   } while (0)
 #define MACE_CHECK_NOTNULL(ptr) MACE_CHECK((ptr) != nullptr)
+// An operator whose delegator key has no registration reports it instead of aborting.
+#define MACE_RETURN_IF_NO_DELEGATOR(ptr, workspace)                                              \
+  do {                                                                                           \
+    if ((ptr) == nullptr)                                                                        \
+      return ::mace::MaceStatus(::mace::MaceStatus::MACE_UNSUPPORTED,                            \
+                                "no delegator registered for " +                                 \
+                                    (workspace)->GetDelegatorRegistry()->last_missing());        \
+  } while (0)
 #define MACE_UNUSED(x) (void)(x)
 
 // ---- Runtime ------------------------------------------------------------------
@@ -286,11 +294,16 @@ class OpDelegatorRegistry {
     general.tag = "general";
     it = registry_.find(general.ToString());
     if (it != registry_.end()) return it->second;
-    std::fprintf(stderr, "Delegator not exist: %s\n", key.ToString().c_str());
-    std::abort();
+    // Unknown key: an empty creator.  Delegator::Create then returns null and the operator
+    // reports MACE_UNSUPPORTED (the reference aborts here, op_delegator_registry.cc:64-102;
+    // behind a C boundary that would take the caller's process down).
+    last_missing_ = key.ToString();
+    return DelegatorCreator();
   }
+  const std::string &last_missing() const { return last_missing_; }
 
  private:
+  mutable std::string last_missing_;
   std::unordered_map<std::string, DelegatorCreator> registry_;
 };
 
@@ -323,6 +336,7 @@ class Workspace {
                                             const ::mace::DelegatorInfo &key,              \
                                             const ::mace::DelegatorParam &param) {         \
     ::mace::DelegatorCreator creator = workspace->GetDelegatorRegistry()->GetCreator(key); \
+    if (!creator) return nullptr;                                                          \
     std::unique_ptr<::mace::OpDelegator> delegator = creator(param);                       \
     return std::unique_ptr<class_name>(static_cast<class_name *>(delegator.release()));    \
   }

@@ -17,7 +17,20 @@
 namespace mace {
 namespace ops {
 
-enum ConvType { K1x1, K3x3S1, K3x3S2, K3x3Winograd };
+enum ConvType {  // mace/ops/delegator/conv_2d.h:28-41, the same values
+  K1x1,
+  K1x7S1,
+  K7x1S1,
+  K1x15S1,
+  K15x1S1,
+  K3x3S1,
+  K3x3S2,
+  K3x3Winograd,
+  K5x5S1,
+  K7x7S1,
+  K7x7S2,
+  K7x7S3,
+};
 
 enum ActivationType {  // mace/ops/common/activation_type.h:21-31
   NOOP = 0, RELU = 1, RELUX = 2, PRELU = 3, TANH = 4, SIGMOID = 5, LEAKYRELU = 6, ELU = 7,

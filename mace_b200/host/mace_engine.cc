@@ -125,7 +125,9 @@ MaceStatus MaceEngine::Init(const proto::NetDef *net_def, const std::vector<std:
     if (output_info_.count(name) == 0)
       return Invalid("'" + name + "' does not belong to model's outputs: " + Keys(output_info_));
 
-  MACE_RETURN_IF_ERROR(runtime_.Init(config_.device));
+  if (config_.runtime_type() != RuntimeType::RT_CUDA)
+    return MaceStatus(MaceStatus::MACE_UNSUPPORTED, "this engine runs RuntimeType::RT_CUDA only (no fallback)");
+  MACE_RETURN_IF_ERROR(runtime_.Init(config_.device()));
   ops::RegisterAllCudaOpDelegators(workspace_.GetDelegatorRegistry());
   ops::RegisterAllCudaOps(&op_registry_);
   net_ = std::make_unique<SerialNet>(&op_registry_, &workspace_, &runtime_);
@@ -157,13 +159,13 @@ MaceStatus MaceEngine::Init(const proto::NetDef *net_def, const std::vector<std:
   }
   for (const auto &kv : output_info_)
     if (!workspace_.HasTensor(kv.first)) return Invalid("no operator produces the model output " + kv.first);
-  if (config_.fuse) net_->ShareSubsampledInputs();
+  if (config_.fuse()) net_->ShareSubsampledInputs();
   initialised_ = true;
   return MaceStatus::MACE_SUCCESS;
 }
 
 MaceStatus MaceEngine::Run(const std::map<std::string, MaceTensor> &inputs, std::map<std::string, MaceTensor> *outputs,
-                           std::vector<CallStats> *run_metadata) {
+                           RunMetadata *run_metadata) {
   if (!initialised_) return Invalid("the engine is not initialised");
   if (outputs == nullptr) return Invalid("null outputs");
   mb_context *ctx = runtime_.ctx();
@@ -219,7 +221,7 @@ MaceStatus MaceEngine::Run(const std::map<std::string, MaceTensor> &inputs, std:
       return Invalid("'" + out.first + "' does not belong to model's outputs: " + Keys(output_info_));
 
   // ---- the net ----
-  if (config_.cuda_graph && !graph_failed_ && !net_->captured() && plain_runs_ >= 1 && run_metadata == nullptr) {
+  if (config_.cuda_graph() && !graph_failed_ && !net_->captured() && plain_runs_ >= 1 && run_metadata == nullptr) {
     if (net_->Capture() != MaceStatus::MACE_SUCCESS) graph_failed_ = true;  // an operator that must wait for the host
   }
   MACE_RETURN_IF_ERROR(net_->Run(run_metadata));
@@ -230,12 +232,12 @@ MaceStatus MaceEngine::Run(const std::map<std::string, MaceTensor> &inputs, std:
     // operator reads it too, so that it can be read back after the run
     std::set<std::string> keep;
     for (const auto &kv : output_info_) keep.insert(kv.first);
-    if (config_.fuse) {
+    if (config_.fuse()) {
       net_->FuseActivations(&keep);
       net_->FuseResidualSums(&keep);
       plain_runs_ = 0;
     }
-    if (config_.plan_memory) {
+    if (config_.plan_memory()) {
       MACE_RETURN_IF_ERROR(net_->PlanMemory(nullptr, nullptr, &keep));
       plain_runs_ = 0;
     }
@@ -296,7 +298,10 @@ MaceStatus CreateMaceEngineFromProto(const unsigned char *model_graph_proto, siz
                                      const unsigned char *model_weights_data, size_t model_weights_data_size,
                                      const std::vector<std::string> &input_nodes,
                                      const std::vector<std::string> &output_nodes, const MaceEngineConfig &config,
-                                     std::shared_ptr<MaceEngine> *engine) {
+                                     std::shared_ptr<MaceEngine> *engine, bool *model_data_unused,
+                                     MaceEngine *tutor, bool fake_warmup) {
+  (void)tutor;
+  (void)fake_warmup;
   if (engine == nullptr) return Invalid("null engine pointer");
   if (model_graph_proto == nullptr || model_graph_proto_size == 0) return Invalid("empty model graph");
   proto::NetDef net_def;
@@ -305,6 +310,7 @@ MaceStatus CreateMaceEngineFromProto(const unsigned char *model_graph_proto, siz
   MACE_RETURN_IF_ERROR(e->Init(&net_def, input_nodes, output_nodes, model_weights_data,
                                static_cast<int64_t>(model_weights_data_size)));
   *engine = std::move(e);
+  if (model_data_unused != nullptr) *model_data_unused = true;
   return MaceStatus::MACE_SUCCESS;
 }
 

@@ -61,16 +61,68 @@ class MaceTensor {
   int64_t buffer_size_ = 0;
 };
 
-struct MaceEngineConfig {
-  int device = 0;
+// Hints of the reference's configuration class that this runtime accepts and ignores
+// (include/mace/public/mace.h:91-143): they steer CPU threads and mobile GPUs.
+enum GPUPerfHint { PERF_DEFAULT = 0, PERF_LOW = 1, PERF_NORMAL = 2, PERF_HIGH = 3 };
+enum GPUPriorityHint { PRIORITY_DEFAULT = 0, PRIORITY_LOW = 1, PRIORITY_NORMAL = 2, PRIORITY_HIGH = 3 };
+enum CPUAffinityPolicy {
+  AFFINITY_NONE = 0, AFFINITY_BIG_ONLY = 1, AFFINITY_LITTLE_ONLY = 2, AFFINITY_HIGH_PERFORMANCE = 3,
+  AFFINITY_POWER_SAVE = 4,
+};
+
+// The setters of include/mace/public/mace.h:372-499 that have a meaning for one CUDA device,
+// with the same names and return types, so that code configuring a MACE engine compiles against
+// this runtime: SetRuntimeType takes RT_CUDA (any other runtime makes Init fail with
+// MACE_UNSUPPORTED, there is no fallback), the CPU and GPU hints are accepted and have no
+// effect.  Additions for this runtime: the device ordinal and the three net-level switches.
+// Unlike the reference's class this one can be copied (one configuration for several engines).
+class MaceEngineConfig {
+ public:
+  MaceEngineConfig() = default;
+  explicit MaceEngineConfig(const RuntimeType runtime_type) : runtime_type_(runtime_type) {}
+
+  void SetRuntimeType(const RuntimeType runtime_type, const char *sub_graph_name = "default_graph") {
+    (void)sub_graph_name;  // one graph per model file
+    runtime_type_ = runtime_type;
+  }
+  MaceStatus SetGPUHints(GPUPerfHint perf_hint, GPUPriorityHint priority_hint) {
+    (void)perf_hint;
+    (void)priority_hint;
+    return MaceStatus::MACE_SUCCESS;
+  }
+  MaceStatus SetCPUThreadPolicy(int num_threads_hint, CPUAffinityPolicy policy) {
+    (void)num_threads_hint;
+    (void)policy;
+    return MaceStatus::MACE_SUCCESS;
+  }
+  // ---- this runtime ----
+  MaceStatus SetCudaDevice(int ordinal) {
+    if (ordinal < 0) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "negative device ordinal");
+    device_ = ordinal;
+    return MaceStatus::MACE_SUCCESS;
+  }
   // After the first run: merge activations and residual sums into their producers
-  // (SerialNet::FuseActivations / FuseResidualSums) ...
-  bool fuse = false;
-  // ... share activation memory (SerialNet::PlanMemory) ...
-  bool plan_memory = false;
-  // ... and record the operator chain into a CUDA graph that later runs with unchanged
-  // input shapes replay.
-  bool cuda_graph = false;
+  // (SerialNet::FuseActivations / FuseResidualSums), share activation memory
+  // (SerialNet::PlanMemory), and record the operator chain into a CUDA graph that later runs
+  // with unchanged input shapes replay.
+  MaceStatus SetCudaNetOptimizations(bool fuse, bool plan_memory, bool cuda_graph) {
+    fuse_ = fuse;
+    plan_memory_ = plan_memory;
+    cuda_graph_ = cuda_graph;
+    return MaceStatus::MACE_SUCCESS;
+  }
+  RuntimeType runtime_type() const { return runtime_type_; }
+  int device() const { return device_; }
+  bool fuse() const { return fuse_; }
+  bool plan_memory() const { return plan_memory_; }
+  bool cuda_graph() const { return cuda_graph_; }
+
+ private:
+  RuntimeType runtime_type_ = RuntimeType::RT_CUDA;
+  int device_ = 0;
+  bool fuse_ = false;
+  bool plan_memory_ = false;
+  bool cuda_graph_ = false;
 };
 
 class MaceEngine {
@@ -85,8 +137,10 @@ class MaceEngine {
   MaceStatus Init(const proto::NetDef *net_def, const std::vector<std::string> &input_nodes,
                   const std::vector<std::string> &output_nodes, const unsigned char *model_data,
                   int64_t model_data_size);
+  // include/mace/public/mace.h:603-607; run_metadata (may be null) receives one OperatorStats per
+  // operator, timed with device events.
   MaceStatus Run(const std::map<std::string, MaceTensor> &inputs, std::map<std::string, MaceTensor> *outputs,
-                 std::vector<CallStats> *run_metadata = nullptr);
+                 RunMetadata *run_metadata = nullptr);
 
   const proto::NetDef &net_def() const { return net_def_; }
   bool is_quantized_model() const { return quantized_; }
@@ -115,11 +169,16 @@ class MaceEngine {
 };
 
 // include/mace/public/mace.h:644-655: parses the graph, builds and initialises an engine.
+// *model_data_unused (may be null) is set to true: every constant tensor is copied to the device
+// during Init, so the caller may release the weights blob.  tutor (an engine whose runtimes the
+// new one would share) and fake_warmup (an OpenCL start-up aid) are accepted and have no effect:
+// every engine of this runtime owns its stream and memory.
 MaceStatus CreateMaceEngineFromProto(const unsigned char *model_graph_proto, size_t model_graph_proto_size,
                                      const unsigned char *model_weights_data, size_t model_weights_data_size,
                                      const std::vector<std::string> &input_nodes,
                                      const std::vector<std::string> &output_nodes, const MaceEngineConfig &config,
-                                     std::shared_ptr<MaceEngine> *engine);
+                                     std::shared_ptr<MaceEngine> *engine, bool *model_data_unused = nullptr,
+                                     MaceEngine *tutor = nullptr, bool fake_warmup = false);
 
 }  // namespace mace
 

@@ -577,6 +577,8 @@ void ConvertOperatorDef(const proto::OperatorDef &src, OperatorDef *dst) {
     QuantizeActivationInfo info;
     info.scale = q.scale;
     info.zero_point = q.zero_point;
+    info.minval = q.minval;
+    info.maxval = q.maxval;
     dst->quantize_info.push_back(info);
   }
 }

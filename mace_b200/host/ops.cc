@@ -1,5 +1,9 @@
 #include "ops.h"
 
+#include <sstream>
+
+#include "logging.h"
+
 #include <algorithm>
 #include <numeric>
 #include <set>
@@ -151,6 +155,7 @@ class Conv2dOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase {
           workspace_, MACE_DELEGATOR_KEY(Conv2d, RuntimeType::RT_CUDA, uint8_t, ImplType::CUDA),
           delegator::Conv2dParam(strides_, dilations_, paddings_, padding_type_));
     }
+    MACE_RETURN_IF_NO_DELEGATOR(conv2d_delegator_, workspace_);
     conv2d_delegator_->SetBias(bias);
     return conv2d_delegator_->Compute(context, input, filter, Output(0));
   }
@@ -209,6 +214,7 @@ class Conv2dOp<RuntimeType::RT_CUDA, float> : public ConvPool2dOpBase {
             workspace_, MACE_DELEGATOR_KEY(Conv2d, RuntimeType::RT_CUDA, float, ImplType::CUDA), param);
       }
     }
+    MACE_RETURN_IF_NO_DELEGATOR(conv2d_delegator_, workspace_);
     conv2d_delegator_->SetBias(bias);
     if (residual_ != nullptr) {
       conv2d_delegator_->SetActivation(sum_.activation, sum_.max_limit, sum_.coefficient);
@@ -280,6 +286,7 @@ class DepthwiseConv2dOp<RuntimeType::RT_CUDA, float> : public ConvPool2dOpBase {
           workspace_, MACE_DELEGATOR_KEY(DepthwiseConv2d, RuntimeType::RT_CUDA, float, ImplType::CUDA),
           delegator::DepthwiseConv2dParam(strides_, dilations_, paddings_, padding_type_));
     }
+    MACE_RETURN_IF_NO_DELEGATOR(delegator_, workspace_);
     delegator_->SetBias(bias);
     delegator_->SetActivation(act, max_limit_, coefficient_);
     return delegator_->Compute(context, input, filter, Output(0));
@@ -298,7 +305,7 @@ template <>
 class MatMulOp<RuntimeType::RT_CUDA, float> : public Operation {
  public:
   explicit MatMulOp(OpConstructContext *context)
-      : Operation(context),
+      : Operation(context), registry_workspace_(context->workspace()),
         transpose_a_(GetOptionalArg<bool>("transpose_a", false)),
         transpose_b_(GetOptionalArg<bool>("transpose_b", false)),
         gemm_(delegator::Gemm::Create(context->workspace(),
@@ -306,6 +313,7 @@ class MatMulOp<RuntimeType::RT_CUDA, float> : public Operation {
                                       delegator::GemmParam())) {}
 
   MaceStatus Run(OpContext *context) override {
+    MACE_RETURN_IF_NO_DELEGATOR(gemm_, registry_workspace_);
     const Tensor *lhs = Input(0), *rhs = Input(1);
     if (InputSize() >= 3) return MaceStatus(MaceStatus::MACE_UNSUPPORTED, "MatMul bias input");
     Tensor *C = Output(0);
@@ -342,6 +350,7 @@ class MatMulOp<RuntimeType::RT_CUDA, float> : public Operation {
   }
 
  private:
+  Workspace *registry_workspace_;
   bool transpose_a_, transpose_b_;
   std::unique_ptr<delegator::Gemm> gemm_;
 };
@@ -352,13 +361,14 @@ template <>
 class FullyConnectedOp<RuntimeType::RT_CUDA, float> : public Operation {
  public:
   explicit FullyConnectedOp(OpConstructContext *context)
-      : Operation(context),
+      : Operation(context), registry_workspace_(context->workspace()),
         activation_name_(GetOptionalArg<std::string>("activation", "NOOP")),
         gemv_(delegator::Gemv::Create(context->workspace(),
                                       MACE_DELEGATOR_KEY(Gemv, RuntimeType::RT_CUDA, float, ImplType::CUDA),
                                       DelegatorParam())) {}
 
   MaceStatus Run(OpContext *context) override {
+    MACE_RETURN_IF_NO_DELEGATOR(gemv_, registry_workspace_);
     const Tensor *input = Input(0), *weight = Input(1);
     const Tensor *bias = InputSize() >= 3 ? Input(2) : nullptr;
     Tensor *output = Output(0);
@@ -375,6 +385,7 @@ class FullyConnectedOp<RuntimeType::RT_CUDA, float> : public Operation {
   }
 
  private:
+  Workspace *registry_workspace_;
   std::string activation_name_;
   std::unique_ptr<delegator::Gemv> gemv_;
 };
@@ -394,6 +405,7 @@ class DepthwiseConv2dOp<RuntimeType::RT_CUDA, uint8_t> : public ConvPool2dOpBase
           workspace_, MACE_DELEGATOR_KEY(DepthwiseConv2d, RuntimeType::RT_CUDA, uint8_t, ImplType::CUDA),
           delegator::DepthwiseConv2dParam(strides_, dilations_, paddings_, padding_type_));
     }
+    MACE_RETURN_IF_NO_DELEGATOR(delegator_, workspace_);
     delegator_->SetBias(bias);
     return delegator_->Compute(context, input, filter, Output(0));
   }
@@ -407,7 +419,7 @@ template <>
 class MatMulOp<RuntimeType::RT_CUDA, uint8_t> : public Operation {
  public:
   explicit MatMulOp(OpConstructContext *context)
-      : Operation(context),
+      : Operation(context), registry_workspace_(context->workspace()),
         transpose_a_(GetOptionalArg<bool>("transpose_a", false)),
         transpose_b_(GetOptionalArg<bool>("transpose_b", false)),
         gemm_(delegator::Gemm::Create(
@@ -416,6 +428,7 @@ class MatMulOp<RuntimeType::RT_CUDA, uint8_t> : public Operation {
             delegator::GemmParam())) {}
 
   MaceStatus Run(OpContext *context) override {
+    MACE_RETURN_IF_NO_DELEGATOR(gemm_, registry_workspace_);
     const Tensor *lhs = Input(0), *rhs = Input(1);
     Tensor *C = Output(0);
     const index_t lhs_rank = lhs->dim_size(), rhs_rank = rhs->dim_size();
@@ -464,6 +477,7 @@ class MatMulOp<RuntimeType::RT_CUDA, uint8_t> : public Operation {
   }
 
  private:
+  Workspace *registry_workspace_;
   bool transpose_a_, transpose_b_;
   std::unique_ptr<delegator::Gemm> gemm_;
 };
@@ -472,13 +486,14 @@ template <>
 class FullyConnectedOp<RuntimeType::RT_CUDA, uint8_t> : public Operation {
  public:
   explicit FullyConnectedOp(OpConstructContext *context)
-      : Operation(context),
+      : Operation(context), registry_workspace_(context->workspace()),
         gemv_(delegator::Gemv::Create(
             context->workspace(),
             MACE_DELEGATOR_KEY(Gemv, RuntimeType::RT_CUDA, uint8_t, ImplType::CUDA),
             DelegatorParam())) {}
 
   MaceStatus Run(OpContext *context) override {
+    MACE_RETURN_IF_NO_DELEGATOR(gemv_, registry_workspace_);
     const Tensor *input = Input(0), *weight = Input(1);
     const Tensor *bias = InputSize() >= 3 ? Input(2) : nullptr;
     Tensor *output = Output(0);
@@ -494,6 +509,7 @@ class FullyConnectedOp<RuntimeType::RT_CUDA, uint8_t> : public Operation {
   }
 
  private:
+  Workspace *registry_workspace_;
   std::unique_ptr<delegator::Gemv> gemv_;
 };
 
@@ -996,6 +1012,10 @@ void RegisterAllCudaOps(OpRegistry *registry) {
 
 // ---- SerialNet -------------------------------------------------------------------
 
+namespace {
+void DescribeOperator(Operation *op, OperatorStats *os);
+}
+
 MaceStatus SerialNet::AddOperator(const OperatorDef &def) {
   DropCapture();
   defs_.push_back(std::make_unique<OperatorDef>(def));
@@ -1235,6 +1255,54 @@ MaceStatus SerialNet::Capture() {
   return MaceStatus::MACE_SUCCESS;
 }
 
+MaceStatus SerialNet::RunProfiledGraph(RunMetadata *run_metadata, int replays) {
+  if (run_metadata == nullptr || replays < 1) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "RunProfiledGraph");
+  mb_context *ctx = runtime_->ctx();
+  OpContext context(runtime_);
+  std::vector<void *> events(operators_.size() + 1, nullptr);
+  MaceStatus st = MaceStatus::MACE_SUCCESS;
+  for (auto &e : events)
+    if (st == MaceStatus::MACE_SUCCESS) st = runtime_->Status(mb_event_create(ctx, &e));
+  void *graph = nullptr;
+  if (st == MaceStatus::MACE_SUCCESS) st = runtime_->Status(mb_graph_begin(ctx));
+  if (st == MaceStatus::MACE_SUCCESS) {
+    st = runtime_->Status(mb_event_record(ctx, events[0]));
+    for (size_t i = 0; i < operators_.size() && st == MaceStatus::MACE_SUCCESS; ++i) {
+      if (!skipped_[i]) st = operators_[i]->Run(&context);
+      if (st == MaceStatus::MACE_SUCCESS) st = runtime_->Status(mb_event_record(ctx, events[i + 1]));
+    }
+    MaceStatus end = runtime_->Status(mb_graph_end(ctx, &graph));
+    if (st == MaceStatus::MACE_SUCCESS) st = end;
+  }
+  std::vector<float> total(operators_.size(), 0.f);
+  for (int r = 0; r <= replays && st == MaceStatus::MACE_SUCCESS; ++r) {  // replay 0 warms up
+    st = runtime_->Status(mb_graph_launch(ctx, graph));
+    if (st == MaceStatus::MACE_SUCCESS) st = runtime_->Status(mb_stream_sync(ctx));
+    for (size_t i = 0; i < operators_.size() && st == MaceStatus::MACE_SUCCESS && r > 0; ++i) {
+      float ms = 0.f;
+      st = runtime_->Status(mb_event_elapsed_ms(ctx, events[i], events[i + 1], &ms));
+      total[i] += ms;
+    }
+  }
+  if (st == MaceStatus::MACE_SUCCESS) {
+    run_metadata->op_stats.clear();
+    float since_start = 0.f;
+    for (size_t i = 0; i < operators_.size(); ++i) {
+      OperatorStats os;
+      DescribeOperator(operators_[i].get(), &os);
+      os.device_ms = total[i] / static_cast<float>(replays);
+      os.stats.start_micros = static_cast<int64_t>(since_start * 1000.f + 0.5f);
+      since_start += os.device_ms;
+      os.stats.end_micros = static_cast<int64_t>(since_start * 1000.f + 0.5f);
+      run_metadata->op_stats.push_back(os);
+    }
+  }
+  if (graph != nullptr) mb_graph_destroy(ctx, graph);
+  for (auto &e : events)
+    if (e != nullptr) mb_event_destroy(ctx, e);
+  return st;
+}
+
 void SerialNet::DropCapture() {
   if (graph_ != nullptr) {
     mb_graph_destroy(runtime_->ctx(), graph_);
@@ -1242,8 +1310,80 @@ void SerialNet::DropCapture() {
   }
 }
 
-MaceStatus SerialNet::Run(std::vector<CallStats> *run_metadata) {
-  if (graph_ != nullptr && run_metadata == nullptr)
+namespace {
+
+// What the reference records about an operator next to its times (serial_net.cc:138-180).
+void DescribeOperator(Operation *op, OperatorStats *os) {
+  const OperatorDef &def = op->debug_def();
+  os->operator_name = def.name;
+  os->type = def.type;
+  const std::string &type = def.type;
+  if (type == "Conv2D" || type == "Deconv2D" || type == "DepthwiseConv2d" || type == "DepthwiseDeconv2d" ||
+      type == "Pooling") {
+    os->args.strides = op->GetRepeatedArgs<int>("strides");
+    os->args.padding_type = op->GetOptionalArg<int>("padding", -1);
+    os->args.paddings = op->GetRepeatedArgs<int>("padding_values");
+    os->args.dilations = op->GetRepeatedArgs<int>("dilations");
+    if (type == "Pooling") {
+      for (int k : op->GetRepeatedArgs<int>("kernels")) os->args.kernels.push_back(k);
+    } else if (op->InputSize() >= 2) {
+      os->args.kernels = op->Input(1)->shape();
+    }
+  } else if (type == "MatMul") {
+    os->args.kernels = op->Input(0)->shape();
+    if (op->GetOptionalArg<bool>("transpose_a", false) && os->args.kernels.size() >= 2)
+      std::swap(os->args.kernels[os->args.kernels.size() - 2], os->args.kernels[os->args.kernels.size() - 1]);
+  } else if (type == "FullyConnected" && op->InputSize() >= 2) {
+    os->args.kernels = op->Input(1)->shape();
+  }
+  for (const Tensor *t : op->Outputs()) os->output_shape.push_back(t->shape());
+}
+
+std::string ShapeString(const std::vector<index_t> &shape) {
+  std::ostringstream ss;
+  ss << "[";
+  for (size_t i = 0; i < shape.size(); ++i) ss << (i ? ", " : "") << shape[i];
+  ss << "]";
+  return ss.str();
+}
+
+// serial_net.cc:185-224: the ranges of an operator's outputs, reduced on the device.
+MaceStatus LogTensorRanges(CudaRuntime *runtime, Operation *op) {
+  const OperatorDef &def = op->debug_def();
+  for (int i = 0; i < op->OutputSize(); ++i) {
+    const Tensor *out = op->Output(i);
+    const std::string &name = static_cast<size_t>(i) < def.output.size() ? def.output[i] : out->name();
+    if (out->dtype() != DT_FLOAT)
+      return MaceStatus(MaceStatus::MACE_INVALID_ARGS,
+                        "On quantize_stat mode, must use float32 model (tensor " + name + ")");
+    if (def.quantize_info.empty()) {
+      float min_v = 0.f, max_v = 0.f;
+      MACE_RETURN_IF_ERROR(runtime->Status(mb_minmax_f32(runtime->ctx(), out->memory<float>(), out->size(),
+                                                         &min_v, &max_v)));
+      LOG(INFO) << "Tensor range @@" << name << "@@" << min_v << "," << max_v;
+    } else {
+      const int bin_size = 2048;
+      for (const QuantizeActivationInfo &q : def.quantize_info) {
+        std::vector<int32_t> bins(bin_size, 0);
+        MACE_RETURN_IF_ERROR(runtime->Status(mb_histogram_f32(runtime->ctx(), out->memory<float>(), out->size(),
+                                                              q.minval, q.maxval, bin_size, bins.data())));
+        std::ostringstream ss;
+        ss << "[";
+        for (int b = 0; b < bin_size; ++b) ss << (b ? ", " : "") << bins[b];
+        ss << "]";
+        LOG(INFO) << "Tensor range @@" << name << "@@" << q.minval << "," << q.maxval << "@@" << ss.str();
+      }
+    }
+  }
+  return MaceStatus::MACE_SUCCESS;
+}
+
+}  // namespace
+
+MaceStatus SerialNet::Run(RunMetadata *run_metadata) {
+  const bool log_ranges = EnvConfEnabled("MACE_LOG_TENSOR_RANGE");
+  MACE_LATENCY_LOGGER(1, "Running net");
+  if (graph_ != nullptr && run_metadata == nullptr && !log_ranges)
     return runtime_->Status(mb_graph_launch(runtime_->ctx(), graph_));
   OpContext context(runtime_);
   std::vector<void *> events;
@@ -1252,24 +1392,39 @@ MaceStatus SerialNet::Run(std::vector<CallStats> *run_metadata) {
     for (auto &e : events) MACE_RETURN_IF_ERROR(runtime_->Status(mb_event_create(runtime_->ctx(), &e)));
     MACE_RETURN_IF_ERROR(runtime_->Status(mb_event_record(runtime_->ctx(), events[0])));
   }
-  for (size_t i = 0; i < operators_.size(); ++i) {
-    if (!skipped_[i]) MACE_RETURN_IF_ERROR(operators_[i]->Run(&context));
-    if (run_metadata != nullptr)
-      MACE_RETURN_IF_ERROR(runtime_->Status(mb_event_record(runtime_->ctx(), events[i + 1])));
-  }
-  if (run_metadata != nullptr) {
-    run_metadata->clear();
-    for (size_t i = 0; i < operators_.size(); ++i) {
-      CallStats cs;
-      cs.operator_name = operators_[i]->debug_def().name;
-      cs.type = operators_[i]->debug_def().type;
-      MACE_RETURN_IF_ERROR(runtime_->Status(
-          mb_event_elapsed_ms(runtime_->ctx(), events[i], events[i + 1], &cs.device_ms)));
-      run_metadata->push_back(cs);
+  MaceStatus st = MaceStatus::MACE_SUCCESS;
+  for (size_t i = 0; i < operators_.size() && st == MaceStatus::MACE_SUCCESS; ++i) {
+    Operation *op = operators_[i].get();
+    if (!skipped_[i]) {
+      MACE_LATENCY_LOGGER(2, "Running operator " + op->debug_def().name + "<CUDA, " + op->debug_def().type + ">");
+      st = op->Run(&context);
+      if (st != MaceStatus::MACE_SUCCESS) {
+        VLOG(0) << "operator " << op->debug_def().name << " (" << op->debug_def().type
+                << ") failed with error: " << st.information();
+        break;
+      }
+      VLOG(3) << "Operator " << op->debug_def().name << " has shape: " << ShapeString(op->Output(0)->shape());
+      if (log_ranges) st = LogTensorRanges(runtime_, op);
     }
-    for (auto &e : events) mb_event_destroy(runtime_->ctx(), e);
+    if (run_metadata != nullptr && st == MaceStatus::MACE_SUCCESS)
+      st = runtime_->Status(mb_event_record(runtime_->ctx(), events[i + 1]));
   }
-  return MaceStatus::MACE_SUCCESS;
+  if (run_metadata != nullptr && st == MaceStatus::MACE_SUCCESS) {
+    run_metadata->op_stats.clear();
+    float since_start = 0.f;
+    for (size_t i = 0; i < operators_.size() && st == MaceStatus::MACE_SUCCESS; ++i) {
+      OperatorStats os;
+      DescribeOperator(operators_[i].get(), &os);
+      st = runtime_->Status(mb_event_elapsed_ms(runtime_->ctx(), events[i], events[i + 1], &os.device_ms));
+      os.stats.start_micros = static_cast<int64_t>(since_start * 1000.f + 0.5f);
+      since_start += os.device_ms;
+      os.stats.end_micros = static_cast<int64_t>(since_start * 1000.f + 0.5f);
+      run_metadata->op_stats.push_back(os);
+    }
+  }
+  for (auto &e : events)
+    if (e != nullptr) mb_event_destroy(runtime_->ctx(), e);
+  return st;
 }
 
 }  // namespace mace

@@ -29,9 +29,11 @@
 
 namespace mace {
 
-struct QuantizeActivationInfo {  // mace.proto:56-59
+struct QuantizeActivationInfo {  // mace.proto:61-66
   float scale = 0.f;
   int32_t zero_point = 0;
+  float minval = 0.f;  // the range a quantize-aware training run recorded (used by range logging)
+  float maxval = 0.f;
 };
 
 struct OperatorDef {
@@ -48,10 +50,35 @@ struct OperatorDef {
   std::vector<QuantizeActivationInfo> quantize_info;
 };
 
-struct CallStats {  // include/mace/public/mace.h:177-180, filled from device events
+// Per-operator statistics of one run, the types of include/mace/public/mace.h:177-201.  Here the
+// times come from CUDA events on the runtime's stream: start_micros / end_micros are device time
+// since the net's first operator was enqueued (rounded to microseconds), device_ms (an
+// addition) keeps the event resolution.
+struct CallStats {
+  int64_t start_micros = 0;
+  int64_t end_micros = 0;
+};
+
+struct ConvPoolArgs {
+  std::vector<int> strides;
+  int padding_type = -1;
+  std::vector<int> paddings;
+  std::vector<int> dilations;
+  std::vector<int64_t> kernels;
+};
+
+struct OperatorStats {
   std::string operator_name;
   std::string type;
+  std::vector<std::vector<int64_t>> output_shape;
+  ConvPoolArgs args;
+  CallStats stats;
   float device_ms = 0.f;
+};
+
+class RunMetadata {
+ public:
+  std::vector<OperatorStats> op_stats;
 };
 
 class OpConstructContext {
@@ -86,6 +113,8 @@ class Operation {
   const Tensor *Input(unsigned int idx) const { return inputs_[idx]; }
   Tensor *Output(unsigned int idx) { return outputs_[idx]; }
   int InputSize() const { return static_cast<int>(inputs_.size()); }
+  int OutputSize() const { return static_cast<int>(outputs_.size()); }
+  const std::vector<Tensor *> &Outputs() const { return outputs_; }
   const OperatorDef &debug_def() const { return *operator_def_; }
 
   // Net-level merging of this operator with the Activation operator that consumes its only
@@ -159,14 +188,24 @@ class SerialNet {
   // The OperatorDef is copied; its tensors must exist (inputs) or are created (outputs).
   MaceStatus AddOperator(const OperatorDef &def);
   // run_metadata may be null; when given, each operator is bracketed by device
-  // events (mace/core/net/serial_net.cc:122-180).
-  MaceStatus Run(std::vector<CallStats> *run_metadata = nullptr);
+  // events and described as the reference describes it (mace/core/net/serial_net.cc:122-180).
+  // With the environment switch MACE_LOG_TENSOR_RANGE on, every operator's outputs are reduced
+  // on the device after it ran and logged as "Tensor range @@<name>@@<min>,<max>" (float models;
+  // with a quantize_info range: plus the 2048-bin histogram), the lines the post-training
+  // quantization tooling reads (serial_net.cc:185-224); a recorded graph is then not replayed.
+  MaceStatus Run(RunMetadata *run_metadata = nullptr);
   // Records one pass over the operators into a CUDA graph; later Run() calls
   // without run_metadata replay it.  Call after at least one plain Run() (so
   // that scratch and cached operands exist) and again after any change of
   // tensor shapes or operators.
   MaceStatus Capture();
   void DropCapture();
+  // Per-operator device times INSIDE a graph replay: records the operator chain into a second
+  // graph with an event-record node behind every operator, replays it `replays` times and
+  // averages the time between consecutive nodes.  Unlike Run(run_metadata) the operators are
+  // launched the way the recorded graph launches them, so the times add up to the graph's
+  // duration.  Call after at least one plain Run().
+  MaceStatus RunProfiledGraph(RunMetadata *run_metadata, int replays = 5);
   // Merges every Activation operator into the operator that produces its input when that
   // operator can absorb it (the float Eltwise: a residual sum and its ReLU become one pass)
   // and nothing else reads the intermediate tensor, which is then no longer written.

@@ -30,6 +30,7 @@ _PROTOS = {
     "mbh_tensor_quant": [_vp, _cp, C.POINTER(_f32), C.POINTER(_i32)],
     "mbh_tensor_read": [_vp, _cp, _vp, _sz],
     "mbh_tensor_write": [_vp, _cp, _vp, _sz],
+    "mbh_tensor_device_ptr": [_vp, _cp, C.POINTER(_vp), C.POINTER(_sz)],
     "mbh_op_begin": [_vp, _cp, _cp],
     "mbh_op_input": [_vp, _cp],
     "mbh_op_output": [_vp, _cp, _int, _f32, _i32],
@@ -50,11 +51,20 @@ _PROTOS = {
     "mbh_run_host_pipelined": [_vp, _cp, _vp, _sz, _cp, _vp, _sz, C.POINTER(_int)],
     "mbh_wait_slot": [_vp, _int],
     "mbh_run_profiled": [_vp, C.POINTER(_f32), _int, C.c_char_p, _sz, C.POINTER(_int)],
+    "mbh_run_profiled_graph": [_vp, _int, C.POINTER(_f32), _int, C.c_char_p, _sz, C.POINTER(_int)],
     "mbh_netdef_describe": [_vp, _sz, C.c_char_p, _sz, C.POINTER(_sz)],
     "mbh_half_to_float": [_vp, _vp, _sz],
     "mbh_model_destroy": [_vp],
     "mbh_model_captured": [_vp],
+    "mbh_model_run_metadata": [_vp, C.c_char_p, _sz, C.POINTER(_sz)],
+    "mbh_shard_bounds": [C.c_int64, _int, _int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)],
+    "mbh_multi_destroy": [_vp],
+    "mbh_multi_shards": [_vp],
+    "mbh_set_vlog_level": [_int],
+    "mbh_vlog_is_on": [_int],
+    "mbh_log": [_int, _cp],
 }
+LOG_SINK = C.CFUNCTYPE(None, _int, _cp)
 _lib = None
 
 
@@ -80,6 +90,15 @@ def lib():
         _lib.mbh_model_last_error.argtypes = [_vp]
         _lib.mbh_model_context.restype = _vp
         _lib.mbh_model_context.argtypes = [_vp]
+        _lib.mbh_multi_create.restype = _int
+        _lib.mbh_multi_create.argtypes = [_int, C.POINTER(_int), _vp, _sz, _vp, _sz, _int, _int, _int,
+                                          C.POINTER(_vp), C.c_char_p, _sz]
+        _lib.mbh_multi_run.restype = _int
+        _lib.mbh_multi_run.argtypes = [_vp, _int, C.POINTER(IoTensor), _int, C.POINTER(IoTensor)]
+        _lib.mbh_multi_last_error.restype = _cp
+        _lib.mbh_multi_last_error.argtypes = [_vp]
+        _lib.mbh_set_log_sink.restype = _int
+        _lib.mbh_set_log_sink.argtypes = [LOG_SINK]
     return _lib
 
 
@@ -149,31 +168,120 @@ class Model:
     def run(self, inputs, outputs):
         """inputs: {name: (array, data_format)}; outputs: {name: (array sized for the largest result,
         data_format)}.  Returns {name: view of the output array with the actual shape}."""
-        ins = (IoTensor * max(1, len(inputs)))()
-        keep = []
-        for k, (name, (a, fmt)) in enumerate(inputs.items()):
-            a = np.ascontiguousarray(a)
-            keep.append(a)
-            ins[k].name, ins[k].data, ins[k].rank = name.encode(), a.ctypes.data, a.ndim
-            ins[k].data_format, ins[k].data_type = fmt, _DT[a.dtype]
-            for d in range(a.ndim):
-                ins[k].shape[d] = a.shape[d]
-        outs = (IoTensor * max(1, len(outputs)))()
-        for k, (name, (a, fmt)) in enumerate(outputs.items()):
-            assert a.flags["C_CONTIGUOUS"]
-            outs[k].name, outs[k].data, outs[k].rank = name.encode(), a.ctypes.data, a.ndim
-            outs[k].data_format, outs[k].data_type = fmt, _DT[a.dtype]
-            for d in range(a.ndim):
-                outs[k].shape[d] = a.shape[d]
+        ins, outs, keep = _marshal_io(inputs, outputs)
         st = lib().mbh_model_run(self.h, len(inputs), ins, len(outputs), outs)
         if st != 0:
             raise capi.MaceB200Error(st, lib().mbh_model_last_error(self.h).decode())
-        result = {}
-        for k, (name, (a, fmt)) in enumerate(outputs.items()):
-            shape = tuple(outs[k].shape[d] for d in range(outs[k].rank))
-            n = int(np.prod(shape)) if shape else 1
-            result[name] = a.reshape(-1)[:n].reshape(shape)
-        return result
+        return _unmarshal_outputs(outputs, outs)
+
+    def run_metadata(self):
+        """Runs the net once more on the inputs of the last run() and returns RunMetadata's
+        per-operator statistics as a list of dicts (times from device events)."""
+        import json
+        need = _sz()
+        buf = C.create_string_buffer(1 << 20)
+        st = lib().mbh_model_run_metadata(self.h, buf, len(buf), C.byref(need))
+        if st != 0:
+            raise capi.MaceB200Error(st, lib().mbh_model_last_error(self.h).decode())
+        assert need.value <= len(buf)
+        return json.loads(buf.value.decode())
+
+
+def _marshal_io(inputs, outputs):
+    ins = (IoTensor * max(1, len(inputs)))()
+    keep = []
+    for k, (name, (a, fmt)) in enumerate(inputs.items()):
+        a = np.ascontiguousarray(a)
+        keep.append(a)
+        ins[k].name, ins[k].data, ins[k].rank = name.encode(), a.ctypes.data, a.ndim
+        ins[k].data_format, ins[k].data_type = fmt, _DT[a.dtype]
+        for d in range(a.ndim):
+            ins[k].shape[d] = a.shape[d]
+    outs = (IoTensor * max(1, len(outputs)))()
+    for k, (name, (a, fmt)) in enumerate(outputs.items()):
+        assert a.flags["C_CONTIGUOUS"]
+        outs[k].name, outs[k].data, outs[k].rank = name.encode(), a.ctypes.data, a.ndim
+        outs[k].data_format, outs[k].data_type = fmt, _DT[a.dtype]
+        for d in range(a.ndim):
+            outs[k].shape[d] = a.shape[d]
+    return ins, outs, keep
+
+
+def _unmarshal_outputs(outputs, outs):
+    result = {}
+    for k, (name, (a, fmt)) in enumerate(outputs.items()):
+        shape = tuple(outs[k].shape[d] for d in range(outs[k].rank))
+        n = int(np.prod(shape)) if shape else 1
+        result[name] = a.reshape(-1)[:n].reshape(shape)
+    return result
+
+
+def shard_bounds(total, parts, index):
+    """Rows [begin, end) of shard `index` of `parts` (the C++ runner's rule); needs no GPU."""
+    b, e = C.c_int64(), C.c_int64()
+    st = lib().mbh_shard_bounds(int(total), int(parts), int(index), C.byref(b), C.byref(e))
+    if st != 0:
+        raise capi.MaceB200Error(st, "mbh_shard_bounds: bad argument")
+    return b.value, e.value
+
+
+class MultiModel:
+    """A converted model replicated over several shards (normally one per GPU): the C++
+    MultiGpuRunner -- one MaceEngine, stream and host thread per shard, the batch split along the
+    first dimension, every shard's output rows copied straight into the caller's buffer."""
+
+    def __init__(self, graph, weights, devices, fuse=False, plan_memory=False, cuda_graph=False):
+        self.h = _vp()
+        err = C.create_string_buffer(1024)
+        dev = (_int * len(devices))(*[int(d) for d in devices])
+        st = lib().mbh_multi_create(len(devices), dev, graph, len(graph), weights, len(weights), int(fuse),
+                                    int(plan_memory), int(cuda_graph), C.byref(self.h), err, len(err))
+        if st != 0:
+            self.h = None
+            raise capi.MaceB200Error(st, err.value.decode())
+
+    def close(self):
+        if self.h:
+            lib().mbh_multi_destroy(self.h)
+            self.h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    @property
+    def shards(self):
+        return lib().mbh_multi_shards(self.h)
+
+    def run(self, inputs, outputs):
+        """As Model.run, on the whole batch."""
+        ins, outs, keep = _marshal_io(inputs, outputs)
+        st = lib().mbh_multi_run(self.h, len(inputs), ins, len(outputs), outs)
+        if st != 0:
+            raise capi.MaceB200Error(st, lib().mbh_multi_last_error(self.h).decode())
+        return _unmarshal_outputs(outputs, outs)
+
+
+class LogCapture:
+    """Collects the host layer's log lines (LOG / VLOG) while active, optionally with another
+    VLOG level than the environment's."""
+
+    def __init__(self, vlog_level=None):
+        self.lines = []
+        self.vlog_level = vlog_level
+        self._cb = LOG_SINK(lambda sev, line: self.lines.append((sev, line.decode())))
+
+    def __enter__(self):
+        lib().mbh_set_log_sink(self._cb)
+        if self.vlog_level is not None:
+            lib().mbh_set_vlog_level(int(self.vlog_level))
+        return self
+
+    def __exit__(self, *a):
+        lib().mbh_set_log_sink(C.cast(None, LOG_SINK))
+        lib().mbh_set_vlog_level(-2 ** 31)
 
 
 class HostEngine:
@@ -237,6 +345,12 @@ class HostEngine:
         out = np.empty(self.shape(name), dtype)
         self._check(lib().mbh_tensor_read(self.h, name.encode(), out.ctypes.data, out.nbytes))
         return out
+
+    def device_ptr(self, name):
+        """(device address, bytes) of a tensor after the last run."""
+        p, n = _vp(), _sz()
+        self._check(lib().mbh_tensor_device_ptr(self.h, name.encode(), C.byref(p), C.byref(n)))
+        return p.value, n.value
 
     def write(self, name, array):
         array = np.ascontiguousarray(array)
@@ -330,5 +444,15 @@ class HostEngine:
         names = C.create_string_buffer(64 * max_ops)
         n = _int()
         self._check(lib().mbh_run_profiled(self.h, ms, max_ops, names, len(names), C.byref(n)))
+        labels = names.value.decode().strip().split("\n")
+        return [(labels[k], float(ms[k])) for k in range(min(n.value, max_ops))]
+
+    def run_profiled_graph(self, replays=5, max_ops=256):
+        """Per-operator device times inside a graph replay (event nodes between the operators of
+        a recorded graph): [(type:name, ms)], adding up to the graph's duration."""
+        ms = (C.c_float * max_ops)()
+        names = C.create_string_buffer(64 * max_ops)
+        n = _int()
+        self._check(lib().mbh_run_profiled_graph(self.h, int(replays), ms, max_ops, names, len(names), C.byref(n)))
         labels = names.value.decode().strip().split("\n")
         return [(labels[k], float(ms[k])) for k in range(min(n.value, max_ops))]

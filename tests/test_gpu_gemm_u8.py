@@ -86,6 +86,33 @@ def test_shapes_and_tails(ctx, orc, shape):
     assert np.array_equal(got, exp)
 
 
+def test_config4_m128_and_batched_512(ctx, orc):
+    """The two sweep shapes that sit between the few-row kernel and the square GEMM: M = 128
+    against K = N = 4096 (one row of 128-row tiles), and the batched 64 x 512^3 MatMul.  Every
+    output byte against the oracle, with and without a bias; for the batched product each of
+    four sampled entries is also run alone (one batch entry) and must give the same bytes as
+    it does inside the batch."""
+    M, N, K = 128, 4096, 4096
+    for bias_len in (None, N):
+        case = gemm_case(orc, 41, 1, M, N, K, bias_len=bias_len)
+        before = ctx.launches_tensor_core
+        got, exp = run_gemm(ctx, orc, case, 1, M, N, K)
+        assert ctx.launches_tensor_core > before, "tensor-core kernel did not run"
+        assert np.array_equal(got, exp)
+        assert len(np.unique(got)) > 100
+    batch, M, N, K = 64, 512, 512, 512
+    case = gemm_case(orc, 42, batch, M, N, K)
+    got, exp = run_gemm(ctx, orc, case, batch, M, N, K)
+    assert np.array_equal(got, exp)
+    assert len(np.unique(got)) > 100
+    got = got.reshape(batch, M, N)
+    for b in (0, 17, 40, 63):
+        one = dict(case, A=np.ascontiguousarray(case["A"][b:b + 1]), B=np.ascontiguousarray(case["B"][b:b + 1]))
+        alone, exp1 = run_gemm(ctx, orc, one, 1, M, N, K)
+        assert np.array_equal(alone, exp1)
+        assert np.array_equal(alone.reshape(M, N), got[b])
+
+
 @pytest.mark.parametrize("a_cm,b_cm", [(False, False), (False, True), (True, False), (True, True)])
 def test_unaligned_generic_path(ctx, orc, a_cm, b_cm):
     """31 x 61 x 67 (matmul_test.cc): no 16-byte alignment anywhere, CUDA-core kernel."""

@@ -4,7 +4,7 @@ uint8 logits must be bit-exact."""
 import numpy as np
 import pytest
 
-import mobilenet_v1 as mn
+from mace_b200.harness import mobilenet_v1 as mn
 
 pytestmark = pytest.mark.gpu
 

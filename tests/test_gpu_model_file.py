@@ -7,9 +7,9 @@ largest magnitude (1e-3 where Winograd convolutions are involved)."""
 import numpy as np
 import pytest
 
-import mobilenet_v1 as mn
-import netdef_wire as W
-import resnet50 as rn
+from mace_b200.harness import mobilenet_v1 as mn
+from mace_b200.harness import netdef_wire as W
+from mace_b200.harness import resnet50 as rn
 
 pytestmark = pytest.mark.gpu
 

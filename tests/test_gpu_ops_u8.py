@@ -225,6 +225,39 @@ def test_dwconv_u8_3x3_variants(ctx, orc, stride, variant):
     assert len(np.unique(got)) > 4
 
 
+def test_dwconv_u8_repack_into_the_same_buffer_then_run_at_once(ctx, orc):
+    """The depthwise kernel fetches cached tap words before it waits for the kernel in front of
+    it.  When that kernel is the one that (re)wrote the tap words -- a delegator's first run, or
+    a weight update -- the fetch has to wait: alternate two filters through ONE prepacked
+    buffer, launching the convolution right behind each repack with nothing in between."""
+    rng = np.random.Generator(np.random.PCG64(77))
+    N, H, W, C = 8, 56, 56, 256
+    x = rng.integers(0, 256, size=(N, H, W, C), dtype=np.uint8)
+    zp_in, zp_f, zp_out = 0, 128, 0
+    mult, shift = orc.output_multiplier_and_shift(np.float32(0.02), np.float32(0.01), np.float32(3.0))
+    filters = [rng.integers(1, 256, size=(3, 3, C, 1), dtype=np.uint8) for _ in range(2)]
+    biases = [np.rint(rng.normal(0, 500, size=C)).astype(np.int32) for _ in range(2)]
+    exps = [orc.dwconv_u8(x, f, b, (1, 1), (1, 1), (1, 1), (H, W), zp_in, zp_f, mult, shift, zp_out)
+            for f, b in zip(filters, biases)]
+    assert not np.array_equal(exps[0], exps[1])
+    dx, do = ctx.upload(x), ctx.alloc(x.size)
+    dfs, dbs = [ctx.upload(f) for f in filters], [ctx.upload(b) for b in biases]
+    packed = ctx.dwconv3x3_u8_prepack(dfs[0], dbs[0], C, zp_in, zp_f)
+    L = __import__("mace_b200").lib()
+    for it in range(6):
+        k = it & 1
+        ctx._check(L.mb_dwconv3x3_u8_prepack(ctx.h, dfs[k].ptr, dbs[k].ptr, C, zp_in, zp_f, packed.ptr))
+        ctx.dwconv_u8(dx, dfs[k], dbs[k], do, N, H, W, C, 1, 3, 3, (1, 1), (1, 1), (1, 1), (H, W),
+                      zp_in, zp_f, mult, shift, zp_out, prepacked=packed)
+        assert np.array_equal(ctx.download(do, x.shape, np.uint8), exps[k]), it
+        # a second launch may fetch early again: the tap words are settled
+        ctx.dwconv_u8(dx, dfs[k], dbs[k], do, N, H, W, C, 1, 3, 3, (1, 1), (1, 1), (1, 1), (H, W),
+                      zp_in, zp_f, mult, shift, zp_out, prepacked=packed)
+        assert np.array_equal(ctx.download(do, x.shape, np.uint8), exps[k]), it
+    for b in [dx, do, packed] + dfs + dbs:
+        b.free()
+
+
 # ---- pooling -----------------------------------------------------------------------
 
 @pytest.mark.parametrize("case", [(64, 7, 7, 1024, 7, 7, 1, "VALID"), (2, 9, 11, 24, 3, 3, 2, "SAME"),

@@ -5,7 +5,7 @@ oracle's direct fp32 convolutions.  Tolerance for the chain: 1e-3 of each activa
 import numpy as np
 import pytest
 
-import resnet50 as rn
+from mace_b200.harness import resnet50 as rn
 
 pytestmark = pytest.mark.gpu
 
@@ -153,6 +153,52 @@ def test_resnet50_graph_against_oracle(orc, cfg):
         ref2 = rn.oracle_forward(orc, nodes, weights, x2)
         got2 = eng.read("fc", np.float32)
         assert float(np.abs(got2 - ref2).max() / np.abs(ref2).max()) <= 1e-4
+    finally:
+        eng.close()
+
+
+def test_resnet50_full_width_224_against_oracle(orc):
+    """The benchmarked network itself (width_div 1, 224 x 224), batch 2: the logits, and three
+    activations from different stages (the Winograd output of the first block, the stride-2
+    opening of stage 3, the last block), against the oracle's direct fp32 convolutions --
+    element-wise |got - ref| <= abs_err + rel_err * |ref| with rel_err 1e-3 (the chain contains
+    F(6,3) Winograd convolutions) and abs_err = rel_err * rms(ref), and range-normalised 1e-3 (the
+    measured values are printed);
+    then the same logits from the merged, memory-planned, graph-replayed net."""
+    from helpers import near_ratio
+    from mace_b200 import hostapi
+    batch = 2
+    nodes, weights = rn.build(seed=0)
+    x = rn.random_images(batch, 11)
+    ref_logits, ref = rn.oracle_forward(orc, nodes, weights, x, keep=True)
+    eng = rn.build_engine(hostapi, nodes, weights, batch)
+    try:
+        eng.write("input", x)
+        eng.run()
+        report = {}
+        for name in ("res2a_branch2b", "res3a_branch1", "res4f", "res5c", "pool5", "fc"):
+            got, want = eng.read(name, np.float32), ref[name]
+            assert got.shape == want.shape, name
+            ratio = near_ratio(got, want, 1e-3)
+            rng_err = float(np.abs(got.astype(np.float64) - want).max() / np.abs(want).max())
+            report[name] = (ratio, rng_err)
+            assert ratio <= 1.0, (name, ratio)
+            assert rng_err <= 1e-3, (name, rng_err)
+        print("full-width ResNet-50, element-wise ratio / range-normalised error:", report)
+        assert np.array_equal(eng.read("fc", np.float32).argmax(1).ravel(), ref_logits.argmax(1).ravel())
+        first = eng.read("fc", np.float32)
+        eng.share_subsampled_inputs()
+        eng.fuse_activations()
+        eng.run()
+        eng.fuse_residual_sums()
+        eng.run()
+        eng.plan_memory()
+        eng.run()
+        eng.capture()
+        eng.run()
+        merged = eng.read("fc", np.float32)
+        assert near_ratio(merged, ref_logits, 1e-3) <= 1.0
+        assert float(np.abs(merged - first).max() / np.abs(first).max()) <= 1e-5
     finally:
         eng.close()
 

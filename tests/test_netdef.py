@@ -9,7 +9,7 @@ import struct
 import numpy as np
 import pytest
 
-import netdef_wire as W
+from mace_b200.harness import netdef_wire as W
 from mace_b200 import capi, hostapi
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")

@@ -58,3 +58,51 @@ def test_two_ranks_shard_and_gather(tmp_path, batch):
     for r in range(world):
         with open("%s.%d" % (out, r)) as fh:
             assert fh.read() == "ok"
+
+
+def _lossy_worker(rank, world, port, mode, out_path):
+    """Rank 1 takes part in the first gather and then drops out before the second one: it exits
+    (mode "exit") or simply never calls the collective (mode "stall").  Rank 0 must come back
+    from its second gather with PeerLost -- by the closed connection or by the process group's
+    short timeout -- instead of waiting forever, and still hold its own rows."""
+    sys.path.insert(0, ROOT)
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch
+    import torch.distributed as dist
+    from mace_b200.sharding import PeerLost, RowGather
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    g = RowGather(dist, 6, (5,), torch.uint8)
+    mine = torch.full((3, 5), rank + 1, dtype=torch.uint8)
+    g.gather(mine)
+    first_ok = g.assemble()[:, 0].tolist() == [1, 1, 1, 2, 2, 2]
+    if rank == 1:
+        if mode == "stall":
+            time.sleep(8)
+        os._exit(0)
+    t0 = time.time()
+    verdict = "no error"
+    try:
+        g.gather(mine)
+    except PeerLost as e:
+        verdict = "peer lost" if "rank 0" in str(e) else "wrong message"
+    waited = time.time() - t0
+    own_rows_intact = bool((g.send[:3] == 1).all())
+    with open(out_path, "w") as fh:
+        fh.write("%s %s %s %.1f" % (first_ok, verdict, own_rows_intact, waited))
+    os._exit(0)
+
+
+@pytest.mark.parametrize("mode", ["exit", "stall"])
+def test_a_rank_that_leaves_before_the_gather_is_noticed(tmp_path, mode):
+    import torch.multiprocessing as mp
+    port = 31500 + (os.getpid() % 2000) + (7 if mode == "stall" else 0)
+    out = str(tmp_path / "verdict")
+    mp.spawn(_lossy_worker, args=(2, port, mode, out), nprocs=2, join=True)
+    first_ok, verdict, verdict2, own, waited = open(out).read().split()
+    assert first_ok == "True"
+    assert (verdict, verdict2) == ("peer", "lost")
+    assert own == "True"
+    assert float(waited) < 30.0

@@ -6,7 +6,10 @@ memory, a callback that may run during a stream capture).  For them the library 
 GEMM's scratch -- the operand byte sums and the kernel's status word -- in a fixed array
 that ships with the library.  This test calls that entry point through the C ABI twice in a
 row, with different problem sizes so that anything left in the shared array by the first
-call would corrupt the second, and requires the same bytes as mb_gemm_u8 produces.
+call would corrupt the second, and requires the same bytes as mb_gemm_u8 produces and as the
+CPU oracle computes; after each call it also reads the kernel's status word back through
+mb_gemm_u8_static_scratch_status (a bounded wait that ran out would otherwise go unnoticed,
+because this entry point has no context whose sync could report it).
 
 The file name sorts last on purpose: a run that stops at the first failure has then already
 run every other test.
@@ -36,9 +39,16 @@ def _run_pair(ctx, lib, orc, seed, M, N, K, a_cm, b_cm, bias_per_row):
         case["zp_a"], case["zp_b"], case["mult"], case["shift"], case["zp_c"],
         int(bias_per_row), msg, len(msg))
     assert st == 0, msg.value.decode()
-    got = ctx.download(new_out, (M, N), np.uint8)
+    status = C.c_int(-1)
+    assert lib.mb_gemm_u8_static_scratch_status(ctx.stream, C.byref(status)) == 0
+    got = ctx.download(new_out, (M, N), np.uint8)  # synchronizes the stream
+    assert status.value == 0, "the kernel gave up a bounded wait (code %d)" % status.value
     # integer arithmetic: the tolerance of the uint8 tests is exact equality
     assert np.array_equal(got, expected)
+    oracle = orc.gemm_u8(case["A"], case["B"], case["bias"], 1, M, N, K, case["zp_a"], case["zp_b"],
+                         case["mult"], case["shift"], case["zp_c"], a_col_major=a_cm,
+                         b_col_major=b_cm, bias_per_row=bias_per_row).reshape(M, N)
+    assert np.array_equal(got, oracle)
     assert len(np.unique(got)) > 16
     for b in (A, B, bias, ref_out, new_out):
         b.free()
@@ -73,5 +83,14 @@ def test_static_scratch_gemm_rejects_what_it_cannot_hold():
                                            31, 67, 61, 0, 0, 0, 0, 1 << 30, 0, 0, 0, msg,
                                            len(msg))
         assert st == 3 and b"16" in msg.value
+        # zero points outside uint8 are rejected before anything is enqueued
+        st = lib.mb_gemm_u8_static_scratch(ctx.stream, buf.ptr, buf.ptr, None, buf.ptr, 0,
+                                           64, 64, 64, 0, 0, 0, 0, 1 << 30, 0, 256, 0, msg,
+                                           len(msg))
+        assert st == 1 and b"zero point" in msg.value
+        st = lib.mb_gemm_u8_static_scratch(ctx.stream, buf.ptr, buf.ptr, None, buf.ptr, 0,
+                                           64, 64, 64, 0, 0, -1, 0, 1 << 30, 0, 0, 0, msg,
+                                           len(msg))
+        assert st == 1 and b"zero point" in msg.value
     finally:
         ctx.close()
