@@ -56,6 +56,10 @@ struct mb_context {
                                  // kernel: while they are equal that kernel is the newest one in
                                  // the stream and the depthwise kernel may not read the tap words
                                  // before it has waited for its predecessor
+  int skinny_max_m = 16;         // row counts up to this take the streaming few-row GEMM
+  int gemv_stream = 1;           // one-vector GEMV through the bulk-copy streaming kernel
+  int split_tail = 1;            // tensor-core GEMM: cut the tiles of a sparse last round into halves
+  int force_bn = 0;              // tensor-core GEMM: 64 / 128 / 256 overrides the tile-width choice
   int dw_waves = 1;              // depthwise 3x3: rounds of resident blocks the grid is sized for
   int wino_plane = 1;            // plane-at-a-time Winograd output transform (0: per-tile kernel)
   int64_t col_budget_bytes = 1ll << 30;  // im2col column matrix of the fp32 general convolution:

@@ -393,6 +393,17 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
   } else if (strcmp(name, "dw_waves") == 0) {
     if (value < 1) return mb_fail(ctx, MB_INVALID_ARGS, "dw_waves must be at least 1");
     ctx->dw_waves = value;
+  } else if (strcmp(name, "skinny_max_m") == 0) {
+    if (value < 0 || value > 16) return mb_fail(ctx, MB_INVALID_ARGS, "skinny_max_m must be 0 .. 16");
+    ctx->skinny_max_m = value;
+  } else if (strcmp(name, "gemv_stream") == 0) {
+    ctx->gemv_stream = value;
+  } else if (strcmp(name, "split_tail") == 0) {
+    ctx->split_tail = value;
+  } else if (strcmp(name, "force_bn") == 0) {
+    if (value != 0 && value != 64 && value != 128 && value != 256)
+      return mb_fail(ctx, MB_INVALID_ARGS, "force_bn must be 0, 64, 128 or 256");
+    ctx->force_bn = value;
   } else if (strcmp(name, "pdl") == 0) {
     ctx->pdl_chain = value;
   } else if (strcmp(name, "wino_plane") == 0) {

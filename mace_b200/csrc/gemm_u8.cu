@@ -103,88 +103,6 @@ __global__ void __launch_bounds__(256) gemm_u8_generic_kernel(const GenericParam
   }
 }
 
-// ---- byte sums ----------------------------------------------------------------
-// Sum of each row of a [rows x len] byte matrix with contiguous rows; one warp
-// per row, 16-byte loads (len % 16 == 0, base 16-byte aligned).
-__global__ void __launch_bounds__(256) rowsum_u8_kernel(const uint8_t *__restrict__ x,
-                                                        uint32_t *__restrict__ out,
-                                                        int64_t rows, int64_t len, int wait_at_end) {
-  // let a dependent GEMM launch now: it waits for this grid only where it reads the sums
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;  // (block 0 always has a live warp 0 for the wait below)
-  const int lane = threadIdx.x & 31;
-  const uint4 *p = reinterpret_cast<const uint4 *>(x + row * len);
-  const int64_t nvec = len >> 4;
-  uint32_t s = 0;
-#pragma unroll 4
-  for (int64_t i = lane; i < nvec; i += 32) {
-    const uint4 v = __ldg(p + i);
-    s = __dp4a(v.x, 0x01010101u, s);
-    s = __dp4a(v.y, 0x01010101u, s);
-    s = __dp4a(v.z, 0x01010101u, s);
-    s = __dp4a(v.w, 0x01010101u, s);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) out[row] = s;
-  // Launched ahead of the kernel before it: do not let this grid END before that one has,
-  // so that whoever waits for this grid has waited for both.
-  if (wait_at_end && threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
-}
-
-// Sum down the columns of a [rows x cols] byte matrix (cols % 16 == 0, base
-// 16-byte aligned).  A block of 32 x 8 threads covers 512 adjacent columns and
-// one slice of rows: each thread owns 16 columns (one 128-bit load per row) and
-// every 8th row of the slice; the 8 partial sums are combined in shared memory
-// and the slice total is added to the zeroed output with integer atomics.
-__global__ void __launch_bounds__(256) colsum_u8_kernel(const uint8_t *__restrict__ x,
-                                                        uint32_t *__restrict__ out,
-                                                        int64_t rows, int64_t cols,
-                                                        int64_t rows_per_slice,
-                                                        int64_t batch_stride, int wait_at_end) {
-  __shared__ uint32_t part[8][32][17];
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int64_t c16 = static_cast<int64_t>(blockIdx.x) * 32 + tx;  // 16-column group
-  const bool active = c16 * 16 < cols;
-  const int b = blockIdx.z;
-  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_slice;
-  const int64_t r1 = min(rows, r0 + rows_per_slice);
-  const uint8_t *base = x + b * batch_stride;
-  uint32_t s[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) s[i] = 0;
-  if (active) {
-#pragma unroll 4
-    for (int64_t r = r0 + ty; r < r1; r += 8) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(base + r * cols) + c16);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        s[4 * q + 0] += w[q] & 0xffu;
-        s[4 * q + 1] += (w[q] >> 8) & 0xffu;
-        s[4 * q + 2] += (w[q] >> 16) & 0xffu;
-        s[4 * q + 3] += w[q] >> 24;
-      }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) part[ty][tx][i] = s[i];
-  __syncthreads();
-  // 512 columns, 256 threads: two columns each
-  for (int c = threadIdx.x; c < 512; c += 256) {
-    const int gx = c >> 4, gi = c & 15;
-    const int64_t col = static_cast<int64_t>(blockIdx.x) * 512 + c;
-    if (col >= cols) continue;
-    uint32_t t = 0;
-#pragma unroll
-    for (int y = 0; y < 8; ++y) t += part[y][gx][gi];
-    atomicAdd(out + b * cols + col, t);
-  }
-  if (wait_at_end && threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
-}
-
 // ---- transpose [rows x cols] -> [cols x rows] bytes ------------------------------
 __global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t *__restrict__ in,
                                                            uint8_t *__restrict__ out,
@@ -201,45 +119,6 @@ __global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t *__rest
     const int c = i >> 6, r = i & 63;
     if (r0 + r < rows && c0 + c < cols) out[batch_off + (c0 + c) * rows + r0 + r] = tile[r][c];
   }
-}
-
-// pdl: launch with programmatic stream serialization, i.e. allowed to start before the kernel
-// launched just before it has ended (that kernel must be the other operand-sum kernel, whose
-// data this one does not touch); the kernel then holds its own end back until that one's.
-template <typename... Args>
-int launch_maybe_pdl(mb_context *ctx, void (*kern)(Args...), dim3 grid, bool pdl, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(256);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = ctx->stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  MB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, args...));
-  ctx->launches++;
-  return MB_SUCCESS;
-}
-
-int launch_rowsum(mb_context *ctx, const uint8_t *x, uint32_t *out, int64_t rows, int64_t len,
-                  bool pdl = false) {
-  return launch_maybe_pdl(ctx, rowsum_u8_kernel, dim3(static_cast<unsigned>(ceil_div64(rows, 8))), pdl, x,
-                          out, rows, len, pdl ? 1 : 0);
-}
-
-// `out` must be zero (mb_zero_colsum); kept apart so that the zeroing can precede BOTH sum kernels.
-int launch_colsum(mb_context *ctx, const uint8_t *x, uint32_t *out, int64_t nb, int64_t rows,
-                  int64_t cols, bool pdl = false) {
-  const int64_t col_blocks = ceil_div64(cols, 512);
-  int64_t slices = ceil_div64(static_cast<int64_t>(ctx->num_sms) * 4, col_blocks * nb);
-  slices = std::max<int64_t>(1, std::min<int64_t>(slices, ceil_div64(rows, 64)));
-  const int64_t rps = ceil_div64(rows, slices);
-  dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(ceil_div64(rows, rps)),
-            static_cast<unsigned>(nb));
-  return launch_maybe_pdl(ctx, colsum_u8_kernel, grid, pdl, x, out, rows, cols, rps, rows * cols,
-                          pdl ? 1 : 0);
 }
 
 int launch_transpose(mb_context *ctx, const uint8_t *in, uint8_t *out, int64_t nb, int64_t rows,
@@ -285,6 +164,16 @@ int mb_gemm_u8_skinny_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B
                              void *C, int out_is_int32, int64_t M, int64_t N, int64_t K, int32_t zp_a,
                              int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c, int bias_per_row);
 
+int mb_operand_sums_slices(const mb_context *ctx, bool mn, int64_t nb, int64_t K, int64_t cols);
+int mb_gemm_u8_tc_launch_sliced(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+                                const uint32_t *sum_a, const uint32_t *sum_b, int sum_a_slices, int sum_b_slices,
+                                const int32_t *bias, void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
+                                int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
+                                int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
+                                int bias_per_row);
+int mb_operand_sums_launch(mb_context *ctx, const uint8_t *A, bool a_mn, int64_t nb_a, int64_t M, uint32_t *sum_a,
+                           const uint8_t *B, bool b_mn, int64_t nb_b, int64_t N, uint32_t *sum_b, int64_t K);
+
 // Row-major-C GEMM on device operands; a_mn / b_mn as in mb_gemm_u8_tc_launch.
 int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, const int32_t *bias,
                         void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
@@ -292,7 +181,7 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
                         int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
                         int bias_per_row) {
   // A few rows against a large row-major B: stream B once over all SMs.
-  if (ctx->use_tensor_cores && mb_gemm_u8_skinny_supported(batch, M, N, K, a_mn, b_mn, A, B))
+  if (ctx->use_tensor_cores && M <= ctx->skinny_max_m && mb_gemm_u8_skinny_supported(batch, M, N, K, a_mn, b_mn, A, B))
     return mb_gemm_u8_skinny_launch(ctx, A, B, bias, C, out_is_int32, M, N, K, zp_a, zp_b, mult, shift,
                                     zp_c, bias_per_row);
   const bool aligned16 =
@@ -316,10 +205,14 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
   const bool fused_sums = !(a_mn && !a_copy) && !(b_mn && !b_copy) && K <= 1024;
   const bool need_sum_a = zp_b != 0 && !fused_sums, need_sum_b = zp_a != 0 && !fused_sums;
   size_t off = 0;
-  const size_t off_sum_a = off; off += need_sum_a ? align_up(sizeof(uint32_t) * nb_a * M, 256) : 0;
-  const size_t off_sum_b = off; off += need_sum_b ? align_up(sizeof(uint32_t) * nb_b * N, 256) : 0;
+  // (an operand that reaches the tensor core MN-major gets its column sums as a few partial rows)
+  const int sl_a = need_sum_a ? mb_operand_sums_slices(ctx, a_mn && !a_copy, nb_a, K, M) : 1;
+  const int sl_b = need_sum_b ? mb_operand_sums_slices(ctx, b_mn && !b_copy, nb_b, K, N) : 1;
+  const size_t off_sum_a = off; off += need_sum_a ? align_up(sizeof(uint32_t) * nb_a * M * sl_a, 256) : 0;
+  const size_t off_sum_b = off; off += need_sum_b ? align_up(sizeof(uint32_t) * nb_b * N * sl_b, 256) : 0;
   const size_t off_at = off; off += a_copy ? align_up(nb_a * M * K, 256) : 0;
   const size_t off_bt = off; off += b_copy ? align_up(nb_b * N * K, 256) : 0;
+
   uint8_t *scratch = nullptr;
   if (off > 0) MB_RETURN_IF_ERROR(mb_scratch(ctx, off, reinterpret_cast<void **>(&scratch)));
   uint32_t *sum_a = need_sum_a ? reinterpret_cast<uint32_t *>(scratch + off_sum_a) : nullptr;
@@ -337,19 +230,9 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
     b_use = scratch + off_bt;
     b_mn_use = false;
   }
-  // column-type sums accumulate with atomics into zeroed outputs: zero them before either kernel
-  if (need_sum_a && a_mn_use) MB_CUDA(ctx, cudaMemsetAsync(sum_a, 0, sizeof(uint32_t) * nb_a * M, ctx->stream));
-  if (need_sum_b && b_mn_use) MB_CUDA(ctx, cudaMemsetAsync(sum_b, 0, sizeof(uint32_t) * nb_b * N, ctx->stream));
-  if (need_sum_a) {
-    if (a_mn_use) MB_RETURN_IF_ERROR(launch_colsum(ctx, a_use, sum_a, nb_a, K, M));
-    else MB_RETURN_IF_ERROR(launch_rowsum(ctx, a_use, sum_a, nb_a * M, K));
-  }
-  if (need_sum_b) {
-    // the second sum kernel may run alongside the first (see launch_maybe_pdl)
-    const bool pdl = need_sum_a && !ctx->capturing;
-    if (b_mn_use) MB_RETURN_IF_ERROR(launch_colsum(ctx, b_use, sum_b, nb_b, K, N, pdl));
-    else MB_RETURN_IF_ERROR(launch_rowsum(ctx, b_use, sum_b, nb_b * N, K, pdl));
-  }
+  // both operands' sums in one launch (see operand_sums.cu)
+  if (need_sum_a || need_sum_b)
+    MB_RETURN_IF_ERROR(mb_operand_sums_launch(ctx, a_use, a_mn_use, nb_a, M, sum_a, b_use, b_mn_use, nb_b, N, sum_b, K));
   if (!mb_gemm_u8_tc_supported(ctx, a_use, b_use, M, N, K, a_mn_use, b_mn_use, a_batched,
                                b_batched)) {
     return launch_generic(ctx, A, B, bias, C, out_is_int32, batch, M, N, K, a_mn, b_mn,
@@ -357,10 +240,10 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
   }
   // The operand-sum kernel was the last launch: the GEMM may overlap it (programmatic
   // dependent launch); its operands were complete before that kernel started.
-  ctx->pdl_next_gemm = (need_sum_a || need_sum_b) && !ctx->capturing ? 1 : 0;
-  return mb_gemm_u8_tc_launch(ctx, a_use, b_use, sum_a, sum_b, bias, C, out_is_int32, batch, M,
-                              N, K, a_mn_use, b_mn_use, a_batched, b_batched, zp_a, zp_b, mult,
-                              shift, zp_c, bias_per_row);
+  ctx->pdl_next_gemm = (need_sum_a || need_sum_b) ? 1 : 0;
+  return mb_gemm_u8_tc_launch_sliced(ctx, a_use, b_use, sum_a, sum_b, sl_a, sl_b, bias, C, out_is_int32, batch, M,
+                                     N, K, a_mn_use, b_mn_use, a_batched, b_batched, zp_a, zp_b, mult,
+                                     shift, zp_c, bias_per_row);
 }
 
 extern "C" int mb_gemm_u8(mb_context *ctx, const uint8_t *A, const uint8_t *B,

@@ -62,12 +62,20 @@ struct TcParams {
   int64_t M, N, K, batch;
   int tiles_m, tiles_n, k_blocks;
   int64_t total_tiles;
+  // Tail splitting (256-wide tiles only).  When the last round of tiles would occupy less than
+  // half of the CTAs, its tiles are cut into two 128-column halves and handed to twice as many
+  // CTAs: the round then takes half as long.  CTA c runs full_rounds full tiles and then, if
+  // c < tail_units, the half (c & 1) of tile tail_first + c / 2.  tail_units == 0: no split.
+  int full_rounds, tail_units;
+  int64_t tail_first;
   // gridDim.x as (step_b, step_n, step_m) in tile coordinates: advancing a CTA to its next
   // tile is three additions and two carries instead of 64-bit divisions
   int step_m, step_n, step_b;
-  const uint32_t *sum_a;  // [batch or 1][M]; null when fused or zp_b == 0
-  const uint32_t *sum_b;  // [batch or 1][N]; null when fused or zp_a == 0
+  // Operand byte sums, each as `slices` partial rows that are added up here:
+  const uint32_t *sum_a;  // [batch or 1][sum_a_slices][M]; null when fused or zp_b == 0
+  const uint32_t *sum_b;  // [batch or 1][sum_b_slices][N]; null when fused or zp_a == 0
   int64_t sum_a_bstride, sum_b_bstride;
+  int sum_a_slices, sum_b_slices;
   int a_batched, b_batched;
   const int32_t *bias;
   int bias_per_row;
@@ -79,6 +87,10 @@ struct TcParams {
   void *C;
   int out_is_int32;
   int c_tma;  // uint8 C written by TMA stores (base and rows 16-byte aligned)
+  // The kernel in front of this one in the stream only computes sum_a / sum_b (the operands
+  // themselves were complete before it started): the main loop starts without waiting for it,
+  // only the preparation warps wait, where they read the sums.
+  int sums_pending;
   int *status;
   // null, or clock stamps written by CTA 0 (profiling aid): 32 milestone slots, then 5
   // slots for each of its first 16 tiles (TMA issued, tile landed, MMAs committed,
@@ -131,6 +143,23 @@ struct TileCfg {
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
+// Adds up the `slices` partial rows of an operand sum for one row / column: eight loads in
+// flight at a time (one after the other they would cost an L2 round trip each, and the terms
+// of a tile have to be ready within the tile's main loop).
+__device__ __forceinline__ uint32_t sum_partials(const uint32_t *p, int slices, int64_t stride) {
+  uint32_t a0 = 0, a1 = 0, a2 = 0, a3 = 0, a4 = 0, a5 = 0, a6 = 0, a7 = 0;
+  int sl = 0;
+  for (; sl + 8 <= slices; sl += 8) {
+    const uint32_t *q = p + sl * stride;
+    const uint32_t v0 = __ldg(q), v1 = __ldg(q + stride), v2 = __ldg(q + 2 * stride), v3 = __ldg(q + 3 * stride);
+    const uint32_t v4 = __ldg(q + 4 * stride), v5 = __ldg(q + 5 * stride), v6 = __ldg(q + 6 * stride),
+                   v7 = __ldg(q + 7 * stride);
+    a0 += v0; a1 += v1; a2 += v2; a3 += v3; a4 += v4; a5 += v5; a6 += v6; a7 += v7;
+  }
+  for (; sl < slices; ++sl) a0 += __ldg(p + sl * stride);
+  return ((a0 + a1) + (a2 + a3)) + ((a4 + a5) + (a6 + a7));
+}
+
 __device__ __forceinline__ uint32_t sum16(const uint4 v, uint32_t s) {
   s = __dp4a(v.x, 0x01010101u, s);
   s = __dp4a(v.y, 0x01010101u, s);
@@ -139,23 +168,50 @@ __device__ __forceinline__ uint32_t sum16(const uint4 v, uint32_t s) {
 }
 
 // Tile coordinates of a persistent CTA: tile index = (b * tiles_n + tn) * tiles_m + tm,
-// advanced by gridDim.x per step.
+// advanced by gridDim.x per step; half = 0 / 1 for a 128-column half of a split tail tile,
+// -1 for a whole tile.
 struct TileIter {
-  int tm, tn, b;
-  __device__ __forceinline__ TileIter(const TcParams &p) {
-    const unsigned t = blockIdx.x;  // < tiles of the first wave, one division pair per kernel
+  int tm, tn, b, half;
+  int left;  // whole tiles this CTA still has to run, this one included
+  __device__ __forceinline__ void locate(const TcParams &p, unsigned t) {  // one division pair
     tm = t % p.tiles_m;
     const unsigned q = t / p.tiles_m;
     tn = q % p.tiles_n;
     b = q / p.tiles_n;
   }
-  __device__ __forceinline__ bool valid(const TcParams &p) const { return b < p.batch; }
+  __device__ __forceinline__ TileIter(const TcParams &p) {
+    half = -1;
+    if (p.tail_units > 0) {
+      left = p.full_rounds;
+    } else {
+      left = blockIdx.x < p.total_tiles ? static_cast<int>((p.total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+    }
+    locate(p, blockIdx.x);
+    if (left == 0) enter_tail(p);
+  }
+  __device__ __forceinline__ void enter_tail(const TcParams &p) {
+    if (half < 0 && static_cast<int>(blockIdx.x) < p.tail_units) {
+      locate(p, static_cast<unsigned>(p.tail_first) + (blockIdx.x >> 1));
+      half = blockIdx.x & 1;
+    } else {
+      half = 2;  // done
+    }
+  }
+  __device__ __forceinline__ bool valid(const TcParams &) const { return half != 2; }
   __device__ __forceinline__ void next(const TcParams &p) {
-    tm += p.step_m;
-    tn += p.step_n;
-    b += p.step_b;
-    if (tm >= p.tiles_m) { tm -= p.tiles_m; ++tn; }
-    if (tn >= p.tiles_n) { tn -= p.tiles_n; ++b; }
+    if (left > 1) {
+      --left;
+      tm += p.step_m;
+      tn += p.step_n;
+      b += p.step_b;
+      if (tm >= p.tiles_m) { tm -= p.tiles_m; ++tn; }
+      if (tn >= p.tiles_n) { tn -= p.tiles_n; ++b; }
+    } else if (left == 1) {
+      left = 0;
+      enter_tail(p);
+    } else {
+      half = 2;
+    }
   }
 };
 
@@ -261,7 +317,8 @@ template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS, int KB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ CUtensorMap tmap_c, const TcParams p) {
+                  const __grid_constant__ CUtensorMap tmap_c,
+                  const __grid_constant__ CUtensorMap tmap_b_half, const TcParams p) {
   using Cfg = TileCfg<BN, B_MN, KB>;
   constexpr int STAGES = Cfg::STAGES;
   // shared-memory descriptor fields for rows of KB bytes: swizzle mode and the distance
@@ -321,9 +378,9 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // Everything above touched only this CTA's shared and tensor memory (and the kernel's
   // parameters); from here on the roles read and write global memory, which the kernel in
   // front of this one in the stream may still be producing.
-  mb_grid_dep_wait();
-
-
+  // (with sums_pending only the preparation warps, which read the sums, wait; the operands were
+  // complete before the sums kernel started, and C is not touched by it)
+  if (!p.sums_pending || (warp >= 2 && warp < 2 + PREP_WARPS)) mb_grid_dep_wait();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -341,6 +398,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
         const int b = it.b, tm = it.tm, tn = it.tn;
         const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
+        const bool half_tile = BN == 256 && it.half >= 0;  // a 128-column half of a split tail tile
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, WAIT_BUDGET)) {
             *abort_flag = 1;
@@ -352,7 +410,8 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + Cfg::A_BYTES;
           const bool skip_b = b_once && local >= STAGES;
-          mbar_arrive_expect_tx(fb, skip_b ? Cfg::A_BYTES : Cfg::STAGE_BYTES);
+          mbar_arrive_expect_tx(fb, skip_b ? Cfg::A_BYTES
+                                           : half_tile ? Cfg::A_BYTES + Cfg::B_BYTES / 2 : Cfg::STAGE_BYTES);
           if (A_MN) {
             tma_load_3d(sa, &tmap_a, fb, tm * BM, kb * KB, ab);
           } else {
@@ -360,6 +419,10 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if (skip_b) {
             // B of this stage is already in place
+          } else if (half_tile) {
+            // the half's 128 columns land at the start of the stage's B area
+            if (B_MN) tma_load_3d(sb, &tmap_b, fb, tn * BN + it.half * 128, kb * KB, bb);
+            else tma_load_3d(sb, &tmap_b_half, fb, kb * KB, tn * BN + it.half * 128, bb);
           } else if (B_MN) {
 #pragma unroll
             for (int j = 0; j < (BN + 127) / 128; ++j)
@@ -384,7 +447,8 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // queue keeps it busy, and for tiles of one K step it is on the critical path outright:
     // the descriptors are one add per step and nothing in the loop is warp-collective.
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, A_MN, B_MN, BM, BN);
+      constexpr uint32_t idesc_full = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, A_MN, B_MN, BM, BN);
+      constexpr uint32_t idesc_half = make_idesc(2, 0, 0, A_MN, B_MN, BM, 128);
       // K-major tile: rows of KB bytes, 8-row groups SBO bytes apart; a K step moves 32 bytes
       // inside the swizzled row.  MN-major tile: k-rows of 128 bytes (128 elements of M or N),
       // 8-k-row groups 1024 bytes apart, 128-element atoms 128 * KB bytes apart; a K step moves
@@ -409,6 +473,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc_buf * BN;
+        const uint32_t idesc = (BN == 256 && it.half >= 0) ? idesc_half : idesc_full;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, WAIT_BUDGET)) {
             *abort_flag = 1;
@@ -458,6 +523,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int local = 0;
     for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
       const int b = it.b, tm = it.tm, tn = it.tn;
+      const int half_off = (BN == 256 && it.half >= 0) ? it.half * 128 : 0;  // first column inside the tile
       uint32_t sa_sum = 0, sb_sum[(BN + 127) / 128];
 #pragma unroll
       for (int j = 0; j < (BN + 127) / 128; ++j) sb_sum[j] = 0;
@@ -465,14 +531,16 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int64_t m = static_cast<int64_t>(tm) * BM + r;
       int32_t row_bias = 0, col_bias[(BN + 127) / 128];
       if (p.bias != nullptr && p.bias_per_row && m < p.M) row_bias = __ldg(p.bias + m);
-      if (!FUSE_SUMS && p.sum_a != nullptr && m < p.M)
-        sa_sum = __ldg(p.sum_a + (p.a_batched ? b : 0) * p.sum_a_bstride + m);
+      if (!FUSE_SUMS && p.sum_a != nullptr && m < p.M) {
+        sa_sum = sum_partials(p.sum_a + (p.a_batched ? b : 0) * p.sum_a_bstride + m, p.sum_a_slices, p.M);
+      }
 #pragma unroll
       for (int j = 0; j < (BN + 127) / 128; ++j) {
-        const int64_t n = static_cast<int64_t>(tn) * BN + j * 128 + r;
+        const int64_t n = static_cast<int64_t>(tn) * BN + half_off + j * 128 + r;
         col_bias[j] = (p.bias != nullptr && !p.bias_per_row && n < p.N) ? __ldg(p.bias + n) : 0;
-        if (!FUSE_SUMS && p.sum_b != nullptr && n < p.N)
-          sb_sum[j] = __ldg(p.sum_b + (p.b_batched ? b : 0) * p.sum_b_bstride + n);
+        if (!FUSE_SUMS && p.sum_b != nullptr && n < p.N) {
+          sb_sum[j] = sum_partials(p.sum_b + (p.b_batched ? b : 0) * p.sum_b_bstride + n, p.sum_b_slices, p.N);
+        }
       }
       if (FUSE_SUMS) {
         for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -578,7 +646,15 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BN +
                              slice * 64;
       const int32_t *ct_base = col_term_sm + acc_buf * BN + slice * 64;
-      const int64_t n_first = static_cast<int64_t>(tn) * BN + slice * 64;
+      const bool half_tile = BN == 256 && it.half >= 0;
+      const int64_t n_first = static_cast<int64_t>(tn) * BN + (half_tile ? it.half * 128 : 0) + slice * 64;
+      if (half_tile && slice >= 2) {
+        // a half tile has two 64-column slices: the other two warp sets only return the buffer
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar + 8 * acc_buf);
+        continue;
+      }
       if (p.c_tma) {
         // one decision per tile (not per chunk or value: with so few warps per scheduler
         // a branch's latency is not hidden)
@@ -692,7 +768,7 @@ int make_map_u8(mb_context *ctx, CUtensorMap *map, const void *base, uint64_t in
 
 template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS = false, int KB = BK>
 int launch_cfg(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc,
-               TcParams &p) {
+               const CUtensorMap &tb_half, TcParams &p) {
   using Cfg = TileCfg<BN, B_MN, KB>;
   auto kern = gemm_u8_tc_kernel<BN, A_MN, B_MN, FUSE_SUMS, KB>;
   // The opt-in shared-memory limit is a per-device function attribute; set it
@@ -708,8 +784,20 @@ int launch_cfg(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, co
   p.step_m = grid % p.tiles_m;
   p.step_n = (grid / p.tiles_m) % p.tiles_n;
   p.step_b = (grid / p.tiles_m) / p.tiles_n;
+  // split the tiles of a sparsely filled last round into halves (see TcParams)
+  p.full_rounds = 0;
+  p.tail_units = 0;
+  p.tail_first = p.total_tiles;
+  if (BN == 256 && !FUSE_SUMS && ctx->split_tail && p.total_tiles > grid) {
+    const int64_t rem = p.total_tiles % grid;
+    if (rem > 0 && 2 * rem <= grid) {
+      p.full_rounds = static_cast<int>(p.total_tiles / grid);
+      p.tail_first = p.total_tiles - rem;
+      p.tail_units = static_cast<int>(2 * rem);
+    }
+  }
   ctx->pdl_next_gemm = 0;
-  MB_CUDA(ctx, mb_launch_chained(ctx, kern, dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, ta, tb, tc, p));
+  MB_CUDA(ctx, mb_launch_chained(ctx, kern, dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, ta, tb, tc, tb_half, p));
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   ctx->launches_tc++;
@@ -740,7 +828,8 @@ bool mb_gemm_u8_tc_supported(const mb_context *ctx, const void *A, const void *B
 // MN-major.  C is row-major M x N.  sum_a / sum_b are the per-row byte sums of
 // the operands (may be null when the other zero point is 0).
 static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
-                          const uint32_t *sum_a, const uint32_t *sum_b, const int32_t *bias,
+                          const uint32_t *sum_a, const uint32_t *sum_b, int sum_a_slices, int sum_b_slices,
+                          const int32_t *bias,
                           void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
                           int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
                           int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
@@ -754,27 +843,44 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   const int KBsel = (kmajor_free && K <= 32) ? 32 : (kmajor_free && K <= 64) ? 64 : BK;
   const bool fuse = kmajor_free && K <= 8 * BK && (zp_a != 0 || zp_b != 0 || KBsel != BK);
   // Tile width.  Long main loops (K > 1024) want the widest tile for operand
-  // reuse.  Short ones are bound by the epilogue, whose cost grows with the
-  // width, plus a fixed cost per tile: pick the width with the fewest rounds
-  // of (width + overhead) over the SMs.
+  // reuse -- unless that leaves most SMs without a tile (a few rows against a
+  // large B): then the width with the fewest columns per SM wins, wider on a
+  // tie, so that B streams through as many SMs as possible.  Short main loops
+  // are bound by the epilogue, whose cost grows with the width, plus a fixed
+  // cost per tile: pick the width with the fewest rounds of (width + overhead)
+  // over the SMs.
   int BN = 64;
   {
     const int64_t tm = ceil_div64(M, BM);
     const int widths[3] = {256, 128, 64};
     int64_t best = -1;
+    bool widest_seen = false, spread = false;
     for (int w : widths) {
       if (w > 64 && N <= w / 2) continue;  // more than half of the tile would be padding
-      const int64_t rounds = ceil_div64(batch * tm * ceil_div64(N, w), ctx->num_sms);
-      const int64_t cost = rounds * (w + 96);
-      if (K > 1024) {  // widest admissible width wins
-        BN = w;
-        break;
+      const int64_t tiles = batch * tm * ceil_div64(N, w);
+      const int64_t rounds = ceil_div64(tiles, ctx->num_sms);
+      if (K > 1024) {
+        if (!widest_seen) {
+          widest_seen = true;
+          BN = w;
+          if (tiles >= ctx->num_sms) break;  // every SM has work at the widest width
+          spread = true;
+          best = rounds * w;
+          continue;
+        }
+        if (spread && rounds * w < best) {
+          best = rounds * w;
+          BN = w;
+        }
+        continue;
       }
+      const int64_t cost = rounds * (w + 96);
       if (best < 0 || cost < best) {
         best = cost;
         BN = w;
       }
     }
+    if (ctx->force_bn != 0 && !(ctx->force_bn > 64 && N <= ctx->force_bn / 2)) BN = ctx->force_bn;
   }
   TcParams p;
   p.M = M; p.N = N; p.K = K; p.batch = batch;
@@ -783,7 +889,8 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.k_blocks = static_cast<int>(ceil_div64(K, KBsel));
   p.total_tiles = batch * p.tiles_m * p.tiles_n;
   p.sum_a = sum_a; p.sum_b = sum_b;
-  p.sum_a_bstride = M; p.sum_b_bstride = N;
+  p.sum_a_slices = sum_a_slices; p.sum_b_slices = sum_b_slices;
+  p.sum_a_bstride = M * sum_a_slices; p.sum_b_bstride = N * sum_b_slices;
   p.a_batched = a_batched; p.b_batched = b_batched;
   p.bias = bias; p.bias_per_row = bias_per_row;
   p.zp_a = zp_a; p.zp_b = zp_b;
@@ -798,8 +905,10 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.c_tma = (!out_is_int32 && cbase % 16 == 0 && N % 16 == 0 && N >= 64 && M >= 32) ? 1 : 0;
   p.status = ctx->dev_status;
   p.timeline = ctx->tc_timeline;
+  p.sums_pending = (ctx->pdl_next_gemm && ctx->pdl_chain && (sum_a != nullptr || sum_b != nullptr)) ? 1 : 0;
 
-  CUtensorMap ta, tb, tc;
+  CUtensorMap ta, tb, tc, tb_half;
+  memset(&tb_half, 0, sizeof(tb_half));
   if (p.c_tma) {
     // the staged box is 32 bytes wide for 256-wide tiles, else 64 (TileCfg::STG_CHUNKS)
     if (BN == 256) {
@@ -823,21 +932,23 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
     MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, N, K, nb_b, N * K, 128, BK));
   } else {
     MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, K, N, nb_b, N * K, KBsel, BN, kswz));
+    // 128-row boxes of the same matrix for the halves of split tail tiles
+    if (BN == 256) MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb_half, B, K, N, nb_b, N * K, KBsel, 128, kswz));
   }
 
 #define MB_TC_DISPATCH(BN_)                                                         \
   if (a_mn) {                                                                       \
-    if (b_mn) return launch_cfg<BN_, true, true>(ctx, ta, tb, tc, p);                   \
-    return launch_cfg<BN_, true, false>(ctx, ta, tb, tc, p);                            \
+    if (b_mn) return launch_cfg<BN_, true, true>(ctx, ta, tb, tc, tb_half, p);                   \
+    return launch_cfg<BN_, true, false>(ctx, ta, tb, tc, tb_half, p);                            \
   } else {                                                                          \
-    if (b_mn) return launch_cfg<BN_, false, true>(ctx, ta, tb, tc, p);                  \
-    return launch_cfg<BN_, false, false>(ctx, ta, tb, tc, p);                           \
+    if (b_mn) return launch_cfg<BN_, false, true>(ctx, ta, tb, tc, tb_half, p);                  \
+    return launch_cfg<BN_, false, false>(ctx, ta, tb, tc, tb_half, p);                           \
   }
   if (fuse) {
 #define MB_TC_FUSED(KB_)                                                                  \
-  if (BN == 256) return launch_cfg<256, false, false, true, KB_>(ctx, ta, tb, tc, p);     \
-  if (BN == 128) return launch_cfg<128, false, false, true, KB_>(ctx, ta, tb, tc, p);     \
-  return launch_cfg<64, false, false, true, KB_>(ctx, ta, tb, tc, p);
+  if (BN == 256) return launch_cfg<256, false, false, true, KB_>(ctx, ta, tb, tc, tb_half, p);     \
+  if (BN == 128) return launch_cfg<128, false, false, true, KB_>(ctx, ta, tb, tc, tb_half, p);     \
+  return launch_cfg<64, false, false, true, KB_>(ctx, ta, tb, tc, tb_half, p);
     if (KBsel == 32) { MB_TC_FUSED(32) }
     if (KBsel == 64) { MB_TC_FUSED(64) }
     MB_TC_FUSED(128)
@@ -855,8 +966,20 @@ int mb_gemm_u8_tc_launch(mb_context *ctx, const uint8_t *A, const uint8_t *B,
                          int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
                          int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
                          int bias_per_row) {
-  return tc_launch_impl(ctx, A, B, sum_a, sum_b, bias, C, out_is_int32, batch, M, N, K, a_mn, b_mn,
+  return tc_launch_impl(ctx, A, B, sum_a, sum_b, 1, 1, bias, C, out_is_int32, batch, M, N, K, a_mn, b_mn,
                         a_batched, b_batched, zp_a, zp_b, mult, shift, zp_c, bias_per_row, 0, 0.f, 0);
+}
+
+// The same with each operand's sums given as `slices` partial rows ([batch or 1][slices][extent]),
+// as mb_operand_sums_launch writes the column sums of an MN-major operand.
+int mb_gemm_u8_tc_launch_sliced(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+                                const uint32_t *sum_a, const uint32_t *sum_b, int sum_a_slices, int sum_b_slices,
+                                const int32_t *bias, void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
+                                int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
+                                int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
+                                int bias_per_row) {
+  return tc_launch_impl(ctx, A, B, sum_a, sum_b, sum_a_slices, sum_b_slices, bias, C, out_is_int32, batch, M, N, K,
+                        a_mn, b_mn, a_batched, b_batched, zp_a, zp_b, mult, shift, zp_c, bias_per_row, 0, 0.f, 0);
 }
 
 // The same product with the Gemv delegators' float requantization rule (see
@@ -865,6 +988,6 @@ int mb_gemm_u8_tc_launch_float_rule(mb_context *ctx, const uint8_t *A, const uin
                                     const int32_t *bias, void *C, int out_is_int32, int64_t M,
                                     int64_t N, int64_t K, int32_t zp_a, int32_t zp_b, float mult_f,
                                     int32_t zp_c, int add_zp) {
-  return tc_launch_impl(ctx, A, B, nullptr, nullptr, bias, C, out_is_int32, 1, M, N, K, false, false, 0,
+  return tc_launch_impl(ctx, A, B, nullptr, nullptr, 1, 1, bias, C, out_is_int32, 1, M, N, K, false, false, 0,
                         0, zp_a, zp_b, 1 << 30, 0, zp_c, 0, 1, mult_f, add_zp);
 }

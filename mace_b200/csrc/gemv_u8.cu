@@ -11,6 +11,7 @@
 // 128-bit loads and integer dot-product instructions.  When the matrix is shared by all
 // batch entries (the FullyConnected case) the warp keeps its row and loops over the vectors.
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace {
 
@@ -129,6 +130,148 @@ __global__ void __launch_bounds__(256) gemv_u8_kernel(const GemvParams p) {
   }
 }
 
+// ---- one vector against a large matrix: the matrix streams through shared memory ---------------
+//
+// The matrix is read exactly once and nothing else moves, so the kernel is a copy engine with
+// a dot product behind it.  A persistent grid (two CTAs per SM) divides the rows into
+// contiguous, equally long runs, one per CTA, so that every SM streams the same number of
+// bytes.  Inside a CTA each of the 8 warps owns a private ring of ST_DEPTH slots of ST_CHUNK
+// bytes; lane 0 asks for a row chunk with one untiled bulk copy (cp.async.bulk) that signals
+// the slot's mbarrier, the warp multiplies the landed chunk with the vector (staged in shared
+// memory once per CTA) and lane 0 refills the slot: up to 8 x ST_DEPTH x 4 KB are in flight per
+// CTA with no thread holding registers for them, and no warp waits for another.
+// Bounded waits: a wait that runs out sets the context's status word and the warp stops.
+constexpr int ST_CHUNK = 4096;   // bytes of a matrix row per bulk copy
+constexpr int ST_DEPTH = 3;      // slots per warp
+constexpr int ST_WARPS = 8;
+constexpr long long ST_WAIT_BUDGET = 1ll << 31;
+
+struct GemvStreamParams {
+  const uint8_t *lhs, *rhs;
+  const int32_t *bias;
+  void *out;
+  int64_t rows, K;
+  int out_is_int32, add_zp_out;
+  int32_t zp_lhs, zp_rhs, zp_out;
+  float multiplier;
+  int *status;
+};
+
+__global__ void __launch_bounds__(ST_WARPS * 32) gemv_u8_stream_kernel(const GemvStreamParams p) {
+  extern __shared__ __align__(128) uint8_t st_smem[];
+  // [ST_WARPS][ST_DEPTH][ST_CHUNK] ring, then the vector (K bytes), then the barriers
+  uint8_t *ring = st_smem;
+  uint4 *xs = reinterpret_cast<uint4 *>(st_smem + ST_WARPS * ST_DEPTH * ST_CHUNK);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(xs) + p.K);
+  __shared__ uint32_t sum_r_sm;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  mb_grid_dep_launch();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < ST_WARPS * ST_DEPTH; ++i) sm100::mbar_init(sm100::smem_u32(bars + i), 1);
+    sum_r_sm = 0;
+    abort_flag = 0;
+    sm100::fence_barrier_init();
+  }
+  __syncthreads();
+  // this CTA's rows: an equal share of the matrix, contiguous
+  const int64_t r_begin = p.rows * blockIdx.x / gridDim.x;
+  const int64_t r_end = p.rows * (blockIdx.x + 1) / gridDim.x;
+  const int chunks_per_row = static_cast<int>((p.K + ST_CHUNK - 1) / ST_CHUNK);
+  // this warp's units: (row, chunk) pairs of rows r_begin + warp, + 8, ...
+  const int64_t my_rows = r_begin + warp < r_end ? (r_end - r_begin - warp + ST_WARPS - 1) / ST_WARPS : 0;
+  const int64_t units = my_rows * chunks_per_row;
+  uint8_t *my_ring = ring + warp * (ST_DEPTH * ST_CHUNK);
+  const uint32_t my_bar = sm100::smem_u32(bars + warp * ST_DEPTH);
+  auto issue = [&](int64_t u) {  // lane 0 only
+    const int64_t row = r_begin + warp + (u / chunks_per_row) * ST_WARPS;
+    const int c = static_cast<int>(u % chunks_per_row);
+    const uint32_t bytes = static_cast<uint32_t>(min(static_cast<int64_t>(ST_CHUNK), p.K - static_cast<int64_t>(c) * ST_CHUNK));
+    const int slot = static_cast<int>(u % ST_DEPTH);
+    sm100::mbar_arrive_expect_tx(my_bar + 8 * slot, bytes);
+    sm100::bulk_load_1d(sm100::smem_u32(my_ring + slot * ST_CHUNK), p.lhs + row * p.K + static_cast<int64_t>(c) * ST_CHUNK,
+                        bytes, my_bar + 8 * slot);
+  };
+  mb_grid_dep_wait();  // from here on global memory is read
+  if (lane == 0)
+    for (int64_t u = 0; u < units && u < ST_DEPTH; ++u) issue(u);
+  // the vector and its byte sum, once per CTA, while the first chunks are on their way
+  {
+    const int nvec = static_cast<int>(p.K >> 4);
+    const uint4 *r4 = reinterpret_cast<const uint4 *>(p.rhs);
+    uint32_t part = 0;
+    for (int i = threadIdx.x; i < nvec; i += ST_WARPS * 32) {
+      const uint4 r = __ldg(r4 + i);
+      xs[i] = r;
+      part = __dp4a(r.x, 0x01010101u, part);
+      part = __dp4a(r.y, 0x01010101u, part);
+      part = __dp4a(r.z, 0x01010101u, part);
+      part = __dp4a(r.w, 0x01010101u, part);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) atomicAdd(&sum_r_sm, part);
+  }
+  __syncthreads();
+  const uint32_t sum_r = sum_r_sm;
+  const uint32_t zero_point_dot = static_cast<uint32_t>(static_cast<int64_t>(p.zp_lhs) * p.zp_rhs * p.K);
+  uint32_t dot = 0, sum_l = 0;
+  for (int64_t u = 0; u < units; ++u) {
+    const int slot = static_cast<int>(u % ST_DEPTH);
+    const uint32_t parity = static_cast<uint32_t>((u / ST_DEPTH) & 1);
+    if (!sm100::mbar_wait_warp(my_bar + 8 * slot, parity, &abort_flag, ST_WAIT_BUDGET)) {
+      abort_flag = 1;
+      if (lane == 0) atomicCAS(p.status, 0, MB_DEV_TIMEOUT_PRODUCER);
+      break;
+    }
+    const int c = static_cast<int>(u % chunks_per_row);
+    const int vec0 = c * (ST_CHUNK / 16);
+    const int nv = static_cast<int>(min(static_cast<int64_t>(ST_CHUNK / 16), (p.K >> 4) - vec0));
+    const uint4 *w4 = reinterpret_cast<const uint4 *>(my_ring + slot * ST_CHUNK);
+#pragma unroll 4
+    for (int i = lane; i < nv; i += 32) {
+      const uint4 lv = w4[i];
+      const uint4 r = xs[vec0 + i];
+      dot = __dp4a(lv.x, r.x, dot); dot = __dp4a(lv.y, r.y, dot);
+      dot = __dp4a(lv.z, r.z, dot); dot = __dp4a(lv.w, r.w, dot);
+      sum_l = __dp4a(lv.x, 0x01010101u, sum_l); sum_l = __dp4a(lv.y, 0x01010101u, sum_l);
+      sum_l = __dp4a(lv.z, 0x01010101u, sum_l); sum_l = __dp4a(lv.w, 0x01010101u, sum_l);
+    }
+    // the slot has been read (the values are in registers): refill it
+    __syncwarp();
+    if (lane == 0 && u + ST_DEPTH < units) {
+      sm100::fence_proxy_async();
+      issue(u + ST_DEPTH);
+    }
+    if (c == chunks_per_row - 1) {  // end of a row
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        sum_l += __shfl_xor_sync(0xffffffffu, sum_l, o);
+      }
+      if (lane == 0) {
+        const int64_t row = r_begin + warp + (u / chunks_per_row) * ST_WARPS;
+        int32_t ret = static_cast<int32_t>(dot - sum_l * static_cast<uint32_t>(p.zp_rhs) -
+                                           sum_r * static_cast<uint32_t>(p.zp_lhs) + zero_point_dot);
+        if (p.bias != nullptr) ret += p.bias[row];
+        if (p.out_is_int32) {
+          static_cast<int32_t *>(p.out)[row] = ret;
+        } else {
+          float v = __fmul_rn(static_cast<float>(ret), p.multiplier);
+          if (p.add_zp_out) v = __fadd_rn(v, static_cast<float>(p.zp_out));
+          static_cast<uint8_t *>(p.out)[row] = static_cast<uint8_t>(mb_saturate_round_u8(v));
+        }
+      }
+      dot = 0;
+      sum_l = 0;
+    }
+  }
+  // a warp that gave up may still have copies in flight into this CTA's shared memory: let
+  // them land before the CTA ends (bounded)
+  if (abort_flag != 0)
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+}
+
 }  // namespace
 
 bool mb_gemm_u8_tc_supported(const mb_context *ctx, const void *A, const void *B, int64_t M,
@@ -160,6 +303,30 @@ extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rh
       mb_gemm_u8_tc_supported(ctx, rhs, lhs, batch, rows, K, false, false, 0, 0)) {
     return mb_gemm_u8_tc_launch_float_rule(ctx, rhs, lhs, bias, out, out_is_int32, batch, rows, K, zp_rhs,
                                            zp_lhs, multiplier, zp_out, add_zp_out);
+  }
+  // One vector against a large matrix: the streaming kernel (see gemv_u8_stream_kernel).
+  if (batch == 1 && ctx->gemv_stream && K % 16 == 0 && K >= 256 && K <= 65536 && rows >= 2ll * ctx->num_sms &&
+      ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs)) & 15u) == 0) {
+    GemvStreamParams sp;
+    sp.lhs = lhs; sp.rhs = rhs; sp.bias = bias; sp.out = out;
+    sp.rows = rows; sp.K = K;
+    sp.out_is_int32 = out_is_int32; sp.add_zp_out = add_zp_out;
+    sp.zp_lhs = zp_lhs; sp.zp_rhs = zp_rhs; sp.zp_out = zp_out; sp.multiplier = multiplier;
+    sp.status = ctx->dev_status;
+    const size_t smem = static_cast<size_t>(ST_WARPS) * ST_DEPTH * ST_CHUNK + static_cast<size_t>(K) +
+                        sizeof(uint64_t) * ST_WARPS * ST_DEPTH;
+    constexpr uint64_t attr_bit = 1ull << 62;
+    if (!(ctx->func_attr_mask & attr_bit)) {
+      MB_CUDA(ctx, cudaFuncSetAttribute(gemv_u8_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        ST_WARPS * ST_DEPTH * ST_CHUNK + 65536 + 8 * ST_WARPS * ST_DEPTH));
+      ctx->func_attr_mask |= attr_bit;
+    }
+    const int per_sm = smem <= 110 * 1024 ? 2 : 1;
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(rows, static_cast<int64_t>(ctx->num_sms) * per_sm));
+    MB_CUDA(ctx, mb_launch_chained(ctx, gemv_u8_stream_kernel, dim3(grid), dim3(ST_WARPS * 32), smem, sp));
+    MB_CUDA(ctx, cudaGetLastError());
+    ctx->launches++;
+    return MB_SUCCESS;
   }
   GemvParams p;
   p.lhs = lhs; p.rhs = rhs; p.bias = bias; p.out = out;

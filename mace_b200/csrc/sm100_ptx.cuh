@@ -150,6 +150,17 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
                : "memory");
 }
 
+// Untiled bulk copy global -> shared of this CTA, completion counted in bytes on an mbarrier of
+// this CTA.  Both addresses 16-byte aligned, the size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void *src, uint32_t bytes,
+                                             uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
 // 3-D tiled load global -> shared of this CTA, completion counted in bytes on
 // an mbarrier of this CTA.  c0 is the innermost coordinate and must keep the
 // copy 16-byte aligned (for uint8: a multiple of 16).

@@ -200,18 +200,21 @@ class Tensor {
   template <typename T> const T *memory() const { return static_cast<const T *>(buffer_); }
   template <typename T> T *mutable_memory() { return static_cast<T *>(buffer_); }
 
+  // On failure (the allocator is out of memory) the tensor keeps its old shape and memory, so
+  // that a caller that retries later finds a consistent tensor.
   MaceStatus Resize(const std::vector<index_t> &shape) {
-    shape_ = shape;
-    const size_t need = static_cast<size_t>(raw_size());
+    size_t need = GetEnumTypeSize(dtype_);
+    for (index_t d : shape) need *= static_cast<size_t>(d);
     if (need > capacity_) {
+      void *fresh = nullptr;
+      MACE_RETURN_IF_ERROR(runtime_->New(need, &fresh));
       // (a tensor that outgrows a shared buffer leaves it and owns its memory again)
       if (buffer_ != nullptr && owns_buffer_) runtime_->Delete(buffer_);
-      buffer_ = nullptr;
-      capacity_ = 0;
-      MACE_RETURN_IF_ERROR(runtime_->New(need, &buffer_));
+      buffer_ = fresh;
       capacity_ = need;
       owns_buffer_ = true;
     }
+    shape_ = shape;
     return MaceStatus::MACE_SUCCESS;
   }
 

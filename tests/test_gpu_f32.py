@@ -71,7 +71,7 @@ def test_gemm_f32_tensor_core(ctx, orc, shape):
     assert ctx.launches_tensor_core == before + 1, "tensor-core kernel did not run"
     got = ctx.download(dC, (batch * M * N,), np.float32)
     ref = orc.gemm_f32(A, B, batch, M, N, K)
-    assert rel_err(got, ref, 1e-5, "gemm_f32_tensor_core") <= 1e-5
+    assert rel_err(got, ref, 1e-4, "gemm_f32_tensor_core") <= 1e-5  # element-wise at the specified 1e-4
     for b in (dA, dB, dC):
         b.free()
 

@@ -85,6 +85,43 @@ def test_gemv_u8(ctx, orc, shape, lhs_batched):
         b.free()
 
 
+@pytest.mark.parametrize("shape", [(4096, 4096), (1000, 1024), (300, 4112), (777, 20000), (5000, 256),
+                                   (296, 65536), (1201, 8192)])
+def test_gemv_u8_streaming_kernel(ctx, orc, shape):
+    """One vector against a large matrix runs through the bulk-copy streaming kernel (a ring of
+    row chunks per warp): rows that are not a multiple of the warp count, K below, equal to and
+    above the chunk size, with a ragged last chunk; the same bytes as the warp-per-row kernel,
+    and as the oracle."""
+    rows, K = shape
+    rng = np.random.Generator(np.random.PCG64(rows + K))
+    lhs = rng.integers(0, 256, size=(1, rows, K), dtype=np.uint8)
+    rhs = rng.integers(0, 256, size=(1, K), dtype=np.uint8)
+    bias = np.rint(rng.normal(0, 1000, size=rows)).astype(np.int32)
+    mult = np.float32(1.0 / (np.sqrt(K) * 74 * 74 * 3 / 127))
+    dl, dr, db, do = ctx.upload(lhs), ctx.upload(rhs), ctx.upload(bias), ctx.alloc(rows * 4 + 64)
+    L = __import__("mace_b200").lib()
+    for zl, zr, add_zp, out_int32 in ((127, 128, True, False), (0, 255, False, False), (120, 0, True, True)):
+        exp = orc.gemv_u8(lhs, rhs, bias, 1, rows, K, zl, zr, mult, 31, add_zp, out_int32=out_int32)
+        got = {}
+        for stream in (1, 0):
+            ctx.set_option("gemv_stream", stream)
+            try:
+                ctx._check(L.mb_memset(ctx.h, do.ptr, 0xA5, do.nbytes))
+                before = ctx.launches
+                ctx.gemv_u8(dl, dr, db, do, 1, rows, K, zl, zr, mult, 31, add_zp, out_int32=out_int32)
+                assert ctx.launches == before + 1
+                raw = ctx.download(do, (do.nbytes,), np.uint8)
+            finally:
+                ctx.set_option("gemv_stream", 1)
+            n = rows * (4 if out_int32 else 1)
+            assert (raw[n:] == 0xA5).all(), "wrote past the output"
+            got[stream] = raw[:n].view(np.int32 if out_int32 else np.uint8)
+            assert np.array_equal(got[stream], exp), (stream, zl, zr)
+    ctx.sync()
+    for b in (dl, dr, db, do):
+        b.free()
+
+
 # ---- Conv2D ------------------------------------------------------------------------
 # shapes in the style of conv_2d_test.cc:1348-1397: N, H, W, C, O, KH, KW, stride, padding
 
