@@ -564,6 +564,9 @@ def run_mobilenet(args, rank, world):
     layers = mn.build(orc, seed=0)
     rig = MobilenetRig(mn, hostapi, layers, BATCH, local, rank)
     eng, ctx = rig.eng, rig.ctx
+    for item in args.opt:  # library switches for A/B runs (mb_set_option), e.g. --opt dw_tma=0
+        name, _, value = item.partition("=")
+        assert ctx.L.mb_set_option(ctx.h, name.encode(), int(value)) == 0, "unknown option " + item
 
     def barrier():
         ctx.sync()
@@ -1225,6 +1228,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="mobilenet_v1_u8_b64: skip the records of the other configurations")
     ap.add_argument("--gemm-size", type=int, default=4096, help="gemm_u8_4096: M = N = K (1024: config 0)")
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=INT",
+                    help="mobilenet_v1_u8_b64: a library option (mb_set_option) to set before the run; repeatable")
     ap.add_argument("--profile", action="store_true",
                     help="run only the device-resident timed loop (for ncu captures)")
     args = ap.parse_args()

@@ -58,8 +58,10 @@ struct mb_context {
                                  // before it has waited for its predecessor
   int skinny_max_m = 16;         // row counts up to this take the streaming few-row GEMM
   int gemv_stream = 1;           // one-vector GEMV through the bulk-copy streaming kernel
-  int split_tail = 1;            // tensor-core GEMM: cut the tiles of a sparse last round into halves
   int force_bn = 0;              // tensor-core GEMM: 64 / 128 / 256 overrides the tile-width choice
+  int tc_rowsum = 1;             // short-K fused GEMM: A's row sums from 16 extra accumulator columns
+  int dw_tma = 1;                // depthwise 3x3 with input zero point 0: rows through shared memory by TMA
+  uint64_t dw_attr_mask = 0;     // TMA depthwise kernels whose shared-memory limit was raised
   int dw_waves = 1;              // depthwise 3x3: rounds of resident blocks the grid is sized for
   int wino_plane = 1;            // plane-at-a-time Winograd output transform (0: per-tile kernel)
   int64_t col_budget_bytes = 1ll << 30;  // im2col column matrix of the fp32 general convolution:

@@ -390,6 +390,10 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
     ctx->use_tensor_cores = value;
   } else if (strcmp(name, "mn_major") == 0) {
     ctx->use_mn_major = value;
+  } else if (strcmp(name, "tc_rowsum") == 0) {
+    ctx->tc_rowsum = value;
+  } else if (strcmp(name, "dw_tma") == 0) {
+    ctx->dw_tma = value;
   } else if (strcmp(name, "dw_waves") == 0) {
     if (value < 1) return mb_fail(ctx, MB_INVALID_ARGS, "dw_waves must be at least 1");
     ctx->dw_waves = value;
@@ -398,8 +402,6 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
     ctx->skinny_max_m = value;
   } else if (strcmp(name, "gemv_stream") == 0) {
     ctx->gemv_stream = value;
-  } else if (strcmp(name, "split_tail") == 0) {
-    ctx->split_tail = value;
   } else if (strcmp(name, "force_bn") == 0) {
     if (value != 0 && value != 64 && value != 128 && value != 256)
       return mb_fail(ctx, MB_INVALID_ARGS, "force_bn must be 0, 64, 128 or 256");

@@ -14,6 +14,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace {
 
@@ -358,6 +359,184 @@ dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows
   }
 }
 
+// ---- the same arithmetic fed from shared memory by TMA ------------------------------------------
+//
+// A CTA owns one image, a run of output rows, a tile of output columns and a chunk of CB
+// channel bytes.  Thread 0 asks for every input row the run needs at once -- one tiled TMA copy
+// per row, a box of [TWB columns x CB channels] with its own mbarrier -- so the whole tile
+// (up to ~70 KB) is in flight while the threads work on the rows that have landed; columns and
+// rows outside the image arrive as zeros, which is the input zero point of the tensors this
+// path takes (activations behind a ReLU; other zero points use the register kernel above), so
+// no thread tests a boundary.  The compute is the register kernel's: a thread owns 4 channels
+// x 4 output columns, reads the 6 (stride 1) or 9 (stride 2) pixel words of a new input row
+// from shared memory, transposes them into 4-pixel windows and multiplies with dp4a; two
+// earlier rows stay in registers.
+struct DwTmaTile {
+  int CB, G;          // channel bytes / channel groups (of 4) per CTA
+  int strips, OWT;    // 4-column strips and output columns per tile (OWT = 4 * strips)
+  int TWB;            // input columns per row box
+  int row_pitch;      // bytes between rows in shared memory (TMA wants 128-byte aligned targets)
+  int rows_out;       // output rows per CTA
+  int col_tiles, chan_chunks, segments;
+  int ring_bytes;     // shared memory for the rows (then one mbarrier per row)
+  int *status;
+};
+constexpr long long DW_WAIT_BUDGET = 1ll << 31;
+
+template <int STRIDE, int VAR>
+__global__ void __launch_bounds__(DW_THREADS, DW_BLOCKS_PER_SM)
+dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwParams p,
+                        const uint4 *__restrict__ packed, const DwTmaTile t, int weights_cached) {
+  extern __shared__ uint8_t dw_smem_raw[];
+  __shared__ int abort_flag;
+  constexpr int COLS = STRIDE == 1 ? 6 : 9;
+  mb_grid_dep_launch();
+  // TMA targets must be 128-byte aligned
+  uint8_t *dw_smem = dw_smem_raw + ((128u - (sm100::smem_u32(dw_smem_raw) & 127u)) & 127u);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(dw_smem + t.ring_bytes);
+  unsigned bid = blockIdx.x;
+  const int cc = bid % t.chan_chunks; bid /= t.chan_chunks;
+  const int ct = bid % t.col_tiles; bid /= t.col_tiles;
+  const int seg = bid % t.segments;
+  const int n = bid / t.segments;
+  const int y0 = seg * t.rows_out;
+  const int y1 = min(p.Ho, y0 + t.rows_out);
+  const int hi0 = y0 * STRIDE - p.pad_top;           // first input row of the run
+  const int rows_in = (y1 - y0 - 1) * STRIDE + 3;
+  const int row_bytes = t.TWB * t.CB;
+  if (threadIdx.x == 0) {
+    sm100::prefetch_tensormap(&tmap_in);
+    for (int r = 0; r < rows_in; ++r) sm100::mbar_init(sm100::smem_u32(bars + r), 1);
+    abort_flag = 0;
+    sm100::fence_barrier_init();
+  }
+  __syncthreads();
+  const int g = threadIdx.x % t.G, strip = threadIdx.x / t.G;
+  const int groups = p.C >> 2;
+  const int gg = cc * t.G + g;  // channel group in the tensor
+  if (!weights_cached) mb_grid_dep_wait();
+  uint4 w1[3][2];
+#pragma unroll
+  for (int kh = 0; kh < 3; ++kh) {
+    w1[kh][0] = __ldg(packed + (kh * 2 + 0) * groups + gg);
+    if (STRIDE == 1) w1[kh][1] = __ldg(packed + (kh * 2 + 1) * groups + gg);
+    else w1[kh][1] = w1[kh][0];
+  }
+  const uint4 st4 = __ldg(packed + 12 * groups + gg);
+  const uint4 flags = __ldg(packed + 13 * groups + gg);
+  const int32_t start[4] = {static_cast<int32_t>(st4.x), static_cast<int32_t>(st4.y),
+                            static_cast<int32_t>(st4.z), static_cast<int32_t>(st4.w)};
+  const bool has_w2 = flags.x != 0;
+  if (weights_cached) mb_grid_dep_wait();
+  if (threadIdx.x == 0) {
+    const int xi0 = ct * t.OWT * STRIDE - p.pad_left;
+    for (int r = 0; r < rows_in; ++r) {
+      const uint32_t bar = sm100::smem_u32(bars + r);
+      sm100::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(row_bytes));
+      sm100::tma_load_4d(sm100::smem_u32(dw_smem + r * t.row_pitch), &tmap_in, bar, cc * t.CB, xi0, hi0 + r, n);
+    }
+  }
+  const int x0 = ct * t.OWT + strip * 4;
+  if (strip >= t.strips || x0 >= p.Wo) return;  // (no CTA-wide barrier follows)
+  const int valid_cols = min(4, p.Wo - x0);
+  const uint32_t out_row_stride = static_cast<uint32_t>(p.Wo) * p.C;
+  const uint32_t out_off = static_cast<uint32_t>(n) * static_cast<uint32_t>(p.Ho) * out_row_stride + gg * 4 +
+                           static_cast<uint32_t>(x0) * p.C;
+  uint8_t *__restrict__ out = p.out;
+  const uint32_t *sm32 = reinterpret_cast<const uint32_t *>(dw_smem);
+  const int row_words = t.row_pitch >> 2;
+  const int thread_word = strip * 4 * STRIDE * t.G + g;  // this thread's first pixel word inside a row
+  bool ok = true;
+
+  // the pixel words of input row r of the run (r = 0 is input row hi0), once they have landed
+  auto read_row = [&](int r, DwRaw<STRIDE> &raw) {
+    if (!sm100::mbar_wait(sm100::smem_u32(bars + r), 0, &abort_flag, DW_WAIT_BUDGET)) {
+      abort_flag = 1;
+      atomicCAS(t.status, 0, MB_DEV_TIMEOUT_PRODUCER);
+      ok = false;
+    }
+    const uint32_t *w = sm32 + r * row_words + thread_word;
+#pragma unroll
+    for (int j = 0; j < COLS; ++j) raw.q[j] = w[j * t.G];
+  };
+  auto emit = [&](int y, const DwRow<STRIDE> &r0, const DwRow<STRIDE> &r1, const DwRow<STRIDE> &r2) {
+    int32_t acc[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[j][c] = start[c];
+    dw_mac<STRIDE>(acc, r0, w1[0][0], w1[0][1]);
+    dw_mac<STRIDE>(acc, r1, w1[1][0], w1[1][1]);
+    dw_mac<STRIDE>(acc, r2, w1[2][0], w1[2][1]);
+    if (has_w2) {
+      dw_mac<STRIDE>(acc, r0, __ldg(packed + 6 * groups + gg), __ldg(packed + 7 * groups + gg));
+      dw_mac<STRIDE>(acc, r1, __ldg(packed + 8 * groups + gg), __ldg(packed + 9 * groups + gg));
+      dw_mac<STRIDE>(acc, r2, __ldg(packed + 10 * groups + gg), __ldg(packed + 11 * groups + gg));
+    }
+    uint32_t o = out_off + static_cast<uint32_t>(y) * out_row_stride;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t word;
+      if (VAR >= 4) {
+        word = mb_requant_pack4<VAR == 5>(acc[j][0], acc[j][1], acc[j][2], acc[j][3], p.rq);
+      } else {
+        uint32_t b[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) b[c] = mb_requant_t<(VAR & 1) != 0, (VAR & 2) != 0>(acc[j][c], p.rq);
+        word = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+      }
+      if (j < valid_cols) *reinterpret_cast<uint32_t *>(out + o) = word;
+      o += p.C;
+    }
+  };
+
+  DwRaw<STRIDE> raw;
+  DwRow<STRIDE> ra, rb, rc;
+  if constexpr (STRIDE == 1) {
+    read_row(0, raw);
+    dw_transpose<STRIDE>(raw, ra);
+    read_row(1, raw);
+    dw_transpose<STRIDE>(raw, rb);
+    for (int y = y0; y < y1 && ok; y += 3) {
+      const int r = y - y0 + 2;  // run-relative index of the output row's last input row
+      read_row(r, raw);
+      dw_transpose<STRIDE>(raw, rc);
+      emit(y, ra, rb, rc);
+      if (y + 1 < y1) {
+        read_row(r + 1, raw);
+        dw_transpose<STRIDE>(raw, ra);
+        emit(y + 1, rb, rc, ra);
+      }
+      if (y + 2 < y1) {
+        read_row(r + 2, raw);
+        dw_transpose<STRIDE>(raw, rb);
+        emit(y + 2, rc, ra, rb);
+      }
+    }
+  } else {
+    read_row(0, raw);
+    dw_transpose<STRIDE>(raw, ra);
+    for (int y = y0; y < y1 && ok; y += 2) {
+      const int r = (y - y0) * 2;
+      read_row(r + 1, raw);
+      dw_transpose<STRIDE>(raw, rb);
+      read_row(r + 2, raw);
+      dw_transpose<STRIDE>(raw, rc);
+      emit(y, ra, rb, rc);
+      if (y + 1 < y1) {
+        read_row(r + 3, raw);
+        dw_transpose<STRIDE>(raw, rb);
+        read_row(r + 4, raw);
+        dw_transpose<STRIDE>(raw, ra);
+        emit(y + 1, rc, rb, ra);
+      }
+    }
+  }
+  // a thread that gave up may leave copies in flight into this CTA's shared memory: let them land
+  if (!ok)
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+}
+
 // General path: any filter size, stride, dilation, channel multiplier and
 // channel count; one thread per output element.
 __global__ void __launch_bounds__(256) dwconv_u8_general_kernel(const DwParams p) {
@@ -446,6 +625,111 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
       MB_CUDA(ctx, cudaGetLastError());
       ctx->launches++;
       packed = fresh;
+    }
+    // Tensors whose out-of-image taps read as zero (input zero point 0, the activations behind a
+    // ReLU) with channel counts TMA can address: rows are fed through shared memory by TMA.
+    if (ctx->dw_tma && zp_in == 0 && C % 16 == 0 && ctx->encode_tiled != nullptr &&
+        (reinterpret_cast<uintptr_t>(in) & 15u) == 0 && H < (1 << 20) && W < (1 << 20)) {
+      DwTmaTile t;
+      // channel chunk: as many channel groups per CTA as fit 256 threads next to a column tile
+      // that wastes the fewest threads (a tile is strips of 4 output columns)
+      int best_cb = 0;
+      double best_waste = 0.0;
+      for (int cb = 16; cb <= 256 && cb <= C; cb <<= 1) {  // (a TMA box holds at most 256 elements per dimension)
+        if (C % cb != 0) continue;
+        const int strips = DW_THREADS / (cb / 4);
+        if (strips < 1) continue;
+        int owt = strips * 4;
+        if (stride_h == 2 && owt * 2 + 1 > 256) owt = 124;  // a TMA box holds at most 256 columns
+        if (stride_h == 1 && owt + 2 > 256) owt = 252;
+        const int64_t tiles = ceil_div64(Wo, owt);
+        const double waste = static_cast<double>(tiles * strips * 4) / static_cast<double>(Wo);
+        if (best_cb == 0 || waste < best_waste - 1e-9 || (waste < best_waste + 1e-9 && cb > best_cb)) {
+          best_cb = cb;
+          best_waste = waste;
+        }
+      }
+      if (best_cb != 0) {
+        t.CB = best_cb;
+        t.G = best_cb / 4;
+        t.strips = DW_THREADS / t.G;
+        t.OWT = t.strips * 4;
+        if (stride_h == 2 && t.OWT * 2 + 1 > 256) { t.OWT = 124; t.strips = 31; }
+        if (stride_h == 1 && t.OWT + 2 > 256) { t.OWT = 252; t.strips = 63; }
+        t.TWB = stride_h == 1 ? t.OWT + 2 : t.OWT * 2 + 1;
+        t.col_tiles = static_cast<int>(ceil_div64(Wo, t.OWT));
+        t.chan_chunks = static_cast<int>(C / t.CB);
+        const int row_bytes = t.TWB * t.CB;
+        t.row_pitch = static_cast<int>(align_up(static_cast<size_t>(row_bytes), 128));
+        // output rows per CTA: what ~72 KB of input rows allow (two CTAs per SM), fewer when
+        // that would leave SMs without a CTA
+        const int max_rows_in = std::max(3, (72 * 1024) / t.row_pitch);
+        int rows_out = std::max(1, (max_rows_in - 3) / stride_h + 1);
+        rows_out = static_cast<int>(std::min<int64_t>(rows_out, Ho));
+        const int64_t per_seg = N * t.col_tiles * t.chan_chunks;
+        while (rows_out > 2 && per_seg * ceil_div64(Ho, rows_out) < 2ll * ctx->num_sms) rows_out = (rows_out + 1) / 2;
+        t.rows_out = rows_out;
+        t.segments = static_cast<int>(ceil_div64(Ho, rows_out));
+        const int rows_in = (rows_out - 1) * stride_h + 3;
+        t.ring_bytes = rows_in * t.row_pitch;
+        t.status = ctx->dev_status;
+        const size_t smem = static_cast<size_t>(t.ring_bytes) + sizeof(uint64_t) * rows_in + 128 /* alignment */;
+        const int64_t grid64 = per_seg * t.segments;
+        if (smem <= 100 * 1024 && grid64 < (1ll << 31) && row_bytes % 16 == 0) {
+          CUtensorMap tmap;
+          const cuuint64_t dims[4] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(W),
+                                      static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(N)};
+          const cuuint64_t strides[3] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(W * C),
+                                         static_cast<cuuint64_t>(H * W * C)};
+          const cuuint32_t box[4] = {static_cast<cuuint32_t>(t.CB), static_cast<cuuint32_t>(t.TWB), 1, 1};
+          const cuuint32_t estr[4] = {1, 1, 1, 1};
+          typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                            const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                            CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                            CUtensorMapFloatOOBfill);
+          const CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
+              &tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t *>(in), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+          if (r != CUDA_SUCCESS)
+            return mb_fail(ctx, MB_RUNTIME_ERROR, "cuTensorMapEncodeTiled (depthwise input) failed (%d)", static_cast<int>(r));
+          const int var = mb_requant_variant(right_shift, zp_out);
+#define MB_DW_TMA_LAUNCH(S, V)                                                                              \
+  do {                                                                                                      \
+    auto kern = dwconv3x3_u8_tma_kernel<S, V>;                                                              \
+    const uint64_t bit = 1ull << ((S - 1) * 6 + V);                                                         \
+    if (!(ctx->dw_attr_mask & bit)) {                                                                       \
+      MB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 101 * 1024));    \
+      ctx->dw_attr_mask |= bit;                                                                             \
+    }                                                                                                       \
+    MB_CUDA(ctx, mb_launch_chained(ctx, kern, dim3(static_cast<unsigned>(grid64)), dim3(DW_THREADS), smem,  \
+                                   tmap, p, packed, t, weights_cached));                                    \
+  } while (0)
+          if (stride_h == 1) {
+            switch (var) {
+              case 5: MB_DW_TMA_LAUNCH(1, 5); break;
+              case 4: MB_DW_TMA_LAUNCH(1, 4); break;
+              case 3: MB_DW_TMA_LAUNCH(1, 3); break;
+              case 2: MB_DW_TMA_LAUNCH(1, 2); break;
+              case 1: MB_DW_TMA_LAUNCH(1, 1); break;
+              default: MB_DW_TMA_LAUNCH(1, 0); break;
+            }
+          } else {
+            switch (var) {
+              case 5: MB_DW_TMA_LAUNCH(2, 5); break;
+              case 4: MB_DW_TMA_LAUNCH(2, 4); break;
+              case 3: MB_DW_TMA_LAUNCH(2, 3); break;
+              case 2: MB_DW_TMA_LAUNCH(2, 2); break;
+              case 1: MB_DW_TMA_LAUNCH(2, 1); break;
+              default: MB_DW_TMA_LAUNCH(2, 0); break;
+            }
+          }
+#undef MB_DW_TMA_LAUNCH
+          MB_CUDA(ctx, cudaGetLastError());
+          ctx->launches++;
+          return MB_SUCCESS;
+        }
+      }
     }
     // Rows per thread: the longest runs for which all blocks are resident at once (two
     // 256-thread blocks per SM), so that there is no partial last wave; tensors too large

@@ -62,12 +62,7 @@ struct TcParams {
   int64_t M, N, K, batch;
   int tiles_m, tiles_n, k_blocks;
   int64_t total_tiles;
-  // Tail splitting (256-wide tiles only).  When the last round of tiles would occupy less than
-  // half of the CTAs, its tiles are cut into two 128-column halves and handed to twice as many
-  // CTAs: the round then takes half as long.  CTA c runs full_rounds full tiles and then, if
-  // c < tail_units, the half (c & 1) of tile tail_first + c / 2.  tail_units == 0: no split.
-  int full_rounds, tail_units;
-  int64_t tail_first;
+
   // gridDim.x as (step_b, step_n, step_m) in tile coordinates: advancing a CTA to its next
   // tile is three additions and two carries instead of 64-bit divisions
   int step_m, step_n, step_b;
@@ -120,12 +115,22 @@ struct TcParams {
   } while (0)
 #endif
 
-template <int BN, bool B_MN, int KB = BK>
+// TCR ("row sums on the tensor core"): the B tile of every stage is followed by 16 constant rows
+// of ones, and the MMA runs with N = BN + 16: accumulator columns BN .. BN + 15 of row m then
+// hold the byte sum of A's row m, which the zero-point correction needs, at the price of an
+// eighth (BN = 128) or a quarter (BN = 64) more work for a tensor pipe that short-K tiles leave
+// idle anyway -- instead of a pass of the preparation warps over every A tile in shared memory,
+// which cost these issue-bound kernels a fifth of their instructions.
+template <int BN, bool B_MN, int KB = BK, bool TCR = false>
 struct TileCfg {
   static_assert(KB == 128 || !B_MN, "short rows are for K-major operands");
+  static_assert(!TCR || (!B_MN && BN <= 128), "ones rows follow a K-major B tile of at most 128 rows");
+  static constexpr int BNX = TCR ? BN + 16 : BN;  // MMA N and TMEM columns per accumulator
   static constexpr int A_BYTES = BM * KB;
-  static constexpr int B_BYTES = B_MN ? ((BN + 127) / 128) * 128 * KB : BN * KB;
+  static constexpr int B_TMA_BYTES = B_MN ? ((BN + 127) / 128) * 128 * KB : BN * KB;  // what TMA brings
+  static constexpr int B_BYTES = B_TMA_BYTES + (TCR ? 16 * KB : 0);
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGE_TX = A_BYTES + B_TMA_BYTES;
   // epilogue staging for the TMA stores: 1 KB (32 rows x 32 bytes) per epilogue warp
   // ... 2 KB (32 rows x 64 bytes: one store per warp and tile) where the ring leaves room
   static constexpr int STG_CHUNKS = BN == 256 ? 2 : 4;   // 16-byte chunks per staged row
@@ -134,7 +139,7 @@ struct TileCfg {
   static constexpr int STAGES = RING_BUDGET / STAGE_BYTES > 8 ? 8 : RING_BUDGET / STAGE_BYTES;
   // all 512 TMEM columns as accumulator buffers: 2 for BN = 256, 4 for 128, 8 for 64, so
   // that narrow tiles (short main loops) keep several tiles in flight
-  static constexpr int NUM_ACC = 512 / BN;
+  static constexpr int NUM_ACC = 512 / BNX;
   static constexpr int TMEM_COLS = 512;
   static constexpr int BAR_BYTES = 512;
   static constexpr int TERM_BYTES = NUM_ACC * (128 + BN) * 4;
@@ -168,50 +173,23 @@ __device__ __forceinline__ uint32_t sum16(const uint4 v, uint32_t s) {
 }
 
 // Tile coordinates of a persistent CTA: tile index = (b * tiles_n + tn) * tiles_m + tm,
-// advanced by gridDim.x per step; half = 0 / 1 for a 128-column half of a split tail tile,
-// -1 for a whole tile.
+// advanced by gridDim.x per step.
 struct TileIter {
-  int tm, tn, b, half;
-  int left;  // whole tiles this CTA still has to run, this one included
-  __device__ __forceinline__ void locate(const TcParams &p, unsigned t) {  // one division pair
+  int tm, tn, b;
+  __device__ __forceinline__ TileIter(const TcParams &p) {
+    const unsigned t = blockIdx.x;  // < tiles of the first wave, one division pair per kernel
     tm = t % p.tiles_m;
     const unsigned q = t / p.tiles_m;
     tn = q % p.tiles_n;
     b = q / p.tiles_n;
   }
-  __device__ __forceinline__ TileIter(const TcParams &p) {
-    half = -1;
-    if (p.tail_units > 0) {
-      left = p.full_rounds;
-    } else {
-      left = blockIdx.x < p.total_tiles ? static_cast<int>((p.total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
-    }
-    locate(p, blockIdx.x);
-    if (left == 0) enter_tail(p);
-  }
-  __device__ __forceinline__ void enter_tail(const TcParams &p) {
-    if (half < 0 && static_cast<int>(blockIdx.x) < p.tail_units) {
-      locate(p, static_cast<unsigned>(p.tail_first) + (blockIdx.x >> 1));
-      half = blockIdx.x & 1;
-    } else {
-      half = 2;  // done
-    }
-  }
-  __device__ __forceinline__ bool valid(const TcParams &) const { return half != 2; }
+  __device__ __forceinline__ bool valid(const TcParams &p) const { return b < p.batch; }
   __device__ __forceinline__ void next(const TcParams &p) {
-    if (left > 1) {
-      --left;
-      tm += p.step_m;
-      tn += p.step_n;
-      b += p.step_b;
-      if (tm >= p.tiles_m) { tm -= p.tiles_m; ++tn; }
-      if (tn >= p.tiles_n) { tn -= p.tiles_n; ++b; }
-    } else if (left == 1) {
-      left = 0;
-      enter_tail(p);
-    } else {
-      half = 2;
-    }
+    tm += p.step_m;
+    tn += p.step_n;
+    b += p.step_b;
+    if (tm >= p.tiles_m) { tm -= p.tiles_m; ++tn; }
+    if (tn >= p.tiles_n) { tn -= p.tiles_n; ++b; }
   }
 };
 
@@ -313,14 +291,18 @@ __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS, int KB>
+template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS, int KB, bool TCR_ON = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ CUtensorMap tmap_c,
-                  const __grid_constant__ CUtensorMap tmap_b_half, const TcParams p) {
-  using Cfg = TileCfg<BN, B_MN, KB>;
+                  const __grid_constant__ CUtensorMap tmap_c, const TcParams p) {
+  constexpr bool TCR = TCR_ON && FUSE_SUMS && BN <= 128;
+  using Cfg = TileCfg<BN, B_MN, KB, TCR>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int BNX = Cfg::BNX;
+  // the preparation warps read the operand tiles in shared memory only for the sums the tensor
+  // core does not deliver: B's (needed when zp_a != 0), and A's without the ones rows
+  const bool prep_reads_tiles = FUSE_SUMS && ((!TCR && p.zp_b != 0) || p.zp_a != 0);
   // shared-memory descriptor fields for rows of KB bytes: swizzle mode and the distance
   // between 8-row groups
   constexpr uint32_t SWZ = KB == 128 ? 2u : KB == 64 ? 4u : 6u;
@@ -356,7 +338,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (p.c_tma) prefetch_tensormap(&tmap_c);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar + 8 * s, 1);
-      mbar_init(empty_bar + 8 * s, FUSE_SUMS ? 1 + PREP_WARPS : 1);
+      mbar_init(empty_bar + 8 * s, prep_reads_tiles ? 1 + PREP_WARPS : 1);
     }
     for (int b = 0; b < NUM_ACC; ++b) {
       mbar_init(tfull_bar + 8 * b, 1);
@@ -369,6 +351,16 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
     tmem_relinquish();
+  }
+  if (TCR) {
+    // the 16 rows of ones behind every stage's B tile (TMA never writes there)
+    constexpr int ONES_VECS = 16 * KB / 16;
+    for (int i = threadIdx.x; i < STAGES * ONES_VECS; i += NUM_THREADS) {
+      const int st = i / ONES_VECS, v = i - st * ONES_VECS;
+      *reinterpret_cast<uint4 *>(smem_aligned + st * Cfg::STAGE_BYTES + Cfg::A_BYTES + Cfg::B_TMA_BYTES + v * 16) =
+          make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+    }
+    fence_proxy_async();  // generic-proxy writes, read by the tensor core through the async proxy
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -398,7 +390,6 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
         const int b = it.b, tm = it.tm, tn = it.tn;
         const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
-        const bool half_tile = BN == 256 && it.half >= 0;  // a 128-column half of a split tail tile
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, WAIT_BUDGET)) {
             *abort_flag = 1;
@@ -410,8 +401,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + Cfg::A_BYTES;
           const bool skip_b = b_once && local >= STAGES;
-          mbar_arrive_expect_tx(fb, skip_b ? Cfg::A_BYTES
-                                           : half_tile ? Cfg::A_BYTES + Cfg::B_BYTES / 2 : Cfg::STAGE_BYTES);
+          mbar_arrive_expect_tx(fb, skip_b ? Cfg::A_BYTES : Cfg::STAGE_TX);
           if (A_MN) {
             tma_load_3d(sa, &tmap_a, fb, tm * BM, kb * KB, ab);
           } else {
@@ -419,10 +409,6 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if (skip_b) {
             // B of this stage is already in place
-          } else if (half_tile) {
-            // the half's 128 columns land at the start of the stage's B area
-            if (B_MN) tma_load_3d(sb, &tmap_b, fb, tn * BN + it.half * 128, kb * KB, bb);
-            else tma_load_3d(sb, &tmap_b_half, fb, kb * KB, tn * BN + it.half * 128, bb);
           } else if (B_MN) {
 #pragma unroll
             for (int j = 0; j < (BN + 127) / 128; ++j)
@@ -447,8 +433,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // queue keeps it busy, and for tiles of one K step it is on the critical path outright:
     // the descriptors are one add per step and nothing in the loop is warp-collective.
     if (lane == 0) {
-      constexpr uint32_t idesc_full = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, A_MN, B_MN, BM, BN);
-      constexpr uint32_t idesc_half = make_idesc(2, 0, 0, A_MN, B_MN, BM, 128);
+      constexpr uint32_t idesc = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, A_MN, B_MN, BM, BNX);
       // K-major tile: rows of KB bytes, 8-row groups SBO bytes apart; a K step moves 32 bytes
       // inside the swizzled row.  MN-major tile: k-rows of 128 bytes (128 elements of M or N),
       // 8-k-row groups 1024 bytes apart, 128-element atoms 128 * KB bytes apart; a K step moves
@@ -472,8 +457,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc_buf * BN;
-        const uint32_t idesc = (BN == 256 && it.half >= 0) ? idesc_half : idesc_full;
+        const uint32_t d_tmem = tmem_base + acc_buf * BNX;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, WAIT_BUDGET)) {
             *abort_flag = 1;
@@ -523,7 +507,6 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int local = 0;
     for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
       const int b = it.b, tm = it.tm, tn = it.tn;
-      const int half_off = (BN == 256 && it.half >= 0) ? it.half * 128 : 0;  // first column inside the tile
       uint32_t sa_sum = 0, sb_sum[(BN + 127) / 128];
 #pragma unroll
       for (int j = 0; j < (BN + 127) / 128; ++j) sb_sum[j] = 0;
@@ -536,13 +519,14 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
 #pragma unroll
       for (int j = 0; j < (BN + 127) / 128; ++j) {
-        const int64_t n = static_cast<int64_t>(tn) * BN + half_off + j * 128 + r;
+        const int64_t n = static_cast<int64_t>(tn) * BN + j * 128 + r;
         col_bias[j] = (p.bias != nullptr && !p.bias_per_row && n < p.N) ? __ldg(p.bias + n) : 0;
         if (!FUSE_SUMS && p.sum_b != nullptr && n < p.N) {
           sb_sum[j] = sum_partials(p.sum_b + (p.b_batched ? b : 0) * p.sum_b_bstride + n, p.sum_b_slices, p.N);
         }
       }
-      if (FUSE_SUMS) {
+      if (prep_reads_tiles) {
+        const bool want_a = !TCR && p.zp_b != 0, want_b = p.zp_a != 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_warp(full_bar + 8 * stage, phase, abort_flag, WAIT_BUDGET)) {
             *abort_flag = 1;
@@ -555,13 +539,15 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // a row is KB bytes = KB / 16 chunks of 16; start at chunk (r mod chunks) so that
           // the threads of a quarter warp spread over the bank groups.  The swizzle only
           // permutes chunks inside a row, which a sum does not see.
+          if (want_a) {
 #pragma unroll
-          for (int i = 0; i < KB / 16; ++i)
-            sa_sum = sum16(*reinterpret_cast<const uint4 *>(ta + r * KB + ((i + r) & (KB / 16 - 1)) * 16), sa_sum);
+            for (int i = 0; i < KB / 16; ++i)
+              sa_sum = sum16(*reinterpret_cast<const uint4 *>(ta + r * KB + ((i + r) & (KB / 16 - 1)) * 16), sa_sum);
+          }
 #pragma unroll
           for (int j = 0; j < (BN + 127) / 128; ++j) {
             const int row = j * 128 + r;
-            if (row < BN) {
+            if (want_b && row < BN) {
 #pragma unroll
               for (int i = 0; i < KB / 16; ++i)
                 sb_sum[j] = sum16(*reinterpret_cast<const uint4 *>(tb + row * KB + ((i + r) & (KB / 16 - 1)) * 16),
@@ -642,19 +628,18 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int m0 = tm * BM + quarter * 32;           // first row of this warp
       const int64_t m = static_cast<int64_t>(m0) + lane;
       const bool row_ok = m < p.M;
-      const int32_t row_term = row_term_sm[acc_buf * 128 + quarter * 32 + lane];
-      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BN +
+      int32_t row_term = row_term_sm[acc_buf * 128 + quarter * 32 + lane];
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BNX +
                              slice * 64;
-      const int32_t *ct_base = col_term_sm + acc_buf * BN + slice * 64;
-      const bool half_tile = BN == 256 && it.half >= 0;
-      const int64_t n_first = static_cast<int64_t>(tn) * BN + (half_tile ? it.half * 128 : 0) + slice * 64;
-      if (half_tile && slice >= 2) {
-        // a half tile has two 64-column slices: the other two warp sets only return the buffer
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar + 8 * acc_buf);
-        continue;
+      if (TCR) {
+        // columns BN .. BN + 15 of this lane's row: the byte sum of A's row (all 16 alike)
+        uint32_t ones_cols[CHUNK];
+        tmem_ld_32x32b_x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc_buf * BNX + BN, ones_cols);
+        tmem_ld_wait_x16(ones_cols);
+        row_term -= p.zp_b * static_cast<int32_t>(ones_cols[0]);
       }
+      const int32_t *ct_base = col_term_sm + acc_buf * BN + slice * 64;
+      const int64_t n_first = static_cast<int64_t>(tn) * BN + slice * 64;
       if (p.c_tma) {
         // one decision per tile (not per chunk or value: with so few warps per scheduler
         // a branch's latency is not hidden)
@@ -766,15 +751,15 @@ int make_map_u8(mb_context *ctx, CUtensorMap *map, const void *base, uint64_t in
   return MB_SUCCESS;
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS = false, int KB = BK>
+template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS = false, int KB = BK, bool TCR_ON = false>
 int launch_cfg(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc,
-               const CUtensorMap &tb_half, TcParams &p) {
-  using Cfg = TileCfg<BN, B_MN, KB>;
-  auto kern = gemm_u8_tc_kernel<BN, A_MN, B_MN, FUSE_SUMS, KB>;
+               TcParams &p) {
+  using Cfg = TileCfg<BN, B_MN, KB, TCR_ON && FUSE_SUMS && BN <= 128>;
+  auto kern = gemm_u8_tc_kernel<BN, A_MN, B_MN, FUSE_SUMS, KB, TCR_ON>;
   // The opt-in shared-memory limit is a per-device function attribute; set it
   // once per context.
   constexpr int cfg_id = (BN == 256 ? 0 : BN == 128 ? 1 : 2) * 4 + (A_MN ? 2 : 0) + (B_MN ? 1 : 0) +
-                         (FUSE_SUMS ? 12 : 0) + (KB == 64 ? 3 : KB == 32 ? 6 : 0);
+                         (FUSE_SUMS ? 12 : 0) + (KB == 64 ? 3 : KB == 32 ? 6 : 0) + (TCR_ON ? 24 : 0);
   if (!(ctx->func_attr_mask & (1ull << cfg_id))) {
     MB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg::SMEM_BYTES));
@@ -784,20 +769,8 @@ int launch_cfg(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, co
   p.step_m = grid % p.tiles_m;
   p.step_n = (grid / p.tiles_m) % p.tiles_n;
   p.step_b = (grid / p.tiles_m) / p.tiles_n;
-  // split the tiles of a sparsely filled last round into halves (see TcParams)
-  p.full_rounds = 0;
-  p.tail_units = 0;
-  p.tail_first = p.total_tiles;
-  if (BN == 256 && !FUSE_SUMS && ctx->split_tail && p.total_tiles > grid) {
-    const int64_t rem = p.total_tiles % grid;
-    if (rem > 0 && 2 * rem <= grid) {
-      p.full_rounds = static_cast<int>(p.total_tiles / grid);
-      p.tail_first = p.total_tiles - rem;
-      p.tail_units = static_cast<int>(2 * rem);
-    }
-  }
   ctx->pdl_next_gemm = 0;
-  MB_CUDA(ctx, mb_launch_chained(ctx, kern, dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, ta, tb, tc, tb_half, p));
+  MB_CUDA(ctx, mb_launch_chained(ctx, kern, dim3(grid), dim3(NUM_THREADS), Cfg::SMEM_BYTES, ta, tb, tc, p));
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   ctx->launches_tc++;
@@ -907,8 +880,7 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.timeline = ctx->tc_timeline;
   p.sums_pending = (ctx->pdl_next_gemm && ctx->pdl_chain && (sum_a != nullptr || sum_b != nullptr)) ? 1 : 0;
 
-  CUtensorMap ta, tb, tc, tb_half;
-  memset(&tb_half, 0, sizeof(tb_half));
+  CUtensorMap ta, tb, tc;
   if (p.c_tma) {
     // the staged box is 32 bytes wide for 256-wide tiles, else 64 (TileCfg::STG_CHUNKS)
     if (BN == 256) {
@@ -932,23 +904,25 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
     MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, N, K, nb_b, N * K, 128, BK));
   } else {
     MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, K, N, nb_b, N * K, KBsel, BN, kswz));
-    // 128-row boxes of the same matrix for the halves of split tail tiles
-    if (BN == 256) MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb_half, B, K, N, nb_b, N * K, KBsel, 128, kswz));
   }
 
 #define MB_TC_DISPATCH(BN_)                                                         \
   if (a_mn) {                                                                       \
-    if (b_mn) return launch_cfg<BN_, true, true>(ctx, ta, tb, tc, tb_half, p);                   \
-    return launch_cfg<BN_, true, false>(ctx, ta, tb, tc, tb_half, p);                            \
+    if (b_mn) return launch_cfg<BN_, true, true>(ctx, ta, tb, tc, p);                   \
+    return launch_cfg<BN_, true, false>(ctx, ta, tb, tc, p);                            \
   } else {                                                                          \
-    if (b_mn) return launch_cfg<BN_, false, true>(ctx, ta, tb, tc, tb_half, p);                  \
-    return launch_cfg<BN_, false, false>(ctx, ta, tb, tc, tb_half, p);                           \
+    if (b_mn) return launch_cfg<BN_, false, true>(ctx, ta, tb, tc, p);                  \
+    return launch_cfg<BN_, false, false>(ctx, ta, tb, tc, p);                           \
   }
   if (fuse) {
 #define MB_TC_FUSED(KB_)                                                                  \
-  if (BN == 256) return launch_cfg<256, false, false, true, KB_>(ctx, ta, tb, tc, tb_half, p);     \
-  if (BN == 128) return launch_cfg<128, false, false, true, KB_>(ctx, ta, tb, tc, tb_half, p);     \
-  return launch_cfg<64, false, false, true, KB_>(ctx, ta, tb, tc, tb_half, p);
+  if (BN == 256) return launch_cfg<256, false, false, true, KB_>(ctx, ta, tb, tc, p);     \
+  if (ctx->tc_rowsum) {                                                                            \
+    if (BN == 128) return launch_cfg<128, false, false, true, KB_, true>(ctx, ta, tb, tc, p); \
+    return launch_cfg<64, false, false, true, KB_, true>(ctx, ta, tb, tc, p);             \
+  }                                                                                                \
+  if (BN == 128) return launch_cfg<128, false, false, true, KB_>(ctx, ta, tb, tc, p);     \
+  return launch_cfg<64, false, false, true, KB_>(ctx, ta, tb, tc, p);
     if (KBsel == 32) { MB_TC_FUSED(32) }
     if (KBsel == 64) { MB_TC_FUSED(64) }
     MB_TC_FUSED(128)

@@ -177,6 +177,19 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap
 
 // Ask for the box of a 3-D tiled tensor to be brought into L2 (no shared memory, no completion
 // to wait for): lets a producer run further ahead of HBM than its shared-memory ring allows.
+// 4-D tiled load (for an NHWC tensor: c0 = channel byte, c1 = column, c2 = row, c3 = image).
+// c0 must keep the copy 16-byte aligned; the other coordinates may lie outside the tensor
+// (negative or too large): those elements arrive as the map's fill value, zero.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const CUtensorMap *map, uint32_t bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap *map, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
                :

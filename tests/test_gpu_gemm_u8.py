@@ -231,42 +231,6 @@ def test_empty_and_bad_arguments(ctx):
     assert e.value.code == 1
 
 
-@pytest.mark.parametrize("b_cm", [False, True])
-@pytest.mark.parametrize("shape", [(4096, 4096, 2048), (2200, 3008, 1088), (2500, 4080, 1040)])
-def test_sparse_last_round_is_split_into_half_tiles(ctx, orc, shape, b_cm):
-    """Long-K GEMMs run 128 x 256 tiles on a persistent grid; when the last round would occupy
-    less than half of the SMs its tiles are cut into 128-column halves.  Same bytes with the
-    split on and off, and sampled rows (the last rows of the matrix included, which belong to
-    the split tiles) against the oracle; row-major and column-major B take different tile
-    maps for the halves; ragged M and N clip inside half tiles."""
-    M, N, K = shape
-    rng = np.random.Generator(np.random.PCG64(M + K))
-    A = rng.integers(0, 256, size=(M, K), dtype=np.uint8)
-    B = rng.integers(0, 256, size=(N, K) if b_cm else (K, N), dtype=np.uint8)
-    bias = np.rint(rng.normal(0, 1000, size=N)).astype(np.int32)
-    case = gemm_case(orc, 0, 1, 64, 64, 64)
-    mult, shift, zp_c = case["mult"], 10, 128
-    dA, dB, db, out = ctx.upload(A), ctx.upload(B), ctx.upload(bias), ctx.alloc(M * N)
-    got = {}
-    for split in (1, 0):
-        ctx.set_option("split_tail", split)
-        try:
-            before = ctx.launches_tensor_core
-            ctx.gemm_u8(dA, dB, db, out, 1, M, N, K, 128, 120, mult, shift, zp_c, b_col_major=b_cm)
-            assert ctx.launches_tensor_core == before + 1
-            got[split] = ctx.download(out, (M, N), np.uint8)
-        finally:
-            ctx.set_option("split_tail", 1)
-    assert np.array_equal(got[1], got[0])
-    rows = np.unique(np.concatenate([rng.choice(M, size=24, replace=False), np.arange(M - 8, M)]))
-    exp = orc.gemm_u8(np.ascontiguousarray(A[rows]), B, bias, 1, len(rows), N, K, 128, 120, mult, shift, zp_c,
-                      b_col_major=b_cm).reshape(len(rows), N)
-    assert np.array_equal(got[1][rows], exp)
-    assert len(np.unique(got[1])) > 100
-    for b in (dA, dB, db, out):
-        b.free()
-
-
 def test_linearity_at_full_size(ctx, orc):
     """K = N = 4096, M = 4096 is too large for the scalar oracle in seconds; check raw int32
     accumulators through properties instead: (a) a random sample of rows against the oracle,

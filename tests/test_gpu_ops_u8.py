@@ -262,6 +262,54 @@ def test_dwconv_u8_3x3_variants(ctx, orc, stride, variant):
     assert len(np.unique(got)) > 4
 
 
+@pytest.mark.parametrize("case", [
+    # N, H, W, C, stride: the MobileNet layer shapes at a small batch ...
+    (2, 112, 112, 32, 1), (2, 112, 112, 64, 2), (3, 56, 56, 128, 1), (2, 56, 56, 128, 2), (4, 28, 28, 256, 1),
+    (2, 28, 28, 256, 2), (3, 14, 14, 512, 1), (5, 14, 14, 512, 2), (6, 7, 7, 1024, 1),
+    # ... and shapes that exercise the tiling: channels that only 16-byte chunks divide, a single
+    # row / column, widths beyond one column tile and beyond the 256-column box limit, odd sizes
+    (1, 9, 13, 48, 1), (2, 5, 6, 16, 2), (1, 3, 3, 16, 1), (1, 1, 1, 32, 1), (1, 40, 300, 16, 1), (1, 33, 515, 16, 2),
+    (2, 31, 29, 80, 1), (1, 64, 7, 2048, 2),
+])
+def test_dwconv_u8_tma_tiled_kernel(ctx, orc, case):
+    """Input zero point 0 (out-of-image taps read as zero): the depthwise kernel whose input rows
+    arrive in shared memory by TMA.  Same bytes as the register kernel and as the oracle, with
+    filters that need the second weight pass, an int32 bias and SAME padding (stride 2 pads only
+    bottom / right)."""
+    N, H, W, C, stride = case
+    rng = np.random.Generator(np.random.PCG64(H * 1000 + W + C))
+    x = rng.integers(0, 256, size=(N, H, W, C), dtype=np.uint8)
+    f = rng.integers(1, 256, size=(3, 3, C, 1), dtype=np.uint8)
+    bias = np.rint(rng.normal(0, 2000, size=C)).astype(np.int32)
+    zp_in, zp_f, zp_out = 0, int(rng.integers(110, 140)), int(rng.integers(0, 2)) * 7
+    mult, shift = orc.output_multiplier_and_shift(np.float32(0.02), np.float32(0.01), np.float32(0.02 * 0.01 * 3 * 128 * 74 * 3 / 127))
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, 3, 3, (1, 1), (stride, stride), PAD["SAME"])
+    exp = orc.dwconv_u8(x, f, bias, (stride, stride), (1, 1), (ph >> 1, pw >> 1), (Ho, Wo), zp_in, zp_f, mult, shift,
+                        zp_out)
+    dx, df, db = ctx.upload(x), ctx.upload(f), ctx.upload(bias)
+    do = ctx.alloc(exp.size + 64)
+    packed = ctx.dwconv3x3_u8_prepack(df, db, C, zp_in, zp_f)
+    L = __import__("mace_b200").lib()
+    got = {}
+    for tma in (1, 0):
+        ctx.set_option("dw_tma", tma)
+        try:
+            for pre in (None, packed):
+                ctx._check(L.mb_memset(ctx.h, do.ptr, 0xA5, do.nbytes))
+                ctx.dwconv_u8(dx, df, db, do, N, H, W, C, 1, 3, 3, (stride, stride), (1, 1), (ph >> 1, pw >> 1),
+                              (Ho, Wo), zp_in, zp_f, mult, shift, zp_out, prepacked=pre)
+                raw = ctx.download(do, (do.nbytes,), np.uint8)
+                assert (raw[exp.size:] == 0xA5).all(), "wrote past the output"
+                got[tma] = raw[:exp.size].reshape(exp.shape)
+                assert np.array_equal(got[tma], exp), (tma, pre is not None)
+        finally:
+            ctx.set_option("dw_tma", 1)
+    ctx.sync()
+    assert len(np.unique(exp)) > 4
+    for b in (dx, df, db, do, packed):
+        b.free()
+
+
 def test_dwconv_u8_repack_into_the_same_buffer_then_run_at_once(ctx, orc):
     """The depthwise kernel fetches cached tap words before it waits for the kernel in front of
     it.  When that kernel is the one that (re)wrote the tap words -- a delegator's first run, or
