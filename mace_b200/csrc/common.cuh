@@ -59,6 +59,7 @@ struct mb_context {
   int skinny_max_m = 16;         // row counts up to this take the streaming few-row GEMM
   int gemv_stream = 1;           // one-vector GEMV through the bulk-copy streaming kernel
   int force_bn = 0;              // tensor-core GEMM: 64 / 128 / 256 overrides the tile-width choice
+  int host_alloc_wc = 0;         // mb_host_alloc returns write-combined pinned memory
   int tc_rowsum = 1;             // short-K fused GEMM: A's row sums from 16 extra accumulator columns
   int dw_tma = 1;                // depthwise 3x3 with input zero point 0: rows through shared memory by TMA
   uint64_t dw_attr_mask = 0;     // TMA depthwise kernels whose shared-memory limit was raised

@@ -179,7 +179,9 @@ int mb_host_alloc(mb_context *ctx, size_t bytes, void **hptr) {
   *hptr = nullptr;
   if (bytes == 0) return MB_SUCCESS;
   MB_CUDA(ctx, cudaSetDevice(ctx->device));
-  MB_CUDA(ctx, cudaMallocHost(hptr, bytes));
+  // host_alloc_wc: write-combined pinned memory -- for buffers the host only writes and the GPU
+  // only reads (input staging): the copy engine reads them without snooping the CPU caches
+  MB_CUDA(ctx, cudaHostAlloc(hptr, bytes, ctx->host_alloc_wc ? cudaHostAllocWriteCombined : cudaHostAllocDefault));
   return MB_SUCCESS;
 }
 
@@ -390,6 +392,8 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
     ctx->use_tensor_cores = value;
   } else if (strcmp(name, "mn_major") == 0) {
     ctx->use_mn_major = value;
+  } else if (strcmp(name, "host_alloc_wc") == 0) {
+    ctx->host_alloc_wc = value;
   } else if (strcmp(name, "tc_rowsum") == 0) {
     ctx->tc_rowsum = value;
   } else if (strcmp(name, "dw_tma") == 0) {
