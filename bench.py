@@ -52,9 +52,9 @@ L2_BYTES = 126 * 1024 * 1024
 # (bytes per step of the kernel family, resp. per launch); outputs that are still in L2 when a
 # kernel's capture ends are not in these sums.
 NCU_TRAFFIC = {
-    "mobilenet_dw": 196.4e6,   # 13 depthwise launches, profiles/mobilenet_v1_u8_b64_launches.md
+    "mobilenet_dw": 196.8e6,   # 13 depthwise launches, profiles/mobilenet_v1_u8_b64_launches.md
     "mobilenet_pw": 130.3e6,   # 13 pointwise + FC GEMM launches, same file
-    "gemm_u8_4096": 33.78e6,   # gemm_u8_tc_kernel<256>, profiles/gemm_u8_tc_kernel_4096.md
+    "gemm_u8_4096": 35.0e6,    # gemm_u8_tc_kernel<256>, profiles/gemm_u8_tc_kernel_4096.md
     "winograd_f32_cfg1": 134.6e6,  # three kernels of one convolution, caches flushed between them
 }
 
@@ -392,8 +392,7 @@ def run_gemm(args, rank, world):
                          "traffic": NCU_TRAFFIC["gemm_u8_4096"] if size == 4096 else None,
                          "peak_source": peak_src,
                          "frac_of_2x_bf16_burst": round(achieved / (2.0 * peaks["bf16_tflops"]), 4),
-                         "kernel": "gemm_u8_tc_kernel<256> (step also holds the two operand "
-                                   "byte-sum kernels)"},
+                         "kernel": "gemm_u8_tc_kernel<256> (step also holds the operand-sum kernel)"},
             "e2e": {"value": round(e2e_val, 3), "unit": wl.unit,
                     "h2d_bytes_per_step": wl.M * wl.K + wl.K * wl.N,
                     "d2h_bytes_per_step": wl.M * wl.N},
@@ -645,7 +644,7 @@ def run_mobilenet(args, rank, world):
         e2e_val = world * BATCH / (e2e_ms / e2e_steps * 1e-3)
         lbytes = mobilenet_layer_bytes(layers, BATCH)
         # group operator times by kernel family
-        fam = {"dw": ["dwconv3x3_u8_kernel", 0.0, 0], "pw": ["gemm_u8_tc_kernel (pointwise)", 0.0, 0],
+        fam = {"dw": ["dwconv3x3_u8_tma_kernel", 0.0, 0], "pw": ["gemm_u8_tc_kernel (pointwise)", 0.0, 0],
                "stem": ["conv_u8_patch_dp4a_kernel", 0.0, 0], "pool": ["avgpool_u8_c4_kernel", 0.0, 0],
                "fc": ["gemm_u8_tc_kernel (FullyConnected, float rule)", 0.0, 0]}
         for label, t in per_op.items():
