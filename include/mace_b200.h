@@ -130,7 +130,15 @@ uint64_t mb_launch_count_tensor_core(const mb_context *ctx);
  * (1 default; 0 launches the kernels of the uint8 operator chain in plain
  * stream order instead of with programmatic stream serialization),
  * "dw_waves" (1 default: the 3x3 depthwise grid is sized so that all blocks
- * are resident at once; n sizes it for n such rounds with shorter row runs). */
+ * are resident at once; n sizes it for n such rounds with shorter row runs),
+ * "split_k" (1 default: a product with fewer output tiles than a quarter of
+ * the SMs and a depth of 2048 or more is computed as 4 or 8 depth runs on as
+ * many times the SMs, their exact int32 results added by a second kernel;
+ * 0 keeps one CTA per output tile),
+ * "gemv_lhs_const" (0 default; 1 promises that the matrix of the following
+ * mb_gemv_u8 calls is not written by work enqueued ahead of them -- a weight,
+ * the reference's Tensor::is_weight(), mace/core/tensor.h -- so its first
+ * bytes may be fetched while the previous kernel still runs). */
 int mb_set_option(mb_context *ctx, const char *name, int value);
 
 /* ---- uint8 GEMM: replaces the gemmlowp calls of MatMulOp<RT_CPU,uint8_t>

@@ -57,7 +57,10 @@ struct mb_context {
                                  // the stream and the depthwise kernel may not read the tap words
                                  // before it has waited for its predecessor
   int skinny_max_m = 16;         // row counts up to this take the streaming few-row GEMM
+  int split_k = 1;               // few-tile, long-depth GEMMs: cut the depth into runs over more SMs
   int gemv_stream = 1;           // one-vector GEMV through the bulk-copy streaming kernel
+  int gemv_lhs_const = 0;        // the GEMV matrix is a weight: it may be fetched ahead of the dependency wait
+  int gemv_const_one_per_sm = 0; // with a constant matrix, leave half of each SM to the next kernel (measured slower: 6.1 vs 5.75 us per 4096 x 4096 product in a chain)
   int force_bn = 0;              // tensor-core GEMM: 64 / 128 / 256 overrides the tile-width choice
   int host_alloc_wc = 0;         // mb_host_alloc returns write-combined pinned memory
   int tc_rowsum = 1;             // short-K fused GEMM: A's row sums from 16 extra accumulator columns

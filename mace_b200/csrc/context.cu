@@ -404,8 +404,14 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
   } else if (strcmp(name, "skinny_max_m") == 0) {
     if (value < 0 || value > 16) return mb_fail(ctx, MB_INVALID_ARGS, "skinny_max_m must be 0 .. 16");
     ctx->skinny_max_m = value;
+  } else if (strcmp(name, "split_k") == 0) {
+    ctx->split_k = value;
   } else if (strcmp(name, "gemv_stream") == 0) {
     ctx->gemv_stream = value;
+  } else if (strcmp(name, "gemv_lhs_const") == 0) {
+    ctx->gemv_lhs_const = value;
+  } else if (strcmp(name, "gemv_const_one_per_sm") == 0) {
+    ctx->gemv_const_one_per_sm = value;
   } else if (strcmp(name, "force_bn") == 0) {
     if (value != 0 && value != 64 && value != 128 && value != 256)
       return mb_fail(ctx, MB_INVALID_ARGS, "force_bn must be 0, 64, 128 or 256");

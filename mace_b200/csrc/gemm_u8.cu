@@ -5,6 +5,8 @@
 //
 // Reference behaviour: MatMulFixpointImpl (mace/ops/matmul.cc:228-394) and the
 // GEMM of the quantized Conv2D (mace/ops/conv_2d.cc:301-315).
+#include <algorithm>
+
 #include "common.cuh"
 
 bool mb_gemm_u8_tc_supported(const mb_context *ctx, const void *A, const void *B, int64_t M,
@@ -172,7 +174,86 @@ int mb_gemm_u8_tc_launch_sliced(mb_context *ctx, const uint8_t *A, const uint8_t
                                 int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
                                 int bias_per_row);
 int mb_operand_sums_launch(mb_context *ctx, const uint8_t *A, bool a_mn, int64_t nb_a, int64_t M, uint32_t *sum_a,
-                           const uint8_t *B, bool b_mn, int64_t nb_b, int64_t N, uint32_t *sum_b, int64_t K);
+                           const uint8_t *B, bool b_mn, int64_t nb_b, int64_t N, uint32_t *sum_b, int64_t K,
+                           int k_split);
+int mb_gemm_u8_tc_launch_splitk(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+                                const uint32_t *sum_a, const uint32_t *sum_b, int sum_a_slices, int sum_b_slices,
+                                int32_t *parts, int k_split, int bn, int64_t M, int64_t N, int64_t K, bool a_mn,
+                                bool b_mn, int32_t zp_a, int32_t zp_b);
+
+namespace {
+
+// ---- few output tiles, long depth: the depth cut into runs ----------------------------
+// A product of 128 rows against a 4096 x 4096 matrix has 32 output tiles for 148 SMs, and each
+// of the 32 pulls a megabyte through one SM.  Cutting the depth into S runs gives S times the
+// CTAs, each streaming 1/S of the bytes; the S exact int32 partial results (zero-point terms
+// included: they are linear in the depth) are added here, then bias and the fixed-point
+// output stage as in the GEMM's own epilogue (mace/ops/common/gemmlowp_util.h:37-74).
+struct SplitReduceParams {
+  const int32_t *parts;   // [splits][M][N]
+  const int32_t *bias;
+  void *C;
+  int64_t M, N;
+  int splits, bias_per_row, out_is_int32;
+  mb_requant_params rq;
+};
+
+template <int VEC>
+__global__ void __launch_bounds__(256) gemm_u8_split_reduce_kernel(const SplitReduceParams p) {
+  mb_grid_dep_launch();
+  mb_grid_dep_wait();
+  const int64_t total = p.M * p.N / VEC;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t e = i * VEC;
+    const int64_t m = e / p.N, n = e % p.N;
+    int32_t acc[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = 0;
+    for (int s = 0; s < p.splits; ++s) {
+      const int32_t *src = p.parts + s * p.M * p.N + e;
+      if (VEC == 4) {
+        const int4 v = *reinterpret_cast<const int4 *>(src);
+        acc[0] += v.x; acc[1 % VEC] += v.y; acc[2 % VEC] += v.z; acc[3 % VEC] += v.w;
+      } else {
+        acc[0] += src[0];
+      }
+    }
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) acc[j] += p.bias[p.bias_per_row ? m : n + j];
+    }
+    if (p.out_is_int32) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) static_cast<int32_t *>(p.C)[e + j] = acc[j];
+    } else if (VEC == 4) {
+      uint32_t w = 0;
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) w |= mb_requant_fast(acc[j], p.rq) << (8 * j);
+      *reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(p.C) + e) = w;
+    } else {
+      static_cast<uint8_t *>(p.C)[e] = static_cast<uint8_t>(mb_requant_fast(acc[0], p.rq));
+    }
+  }
+}
+
+// The number of runs for this shape (1: do not cut), and the tile width to run them with.
+int split_k_choice(const mb_context *ctx, int64_t batch, int64_t M, int64_t N, int64_t K, int *bn) {
+  if (!ctx->split_k || batch != 1 || K < 2048) return 1;
+  *bn = N >= 128 ? 128 : 64;
+  const int64_t tiles = ceil_div64(M, 128) * ceil_div64(N, *bn);
+  int best = 1;
+  for (int s : {2, 4, 8}) {
+    if (tiles * s > ctx->num_sms) break;
+    if (K % (static_cast<int64_t>(s) * 128) != 0 || K / s < 512) break;
+    best = s;
+  }
+  // two runs do not pay for the extra kernel and the int32 round trip (measured at
+  // M = 256, K = N = 4096: 15.2 us against 13.9 us undivided)
+  return best >= 4 ? best : 1;
+}
+
+}  // namespace
 
 // Row-major-C GEMM on device operands; a_mn / b_mn as in mb_gemm_u8_tc_launch.
 int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, const int32_t *bias,
@@ -180,14 +261,23 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
                         int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
                         int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
                         int bias_per_row) {
-  // A few rows against a large row-major B: stream B once over all SMs.
-  if (ctx->use_tensor_cores && M <= ctx->skinny_max_m && mb_gemm_u8_skinny_supported(batch, M, N, K, a_mn, b_mn, A, B))
-    return mb_gemm_u8_skinny_launch(ctx, A, B, bias, C, out_is_int32, M, N, K, zp_a, zp_b, mult, shift,
-                                    zp_c, bias_per_row);
   const bool aligned16 =
       ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15u) == 0;
   bool use_tc = ctx->use_tensor_cores && ctx->encode_tiled != nullptr && aligned16 &&
                 K % 16 == 0 && K <= 33000 && M >= 1 && N >= 1;
+  // A few rows against a large row-major B: stream B once over all SMs with CUDA cores.  From
+  // four rows on the tensor-core kernel over depth runs is faster where it applies (measured at
+  // K = N = 4096: 13.7 us against 14.0 at M = 4, 14.4 against 28.8 at M = 16; 13.8 against 11.1
+  // at M = 1).
+  if (ctx->use_tensor_cores && M <= ctx->skinny_max_m && mb_gemm_u8_skinny_supported(batch, M, N, K, a_mn, b_mn, A, B)) {
+    int bn_unused = 0;
+    const bool runs_apply = M >= 4 && use_tc && !(a_mn && !(ctx->use_mn_major && M % 16 == 0)) &&
+                            !(b_mn && !(ctx->use_mn_major && N % 16 == 0)) &&
+                            split_k_choice(ctx, batch, M, N, K, &bn_unused) > 1;
+    if (!runs_apply)
+      return mb_gemm_u8_skinny_launch(ctx, A, B, bias, C, out_is_int32, M, N, K, zp_a, zp_b, mult, shift,
+                                      zp_c, bias_per_row);
+  }
   // How each operand reaches the tensor core: natively in its own major, or
   // through a K-major copy in scratch.
   bool a_copy = false, b_copy = false;
@@ -200,6 +290,45 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
                           a_batched, b_batched, zp_a, zp_b, mult, shift, zp_c, bias_per_row);
   }
   const int64_t nb_a = a_batched ? batch : 1, nb_b = b_batched ? batch : 1;
+  int split_bn = 0;
+  const int splits = (a_copy || b_copy) ? 1 : split_k_choice(ctx, batch, M, N, K, &split_bn);
+  if (splits > 1 && mb_gemm_u8_tc_supported(ctx, A, B, M, N, K / splits, a_mn, b_mn, 0, 0)) {
+    const int64_t Ks = K / splits;
+    // runs no longer than 1024 with a K-major A: the kernel sums the bytes of its own tiles
+    const bool fused = !a_mn && Ks <= 1024;
+    const bool want_a = zp_b != 0 && !fused, want_b = zp_a != 0 && !fused;
+    const int sl_a = want_a ? mb_operand_sums_slices(ctx, a_mn, splits, Ks, M) : 1;
+    const int sl_b = want_b ? mb_operand_sums_slices(ctx, b_mn, splits, Ks, N) : 1;
+    size_t off = 0;
+    const size_t off_parts = off; off += align_up(sizeof(int32_t) * splits * M * N, 256);
+    const size_t off_sa = off; off += want_a ? align_up(sizeof(uint32_t) * splits * M * sl_a, 256) : 0;
+    const size_t off_sb = off; off += want_b ? align_up(sizeof(uint32_t) * splits * N * sl_b, 256) : 0;
+    uint8_t *scratch = nullptr;
+    MB_RETURN_IF_ERROR(mb_scratch(ctx, off, reinterpret_cast<void **>(&scratch)));
+    int32_t *parts = reinterpret_cast<int32_t *>(scratch + off_parts);
+    uint32_t *sum_a = want_a ? reinterpret_cast<uint32_t *>(scratch + off_sa) : nullptr;
+    uint32_t *sum_b = want_b ? reinterpret_cast<uint32_t *>(scratch + off_sb) : nullptr;
+    if (want_a || want_b)
+      MB_RETURN_IF_ERROR(mb_operand_sums_launch(ctx, A, a_mn, 1, M, sum_a, B, b_mn, 1, N, sum_b, K, splits));
+    ctx->pdl_next_gemm = (want_a || want_b) ? 1 : 0;
+    MB_RETURN_IF_ERROR(mb_gemm_u8_tc_launch_splitk(ctx, A, B, sum_a, sum_b, sl_a, sl_b, parts, splits, split_bn, M, N,
+                                                   K, a_mn, b_mn, zp_a, zp_b));
+    SplitReduceParams rp;
+    rp.parts = parts; rp.bias = bias; rp.C = C; rp.M = M; rp.N = N;
+    rp.splits = splits; rp.bias_per_row = bias_per_row; rp.out_is_int32 = out_is_int32;
+    rp.rq = mb_make_requant(mult, shift, zp_c);
+    const bool vec4 = N % 4 == 0 && (reinterpret_cast<uintptr_t>(C) & 3u) == 0;
+    const int64_t work = M * N / (vec4 ? 4 : 1);
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ceil_div64(work, 256), 8ll * ctx->num_sms));
+    if (vec4) {
+      MB_CUDA(ctx, mb_launch_chained(ctx, gemm_u8_split_reduce_kernel<4>, dim3(grid), dim3(256), 0, rp));
+    } else {
+      MB_CUDA(ctx, mb_launch_chained(ctx, gemm_u8_split_reduce_kernel<1>, dim3(grid), dim3(256), 0, rp));
+    }
+    MB_CUDA(ctx, cudaGetLastError());
+    ctx->launches++;
+    return MB_SUCCESS;
+  }
   // K-major operands with K <= 1024: the tensor-core kernel sums the operand
   // bytes itself from the tiles it has in shared memory.
   const bool fused_sums = !(a_mn && !a_copy) && !(b_mn && !b_copy) && K <= 1024;
@@ -232,7 +361,7 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
   }
   // both operands' sums in one launch (see operand_sums.cu)
   if (need_sum_a || need_sum_b)
-    MB_RETURN_IF_ERROR(mb_operand_sums_launch(ctx, a_use, a_mn_use, nb_a, M, sum_a, b_use, b_mn_use, nb_b, N, sum_b, K));
+    MB_RETURN_IF_ERROR(mb_operand_sums_launch(ctx, a_use, a_mn_use, nb_a, M, sum_a, b_use, b_mn_use, nb_b, N, sum_b, K, 1));
   if (!mb_gemm_u8_tc_supported(ctx, a_use, b_use, M, N, K, a_mn_use, b_mn_use, a_batched,
                                b_batched)) {
     return launch_generic(ctx, A, B, bias, C, out_is_int32, batch, M, N, K, a_mn, b_mn,

@@ -547,7 +547,21 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int j = 0; j < (BN + 127) / 128; ++j) {
             const int row = j * 128 + r;
-            if (want_b && row < BN) {
+            if (B_MN) {
+              // the tile is [128-column panel][KB depth rows][128 bytes], the 16-byte chunks of
+              // a row permuted by the row's low three bits: this thread adds up column r of
+              // panel j (the lanes of a warp read 32 adjacent bytes of a row: no conflicts)
+              if (want_b && row < ((BN + 127) / 128) * 128) {
+                const uint8_t *col = tb + j * 128 * KB + (r & 15);
+                uint32_t s0 = 0, s1 = 0;
+#pragma unroll 8
+                for (int k = 0; k < KB; k += 2) {
+                  s0 += col[k * 128 + (((r >> 4) ^ (k & 7)) << 4)];
+                  s1 += col[(k + 1) * 128 + (((r >> 4) ^ ((k + 1) & 7)) << 4)];
+                }
+                sb_sum[j] += s0 + s1;
+              }
+            } else if (want_b && row < BN) {
 #pragma unroll
               for (int i = 0; i < KB / 16; ++i)
                 sb_sum[j] = sum16(*reinterpret_cast<const uint4 *>(tb + row * KB + ((i + r) & (KB / 16 - 1)) * 16),
@@ -659,6 +673,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint8_t *c8 = static_cast<uint8_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
         const bool words_ok = !p.out_is_int32 && (p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 3u) == 0;
         int32_t *c32 = static_cast<int32_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m) * p.N;
+        const bool quads_ok = p.out_is_int32 && (p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15u) == 0;
         uint32_t r[1][CHUNK];
         tmem_ld_32x32b_x16(tbase, r[0]);
 #pragma unroll 1
@@ -689,6 +704,17 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               uint32_t *cw = reinterpret_cast<uint32_t *>(c8 + n0);
 #pragma unroll
               for (int q = 0; q < CHUNK / 4; ++q) cw[q] = packed[q];
+            }
+          } else if (quads_ok && n0 + CHUNK <= p.N) {
+            // a whole chunk of an int32 row: four 16-byte stores instead of sixteen words
+            if (row_ok) {
+              int4 *cq = reinterpret_cast<int4 *>(c32 + n0);
+#pragma unroll
+              for (int q = 0; q < CHUNK / 4; ++q)
+                cq[q] = make_int4(static_cast<int32_t>(v[4 * q + 0]) + row_term + ct[4 * q + 0],
+                                  static_cast<int32_t>(v[4 * q + 1]) + row_term + ct[4 * q + 1],
+                                  static_cast<int32_t>(v[4 * q + 2]) + row_term + ct[4 * q + 2],
+                                  static_cast<int32_t>(v[4 * q + 3]) + row_term + ct[4 * q + 3]);
             }
           } else if (row_ok && n0 < p.N) {
 #pragma unroll
@@ -737,9 +763,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 // tiles, 32-byte swizzle for the output staging boxes.
 int make_map_u8(mb_context *ctx, CUtensorMap *map, const void *base, uint64_t inner,
                 uint64_t rows, uint64_t batch, uint64_t batch_stride_bytes, uint32_t box_inner,
-                uint32_t box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+                uint32_t box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B,
+                uint64_t row_pitch = 0) {
   const cuuint64_t dims[3] = {inner, rows, batch};
-  const cuuint64_t strides[2] = {inner, batch_stride_bytes};
+  const cuuint64_t strides[2] = {row_pitch != 0 ? row_pitch : inner, batch_stride_bytes};
   const cuuint32_t box[3] = {box_inner, box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
@@ -806,7 +833,17 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
                           void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
                           int64_t K, bool a_mn, bool b_mn, int a_batched, int b_batched,
                           int32_t zp_a, int32_t zp_b, int32_t mult, int32_t shift, int32_t zp_c,
-                          int bias_per_row, int float_rule, float mult_f, int add_zp) {
+                          int bias_per_row, int float_rule, float mult_f, int add_zp, int k_split = 1,
+                          int bn_forced = 0) {
+  // k_split > 1: one product whose depth is cut into k_split equal runs, computed as a batch of
+  // k_split products (int32 results [k_split][M][N], each with its own zero-point terms, which
+  // are linear in the depth); the caller adds them up.
+  const int64_t k_full = K;
+  if (k_split > 1) {
+    K /= k_split;
+    batch = k_split;
+    a_batched = b_batched = 1;
+  }
   // Operand sums computed inside the kernel: K-major operands, short K, and the
   // caller passed no precomputed sums although a zero point needs them.
   // Rows of 64 or 32 bytes for K-major operands with K <= 64 (the first pointwise
@@ -815,6 +852,10 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   const bool kmajor_free = !a_mn && !b_mn && sum_a == nullptr && sum_b == nullptr;
   const int KBsel = (kmajor_free && K <= 32) ? 32 : (kmajor_free && K <= 64) ? 64 : BK;
   const bool fuse = kmajor_free && K <= 8 * BK && (zp_a != 0 || zp_b != 0 || KBsel != BK);
+  // depth runs of a K-major A against a row-major B: B's column sums are taken from the tiles
+  // too (these launches are bound by the bytes each SM can pull, the tile readers are idle)
+  const bool fuse_bmn = k_split > 1 && !a_mn && b_mn && sum_a == nullptr && sum_b == nullptr && K <= 8 * BK &&
+                        (zp_a != 0 || zp_b != 0) && (bn_forced == 64 || bn_forced == 128);
   // Tile width.  Long main loops (K > 1024) want the widest tile for operand
   // reuse -- unless that leaves most SMs without a tile (a few rows against a
   // large B): then the width with the fewest columns per SM wins, wider on a
@@ -854,6 +895,7 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
       }
     }
     if (ctx->force_bn != 0 && !(ctx->force_bn > 64 && N <= ctx->force_bn / 2)) BN = ctx->force_bn;
+    if (bn_forced != 0) BN = bn_forced;
   }
   TcParams p;
   p.M = M; p.N = N; p.K = K; p.batch = batch;
@@ -895,15 +937,17 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   const CUtensorMapSwizzle kswz = KBsel == 32   ? CU_TENSOR_MAP_SWIZZLE_32B
                                   : KBsel == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
                                                 : CU_TENSOR_MAP_SWIZZLE_128B;
+  // (a run of the depth: K-major rows keep the pitch of the whole matrix and the runs lie side by
+  // side; MN-major runs are whole row blocks, one behind the other)
   if (a_mn) {
     MB_RETURN_IF_ERROR(make_map_u8(ctx, &ta, A, M, K, nb_a, M * K, 128, BK));
   } else {
-    MB_RETURN_IF_ERROR(make_map_u8(ctx, &ta, A, K, M, nb_a, M * K, KBsel, BM, kswz));
+    MB_RETURN_IF_ERROR(make_map_u8(ctx, &ta, A, K, M, nb_a, k_split > 1 ? K : M * K, KBsel, BM, kswz, k_full));
   }
   if (b_mn) {
     MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, N, K, nb_b, N * K, 128, BK));
   } else {
-    MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, K, N, nb_b, N * K, KBsel, BN, kswz));
+    MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, K, N, nb_b, k_split > 1 ? K : N * K, KBsel, BN, kswz, k_full));
   }
 
 #define MB_TC_DISPATCH(BN_)                                                         \
@@ -913,6 +957,10 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   } else {                                                                          \
     if (b_mn) return launch_cfg<BN_, false, true>(ctx, ta, tb, tc, p);                  \
     return launch_cfg<BN_, false, false>(ctx, ta, tb, tc, p);                           \
+  }
+  if (fuse_bmn) {
+    if (BN == 128) return launch_cfg<128, false, true, true>(ctx, ta, tb, tc, p);
+    return launch_cfg<64, false, true, true>(ctx, ta, tb, tc, p);
   }
   if (fuse) {
 #define MB_TC_FUSED(KB_)                                                                  \
@@ -954,6 +1002,17 @@ int mb_gemm_u8_tc_launch_sliced(mb_context *ctx, const uint8_t *A, const uint8_t
                                 int bias_per_row) {
   return tc_launch_impl(ctx, A, B, sum_a, sum_b, sum_a_slices, sum_b_slices, bias, C, out_is_int32, batch, M, N, K,
                         a_mn, b_mn, a_batched, b_batched, zp_a, zp_b, mult, shift, zp_c, bias_per_row, 0, 0.f, 0);
+}
+
+// One product with its depth cut into k_split equal runs (K % (k_split * 128) == 0): `parts`
+// receives the k_split int32 results [k_split][M][N], each the exact sum over its run of
+// (A - zp_a)(B - zp_b); the sums are per run ([k_split][...], see mb_operand_sums_launch).
+int mb_gemm_u8_tc_launch_splitk(mb_context *ctx, const uint8_t *A, const uint8_t *B,
+                                const uint32_t *sum_a, const uint32_t *sum_b, int sum_a_slices, int sum_b_slices,
+                                int32_t *parts, int k_split, int bn, int64_t M, int64_t N, int64_t K, bool a_mn,
+                                bool b_mn, int32_t zp_a, int32_t zp_b) {
+  return tc_launch_impl(ctx, A, B, sum_a, sum_b, sum_a_slices, sum_b_slices, nullptr, parts, 1, 1, M, N, K, a_mn,
+                        b_mn, 0, 0, zp_a, zp_b, 1 << 30, 0, 0, 0, 0, 0.f, 0, k_split, bn);
 }
 
 // The same product with the Gemv delegators' float requantization rule (see

@@ -154,6 +154,7 @@ struct GemvStreamParams {
   int out_is_int32, add_zp_out;
   int32_t zp_lhs, zp_rhs, zp_out;
   float multiplier;
+  int lhs_const;   // the matrix is not written by work ahead in the stream (a weight)
   int *status;
 };
 
@@ -192,8 +193,13 @@ __global__ void __launch_bounds__(ST_WARPS * 32) gemv_u8_stream_kernel(const Gem
     sm100::bulk_load_1d(sm100::smem_u32(my_ring + slot * ST_CHUNK), p.lhs + row * p.K + static_cast<int64_t>(c) * ST_CHUNK,
                         bytes, my_bar + 8 * slot);
   };
-  mb_grid_dep_wait();  // from here on global memory is read
-  if (lane == 0)
+  // A weight matrix may be fetched before the work ahead in the stream has finished: the ring's
+  // first fill then overlaps the previous kernel's tail (or all of it, for a chain of such
+  // products).  The vector and the output are touched only after the wait.
+  if (p.lhs_const && lane == 0)
+    for (int64_t u = 0; u < units && u < ST_DEPTH; ++u) issue(u);
+  mb_grid_dep_wait();  // from here on every operand may be read
+  if (!p.lhs_const && lane == 0)
     for (int64_t u = 0; u < units && u < ST_DEPTH; ++u) issue(u);
   // the vector and its byte sum, once per CTA, while the first chunks are on their way
   {
@@ -313,6 +319,7 @@ extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rh
     sp.out_is_int32 = out_is_int32; sp.add_zp_out = add_zp_out;
     sp.zp_lhs = zp_lhs; sp.zp_rhs = zp_rhs; sp.zp_out = zp_out; sp.multiplier = multiplier;
     sp.status = ctx->dev_status;
+    sp.lhs_const = ctx->gemv_lhs_const;
     const size_t smem = static_cast<size_t>(ST_WARPS) * ST_DEPTH * ST_CHUNK + static_cast<size_t>(K) +
                         sizeof(uint64_t) * ST_WARPS * ST_DEPTH;
     constexpr uint64_t attr_bit = 1ull << 62;
@@ -321,7 +328,9 @@ extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rh
                                         ST_WARPS * ST_DEPTH * ST_CHUNK + 65536 + 8 * ST_WARPS * ST_DEPTH));
       ctx->func_attr_mask |= attr_bit;
     }
-    const int per_sm = smem <= 110 * 1024 ? 2 : 1;
+    // two CTAs fit an SM; with a constant matrix one of the two places is left to the next
+    // kernel of the chain, whose first fill is then under way while this one streams
+    const int per_sm = (smem <= 110 * 1024 && !(sp.lhs_const && ctx->gemv_const_one_per_sm)) ? 2 : 1;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(rows, static_cast<int64_t>(ctx->num_sms) * per_sm));
     MB_CUDA(ctx, mb_launch_chained(ctx, gemv_u8_stream_kernel, dim3(grid), dim3(ST_WARPS * 32), smem, sp));
     MB_CUDA(ctx, cudaGetLastError());

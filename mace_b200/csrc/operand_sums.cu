@@ -24,6 +24,7 @@ struct SumJob {
   int kind;                  // 0: nothing, 1: row sums, 2: column sums
   int64_t nb;                // matrices
   int64_t rows, cols;        // kind 1: rows x cols(=K) per matrix; kind 2: K rows x cols
+  int64_t pitch, mat_stride; // kind 1: bytes from row to row and from matrix to matrix
   int num_blocks;
   // column sums: out is [nb][slices][cols]
   int col_blocks, slices;
@@ -37,7 +38,7 @@ __device__ __forceinline__ void row_sums(const SumJob &j, int block) {
   const int64_t nvec = j.cols >> 4;
   for (int64_t row = static_cast<int64_t>(block) * WARPS + (threadIdx.x >> 5); row < total;
        row += static_cast<int64_t>(j.num_blocks) * WARPS) {
-    const uint4 *p = reinterpret_cast<const uint4 *>(j.x + row * j.cols);
+    const uint4 *p = reinterpret_cast<const uint4 *>(j.x + (row / j.rows) * j.mat_stride + (row % j.rows) * j.pitch);
     uint32_t s = 0;
 #pragma unroll 8
     for (int64_t i = lane; i < nvec; i += 32) {
@@ -125,8 +126,16 @@ int mb_operand_sums_slices(const mb_context *ctx, bool mn, int64_t nb, int64_t K
 
 // Sums for A (row sums when K-major; partial column sums, mb_operand_sums_slices() rows of them,
 // when a_mn) into sum_a and for B into sum_b; either output may be null (not needed).
+// k_split > 1: single matrices (nb_a = nb_b = 1) whose depth is cut into k_split equal runs, each
+// summed on its own as if it were a matrix of a batch (outputs [k_split][...]).
 int mb_operand_sums_launch(mb_context *ctx, const uint8_t *A, bool a_mn, int64_t nb_a, int64_t M, uint32_t *sum_a,
-                           const uint8_t *B, bool b_mn, int64_t nb_b, int64_t N, uint32_t *sum_b, int64_t K) {
+                           const uint8_t *B, bool b_mn, int64_t nb_b, int64_t N, uint32_t *sum_b, int64_t K,
+                           int k_split) {
+  const int64_t k_full = K;
+  if (k_split > 1) {
+    K /= k_split;
+    nb_a = nb_b = k_split;
+  }
   auto make = [&](const uint8_t *x, bool mn, int64_t nb, int64_t extent, uint32_t *out) {
     SumJob j = {};
     if (out == nullptr) return j;
@@ -134,6 +143,8 @@ int mb_operand_sums_launch(mb_context *ctx, const uint8_t *A, bool a_mn, int64_t
     if (!mn) {  // [extent x K], K contiguous
       j.kind = 1;
       j.rows = extent; j.cols = K;
+      j.pitch = k_full;
+      j.mat_stride = k_split > 1 ? K : extent * K;
       j.num_blocks = static_cast<int>(std::min<int64_t>(ceil_div64(nb * extent, SUM_WARPS),
                                                         static_cast<int64_t>(ctx->num_sms) * 8));
     } else {    // [K x extent] -> [slices][extent] partial rows

@@ -148,6 +148,7 @@ class Gemv : public delegator::Gemv {
         return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "output scale must not be zero");
       multiplier = lhs->scale() * rhs->scale() / output->scale();
     }
+    mb_set_option(rt->ctx(), "gemv_lhs_const", lhs->is_weight() ? 1 : 0);
     return rt->Status(mb_gemv_u8(rt->ctx(), lhs->memory<uint8_t>(), rhs->memory<uint8_t>(),
                                  bias ? bias->memory<int32_t>() : nullptr,
                                  output->mutable_memory<void>(), out_int32 ? 1 : 0, batch,

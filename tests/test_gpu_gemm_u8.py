@@ -114,6 +114,45 @@ def test_config4_m128_and_batched_512(ctx, orc):
 
 
 @pytest.mark.parametrize("a_cm,b_cm", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(128, 1024, 4096), (16, 2048, 2048), (100, 512, 3072), (200, 640, 2048)])
+def test_depth_cut_into_runs(ctx, orc, shape, a_cm, b_cm):
+    """Few output tiles and a long depth: the product runs as several depth runs over more SMs
+    plus a kernel that adds the int32 partial results (operand sums per run for MN-major
+    operands, inside the kernel for K-major ones).  Every byte against the oracle and against
+    the undivided product: zero points on either side or none, bias per column / per row /
+    none, uint8 and int32 output."""
+    M, N, K = shape
+    if a_cm and M % 16 != 0:
+        pytest.skip("MN-major A with M % 16 != 0 goes through a K-major copy, which is not cut")
+    variants = [dict(zp_a=128, zp_b=120, bias_len=N), dict(zp_a=0, zp_b=0), dict(zp_a=7, zp_b=0, bias_len=M),
+                dict(zp_a=0, zp_b=255)]
+    for i, v in enumerate(variants):
+        per_row = v.get("bias_len") == M and M != N
+        case = gemm_case(orc, 50 + i, 1, M, N, K, bias_len=v.get("bias_len"), a_col_major=a_cm, b_col_major=b_cm,
+                         zp_a=v["zp_a"], zp_b=v["zp_b"])
+        for out_int32 in ((False, True) if i < 2 else (False,)):
+            got = {}
+            for split in (1, 0):
+                ctx.set_option("split_k", split)
+                ctx.set_option("skinny_max_m", 0)
+                try:
+                    before = ctx.launches
+                    got[split], exp = run_gemm(ctx, orc, case, 1, M, N, K, a_col_major=a_cm, b_col_major=b_cm,
+                                               out_int32=out_int32, bias_per_row=per_row)
+                    launches = ctx.launches - before
+                finally:
+                    ctx.set_option("split_k", 1)
+                    ctx.set_option("skinny_max_m", 16)
+                assert np.array_equal(got[split], exp), (split, v, out_int32)
+                if split:
+                    assert launches in (2, 3), launches  # [operand sums,] the runs, the add-up kernel
+                else:
+                    assert launches in (1, 2), launches
+            if not out_int32 and i == 0:
+                assert len(np.unique(got[1])) > 50
+
+
+@pytest.mark.parametrize("a_cm,b_cm", [(False, False), (False, True), (True, False), (True, True)])
 def test_unaligned_generic_path(ctx, orc, a_cm, b_cm):
     """31 x 61 x 67 (matmul_test.cc): no 16-byte alignment anywhere, CUDA-core kernel."""
     case = gemm_case(orc, 5, 2, 31, 67, 61, a_col_major=a_cm, b_col_major=b_cm)
@@ -196,15 +235,26 @@ def test_requantization_variants(ctx, orc, zp_c, shift):
 @pytest.mark.parametrize("out_int32", [False, True])
 def test_few_rows_against_row_major_b(ctx, orc, shape, out_int32):
     """M <= 16 with a row-major B (the M = 1 / M = 16 cases of the K = N = 4096 sweep): the
-    split-K streaming kernel, twice in a row (its workspace must come back zeroed), with a
-    bias, ragged N and K, and interleaved with a differently shaped call."""
+    CUDA-core streaming kernel, twice in a row (its workspace must come back zeroed), with a
+    bias, ragged N and K, and interleaved with a differently shaped call.  (With the default
+    options M = 16 against 4096 x 4096 goes to the tensor core over depth runs instead, which
+    test_depth_cut_into_runs covers; here that route is switched off.)"""
     M, N, K = shape
     case = gemm_case(orc, M + N, 1, M, N, K, bias_len=N)
-    before = ctx.launches_tensor_core
-    for _ in range(2):
+    if M >= 4 and K >= 2048:
+        before = ctx.launches_tensor_core
         got, exp = run_gemm(ctx, orc, case, 1, M, N, K, out_int32=out_int32)
         assert np.array_equal(got, exp)
-    assert ctx.launches_tensor_core == before, "expected the CUDA-core streaming kernel"
+        assert ctx.launches_tensor_core > before, "expected the tensor-core kernel over depth runs"
+    ctx.set_option("split_k", 0)
+    try:
+        before = ctx.launches_tensor_core
+        for _ in range(2):
+            got, exp = run_gemm(ctx, orc, case, 1, M, N, K, out_int32=out_int32)
+            assert np.array_equal(got, exp)
+        assert ctx.launches_tensor_core == before, "expected the CUDA-core streaming kernel"
+    finally:
+        ctx.set_option("split_k", 1)
     other = gemm_case(orc, 5, 1, 2, 512, 256, bias_len=2)
     got, exp = run_gemm(ctx, orc, other, 1, 2, 512, 256, bias_per_row=True)
     assert np.array_equal(got, exp)

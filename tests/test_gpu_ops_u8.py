@@ -122,6 +122,54 @@ def test_gemv_u8_streaming_kernel(ctx, orc, shape):
         b.free()
 
 
+def test_gemv_u8_chain_with_constant_matrices(ctx, orc):
+    """A stack of one-vector products, each consuming the previous one's output, with the
+    matrices declared constant (what the Gemv delegator does for weight tensors): the kernels
+    fetch their first matrix bytes ahead of the dependency wait, the vector only after it.
+    Every stage must equal the oracle chain, also when replayed from a graph."""
+    import ctypes
+    rows = K = 1024
+    depth = 6
+    rng = np.random.Generator(np.random.PCG64(77))
+    mats = [rng.integers(0, 256, size=(1, rows, K), dtype=np.uint8) for _ in range(depth)]
+    x0 = rng.integers(0, 256, size=(1, K), dtype=np.uint8)
+    mult = np.float32(1.0 / (np.sqrt(K) * 74))  # keeps the spread of the values from stage to stage
+    exp, v = [], x0
+    for m in mats:
+        v = orc.gemv_u8(m, v, None, 1, rows, K, 127, 128, mult, 128, True).reshape(1, K)
+        exp.append(v.copy())
+    assert len({e.tobytes() for e in exp}) == depth and all(e.std() > 30 for e in exp), "degenerate chain"
+    dm = [ctx.upload(m) for m in mats]
+    acts = [ctx.upload(x0)] + [ctx.alloc(rows) for _ in range(depth)]
+    L = __import__("mace_b200").lib()
+
+    def enqueue():
+        for i in range(depth):
+            ctx.gemv_u8(dm[i], acts[i], None, acts[i + 1], 1, rows, K, 127, 128, mult, 128, True)
+
+    ctx.set_option("gemv_lhs_const", 1)
+    try:
+        enqueue()
+        for i in range(depth):
+            assert np.array_equal(ctx.download(acts[i + 1], (1, K), np.uint8), exp[i]), i
+        ctx._check(L.mb_graph_begin(ctx.h))
+        enqueue()
+        graph = ctypes.c_void_p()
+        ctx._check(L.mb_graph_end(ctx.h, ctypes.byref(graph)))
+        for _ in range(3):
+            for a in acts[1:]:
+                ctx._check(L.mb_memset(ctx.h, a.ptr, 0, a.nbytes))
+            ctx._check(L.mb_graph_launch(ctx.h, graph))
+            for i in range(depth):
+                assert np.array_equal(ctx.download(acts[i + 1], (1, K), np.uint8), exp[i]), i
+        ctx._check(L.mb_graph_destroy(ctx.h, graph))
+    finally:
+        ctx.set_option("gemv_lhs_const", 0)
+    ctx.sync()
+    for b in dm + acts:
+        b.free()
+
+
 # ---- Conv2D ------------------------------------------------------------------------
 # shapes in the style of conv_2d_test.cc:1348-1397: N, H, W, C, O, KH, KW, stride, padding
 
