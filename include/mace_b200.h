@@ -120,6 +120,10 @@ int mb_graph_destroy(mb_context *ctx, void *graph_exec);
  * counts only tcgen05 tensor-core GEMM launches. */
 uint64_t mb_launch_count(const mb_context *ctx);
 uint64_t mb_launch_count_tensor_core(const mb_context *ctx);
+/* ... and how many of those ran on CTA pairs (see the "pair" option). */
+uint64_t mb_launch_count_pair(const mb_context *ctx);
+/* How many such pairs the device holds at once (0 before the first pair launch). */
+int mb_pair_clusters(const mb_context *ctx);
 /* Options: "tensor_cores" (1 default; 0 forces the CUDA-core GEMM, for A/B
  * tests), "mn_major" (1 default; 0 transposes MN-major operands to K-major
  * in scratch instead of describing them to the tensor core directly),
@@ -131,6 +135,10 @@ uint64_t mb_launch_count_tensor_core(const mb_context *ctx);
  * stream order instead of with programmatic stream serialization),
  * "dw_waves" (1 default: the 3x3 depthwise grid is sized so that all blocks
  * are resident at once; n sizes it for n such rounds with shorter row runs),
+ * "pair" (0 default; 1: uint8 GEMMs of at least one round of 256 x 256 tiles
+ * over the SM pairs run on clusters of two CTAs -- tcgen05.mma.cta_group::2,
+ * each CTA loading half of a tile's operands; 2: wherever that kernel can
+ * run, for tests.  Measured no faster than one CTA per 128 x 256 tile),
  * "split_k" (1 default: a product with fewer output tiles than a quarter of
  * the SMs and a depth of 2048 or more is computed as 4 or 8 depth runs on as
  * many times the SMs, their exact int32 results added by a second kernel;

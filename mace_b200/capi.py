@@ -63,6 +63,8 @@ PROTOTYPES = {
     "mb_graph_destroy": (_int, [_vp, _vp]),
     "mb_launch_count": (C.c_uint64, [_vp]),
     "mb_launch_count_tensor_core": (C.c_uint64, [_vp]),
+    "mb_launch_count_pair": (C.c_uint64, [_vp]),
+    "mb_pair_clusters": (C.c_int, [_vp]),
     "mb_set_option": (_int, [_vp, C.c_char_p, _int]),
     "mb_gemm_u8": (_int, [_vp] * 5 + [_int] + [_i64] * 4 + [_int] * 5 + [_i32] * 5 + [_int]),
     "mb_gemv_u8": (_int, [_vp] * 5 + [_int] + [_i64] * 3 + [_int] * 2 + [_i32] * 2 +
@@ -232,6 +234,10 @@ class Context:
     @property
     def launches_tensor_core(self):
         return int(lib().mb_launch_count_tensor_core(self.h))
+
+    @property
+    def launches_pair(self):
+        return int(lib().mb_launch_count_pair(self.h))
 
     @property
     def stream(self):

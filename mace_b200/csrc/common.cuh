@@ -41,6 +41,7 @@ struct mb_context {
   int use_mn_major = 1;
   uint64_t launches = 0;         // kernels launched through this context
   uint64_t launches_tc = 0;      // of which tcgen05 GEMM launches
+  uint64_t launches_pair = 0;    // of which on CTA pairs (not adjusted for graph replays)
   int capturing = 0;             // inside mb_graph_begin / mb_graph_end
   long long *tc_timeline = nullptr;  // optional device buffer: per-role clock stamps of CTA 0
   uint64_t capture_launches0 = 0, capture_launches_tc0 = 0;
@@ -57,6 +58,11 @@ struct mb_context {
                                  // the stream and the depthwise kernel may not read the tap words
                                  // before it has waited for its predecessor
   int skinny_max_m = 16;         // row counts up to this take the streaming few-row GEMM
+  int max_pair_clusters = 0;     // co-resident clusters of the pair GEMM (0: not asked yet)
+  int pair_gemm = 0;             // large GEMMs on CTA pairs (clusters of two sharing each tile's B): 1 where
+                                 // it applies, 2 wherever it can run.  Off by default: measured equal at 8192^3
+                                 // (409 vs 410 us) and slower at 4096^3 (54.7 vs 51.6 us): the main loop is paced
+                                 // by the tensor pipe at the clocks the power cap leaves, not by operand traffic
   int split_k = 1;               // few-tile, long-depth GEMMs: cut the depth into runs over more SMs
   int gemv_stream = 1;           // one-vector GEMV through the bulk-copy streaming kernel
   int gemv_lhs_const = 0;        // the GEMV matrix is a weight: it may be fetched ahead of the dependency wait

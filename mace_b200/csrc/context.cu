@@ -386,6 +386,10 @@ uint64_t mb_launch_count_tensor_core(const mb_context *ctx) {
   return ctx ? ctx->launches_tc : 0;
 }
 
+uint64_t mb_launch_count_pair(const mb_context *ctx) { return ctx ? ctx->launches_pair : 0; }
+
+int mb_pair_clusters(const mb_context *ctx) { return ctx ? ctx->max_pair_clusters : 0; }
+
 int mb_set_option(mb_context *ctx, const char *name, int value) {
   if (ctx == nullptr || name == nullptr) return MB_INVALID_ARGS;
   if (strcmp(name, "tensor_cores") == 0) {
@@ -404,6 +408,8 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
   } else if (strcmp(name, "skinny_max_m") == 0) {
     if (value < 0 || value > 16) return mb_fail(ctx, MB_INVALID_ARGS, "skinny_max_m must be 0 .. 16");
     ctx->skinny_max_m = value;
+  } else if (strcmp(name, "pair") == 0) {
+    ctx->pair_gemm = value;
   } else if (strcmp(name, "split_k") == 0) {
     ctx->split_k = value;
   } else if (strcmp(name, "gemv_stream") == 0) {

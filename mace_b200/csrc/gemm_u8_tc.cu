@@ -39,6 +39,8 @@
 //                the TMA boxes of the first pointwise convolutions carry no padding.
 // Every wait is bounded; on a timeout the kernel records a status word, lets
 // outstanding copies land, frees its TMEM and returns.
+#include <algorithm>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -121,13 +123,17 @@ struct TcParams {
 // eighth (BN = 128) or a quarter (BN = 64) more work for a tensor pipe that short-K tiles leave
 // idle anyway -- instead of a pass of the preparation warps over every A tile in shared memory,
 // which cost these issue-bound kernels a fifth of their instructions.
-template <int BN, bool B_MN, int KB = BK, bool TCR = false>
+// PAIR: two CTAs of a cluster work on one 256 x 256 tile: each holds 128 rows of A and 128 of
+// the 256 columns of B in its shared memory (two thirds of the operand bytes per row of C that
+// a lone CTA pulls for 128 x 256), and its own 128 rows of the accumulator in its tensor memory.
+template <int BN, bool B_MN, int KB = BK, bool TCR = false, bool PAIR = false>
 struct TileCfg {
+  static_assert(!PAIR || (BN == 256 && KB == 128 && !TCR), "pairs: 256 columns, 128-byte rows");
   static_assert(KB == 128 || !B_MN, "short rows are for K-major operands");
   static_assert(!TCR || (!B_MN && BN <= 128), "ones rows follow a K-major B tile of at most 128 rows");
   static constexpr int BNX = TCR ? BN + 16 : BN;  // MMA N and TMEM columns per accumulator
   static constexpr int A_BYTES = BM * KB;
-  static constexpr int B_TMA_BYTES = B_MN ? ((BN + 127) / 128) * 128 * KB : BN * KB;  // what TMA brings
+  static constexpr int B_TMA_BYTES = PAIR ? 128 * KB : B_MN ? ((BN + 127) / 128) * 128 * KB : BN * KB;  // what TMA brings
   static constexpr int B_BYTES = B_TMA_BYTES + (TCR ? 16 * KB : 0);
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGE_TX = A_BYTES + B_TMA_BYTES;
@@ -176,8 +182,8 @@ __device__ __forceinline__ uint32_t sum16(const uint4 v, uint32_t s) {
 // advanced by gridDim.x per step.
 struct TileIter {
   int tm, tn, b;
-  __device__ __forceinline__ TileIter(const TcParams &p) {
-    const unsigned t = blockIdx.x;  // < tiles of the first wave, one division pair per kernel
+  __device__ __forceinline__ TileIter(const TcParams &p, bool pair = false) {
+    const unsigned t = pair ? blockIdx.x >> 1 : blockIdx.x;  // < tiles of the first wave, one division pair per kernel
     tm = t % p.tiles_m;
     const unsigned q = t / p.tiles_m;
     tn = q % p.tiles_n;
@@ -244,6 +250,7 @@ struct EpiTile {
   int32_t row_term;
   const int32_t *ct_base;  // column terms of the 64 columns (shared memory)
   uint32_t tempty;         // barrier that returns the accumulator buffer
+  uint32_t tempty_leader;  // pairs, odd CTA: the even CTA's barrier too (shared::cluster address)
   uint4 *stage_row;        // this lane's row of the staging buffer (STG chunks of 16 bytes)
   int swz;
   uint32_t stage_addr;
@@ -254,7 +261,7 @@ struct EpiTile {
 // 32 rows x 64 columns of one tile: four 16-column chunks from TMEM (the next one in flight
 // while the current one is requantized), staged STG chunks at a time for a TMA store of
 // 32 rows x 16*STG bytes.
-template <int STG, int MODE>
+template <int STG, int MODE, bool PAIR = false>
 __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap &tmap_c,
                                              const TcParams &p) {
   uint32_t r[2][CHUNK];
@@ -271,7 +278,10 @@ __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap
       // barrier) back before the staging and the store.
       tc_fence_before_sync();
       __syncwarp();
-      if (e.lane == 0) mbar_arrive(e.tempty);
+      if (e.lane == 0) {
+        mbar_arrive(e.tempty);
+        if (PAIR && e.tempty_leader != 0) mbar_arrive_cluster(e.tempty_leader);
+      }
     }
     if ((i & (STG - 1)) == 0) {
       // the previous store must have read the staging buffer before it is refilled
@@ -291,14 +301,18 @@ __device__ __forceinline__ void epi_tma_tile(const EpiTile &e, const CUtensorMap
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS, int KB, bool TCR_ON = false>
+template <int BN, bool A_MN, bool B_MN, bool FUSE_SUMS, int KB, bool TCR_ON = false, bool PAIR = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_c, const TcParams p) {
   constexpr bool TCR = TCR_ON && FUSE_SUMS && BN <= 128;
-  using Cfg = TileCfg<BN, B_MN, KB, TCR>;
+  static_assert(!PAIR || !FUSE_SUMS, "pairs take their operand sums from the sums kernel");
+  using Cfg = TileCfg<BN, B_MN, KB, TCR, PAIR>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;  // rows of C per tile (of the pair)
+  // pairs: the even CTA issues the MMAs for both; rank is this CTA's half of the rows and columns
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
   constexpr int BNX = Cfg::BNX;
   // the preparation warps read the operand tiles in shared memory only for the sums the tensor
   // core does not deliver: B's (needed when zp_a != 0), and A's without the ones rows
@@ -342,15 +356,21 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int b = 0; b < NUM_ACC; ++b) {
       mbar_init(tfull_bar + 8 * b, 1);
-      mbar_init(tempty_bar + 8 * b, 4 * (BN / 64));
+      // (pairs: the even CTA's barrier also counts the odd CTA's epilogue warps)
+      mbar_init(tempty_bar + 8 * b, (PAIR && rank == 0 ? 2 : 1) * 4 * (BN / 64));
       mbar_init(terms_bar + 8 * b, PREP_WARPS);
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   if (TCR) {
     // the 16 rows of ones behind every stage's B tile (TMA never writes there)
@@ -364,6 +384,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // both CTAs' barriers exist before either arrives on the other's
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) MB_STAMP(1);
@@ -387,7 +408,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // of B is loaded once, on the first pass through the ring, and then left in place: TMA
       // handles short rows one by one, and the B rows would be a third to a half of them.
       const bool b_once = p.tiles_n == 1 && p.k_blocks == 1 && !p.b_batched;
-      for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
+      for (TileIter it(p, PAIR); ok && it.valid(p); it.next(p), ++local) {
         const int b = it.b, tm = it.tm, tn = it.tn;
         const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -401,6 +422,16 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sb = sa + Cfg::A_BYTES;
           const bool skip_b = b_once && local >= STAGES;
+          if (PAIR) {
+            // Both CTAs' bytes are counted on the even CTA's barrier, which its MMA thread
+            // waits on: this CTA's 128 rows of A and 128 of the tile's 256 columns of B.
+            if (rank == 0) mbar_arrive_expect_tx(fb, 2 * Cfg::STAGE_TX);
+            const uint32_t fbc = mapa_shared(fb, 0);
+            if (A_MN) tma_load_3d_pair(sa, &tmap_a, fbc, tm * TILE_M + rank * BM, kb * KB, ab);
+            else tma_load_3d_pair(sa, &tmap_a, fbc, kb * KB, tm * TILE_M + rank * BM, ab);
+            if (B_MN) tma_load_3d_pair(sb, &tmap_b, fbc, tn * BN + rank * 128, kb * KB, bb);
+            else tma_load_3d_pair(sb, &tmap_b, fbc, kb * KB, tn * BN + rank * 128, bb);
+          } else {
           mbar_arrive_expect_tx(fb, skip_b ? Cfg::A_BYTES : Cfg::STAGE_TX);
           if (A_MN) {
             tma_load_3d(sa, &tmap_a, fb, tm * BM, kb * KB, ab);
@@ -415,6 +446,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               tma_load_3d(sb + j * 128 * KB, &tmap_b, fb, tn * BN + j * 128, kb * KB, bb);
           } else {
             tma_load_3d(sb, &tmap_b, fb, kb * KB, tn * BN, bb);
+          }
           }
           if (local == 0) MB_STAMP(2 + (kb < 3 ? kb : 3));  // TMA of k-block kb issued
           if (kb == 0) MB_STAMP_TILE(local, 0);
@@ -432,8 +464,10 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // What the thread does between two MMAs has to fit into the time the tensor pipe's short
     // queue keeps it busy, and for tiles of one K step it is on the critical path outright:
     // the descriptors are one add per step and nothing in the loop is warp-collective.
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, A_MN, B_MN, BM, BNX);
+    if (PAIR && rank != 0) {
+      // the odd CTA issues no MMAs: the even CTA's thread drives both tensor cores
+    } else if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, A_MN, B_MN, TILE_M, BNX);
       // K-major tile: rows of KB bytes, 8-row groups SBO bytes apart; a K step moves 32 bytes
       // inside the swizzled row.  MN-major tile: k-rows of 128 bytes (128 elements of M or N),
       // 8-k-row groups 1024 bytes apart, 128-element atoms 128 * KB bytes apart; a K step moves
@@ -450,7 +484,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       int local = 0;
-      for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
+      for (TileIter it(p, PAIR); ok && it.valid(p); it.next(p), ++local) {
         if (!mbar_wait(tempty_bar + 8 * acc_buf, acc_phase ^ 1, abort_flag, WAIT_BUDGET)) {
           *abort_flag = 1;
           atomicCAS(p.status, 0, MB_DEV_TIMEOUT_MMA);
@@ -471,6 +505,12 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
           const uint64_t a_desc = a_base | static_cast<uint64_t>((sa >> 4) & 0x3FFFu);
           const uint64_t b_desc = b_base | static_cast<uint64_t>(((sa + Cfg::A_BYTES) >> 4) & 0x3FFFu);
+          if (PAIR) {
+            const int ksteps = (kb + 1 < p.k_blocks) ? KB / UMMA_K : last_ksteps;
+            for (int j = 0; j < ksteps; ++j)
+              mma_i8_ss_pair(d_tmem, a_desc + j * a_step, b_desc + j * b_step, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+            mma_commit_pair(empty_bar + 8 * stage, 3);  // frees the stage in both CTAs
+          } else {
           if (kb + 1 < p.k_blocks || last_ksteps == KB / UMMA_K) {
 #pragma unroll
             for (int j = 0; j < KB / UMMA_K; ++j)
@@ -480,13 +520,15 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               mma_i8_ss(d_tmem, a_desc + j * a_step, b_desc + j * b_step, idesc, (kb > 0 || j > 0) ? 1u : 0u);
           }
           mma_commit(empty_bar + 8 * stage);  // frees the stage when the MMAs have read it
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        mma_commit(tfull_bar + 8 * acc_buf);  // accumulator complete
+        if (PAIR) mma_commit_pair(tfull_bar + 8 * acc_buf, 3);  // accumulator complete, in both CTAs
+        else mma_commit(tfull_bar + 8 * acc_buf);               // accumulator complete
         if (local == 0) MB_STAMP(10);
         MB_STAMP_TILE(local, 2);
         if (++acc_buf == NUM_ACC) {
@@ -505,13 +547,13 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t acc_phase = 0;
     bool ok = true;
     int local = 0;
-    for (TileIter it(p); ok && it.valid(p); it.next(p), ++local) {
+    for (TileIter it(p, PAIR); ok && it.valid(p); it.next(p), ++local) {
       const int b = it.b, tm = it.tm, tn = it.tn;
       uint32_t sa_sum = 0, sb_sum[(BN + 127) / 128];
 #pragma unroll
       for (int j = 0; j < (BN + 127) / 128; ++j) sb_sum[j] = 0;
       // global inputs of the terms, requested before the main loop is followed
-      const int64_t m = static_cast<int64_t>(tm) * BM + r;
+      const int64_t m = static_cast<int64_t>(tm) * TILE_M + rank * BM + r;
       int32_t row_bias = 0, col_bias[(BN + 127) / 128];
       if (p.bias != nullptr && p.bias_per_row && m < p.M) row_bias = __ldg(p.bias + m);
       if (!FUSE_SUMS && p.sum_a != nullptr && m < p.M) {
@@ -625,7 +667,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // 64-byte swizzle: chunk c of row r at (c ^ (r >> 1)) & 3
     const int swz = STG == 2 ? ((lane >> 2) & 1) : ((lane >> 1) & 3);
     int local = 0;
-    for (TileIter it(p); it.valid(p); it.next(p), ++local) {
+    for (TileIter it(p, PAIR); it.valid(p); it.next(p), ++local) {
       if (local % GROUPS != group) continue;
       const int b = it.b, tm = it.tm, tn = it.tn;
       const int acc_buf = local % NUM_ACC;
@@ -639,7 +681,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after_sync();
       if (local == 0 && warp == FIRST_EPI_WARP && lane == 0) MB_STAMP(12);
       if (warp == FIRST_EPI_WARP && lane == 0) MB_STAMP_TILE(local, 3);
-      const int m0 = tm * BM + quarter * 32;           // first row of this warp
+      const int m0 = tm * TILE_M + rank * BM + quarter * 32;  // first row of this warp
       const int64_t m = static_cast<int64_t>(m0) + lane;
       const bool row_ok = m < p.M;
       int32_t row_term = row_term_sm[acc_buf * 128 + quarter * 32 + lane];
@@ -657,16 +699,17 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (p.c_tma) {
         // one decision per tile (not per chunk or value: with so few warps per scheduler
         // a branch's latency is not hidden)
-        const EpiTile e{tbase, row_term, ct_base, tempty_bar + 8 * acc_buf, stage_row, swz, stage_addr,
-                        n_first, m0, b, lane};
+        const EpiTile e{tbase, row_term, ct_base, tempty_bar + 8 * acc_buf,
+                        (PAIR && rank != 0) ? mapa_shared(tempty_bar + 8 * acc_buf, 0) : 0u, stage_row, swz,
+                        stage_addr, n_first, m0, b, lane};
         switch (p.rq_variant) {
-          case 8: epi_tma_tile<STG, 8>(e, tmap_c, p); break;
-          case 5: epi_tma_tile<STG, 5>(e, tmap_c, p); break;
-          case 4: epi_tma_tile<STG, 4>(e, tmap_c, p); break;
-          case 3: epi_tma_tile<STG, 3>(e, tmap_c, p); break;
-          case 2: epi_tma_tile<STG, 2>(e, tmap_c, p); break;
-          case 1: epi_tma_tile<STG, 1>(e, tmap_c, p); break;
-          default: epi_tma_tile<STG, 0>(e, tmap_c, p); break;
+          case 8: epi_tma_tile<STG, 8, PAIR>(e, tmap_c, p); break;
+          case 5: epi_tma_tile<STG, 5, PAIR>(e, tmap_c, p); break;
+          case 4: epi_tma_tile<STG, 4, PAIR>(e, tmap_c, p); break;
+          case 3: epi_tma_tile<STG, 3, PAIR>(e, tmap_c, p); break;
+          case 2: epi_tma_tile<STG, 2, PAIR>(e, tmap_c, p); break;
+          case 1: epi_tma_tile<STG, 1, PAIR>(e, tmap_c, p); break;
+          default: epi_tma_tile<STG, 0, PAIR>(e, tmap_c, p); break;
         }
       } else {
         // direct stores: int32 output, or a uint8 output whose rows TMA cannot address
@@ -730,7 +773,10 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar + 8 * acc_buf);
+        if (lane == 0) {
+          mbar_arrive(tempty_bar + 8 * acc_buf);
+          if (PAIR && rank != 0) mbar_arrive_cluster(mapa_shared(tempty_bar + 8 * acc_buf, 0));
+        }
       }
       if (warp == FIRST_EPI_WARP && lane == 0) MB_STAMP(local == 0 ? 13 : 14);
       if (warp == FIRST_EPI_WARP && lane == 0) MB_STAMP_TILE(local, 4);
@@ -748,9 +794,14 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  // pairs: neither CTA's shared or tensor memory may go away while the other can still reach
+  // it (the even CTA's MMAs read the odd CTA's tiles; the odd CTA arrives on the even one's
+  // barriers)
+  if (PAIR) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -801,6 +852,64 @@ int launch_cfg(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, co
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   ctx->launches_tc++;
+  return MB_SUCCESS;
+}
+
+// The CTA-pair kernel: clusters of two, as many as there are SM pairs (or tiles).
+template <bool A_MN, bool B_MN>
+int launch_pair(mb_context *ctx, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc, TcParams &p) {
+  using Cfg = TileCfg<256, B_MN, BK, false, true>;
+  auto kern = gemm_u8_tc_kernel<256, A_MN, B_MN, false, BK, false, true>;
+  constexpr int cfg_id = 56 + (A_MN ? 2 : 0) + (B_MN ? 1 : 0);
+  if (!(ctx->func_attr_mask & (1ull << cfg_id))) {
+    MB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    ctx->func_attr_mask |= (1ull << cfg_id);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(NUM_THREADS);
+  // The tiles are dealt out to the clusters once, so every cluster of the launch has to be
+  // resident at the same time: ask how many fit (the SMs of a pair share a TPC, and not every
+  // TPC of every GPC need be available), once per context.
+  if (ctx->max_pair_clusters == 0) {
+    cudaLaunchConfig_t probe = {};
+    probe.gridDim = dim3(2 * (ctx->num_sms / 2));
+    probe.blockDim = dim3(NUM_THREADS);
+    probe.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cudaLaunchAttribute pa[1];
+    pa[0].id = cudaLaunchAttributeClusterDimension;
+    pa[0].val.clusterDim.x = 2;
+    pa[0].val.clusterDim.y = 1;
+    pa[0].val.clusterDim.z = 1;
+    probe.attrs = pa;
+    probe.numAttrs = 1;
+    int n = 0;
+    MB_CUDA(ctx, cudaOccupancyMaxActiveClusters(&n, kern, &probe));
+    if (n < 1) return mb_fail(ctx, MB_RUNTIME_ERROR, "no CTA pair of the GEMM kernel fits the device");
+    ctx->max_pair_clusters = n;
+  }
+  const int64_t pairs = std::min<int64_t>(ctx->num_sms / 2, ctx->max_pair_clusters);
+  const int clusters = static_cast<int>(p.total_tiles < pairs ? p.total_tiles : pairs);
+  p.step_m = clusters % p.tiles_m;
+  p.step_n = (clusters / p.tiles_m) % p.tiles_n;
+  p.step_b = (clusters / p.tiles_m) / p.tiles_n;
+  ctx->pdl_next_gemm = 0;
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl_chain ? 2 : 1;
+  MB_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p));
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  ctx->launches_tc++;
+  ctx->launches_pair++;
   return MB_SUCCESS;
 }
 
@@ -921,6 +1030,18 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.status = ctx->dev_status;
   p.timeline = ctx->tc_timeline;
   p.sums_pending = (ctx->pdl_next_gemm && ctx->pdl_chain && (sum_a != nullptr || sum_b != nullptr)) ? 1 : 0;
+  // At least one round of 256 x 256 tiles over the SM pairs: two CTAs per tile, each loading
+  // half of it (the lone-CTA kernel is bound by the bytes its 128 x 256 tiles pull from L2).
+  // (option value 2 takes the pair kernel wherever it can run, for tests on small shapes)
+  const bool pair = ctx->pair_gemm && !fuse && !fuse_bmn && k_split == 1 && p.c_tma && ctx->num_sms >= 2 &&
+                    (ctx->pair_gemm == 2 ||
+                     (BN == 256 && K >= 512 && batch * ceil_div64(M, 256) * ceil_div64(N, 256) >= ctx->num_sms / 2));
+  if (pair) {
+    BN = 256;
+    p.tiles_n = static_cast<int>(ceil_div64(N, 256));
+    p.tiles_m = static_cast<int>(ceil_div64(M, 256));
+    p.total_tiles = batch * p.tiles_m * p.tiles_n;
+  }
 
   CUtensorMap ta, tb, tc;
   if (p.c_tma) {
@@ -947,7 +1068,15 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   if (b_mn) {
     MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, N, K, nb_b, N * K, 128, BK));
   } else {
-    MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, K, N, nb_b, k_split > 1 ? K : N * K, KBsel, BN, kswz, k_full));
+    MB_RETURN_IF_ERROR(make_map_u8(ctx, &tb, B, K, N, nb_b, k_split > 1 ? K : N * K, KBsel, pair ? 128 : BN, kswz, k_full));
+  }
+  if (pair) {
+    if (a_mn) {
+      if (b_mn) return launch_pair<true, true>(ctx, ta, tb, tc, p);
+      return launch_pair<true, false>(ctx, ta, tb, tc, p);
+    }
+    if (b_mn) return launch_pair<false, true>(ctx, ta, tb, tc, p);
+    return launch_pair<false, false>(ctx, ta, tb, tc, p);
   }
 
 #define MB_TC_DISPATCH(BN_)                                                         \

@@ -264,6 +264,32 @@ def test_few_rows_against_row_major_b(ctx, orc, shape, out_int32):
         assert len(np.unique(got)) > 16
 
 
+@pytest.mark.parametrize("shape", [(256, 256, 512, False, False, 1), (384, 320, 640, False, False, 1),
+                                   (512, 256, 256, True, False, 1), (272, 528, 384, True, True, 2),
+                                   (640, 1024, 2048, False, True, 1)])
+def test_cta_pair_kernel(ctx, orc, shape):
+    """The GEMM on clusters of two CTAs (one 256 x 256 tile per pair, the even CTA issuing the
+    MMAs for both, each CTA loading its half of the operands and draining its own 128 rows):
+    all four operand orders, ragged M and N (the odd CTA's rows partly or wholly outside the
+    matrix), a batch, several tiles per pair; every byte against the oracle and against the
+    one-CTA kernel."""
+    M, N, K, a_cm, b_cm, batch = shape
+    case = gemm_case(orc, 7, batch, M, N, K, bias_len=N, a_col_major=a_cm, b_col_major=b_cm)
+    got = {}
+    for pair in (2, 0):
+        ctx.set_option("pair", pair)
+        ctx.set_option("split_k", 0)
+        try:
+            before = ctx.launches_pair
+            got[pair], exp = run_gemm(ctx, orc, case, batch, M, N, K, a_col_major=a_cm, b_col_major=b_cm)
+            assert (ctx.launches_pair - before) == (1 if pair else 0)
+        finally:
+            ctx.set_option("pair", 0)
+            ctx.set_option("split_k", 1)
+        assert np.array_equal(got[pair], exp), pair
+    assert len(np.unique(got[2])) > 50
+
+
 def test_empty_and_bad_arguments(ctx):
     import mace_b200
     buf = ctx.alloc(64)
