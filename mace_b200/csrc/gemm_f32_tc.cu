@@ -162,6 +162,7 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  mb_grid_dep_launch();  // the kernel behind this one may start its own prologue
 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tmap_x);
@@ -187,6 +188,9 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched only this CTA's shared and tensor memory; from here on the roles read
+  // and write global memory, which the kernel in front of this one may still be producing
+  mb_grid_dep_wait();
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -579,7 +583,7 @@ int launch_f32(mb_context *ctx, const CUtensorMap &tx, const CUtensorMap &tw, co
   p.step_m = grid % p.tiles_m;
   p.step_n = (grid / p.tiles_m) % p.tiles_n;
   p.step_b = (grid / p.tiles_m) / p.tiles_n;
-  kern<<<grid, F_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tx, tw, tc, p);
+  MB_CUDA(ctx, mb_launch_chained(ctx, kern, dim3(grid), dim3(F_THREADS), Cfg::SMEM_BYTES, tx, tw, tc, p));
   MB_CUDA(ctx, cudaGetLastError());
   ctx->launches++;
   ctx->launches_tc++;

@@ -138,6 +138,8 @@ __device__ __forceinline__ void at8(const float d[8], float o[6]) {
 template <int TILE>
 __global__ void __launch_bounds__(256) wino_input_kernel(const WinoParams p) {
   constexpr int IN = TILE + 2;
+  mb_grid_dep_launch();
+  mb_grid_dep_wait();
   const int tiles = p.th * p.tw;
   const int64_t total = static_cast<int64_t>(p.N) * p.C * tiles;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -201,6 +203,8 @@ __global__ void __launch_bounds__(256) wino_input_kernel(const WinoParams p) {
 // ---- output transform: M[T][O][N*tiles] -> NCHW (+ bias, activation) --------------------
 template <int TILE>
 __global__ void __launch_bounds__(256) wino_output_kernel(const WinoParams p) {
+  mb_grid_dep_launch();
+  mb_grid_dep_wait();
   const int tiles = p.th * p.tw;
   const int64_t total = static_cast<int64_t>(p.N) * p.O * tiles;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -272,6 +276,8 @@ template <int TILE>
 __global__ void __launch_bounds__(256)
 wino_output_plane_kernel(const WinoParams p, int threads_per_plane, int planes_per_block) {
   extern __shared__ float sm[];  // [planes_per_block][Ho * Wo]
+  mb_grid_dep_launch();
+  mb_grid_dep_wait();
   const int tiles = p.th * p.tw;
   const int hw = p.Ho * p.Wo;
   const int64_t planes = static_cast<int64_t>(p.N) * p.O;
@@ -417,8 +423,10 @@ int mb_conv3x3_winograd_f32_nchw(mb_context *ctx, const float *in, const float *
   p.act = activation; p.max_limit = max_limit; p.coef = coefficient;
   {
     const unsigned blocks = static_cast<unsigned>(ceil_div64(N * C * tiles, 256));
-    if (tile == 2) wino_input_kernel<2><<<blocks, 256, 0, ctx->stream>>>(p);
-    else wino_input_kernel<6><<<blocks, 256, 0, ctx->stream>>>(p);
+    // (all three kernels of the convolution are chained: each waits for its predecessor where it
+    // first touches global memory and lets its successor's CTAs set up meanwhile)
+    if (tile == 2) MB_CUDA(ctx, mb_launch_chained(ctx, wino_input_kernel<2>, dim3(blocks), dim3(256), 0, p));
+    else MB_CUDA(ctx, mb_launch_chained(ctx, wino_input_kernel<6>, dim3(blocks), dim3(256), 0, p));
     MB_CUDA(ctx, cudaGetLastError());
     ctx->launches++;
   }
@@ -436,13 +444,14 @@ int mb_conv3x3_winograd_f32_nchw(mb_context *ctx, const float *in, const float *
   if (plane_out) {
     const unsigned blocks = static_cast<unsigned>(ceil_div64(N * O, planes_per_block));
     const size_t smem = planes_per_block * out_plane_bytes;
-    wino_output_plane_kernel<6><<<blocks, 256, smem, ctx->stream>>>(p, threads_per_plane, planes_per_block);
+    MB_CUDA(ctx, mb_launch_chained(ctx, wino_output_plane_kernel<6>, dim3(blocks), dim3(256), smem, p, threads_per_plane,
+                                   planes_per_block));
     MB_CUDA(ctx, cudaGetLastError());
     ctx->launches++;
   } else {
     const unsigned blocks = static_cast<unsigned>(ceil_div64(N * O * tiles, 256));
-    if (tile == 2) wino_output_kernel<2><<<blocks, 256, 0, ctx->stream>>>(p);
-    else wino_output_kernel<6><<<blocks, 256, 0, ctx->stream>>>(p);
+    if (tile == 2) MB_CUDA(ctx, mb_launch_chained(ctx, wino_output_kernel<2>, dim3(blocks), dim3(256), 0, p));
+    else MB_CUDA(ctx, mb_launch_chained(ctx, wino_output_kernel<6>, dim3(blocks), dim3(256), 0, p));
     MB_CUDA(ctx, cudaGetLastError());
     ctx->launches++;
   }
