@@ -70,6 +70,14 @@ int mb_memcpy_d2d(mb_context *ctx, void *dst_dev, const void *src_dev, size_t by
 int mb_upload_h2d(mb_context *ctx, void *dst_dev, const void *src_host, size_t bytes);
 int mb_upload_wait_event(mb_context *ctx, void *event);
 int mb_upload_signal(mb_context *ctx);
+/* The other direction: a copy to PINNED host memory that starts when the compute stream has
+ * reached this call but runs on a third stream, so the kernels enqueued behind it do not wait
+ * for it; done_event (from mb_event_create, may be NULL) is recorded behind the copy.  Whoever
+ * overwrites src_dev later must wait for that event: mb_stream_wait_event makes the compute
+ * stream do so.  (No counterpart in the reference: its runtimes copy synchronously,
+ * mace/core/runtime/runtime.h.) */
+int mb_download_d2h(mb_context *ctx, void *dst_host, const void *src_dev, size_t bytes, void *done_event);
+int mb_stream_wait_event(mb_context *ctx, void *event);
 int mb_stream_sync(mb_context *ctx);
 
 /* ---- Failure paths ---------------------------------------------------------

@@ -50,6 +50,8 @@ PROTOTYPES = {
     "mb_upload_h2d": (_int, [_vp, _vp, _vp, _sz]),
     "mb_upload_wait_event": (_int, [_vp, _vp]),
     "mb_upload_signal": (_int, [_vp]),
+    "mb_download_d2h": (C.c_int, [_vp, _vp, _vp, C.c_size_t, _vp]),
+    "mb_stream_wait_event": (C.c_int, [_vp, _vp]),
     "mb_event_sync": (_int, [_vp, _vp]),
     "mb_stream_sync": (_int, [_vp]),
     "mb_stream": (_vp, [_vp]),

@@ -29,6 +29,8 @@ struct mb_context {
   cudaStream_t stream = nullptr;
   cudaStream_t upload_stream = nullptr;  // created on first use: uploads that overlap the compute stream
   cudaEvent_t upload_event = nullptr;    // last mb_upload_signal
+  cudaStream_t download_stream = nullptr;  // created on first use: result copies that do not hold up the compute stream
+  cudaEvent_t download_event = nullptr;    // "the compute stream has reached this mb_download_d2h"
   // Scratch arena, the analogue of the runtime's RENT_SCRATCH buffers
   // (mace/core/runtime/runtime.cc:153-182): one growable device block that a
   // call carves from the start; contents do not survive the call.

@@ -97,6 +97,11 @@ int mb_destroy(mb_context *ctx) {
   if (ctx == nullptr) return MB_INVALID_ARGS;
   cudaSetDevice(ctx->device);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  if (ctx->download_stream) {
+    cudaStreamSynchronize(ctx->download_stream);
+    cudaEventDestroy(ctx->download_event);
+    cudaStreamDestroy(ctx->download_stream);
+  }
   if (ctx->upload_stream) {
     cudaStreamSynchronize(ctx->upload_stream);
     cudaEventDestroy(ctx->upload_event);
@@ -246,6 +251,28 @@ int mb_upload_signal(mb_context *ctx) {
   MB_RETURN_IF_ERROR(upload_stream_ready(ctx));
   MB_CUDA(ctx, cudaEventRecord(ctx->upload_event, ctx->upload_stream));
   MB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->upload_event, 0));
+  return MB_SUCCESS;
+}
+
+int mb_download_d2h(mb_context *ctx, void *dst, const void *src, size_t bytes, void *done_event) {
+  if (ctx == nullptr || (bytes && (!dst || !src))) return MB_INVALID_ARGS;
+  if (ctx->capturing) return mb_fail(ctx, MB_INVALID_ARGS, "mb_download_d2h: not inside a graph capture");
+  if (ctx->download_stream == nullptr) {
+    MB_CUDA(ctx, cudaSetDevice(ctx->device));
+    MB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->download_stream, cudaStreamNonBlocking));
+    MB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->download_event, cudaEventDisableTiming));
+  }
+  MB_CUDA(ctx, cudaEventRecord(ctx->download_event, ctx->stream));
+  MB_CUDA(ctx, cudaStreamWaitEvent(ctx->download_stream, ctx->download_event, 0));
+  if (bytes != 0) MB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->download_stream));
+  if (done_event != nullptr) MB_CUDA(ctx, cudaEventRecord(static_cast<cudaEvent_t>(done_event), ctx->download_stream));
+  return MB_SUCCESS;
+}
+
+int mb_stream_wait_event(mb_context *ctx, void *event) {
+  if (ctx == nullptr || event == nullptr) return MB_INVALID_ARGS;
+  if (ctx->capturing) return mb_fail(ctx, MB_INVALID_ARGS, "mb_stream_wait_event: not inside a graph capture");
+  MB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, static_cast<cudaEvent_t>(event), 0));
   return MB_SUCCESS;
 }
 

@@ -24,11 +24,10 @@ struct mbh_engine {
   OperatorDef pending;
   bool building = false;
   std::string last_error;
-  // mbh_run_host_pipelined: two staging copies of the input, per slot an event "staging
-  // consumed" and an event "output in host memory"
-  void *staging[2] = {nullptr, nullptr};
-  size_t staging_bytes = 0;
-  void *consumed[2] = {nullptr, nullptr};
+  // mbh_run_host_pipelined: an event "the net has read its input" and, per slot, an event
+  // "output in host memory"
+  void *consumed = nullptr;
+  std::string watched_input;
   void *done[2] = {nullptr, nullptr};
   uint64_t pipelined_calls = 0;
 };
@@ -75,11 +74,10 @@ int mbh_engine_create(int device, mbh_engine **engine) {
 int mbh_engine_destroy(mbh_engine *engine) {
   if (engine == nullptr) return MaceStatus::MACE_INVALID_ARGS;
   mb_stream_sync(engine->runtime.ctx());
-  for (int i = 0; i < 2; ++i) {
-    if (engine->staging[i] != nullptr) mb_free(engine->runtime.ctx(), engine->staging[i]);
-    if (engine->consumed[i] != nullptr) mb_event_destroy(engine->runtime.ctx(), engine->consumed[i]);
+  if (engine->net != nullptr) engine->net->WatchInput("", nullptr);
+  if (engine->consumed != nullptr) mb_event_destroy(engine->runtime.ctx(), engine->consumed);
+  for (int i = 0; i < 2; ++i)
     if (engine->done[i] != nullptr) mb_event_destroy(engine->runtime.ctx(), engine->done[i]);
-  }
   delete engine;
   return MaceStatus::MACE_SUCCESS;
 }
@@ -253,8 +251,15 @@ int mbh_op_end(mbh_engine *e) {
   return MaceStatus::MACE_SUCCESS;
 }
 
+// A run that is not part of the pipelined sequence must not overwrite the output tensor while the
+// last pipelined call's copy to the host may still read it.
+static void WaitForLastDownload(mbh_engine *e) {
+  if (e->pipelined_calls >= 1) e->net->WaitBehindWatchPoint(e->done[(e->pipelined_calls - 1) & 1]);
+}
+
 int mbh_run(mbh_engine *e) {
   if (e == nullptr) return MaceStatus::MACE_INVALID_ARGS;
+  WaitForLastDownload(e);
   MBH_TRY(e, e->net->Run(nullptr));
   return MaceStatus::MACE_SUCCESS;
 }
@@ -305,6 +310,7 @@ int mbh_run_host(mbh_engine *e, const char *input_name, const void *host_in, siz
   if (input_bytes != static_cast<size_t>(in->raw_size()))
     return Fail(e, MaceStatus::MACE_INVALID_ARGS, "input size does not match the input tensor");
   MBH_TRY(e, e->runtime.Status(mb_memcpy_h2d(e->runtime.ctx(), in->mutable_memory<void>(), host_in, input_bytes)));
+  WaitForLastDownload(e);
   MBH_TRY(e, e->net->Run(nullptr));
   Tensor *out = FindTensor(e, output_name);
   if (out == nullptr) return MaceStatus::MACE_INVALID_ARGS;
@@ -326,28 +332,28 @@ int mbh_run_host_pipelined(mbh_engine *e, const char *input_name, const void *ho
   if (output_bytes != static_cast<size_t>(out->raw_size()))
     return Fail(e, MaceStatus::MACE_INVALID_ARGS, "output size does not match the output tensor (run the net once first)");
   mb_context *ctx = e->runtime.ctx();
-  if (e->staging_bytes < input_bytes) {
-    for (int i = 0; i < 2; ++i) {
-      if (e->staging[i] != nullptr) MBH_TRY(e, e->runtime.Status(mb_free(ctx, e->staging[i])));
-      MBH_TRY(e, e->runtime.Status(mb_malloc(ctx, input_bytes, &e->staging[i])));
-      if (e->consumed[i] == nullptr) MBH_TRY(e, e->runtime.Status(mb_event_create(ctx, &e->consumed[i])));
-      if (e->done[i] == nullptr) MBH_TRY(e, e->runtime.Status(mb_event_create(ctx, &e->done[i])));
-    }
-    e->staging_bytes = input_bytes;
+  for (int i = 0; i < 2; ++i)
+    if (e->done[i] == nullptr) MBH_TRY(e, e->runtime.Status(mb_event_create(ctx, &e->done[i])));
+  if (e->consumed == nullptr) MBH_TRY(e, e->runtime.Status(mb_event_create(ctx, &e->consumed)));
+  // The net records `consumed` behind the last operator that reads the input tensor (a captured
+  // net is two graphs with the event between them), so the upload of the NEXT call goes
+  // straight into the input tensor as soon as this call's first operators are through, while
+  // the rest of the net still runs: no staging copy inside device memory.
+  if (e->watched_input != input_name) {
+    MBH_TRY(e, e->net->WatchInput(input_name, e->consumed));
+    e->watched_input = input_name;
     e->pipelined_calls = 0;
   }
   const int slot = static_cast<int>(e->pipelined_calls & 1);
-  // upload stream: wait until the copy out of this staging buffer two calls ago has run, then
-  // fill it; compute stream: wait for the upload, move it into the input tensor (a copy inside
-  // device memory: microseconds), run the net, bring the output back
-  if (e->pipelined_calls >= 2) MBH_TRY(e, e->runtime.Status(mb_upload_wait_event(ctx, e->consumed[slot])));
-  MBH_TRY(e, e->runtime.Status(mb_upload_h2d(ctx, e->staging[slot], host_in, input_bytes)));
+  if (e->pipelined_calls >= 1) MBH_TRY(e, e->runtime.Status(mb_upload_wait_event(ctx, e->consumed)));
+  MBH_TRY(e, e->runtime.Status(mb_upload_h2d(ctx, in->mutable_memory<void>(), host_in, input_bytes)));
   MBH_TRY(e, e->runtime.Status(mb_upload_signal(ctx)));
-  MBH_TRY(e, e->runtime.Status(mb_memcpy_d2d(ctx, in->mutable_memory<void>(), e->staging[slot], input_bytes)));
-  MBH_TRY(e, e->runtime.Status(mb_event_record(ctx, e->consumed[slot])));
+  // The copy of the output to the host runs on its own stream, so the next call's first
+  // operators do not queue behind it; that call's net waits for it behind its watch point, before
+  // any later operator can overwrite the output tensor.
+  if (e->pipelined_calls >= 1) e->net->WaitBehindWatchPoint(e->done[slot ^ 1]);
   MBH_TRY(e, e->net->Run(nullptr));
-  MBH_TRY(e, e->runtime.Status(mb_memcpy_d2h(ctx, host_out, out->memory<void>(), output_bytes)));
-  MBH_TRY(e, e->runtime.Status(mb_event_record(ctx, e->done[slot])));
+  MBH_TRY(e, e->runtime.Status(mb_download_d2h(ctx, host_out, out->memory<void>(), output_bytes, e->done[slot])));
   e->pipelined_calls++;
   if (slot_out != nullptr) *slot_out = slot;
   return MaceStatus::MACE_SUCCESS;

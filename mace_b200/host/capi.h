@@ -80,10 +80,13 @@ int mbh_share_subsampled_inputs(mbh_engine *engine, int *groups);
 int mbh_plan_memory(mbh_engine *engine, size_t *separate_bytes, size_t *shared_bytes);
 
 /* The same as mbh_run_host without waiting: the upload of this call's input (from PINNED host
- * memory, through one of two staging buffers on the runtime's upload stream) overlaps the net's
- * run on the previous input.  *slot (0 or 1, may be NULL) names the call for mbh_wait_slot, which
- * blocks until that call's output is in host_out; host_in and host_out must stay untouched until
- * then, so rotate at least two host buffers of each.  Run the net once the ordinary way first. */
+ * memory, on the runtime's upload stream, straight into the input tensor) starts as soon as the
+ * previous call's net has passed the last operator that reads that tensor (the net records an
+ * event there; a captured net is replayed as two graphs around it) and overlaps the rest of the
+ * previous run.  *slot (0 or 1, may be NULL) names the call for mbh_wait_slot, which blocks until
+ * that call's output is in host_out; host_in and host_out must stay untouched until then, so
+ * rotate at least two host buffers of each.  Run the net once the ordinary way first.  Use one
+ * input name per engine between plain runs (a plain mbh_run_host in between is fine). */
 int mbh_run_host_pipelined(mbh_engine *engine, const char *input_name, const void *host_in, size_t input_bytes,
                            const char *output_name, void *host_out, size_t output_bytes, int *slot);
 int mbh_wait_slot(mbh_engine *engine, int slot);

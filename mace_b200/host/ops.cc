@@ -1240,18 +1240,48 @@ MaceStatus SerialNet::PlanMemory(size_t *separate_bytes, size_t *shared_bytes, c
 MaceStatus SerialNet::Capture() {
   DropCapture();
   OpContext context(runtime_);
-  MACE_RETURN_IF_ERROR(runtime_->Status(mb_graph_begin(runtime_->ctx())));
+  // one graph, or two when an input is watched: [0, watch_index_] and the rest
+  const size_t n = operators_.size();
+  const size_t cut = (watch_event_ != nullptr && watch_index_ >= 0 && static_cast<size_t>(watch_index_) + 1 < n)
+                         ? static_cast<size_t>(watch_index_) + 1
+                         : n;
+  void *graphs[2] = {nullptr, nullptr};
   MaceStatus st = MaceStatus::MACE_SUCCESS;
-  for (size_t i = 0; i < operators_.size() && st == MaceStatus::MACE_SUCCESS; ++i)
-    if (!skipped_[i]) st = operators_[i]->Run(&context);
-  void *graph = nullptr;
-  MaceStatus end = runtime_->Status(mb_graph_end(runtime_->ctx(), &graph));
+  for (int part = 0; part < 2 && st == MaceStatus::MACE_SUCCESS; ++part) {
+    const size_t begin = part == 0 ? 0 : cut, end_op = part == 0 ? cut : n;
+    if (begin >= end_op) continue;
+    st = runtime_->Status(mb_graph_begin(runtime_->ctx()));
+    if (st != MaceStatus::MACE_SUCCESS) break;
+    for (size_t i = begin; i < end_op && st == MaceStatus::MACE_SUCCESS; ++i)
+      if (!skipped_[i]) st = operators_[i]->Run(&context);
+    MaceStatus end = runtime_->Status(mb_graph_end(runtime_->ctx(), &graphs[part]));
+    if (st == MaceStatus::MACE_SUCCESS) st = end;
+  }
   if (st != MaceStatus::MACE_SUCCESS) {
-    if (graph != nullptr) mb_graph_destroy(runtime_->ctx(), graph);
+    for (void *g : graphs)
+      if (g != nullptr) mb_graph_destroy(runtime_->ctx(), g);
     return st;
   }
-  MACE_RETURN_IF_ERROR(end);
-  graph_ = graph;
+  graph_ = graphs[0];
+  graph_tail_ = graphs[1];
+  return MaceStatus::MACE_SUCCESS;
+}
+
+MaceStatus SerialNet::WatchInput(const std::string &input_name, void *event) {
+  int last = -1;
+  if (event != nullptr) {
+    for (size_t i = 0; i < defs_.size(); ++i) {
+      if (skipped_[i]) continue;
+      for (const std::string &in : defs_[i]->input)
+        if (in == input_name) last = static_cast<int>(i);
+    }
+    if (last < 0) return MaceStatus(MaceStatus::MACE_INVALID_ARGS, "no operator of the net reads " + input_name);
+  }
+  if (last == watch_index_ && event == watch_event_) return MaceStatus::MACE_SUCCESS;
+  const bool was_captured = captured();
+  watch_index_ = last;
+  watch_event_ = event;
+  if (was_captured) return Capture();  // the split point moved
   return MaceStatus::MACE_SUCCESS;
 }
 
@@ -1307,6 +1337,10 @@ void SerialNet::DropCapture() {
   if (graph_ != nullptr) {
     mb_graph_destroy(runtime_->ctx(), graph_);
     graph_ = nullptr;
+  }
+  if (graph_tail_ != nullptr) {
+    mb_graph_destroy(runtime_->ctx(), graph_tail_);
+    graph_tail_ = nullptr;
   }
 }
 
@@ -1383,8 +1417,19 @@ MaceStatus LogTensorRanges(CudaRuntime *runtime, Operation *op) {
 MaceStatus SerialNet::Run(RunMetadata *run_metadata) {
   const bool log_ranges = EnvConfEnabled("MACE_LOG_TENSOR_RANGE");
   MACE_LATENCY_LOGGER(1, "Running net");
-  if (graph_ != nullptr && run_metadata == nullptr && !log_ranges)
-    return runtime_->Status(mb_graph_launch(runtime_->ctx(), graph_));
+  void *wait_event = wait_event_;
+  wait_event_ = nullptr;
+  const bool watching = watch_event_ != nullptr && watch_index_ >= 0;
+  if (wait_event != nullptr && !watching)
+    MACE_RETURN_IF_ERROR(runtime_->Status(mb_stream_wait_event(runtime_->ctx(), wait_event)));
+  if (graph_ != nullptr && run_metadata == nullptr && !log_ranges) {
+    MACE_RETURN_IF_ERROR(runtime_->Status(mb_graph_launch(runtime_->ctx(), graph_)));
+    if (watch_event_ != nullptr) MACE_RETURN_IF_ERROR(runtime_->Status(mb_event_record(runtime_->ctx(), watch_event_)));
+    if (wait_event != nullptr && watching)
+      MACE_RETURN_IF_ERROR(runtime_->Status(mb_stream_wait_event(runtime_->ctx(), wait_event)));
+    if (graph_tail_ != nullptr) MACE_RETURN_IF_ERROR(runtime_->Status(mb_graph_launch(runtime_->ctx(), graph_tail_)));
+    return MaceStatus::MACE_SUCCESS;
+  }
   OpContext context(runtime_);
   std::vector<void *> events;
   if (run_metadata != nullptr) {
@@ -1405,6 +1450,11 @@ MaceStatus SerialNet::Run(RunMetadata *run_metadata) {
       }
       VLOG(3) << "Operator " << op->debug_def().name << " has shape: " << ShapeString(op->Output(0)->shape());
       if (log_ranges) st = LogTensorRanges(runtime_, op);
+    }
+    if (watch_event_ != nullptr && static_cast<int>(i) == watch_index_ && st == MaceStatus::MACE_SUCCESS) {
+      st = runtime_->Status(mb_event_record(runtime_->ctx(), watch_event_));
+      if (wait_event != nullptr && st == MaceStatus::MACE_SUCCESS)
+        st = runtime_->Status(mb_stream_wait_event(runtime_->ctx(), wait_event));
     }
     if (run_metadata != nullptr && st == MaceStatus::MACE_SUCCESS)
       st = runtime_->Status(mb_event_record(runtime_->ctx(), events[i + 1]));

@@ -237,6 +237,16 @@ class SerialNet {
   // outputs, which some operator may read as well) stay out of the plan.
   MaceStatus PlanMemory(size_t *separate_bytes, size_t *shared_bytes, const std::set<std::string> *keep = nullptr);
   bool captured() const { return graph_ != nullptr; }
+  // Records `event` on the runtime's stream right after the last operator that reads the tensor
+  // `input_name` (a net input), in every later Run(): the caller may refill that tensor for the
+  // next run as soon as the event has happened, while the rest of the net still runs.  A
+  // captured net is split into two graphs at that operator (the event is an ordinary stream
+  // event between two graph launches).  event == nullptr takes the watch away.
+  MaceStatus WatchInput(const std::string &input_name, void *event);
+  // The next Run() makes the stream wait for `event` right behind the watch point (or at its
+  // start when no input is watched): for a caller whose copy of the previous run's output must
+  // be over before this run's later operators overwrite that tensor.  One-shot; nullptr = none.
+  void WaitBehindWatchPoint(void *event) { wait_event_ = event; }
   ~SerialNet();
   size_t size() const { return operators_.size(); }
 
@@ -249,6 +259,10 @@ class SerialNet {
   std::vector<char> skipped_;  // operators merged into their producer
   std::vector<void *> shared_buffers_;  // activation memory handed out by PlanMemory
   void *graph_ = nullptr;
+  void *graph_tail_ = nullptr;   // the operators behind watch_index_ when an input is watched
+  int watch_index_ = -1;         // last operator that reads the watched input
+  void *watch_event_ = nullptr;
+  void *wait_event_ = nullptr;   // one-shot: see WaitBehindWatchPoint
 };
 
 }  // namespace mace

@@ -115,9 +115,65 @@ def test_mobilenet_batch64_logits_and_host_buffers(orc, layers):
         eng.close()
 
 
+@pytest.mark.parametrize("captured", [True, False])
+def test_mobilenet_pipelined_uploads_do_not_overtake_the_stem(orc, layers, captured):
+    """The pipelined entry point uploads call i + 1's images straight into the input tensor as soon
+    as call i's net has passed the operator that reads it.  Batch 32 from pinned buffers, twelve
+    calls back to back with alternating, very different inputs (all black / random): had an
+    upload started before the stem of the call in front had read its images, that call's logits
+    would be those of the wrong input.  Replayed from the (split) graph and operator by operator."""
+    import ctypes
+    import mace_b200
+    from mace_b200 import hostapi
+    batch = 32
+    xs = [mn.random_images(batch, seed=40), np.zeros_like(mn.random_images(batch, seed=40)),
+          mn.random_images(batch, seed=41)]
+    exps = [mn.oracle_forward(orc, layers, x) for x in xs]
+    assert not np.array_equal(exps[0], exps[1]) and not np.array_equal(exps[0], exps[2])
+    eng = mn.build_engine(hostapi, layers, batch)
+    try:
+        L = mace_b200.lib()
+        ctx = ctypes.c_void_p(eng.context)
+
+        def pinned(nbytes):
+            p = ctypes.c_void_p()
+            assert L.mb_host_alloc(ctx, int(nbytes), ctypes.byref(p)) == 0
+            return np.ctypeslib.as_array((ctypes.c_uint8 * int(nbytes)).from_address(p.value))
+
+        hin = [pinned(x.nbytes) for x in xs]
+        for h, x in zip(hin, xs):
+            h[:] = x.ravel()
+        houts = [pinned(batch * mn.NUM_CLASSES) for _ in range(2)]
+        eng.write("input", xs[0])
+        eng.run()
+        if captured:
+            eng.capture()
+        order = [0, 1, 2, 1, 0, 2, 1, 1, 0, 2, 0, 1]
+        prev = None
+        for i, k in enumerate(order):
+            slot = eng.run_host_pipelined("input", hin[k], "fc", houts[i & 1])
+            if prev is not None:
+                eng.wait_slot(prev[0])
+                assert np.array_equal(houts[prev[1]].reshape(batch, -1), exps[prev[2]]), "call %d" % (i - 1)
+            prev = (slot, i & 1, k)
+        eng.wait_slot(prev[0])
+        assert np.array_equal(houts[prev[1]].reshape(batch, -1), exps[prev[2]])
+        eng.sync()
+        # a plain run after the pipelined ones, then pipelined again
+        out = np.empty((batch, mn.NUM_CLASSES), np.uint8)
+        eng.run_host("input", xs[2], "fc", out)
+        assert np.array_equal(out, exps[2])
+        slot = eng.run_host_pipelined("input", hin[0], "fc", houts[0])
+        eng.wait_slot(slot)
+        assert np.array_equal(houts[0].reshape(batch, -1), exps[0])
+    finally:
+        eng.close()
+
+
 def test_mobilenet_pipelined_host_runs(orc, layers):
-    """mbh_run_host_pipelined: uploads overlap the previous call's chain through two staging
-    buffers; every call's logits, read after wait_slot, are those of ITS input."""
+    """mbh_run_host_pipelined: every call's logits, read after wait_slot, are those of ITS input
+    (pageable host arrays here; the upload goes straight into the input tensor once the previous
+    call's stem has read it)."""
     from mace_b200 import hostapi
     batch = 4
     xs = [mn.random_images(batch, seed=20 + i) for i in range(6)]
