@@ -74,7 +74,6 @@ int mbh_engine_create(int device, mbh_engine **engine) {
 int mbh_engine_destroy(mbh_engine *engine) {
   if (engine == nullptr) return MaceStatus::MACE_INVALID_ARGS;
   mb_stream_sync(engine->runtime.ctx());
-  if (engine->net != nullptr) engine->net->WatchInput("", nullptr);
   if (engine->consumed != nullptr) mb_event_destroy(engine->runtime.ctx(), engine->consumed);
   for (int i = 0; i < 2; ++i)
     if (engine->done[i] != nullptr) mb_event_destroy(engine->runtime.ctx(), engine->done[i]);
