@@ -148,7 +148,9 @@ struct TileCfg {
   static constexpr int NUM_ACC = 512 / BNX;
   static constexpr int TMEM_COLS = 512;
   static constexpr int BAR_BYTES = 512;
-  static constexpr int TERM_BYTES = NUM_ACC * (128 + BN) * 4;
+  // + for a row-major B: the preparation warps' partial column sums, [tile parity][k quarter][columns]
+  static constexpr int PART_INTS = B_MN ? 4 * ((BN + 127) / 128) * 128 : 0;
+  static constexpr int TERM_BYTES = NUM_ACC * (128 + BN) * 4 + 2 * PART_INTS * 4;
   static constexpr int SMEM_BYTES =
       STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + BAR_BYTES + TERM_BYTES;
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -333,13 +335,15 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tfull_bar = empty_bar + 8 * STAGES;         // [NUM_ACC] accumulator complete
   const uint32_t tempty_bar = tfull_bar + 8 * NUM_ACC;       // [NUM_ACC] accumulator drained
   const uint32_t terms_bar = tempty_bar + 8 * NUM_ACC;       // [NUM_ACC] epilogue terms ready
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 3 * NUM_ACC);
+  const uint32_t part_bar = terms_bar + 8 * NUM_ACC;          // the four quarters of a tile's column sums are written
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 3 * NUM_ACC + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   // per accumulator buffer: row terms [128] and column terms [BN]
   int32_t *row_term_sm =
       reinterpret_cast<int32_t *>(smem_aligned + STAGES * Cfg::STAGE_BYTES + Cfg::STAGING_BYTES +
                                   Cfg::BAR_BYTES);
   int32_t *col_term_sm = row_term_sm + NUM_ACC * 128;
+  uint32_t *part_sm = reinterpret_cast<uint32_t *>(col_term_sm + NUM_ACC * BN);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -354,6 +358,7 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, prep_reads_tiles ? 1 + PREP_WARPS : 1);
     }
+    mbar_init(part_bar, PREP_WARPS);
     for (int b = 0; b < NUM_ACC; ++b) {
       mbar_init(tfull_bar + 8 * b, 1);
       // (pairs: the even CTA's barrier also counts the odd CTA's epilogue warps)
@@ -550,8 +555,12 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (TileIter it(p, PAIR); ok && it.valid(p); it.next(p), ++local) {
       const int b = it.b, tm = it.tm, tn = it.tn;
       uint32_t sa_sum = 0, sb_sum[(BN + 127) / 128];
+      uint32_t cs[(BN + 127) / 128][4];  // row-major B: four columns of each panel over this warp's k rows
 #pragma unroll
-      for (int j = 0; j < (BN + 127) / 128; ++j) sb_sum[j] = 0;
+      for (int j = 0; j < (BN + 127) / 128; ++j) {
+        sb_sum[j] = 0;
+        cs[j][0] = cs[j][1] = cs[j][2] = cs[j][3] = 0;
+      }
       // global inputs of the terms, requested before the main loop is followed
       const int64_t m = static_cast<int64_t>(tm) * TILE_M + rank * BM + r;
       int32_t row_bias = 0, col_bias[(BN + 127) / 128];
@@ -590,18 +599,26 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int j = 0; j < (BN + 127) / 128; ++j) {
             const int row = j * 128 + r;
             if (B_MN) {
-              // the tile is [128-column panel][KB depth rows][128 bytes], the 16-byte chunks of
-              // a row permuted by the row's low three bits: this thread adds up column r of
-              // panel j (the lanes of a warp read 32 adjacent bytes of a row: no conflicts)
-              if (want_b && row < ((BN + 127) / 128) * 128) {
-                const uint8_t *col = tb + j * 128 * KB + (r & 15);
-                uint32_t s0 = 0, s1 = 0;
+              // The tile is [128-column panel][KB depth rows][128 bytes], the 16-byte chunks of a
+              // row permuted by the row's low three bits.  Warp q takes depth rows 32 q .. 32 q + 31,
+              // lane w the 32-bit word w of every such row (columns 4 w .. 4 w + 3 of the panel:
+              // a warp reads a whole row per load, no conflicts), and adds the four bytes as two
+              // pairs of 16-bit counts (32 rows x 255 fit); the four warps' counts meet below.
+              if (want_b) {
+                const uint8_t *pan = tb + j * 128 * KB + (lane & 3) * 4;
+                const int c = lane >> 2, q = warp - 2;
+                uint32_t ev = 0, od = 0;
 #pragma unroll 8
-                for (int k = 0; k < KB; k += 2) {
-                  s0 += col[k * 128 + (((r >> 4) ^ (k & 7)) << 4)];
-                  s1 += col[(k + 1) * 128 + (((r >> 4) ^ ((k + 1) & 7)) << 4)];
+                for (int kk = 0; kk < 32; ++kk) {
+                  const int k = q * 32 + kk;
+                  const uint32_t wd = *reinterpret_cast<const uint32_t *>(pan + k * 128 + ((c ^ (k & 7)) << 4));
+                  ev += wd & 0x00ff00ffu;
+                  od += (wd >> 8) & 0x00ff00ffu;
                 }
-                sb_sum[j] += s0 + s1;
+                cs[j][0] += ev & 0xffffu;
+                cs[j][1] += od & 0xffffu;
+                cs[j][2] += ev >> 16;
+                cs[j][3] += od >> 16;
               }
             } else if (want_b && row < BN) {
 #pragma unroll
@@ -618,6 +635,26 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         if (!ok) break;
+        if (B_MN && want_b) {
+          // the four k quarters of every column: through shared memory (two buffers, by tile parity)
+          constexpr int COLS = ((BN + 127) / 128) * 128;
+          uint32_t *part = part_sm + (local & 1) * Cfg::PART_INTS;
+#pragma unroll
+          for (int j = 0; j < (BN + 127) / 128; ++j)
+            *reinterpret_cast<uint4 *>(part + (warp - 2) * COLS + j * 128 + 4 * lane) =
+                make_uint4(cs[j][0], cs[j][1], cs[j][2], cs[j][3]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(part_bar);
+          if (!mbar_wait_warp(part_bar, static_cast<uint32_t>(local & 1), abort_flag, WAIT_BUDGET)) {
+            *abort_flag = 1;
+            atomicCAS(p.status, 0, MB_DEV_TIMEOUT_EPILOGUE);
+            break;
+          }
+#pragma unroll
+          for (int j = 0; j < (BN + 127) / 128; ++j)
+            sb_sum[j] = part[j * 128 + r] + part[COLS + j * 128 + r] + part[2 * COLS + j * 128 + r] +
+                        part[3 * COLS + j * 128 + r];
+        }
       }
       // terms of this tile (operand sums are zero where no correction is needed)
       const int32_t row_term = row_bias - p.zp_b * static_cast<int32_t>(sa_sum);
