@@ -116,9 +116,11 @@ int mb_operand_sums_slices(const mb_context *ctx, bool mn, int64_t nb, int64_t K
   if (!mn) return 1;
   const int64_t col_blocks = ceil_div64(cols, 512);
   // enough blocks that the loads in flight (8 x 16 bytes per thread) cover the memory latency of
-  // the whole GPU: measured on a 4096 x 4096 operand, 512 blocks of 256 threads read it in 8 us,
-  // 256 blocks of 128 threads in 12 us
-  int64_t slices = ceil_div64(4ll * ctx->num_sms, col_blocks * nb);
+  // the whole GPU (measured on a 4096 x 4096 operand: 512 blocks of 256 threads read it in 8 us,
+  // 256 blocks of 128 threads in 12 us), but, together with the row-sum blocks of the other
+  // operand (two per SM), no more than the five blocks per SM that are resident at once: a
+  // second, partial round of blocks cost the 4096^3 GEMM about a microsecond
+  int64_t slices = ceil_div64(3ll * ctx->num_sms, col_blocks * nb);
   slices = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(slices, 64), ceil_div64(K, 32)));
   const int64_t rps = ceil_div64(K, slices);
   return static_cast<int>(ceil_div64(K, rps));
@@ -146,7 +148,7 @@ int mb_operand_sums_launch(mb_context *ctx, const uint8_t *A, bool a_mn, int64_t
       j.pitch = k_full;
       j.mat_stride = k_split > 1 ? K : extent * K;
       j.num_blocks = static_cast<int>(std::min<int64_t>(ceil_div64(nb * extent, SUM_WARPS),
-                                                        static_cast<int64_t>(ctx->num_sms) * 8));
+                                                        static_cast<int64_t>(ctx->num_sms) * 2));
     } else {    // [K x extent] -> [slices][extent] partial rows
       j.kind = 2;
       j.rows = K; j.cols = extent;
