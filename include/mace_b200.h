@@ -154,7 +154,9 @@ int mb_pair_clusters(const mb_context *ctx);
  * "gemv_lhs_const" (0 default; 1 promises that the matrix of the following
  * mb_gemv_u8 calls is not written by work enqueued ahead of them -- a weight,
  * the reference's Tensor::is_weight(), mace/core/tensor.h -- so its first
- * bytes may be fetched while the previous kernel still runs). */
+ * bytes may be fetched while the previous kernel still runs; such launches use
+ * 2 KB chunks so that a launch and its successor share the SMs,
+ * "gemv_chain_chunks" = 0 keeps 4 KB chunks). */
 int mb_set_option(mb_context *ctx, const char *name, int value);
 
 /* ---- uint8 GEMM: replaces the gemmlowp calls of MatMulOp<RT_CPU,uint8_t>

@@ -68,6 +68,7 @@ struct mb_context {
   int split_k = 1;               // few-tile, long-depth GEMMs: cut the depth into runs over more SMs
   int gemv_stream = 1;           // one-vector GEMV through the bulk-copy streaming kernel
   int gemv_lhs_const = 0;        // the GEMV matrix is a weight: it may be fetched ahead of the dependency wait
+  int gemv_chain_chunks = 1;     // constant matrix: 2 KB chunks so that a launch and its successor share the SMs
   int gemv_const_one_per_sm = 0; // with a constant matrix, leave half of each SM to the next kernel (measured slower: 6.1 vs 5.75 us per 4096 x 4096 product in a chain)
   int force_bn = 0;              // tensor-core GEMM: 64 / 128 / 256 overrides the tile-width choice
   int host_alloc_wc = 0;         // mb_host_alloc returns write-combined pinned memory

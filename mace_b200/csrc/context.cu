@@ -443,6 +443,8 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
     ctx->gemv_stream = value;
   } else if (strcmp(name, "gemv_lhs_const") == 0) {
     ctx->gemv_lhs_const = value;
+  } else if (strcmp(name, "gemv_chain_chunks") == 0) {
+    ctx->gemv_chain_chunks = value;
   } else if (strcmp(name, "gemv_const_one_per_sm") == 0) {
     ctx->gemv_const_one_per_sm = value;
   } else if (strcmp(name, "force_bn") == 0) {

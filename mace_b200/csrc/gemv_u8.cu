@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(256) gemv_u8_kernel(const GemvParams p) {
 // memory once per CTA) and lane 0 refills the slot: up to 8 x ST_DEPTH x 4 KB are in flight per
 // CTA with no thread holding registers for them, and no warp waits for another.
 // Bounded waits: a wait that runs out sets the context's status word and the warp stops.
-constexpr int ST_CHUNK = 4096;   // bytes of a matrix row per bulk copy
+constexpr int ST_CHUNK_MAX = 4096;   // bytes of a matrix row per bulk copy (template CHUNK: 4096, or 2048 for chains)
 constexpr int ST_DEPTH = 3;      // slots per warp
 constexpr int ST_WARPS = 8;
 constexpr long long ST_WAIT_BUDGET = 1ll << 31;
@@ -158,6 +158,7 @@ struct GemvStreamParams {
   int *status;
 };
 
+template <int ST_CHUNK>
 __global__ void __launch_bounds__(ST_WARPS * 32) gemv_u8_stream_kernel(const GemvStreamParams p) {
   extern __shared__ __align__(128) uint8_t st_smem[];
   // [ST_WARPS][ST_DEPTH][ST_CHUNK] ring, then the vector (K bytes), then the barriers
@@ -320,19 +321,30 @@ extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rh
     sp.zp_lhs = zp_lhs; sp.zp_rhs = zp_rhs; sp.zp_out = zp_out; sp.multiplier = multiplier;
     sp.status = ctx->dev_status;
     sp.lhs_const = ctx->gemv_lhs_const;
-    const size_t smem = static_cast<size_t>(ST_WARPS) * ST_DEPTH * ST_CHUNK + static_cast<size_t>(K) +
+    // A constant matrix in a chain of such products: half-size chunks, so that FOUR CTAs fit an
+    // SM -- two of this launch and two of the next one, whose first ring fill (issued ahead of
+    // its dependency wait) is then under way while this launch still streams.  (option
+    // gemv_const_one_per_sm = 1 instead leaves one of two full-size places to the successor.)
+    const bool small_chunks = sp.lhs_const && ctx->gemv_chain_chunks && !ctx->gemv_const_one_per_sm;
+    const int chunk = small_chunks ? 2048 : ST_CHUNK_MAX;
+    const size_t smem = static_cast<size_t>(ST_WARPS) * ST_DEPTH * chunk + static_cast<size_t>(K) +
                         sizeof(uint64_t) * ST_WARPS * ST_DEPTH;
-    constexpr uint64_t attr_bit = 1ull << 62;
+    const uint64_t attr_bit = small_chunks ? (1ull << 61) : (1ull << 62);
     if (!(ctx->func_attr_mask & attr_bit)) {
-      MB_CUDA(ctx, cudaFuncSetAttribute(gemv_u8_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        ST_WARPS * ST_DEPTH * ST_CHUNK + 65536 + 8 * ST_WARPS * ST_DEPTH));
+      if (small_chunks)
+        MB_CUDA(ctx, cudaFuncSetAttribute(gemv_u8_stream_kernel<2048>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          ST_WARPS * ST_DEPTH * 2048 + 65536 + 8 * ST_WARPS * ST_DEPTH));
+      else
+        MB_CUDA(ctx, cudaFuncSetAttribute(gemv_u8_stream_kernel<ST_CHUNK_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          ST_WARPS * ST_DEPTH * ST_CHUNK_MAX + 65536 + 8 * ST_WARPS * ST_DEPTH));
       ctx->func_attr_mask |= attr_bit;
     }
-    // two CTAs fit an SM; with a constant matrix one of the two places is left to the next
-    // kernel of the chain, whose first fill is then under way while this one streams
     const int per_sm = (smem <= 110 * 1024 && !(sp.lhs_const && ctx->gemv_const_one_per_sm)) ? 2 : 1;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(rows, static_cast<int64_t>(ctx->num_sms) * per_sm));
-    MB_CUDA(ctx, mb_launch_chained(ctx, gemv_u8_stream_kernel, dim3(grid), dim3(ST_WARPS * 32), smem, sp));
+    if (small_chunks)
+      MB_CUDA(ctx, mb_launch_chained(ctx, gemv_u8_stream_kernel<2048>, dim3(grid), dim3(ST_WARPS * 32), smem, sp));
+    else
+      MB_CUDA(ctx, mb_launch_chained(ctx, gemv_u8_stream_kernel<ST_CHUNK_MAX>, dim3(grid), dim3(ST_WARPS * 32), smem, sp));
     MB_CUDA(ctx, cudaGetLastError());
     ctx->launches++;
     return MB_SUCCESS;
