@@ -329,9 +329,10 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
     ctx->launches++;
     return MB_SUCCESS;
   }
-  // K-major operands with K <= 1024: the tensor-core kernel sums the operand
+  // A K-major A with K <= 1024 (B in either order): the tensor-core kernel sums the operand
   // bytes itself from the tiles it has in shared memory.
-  const bool fused_sums = !(a_mn && !a_copy) && !(b_mn && !b_copy) && K <= 1024;
+  // (option pair = 2, the CTA-pair kernel wherever it can run, takes its sums from the sums kernel)
+  const bool fused_sums = !(a_mn && !a_copy) && K <= 1024 && ctx->pair_gemm != 2;
   const bool need_sum_a = zp_b != 0 && !fused_sums, need_sum_b = zp_a != 0 && !fused_sums;
   size_t off = 0;
   // (an operand that reaches the tensor core MN-major gets its column sums as a few partial rows)

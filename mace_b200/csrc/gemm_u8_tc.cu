@@ -998,10 +998,11 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   const bool kmajor_free = !a_mn && !b_mn && sum_a == nullptr && sum_b == nullptr;
   const int KBsel = (kmajor_free && K <= 32) ? 32 : (kmajor_free && K <= 64) ? 64 : BK;
   const bool fuse = kmajor_free && K <= 8 * BK && (zp_a != 0 || zp_b != 0 || KBsel != BK);
-  // depth runs of a K-major A against a row-major B: B's column sums are taken from the tiles
-  // too (these launches are bound by the bytes each SM can pull, the tile readers are idle)
-  const bool fuse_bmn = k_split > 1 && !a_mn && b_mn && sum_a == nullptr && sum_b == nullptr && K <= 8 * BK &&
-                        (zp_a != 0 || zp_b != 0) && (bn_forced == 64 || bn_forced == 128);
+  // a K-major A against a row-major B with a depth (or depth run) of at most 1024: B's column
+  // sums are taken from the tiles too, word by word (depth runs are bound by the bytes each SM
+  // can pull and short-depth products by their epilogue: the tile readers have the time)
+  const bool fuse_bmn = !a_mn && b_mn && sum_a == nullptr && sum_b == nullptr && K <= 8 * BK &&
+                        (zp_a != 0 || zp_b != 0);
   // Tile width.  Long main loops (K > 1024) want the widest tile for operand
   // reuse -- unless that leaves most SMs without a tile (a few rows against a
   // large B): then the width with the fewest columns per SM wins, wider on a
@@ -1125,6 +1126,7 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
     return launch_cfg<BN_, false, false>(ctx, ta, tb, tc, p);                           \
   }
   if (fuse_bmn) {
+    if (BN == 256) return launch_cfg<256, false, true, true>(ctx, ta, tb, tc, p);
     if (BN == 128) return launch_cfg<128, false, true, true>(ctx, ta, tb, tc, p);
     return launch_cfg<64, false, true, true>(ctx, ta, tb, tc, p);
   }
