@@ -605,15 +605,18 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               // a warp reads a whole row per load, no conflicts), and adds the four bytes as two
               // pairs of 16-bit counts (32 rows x 255 fit); the four warps' counts meet below.
               if (want_b) {
-                const uint8_t *pan = tb + j * 128 * KB + (lane & 3) * 4;
                 const int c = lane >> 2, q = warp - 2;
+                const uint8_t *pan = tb + j * 128 * KB + q * 32 * 128 + (lane & 3) * 4;
                 uint32_t ev = 0, od = 0;
-#pragma unroll 8
-                for (int kk = 0; kk < 32; ++kk) {
-                  const int k = q * 32 + kk;
-                  const uint32_t wd = *reinterpret_cast<const uint32_t *>(pan + k * 128 + ((c ^ (k & 7)) << 4));
-                  ev += wd & 0x00ff00ffu;
-                  od += (wd >> 8) & 0x00ff00ffu;
+                // (fully unrolled: the eight chunk offsets (c ^ 0..7) << 4 are computed once, every
+                // load is register + immediate, two rows share one three-input add per count pair)
+#pragma unroll
+                for (int kk = 0; kk < 32; kk += 2) {
+                  const uint32_t w0 = *reinterpret_cast<const uint32_t *>(pan + kk * 128 + ((c ^ (kk & 7)) << 4));
+                  const uint32_t w1 =
+                      *reinterpret_cast<const uint32_t *>(pan + (kk + 1) * 128 + ((c ^ ((kk + 1) & 7)) << 4));
+                  ev += (w0 & 0x00ff00ffu) + (w1 & 0x00ff00ffu);
+                  od += __byte_perm(w0, 0, 0x4341) + __byte_perm(w1, 0, 0x4341);
                 }
                 cs[j][0] += ev & 0xffffu;
                 cs[j][1] += od & 0xffffu;
