@@ -65,6 +65,7 @@ struct mb_context {
                                  // it applies, 2 wherever it can run.  Off by default: measured equal at 8192^3
                                  // (409 vs 410 us) and slower at 4096^3 (54.7 vs 51.6 us): the main loop is paced
                                  // by the tensor pipe at the clocks the power cap leaves, not by operand traffic
+  int runs_min_m = 2;             // from this many rows on, depth runs on the tensor core replace the few-row kernel
   int split_k = 1;               // few-tile, long-depth GEMMs: cut the depth into runs over more SMs
   int gemv_stream = 1;           // one-vector GEMV through the bulk-copy streaming kernel
   int gemv_lhs_const = 0;        // the GEMV matrix is a weight: it may be fetched ahead of the dependency wait

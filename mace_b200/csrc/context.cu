@@ -437,6 +437,8 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
     ctx->skinny_max_m = value;
   } else if (strcmp(name, "pair") == 0) {
     ctx->pair_gemm = value;
+  } else if (strcmp(name, "runs_min_m") == 0) {
+    ctx->runs_min_m = value;
   } else if (strcmp(name, "split_k") == 0) {
     ctx->split_k = value;
   } else if (strcmp(name, "gemv_stream") == 0) {

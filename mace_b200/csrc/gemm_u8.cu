@@ -266,12 +266,12 @@ int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, con
   bool use_tc = ctx->use_tensor_cores && ctx->encode_tiled != nullptr && aligned16 &&
                 K % 16 == 0 && K <= 33000 && M >= 1 && N >= 1;
   // A few rows against a large row-major B: stream B once over all SMs with CUDA cores.  From
-  // four rows on the tensor-core kernel over depth runs is faster where it applies (measured at
-  // K = N = 4096: 13.7 us against 14.0 at M = 4, 14.4 against 28.8 at M = 16; 13.8 against 11.1
-  // at M = 1).
+  // two rows on the tensor-core kernel over depth runs is faster where it applies (measured at
+  // K = N = 4096: 11.4 us against 12.4 at M = 2, 11.4 against 14.0 at M = 4, 11.7 against 28.8 at
+  // M = 16; a tie, 11.4 / 11.2, at M = 1).
   if (ctx->use_tensor_cores && M <= ctx->skinny_max_m && mb_gemm_u8_skinny_supported(batch, M, N, K, a_mn, b_mn, A, B)) {
     int bn_unused = 0;
-    const bool runs_apply = M >= 4 && use_tc && !(a_mn && !(ctx->use_mn_major && M % 16 == 0)) &&
+    const bool runs_apply = M >= ctx->runs_min_m && use_tc && !(a_mn && !(ctx->use_mn_major && M % 16 == 0)) &&
                             !(b_mn && !(ctx->use_mn_major && N % 16 == 0)) &&
                             split_k_choice(ctx, batch, M, N, K, &bn_unused) > 1;
     if (!runs_apply)

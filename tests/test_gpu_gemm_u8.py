@@ -241,7 +241,7 @@ def test_few_rows_against_row_major_b(ctx, orc, shape, out_int32):
     test_depth_cut_into_runs covers; here that route is switched off.)"""
     M, N, K = shape
     case = gemm_case(orc, M + N, 1, M, N, K, bias_len=N)
-    if M >= 4 and K >= 2048:
+    if M >= 2 and K >= 2048:
         before = ctx.launches_tensor_core
         got, exp = run_gemm(ctx, orc, case, 1, M, N, K, out_int32=out_int32)
         assert np.array_equal(got, exp)
