@@ -290,6 +290,38 @@ def test_cta_pair_kernel(ctx, orc, shape):
     assert len(np.unique(got[2])) > 50
 
 
+@pytest.mark.parametrize("force_bn", [0, 64, 128, 256])
+@pytest.mark.parametrize("shape", [(200, 272, 1000), (128, 256, 1024), (77, 112, 48), (300, 528, 144)])
+def test_column_sums_from_row_major_b_tiles(ctx, orc, shape, force_bn):
+    """K-major A against a row-major B with a depth of at most 1024: no sums kernel runs, the
+    preparation warps add B's columns from the swizzled tiles (16-bit count pairs per 32 depth
+    rows, the four warps' quarters joined in shared memory).  Ragged M, N and K (a last K block
+    that TMA fills with zeros), every tile width, all-255 operands (no count may wrap), either
+    zero point alone; every byte against the oracle."""
+    M, N, K = shape
+    rng = np.random.Generator(np.random.PCG64(M + N + K))
+    if force_bn:
+        ctx.set_option("force_bn", force_bn)
+    try:
+        for zp_a, zp_b, fill in ((128, 120, None), (255, 0, None), (0, 255, None), (128, 120, 255)):
+            A = rng.integers(0, 256, size=(1, M, K), dtype=np.uint8)
+            B = rng.integers(0, 256, size=(1, K, N), dtype=np.uint8)
+            if fill is not None:
+                A[:] = fill
+                B[:] = fill
+            bias = np.rint(rng.normal(0, 1000, size=N)).astype(np.int32)
+            acc = orc.gemm_u8(A, B, None, 1, M, N, K, zp_a, zp_b, out_int32=True).astype(np.float64)
+            s_c = max(float(np.abs(acc).max()), 1.0) * 1e-4 / 127.0
+            mult, shift = orc.output_multiplier_and_shift(np.float32(0.01), np.float32(0.01), np.float32(s_c))
+            case = dict(A=A, B=B, bias=bias, zp_a=zp_a, zp_b=zp_b, mult=mult, shift=shift, zp_c=128)
+            before = ctx.launches
+            got, exp = run_gemm(ctx, orc, case, 1, M, N, K)
+            assert ctx.launches - before == 1, "expected the GEMM alone (sums from its tiles)"
+            assert np.array_equal(got, exp), (zp_a, zp_b, fill)
+    finally:
+        ctx.set_option("force_bn", 0)
+
+
 def test_empty_and_bad_arguments(ctx):
     import mace_b200
     buf = ctx.alloc(64)
