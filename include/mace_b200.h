@@ -156,7 +156,10 @@ int mb_pair_clusters(const mb_context *ctx);
  * the reference's Tensor::is_weight(), mace/core/tensor.h -- so its first
  * bytes may be fetched while the previous kernel still runs; such launches use
  * 2 KB chunks so that a launch and its successor share the SMs,
- * "gemv_chain_chunks" = 0 keeps 4 KB chunks). */
+ * "gemv_chain_chunks" = 0 keeps 4 KB chunks),
+ * "stem_tc" (1 default: a 3x3 convolution over 3 channels whose output
+ * channel count is a multiple of 16 takes one tensor-core product per 128
+ * pixels; 0 keeps the dp4a kernel that serves the other channel counts). */
 int mb_set_option(mb_context *ctx, const char *name, int value);
 
 /* ---- uint8 GEMM: replaces the gemmlowp calls of MatMulOp<RT_CPU,uint8_t>

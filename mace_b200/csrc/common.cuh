@@ -61,6 +61,7 @@ struct mb_context {
                                  // before it has waited for its predecessor
   int skinny_max_m = 16;         // row counts up to this take the streaming few-row GEMM
   int max_pair_clusters = 0;     // co-resident clusters of the pair GEMM (0: not asked yet)
+  int stem_tc = 1;               // 3x3x3 first-layer convolution: the products on the tensor core
   int pair_gemm = 0;             // large GEMMs on CTA pairs (clusters of two sharing each tile's B): 1 where
                                  // it applies, 2 wherever it can run.  Off by default: measured equal at 8192^3
                                  // (409 vs 410 us) and slower at 4096^3 (54.7 vs 51.6 us): the main loop is paced

@@ -435,6 +435,8 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
   } else if (strcmp(name, "skinny_max_m") == 0) {
     if (value < 0 || value > 16) return mb_fail(ctx, MB_INVALID_ARGS, "skinny_max_m must be 0 .. 16");
     ctx->skinny_max_m = value;
+  } else if (strcmp(name, "stem_tc") == 0) {
+    ctx->stem_tc = value;
   } else if (strcmp(name, "pair") == 0) {
     ctx->pair_gemm = value;
   } else if (strcmp(name, "runs_min_m") == 0) {

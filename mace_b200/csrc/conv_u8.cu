@@ -15,6 +15,7 @@
 //   everything else   -> patch gather into scratch (rows padded to 16 bytes)
 //                        + tensor-core GEMM
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 int mb_gemm_u8_rowmajor(mb_context *ctx, const uint8_t *A, const uint8_t *B, const int32_t *bias,
                         void *C, int out_is_int32, int64_t batch, int64_t M, int64_t N,
@@ -142,42 +143,21 @@ __device__ __forceinline__ void patch_outputs(const uint32_t (&patch)[DW], const
     *reinterpret_cast<uint32_t *>(outp + o0) = patch_outputs4<DW, DWP, VAR>(patch, smem_w, cterm, in_term, p, o0);
 }
 
+// The KH*KW*C bytes under the filter window of output pixel `pix`, packed into 32-bit words
+// (byte d of the patch = tap (d / C) channel d % C; out-of-image taps hold the input zero point,
+// the bytes past the patch are zero).
 template <int KH, int KW, int C>
-__global__ void __launch_bounds__(128) conv_u8_patch_dp4a_kernel(const ConvParams p) {
+__device__ __forceinline__ void gather_patch(const ConvParams &p, int64_t pix, uint32_t (&patch)[(KH * KW * C + 3) / 4]) {
   constexpr int DEPTH = KH * KW * C;
   constexpr int DW = (DEPTH + 3) / 4;
-  constexpr int DWP = (DW + 3) / 4 * 4;  // words per filter row in shared memory
-  extern __shared__ uint32_t smem_w[];   // [O][DWP] filter words, then [O] constants
-  int32_t *cterm = reinterpret_cast<int32_t *>(smem_w + p.O * DWP);
-  mb_grid_dep_launch();
-  mb_grid_dep_wait();
-  for (int i = threadIdx.x; i < p.O * DWP; i += blockDim.x) {
-    const int o = i / DWP, w = i % DWP;
-    uint32_t v = 0;
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      const int d = w * 4 + b;
-      if (d < DEPTH) v |= static_cast<uint32_t>(p.filter[o * DEPTH + d]) << (8 * b);
-    }
-    smem_w[i] = v;
-  }
-  for (int o = threadIdx.x; o < p.O; o += blockDim.x) {
-    int32_t fs = 0;
-    for (int d = 0; d < DEPTH; ++d) fs += p.filter[o * DEPTH + d];
-    cterm[o] = (p.bias != nullptr ? p.bias[o] : 0) - p.zp_in * fs + DEPTH * p.zp_in * p.zp_f;
-  }
-  __syncthreads();
-  // a block walks over several 128-pixel groups, so that packing the filter above is paid
-  // once per block and not once per 128 pixels
-  const int64_t npix = static_cast<int64_t>(p.N) * p.Ho * p.Wo;
-  for (int64_t pix = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; pix < npix;
-       pix += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-  const int wo = static_cast<int>(pix % p.Wo);
-  const int ho = static_cast<int>((pix / p.Wo) % p.Ho);
-  const int n = static_cast<int>(pix / (static_cast<int64_t>(p.Wo) * p.Ho));
+  // (the pixel count is below 2^31: 32-bit divisions)
+  const uint32_t pix32 = static_cast<uint32_t>(pix);
+  const int wo = static_cast<int>(pix32 % static_cast<uint32_t>(p.Wo));
+  const uint32_t row32 = pix32 / static_cast<uint32_t>(p.Wo);
+  const int ho = static_cast<int>(row32 % static_cast<uint32_t>(p.Ho));
+  const int n = static_cast<int>(row32 / static_cast<uint32_t>(p.Ho));
   const int hi0 = ho * p.stride_h - p.pad_top, wi0 = wo * p.stride_w - p.pad_left;
   const uint8_t *in_n = p.in + static_cast<int64_t>(n) * p.H * p.W * C;
-  uint32_t patch[DW];
 #pragma unroll
   for (int i = 0; i < DW; ++i) patch[i] = 0;
   const uint32_t zi = static_cast<uint32_t>(p.zp_in);
@@ -226,6 +206,40 @@ __global__ void __launch_bounds__(128) conv_u8_patch_dp4a_kernel(const ConvParam
     }
   }
   }
+}
+
+template <int KH, int KW, int C>
+__global__ void __launch_bounds__(128) conv_u8_patch_dp4a_kernel(const ConvParams p) {
+  constexpr int DEPTH = KH * KW * C;
+  constexpr int DW = (DEPTH + 3) / 4;
+  constexpr int DWP = (DW + 3) / 4 * 4;  // words per filter row in shared memory
+  extern __shared__ uint32_t smem_w[];   // [O][DWP] filter words, then [O] constants
+  int32_t *cterm = reinterpret_cast<int32_t *>(smem_w + p.O * DWP);
+  mb_grid_dep_launch();
+  mb_grid_dep_wait();
+  for (int i = threadIdx.x; i < p.O * DWP; i += blockDim.x) {
+    const int o = i / DWP, w = i % DWP;
+    uint32_t v = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int d = w * 4 + b;
+      if (d < DEPTH) v |= static_cast<uint32_t>(p.filter[o * DEPTH + d]) << (8 * b);
+    }
+    smem_w[i] = v;
+  }
+  for (int o = threadIdx.x; o < p.O; o += blockDim.x) {
+    int32_t fs = 0;
+    for (int d = 0; d < DEPTH; ++d) fs += p.filter[o * DEPTH + d];
+    cterm[o] = (p.bias != nullptr ? p.bias[o] : 0) - p.zp_in * fs + DEPTH * p.zp_in * p.zp_f;
+  }
+  __syncthreads();
+  // a block walks over several 128-pixel groups, so that packing the filter above is paid
+  // once per block and not once per 128 pixels
+  const int64_t npix = static_cast<int64_t>(p.N) * p.Ho * p.Wo;
+  for (int64_t pix = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; pix < npix;
+       pix += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+  uint32_t patch[DW];
+  gather_patch<KH, KW, C>(p, pix, patch);
   uint32_t sum_in = 0;
 #pragma unroll
   for (int i = 0; i < DW; ++i) sum_in = __dp4a(patch[i], 0x01010101u, sum_in);
@@ -254,6 +268,161 @@ __global__ void __launch_bounds__(128) conv_u8_patch_dp4a_kernel(const ConvParam
   }
   }
 }
+
+// ---- the same first-layer convolution with the products on the tensor core -----------------
+// out[pixel][o] = sum_d patch[pixel][d] * filter[o][d] is a GEMM with K = 27: one tcgen05.mma
+// (kind::i8, K = 32) per 128 pixels does what 7 dp4a per output value do above.  The block keeps
+// the shape of the dp4a kernel -- 128 threads, a thread per pixel, several blocks per SM, whose
+// latencies hide one another -- and per group of 128 pixels: every thread gathers its 27-byte
+// patch (gather_patch) and stores it as a row of the MMA's A operand (K-major without swizzle:
+// two planes of 16-byte pieces, [half of K][pixel][16 bytes]); one thread issues the MMA against
+// B = the raw filter rows; every thread reads its pixel's row of the accumulator from tensor
+// memory and applies
+//   sum (in - zi)(f - zf) = sum in*f - zf * sum in + (bias - zi * sum f + depth * zi * zf)
+// (the byte sum of its own patch: seven dp4a) and the requantization.  Each block holds as many
+// columns of tensor memory as there are output channels (32 at least); registers let eight blocks
+// share an SM, and the shared-memory request is padded so that never more blocks are resident
+// than the SM's 512 columns serve.
+namespace stem {
+
+using namespace sm100;
+
+struct Params {
+  ConvParams c;
+  int n_cols;     // MMA N = O (a multiple of 16)
+  int acc_cols;   // tensor-memory columns of the block (power of two >= n_cols, at least 32)
+  int64_t tiles;  // groups of 128 pixels
+  int *status;
+};
+
+template <int VAR>
+__global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q) {
+  const ConvParams &p = q.c;
+  extern __shared__ uint8_t stem_raw[];
+  const uint32_t base = (smem_u32(stem_raw) + 127u) & ~127u;
+  uint8_t *sm = stem_raw + (base - smem_u32(stem_raw));
+  // layout: A tile (4 KB) | B ([2][n_cols][16]) | constants [O] | mbarrier, tmem slot
+  uint8_t *b_tile = sm + 4096;
+  int32_t *cterm = reinterpret_cast<int32_t *>(b_tile + q.n_cols * 32);
+  uint64_t *bar = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(cterm) + ((p.O * 4 + 127) & ~127));
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+  const uint32_t mma_bar = smem_u32(bar);
+  const int warp = threadIdx.x >> 5;
+  mb_grid_dep_launch();
+  if (threadIdx.x == 0) {
+    mbar_init(mma_bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), static_cast<uint32_t>(q.acc_cols));
+    tmem_relinquish();
+  }
+  mb_grid_dep_wait();
+  // B: row o = the filter row (27 bytes, zero tail); byte k of row n lives at [k / 16][n][k % 16].
+  for (int i = threadIdx.x; i < q.n_cols * 2; i += 128) {
+    const int n = i >> 1, half = i & 1;
+    uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int b = 0; b < 16; ++b) {
+      const int k = half * 16 + b;
+      uint32_t v = 0;
+      if (k < 27) v = static_cast<uint32_t>(__ldg(p.filter + n * 27 + k));
+      w[b >> 2] |= v << (8 * (b & 3));
+    }
+    *reinterpret_cast<uint4 *>(b_tile + half * q.n_cols * 16 + n * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  for (int o = threadIdx.x; o < p.O; o += 128) {
+    int32_t fs = 0;
+    for (int d = 0; d < 27; ++d) fs += __ldg(p.filter + o * 27 + d);
+    cterm[o] = (p.bias != nullptr ? p.bias[o] : 0) - p.zp_in * fs + 27 * p.zp_in * p.zp_f;
+  }
+  fence_proxy_async();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const int64_t npix = static_cast<int64_t>(p.N) * p.Ho * p.Wo;
+  const uint32_t idesc = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, false, false, 128, static_cast<uint32_t>(q.n_cols));
+  const uint64_t a_desc = make_smem_desc(base, 2048, 128, 0);
+  const uint64_t b_desc = make_smem_desc(smem_u32(b_tile), static_cast<uint32_t>(q.n_cols) * 16, 128, 0);
+  const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+  const int groups = p.O >> 4;
+  __shared__ int give_up;
+  if (threadIdx.x == 0) give_up = 0;
+  uint32_t phase = 0;
+  for (int64_t t = blockIdx.x; t < q.tiles; t += gridDim.x, phase ^= 1) {
+    const int64_t pix = t * 128 + threadIdx.x;
+    uint32_t patch[7] = {0, 0, 0, 0, 0, 0, 0};
+    if (pix < npix) gather_patch<3, 3, 3>(p, pix, patch);
+    uint32_t sum_in = 0;
+#pragma unroll
+    for (int i = 0; i < 7; ++i) sum_in = __dp4a(patch[i], 0x01010101u, sum_in);
+    *reinterpret_cast<uint4 *>(sm + threadIdx.x * 16) = make_uint4(patch[0], patch[1], patch[2], patch[3]);
+    *reinterpret_cast<uint4 *>(sm + 2048 + threadIdx.x * 16) = make_uint4(patch[4], patch[5], patch[6], 0);
+    fence_proxy_async();
+    tc_fence_before_sync();
+    __syncthreads();  // the tile is complete; every warp has read the previous accumulator
+    if (threadIdx.x == 0) {
+      tc_fence_after_sync();
+      mma_i8_ss(tmem_base, a_desc, b_desc, idesc, 0u);
+      mma_commit(mma_bar);
+      // one thread waits for the MMA (bounded; on a timeout the block records it and leaves), the
+      // others wait at the block barrier, which costs no issue slots
+      bool done = mbar_try_wait(mma_bar, phase);
+      if (!done) {
+        const long long start = clock64();
+        while (!(done = mbar_try_wait(mma_bar, phase))) {
+          __nanosleep(32);
+          if (clock64() - start > (1ll << 31)) break;
+        }
+      }
+      if (!done) give_up = 1;
+    }
+    __syncthreads();
+    if (give_up != 0) {
+      if (threadIdx.x == 0) atomicCAS(q.status, 0, MB_DEV_TIMEOUT_MMA);
+      break;
+    }
+    tc_fence_after_sync();
+    uint32_t v[16], vn[16];
+    tmem_ld_32x32b_x16(taddr, v);
+    for (int cg = 0; cg < groups; ++cg) {
+      // the next group's columns are on their way while this one is requantized
+      if (cg + 1 < groups) tmem_ld_32x32b_x16(taddr + (cg + 1) * 16, vn);
+      if (cg == 0) tmem_ld_wait_x16(v);
+      const int32_t in_term = -p.zp_f * static_cast<int32_t>(sum_in);
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int4 ct = *reinterpret_cast<const int4 *>(cterm + cg * 16 + 4 * j);
+        const int32_t a0 = static_cast<int32_t>(v[4 * j + 0]) + in_term + ct.x;
+        const int32_t a1 = static_cast<int32_t>(v[4 * j + 1]) + in_term + ct.y;
+        const int32_t a2 = static_cast<int32_t>(v[4 * j + 2]) + in_term + ct.z;
+        const int32_t a3 = static_cast<int32_t>(v[4 * j + 3]) + in_term + ct.w;
+        if (VAR >= 4) {
+          w[j] = mb_requant_pack4<VAR == 5>(a0, a1, a2, a3, p.rq);
+        } else {
+          w[j] = mb_requant_fast(a0, p.rq) | (mb_requant_fast(a1, p.rq) << 8) | (mb_requant_fast(a2, p.rq) << 16) |
+                 (mb_requant_fast(a3, p.rq) << 24);
+        }
+      }
+      if (pix < npix) *reinterpret_cast<uint4 *>(p.out + pix * p.O + cg * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      if (cg + 1 < groups) {
+        tmem_ld_wait_x16(vn);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = vn[j];
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, static_cast<uint32_t>(q.acc_cols));
+  }
+}
+
+}  // namespace stem
 
 // Patch gather: row `pix` of the [pixels x depth_padded] matrix receives the
 // KH*KW*C bytes under the filter window.  Out-of-image taps and the alignment
@@ -350,6 +519,35 @@ extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
   p.rq = mb_make_requant(multiplier, right_shift, zp_out);
   p.rq_variant = mb_requant_variant(right_shift, zp_out);
 
+  if (ctx->stem_tc && ctx->use_tensor_cores && KH == 3 && KW == 3 && C == 3 && O % 16 == 0 && O <= 256 &&
+      (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && pixels >= 128) {
+    stem::Params q;
+    q.c = p;
+    q.n_cols = static_cast<int>(O);
+    q.acc_cols = q.n_cols <= 32 ? 32 : q.n_cols <= 64 ? 64 : q.n_cols <= 128 ? 128 : 256;
+    q.tiles = ceil_div64(pixels, 128);
+    q.status = ctx->dev_status;
+    const int per_sm = 512 / q.acc_cols;
+    // (the request is padded so that no more blocks fit an SM than its tensor memory serves: a
+    // further block would sit in tcgen05.alloc until another one has finished all its pixels)
+    const size_t smem = std::max<size_t>(128 + 4096 + static_cast<size_t>(q.n_cols) * 32 +
+                                             align_up(static_cast<size_t>(O) * 4, 128) + 64,
+                                         static_cast<size_t>(208 * 1024) / per_sm);
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(q.tiles, static_cast<int64_t>(ctx->num_sms) * per_sm));
+    const int var = p.rq_variant == 5 ? 5 : p.rq_variant == 4 ? 4 : 0;
+    if (!(ctx->func_attr_mask & (1ull << 60))) {
+      MB_CUDA(ctx, cudaFuncSetAttribute(stem::conv_u8_stem_mma_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+      MB_CUDA(ctx, cudaFuncSetAttribute(stem::conv_u8_stem_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+      MB_CUDA(ctx, cudaFuncSetAttribute(stem::conv_u8_stem_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+      ctx->func_attr_mask |= (1ull << 60);
+    }
+    if (var == 5) MB_CUDA(ctx, mb_launch_chained(ctx, stem::conv_u8_stem_mma_kernel<5>, dim3(grid), dim3(128), smem, q));
+    else if (var == 4) MB_CUDA(ctx, mb_launch_chained(ctx, stem::conv_u8_stem_mma_kernel<4>, dim3(grid), dim3(128), smem, q));
+    else MB_CUDA(ctx, mb_launch_chained(ctx, stem::conv_u8_stem_mma_kernel<0>, dim3(grid), dim3(128), smem, q));
+    MB_CUDA(ctx, cudaGetLastError());
+    ctx->launches++;
+    return MB_SUCCESS;
+  }
   if (KH == 3 && KW == 3 && C == 3 && O <= 256 &&
       (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {
     const size_t smem = static_cast<size_t>(O) * (8 * 4 + 4);

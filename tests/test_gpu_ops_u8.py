@@ -220,6 +220,58 @@ def test_conv2d_u8_pointwise_uses_tensor_core(ctx, orc):
     assert ctx.launches_tensor_core == before + 1
 
 
+@pytest.mark.parametrize("case", [
+    # N, H, W, O, stride, padding, zp_in, zp_out  (None: drawn by the case)
+    (1, 32, 32, 32, 4, "SAME", None, None),      # 64 output pixels: below one group, integer kernel both times
+    (1, 16, 16, 32, 1, "SAME", None, None),      # exactly two groups of 128 pixels
+    (2, 32, 32, 32, 1, "SAME", None, None),
+    (1, 224, 224, 32, 2, "SAME", None, None),    # MobileNet stem at full size
+    (3, 17, 23, 16, 2, "VALID", None, None),     # ragged last group, narrowest channel count
+    (2, 9, 9, 64, 1, "SAME", None, None),
+    (1, 30, 30, 256, 2, "SAME", None, None),     # widest channel count (whole accumulator block)
+    (1, 40, 36, 48, 1, "VALID", None, None),     # accumulator columns rounded up to 64
+    (2, 64, 64, 32, 2, "SAME", 0, 0),
+    (2, 64, 64, 32, 2, "SAME", 255, 255),        # padding bytes and outputs at the top of the range
+])
+def test_conv2d_u8_three_channel_stem_on_tensor_cores(ctx, orc, case):
+    """A 3x3 filter over 3 channels runs as one 128 x O x 32 tensor-core product per 128 pixels; the
+    integer kernel it replaces stays selectable.  Both must equal the reference arithmetic
+    (conv_2d.cc:206-318 of the reference's quantized Conv2d) and leave the bytes behind the output
+    alone."""
+    N, H, W, O, stride, padding, zi_forced, zo_forced = case
+    rng = np.random.Generator(np.random.PCG64(H * 131 + O))
+    x, f, zp_in, zp_f, mult, shift = conv_quant(orc, rng, (N, H, W, 3), (O, 3, 3, 3), 27)
+    if zi_forced is not None:
+        zp_in = zi_forced
+    bias = np.rint(rng.normal(0, 2000, size=O)).astype(np.int32)
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, 3, 3, (1, 1), (stride, stride),
+                                                      PAD[padding])
+    zp_out = int(rng.integers(96, 161)) if zo_forced is None else zo_forced
+    exp = orc.conv2d_u8(x, f, bias, (stride, stride), (ph, pw), (Ho, Wo), zp_in, zp_f, mult,
+                        shift, zp_out)
+    dx, df, db = ctx.upload(x), ctx.upload(f), ctx.upload(bias)
+    do = ctx.alloc(exp.size + 64)
+    import mace_b200
+    L = mace_b200.lib()
+    try:
+        for tc in (1, 0):
+            ctx.set_option("stem_tc", tc)
+            ctx._check(L.mb_memset(ctx.h, do.ptr, 0xA5, do.nbytes))
+            before = ctx.launches
+            ctx.conv2d_u8(dx, df, db, do, N, H, W, 3, O, 3, 3, (stride, stride),
+                          (ph >> 1, pw >> 1), (Ho, Wo), zp_in, zp_f, mult, shift, zp_out)
+            assert ctx.launches == before + 1
+            raw = ctx.download(do, (do.nbytes,), np.uint8)
+            assert np.array_equal(raw[:exp.size].reshape(exp.shape), exp), "stem_tc=%d" % tc
+            assert (raw[exp.size:] == 0xA5).all()
+        ctx.sync()   # raises if a block gave up its bounded wait
+    finally:
+        ctx.set_option("stem_tc", 1)
+        for b in (dx, df, db, do):
+            b.free()
+    assert len(np.unique(exp)) > 4
+
+
 # ---- DepthwiseConv2d ---------------------------------------------------------------
 
 @pytest.mark.parametrize("case", [
