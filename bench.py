@@ -645,7 +645,7 @@ def run_mobilenet(args, rank, world):
         lbytes = mobilenet_layer_bytes(layers, BATCH)
         # group operator times by kernel family
         fam = {"dw": ["dwconv3x3_u8_tma_kernel", 0.0, 0], "pw": ["gemm_u8_tc_kernel (pointwise)", 0.0, 0],
-               "stem": ["conv_u8_patch_dp4a_kernel", 0.0, 0], "pool": ["avgpool_u8_c4_kernel", 0.0, 0],
+               "stem": ["conv_u8_stem_mma_kernel", 0.0, 0], "pool": ["avgpool_u8_c4_kernel", 0.0, 0],
                "fc": ["gemm_u8_tc_kernel (FullyConnected, float rule)", 0.0, 0]}
         for label, t in per_op.items():
             name = label.split(":")[1]
