@@ -161,33 +161,58 @@ __device__ __forceinline__ void gather_patch(const ConvParams &p, int64_t pix, u
 #pragma unroll
   for (int i = 0; i < DW; ++i) patch[i] = 0;
   const uint32_t zi = static_cast<uint32_t>(p.zp_in);
-  // Interior pixels of a 3x3x3 window: a window row is 9 contiguous bytes (3 pixels x 3
-  // channels).  Three aligned 32-bit loads cover it (plus up to 3 bytes, which the "wi0 + 3 < W"
-  // condition keeps inside the tensor), a funnel shift removes the misalignment, and the three
-  // rows are spliced into the 27-byte patch at byte offsets 0, 9 and 18: 9 loads and about 20
-  // logic instructions instead of 27 byte loads with their address arithmetic and merges.
-  const bool interior = KH == 3 && KW == 3 && C == 3 && hi0 >= 0 && wi0 >= 0 && hi0 + 2 < p.H &&
-                        wi0 + 3 < p.W && (reinterpret_cast<uintptr_t>(p.in) & 3u) == 0;
-  if (interior) {
-    uint32_t r[3][3];
+  // A row of a 3x3x3 window is 9 contiguous bytes (3 pixels x 3 channels).  Three aligned 32-bit
+  // loads cover it, a funnel shift removes the misalignment, and the three rows are spliced into
+  // the 27-byte patch at byte offsets 0, 9 and 18: 9 loads and about 50 logic instructions instead
+  // of 27 byte loads with their address arithmetic and merges.  Taps outside the image take the
+  // input zero point through byte masks (columns) and selects (rows), so border pixels follow the
+  // same instruction stream as interior ones and a warp that holds a border pixel does not run
+  // both versions.  The 12 bytes of a row's loads may start up to 3 bytes before and end up to
+  // 3 bytes behind the 9 wanted ones: only pixels for which that would leave the tensor (its
+  // first and last few bytes) take the byte-wise version below.
+  bool words = false;
+  if constexpr (KH == 3 && KW == 3 && C == 3) {
+    const int64_t total = static_cast<int64_t>(p.N) * p.H * p.W * 3;
+    const bool c0 = static_cast<unsigned>(wi0) < static_cast<unsigned>(p.W);
+    const bool c1 = static_cast<unsigned>(wi0 + 1) < static_cast<unsigned>(p.W);
+    const bool c2 = static_cast<unsigned>(wi0 + 2) < static_cast<unsigned>(p.W);
+    int64_t a[3];
+    bool row_ok[3];
+    words = (reinterpret_cast<uintptr_t>(p.in) & 3u) == 0;
 #pragma unroll
     for (int kh = 0; kh < 3; ++kh) {
-      const int64_t a = (static_cast<int64_t>(n) * p.H + hi0 + kh) * p.W * 3 + static_cast<int64_t>(wi0) * 3;
-      const uint32_t *wp = reinterpret_cast<const uint32_t *>(p.in + (a & ~static_cast<int64_t>(3)));
-      const uint32_t sh = (static_cast<uint32_t>(a) & 3u) * 8;
-      const uint32_t w0 = __ldg(wp), w1 = __ldg(wp + 1), w2 = __ldg(wp + 2);
-      r[kh][0] = __funnelshift_r(w0, w1, sh);
-      r[kh][1] = __funnelshift_r(w1, w2, sh);
-      r[kh][2] = (w2 >> sh) & 0xffu;  // the row's ninth byte
+      const int hi = hi0 + kh;
+      row_ok[kh] = static_cast<unsigned>(hi) < static_cast<unsigned>(p.H);
+      a[kh] = ((static_cast<int64_t>(n) * p.H + (row_ok[kh] ? hi : 0)) * p.W + wi0) * 3;
+      const int64_t first = a[kh] & ~static_cast<int64_t>(3);
+      words = words && first >= 0 && first + 12 <= total;
     }
-    patch[0] = r[0][0];
-    patch[1] = r[0][1];
-    patch[2] = r[0][2] | (r[1][0] << 8);
-    patch[3] = __funnelshift_r(r[1][0], r[1][1], 24);
-    patch[4] = (r[1][1] >> 24) | (r[1][2] << 8) | (r[2][0] << 16);
-    patch[5] = __funnelshift_r(r[2][0], r[2][1], 16);
-    patch[6] = (r[2][1] >> 16) | (r[2][2] << 16);
-  } else {
+    if (words) {
+      const uint32_t zi4 = zi * 0x01010101u;
+      const uint32_t m0 = (c0 ? 0x00ffffffu : 0u) | (c1 ? 0xff000000u : 0u);
+      const uint32_t m1 = (c1 ? 0x0000ffffu : 0u) | (c2 ? 0xffff0000u : 0u);
+      const uint32_t m2 = c2 ? 0xffu : 0u;
+      uint32_t r[3][3];
+#pragma unroll
+      for (int kh = 0; kh < 3; ++kh) {
+        const uint32_t *wp = reinterpret_cast<const uint32_t *>(p.in + (a[kh] & ~static_cast<int64_t>(3)));
+        const uint32_t sh = (static_cast<uint32_t>(a[kh]) & 3u) * 8;
+        const uint32_t w0 = __ldg(wp), w1 = __ldg(wp + 1), w2 = __ldg(wp + 2);
+        const uint32_t f0 = __funnelshift_r(w0, w1, sh), f1 = __funnelshift_r(w1, w2, sh), f2 = w2 >> sh;
+        r[kh][0] = row_ok[kh] ? ((f0 & m0) | (zi4 & ~m0)) : zi4;
+        r[kh][1] = row_ok[kh] ? ((f1 & m1) | (zi4 & ~m1)) : zi4;
+        r[kh][2] = row_ok[kh] ? ((f2 & m2) | (zi & ~m2)) : zi;  // the row's ninth byte
+      }
+      patch[0] = r[0][0];
+      patch[1] = r[0][1];
+      patch[2] = r[0][2] | (r[1][0] << 8);
+      patch[3] = __funnelshift_r(r[1][0], r[1][1], 24);
+      patch[4] = (r[1][1] >> 24) | (r[1][2] << 8) | (r[2][0] << 16);
+      patch[5] = __funnelshift_r(r[2][0], r[2][1], 16);
+      patch[6] = (r[2][1] >> 16) | (r[2][2] << 16);
+    }
+  }
+  if (!words) {
 #pragma unroll
   for (int kh = 0; kh < KH; ++kh) {
     const int hi = hi0 + kh;
