@@ -34,7 +34,23 @@ struct ConvParams {
   int32_t zp_in, zp_f;
   mb_requant_params rq;
   int rq_variant;  // mb_requant_variant()
+  // pixel index -> (image, row, column) without a hardware division: see FastDiv
+  uint32_t wo_mul, wo_shift, ho_mul, ho_shift;
 };
+
+// Division of a dividend below 2^31 by a divisor fixed at launch: with s = ceil(log2 d) and
+// m = ceil(2^(31 + s) / d) (which fits 32 bits), floor(n / d) = (n * m) >> (31 + s) for every
+// n < 2^31, because m * d - 2^(31 + s) < d <= 2^s.  d = 1 is encoded as m = 0.
+static inline void fast_div_make(uint32_t d, uint32_t *mul, uint32_t *shift) {
+  if (d <= 1) { *mul = 0; *shift = 0; return; }
+  uint32_t s = 0;
+  while ((1ull << s) < d) ++s;
+  *mul = static_cast<uint32_t>(((1ull << (31 + s)) + d - 1) / d);
+  *shift = s - 1;
+}
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shift) {
+  return mul == 0 ? n : (__umulhi(n, mul) >> shift);
+}
 
 // Direct convolution: thread = one output pixel, OT output channels at a time.
 // Filter (zero point removed, int16) lives in shared memory as [depth][O].
@@ -152,10 +168,10 @@ __device__ __forceinline__ void gather_patch(const ConvParams &p, int64_t pix, u
   constexpr int DW = (DEPTH + 3) / 4;
   // (the pixel count is below 2^31: 32-bit divisions)
   const uint32_t pix32 = static_cast<uint32_t>(pix);
-  const int wo = static_cast<int>(pix32 % static_cast<uint32_t>(p.Wo));
-  const uint32_t row32 = pix32 / static_cast<uint32_t>(p.Wo);
-  const int ho = static_cast<int>(row32 % static_cast<uint32_t>(p.Ho));
-  const int n = static_cast<int>(row32 / static_cast<uint32_t>(p.Ho));
+  const uint32_t row32 = fast_div(pix32, p.wo_mul, p.wo_shift);
+  const int wo = static_cast<int>(pix32 - row32 * static_cast<uint32_t>(p.Wo));
+  const int n = static_cast<int>(fast_div(row32, p.ho_mul, p.ho_shift));
+  const int ho = static_cast<int>(row32 - static_cast<uint32_t>(n) * static_cast<uint32_t>(p.Ho));
   const int hi0 = ho * p.stride_h - p.pad_top, wi0 = wo * p.stride_w - p.pad_left;
   const uint8_t *in_n = p.in + static_cast<int64_t>(n) * p.H * p.W * C;
 #pragma unroll
@@ -172,20 +188,25 @@ __device__ __forceinline__ void gather_patch(const ConvParams &p, int64_t pix, u
   // first and last few bytes) take the byte-wise version below.
   bool words = false;
   if constexpr (KH == 3 && KW == 3 && C == 3) {
-    const int64_t total = static_cast<int64_t>(p.N) * p.H * p.W * 3;
+    // (the host sends only images of fewer than 2^31 bytes here: offsets inside an image are 32-bit)
+    const int32_t img_bytes = p.H * p.W * 3;
+    const uint32_t img_mis = static_cast<uint32_t>(n) * static_cast<uint32_t>(img_bytes);  // low bits decide the alignment
     const bool c0 = static_cast<unsigned>(wi0) < static_cast<unsigned>(p.W);
     const bool c1 = static_cast<unsigned>(wi0 + 1) < static_cast<unsigned>(p.W);
     const bool c2 = static_cast<unsigned>(wi0 + 2) < static_cast<unsigned>(p.W);
-    int64_t a[3];
+    int32_t first[3];   // offset, inside the image, of the aligned word that holds the row's first byte
+    uint32_t sh[3];
     bool row_ok[3];
     words = (reinterpret_cast<uintptr_t>(p.in) & 3u) == 0;
 #pragma unroll
     for (int kh = 0; kh < 3; ++kh) {
       const int hi = hi0 + kh;
       row_ok[kh] = static_cast<unsigned>(hi) < static_cast<unsigned>(p.H);
-      a[kh] = ((static_cast<int64_t>(n) * p.H + (row_ok[kh] ? hi : 0)) * p.W + wi0) * 3;
-      const int64_t first = a[kh] & ~static_cast<int64_t>(3);
-      words = words && first >= 0 && first + 12 <= total;
+      const int32_t off = ((row_ok[kh] ? hi : 0) * p.W + wi0) * 3;
+      const uint32_t mis = (img_mis + static_cast<uint32_t>(off)) & 3u;
+      first[kh] = off - static_cast<int32_t>(mis);
+      sh[kh] = mis * 8;
+      words = words && (first[kh] >= 0 || n > 0) && (first[kh] + 12 <= img_bytes || n + 1 < p.N);
     }
     if (words) {
       const uint32_t zi4 = zi * 0x01010101u;
@@ -195,10 +216,9 @@ __device__ __forceinline__ void gather_patch(const ConvParams &p, int64_t pix, u
       uint32_t r[3][3];
 #pragma unroll
       for (int kh = 0; kh < 3; ++kh) {
-        const uint32_t *wp = reinterpret_cast<const uint32_t *>(p.in + (a[kh] & ~static_cast<int64_t>(3)));
-        const uint32_t sh = (static_cast<uint32_t>(a[kh]) & 3u) * 8;
+        const uint32_t *wp = reinterpret_cast<const uint32_t *>(in_n + first[kh]);
         const uint32_t w0 = __ldg(wp), w1 = __ldg(wp + 1), w2 = __ldg(wp + 2);
-        const uint32_t f0 = __funnelshift_r(w0, w1, sh), f1 = __funnelshift_r(w1, w2, sh), f2 = w2 >> sh;
+        const uint32_t f0 = __funnelshift_r(w0, w1, sh[kh]), f1 = __funnelshift_r(w1, w2, sh[kh]), f2 = w2 >> sh[kh];
         r[kh][0] = row_ok[kh] ? ((f0 & m0) | (zi4 & ~m0)) : zi4;
         r[kh][1] = row_ok[kh] ? ((f1 & m1) | (zi4 & ~m1)) : zi4;
         r[kh][2] = row_ok[kh] ? ((f2 & m2) | (zi & ~m2)) : zi;  // the row's ninth byte
@@ -543,8 +563,11 @@ extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
   p.zp_in = zp_in; p.zp_f = zp_f;
   p.rq = mb_make_requant(multiplier, right_shift, zp_out);
   p.rq_variant = mb_requant_variant(right_shift, zp_out);
+  fast_div_make(static_cast<uint32_t>(Wo), &p.wo_mul, &p.wo_shift);
+  fast_div_make(static_cast<uint32_t>(Ho), &p.ho_mul, &p.ho_shift);
+  const bool image_32bit = H * W * C < (1ll << 31) - 16;
 
-  if (ctx->stem_tc && ctx->use_tensor_cores && KH == 3 && KW == 3 && C == 3 && O % 16 == 0 && O <= 256 &&
+  if (image_32bit && ctx->stem_tc && ctx->use_tensor_cores && KH == 3 && KW == 3 && C == 3 && O % 16 == 0 && O <= 256 &&
       (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && pixels >= 128) {
     stem::Params q;
     q.c = p;
@@ -573,7 +596,7 @@ extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
     ctx->launches++;
     return MB_SUCCESS;
   }
-  if (KH == 3 && KW == 3 && C == 3 && O <= 256 &&
+  if (image_32bit && KH == 3 && KW == 3 && C == 3 && O <= 256 &&
       (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {
     const size_t smem = static_cast<size_t>(O) * (8 * 4 + 4);
     const unsigned blocks = static_cast<unsigned>(ceil_div64(pixels, 128));
