@@ -429,13 +429,8 @@ __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q
       break;
     }
     tc_fence_after_sync();
-    uint32_t v[16], vn[16];
-    tmem_ld_32x32b_x16(taddr, v);
-    for (int cg = 0; cg < groups; ++cg) {
-      // the next group's columns are on their way while this one is requantized
-      if (cg + 1 < groups) tmem_ld_32x32b_x16(taddr + (cg + 1) * 16, vn);
-      if (cg == 0) tmem_ld_wait_x16(v);
-      const int32_t in_term = -p.zp_f * static_cast<int32_t>(sum_in);
+    const int32_t in_term = -p.zp_f * static_cast<int32_t>(sum_in);
+    auto emit = [&](const uint32_t (&v)[16], int cg) {
       uint32_t w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -452,10 +447,18 @@ __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q
         }
       }
       if (pix < npix) *reinterpret_cast<uint4 *>(p.out + pix * p.O + cg * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-      if (cg + 1 < groups) {
-        tmem_ld_wait_x16(vn);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = vn[j];
+    };
+    // two groups of 16 channels per round trip to tensor memory
+    for (int cg = 0; cg < groups; cg += 2) {
+      uint32_t v0[16], v1[16];
+      const bool two = cg + 1 < groups;
+      tmem_ld_32x32b_x16(taddr + cg * 16, v0);
+      if (two) tmem_ld_32x32b_x16(taddr + (cg + 1) * 16, v1);
+      tmem_ld_wait_x16(v0);
+      emit(v0, cg);
+      if (two) {
+        tmem_ld_wait_x16(v1);
+        emit(v1, cg + 1);
       }
     }
   }
