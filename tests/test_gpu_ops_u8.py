@@ -232,6 +232,8 @@ def test_conv2d_u8_pointwise_uses_tensor_core(ctx, orc):
     (1, 40, 36, 48, 1, "VALID", None, None),     # accumulator columns rounded up to 64
     (2, 64, 64, 32, 2, "SAME", 0, 0),
     (2, 64, 64, 32, 2, "SAME", 255, 255),        # padding bytes and outputs at the top of the range
+    (200, 3, 3, 32, 1, "VALID", None, None),     # one output pixel per image: row and column divisors of 1
+    (2, 13, 131, 32, 1, "SAME", None, None),     # prime row length, borders on every side
 ])
 def test_conv2d_u8_three_channel_stem_on_tensor_cores(ctx, orc, case):
     """A 3x3 filter over 3 channels runs as one 128 x O x 32 tensor-core product per 128 pixels; the
@@ -270,6 +272,35 @@ def test_conv2d_u8_three_channel_stem_on_tensor_cores(ctx, orc, case):
         for b in (dx, df, db, do):
             b.free()
     assert len(np.unique(exp)) > 4
+
+
+def test_conv2d_u8_three_channel_input_off_the_word_grid(ctx, orc):
+    """The word-wise window loads of the 3x3x3 kernels need a 4-byte aligned input; any other input
+    address takes the byte-wise gather and must give the same bytes."""
+    import types
+    rng = np.random.Generator(np.random.PCG64(77))
+    N, H, W, O = 2, 20, 24, 32
+    x, f, zp_in, zp_f, mult, shift = conv_quant(orc, rng, (N, H, W, 3), (O, 3, 3, 3), 27)
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, 3, 3, (1, 1), (1, 1), PAD["SAME"])
+    exp = orc.conv2d_u8(x, f, None, (1, 1), (ph, pw), (Ho, Wo), zp_in, zp_f, mult, shift, 90)
+    raw = np.zeros(x.size + 8, np.uint8)
+    df, do = ctx.upload(f), ctx.alloc(exp.size)
+    try:
+        for shift_bytes in (1, 2, 3):
+            raw[:] = 0
+            raw[shift_bytes:shift_bytes + x.size] = x.reshape(-1)
+            dx = ctx.upload(raw)
+            view = types.SimpleNamespace(ptr=dx.ptr + shift_bytes)
+            for tc in (1, 0):
+                ctx.set_option("stem_tc", tc)
+                ctx.conv2d_u8(view, df, None, do, N, H, W, 3, O, 3, 3, (1, 1), (ph >> 1, pw >> 1),
+                              (Ho, Wo), zp_in, zp_f, mult, shift, 90)
+                assert np.array_equal(ctx.download(do, exp.shape, np.uint8), exp), (shift_bytes, tc)
+            dx.free()
+    finally:
+        ctx.set_option("stem_tc", 1)
+        df.free()
+        do.free()
 
 
 # ---- DepthwiseConv2d ---------------------------------------------------------------
