@@ -48,6 +48,7 @@ struct mb_context {
   long long *tc_timeline = nullptr;  // optional device buffer: per-role clock stamps of CTA 0
   uint64_t capture_launches0 = 0, capture_launches_tc0 = 0;
   uint64_t func_attr_mask = 0;   // kernels whose shared-memory limit was raised
+  uint64_t func_attr_mask2 = 0;  // the same for the thread-per-pixel convolution kernels
   int pdl_next_gemm = 0;         // the next tensor-core GEMM may start before its predecessor (the
                                  // operand-sum kernel) ends; it waits for it where it reads the sums
   void *skinny_ws = nullptr;     // arrival counters of the few-row GEMM (zero between calls)
@@ -62,6 +63,7 @@ struct mb_context {
   int skinny_max_m = 16;         // row counts up to this take the streaming few-row GEMM
   int max_pair_clusters = 0;     // co-resident clusters of the pair GEMM (0: not asked yet)
   int stem_tc = 1;               // 3x3x3 first-layer convolution: the products on the tensor core
+  int thin_pw = 1;               // pointwise layers of depth 32 / 64 (2: also 128) on the same thread-per-pixel kernel
   int pair_gemm = 0;             // large GEMMs on CTA pairs (clusters of two sharing each tile's B): 1 where
                                  // it applies, 2 wherever it can run.  Off by default: measured equal at 8192^3
                                  // (409 vs 410 us) and slower at 4096^3 (54.7 vs 51.6 us): the main loop is paced

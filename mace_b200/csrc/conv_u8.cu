@@ -340,15 +340,21 @@ struct Params {
   int *status;
 };
 
-template <int VAR>
+// KD: 27 = the 3x3x3 window (gathered, zero tail up to 32); 32 / 64 / 128 = a pointwise layer
+// of that depth, whose A row is the pixel's own KD contiguous bytes.
+// GROUPS: the number of 16-channel groups when it is fixed at compile time (2, 4: the epilogue is
+// then straight-line code without per-group address arithmetic), 0 = taken from the parameters.
+template <int VAR, int KD, int GROUPS>
 __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q) {
+  constexpr int KPAD = KD == 27 ? 32 : KD;   // bytes of an A / B row
+  constexpr int PLANES = KPAD / 16;          // 16-byte pieces per row
   const ConvParams &p = q.c;
   extern __shared__ uint8_t stem_raw[];
   const uint32_t base = (smem_u32(stem_raw) + 127u) & ~127u;
   uint8_t *sm = stem_raw + (base - smem_u32(stem_raw));
-  // layout: A tile (4 KB) | B ([2][n_cols][16]) | constants [O] | mbarrier, tmem slot
-  uint8_t *b_tile = sm + 4096;
-  int32_t *cterm = reinterpret_cast<int32_t *>(b_tile + q.n_cols * 32);
+  // layout: A tile ([PLANES][128][16]) | B ([PLANES][n_cols][16]) | constants [O] | mbarrier, tmem slot
+  uint8_t *b_tile = sm + PLANES * 2048;
+  int32_t *cterm = reinterpret_cast<int32_t *>(b_tile + q.n_cols * KPAD);
   uint64_t *bar = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(cterm) + ((p.O * 4 + 127) & ~127));
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
   const uint32_t mma_bar = smem_u32(bar);
@@ -363,23 +369,38 @@ __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q
     tmem_relinquish();
   }
   mb_grid_dep_wait();
-  // B: row o = the filter row (27 bytes, zero tail); byte k of row n lives at [k / 16][n][k % 16].
-  for (int i = threadIdx.x; i < q.n_cols * 2; i += 128) {
-    const int n = i >> 1, half = i & 1;
-    uint32_t w[4] = {0, 0, 0, 0};
+  // B: row o = the filter row (KD bytes, zero tail); byte k of row n lives at [k / 16][n][k % 16].
+  const bool filter_words = KD != 27 && (reinterpret_cast<uintptr_t>(p.filter) & 15u) == 0;
+  for (int i = threadIdx.x; i < q.n_cols * PLANES; i += 128) {
+    const int n = i / PLANES, piece = i % PLANES;
+    uint4 v4;
+    if (filter_words) {
+      v4 = __ldg(reinterpret_cast<const uint4 *>(p.filter + n * KD + piece * 16));
+    } else {
+      uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int b = 0; b < 16; ++b) {
-      const int k = half * 16 + b;
-      uint32_t v = 0;
-      if (k < 27) v = static_cast<uint32_t>(__ldg(p.filter + n * 27 + k));
-      w[b >> 2] |= v << (8 * (b & 3));
+      for (int b = 0; b < 16; ++b) {
+        const int k = piece * 16 + b;
+        uint32_t v = 0;
+        if (k < KD) v = static_cast<uint32_t>(__ldg(p.filter + n * KD + k));
+        w[b >> 2] |= v << (8 * (b & 3));
+      }
+      v4 = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    *reinterpret_cast<uint4 *>(b_tile + half * q.n_cols * 16 + n * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4 *>(b_tile + piece * q.n_cols * 16 + n * 16) = v4;
   }
-  for (int o = threadIdx.x; o < p.O; o += 128) {
-    int32_t fs = 0;
-    for (int d = 0; d < 27; ++d) fs += __ldg(p.filter + o * 27 + d);
-    cterm[o] = (p.bias != nullptr ? p.bias[o] : 0) - p.zp_in * fs + 27 * p.zp_in * p.zp_f;
+  __syncthreads();
+  for (int o = threadIdx.x; o < p.O; o += 128) {  // (from the tile just written: 16 bytes a load)
+    uint32_t fs = 0;
+#pragma unroll
+    for (int piece = 0; piece < PLANES; ++piece) {
+      const uint4 v = *reinterpret_cast<const uint4 *>(b_tile + piece * q.n_cols * 16 + o * 16);
+      fs = __dp4a(v.x, 0x01010101u, fs);
+      fs = __dp4a(v.y, 0x01010101u, fs);
+      fs = __dp4a(v.z, 0x01010101u, fs);
+      fs = __dp4a(v.w, 0x01010101u, fs);
+    }
+    cterm[o] = (p.bias != nullptr ? p.bias[o] : 0) - p.zp_in * static_cast<int32_t>(fs) + KD * p.zp_in * p.zp_f;
   }
   fence_proxy_async();
   tc_fence_before_sync();
@@ -388,28 +409,77 @@ __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q
   const uint32_t tmem_base = *tmem_slot;
   const int64_t npix = static_cast<int64_t>(p.N) * p.Ho * p.Wo;
   const uint32_t idesc = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, false, false, 128, static_cast<uint32_t>(q.n_cols));
+  // K-major without swizzle: 8-row x 16-byte core matrices, 128 bytes from one group of 8 rows to
+  // the next, a plane (all rows) from one 16-byte piece of K to the next; an MMA covers two planes
   const uint64_t a_desc = make_smem_desc(base, 2048, 128, 0);
   const uint64_t b_desc = make_smem_desc(smem_u32(b_tile), static_cast<uint32_t>(q.n_cols) * 16, 128, 0);
   const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-  const int groups = p.O >> 4;
+  const int groups = GROUPS != 0 ? GROUPS : (p.O >> 4);
+  const int n_out = GROUPS != 0 ? GROUPS * 16 : p.O;
   __shared__ int give_up;
   if (threadIdx.x == 0) give_up = 0;
   uint32_t phase = 0;
+  uint4 ahead[PLANES <= 4 ? PLANES : 1];
+  if constexpr (KD != 27 && PLANES <= 4) {
+    const int64_t first_pix = static_cast<int64_t>(blockIdx.x) * 128 + threadIdx.x;
+    const uint4 *row = reinterpret_cast<const uint4 *>(p.in + first_pix * KD);
+#pragma unroll
+    for (int j = 0; j < PLANES; ++j) ahead[j] = first_pix < npix ? __ldg(row + j) : make_uint4(0, 0, 0, 0);
+  }
   for (int64_t t = blockIdx.x; t < q.tiles; t += gridDim.x, phase ^= 1) {
     const int64_t pix = t * 128 + threadIdx.x;
-    uint32_t patch[7] = {0, 0, 0, 0, 0, 0, 0};
-    if (pix < npix) gather_patch<3, 3, 3>(p, pix, patch);
     uint32_t sum_in = 0;
+    if constexpr (KD == 27) {
+      uint32_t patch[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (pix < npix) gather_patch<3, 3, 3>(p, pix, reinterpret_cast<uint32_t (&)[7]>(patch));
 #pragma unroll
-    for (int i = 0; i < 7; ++i) sum_in = __dp4a(patch[i], 0x01010101u, sum_in);
-    *reinterpret_cast<uint4 *>(sm + threadIdx.x * 16) = make_uint4(patch[0], patch[1], patch[2], patch[3]);
-    *reinterpret_cast<uint4 *>(sm + 2048 + threadIdx.x * 16) = make_uint4(patch[4], patch[5], patch[6], 0);
+      for (int i = 0; i < 7; ++i) sum_in = __dp4a(patch[i], 0x01010101u, sum_in);
+      *reinterpret_cast<uint4 *>(sm + threadIdx.x * 16) = make_uint4(patch[0], patch[1], patch[2], patch[3]);
+      *reinterpret_cast<uint4 *>(sm + 2048 + threadIdx.x * 16) = make_uint4(patch[4], patch[5], patch[6], 0);
+    } else if constexpr (PLANES <= 4) {
+      // the pixel's own row; the row of this thread's pixel in the block's NEXT group is requested
+      // here, so that it travels while this group's product and epilogue run
+#pragma unroll
+      for (int j = 0; j < PLANES; ++j) {
+        sum_in = __dp4a(ahead[j].x, 0x01010101u, sum_in);
+        sum_in = __dp4a(ahead[j].y, 0x01010101u, sum_in);
+        sum_in = __dp4a(ahead[j].z, 0x01010101u, sum_in);
+        sum_in = __dp4a(ahead[j].w, 0x01010101u, sum_in);
+        *reinterpret_cast<uint4 *>(sm + j * 2048 + threadIdx.x * 16) = ahead[j];
+      }
+      const int64_t next_pix = pix + static_cast<int64_t>(gridDim.x) * 128;
+      const uint4 *row = reinterpret_cast<const uint4 *>(p.in + next_pix * KD);
+#pragma unroll
+      for (int j = 0; j < PLANES; ++j) ahead[j] = next_pix < npix ? __ldg(row + j) : make_uint4(0, 0, 0, 0);
+    } else {
+      // the pixel's own row, four 16-byte pieces at a time (all four requested before the first is used)
+      const uint4 *row = reinterpret_cast<const uint4 *>(p.in + pix * KD);
+#pragma unroll
+      for (int p0 = 0; p0 < PLANES; p0 += 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (p0 + j < PLANES) v[j] = pix < npix ? __ldg(row + p0 + j) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (p0 + j < PLANES) {
+            sum_in = __dp4a(v[j].x, 0x01010101u, sum_in);
+            sum_in = __dp4a(v[j].y, 0x01010101u, sum_in);
+            sum_in = __dp4a(v[j].z, 0x01010101u, sum_in);
+            sum_in = __dp4a(v[j].w, 0x01010101u, sum_in);
+            *reinterpret_cast<uint4 *>(sm + (p0 + j) * 2048 + threadIdx.x * 16) = v[j];
+          }
+      }
+    }
     fence_proxy_async();
     tc_fence_before_sync();
     __syncthreads();  // the tile is complete; every warp has read the previous accumulator
     if (threadIdx.x == 0) {
       tc_fence_after_sync();
-      mma_i8_ss(tmem_base, a_desc, b_desc, idesc, 0u);
+#pragma unroll
+      for (int kk = 0; kk < PLANES / 2; ++kk)
+        mma_i8_ss(tmem_base, a_desc + static_cast<uint64_t>(kk * (4096 >> 4)),
+                  b_desc + static_cast<uint64_t>(kk * ((q.n_cols * 32) >> 4)), idesc, kk > 0 ? 1u : 0u);
       mma_commit(mma_bar);
       // one thread waits for the MMA (bounded; on a timeout the block records it and leaves), the
       // others wait at the block barrier, which costs no issue slots
@@ -446,9 +516,10 @@ __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q
                  (mb_requant_fast(a3, p.rq) << 24);
         }
       }
-      if (pix < npix) *reinterpret_cast<uint4 *>(p.out + pix * p.O + cg * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      if (pix < npix) *reinterpret_cast<uint4 *>(p.out + pix * n_out + cg * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     };
     // two groups of 16 channels per round trip to tensor memory
+#pragma unroll
     for (int cg = 0; cg < groups; cg += 2) {
       uint32_t v0[16], v1[16];
       const bool two = cg + 1 < groups;
@@ -467,6 +538,55 @@ __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q
   if (warp == 0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, static_cast<uint32_t>(q.acc_cols));
+  }
+}
+
+template <int KD, int GROUPS>
+static int launch_kdg(mb_context *ctx, const Params &q, unsigned grid, size_t smem, int attr_bit) {
+  const int var = q.c.rq_variant == 5 ? 5 : q.c.rq_variant == 4 ? 4 : 0;
+  if (!(ctx->func_attr_mask2 & (1ull << attr_bit))) {
+    MB_CUDA(ctx, cudaFuncSetAttribute(conv_u8_stem_mma_kernel<5, KD, GROUPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+    MB_CUDA(ctx, cudaFuncSetAttribute(conv_u8_stem_mma_kernel<4, KD, GROUPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+    MB_CUDA(ctx, cudaFuncSetAttribute(conv_u8_stem_mma_kernel<0, KD, GROUPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+    ctx->func_attr_mask2 |= (1ull << attr_bit);
+  }
+  if (var == 5) MB_CUDA(ctx, mb_launch_chained(ctx, conv_u8_stem_mma_kernel<5, KD, GROUPS>, dim3(grid), dim3(128), smem, q));
+  else if (var == 4) MB_CUDA(ctx, mb_launch_chained(ctx, conv_u8_stem_mma_kernel<4, KD, GROUPS>, dim3(grid), dim3(128), smem, q));
+  else MB_CUDA(ctx, mb_launch_chained(ctx, conv_u8_stem_mma_kernel<0, KD, GROUPS>, dim3(grid), dim3(128), smem, q));
+  MB_CUDA(ctx, cudaGetLastError());
+  ctx->launches++;
+  return MB_SUCCESS;
+}
+
+template <int KD>
+static int launch_kd(mb_context *ctx, const Params &q, unsigned grid, size_t smem, int attr_bit) {
+  if (KD <= 32 && q.n_cols == 32) return launch_kdg<KD, (KD <= 32 ? 2 : 0)>(ctx, q, grid, smem, attr_bit + 1);
+  if (KD <= 32 && q.n_cols == 64) return launch_kdg<KD, (KD <= 32 ? 4 : 0)>(ctx, q, grid, smem, attr_bit + 2);
+  return launch_kdg<KD, 0>(ctx, q, grid, smem, attr_bit);
+}
+
+// kd: 27 (the 3x3x3 window) or the depth of a pointwise layer (32, 64, 128); O a multiple of 16, at
+// most 256; the output 16-byte aligned (and the input too, for a pointwise layer).
+static int launch(mb_context *ctx, const ConvParams &p, int kd, int64_t pixels) {
+  Params q;
+  q.c = p;
+  q.n_cols = p.O;
+  q.acc_cols = q.n_cols <= 32 ? 32 : q.n_cols <= 64 ? 64 : q.n_cols <= 128 ? 128 : 256;
+  q.tiles = ceil_div64(pixels, 128);
+  q.status = ctx->dev_status;
+  const int kpad = kd == 27 ? 32 : kd;
+  const int per_sm = 512 / q.acc_cols;
+  // (the request is padded so that no more blocks fit an SM than its tensor memory serves: a
+  // further block would sit in tcgen05.alloc until another one has finished all its pixels)
+  const size_t smem = std::max<size_t>(128 + static_cast<size_t>(kpad / 16) * 2048 + static_cast<size_t>(q.n_cols) * kpad +
+                                           align_up(static_cast<size_t>(p.O) * 4, 128) + 64,
+                                       static_cast<size_t>(208 * 1024) / per_sm);
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(q.tiles, static_cast<int64_t>(ctx->num_sms) * per_sm));
+  switch (kd) {
+    case 27: return launch_kd<27>(ctx, q, grid, smem, 0);
+    case 32: return launch_kd<32>(ctx, q, grid, smem, 3);
+    case 64: return launch_kd<64>(ctx, q, grid, smem, 6);
+    default: return launch_kd<128>(ctx, q, grid, smem, 9);
   }
 }
 
@@ -550,6 +670,24 @@ extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
       Ho == H && Wo == W) {
     // out[pixel][o] = sum_c in[pixel][c] * filter[o][c]: A = input (K-major),
     // B^T = filter (K-major), C row-major = NHWC, bias per column (= channel).
+    // a short depth makes a 128-pixel tile of the persistent GEMM mostly hand-over: such layers
+    // take the thread-per-pixel kernel (see namespace stem)
+    if (ctx->thin_pw && ctx->use_tensor_cores && (C == 32 || (C == 64 && ctx->thin_pw >= 2) || (C == 128 && ctx->thin_pw >= 3)) && O % 16 == 0 &&
+        O <= 128 && pixels >= 128 * static_cast<int64_t>(ctx->num_sms) &&
+        ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(in)) & 15u) == 0) {
+      ConvParams p;
+      p.in = in; p.filter = filter; p.bias = bias; p.out = out;
+      p.N = static_cast<int>(N); p.H = static_cast<int>(H); p.W = static_cast<int>(W);
+      p.C = static_cast<int>(C); p.O = static_cast<int>(O);
+      p.KH = 1; p.KW = 1; p.stride_h = 1; p.stride_w = 1; p.pad_top = 0; p.pad_left = 0;
+      p.Ho = static_cast<int>(Ho); p.Wo = static_cast<int>(Wo);
+      p.depth = static_cast<int>(depth); p.depth_padded = p.depth;
+      p.zp_in = zp_in; p.zp_f = zp_f;
+      p.rq = mb_make_requant(multiplier, right_shift, zp_out);
+      p.rq_variant = mb_requant_variant(right_shift, zp_out);
+      p.wo_mul = p.wo_shift = p.ho_mul = p.ho_shift = 0;
+      return stem::launch(ctx, p, static_cast<int>(C), pixels);
+    }
     return mb_gemm_u8_rowmajor(ctx, in, filter, bias, out, 0, 1, pixels, O, depth, false, false,
                                0, 0, zp_in, zp_f, multiplier, right_shift, zp_out, 0);
   }
@@ -571,34 +709,8 @@ extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
   const bool image_32bit = H * W * C < (1ll << 31) - 16;
 
   if (image_32bit && ctx->stem_tc && ctx->use_tensor_cores && KH == 3 && KW == 3 && C == 3 && O % 16 == 0 && O <= 256 &&
-      (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && pixels >= 128) {
-    stem::Params q;
-    q.c = p;
-    q.n_cols = static_cast<int>(O);
-    q.acc_cols = q.n_cols <= 32 ? 32 : q.n_cols <= 64 ? 64 : q.n_cols <= 128 ? 128 : 256;
-    q.tiles = ceil_div64(pixels, 128);
-    q.status = ctx->dev_status;
-    const int per_sm = 512 / q.acc_cols;
-    // (the request is padded so that no more blocks fit an SM than its tensor memory serves: a
-    // further block would sit in tcgen05.alloc until another one has finished all its pixels)
-    const size_t smem = std::max<size_t>(128 + 4096 + static_cast<size_t>(q.n_cols) * 32 +
-                                             align_up(static_cast<size_t>(O) * 4, 128) + 64,
-                                         static_cast<size_t>(208 * 1024) / per_sm);
-    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(q.tiles, static_cast<int64_t>(ctx->num_sms) * per_sm));
-    const int var = p.rq_variant == 5 ? 5 : p.rq_variant == 4 ? 4 : 0;
-    if (!(ctx->func_attr_mask & (1ull << 60))) {
-      MB_CUDA(ctx, cudaFuncSetAttribute(stem::conv_u8_stem_mma_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
-      MB_CUDA(ctx, cudaFuncSetAttribute(stem::conv_u8_stem_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
-      MB_CUDA(ctx, cudaFuncSetAttribute(stem::conv_u8_stem_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
-      ctx->func_attr_mask |= (1ull << 60);
-    }
-    if (var == 5) MB_CUDA(ctx, mb_launch_chained(ctx, stem::conv_u8_stem_mma_kernel<5>, dim3(grid), dim3(128), smem, q));
-    else if (var == 4) MB_CUDA(ctx, mb_launch_chained(ctx, stem::conv_u8_stem_mma_kernel<4>, dim3(grid), dim3(128), smem, q));
-    else MB_CUDA(ctx, mb_launch_chained(ctx, stem::conv_u8_stem_mma_kernel<0>, dim3(grid), dim3(128), smem, q));
-    MB_CUDA(ctx, cudaGetLastError());
-    ctx->launches++;
-    return MB_SUCCESS;
-  }
+      (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && pixels >= 128)
+    return stem::launch(ctx, p, 27, pixels);
   if (image_32bit && KH == 3 && KW == 3 && C == 3 && O <= 256 &&
       (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {
     const size_t smem = static_cast<size_t>(O) * (8 * 4 + 4);

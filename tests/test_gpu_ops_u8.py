@@ -274,6 +274,56 @@ def test_conv2d_u8_three_channel_stem_on_tensor_cores(ctx, orc, case):
     assert len(np.unique(exp)) > 4
 
 
+@pytest.mark.parametrize("case", [
+    # N, H, W, C, O, zp_in, zp_out, bias
+    (2, 112, 112, 32, 64, None, None, True),     # MobileNet's first pointwise layer (reduced batch)
+    (4, 56, 57, 64, 128, None, None, True),      # depth 64: two products per group of pixels
+    (3, 80, 80, 128, 128, None, None, True),     # depth 128
+    (1, 150, 127, 32, 16, None, None, True),     # ragged last group, narrowest channel count
+    (2, 100, 100, 64, 48, None, None, True),     # accumulator columns rounded up
+    (1, 139, 137, 128, 80, None, None, True),
+    (2, 112, 112, 32, 64, 0, 0, False),          # no bias, zero points 0 (the packed requantization)
+    (2, 112, 112, 64, 128, 255, 255, True),
+    (2, 112, 112, 32, 32, None, None, True),
+])
+def test_conv2d_u8_pointwise_with_short_depth(ctx, orc, case):
+    """Pointwise layers of depth 32 (by default), 64 and 128 (by option) can run on the
+    thread-per-pixel tensor-core kernel instead of the persistent GEMM: both must equal the
+    reference arithmetic (conv_2d.cc:206-318) and leave the bytes behind the output alone."""
+    import mace_b200
+    N, H, W, C, O, zi_forced, zo_forced, with_bias = case
+    rng = np.random.Generator(np.random.PCG64(H * 131 + O + C))
+    x, f, zp_in, zp_f, mult, shift = conv_quant(orc, rng, (N, H, W, C), (O, 1, 1, C), C)
+    if zi_forced is not None:
+        zp_in = zi_forced
+    bias = np.rint(rng.normal(0, 2000, size=O)).astype(np.int32) if with_bias else None
+    zp_out = int(rng.integers(96, 161)) if zo_forced is None else zo_forced
+    exp = orc.conv2d_u8(x, f, bias, (1, 1), (0, 0), (H, W), zp_in, zp_f, mult, shift, zp_out)
+    dx, df = ctx.upload(x), ctx.upload(f)
+    db = ctx.upload(bias) if with_bias else None
+    do = ctx.alloc(exp.size + 64)
+    L = mace_b200.lib()
+    try:
+        for level in (3, 0):
+            ctx.set_option("thin_pw", level)
+            ctx._check(L.mb_memset(ctx.h, do.ptr, 0xA5, do.nbytes))
+            tc_before = ctx.launches_tensor_core
+            ctx.conv2d_u8(dx, df, db, do, N, H, W, C, O, 1, 1, (1, 1), (0, 0), (H, W), zp_in, zp_f,
+                          mult, shift, zp_out)
+            # (the persistent GEMM counts as a tensor-core GEMM launch, the per-pixel kernel does not)
+            assert (ctx.launches_tensor_core == tc_before) == (level == 3)
+            raw = ctx.download(do, (do.nbytes,), np.uint8)
+            assert np.array_equal(raw[:exp.size].reshape(exp.shape), exp), "thin_pw=%d" % level
+            assert (raw[exp.size:] == 0xA5).all()
+        ctx.sync()   # raises if a block gave up its bounded wait
+    finally:
+        ctx.set_option("thin_pw", 1)
+        for b in (dx, df, db, do):
+            if b is not None:
+                b.free()
+    assert len(np.unique(exp)) > 4
+
+
 def test_conv2d_u8_three_channel_input_off_the_word_grid(ctx, orc):
     """The word-wise window loads of the 3x3x3 kernels need a 4-byte aligned input; any other input
     address takes the byte-wise gather and must give the same bytes."""
