@@ -644,7 +644,7 @@ def run_mobilenet(args, rank, world):
         e2e_val = world * BATCH / (e2e_ms / e2e_steps * 1e-3)
         lbytes = mobilenet_layer_bytes(layers, BATCH)
         # group operator times by kernel family
-        fam = {"dw": ["dwconv3x3_u8_tma_kernel", 0.0, 0], "pw": ["gemm_u8_tc_kernel (pointwise)", 0.0, 0],
+        fam = {"dw": ["dwconv3x3_u8_tma_kernel", 0.0, 0], "pw": ["gemm_u8_tc_kernel (pointwise; the depth-32 first one on conv_u8_stem_mma_kernel)", 0.0, 0],
                "stem": ["conv_u8_stem_mma_kernel", 0.0, 0], "pool": ["avgpool_u8_c4_kernel", 0.0, 0],
                "fc": ["gemm_u8_tc_kernel (FullyConnected, float rule)", 0.0, 0]}
         for label, t in per_op.items():

@@ -125,7 +125,9 @@ int mb_graph_end(mb_context *ctx, void **graph_exec);
 int mb_graph_launch(mb_context *ctx, void *graph_exec);
 int mb_graph_destroy(mb_context *ctx, void *graph_exec);
 /* Number of kernels launched through this context so far; the second form
- * counts only tcgen05 tensor-core GEMM launches. */
+ * counts only launches of the persistent tcgen05 GEMM kernels (the
+ * thread-per-pixel convolution kernels, which also multiply on the tensor
+ * core, are not in it). */
 uint64_t mb_launch_count(const mb_context *ctx);
 uint64_t mb_launch_count_tensor_core(const mb_context *ctx);
 /* ... and how many of those ran on CTA pairs (see the "pair" option). */
@@ -159,7 +161,12 @@ int mb_pair_clusters(const mb_context *ctx);
  * "gemv_chain_chunks" = 0 keeps 4 KB chunks),
  * "stem_tc" (1 default: a 3x3 convolution over 3 channels whose output
  * channel count is a multiple of 16 takes one tensor-core product per 128
- * pixels; 0 keeps the dp4a kernel that serves the other channel counts). */
+ * pixels; 0 keeps the dp4a kernel that serves the other channel counts),
+ * "thin_pw" (1 default: a pointwise convolution of depth 32 with at most 128
+ * output channels, a multiple of 16, and at least 128 pixels per SM runs on
+ * the same thread-per-pixel kernel instead of the persistent GEMM, whose
+ * 128-pixel tiles are mostly hand-over at that depth; 2 adds depth 64, 3
+ * depth 128 -- both measured slower than the GEMM; 0 switches it off). */
 int mb_set_option(mb_context *ctx, const char *name, int value);
 
 /* ---- uint8 GEMM: replaces the gemmlowp calls of MatMulOp<RT_CPU,uint8_t>

@@ -419,13 +419,6 @@ __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q
   __shared__ int give_up;
   if (threadIdx.x == 0) give_up = 0;
   uint32_t phase = 0;
-  uint4 ahead[PLANES <= 4 ? PLANES : 1];
-  if constexpr (KD != 27 && PLANES <= 4) {
-    const int64_t first_pix = static_cast<int64_t>(blockIdx.x) * 128 + threadIdx.x;
-    const uint4 *row = reinterpret_cast<const uint4 *>(p.in + first_pix * KD);
-#pragma unroll
-    for (int j = 0; j < PLANES; ++j) ahead[j] = first_pix < npix ? __ldg(row + j) : make_uint4(0, 0, 0, 0);
-  }
   for (int64_t t = blockIdx.x; t < q.tiles; t += gridDim.x, phase ^= 1) {
     const int64_t pix = t * 128 + threadIdx.x;
     uint32_t sum_in = 0;
@@ -436,21 +429,6 @@ __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q
       for (int i = 0; i < 7; ++i) sum_in = __dp4a(patch[i], 0x01010101u, sum_in);
       *reinterpret_cast<uint4 *>(sm + threadIdx.x * 16) = make_uint4(patch[0], patch[1], patch[2], patch[3]);
       *reinterpret_cast<uint4 *>(sm + 2048 + threadIdx.x * 16) = make_uint4(patch[4], patch[5], patch[6], 0);
-    } else if constexpr (PLANES <= 4) {
-      // the pixel's own row; the row of this thread's pixel in the block's NEXT group is requested
-      // here, so that it travels while this group's product and epilogue run
-#pragma unroll
-      for (int j = 0; j < PLANES; ++j) {
-        sum_in = __dp4a(ahead[j].x, 0x01010101u, sum_in);
-        sum_in = __dp4a(ahead[j].y, 0x01010101u, sum_in);
-        sum_in = __dp4a(ahead[j].z, 0x01010101u, sum_in);
-        sum_in = __dp4a(ahead[j].w, 0x01010101u, sum_in);
-        *reinterpret_cast<uint4 *>(sm + j * 2048 + threadIdx.x * 16) = ahead[j];
-      }
-      const int64_t next_pix = pix + static_cast<int64_t>(gridDim.x) * 128;
-      const uint4 *row = reinterpret_cast<const uint4 *>(p.in + next_pix * KD);
-#pragma unroll
-      for (int j = 0; j < PLANES; ++j) ahead[j] = next_pix < npix ? __ldg(row + j) : make_uint4(0, 0, 0, 0);
     } else {
       // the pixel's own row, four 16-byte pieces at a time (all four requested before the first is used)
       const uint4 *row = reinterpret_cast<const uint4 *>(p.in + pix * KD);

@@ -277,7 +277,7 @@ def test_conv2d_u8_three_channel_stem_on_tensor_cores(ctx, orc, case):
 @pytest.mark.parametrize("case", [
     # N, H, W, C, O, zp_in, zp_out, bias
     (2, 112, 112, 32, 64, None, None, True),     # MobileNet's first pointwise layer (reduced batch)
-    (4, 56, 57, 64, 128, None, None, True),      # depth 64: two products per group of pixels
+    (6, 56, 57, 64, 128, None, None, True),      # depth 64: two products per group of pixels
     (3, 80, 80, 128, 128, None, None, True),     # depth 128
     (1, 150, 127, 32, 16, None, None, True),     # ragged last group, narrowest channel count
     (2, 100, 100, 64, 48, None, None, True),     # accumulator columns rounded up
