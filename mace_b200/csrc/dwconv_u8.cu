@@ -64,7 +64,7 @@ __device__ __forceinline__ uint32_t dw_requant(int32_t acc, const DwParams &p) {
 //   0..5   w1[kh][align] : x,y,z,w = channels; bytes = [w0,w1,w2,0] (align 0) / [0,w0,w1,w2]
 //   6..11  w2[kh][align]
 //   12     start[c] = bias[c] - zp_in * sum_t w[t][c]
-//   13     flags: x = group has a non-zero w2
+//   13     flags: x = group has a non-zero w2; y = bit kh set when filter row kh has one
 constexpr int DW_PACK_ITEMS = 14;
 #ifndef DW_THREADS
 #define DW_THREADS 256
@@ -91,6 +91,7 @@ dwconv3x3_prepack_kernel(const uint8_t *__restrict__ filter, const int32_t *__re
     for (int c = 0; c < 4; ++c) w[t][c] = static_cast<int32_t>((v >> (8 * c)) & 0xffu) - zp_f;
   }
   int32_t any_w2 = 0;
+  uint32_t rows_w2 = 0;
   uint32_t v1[3][2][4], v2[3][2][4];
   int32_t start[4];
 #pragma unroll
@@ -105,6 +106,7 @@ dwconv3x3_prepack_kernel(const uint8_t *__restrict__ filter, const int32_t *__re
         const int32_t a = min(127, max(-128, x)), b = x - a;
         sum += x;
         any_w2 |= b;
+        if (b != 0) rows_w2 |= 1u << kh;
         p1 |= (static_cast<uint32_t>(a) & 0xffu) << (8 * kw);
         p2 |= (static_cast<uint32_t>(b) & 0xffu) << (8 * kw);
       }
@@ -124,7 +126,7 @@ dwconv3x3_prepack_kernel(const uint8_t *__restrict__ filter, const int32_t *__re
           make_uint4(v2[kh][al][0], v2[kh][al][1], v2[kh][al][2], v2[kh][al][3]);
     }
   packed[12 * groups + g] = make_uint4(start[0], start[1], start[2], start[3]);
-  packed[13 * groups + g] = make_uint4(any_w2 != 0 ? 1u : 0u, 0u, 0u, 0u);
+  packed[13 * groups + g] = make_uint4(any_w2 != 0 ? 1u : 0u, rows_w2, 0u, 0u);
 }
 
 // Windows of one input row: win[j][c] holds, for channel c, the 4 horizontally adjacent
@@ -256,6 +258,7 @@ dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows
   const int32_t start[4] = {static_cast<int32_t>(st4.x), static_cast<int32_t>(st4.y),
                             static_cast<int32_t>(st4.z), static_cast<int32_t>(st4.w)};
   const bool has_w2 = flags.x != 0;
+  const uint32_t rows_w2 = flags.y;  // the filter rows that have a 9-bit tap (rare: most warps skip most rows)
   if (weights_cached) mb_grid_dep_wait();
 
   // columns: byte offsets inside a row and validity bits, fixed for the thread
@@ -290,9 +293,9 @@ dwconv3x3_u8_kernel(const DwParams p, const uint4 *__restrict__ packed, int rows
     dw_mac<STRIDE>(acc, r1, w1[1][0], w1[1][1]);
     dw_mac<STRIDE>(acc, r2, w1[2][0], w1[2][1]);
     if (has_w2) {
-      dw_mac<STRIDE>(acc, r0, __ldg(packed + 6 * groups + g), __ldg(packed + 7 * groups + g));
-      dw_mac<STRIDE>(acc, r1, __ldg(packed + 8 * groups + g), __ldg(packed + 9 * groups + g));
-      dw_mac<STRIDE>(acc, r2, __ldg(packed + 10 * groups + g), __ldg(packed + 11 * groups + g));
+      if (rows_w2 & 1u) dw_mac<STRIDE>(acc, r0, __ldg(packed + 6 * groups + g), __ldg(packed + 7 * groups + g));
+      if (rows_w2 & 2u) dw_mac<STRIDE>(acc, r1, __ldg(packed + 8 * groups + g), __ldg(packed + 9 * groups + g));
+      if (rows_w2 & 4u) dw_mac<STRIDE>(acc, r2, __ldg(packed + 10 * groups + g), __ldg(packed + 11 * groups + g));
     }
     uint32_t o = out_off + static_cast<uint32_t>(y) * out_row_stride;
 #pragma unroll
@@ -427,6 +430,7 @@ dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwPar
   const int32_t start[4] = {static_cast<int32_t>(st4.x), static_cast<int32_t>(st4.y),
                             static_cast<int32_t>(st4.z), static_cast<int32_t>(st4.w)};
   const bool has_w2 = flags.x != 0;
+  const uint32_t rows_w2 = flags.y;  // the filter rows that have a 9-bit tap (rare: most warps skip most rows)
   if (weights_cached) mb_grid_dep_wait();
   if (threadIdx.x == 0) {
     const int xi0 = ct * t.OWT * STRIDE - p.pad_left;
@@ -469,9 +473,9 @@ dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwPar
     dw_mac<STRIDE>(acc, r1, w1[1][0], w1[1][1]);
     dw_mac<STRIDE>(acc, r2, w1[2][0], w1[2][1]);
     if (has_w2) {
-      dw_mac<STRIDE>(acc, r0, __ldg(packed + 6 * groups + gg), __ldg(packed + 7 * groups + gg));
-      dw_mac<STRIDE>(acc, r1, __ldg(packed + 8 * groups + gg), __ldg(packed + 9 * groups + gg));
-      dw_mac<STRIDE>(acc, r2, __ldg(packed + 10 * groups + gg), __ldg(packed + 11 * groups + gg));
+      if (rows_w2 & 1u) dw_mac<STRIDE>(acc, r0, __ldg(packed + 6 * groups + gg), __ldg(packed + 7 * groups + gg));
+      if (rows_w2 & 2u) dw_mac<STRIDE>(acc, r1, __ldg(packed + 8 * groups + gg), __ldg(packed + 9 * groups + gg));
+      if (rows_w2 & 4u) dw_mac<STRIDE>(acc, r2, __ldg(packed + 10 * groups + gg), __ldg(packed + 11 * groups + gg));
     }
     uint32_t o = out_off + static_cast<uint32_t>(y) * out_row_stride;
 #pragma unroll

@@ -443,6 +443,37 @@ def test_dwconv_u8_3x3_variants(ctx, orc, stride, variant):
     assert len(np.unique(got)) > 4
 
 
+@pytest.mark.parametrize("stride", [1, 2])
+@pytest.mark.parametrize("zp_in", [0, 129])      # 0: rows through shared memory by TMA; else the register kernel
+@pytest.mark.parametrize("rows", [(0,), (1,), (2,), (0, 2), (0, 1, 2), ()])
+def test_dwconv_u8_nine_bit_taps_in_chosen_filter_rows(ctx, orc, stride, zp_in, rows):
+    """Weights beyond the signed 8-bit range take a second multiply pass, which runs per filter row
+    and only for the rows that hold such a tap: place them in chosen rows of a few channels."""
+    N, H, W, C = 2, 19, 22, 64
+    rng = np.random.Generator(np.random.PCG64(stride * 11 + zp_in + sum(rows) * 3 + len(rows)))
+    x = rng.integers(0, 256, size=(N, H, W, C), dtype=np.uint8)
+    zp_f, zp_out = 100, 0
+    f = rng.integers(0, 228, size=(3, 3, C, 1), dtype=np.uint8)   # f - 100 <= 127 everywhere
+    for i, kh in enumerate(rows):
+        for c in (3 + 8 * i, 17 + 4 * i, 40):                         # f - 100 = 140 .. 155 there
+            f[kh, int(rng.integers(0, 3)), c, 0] = int(rng.integers(240, 256))
+    bias = np.rint(rng.normal(0, 500, size=C)).astype(np.int32)
+    mult, shift = orc.output_multiplier_and_shift(np.float32(0.02), np.float32(0.01),
+                                                  np.float32(0.02 * 0.01 * 3 * 74 * 74 * 3 / 127))
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, 3, 3, (1, 1), (stride, stride), PAD["SAME"])
+    exp = orc.dwconv_u8(x, f, bias, (stride, stride), (1, 1), (ph >> 1, pw >> 1), (Ho, Wo), zp_in,
+                        zp_f, mult, shift, zp_out)
+    dx, df, db = ctx.upload(x), ctx.upload(f), ctx.upload(bias)
+    do = ctx.alloc(exp.size)
+    ctx.dwconv_u8(dx, df, db, do, N, H, W, C, 1, 3, 3, (stride, stride), (1, 1), (ph >> 1, pw >> 1),
+                  (Ho, Wo), zp_in, zp_f, mult, shift, zp_out)
+    got = ctx.download(do, exp.shape, np.uint8)
+    for b in (dx, df, db, do):
+        b.free()
+    assert np.array_equal(got, exp)
+    assert len(np.unique(got)) > 4
+
+
 @pytest.mark.parametrize("case", [
     # N, H, W, C, stride: the MobileNet layer shapes at a small batch ...
     (2, 112, 112, 32, 1), (2, 112, 112, 64, 2), (3, 56, 56, 128, 1), (2, 56, 56, 128, 2), (4, 28, 28, 256, 1),
