@@ -36,7 +36,19 @@ struct WinoParams {
   int N, C, H, W, O, pad_t, pad_l, Ho, Wo, th, tw;
   int act;
   float max_limit, coef;
+  // bytes from one transform position to the next in V and in M (below 2^32: the host checks)
+  uint32_t v_pos_bytes, m_pos_bytes;
 };
+
+// Element `pos` positions further on: one 32 x 32 -> 64-bit multiply-add per address.
+__device__ __forceinline__ float *at_pos(float *base, int pos, uint32_t pos_bytes) {
+  return reinterpret_cast<float *>(reinterpret_cast<char *>(base) +
+                                   static_cast<uint64_t>(static_cast<uint32_t>(pos)) * pos_bytes);
+}
+__device__ __forceinline__ const float *at_pos(const float *base, int pos, uint32_t pos_bytes) {
+  return reinterpret_cast<const float *>(reinterpret_cast<const char *>(base) +
+                                         static_cast<uint64_t>(static_cast<uint32_t>(pos)) * pos_bytes);
+}
 
 __device__ __forceinline__ float act_apply(float x, int act, float max_limit, float coef) {
   switch (act) {
@@ -151,17 +163,19 @@ __global__ void __launch_bounds__(256) wino_input_kernel(const WinoParams p) {
   const int h0 = (tile / p.tw) * TILE - p.pad_t, w0 = (tile % p.tw) * TILE - p.pad_l;
   const float *ip = p.in + (static_cast<int64_t>(n) * p.C + c) * p.H * p.W;
   float d[IN][IN];
+  // one address per patch row (the columns are constant offsets from it), the column tests made once
+  bool col_ok[IN];
+#pragma unroll
+  for (int j = 0; j < IN; ++j) col_ok[j] = static_cast<unsigned>(w0 + j) < static_cast<unsigned>(p.W);
 #pragma unroll
   for (int i = 0; i < IN; ++i) {
     const int h = h0 + i;
+    const bool row_ok = static_cast<unsigned>(h) < static_cast<unsigned>(p.H);
+    const float *rowp = ip + ((row_ok ? h : 0) * p.W + w0);
 #pragma unroll
-    for (int j = 0; j < IN; ++j) {
-      const int w = w0 + j;
-      d[i][j] = (h >= 0 && h < p.H && w >= 0 && w < p.W) ? __ldg(ip + h * p.W + w) : 0.f;
-    }
+    for (int j = 0; j < IN; ++j) d[i][j] = (row_ok && col_ok[j]) ? __ldg(rowp + j) : 0.f;
   }
   const int64_t ncols = static_cast<int64_t>(p.N) * tiles;
-  const int64_t tstride = static_cast<int64_t>(p.C) * ncols;
   float *op = p.V + static_cast<int64_t>(c) * ncols + static_cast<int64_t>(n) * tiles + tile;
   if (TILE == 2) {
     const float *x = &d[0][0];
@@ -183,7 +197,7 @@ __global__ void __launch_bounds__(256) wino_input_kernel(const WinoParams p) {
     s[14] = (x[6] - x[14]) - (x[5] - x[13]);
     s[15] = (x[5] - x[13]) - (x[7] - x[15]);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) op[i * tstride] = s[i];
+    for (int i = 0; i < 16; ++i) *at_pos(op, i, p.v_pos_bytes) = s[i];
   } else {
     float s[8][8];
 #pragma unroll
@@ -195,7 +209,7 @@ __global__ void __launch_bounds__(256) wino_input_kernel(const WinoParams p) {
       for (int j = 0; j < 8; ++j) col[j] = s[j][i];
       bt8(col, o);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) op[(j * 8 + i) * tstride] = o[j];
+      for (int j = 0; j < 8; ++j) *at_pos(op, j * 8 + i, p.v_pos_bytes) = o[j];
     }
   }
 }
@@ -214,7 +228,6 @@ __global__ void __launch_bounds__(256) wino_output_kernel(const WinoParams p) {
   const int m = static_cast<int>(r % p.O);
   const int n = static_cast<int>(r / p.O);
   const int64_t ncols = static_cast<int64_t>(p.N) * tiles;
-  const int64_t tstride = static_cast<int64_t>(p.O) * ncols;
   const float *ip = p.Mx + static_cast<int64_t>(m) * ncols + static_cast<int64_t>(n) * tiles + tile;
   const int h0 = (tile / p.tw) * TILE, w0 = (tile % p.tw) * TILE;
   float *op = p.out + (static_cast<int64_t>(n) * p.O + m) * p.Ho * p.Wo;
@@ -222,7 +235,7 @@ __global__ void __launch_bounds__(256) wino_output_kernel(const WinoParams p) {
   if (TILE == 2) {
     float d[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) d[i] = ip[i * tstride];
+    for (int i = 0; i < 16; ++i) d[i] = *at_pos(ip, i, p.m_pos_bytes);
     const float s0 = d[0] + d[1] + d[2], s1 = d[1] - d[2] - d[3];
     const float s2 = d[4] + d[5] + d[6], s3 = d[5] - d[6] - d[7];
     const float s4 = d[8] + d[9] + d[10], s5 = d[9] - d[10] - d[11];
@@ -243,7 +256,7 @@ __global__ void __launch_bounds__(256) wino_output_kernel(const WinoParams p) {
     for (int i = 0; i < 8; ++i) {
       float d[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) d[j] = ip[(i * 8 + j) * tstride];
+      for (int j = 0; j < 8; ++j) d[j] = *at_pos(ip, i * 8 + j, p.m_pos_bytes);
       at8(d, s[i]);
     }
 #pragma unroll
@@ -287,7 +300,6 @@ wino_output_plane_kernel(const WinoParams p, int threads_per_plane, int planes_p
   if (pl < planes_per_block && plane < planes && tile < tiles) {
     const int n = static_cast<int>(plane / p.O), m = static_cast<int>(plane - static_cast<int64_t>(n) * p.O);
     const int64_t ncols = static_cast<int64_t>(p.N) * tiles;
-    const int64_t tstride = static_cast<int64_t>(p.O) * ncols;
     const float *ip = p.Mx + static_cast<int64_t>(m) * ncols + static_cast<int64_t>(n) * tiles + tile;
     const int ty = tile / p.tw, tx = tile - ty * p.tw;
     const int h0 = ty * TILE, w0 = tx * TILE;
@@ -296,7 +308,7 @@ wino_output_plane_kernel(const WinoParams p, int threads_per_plane, int planes_p
     if (TILE == 2) {
       float d[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) d[i] = ip[i * tstride];
+      for (int i = 0; i < 16; ++i) d[i] = *at_pos(ip, i, p.m_pos_bytes);
       const float s0 = d[0] + d[1] + d[2], s1 = d[1] - d[2] - d[3];
       const float s2 = d[4] + d[5] + d[6], s3 = d[5] - d[6] - d[7];
       const float s4 = d[8] + d[9] + d[10], s5 = d[9] - d[10] - d[11];
@@ -317,7 +329,7 @@ wino_output_plane_kernel(const WinoParams p, int threads_per_plane, int planes_p
       for (int i = 0; i < 8; ++i) {
         float d[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) d[j] = ip[(i * 8 + j) * tstride];
+        for (int j = 0; j < 8; ++j) d[j] = *at_pos(ip, i * 8 + j, p.m_pos_bytes);
         at8(d, s[i]);
       }
 #pragma unroll
@@ -398,7 +410,7 @@ int mb_conv3x3_winograd_f32_nchw(mb_context *ctx, const float *in, const float *
   const int T = (tile + 2) * (tile + 2);
   const int64_t th = ceil_div64(Ho, tile), tw = ceil_div64(Wo, tile), tiles = th * tw;
   const int64_t ncols = N * tiles;
-  if (ncols >= (1ll << 31) || O * C >= (1ll << 31))
+  if (ncols >= (1ll << 31) || O * C >= (1ll << 31) || C * ncols >= (1ll << 30) || O * ncols >= (1ll << 30))
     return mb_fail(ctx, MB_UNSUPPORTED, "mb_conv3x3_winograd_f32_nchw: tensor too large");
   size_t off = 0;
   const size_t off_u = off; off += transformed_filter == nullptr ? align_up(sizeof(float) * T * O * C, 256) : 0;
@@ -421,6 +433,8 @@ int mb_conv3x3_winograd_f32_nchw(mb_context *ctx, const float *in, const float *
   p.Ho = static_cast<int>(Ho); p.Wo = static_cast<int>(Wo);
   p.th = static_cast<int>(th); p.tw = static_cast<int>(tw);
   p.act = activation; p.max_limit = max_limit; p.coef = coefficient;
+  p.v_pos_bytes = static_cast<uint32_t>(C * ncols * 4);
+  p.m_pos_bytes = static_cast<uint32_t>(O * ncols * 4);
   {
     const unsigned blocks = static_cast<unsigned>(ceil_div64(N * C * tiles, 256));
     // (all three kernels of the convolution are chained: each waits for its predecessor where it
