@@ -139,9 +139,10 @@ struct FTileIter {
 
 namespace {
 
-// PLAIN: no bias, no residual, no activation (the Winograd products, whose output transform
-// applies them): the accumulator is the result, and the epilogue is a copy.
-template <int BN, bool PLAIN = false>
+// EPI selects the epilogue's arithmetic: 1 = no bias, no residual, no activation (the Winograd
+// products, whose output transform applies them): the accumulator is the result; 2 = bias,
+// residual and a clamp (NOOP / RELU / RELUX); 0 = all of that plus the leaky term.
+template <int BN, int EPI = 0>
 __global__ void __launch_bounds__(F_THREADS, 1)
 gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
                    const __grid_constant__ CUtensorMap tmap_w,
@@ -492,9 +493,16 @@ gemm_f32_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
           for (int j = 0; j < 16; ++j) r_next[j] = __ldg(res + min(n0 + 16 + j, Ndim - 1) * p.c_row_stride);
         }
         float v[16];
-        if constexpr (PLAIN) {
+        if constexpr (EPI == 1) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[i & 1][j]);
+        } else if constexpr (EPI == 2) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float bj = __shfl_sync(0xffffffffu, b_cur, j);
+            const float x = (__uint_as_float(r[i & 1][j]) + bj) + r_cur[j];
+            v[j] = fminf(fmaxf(x, act_lo), act_hi);
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -576,15 +584,15 @@ int make_map_f32(mb_context *ctx, CUtensorMap *map, const void *base, uint64_t i
   return MB_SUCCESS;
 }
 
-template <int BN, bool PLAIN = false>
+template <int BN, int EPI = 0>
 int launch_f32(mb_context *ctx, const CUtensorMap &tx, const CUtensorMap &tw, const CUtensorMap &tc,
                F32TcParams &p, int cfg_bit) {
   using Cfg = F32Cfg<BN>;
-  auto kern = gemm_f32_tc_kernel<BN, PLAIN>;
-  uint64_t &mask = PLAIN ? ctx->func_attr_mask2 : ctx->func_attr_mask;
-  if (!(mask & (1ull << cfg_bit))) {
+  auto kern = gemm_f32_tc_kernel<BN, EPI>;
+  uint64_t &mask = EPI != 0 ? ctx->func_attr_mask2 : ctx->func_attr_mask;
+  if (!(mask & (1ull << (cfg_bit + 2 * EPI)))) {
     MB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-    mask |= (1ull << cfg_bit);
+    mask |= (1ull << (cfg_bit + 2 * EPI));
   }
   const int64_t total = p.batch * p.tiles_m * p.tiles_n;
   const int grid = static_cast<int>(total < ctx->num_sms ? total : ctx->num_sms);
@@ -647,8 +655,12 @@ int mb_gemm_f32_tc_launch(mb_context *ctx, const float *X, const float *W, const
     memset(&tc, 0, sizeof(tc));
   }
   if (bias == nullptr && residual == nullptr && act == 0) {
-    if (BN == 128) return launch_f32<128, true>(ctx, tx, tw, tc, p, 41);
-    return launch_f32<64, true>(ctx, tx, tw, tc, p, 42);
+    if (BN == 128) return launch_f32<128, 1>(ctx, tx, tw, tc, p, 41);
+    return launch_f32<64, 1>(ctx, tx, tw, tc, p, 42);
+  }
+  if (act != 6) {
+    if (BN == 128) return launch_f32<128, 2>(ctx, tx, tw, tc, p, 41);
+    return launch_f32<64, 2>(ctx, tx, tw, tc, p, 42);
   }
   if (BN == 128) return launch_f32<128>(ctx, tx, tw, tc, p, 41);
   return launch_f32<64>(ctx, tx, tw, tc, p, 42);
