@@ -166,7 +166,10 @@ int mb_pair_clusters(const mb_context *ctx);
  * output channels, a multiple of 16, and at least 128 pixels per SM runs on
  * the same thread-per-pixel kernel instead of the persistent GEMM, whose
  * 128-pixel tiles are mostly hand-over at that depth; 2 adds depth 64, 3
- * depth 128 -- both measured slower than the GEMM; 0 switches it off). */
+ * depth 128 -- both measured slower than the GEMM; 0 switches it off),
+ * "dw_fixed_groups" (1 default: the TMA-fed 3x3 depthwise kernel takes a
+ * variant that knows the number of channel groups per CTA at compile time;
+ * 0 keeps the generic one, for A/B tests). */
 int mb_set_option(mb_context *ctx, const char *name, int value);
 
 /* ---- uint8 GEMM: replaces the gemmlowp calls of MatMulOp<RT_CPU,uint8_t>

@@ -439,6 +439,8 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
     ctx->stem_tc = value;
   } else if (strcmp(name, "thin_pw") == 0) {
     ctx->thin_pw = value;
+  } else if (strcmp(name, "dw_fixed_groups") == 0) {
+    ctx->dw_fixed_groups = value;
   } else if (strcmp(name, "pair") == 0) {
     ctx->pair_gemm = value;
   } else if (strcmp(name, "runs_min_m") == 0) {

@@ -386,7 +386,9 @@ struct DwTmaTile {
 };
 constexpr long long DW_WAIT_BUDGET = 1ll << 31;
 
-template <int STRIDE, int VAR>
+// GT: the number of channel groups per CTA when it is fixed at compile time (8, 16, 32, 64: the
+// pixel words of a row are then read at constant offsets from one address), 0 = from the tile.
+template <int STRIDE, int VAR, int GT = 0>
 __global__ void __launch_bounds__(DW_THREADS, DW_BLOCKS_PER_SM)
 dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwParams p,
                         const uint4 *__restrict__ packed, const DwTmaTile t, int weights_cached) {
@@ -414,9 +416,10 @@ dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwPar
     sm100::fence_barrier_init();
   }
   __syncthreads();
-  const int g = threadIdx.x % t.G, strip = threadIdx.x / t.G;
+  const int G = GT != 0 ? GT : t.G;
+  const int g = threadIdx.x % G, strip = threadIdx.x / G;
   const int groups = p.C >> 2;
-  const int gg = cc * t.G + g;  // channel group in the tensor
+  const int gg = cc * G + g;  // channel group in the tensor
   if (!weights_cached) mb_grid_dep_wait();
   uint4 w1[3][2];
 #pragma unroll
@@ -449,7 +452,7 @@ dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwPar
   uint8_t *__restrict__ out = p.out;
   const uint32_t *sm32 = reinterpret_cast<const uint32_t *>(dw_smem);
   const int row_words = t.row_pitch >> 2;
-  const int thread_word = strip * 4 * STRIDE * t.G + g;  // this thread's first pixel word inside a row
+  const int thread_word = strip * 4 * STRIDE * G + g;  // this thread's first pixel word inside a row
   bool ok = true;
 
   // the pixel words of input row r of the run (r = 0 is input row hi0), once they have landed
@@ -461,7 +464,7 @@ dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwPar
     }
     const uint32_t *w = sm32 + r * row_words + thread_word;
 #pragma unroll
-    for (int j = 0; j < COLS; ++j) raw.q[j] = w[j * t.G];
+    for (int j = 0; j < COLS; ++j) raw.q[j] = w[j * G];
   };
   auto emit = [&](int y, const DwRow<STRIDE> &r0, const DwRow<STRIDE> &r1, const DwRow<STRIDE> &r2) {
     int32_t acc[4][4];
@@ -698,10 +701,10 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
           if (r != CUDA_SUCCESS)
             return mb_fail(ctx, MB_RUNTIME_ERROR, "cuTensorMapEncodeTiled (depthwise input) failed (%d)", static_cast<int>(r));
           const int var = mb_requant_variant(right_shift, zp_out);
-#define MB_DW_TMA_LAUNCH(S, V)                                                                              \
+#define MB_DW_TMA_LAUNCH_G(S, V, GT, SLOT)                                                                   \
   do {                                                                                                      \
-    auto kern = dwconv3x3_u8_tma_kernel<S, V>;                                                              \
-    const uint64_t bit = 1ull << ((S - 1) * 6 + V);                                                         \
+    auto kern = dwconv3x3_u8_tma_kernel<S, V, GT>;                                                          \
+    const uint64_t bit = 1ull << (SLOT);                                                                    \
     if (!(ctx->dw_attr_mask & bit)) {                                                                       \
       MB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 101 * 1024));    \
       ctx->dw_attr_mask |= bit;                                                                             \
@@ -709,6 +712,25 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
     MB_CUDA(ctx, mb_launch_chained(ctx, kern, dim3(static_cast<unsigned>(grid64)), dim3(DW_THREADS), smem,  \
                                    tmap, p, packed, t, weights_cached));                                    \
   } while (0)
+#define MB_DW_TMA_LAUNCH(S, V) MB_DW_TMA_LAUNCH_G(S, V, 0, (S - 1) * 6 + V)
+          // the packed requantization forms (what a network's layers use) with the usual group counts
+          // get kernels that know the count; slots 12.. of the attribute mask
+          const int gslot = t.G == 8 ? 0 : t.G == 16 ? 1 : t.G == 32 ? 2 : t.G == 64 ? 3 : -1;
+          if (gslot >= 0 && (var == 4 || var == 5) && ctx->dw_fixed_groups) {
+            const int slot = 12 + ((stride_h - 1) * 2 + (var - 4)) * 4 + gslot;
+#define MB_DW_G4(S, V)                                                  \
+  switch (gslot) {                                                      \
+    case 0: MB_DW_TMA_LAUNCH_G(S, V, 8, slot); break;                   \
+    case 1: MB_DW_TMA_LAUNCH_G(S, V, 16, slot); break;                  \
+    case 2: MB_DW_TMA_LAUNCH_G(S, V, 32, slot); break;                  \
+    default: MB_DW_TMA_LAUNCH_G(S, V, 64, slot); break;                 \
+  }
+            if (stride_h == 1 && var == 5) { MB_DW_G4(1, 5) }
+            else if (stride_h == 1) { MB_DW_G4(1, 4) }
+            else if (var == 5) { MB_DW_G4(2, 5) }
+            else { MB_DW_G4(2, 4) }
+#undef MB_DW_G4
+          } else
           if (stride_h == 1) {
             switch (var) {
               case 5: MB_DW_TMA_LAUNCH(1, 5); break;
@@ -729,6 +751,7 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
             }
           }
 #undef MB_DW_TMA_LAUNCH
+#undef MB_DW_TMA_LAUNCH_G
           MB_CUDA(ctx, cudaGetLastError());
           ctx->launches++;
           return MB_SUCCESS;
