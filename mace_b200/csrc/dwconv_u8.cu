@@ -674,7 +674,7 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
         int rows_out = std::max(1, (max_rows_in - 3) / stride_h + 1);
         rows_out = static_cast<int>(std::min<int64_t>(rows_out, Ho));
         const int64_t per_seg = N * t.col_tiles * t.chan_chunks;
-        while (rows_out > 2 && per_seg * ceil_div64(Ho, rows_out) < 2ll * ctx->num_sms) rows_out = (rows_out + 1) / 2;
+        while (rows_out > 2 && per_seg * ceil_div64(Ho, rows_out) < static_cast<int64_t>(ctx->dw_tma_fill) * ctx->num_sms / 4) rows_out = (rows_out + 1) / 2;
         t.rows_out = rows_out;
         t.segments = static_cast<int>(ceil_div64(Ho, rows_out));
         const int rows_in = (rows_out - 1) * stride_h + 3;
