@@ -169,7 +169,12 @@ int mb_pair_clusters(const mb_context *ctx);
  * depth 128 -- both measured slower than the GEMM; 0 switches it off),
  * "dw_fixed_groups" (1 default: the TMA-fed 3x3 depthwise kernel takes a
  * variant that knows the number of channel groups per CTA at compile time;
- * 0 keeps the generic one, for A/B tests). */
+ * 0 keeps the generic one, for A/B tests),
+ * "dw_tma_fill" (4 default: that kernel's row runs are halved until the grid
+ * has this many quarter-CTAs per SM, i.e. one CTA per SM; 8 = two per SM was
+ * the earlier rule and 2.4 % slower on MobileNet-v1),
+ * "stem_grid" (1 default: the thread-per-pixel convolution kernels launch
+ * this many times the blocks that are resident at once). */
 int mb_set_option(mb_context *ctx, const char *name, int value);
 
 /* ---- uint8 GEMM: replaces the gemmlowp calls of MatMulOp<RT_CPU,uint8_t>

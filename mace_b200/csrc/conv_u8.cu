@@ -559,7 +559,9 @@ static int launch(mb_context *ctx, const ConvParams &p, int kd, int64_t pixels) 
   const size_t smem = std::max<size_t>(128 + static_cast<size_t>(kpad / 16) * 2048 + static_cast<size_t>(q.n_cols) * kpad +
                                            align_up(static_cast<size_t>(p.O) * 4, 128) + 64,
                                        static_cast<size_t>(208 * 1024) / per_sm);
-  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(q.tiles, static_cast<int64_t>(ctx->num_sms) * per_sm));
+  // blocks: registers let eight be resident per SM; stem_grid = 1 launches exactly those, 2 twice as many
+  const int resident = std::min(per_sm, 8);
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(q.tiles, static_cast<int64_t>(ctx->num_sms) * resident * ctx->stem_grid));
   switch (kd) {
     case 27: return launch_kd<27>(ctx, q, grid, smem, 0);
     case 32: return launch_kd<32>(ctx, q, grid, smem, 3);
