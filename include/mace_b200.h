@@ -173,6 +173,8 @@ int mb_pair_clusters(const mb_context *ctx);
  * "dw_tma_fill" (4 default: that kernel's row runs are halved until the grid
  * has this many quarter-CTAs per SM, i.e. one CTA per SM; 8 = two per SM was
  * the earlier rule and 2.4 % slower on MobileNet-v1),
+ * "dw_lane_setup" (1 default: a lane per input row requests that kernel's
+ * row copies; 0: one thread does, for A/B tests),
  * "stem_grid" (1 default: the thread-per-pixel convolution kernels launch
  * this many times the blocks that are resident at once). */
 int mb_set_option(mb_context *ctx, const char *name, int value);

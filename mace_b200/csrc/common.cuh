@@ -65,6 +65,7 @@ struct mb_context {
   int stem_tc = 1;               // 3x3x3 first-layer convolution: the products on the tensor core
   int dw_tma_fill = 4;           // TMA-fed depthwise: row runs are halved until the grid has this many quarter-CTAs per SM
   int stem_grid = 1;             // thread-per-pixel convolution kernels: grid in multiples of the resident blocks
+  int dw_lane_setup = 1;         // TMA-fed depthwise: a lane per input row requests the copies (0: one thread, for A/B)
   int dw_fixed_groups = 1;       // TMA-fed depthwise kernels specialised on the channel groups per CTA (0: generic, for A/B)
   int thin_pw = 1;               // pointwise layers of depth 32 / 64 (2: also 128) on the same thread-per-pixel kernel
   int pair_gemm = 0;             // large GEMMs on CTA pairs (clusters of two sharing each tile's B): 1 where

@@ -382,6 +382,7 @@ struct DwTmaTile {
   int rows_out;       // output rows per CTA
   int col_tiles, chan_chunks, segments;
   int ring_bytes;     // shared memory for the rows (then one mbarrier per row)
+  int setup_lanes;    // threads that share the per-row set-up (barrier, copy request): 32, or 1
   int *status;
 };
 constexpr long long DW_WAIT_BUDGET = 1ll << 31;
@@ -409,10 +410,14 @@ dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwPar
   const int hi0 = y0 * STRIDE - p.pad_top;           // first input row of the run
   const int rows_in = (y1 - y0 - 1) * STRIDE + 3;
   const int row_bytes = t.TWB * t.CB;
-  if (threadIdx.x == 0) {
-    sm100::prefetch_tensormap(&tmap_in);
-    for (int r = 0; r < rows_in; ++r) sm100::mbar_init(sm100::smem_u32(bars + r), 1);
-    abort_flag = 0;
+  // (the first warp shares the per-row set-up: a lane per input row)
+  if (threadIdx.x < 32) {
+    if (threadIdx.x == 0) {
+      sm100::prefetch_tensormap(&tmap_in);
+      abort_flag = 0;
+    }
+    if (threadIdx.x < t.setup_lanes)
+      for (int r = threadIdx.x; r < rows_in; r += t.setup_lanes) sm100::mbar_init(sm100::smem_u32(bars + r), 1);
     sm100::fence_barrier_init();
   }
   __syncthreads();
@@ -435,9 +440,9 @@ dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwPar
   const bool has_w2 = flags.x != 0;
   const uint32_t rows_w2 = flags.y;  // the filter rows that have a 9-bit tap (rare: most warps skip most rows)
   if (weights_cached) mb_grid_dep_wait();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < t.setup_lanes) {
     const int xi0 = ct * t.OWT * STRIDE - p.pad_left;
-    for (int r = 0; r < rows_in; ++r) {
+    for (int r = threadIdx.x; r < rows_in; r += t.setup_lanes) {
       const uint32_t bar = sm100::smem_u32(bars + r);
       sm100::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(row_bytes));
       sm100::tma_load_4d(sm100::smem_u32(dw_smem + r * t.row_pitch), &tmap_in, bar, cc * t.CB, xi0, hi0 + r, n);
@@ -680,6 +685,7 @@ static int dwconv_u8_impl(mb_context *ctx, const uint8_t *in, const uint8_t *fil
         const int rows_in = (rows_out - 1) * stride_h + 3;
         t.ring_bytes = rows_in * t.row_pitch;
         t.status = ctx->dev_status;
+        t.setup_lanes = ctx->dw_lane_setup ? 32 : 1;
         const size_t smem = static_cast<size_t>(t.ring_bytes) + sizeof(uint64_t) * rows_in + 128 /* alignment */;
         const int64_t grid64 = per_seg * t.segments;
         if (smem <= 100 * 1024 && grid64 < (1ll << 31) && row_bytes % 16 == 0) {
