@@ -324,6 +324,17 @@ def test_conv2d_u8_pointwise_with_short_depth(ctx, orc, case):
     assert len(np.unique(exp)) > 4
 
 
+def test_conv2d_u8_thread_per_pixel_grid_multiples(ctx, orc):
+    """More blocks than are resident at once (option stem_grid) change no byte."""
+    try:
+        for g in (2, 3):
+            ctx.set_option("stem_grid", g)
+            _conv_case(ctx, orc, 2, 224, 224, 3, 32, 3, 3, 2, "SAME")
+            _conv_case(ctx, orc, 2, 112, 112, 32, 64, 1, 1, 1, "VALID")
+    finally:
+        ctx.set_option("stem_grid", 1)
+
+
 def test_conv2d_u8_three_channel_input_off_the_word_grid(ctx, orc):
     """The word-wise window loads of the 3x3x3 kernels need a 4-byte aligned input; any other input
     address takes the byte-wise gather and must give the same bytes."""
@@ -470,6 +481,40 @@ def test_dwconv_u8_nine_bit_taps_in_chosen_filter_rows(ctx, orc, stride, zp_in, 
     got = ctx.download(do, exp.shape, np.uint8)
     for b in (dx, df, db, do):
         b.free()
+    assert np.array_equal(got, exp)
+    assert len(np.unique(got)) > 4
+
+
+@pytest.mark.parametrize("option,value", [("dw_fixed_groups", 0), ("dw_tma_fill", 8), ("dw_tma_fill", 1),
+                                          ("dw_lane_setup", 0), ("dw_tma", 0)])
+@pytest.mark.parametrize("shape", [(3, 14, 14, 512, 1), (2, 28, 28, 256, 2), (2, 56, 56, 64, 1)])
+def test_dwconv_u8_launch_variants(ctx, orc, option, value, shape):
+    """The switches that pick the depthwise kernel variant and its launch geometry (generic instead of
+    fixed channel-group count, other grid fill rules, one thread instead of a lane per row for the
+    copy requests, the register kernel) change no byte of the result."""
+    N, H, W, C, stride = shape
+    defaults = {"dw_fixed_groups": 1, "dw_tma_fill": 4, "dw_lane_setup": 1, "dw_tma": 1}
+    rng = np.random.Generator(np.random.PCG64(H * 7 + C + stride))
+    x = rng.integers(0, 256, size=(N, H, W, C), dtype=np.uint8)
+    f = rng.integers(0, 256, size=(3, 3, C, 1), dtype=np.uint8)
+    bias = np.rint(rng.normal(0, 500, size=C)).astype(np.int32)
+    zp_in, zp_f, zp_out = 0, 121, 0
+    mult, shift = orc.output_multiplier_and_shift(np.float32(0.02), np.float32(0.01),
+                                                  np.float32(0.02 * 0.01 * 3 * 74 * 74 * 3 / 127))
+    Ho, Wo, ph, pw = orc.calc_padding_and_output_size(H, W, 3, 3, (1, 1), (stride, stride), PAD["SAME"])
+    exp = orc.dwconv_u8(x, f, bias, (stride, stride), (1, 1), (ph >> 1, pw >> 1), (Ho, Wo), zp_in,
+                        zp_f, mult, shift, zp_out)
+    dx, df, db = ctx.upload(x), ctx.upload(f), ctx.upload(bias)
+    do = ctx.alloc(exp.size)
+    try:
+        ctx.set_option(option, value)
+        ctx.dwconv_u8(dx, df, db, do, N, H, W, C, 1, 3, 3, (stride, stride), (1, 1), (ph >> 1, pw >> 1),
+                      (Ho, Wo), zp_in, zp_f, mult, shift, zp_out)
+        got = ctx.download(do, exp.shape, np.uint8)
+    finally:
+        ctx.set_option(option, defaults[option])
+        for b in (dx, df, db, do):
+            b.free()
     assert np.array_equal(got, exp)
     assert len(np.unique(got)) > 4
 
