@@ -6,10 +6,13 @@
 // int32 bias and the fixed-point output pipeline.  Padding with the zero point
 // contributes (zp - zp) * w = 0, i.e. exactly the sum over in-bounds taps.
 //
-// Three routes:
+// Routes:
 //   1x1 stride 1      -> the NHWC tensor already is the [pixels x C] K-major
-//                        GEMM operand; no copy (conv_2d.cc:279-281)
-//   3x3 on 3 channels -> packed-patch dp4a kernel (MobileNet's 3x3x3 stem)
+//                        GEMM operand; no copy (conv_2d.cc:279-281); depth 32
+//                        on many pixels: the thread-per-pixel kernel below
+//   3x3 on 3 channels -> thread-per-pixel tensor-core kernel (namespace stem:
+//                        MobileNet's 3x3x3 first layer), or the packed-patch
+//                        dp4a kernel when the channel count is no multiple of 16
 //   small depth * O   -> direct kernel, one thread per output pixel, the whole
 //                        filter in shared memory
 //   everything else   -> patch gather into scratch (rows padded to 16 bytes)
