@@ -437,8 +437,10 @@ dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwPar
   const uint4 flags = __ldg(packed + 13 * groups + gg);
   const int32_t start[4] = {static_cast<int32_t>(st4.x), static_cast<int32_t>(st4.y),
                             static_cast<int32_t>(st4.z), static_cast<int32_t>(st4.w)};
-  const bool has_w2 = flags.x != 0;
-  const uint32_t rows_w2 = flags.y;  // the filter rows that have a 9-bit tap (rare: most warps skip most rows)
+  // the filter rows that have a 9-bit tap in ANY lane's channel group (rare: most warps skip most
+  // rows); the same for all lanes, so that the tests below do not diverge -- groups without such a
+  // tap hold zeros in those weight words
+  const uint32_t rows_w2 = __reduce_or_sync(0xffffffffu, flags.x != 0 ? flags.y : 0u);
   if (weights_cached) mb_grid_dep_wait();
   if (threadIdx.x < t.setup_lanes) {
     const int xi0 = ct * t.OWT * STRIDE - p.pad_left;
@@ -480,11 +482,9 @@ dwconv3x3_u8_tma_kernel(const __grid_constant__ CUtensorMap tmap_in, const DwPar
     dw_mac<STRIDE>(acc, r0, w1[0][0], w1[0][1]);
     dw_mac<STRIDE>(acc, r1, w1[1][0], w1[1][1]);
     dw_mac<STRIDE>(acc, r2, w1[2][0], w1[2][1]);
-    if (has_w2) {
-      if (rows_w2 & 1u) dw_mac<STRIDE>(acc, r0, __ldg(packed + 6 * groups + gg), __ldg(packed + 7 * groups + gg));
-      if (rows_w2 & 2u) dw_mac<STRIDE>(acc, r1, __ldg(packed + 8 * groups + gg), __ldg(packed + 9 * groups + gg));
-      if (rows_w2 & 4u) dw_mac<STRIDE>(acc, r2, __ldg(packed + 10 * groups + gg), __ldg(packed + 11 * groups + gg));
-    }
+    if (rows_w2 & 1u) dw_mac<STRIDE>(acc, r0, __ldg(packed + 6 * groups + gg), __ldg(packed + 7 * groups + gg));
+    if (rows_w2 & 2u) dw_mac<STRIDE>(acc, r1, __ldg(packed + 8 * groups + gg), __ldg(packed + 9 * groups + gg));
+    if (rows_w2 & 4u) dw_mac<STRIDE>(acc, r2, __ldg(packed + 10 * groups + gg), __ldg(packed + 11 * groups + gg));
     uint32_t o = out_off + static_cast<uint32_t>(y) * out_row_stride;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
