@@ -201,25 +201,6 @@ struct TileIter {
   }
 };
 
-// 32 rows x 16 bytes held one row per lane (w0..w3) -> global memory, written along the rows:
-// through the warp's staging rows, so that a store instruction writes the 16 bytes of two rows
-// instead of one byte of each of 32 rows.  Out of line: it serves the rare outputs whose row pitch
-// TMA cannot address, and its registers should not weigh on the tile loop.
-__device__ __noinline__ void store_chunk_along_rows(uint8_t *stage, int lane, uint32_t w0, uint32_t w1, uint32_t w2,
-                                                    uint32_t w3, uint8_t *dst, int64_t pitch, int rows, int cols) {
-  __syncwarp();
-  reinterpret_cast<uint4 *>(stage)[lane] = make_uint4(w0, w1, w2, w3);
-  __syncwarp();
-  const int col = lane & 15;
-  if (col >= cols) return;
-  uint8_t *d = dst + col;
-#pragma unroll 4
-  for (int k = 0; k < 16; ++k) {
-    const int rr = 2 * k + (lane >> 4);
-    if (rr < rows) d[static_cast<int64_t>(rr) * pitch] = stage[rr * 16 + col];
-  }
-}
-
 // Requantizes one 16-column chunk of an accumulator row and packs it into four words.
 // MODE: 0..3 = mb_requant_t<ZP0 = bit 0, SGE1 = bit 1>; 4 / 5 = packed saturating form
 // (zero point != 0 / == 0); 8 = the Gemv delegators' float rule.
@@ -787,9 +768,10 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (i + 1 < CHUNKS_PER_WARP) tmem_ld_32x32b_x16(tbase + (i + 1) * CHUNK, r[0]);
           const int64_t n0 = n_first + i * CHUNK;
           const int32_t *ct = ct_base + i * CHUNK;
-          if (!p.out_is_int32 && n0 < p.N) {
-            // uint8 rows that TMA cannot address (a row pitch that is no multiple of 16 bytes, e.g.
-            // the 1000 or 1001 logits of a classifier): requantize without a branch per value ...
+          if (words_ok && n0 + CHUNK <= p.N) {
+            // a whole chunk of a uint8 row whose words are 4-byte aligned (N % 4 == 0, e.g. the
+            // 1000 logits of a classifier, which TMA cannot address): requantize without a
+            // branch per value and store four words instead of sixteen bytes
             uint32_t packed[CHUNK / 4];
             const int4 *ct4 = reinterpret_cast<const int4 *>(ct);
             switch (p.rq_variant) {
@@ -801,21 +783,10 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
               case 1: requant_chunk<1>(v, row_term, ct4, p, packed); break;
               default: requant_chunk<0>(v, row_term, ct4, p, packed); break;
             }
-            if (words_ok && n0 + CHUNK <= p.N) {
-              // ... and store four aligned words (N % 4 == 0)
-              if (row_ok) {
-                uint32_t *cw = reinterpret_cast<uint32_t *>(c8 + n0);
+            if (row_ok) {
+              uint32_t *cw = reinterpret_cast<uint32_t *>(c8 + n0);
 #pragma unroll
-                for (int q = 0; q < CHUNK / 4; ++q) cw[q] = packed[q];
-              }
-            } else {
-              // ... or bytes, but along the rows: a lane's 16 bytes go through the warp's staging
-              // rows, and each store instruction then writes the 16 bytes of two rows (two sectors)
-              // instead of one byte of each of 32 rows (32 sectors)
-              store_chunk_along_rows(stage_ptr, lane, packed[0], packed[1], packed[2], packed[3],
-                                     static_cast<uint8_t *>(p.C) + (static_cast<int64_t>(b) * p.M + m0) * p.N + n0,
-                                     p.N, static_cast<int>(min(static_cast<int64_t>(32), p.M - m0)),
-                                     static_cast<int>(min(static_cast<int64_t>(16), p.N - n0)));
+              for (int q = 0; q < CHUNK / 4; ++q) cw[q] = packed[q];
             }
           } else if (quads_ok && n0 + CHUNK <= p.N) {
             // a whole chunk of an int32 row: four 16-byte stores instead of sixteen words
