@@ -175,6 +175,11 @@ int mb_pair_clusters(const mb_context *ctx);
  * the earlier rule and 2.4 % slower on MobileNet-v1),
  * "dw_lane_setup" (1 default: a lane per input row requests that kernel's
  * row copies; 0: one thread does, for A/B tests),
+ * "conv_filter_const" (0 default; 1 promises that filter and bias of the
+ * following mb_conv2d_u8_nhwc calls are not written by work enqueued ahead
+ * of them -- weights, the reference's Tensor::is_weight() -- so the
+ * thread-per-pixel kernels read them before they wait for the kernel in
+ * front; the Conv2d delegator sets it per call),
  * "stem_grid" (1 default: the thread-per-pixel convolution kernels launch
  * this many times the blocks that are resident at once). */
 int mb_set_option(mb_context *ctx, const char *name, int value);

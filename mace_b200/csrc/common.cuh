@@ -64,6 +64,7 @@ struct mb_context {
   int max_pair_clusters = 0;     // co-resident clusters of the pair GEMM (0: not asked yet)
   int stem_tc = 1;               // 3x3x3 first-layer convolution: the products on the tensor core
   int dw_tma_fill = 4;           // TMA-fed depthwise: row runs are halved until the grid has this many quarter-CTAs per SM
+  int conv_filter_const = 0;     // promise: filter and bias of the following mb_conv2d_u8_nhwc calls are weights
   int stem_grid = 1;             // thread-per-pixel convolution kernels: grid in multiples of the resident blocks
   int dw_lane_setup = 1;         // TMA-fed depthwise: a lane per input row requests the copies (0: one thread, for A/B)
   int dw_fixed_groups = 1;       // TMA-fed depthwise kernels specialised on the channel groups per CTA (0: generic, for A/B)

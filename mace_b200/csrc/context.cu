@@ -443,6 +443,8 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
     ctx->dw_fixed_groups = value;
   } else if (strcmp(name, "dw_lane_setup") == 0) {
     ctx->dw_lane_setup = value;
+  } else if (strcmp(name, "conv_filter_const") == 0) {
+    ctx->conv_filter_const = value;
   } else if (strcmp(name, "stem_grid") == 0) {
     if (value < 1 || value > 16) return mb_fail(ctx, MB_INVALID_ARGS, "stem_grid: 1..16");
     ctx->stem_grid = value;

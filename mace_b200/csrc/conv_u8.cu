@@ -341,6 +341,7 @@ struct Params {
   int acc_cols;   // tensor-memory columns of the block (power of two >= n_cols, at least 32)
   int64_t tiles;  // groups of 128 pixels
   int *status;
+  int filter_const;  // filter and bias are not written by work enqueued ahead (weights): read them before the wait
 };
 
 // KD: 27 = the 3x3x3 window (gathered, zero tail up to 32); 32 / 64 / 128 = a pointwise layer
@@ -371,7 +372,7 @@ __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q
     tmem_alloc(smem_u32(tmem_slot), static_cast<uint32_t>(q.acc_cols));
     tmem_relinquish();
   }
-  mb_grid_dep_wait();
+  if (!q.filter_const) mb_grid_dep_wait();
   // B: row o = the filter row (KD bytes, zero tail); byte k of row n lives at [k / 16][n][k % 16].
   const bool filter_words = KD != 27 && (reinterpret_cast<uintptr_t>(p.filter) & 15u) == 0;
   for (int i = threadIdx.x; i < q.n_cols * PLANES; i += 128) {
@@ -409,6 +410,7 @@ __global__ void __launch_bounds__(128, 8) conv_u8_stem_mma_kernel(const Params q
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  if (q.filter_const) mb_grid_dep_wait();  // the pixels come from the kernel in front
   const uint32_t tmem_base = *tmem_slot;
   const int64_t npix = static_cast<int64_t>(p.N) * p.Ho * p.Wo;
   const uint32_t idesc = make_idesc(/*c s32*/ 2, /*a u8*/ 0, /*b u8*/ 0, false, false, 128, static_cast<uint32_t>(q.n_cols));
@@ -555,6 +557,7 @@ static int launch(mb_context *ctx, const ConvParams &p, int kd, int64_t pixels) 
   q.acc_cols = q.n_cols <= 32 ? 32 : q.n_cols <= 64 ? 64 : q.n_cols <= 128 ? 128 : 256;
   q.tiles = ceil_div64(pixels, 128);
   q.status = ctx->dev_status;
+  q.filter_const = ctx->conv_filter_const;
   const int kpad = kd == 27 ? 32 : kd;
   const int per_sm = 512 / q.acc_cols;
   // (the request is padded so that no more blocks fit an SM than its tensor memory serves: a

@@ -194,6 +194,10 @@ class Conv2d : public delegator::Conv2d {
     // Pipeline::Make(bias, channels, filter scale, input scale, output scale, zp)
     MACE_RETURN_IF_ERROR(GetOutputMultiplierAndShift(filter->scale(), input->scale(),
                                                      output->scale(), &multiplier, &right_shift));
+    // weights (Tensor::is_weight(), mace/core/tensor.h) are not written by the work enqueued ahead of
+    // this call, so a kernel may read them while its predecessor still runs
+    mb_set_option(rt->ctx(), "conv_filter_const",
+                  filter->is_weight() && (bias_ == nullptr || bias_->is_weight()) ? 1 : 0);
     return rt->Status(mb_conv2d_u8_nhwc(
         rt->ctx(), input->memory<uint8_t>(), filter->memory<uint8_t>(), bias_data,
         output->mutable_memory<uint8_t>(), input->dim(0), input->dim(1), input->dim(2),

@@ -335,6 +335,33 @@ def test_conv2d_u8_thread_per_pixel_grid_multiples(ctx, orc):
         ctx.set_option("stem_grid", 1)
 
 
+def test_conv2d_u8_weights_read_before_the_wait(ctx, orc):
+    """With the filter declared constant the thread-per-pixel kernels fetch it before they wait for
+    the kernel in front; a chain of such convolutions (each reads the previous one's output) must
+    still equal the oracle."""
+    rng = np.random.Generator(np.random.PCG64(5))
+    N, H, W = 2, 112, 112
+    x, f1, zp_in, zp_f1, mult1, shift1 = conv_quant(orc, rng, (N, H, W, 32), (32, 1, 1, 32), 32)
+    f2 = rng.integers(0, 256, size=(64, 1, 1, 32), dtype=np.uint8)
+    y1 = orc.conv2d_u8(x, f1, None, (1, 1), (0, 0), (H, W), zp_in, zp_f1, mult1, shift1, 0)
+    y2 = orc.conv2d_u8(y1, f2, None, (1, 1), (0, 0), (H, W), 0, 119, mult1, shift1, 3)
+    dx, d1, d2 = ctx.upload(x), ctx.upload(f1), ctx.upload(f2)
+    o1, o2 = ctx.alloc(y1.size), ctx.alloc(y2.size)
+    try:
+        ctx.set_option("conv_filter_const", 1)
+        for _ in range(3):
+            ctx.conv2d_u8(dx, d1, None, o1, N, H, W, 32, 32, 1, 1, (1, 1), (0, 0), (H, W), zp_in, zp_f1,
+                          mult1, shift1, 0)
+            ctx.conv2d_u8(o1, d2, None, o2, N, H, W, 32, 64, 1, 1, (1, 1), (0, 0), (H, W), 0, 119,
+                          mult1, shift1, 3)
+        assert np.array_equal(ctx.download(o1, y1.shape, np.uint8), y1)
+        assert np.array_equal(ctx.download(o2, y2.shape, np.uint8), y2)
+    finally:
+        ctx.set_option("conv_filter_const", 0)
+        for b in (dx, d1, d2, o1, o2):
+            b.free()
+
+
 def test_conv2d_u8_three_channel_input_off_the_word_grid(ctx, orc):
     """The word-wise window loads of the 3x3x3 kernels need a 4-byte aligned input; any other input
     address takes the byte-wise gather and must give the same bytes."""
