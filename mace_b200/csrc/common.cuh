@@ -64,6 +64,8 @@ struct mb_context {
   int max_pair_clusters = 0;     // co-resident clusters of the pair GEMM (0: not asked yet)
   int stem_tc = 1;               // 3x3x3 first-layer convolution: the products on the tensor core
   int dw_tma_fill = 4;           // TMA-fed depthwise: row runs are halved until the grid has this many quarter-CTAs per SM
+  int gemm_b_const = 0;          // set around a GEMM whose B operand is a weight (see conv_filter_const)
+  int b_prefetch = 1;            // such a GEMM asks for its first B tiles before it waits for its predecessor (0: A/B tests)
   int conv_filter_const = 0;     // promise: filter and bias of the following mb_conv2d_u8_nhwc calls are weights
   int stem_grid = 1;             // thread-per-pixel convolution kernels: grid in multiples of the resident blocks
   int dw_lane_setup = 1;         // TMA-fed depthwise: a lane per input row requests the copies (0: one thread, for A/B)

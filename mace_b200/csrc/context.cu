@@ -443,6 +443,8 @@ int mb_set_option(mb_context *ctx, const char *name, int value) {
     ctx->dw_fixed_groups = value;
   } else if (strcmp(name, "dw_lane_setup") == 0) {
     ctx->dw_lane_setup = value;
+  } else if (strcmp(name, "b_prefetch") == 0) {
+    ctx->b_prefetch = value;
   } else if (strcmp(name, "conv_filter_const") == 0) {
     ctx->conv_filter_const = value;
   } else if (strcmp(name, "stem_grid") == 0) {

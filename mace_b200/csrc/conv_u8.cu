@@ -674,8 +674,11 @@ extern "C" int mb_conv2d_u8_nhwc(mb_context *ctx, const uint8_t *in, const uint8
       p.wo_mul = p.wo_shift = p.ho_mul = p.ho_shift = 0;
       return stem::launch(ctx, p, static_cast<int>(C), pixels);
     }
-    return mb_gemm_u8_rowmajor(ctx, in, filter, bias, out, 0, 1, pixels, O, depth, false, false,
-                               0, 0, zp_in, zp_f, multiplier, right_shift, zp_out, 0);
+    ctx->gemm_b_const = ctx->conv_filter_const;  // the filter is the GEMM's B
+    const int st = mb_gemm_u8_rowmajor(ctx, in, filter, bias, out, 0, 1, pixels, O, depth, false, false,
+                                       0, 0, zp_in, zp_f, multiplier, right_shift, zp_out, 0);
+    ctx->gemm_b_const = 0;
+    return st;
   }
 
   ConvParams p;

@@ -88,6 +88,7 @@ struct TcParams {
   // themselves were complete before it started): the main loop starts without waiting for it,
   // only the preparation warps wait, where they read the sums.
   int sums_pending;
+  int b_const;  // B is a weight: its first tiles may be asked into L2 before the wait for the kernel in front
   int *status;
   // null, or clock stamps written by CTA 0 (profiling aid): 32 milestone slots, then 5
   // slots for each of its first 16 tiles (TMA issued, tile landed, MMAs committed,
@@ -398,6 +399,24 @@ gemm_u8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // front of this one in the stream may still be producing.
   // (with sums_pending only the preparation warps, which read the sums, wait; the operands were
   // complete before the sums kernel started, and C is not touched by it)
+  if (!PAIR && p.b_const && warp == 0 && lane == 0) {
+    // a weight matrix is usually not in L2 any more (the activations of a whole network pass have
+    // gone through it since): ask for this CTA's first B tiles now, so that they travel from HBM
+    // while the kernel in front finishes
+    TileIter it(p, PAIR);
+    if (it.valid(p)) {
+      const int bb = p.b_batched ? it.b : 0;
+      const int ahead = p.k_blocks < STAGES ? p.k_blocks : STAGES;
+      for (int kb = 0; kb < ahead; ++kb) {
+        if (B_MN) {
+#pragma unroll
+          for (int j = 0; j < (BN + 127) / 128; ++j) tma_prefetch_3d(&tmap_b, it.tn * BN + j * 128, kb * KB, bb);
+        } else {
+          tma_prefetch_3d(&tmap_b, kb * KB, it.tn * BN, bb);
+        }
+      }
+    }
+  }
   if (!p.sums_pending || (warp >= 2 && warp < 2 + PREP_WARPS)) mb_grid_dep_wait();
 
   if (warp == 0) {
@@ -1070,6 +1089,7 @@ static int tc_launch_impl(mb_context *ctx, const uint8_t *A, const uint8_t *B,
   p.c_tma = (!out_is_int32 && cbase % 16 == 0 && N % 16 == 0 && N >= 64 && M >= 32) ? 1 : 0;
   p.status = ctx->dev_status;
   p.timeline = ctx->tc_timeline;
+  p.b_const = (ctx->gemm_b_const && ctx->b_prefetch) ? 1 : 0;
   p.sums_pending = (ctx->pdl_next_gemm && ctx->pdl_chain && (sum_a != nullptr || sum_b != nullptr)) ? 1 : 0;
   // At least one round of 256 x 256 tiles over the SM pairs: two CTAs per tile, each loading
   // half of it (the lone-CTA kernel is bound by the bytes its 128 x 256 tiles pull from L2).
