@@ -180,6 +180,10 @@ int mb_pair_clusters(const mb_context *ctx);
  * of them -- weights, the reference's Tensor::is_weight() -- so the
  * thread-per-pixel kernels read them before they wait for the kernel in
  * front; the Conv2d delegator sets it per call),
+ * "b_prefetch" (1 default: a tensor-core GEMM whose B operand was declared
+ * a weight -- conv_filter_const for 1x1 convolutions, gemv_lhs_const for a
+ * batched FullyConnected -- asks for its first B tiles into L2 before it
+ * waits for the kernel in front; 0 switches that off, for A/B tests),
  * "stem_grid" (1 default: the thread-per-pixel convolution kernels launch
  * this many times the blocks that are resident at once). */
 int mb_set_option(mb_context *ctx, const char *name, int value);

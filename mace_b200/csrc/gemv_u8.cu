@@ -308,8 +308,11 @@ extern "C" int mb_gemv_u8(mb_context *ctx, const uint8_t *lhs, const uint8_t *rh
   // requantization rule in its epilogue reads the matrix once instead of once per vector.
   if (!lhs_batched && rhs_batched && batch >= 16 && K % 16 == 0 && K <= 1024 && ctx->use_tensor_cores &&
       mb_gemm_u8_tc_supported(ctx, rhs, lhs, batch, rows, K, false, false, 0, 0)) {
-    return mb_gemm_u8_tc_launch_float_rule(ctx, rhs, lhs, bias, out, out_is_int32, batch, rows, K, zp_rhs,
+    ctx->gemm_b_const = ctx->gemv_lhs_const;  // the matrix is the GEMM's B
+    const int st = mb_gemm_u8_tc_launch_float_rule(ctx, rhs, lhs, bias, out, out_is_int32, batch, rows, K, zp_rhs,
                                            zp_lhs, multiplier, zp_out, add_zp_out);
+    ctx->gemm_b_const = 0;
+    return st;
   }
   // One vector against a large matrix: the streaming kernel (see gemv_u8_stream_kernel).
   if (batch == 1 && ctx->gemv_stream && K % 16 == 0 && K >= 256 && K <= 65536 && rows >= 2ll * ctx->num_sms &&
